@@ -1,0 +1,196 @@
+"""Python mirror of the HELLM::HEMMer call surface (ciphertext/include/HELLM/HEMMer.hpp).
+
+Every method forwards to the native ``hb_hemmer_*`` entry points (C++ schedules over the
+CUDA C ABI).  The only Python-side work is laying matrices out into slot vectors the way
+``HEMMer::encode`` / ``encode2`` / ``msgDiagonalToRow4`` do (HEMMer.cpp:232-275, 353-398)
+when a caller prefers to hand in numpy arrays.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import numpy as np
+
+from .capi import Handle, Lib, HBError
+
+
+class CtxtTensor:
+    """HETensor<Ciphertext> (HETensor.hpp:46-86): a ciphertext handle plus its tile shape."""
+
+    def __init__(self, ct: Handle, rows: int, cols: int, width: int | None = None):
+        if width is None:
+            width = 1
+            while cols > width:
+                width <<= 1
+        self.ct, self.rows, self.cols, self.width = ct, rows, cols, width
+
+    @property
+    def shape(self):
+        return (self.rows, self.cols, self.width)
+
+
+class PtxtTensor(CtxtTensor):
+    """HETensor<Plaintext>."""
+
+
+# ---- slot layouts (pure data movement) ----
+def layout1(m, slots):
+    """HEMMer::encode: row-major copy into the first rows*cols slots."""
+    v = np.zeros(slots, dtype=np.complex128)
+    v[: m.size] = np.asarray(m).reshape(-1)
+    return v
+
+
+def layout2(a, b, slots):
+    """HEMMer::message2: [A | B] concatenated on columns."""
+    return layout1(np.concatenate([a, b], axis=1), slots)
+
+
+def layout_diag_to_row4(w1, w2, w3, w4, slots):
+    """HEMMer::msgDiagonalToRow4: 1/2 (W1 - i W3) | 1/2 (W2 - i W4), column j rolled up by j."""
+    left = 0.5 * (np.asarray(w1, dtype=np.float64) - 1j * np.asarray(w3, dtype=np.float64))
+    right = 0.5 * (np.asarray(w2, dtype=np.float64) - 1j * np.asarray(w4, dtype=np.float64))
+    for j in range(1, left.shape[1]):
+        left[:, j] = np.roll(left[:, j], -j)
+        right[:, j] = np.roll(right[:, j], -j)
+    return layout1(np.concatenate([left, right], axis=1), slots)
+
+
+class Hemmer:
+    def __init__(self, lib: Lib, dll: C.CDLL | None = None, prefix: str | None = None):
+        self.lib = lib
+        self.dll = dll if dll is not None else lib.dll
+        self.prefix = prefix if prefix is not None else lib.prefix + "hemmer_"
+        self.h = C.c_void_p()
+        self._fn("destroy").restype = None
+        rc = self._fn("create")(lib.ctx, C.byref(self.h))
+        if rc != 0:
+            raise HBError(rc, "hemmer_create failed")
+        self._nonce = 1000
+
+    def _fn(self, name):
+        return getattr(self.dll, self.prefix + name)
+
+    def close(self):
+        if self.h:
+            self._fn("destroy")(self.h)
+            self.h = C.c_void_p()
+
+    def _call(self, name, *args, n_out=1):
+        outs = [C.c_void_p() for _ in range(n_out)]
+        rc = self._fn(name)(self.h, *args, *[C.byref(o) for o in outs])
+        self.lib._chk(rc)
+        hs = [Handle(self.lib, o, "ct") for o in outs]
+        return hs[0] if n_out == 1 else hs
+
+    @staticmethod
+    def _shp(t):
+        return (C.c_int(t.rows), C.c_int(t.cols), C.c_int(t.width))
+
+    # ---- encode / encrypt / decrypt (HEMMer.hpp:65-98) ----
+    def next_nonce(self):
+        self._nonce += 1
+        return self._nonce
+
+    def encode(self, data, level=0):
+        level = level or self.lib.L
+        return PtxtTensor(self.lib.encode(layout1(data, self.lib.slots), level), data.shape[0], data.shape[1])
+
+    def encode2(self, d1, d2, level=0):
+        level = level or self.lib.L
+        return PtxtTensor(self.lib.encode(layout2(d1, d2, self.lib.slots), level), d1.shape[0], d1.shape[1], 2 * d1.shape[1])
+
+    def encode_diagonal_to_row4(self, w1, w2, w3, w4, level=0):
+        level = level or self.lib.L
+        return PtxtTensor(self.lib.encode(layout_diag_to_row4(w1, w2, w3, w4, self.lib.slots), level),
+                          w1.shape[0], w1.shape[1], 2 * w1.shape[1])
+
+    def encrypt(self, data, nonce=None):
+        pt = self.encode(data)
+        return CtxtTensor(self.lib.encrypt(pt.ct, self.next_nonce() if nonce is None else nonce), pt.rows, pt.cols, pt.width)
+
+    def encrypt2(self, d1, d2, nonce=None):
+        pt = self.encode2(d1, d2)
+        return CtxtTensor(self.lib.encrypt(pt.ct, self.next_nonce() if nonce is None else nonce), pt.rows, pt.cols, pt.width)
+
+    def decrypt(self, t):
+        z = self.lib.decrypt(t.ct)
+        return z[: t.rows * t.cols].real.reshape(t.rows, t.cols)
+
+    def decrypt2(self, t):
+        z = self.lib.decrypt(t.ct)[: t.rows * 2 * t.cols].real.reshape(t.rows, 2 * t.cols)
+        return np.stack([z[:, : t.cols], z[:, t.cols:]])
+
+    # ---- matmul family ----
+    def add_inplace(self, a, b):
+        a.ct = self.lib.add(a.ct, b.ct)
+
+    def single_cc_matmul(self, a, b, target_level=4):
+        ct = self._call("matmul_cc", a.ct.ptr, C.c_int(a.rows), C.c_int(a.cols), b.ct.ptr, C.c_int(b.rows), C.c_int(b.cols),
+                        C.c_int(a.width), C.c_int(target_level))
+        return CtxtTensor(ct, a.rows, b.cols, a.width)
+
+    def packed_matmul(self, a, b, target_level=4):
+        ct = self._call("packed_matmul", a.ct.ptr, C.c_int(a.rows), C.c_int(a.cols), b.ct.ptr, C.c_int(b.rows), C.c_int(b.cols),
+                        C.c_int(a.width), C.c_int(target_level))
+        return CtxtTensor(ct, a.rows, b.cols, a.width)
+
+    def transpose_inplace(self, t, target_level=0):
+        t.ct = self._call("transpose", t.ct.ptr, *self._shp(t), C.c_int(target_level))
+        t.rows, t.cols = t.cols, t.rows
+
+    def sigma(self, t):
+        return CtxtTensor(self._call("sigma", t.ct.ptr, *self._shp(t)), *t.shape)
+
+    def tau(self, t):
+        return CtxtTensor(self._call("tau", t.ct.ptr, *self._shp(t)), *t.shape)
+
+    def matmul_pre(self, a, target_level=4):
+        return self._call("matmul_pre", a.ct.ptr, *self._shp(a), C.c_int(target_level))
+
+    def matmul_reuse(self, pre, w):
+        return CtxtTensor(self._call("matmul_reuse", pre.ptr, w.ct.ptr, *self._shp(w)), *w.shape)
+
+    def matmul_pre_rev(self, b, target_level=4):
+        return CtxtTensor(self._call("matmul_pre_rev", b.ct.ptr, *self._shp(b), C.c_int(target_level)), *b.shape)
+
+    def matmul_cc_reuse(self, pre, b):
+        return CtxtTensor(self._call("matmul_cc_reuse", pre.ptr, b.ct.ptr, *self._shp(b)), *b.shape)
+
+    def packed_matmul_pre(self, a, target_level=4):
+        return CtxtTensor(self._call("packed_matmul_pre", a.ct.ptr, *self._shp(a), C.c_int(target_level)), *a.shape)
+
+    def packed_matmul_pre_rot(self, a, target_level=4):
+        return self._call("packed_matmul_pre_rot", a.ct.ptr, *self._shp(a), C.c_int(target_level))
+
+    def packed_matmul_pre_rev(self, b, target_level=4):
+        return CtxtTensor(self._call("packed_matmul_pre_rev", b.ct.ptr, *self._shp(b), C.c_int(target_level)), *b.shape)
+
+    def packed_matmul_cc_reuse(self, pre, b):
+        return CtxtTensor(self._call("packed_matmul_cc_reuse", pre.ptr, b.ct.ptr, *self._shp(b)), *b.shape)
+
+    # ---- packing helpers ----
+    def complex_packing_inplace(self, t):
+        t.ct = self._call("complex_packing", t.ct.ptr, *self._shp(t))
+
+    def complex_packing_row_inplace(self, t):
+        t.ct = self._call("complex_packing_row", t.ct.ptr, *self._shp(t))
+
+    def transpose_complex_packing_inplace(self, t, target_level=0):
+        t.ct = self._call("transpose_complex_packing", t.ct.ptr, *self._shp(t), C.c_int(target_level))
+        t.rows, t.cols = t.cols, t.rows
+
+    def split_in_two(self, t):
+        a, b = self._call("split_in_two", t.ct.ptr, *self._shp(t), n_out=2)
+        return CtxtTensor(a, *t.shape), CtxtTensor(b, *t.shape)
+
+    def repack_cc(self, t):
+        return CtxtTensor(self._call("repack_cc", t.ct.ptr), *t.shape)
+
+    def complex_packing(self, a, b):
+        return CtxtTensor(self._call("complex_packing2", a.ct.ptr, b.ct.ptr), *b.shape)
+
+    def complex_packing_rev(self, a, b):
+        return CtxtTensor(self._call("complex_packing_rev", a.ct.ptr, b.ct.ptr), *b.shape)
+
+    def repack_not_bts(self, a, b):
+        return CtxtTensor(self._call("repack_not_bts", a.ct.ptr, b.ct.ptr), *a.shape)

@@ -1,0 +1,139 @@
+/* hemmer_b200.h -- C ABI of libhemmer_b200.so: RNS-CKKS primitives on one B200.
+ *
+ * The reference reaches its GPU arithmetic through the C++ classes of the closed HEaaN
+ * library (headers under ciphertext/external/include/HEaaN/).  There is no C ABI in the
+ * reference; each entry point below names the HEaaN call (header:line) whose role it
+ * takes.  The C++ HELLM::HEMMer layer of this repository calls only these functions.
+ *
+ * Conventions
+ *   - every function returns 0 on success or a negative HB_E_* code; hb_last_error()
+ *     gives a message for the last failure on that context;
+ *   - handles are caller-owned and released with hb_ct_free / hb_pt_free / hb_ctx_destroy;
+ *   - a ciphertext handle holds a BATCH of `batch` independent ciphertexts of equal level,
+ *     device layout [batch][poly][limb][N] of uint64 residues in NTT form, fully reduced;
+ *   - a context is used from one host thread at a time; all work runs on one CUDA stream;
+ *   - nothing here falls back to the CPU: without a CUDA device hb_ctx_create fails.
+ */
+#ifndef HEMMER_B200_H
+#define HEMMER_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct hb_ctx hb_ctx;
+typedef struct hb_ct hb_ct;
+typedef struct hb_pt hb_pt;
+
+enum {
+    HB_OK = 0,
+    HB_E_ARG = -1,      /* bad argument (std::invalid_argument in the reference, MatrixUtils.cpp:27,36,680) */
+    HB_E_LEVEL = -2,    /* level too low / mismatch (MatrixUtils.cpp:1320-1324) */
+    HB_E_SHAPE = -3,    /* batch / poly-count / scale mismatch */
+    HB_E_NOKEY = -4,    /* rotation key missing (HEaaN RuntimeException) */
+    HB_E_CUDA = -5,     /* CUDA runtime error */
+    HB_E_OOM = -6,      /* device allocation failed */
+    HB_E_NCCL = -7,     /* collective failed */
+    HB_E_TIMEOUT = -8,  /* a bounded device-side wait gave up */
+    HB_E_LIMIT = -9     /* size beyond a fixed capacity */
+};
+
+/* Parameters; HEaaN fixes them through ParameterPreset::FGb (ParameterPreset.hpp:34, HEMMer.hpp:36). */
+typedef struct hb_params {
+    int32_t log_n;          /* ring degree N = 2^log_n */
+    int32_t max_level;      /* L: moduli q_0..q_L */
+    int32_t dnum;           /* gadget rank (Context.hpp:43-87) */
+    int32_t num_special;    /* K special primes */
+    int32_t q0_bits, q_bits, p_bits;
+    int32_t hamming_weight;
+    double sigma;
+    uint64_t seed[4];       /* ChaCha20 key for every random stream (Randomseeds.hpp:26) */
+} hb_params;
+
+/* makeContext(preset, {device}) -- Context.hpp:88-92 */
+int hb_ctx_create(const hb_params *prm, int device, hb_ctx **out);
+void hb_ctx_destroy(hb_ctx *ctx);
+const char *hb_last_error(const hb_ctx *ctx);
+/* getPrimeList / scale factors -- Context.hpp:203-206.  primes[L+1+K], scales[L+1]. */
+int hb_ctx_info(const hb_ctx *ctx, uint64_t *primes, double *scales);
+/* CudaTools::cudaDeviceSynchronize -- HEaaN/device/CudaTools.hpp:24 */
+int hb_sync(hb_ctx *ctx);
+/* bytes currently held by the context's device pool (cudaMemGetInfo print in bert-matmul.cpp:240-243) */
+int hb_mem_info(const hb_ctx *ctx, uint64_t *pool_bytes, uint64_t *in_use_bytes);
+/* the CUDA stream all kernels of this context run on (as a void* cudaStream_t) */
+void *hb_stream(const hb_ctx *ctx);
+
+/* KeyGenerator::genCommonKeys -- KeyGenerator.hpp:160-165: secret, multiplication and conjugation keys */
+int hb_keygen(hb_ctx *ctx);
+/* KeyGenerator::genRotKeyBundle -- KeyGenerator.hpp:89.  One direct key per left-rotation step. */
+int hb_gen_rot_keys(hb_ctx *ctx, const int64_t *left_steps, int n);
+/* copy a switching key to the host: galois = 0 selects the multiplication key.
+ * Layout [digit][2][L+1+K][N]; *digits receives the digit count when host == NULL. */
+int hb_evk_export(hb_ctx *ctx, uint64_t galois, uint64_t *host, int *digits);
+uint64_t hb_galois_for_rotation(const hb_ctx *ctx, int64_t left_steps);
+
+/* EnDecoder::encode / decode -- EnDecoder.hpp:51,66.  im may be NULL (real message). */
+int hb_encode(hb_ctx *ctx, const double *re, const double *im, size_t n_slots, int level, hb_pt **out);
+int hb_decode(hb_ctx *ctx, const hb_pt *pt, double *re, double *im);
+/* Encryptor::encrypt(ptxt, sk, ctxt) -- Encryptor.hpp:84; `nonce` selects the random streams */
+int hb_encrypt(hb_ctx *ctx, const hb_pt *pt, uint64_t nonce, hb_ct **out);
+/* Decryptor::decrypt -- Decryptor.hpp:36; decrypts entry `index` of the batch */
+int hb_decrypt(hb_ctx *ctx, const hb_ct *ct, int index, double *re, double *im);
+
+/* Ciphertext construction / metadata / raw residues -- Ciphertext.hpp:83-131 */
+int hb_ct_create(hb_ctx *ctx, int level, int n_poly, int batch, int scale_pow, hb_ct **out);
+int hb_ct_clone(hb_ctx *ctx, const hb_ct *src, hb_ct **out);
+void hb_ct_free(hb_ct *ct);
+void hb_pt_free(hb_pt *pt);
+int hb_ct_meta(const hb_ct *ct, int *level, int *n_poly, int *batch, int *scale_pow);
+int hb_pt_meta(const hb_pt *pt, int *level, int *scale_pow);
+int hb_ct_import(hb_ctx *ctx, hb_ct *ct, const uint64_t *host);
+int hb_ct_export(hb_ctx *ctx, const hb_ct *ct, uint64_t *host);
+int hb_pt_export(hb_ctx *ctx, const hb_pt *pt, uint64_t *host);
+void *hb_ct_device_ptr(const hb_ct *ct);
+int hb_batch_set(hb_ctx *ctx, hb_ct *dst, int index, const hb_ct *src);
+int hb_batch_get(hb_ctx *ctx, const hb_ct *src, int index, hb_ct **out);
+
+/* HomEvaluator primitives; `out` receives a new handle unless stated otherwise. */
+int hb_add(hb_ctx *ctx, const hb_ct *a, const hb_ct *b, hb_ct **out);           /* HomEvaluator.hpp:143-146 */
+int hb_sub(hb_ctx *ctx, const hb_ct *a, const hb_ct *b, hb_ct **out);           /* :222-225 */
+int hb_negate(hb_ctx *ctx, const hb_ct *a, hb_ct **out);                        /* :66-68 */
+int hb_mult_imag(hb_ctx *ctx, const hb_ct *a, hb_ct **out);                     /* multImagUnit :329-331 */
+int hb_mult_int(hb_ctx *ctx, const hb_ct *a, int64_t k, hb_ct **out);           /* multInteger :346-348 */
+int hb_mul_pt(hb_ctx *ctx, const hb_ct *a, const hb_pt *p, hb_ct **out);        /* mult(ct,ptxt) :299-301 */
+int hb_mul_pt_norescale(hb_ctx *ctx, const hb_ct *a, const hb_pt *p, hb_ct **out); /* multWithoutRescale :490-493 */
+int hb_rescale(hb_ctx *ctx, const hb_ct *a, hb_ct **out);                       /* rescale :539-540 */
+int hb_level_down(hb_ctx *ctx, const hb_ct *a, int target, hb_ct **out);        /* levelDown :574-576 */
+int hb_tensor(hb_ctx *ctx, const hb_ct *a, const hb_ct *b, hb_ct **out);        /* tensor :518 */
+int hb_relin(hb_ctx *ctx, const hb_ct *a, hb_ct **out);                         /* relinearize :524 */
+int hb_mul(hb_ctx *ctx, const hb_ct *a, const hb_ct *b, hb_ct **out);           /* mult(ct,ct) :311-312 */
+int hb_rotate(hb_ctx *ctx, const hb_ct *a, int64_t left_steps, hb_ct **out);    /* leftRotate :383 / rightRotate :403 */
+int hb_conjugate(hb_ctx *ctx, const hb_ct *a, hb_ct **out);                     /* conjugate :465 */
+/* raw forward / inverse NTT of every limb of the batch, in place (primitive sweep) */
+int hb_ntt(hb_ctx *ctx, hb_ct *a, int inverse);
+
+/* Fused forms used by the matmul schedules (bit-identical to the unfused sequences). */
+/* out = rescale(a (.) pa + b (.) pb)   -- MatrixUtils.cpp:1424-1427 "assemble" */
+int hb_mul2_add_rescale(hb_ctx *ctx, const hb_ct *a, const hb_pt *pa, const hb_ct *b, const hb_pt *pb, hb_ct **out);
+/* acc += tensor(a, b); *acc may be NULL on entry -- MatrixUtils.cpp:1434-1439 */
+int hb_tensor_acc(hb_ctx *ctx, const hb_ct *a, const hb_ct *b, hb_ct **acc);
+/* out = sum_k pre[k] (.) rot_rows(pt, k * row_step), un-rescaled -- HomEvaluator::matmul :595-601 */
+int hb_matmul_acc(hb_ctx *ctx, const hb_ct *pre, const hb_pt *pt, int64_t row_step, hb_ct **out);
+/* rotation of a plaintext (pure slot permutation, no key) -- leftRotate(ptxt) used at MatrixUtils.cpp:1503 */
+int hb_pt_rotate(hb_ctx *ctx, const hb_pt *p, int64_t left_steps, hb_pt **out);
+/* modReduct after a lazy sum across ranks -- HomEvaluator.hpp:602-605 */
+int hb_mod_reduce(hb_ctx *ctx, hb_ct *a);
+
+/* Multi-GPU: sum (or gather) ciphertext tiles across ranks.  The communicator is created by the
+ * caller (ncclComm_t passed as void*); replaces HEMMer::ncclAllReduceWrapper (HEMMer.cpp:2625-2635)
+ * and TransformerBlock::ncclReduceWrapper* (TransformerBlock.cpp:11100-11154). */
+int hb_allreduce_sum(hb_ctx *ctx, hb_ct *a, void *nccl_comm);
+int hb_allgather(hb_ctx *ctx, const hb_ct *mine, hb_ct *all, void *nccl_comm);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* HEMMER_B200_H */

@@ -1,0 +1,643 @@
+// CPU ORACLE -- TEST INFRASTRUCTURE ONLY (see ckks_oracle.hpp for scope and "parity unpinned").
+//
+// Restatement of the reference's matrix-multiplication schedules over the oracle's
+// primitives.  Each function names the reference function it follows
+// (ciphertext/src/MatrixUtils.cpp and ciphertext/src/HEMMer.cpp); operation order is
+// kept exactly, because the ciphertext residues depend on it.  The slot count is a
+// parameter here (the reference hard-codes 2^15, MatrixUtils.cpp:84) and the tile side
+// of the HEMMer-level masks is d = sqrt(slots/2) (the reference hard-codes 128,
+// ModelArgs.hpp:33-72).
+#pragma once
+#include "ckks_oracle.hpp"
+
+namespace orc {
+
+using Message = std::vector<cplx>;
+
+// TileTensorShape -- include/HELLM/HETensor.hpp:16-44
+struct Shape {
+    i64 rows = 0, cols = 0, width = 0;
+    Shape() {}
+    Shape(i64 r, i64 c, i64 w) : rows(r), cols(c), width(w) {}
+    Shape(i64 r, i64 c) : rows(r), cols(c) { i64 i = 1; while (c > i) i <<= 1; width = i; }
+    bool operator<(const Shape &o) const { return std::tie(rows, cols, width) < std::tie(o.rows, o.cols, o.width); }
+};
+// HETensor<Ciphertext> / HETensor<Plaintext> -- include/HELLM/HETensor.hpp:46-86
+struct CtT { Ct ct; Shape sh; };
+struct PtT { Pt pt; Shape sh; };
+
+inline Message msg_rotate_right(const Message &m, i64 r) {
+    const i64 n = (i64)m.size(); r %= n; if (r < 0) r += n;
+    Message o(m.size());
+    for (i64 i = 0; i < n; ++i) o[(size_t)((i + r) % n)] = m[(size_t)i];
+    return o;
+}
+inline Message msg_rotate_left(const Message &m, i64 r) { return msg_rotate_right(m, -r); }
+
+// A cleartext mask with its per-level encodings (the reference re-encodes a Message inside every
+// eval.mult(ct, Message); encoding is deterministic, so caching changes no bit).
+struct Mask {
+    Message msg;
+    std::map<int, Pt> enc;
+};
+
+struct Hemmer {
+    Context &cx; Evaluator &ev;
+    const i64 slots;
+    i64 tile; // side of the square tile that fills half the slots of a two-tile ciphertext
+
+    std::map<Shape, std::map<i64, Mask>> diagonal_mask_, horizontal_mask_, vertical_mask_, packed_horizontal_mask_, packed_vertical_mask_;
+    std::map<std::pair<int, Shape>, std::vector<Pt>> row_mask_, col_mask_;
+    Mask col_mask_even_, row_mask_even_, mask_left_half_;
+    std::map<int, Pt> mask_matmul_;
+
+    Hemmer(Context &c, Evaluator &e) : cx(c), ev(e), slots(c.slots) {
+        tile = 1; while (2 * tile * tile < slots) tile <<= 1;
+        gen_axis_masks();
+    }
+
+    // ---------------- primitive wrappers ----------------
+    Ct rotL(const Ct &x, i64 r) { ev.gen_rot_key(r); return ev.rotate(x, r); }
+    Ct rotR(const Ct &x, i64 r) { return rotL(x, -r); }
+    const Pt &enc_mask(Mask &m, int level) {
+        auto it = m.enc.find(level);
+        if (it == m.enc.end()) it = m.enc.emplace(level, ev.encode(m.msg.data(), m.msg.size(), level)).first;
+        return it->second;
+    }
+    // eval.mult(ct, Message) -- HomEvaluator.hpp:287-289
+    Ct mult_msg(const Ct &x, Mask &m) { return ev.mul_pt(x, enc_mask(m, x.level)); }
+
+    // ---------------- TransformMask generators ----------------
+    // generateDiagoanlMask -- MatrixUtils.cpp:90-127
+    std::map<i64, Mask> &get_diagonal_mask(const Shape &s) {
+        auto &mp = diagonal_mask_[s];
+        if (!mp.empty()) return mp;
+        const i64 num_rows = s.rows, num_cols = s.cols, width = s.width;
+        const i64 num_mask = num_rows + num_cols - 1;
+        const i64 bs = (i64)std::ceil(std::sqrt((double)num_mask));
+        const i64 gs = (i64)std::ceil((double)num_mask / (double)bs);
+        for (i64 i = 0; i < gs; i++) {
+            const i64 rot_num = i * bs * (width - 1);
+            for (i64 j = 0; j < bs; j++) {
+                const i64 idx = 1 - num_rows + i * bs + j;
+                if (idx >= num_cols) break;
+                Message msg((size_t)slots, cplx(0, 0));
+                const i64 start_row = (idx < 0) ? -idx : 0, start_col = (idx < 0) ? 0 : idx;
+                for (i64 row = start_row, col = start_col; row < num_rows && col < num_cols; row++, col++) {
+                    msg[(size_t)(row * width + col)] = 1;
+                    if (width != num_cols) msg[(size_t)(row * width + num_rows + col)] = 1;
+                }
+                mp[idx].msg = msg_rotate_right(msg, rot_num);
+            }
+        }
+        return mp;
+    }
+    void fill_blocks(Message &msg, i64 row, i64 col, const Shape &s, double v = 1.0) {
+        const i64 height = slots / s.width;
+        for (i64 rb = 0; rb < height; rb += s.rows)
+            for (i64 cb = 0; cb < s.width; cb += s.cols) msg[(size_t)((rb + row) * s.width + cb + col)] = v;
+    }
+    // generateHorizontalMask -- MatrixUtils.cpp:129-217
+    std::map<i64, Mask> &get_horizontal_mask(const Shape &s) {
+        auto &mp = horizontal_mask_[s];
+        if (!mp.empty()) return mp;
+        const i64 num_rows = s.rows, num_cols = s.cols;
+        const i64 sub_dim = (num_rows > num_cols) ? num_cols : num_rows;
+        const i64 bs = (i64)std::ceil(std::sqrt((double)(2 * sub_dim - 1)));
+        const i64 gs = (i64)std::ceil((double)(sub_dim - 1) / (double)bs);
+        for (i64 i = 0; i < gs; i++) {
+            if (i == 0) {
+                Message msg((size_t)slots, cplx(0, 0));
+                for (i64 row = 0; row < num_rows; row += sub_dim)
+                    for (i64 col = 0; col < num_cols; col++) fill_blocks(msg, row, col, s);
+                mp[0].msg = msg;
+            }
+            const i64 rot_num = i * bs;
+            for (i64 j = 0; j < bs; j++) {
+                const i64 idx = 1 + i * bs + j - num_cols;
+                if (idx >= sub_dim - num_cols) break;
+                Message msg((size_t)slots, cplx(0, 0));
+                for (i64 row = num_cols + idx; row < num_rows; row += sub_dim)
+                    for (i64 col = -idx; col < num_cols; col++) fill_blocks(msg, row, col, s);
+                mp[idx].msg = msg_rotate_right(msg, rot_num - num_cols);
+            }
+            for (i64 j = 0; j < bs; j++) {
+                const i64 idx = 1 + i * bs + j;
+                if (idx >= sub_dim) break;
+                Message msg((size_t)slots, cplx(0, 0));
+                for (i64 row = idx; row < num_rows; row += sub_dim)
+                    for (i64 col = 0; col < num_cols - idx; col++) fill_blocks(msg, row, col, s);
+                mp[idx].msg = msg_rotate_right(msg, rot_num);
+            }
+        }
+        return mp;
+    }
+    // generateVerticalMask -- MatrixUtils.cpp:330-419
+    std::map<i64, Mask> &get_vertical_mask(const Shape &s) {
+        auto &mp = vertical_mask_[s];
+        if (!mp.empty()) return mp;
+        const i64 num_rows = s.rows, num_cols = s.cols, width = s.width;
+        const i64 sub_dim = (num_cols > num_rows) ? num_rows : num_cols;
+        const i64 bs = (i64)std::ceil(std::sqrt((double)(2 * sub_dim - 1)));
+        const i64 gs = (i64)std::ceil((double)(sub_dim - 1) / (double)bs);
+        for (i64 i = 0; i < gs; i++) {
+            if (i == 0) {
+                Message msg((size_t)slots, cplx(0, 0));
+                for (i64 col = 0; col < num_cols; col += sub_dim)
+                    for (i64 row = 0; row < num_rows; row++) fill_blocks(msg, row, col, s);
+                mp[0].msg = msg;
+            }
+            const i64 rot_num = i * bs * width;
+            for (i64 j = 0; j < bs; j++) {
+                const i64 idx = 1 + i * bs + j - num_rows;
+                if (idx >= sub_dim - num_rows) break;
+                Message msg((size_t)slots, cplx(0, 0));
+                for (i64 col = num_rows + idx; col < num_cols; col += sub_dim)
+                    for (i64 row = -idx; row < num_rows; row++) fill_blocks(msg, row, col, s);
+                mp[idx].msg = msg_rotate_left(msg, num_rows * width - rot_num);
+            }
+            for (i64 j = 0; j < bs; j++) {
+                const i64 idx = 1 + i * bs + j;
+                if (idx >= sub_dim) break;
+                Message msg((size_t)slots, cplx(0, 0));
+                for (i64 col = idx; col < num_cols; col += sub_dim)
+                    for (i64 row = 0; row < num_rows - idx; row++) fill_blocks(msg, row, col, s);
+                mp[idx].msg = msg_rotate_right(msg, rot_num);
+            }
+        }
+        return mp;
+    }
+    void fill_packed(Message &msg, i64 row, i64 col, i64 width, i64 num_cols, double v) {
+        for (i64 dr = 0; dr < 2; ++dr)
+            for (i64 dc = 0; dc < 2; ++dc) {
+                msg[(size_t)((2 * row + dr) * width + (2 * col + dc))] = v;
+                if (width != num_cols) msg[(size_t)((2 * row + dr) * width + 2 * num_cols + (2 * col + dc))] = v;
+            }
+    }
+    // generatePackedHorizontalMask -- MatrixUtils.cpp:219-328 (value 0.5)
+    std::map<i64, Mask> &get_packed_horizontal_mask(const Shape &s) {
+        auto &mp = packed_horizontal_mask_[s];
+        if (!mp.empty()) return mp;
+        const i64 num_rows = s.rows / 2, num_cols = s.cols / 2, width = s.width;
+        const i64 sub_dim = (num_rows > num_cols) ? num_cols : num_rows;
+        const i64 bs = (i64)std::ceil(std::sqrt((double)(2 * sub_dim - 1)));
+        const i64 gs = (i64)std::ceil((double)(sub_dim - 1) / (double)bs);
+        for (i64 i = 0; i < gs; i++) {
+            if (i == 0) {
+                Message msg((size_t)slots, cplx(0, 0));
+                for (i64 row = 0; row < num_rows; row += sub_dim)
+                    for (i64 col = 0; col < num_cols; col++) fill_packed(msg, row, col, width, num_cols, 0.5);
+                mp[0].msg = msg;
+            }
+            const i64 rot_num = 2 * i * bs;
+            for (i64 j = 0; j < bs; j++) {
+                const i64 idx = 1 + i * bs + j - num_cols;
+                if (idx >= sub_dim - num_cols) break;
+                Message msg((size_t)slots, cplx(0, 0));
+                for (i64 row = num_cols + idx; row < num_rows; row += sub_dim)
+                    for (i64 col = -idx; col < num_cols; col++) fill_packed(msg, row, col, width, num_cols, 0.5);
+                mp[idx].msg = msg_rotate_right(msg, rot_num - 2 * num_cols);
+            }
+            for (i64 j = 0; j < bs; j++) {
+                const i64 idx = 1 + i * bs + j;
+                if (idx >= sub_dim) break;
+                Message msg((size_t)slots, cplx(0, 0));
+                for (i64 row = idx; row < num_rows; row += sub_dim)
+                    for (i64 col = 0; col < num_cols - idx; col++) fill_packed(msg, row, col, width, num_cols, 0.5);
+                mp[idx].msg = msg_rotate_right(msg, rot_num);
+            }
+        }
+        return mp;
+    }
+    // generatePackedVerticalMask -- MatrixUtils.cpp:421-527 (value 1)
+    std::map<i64, Mask> &get_packed_vertical_mask(const Shape &s) {
+        auto &mp = packed_vertical_mask_[s];
+        if (!mp.empty()) return mp;
+        const i64 num_rows = s.rows / 2, num_cols = s.cols / 2, width = s.width;
+        const i64 sub_dim = (num_cols > num_rows) ? num_rows : num_cols;
+        const i64 bs = (i64)std::ceil(std::sqrt((double)(2 * sub_dim - 1)));
+        const i64 gs = (i64)std::ceil((double)(sub_dim - 1) / (double)bs);
+        for (i64 i = 0; i < gs; i++) {
+            if (i == 0) {
+                Message msg((size_t)slots, cplx(0, 0));
+                for (i64 col = 0; col < num_cols; col += sub_dim)
+                    for (i64 row = 0; row < num_rows; row++) fill_packed(msg, row, col, width, num_cols, 1.0);
+                mp[0].msg = msg;
+            }
+            const i64 rot_num = 2 * i * bs * width;
+            for (i64 j = 0; j < bs; j++) {
+                const i64 idx = 1 + i * bs + j - num_rows;
+                if (idx >= sub_dim - num_rows) break;
+                Message msg((size_t)slots, cplx(0, 0));
+                for (i64 col = num_rows + idx; col < num_cols; col += sub_dim)
+                    for (i64 row = -idx; row < num_rows; row++) fill_packed(msg, row, col, width, num_cols, 1.0);
+                mp[idx].msg = msg_rotate_left(msg, 2 * num_rows * width - rot_num);
+            }
+            for (i64 j = 0; j < bs; j++) {
+                const i64 idx = 1 + i * bs + j;
+                if (idx >= sub_dim) break;
+                Message msg((size_t)slots, cplx(0, 0));
+                for (i64 col = idx; col < num_cols; col += sub_dim)
+                    for (i64 row = 0; row < num_rows - idx; row++) fill_packed(msg, row, col, width, num_cols, 1.0);
+                mp[idx].msg = msg_rotate_right(msg, rot_num);
+            }
+        }
+        return mp;
+    }
+    // generateRowMask -- MatrixUtils.cpp:529-552 (plaintexts at target_level, two per shift)
+    std::vector<Pt> &get_row_mask(const Shape &s, int target_level) {
+        auto &v = row_mask_[{target_level, s}];
+        if (!v.empty()) return v;
+        for (i64 i = 0; i < s.rows; i++) {
+            Message msg((size_t)slots, cplx(1, 0)), rev((size_t)slots, cplx(0, 0));
+            for (i64 j = 0; j < slots; j++)
+                if ((j / s.width) % s.rows < s.rows - i) { msg[(size_t)j] = 0; rev[(size_t)j] = 1; }
+            v.push_back(ev.encode(msg.data(), msg.size(), target_level));
+            v.push_back(ev.encode(rev.data(), rev.size(), target_level));
+        }
+        return v;
+    }
+    // generateColMask -- MatrixUtils.cpp:554-578
+    std::vector<Pt> &get_col_mask(const Shape &s, int target_level) {
+        auto &v = col_mask_[{target_level, s}];
+        if (!v.empty()) return v;
+        for (i64 i = 0; i < s.cols; i++) {
+            Message msg((size_t)slots, cplx(1, 0)), rev((size_t)slots, cplx(0, 0));
+            for (i64 j = 0; j < slots; j++)
+                if (j % s.cols < s.cols - i) { msg[(size_t)j] = 0; rev[(size_t)j] = 1; }
+            v.push_back(ev.encode(msg.data(), msg.size(), target_level));
+            v.push_back(ev.encode(rev.data(), rev.size(), target_level));
+        }
+        return v;
+    }
+
+    // ---------------- MatrixTransformer ----------------
+    // transpose<Ciphertext> -- MatrixUtils.cpp:671-739
+    CtT transpose(const CtT &op) {
+        const i64 num_cols = op.sh.rows, num_rows = op.sh.cols, width = op.sh.width;
+        if (num_cols > width) throw std::invalid_argument("[transpose] num_cols > width.");
+        Shape ms(num_rows, num_cols, width);
+        auto &dm = get_diagonal_mask(ms);
+        const i64 bs = (i64)std::ceil(std::sqrt((double)(num_rows + num_cols - 1)));
+        const i64 gs = (i64)std::ceil((double)(num_rows + num_cols - 1) / (double)bs);
+        const i64 gap = width - 1;
+        std::vector<Ct> bs_rot((size_t)bs);
+        bs_rot[0] = rotR(op.ct, (num_rows - 1) * gap);
+        for (i64 j = 1; j < bs; j++) bs_rot[(size_t)j] = rotL(bs_rot[(size_t)j - 1], gap);
+        Ct res, gs_tmp;
+        for (i64 i = 0; i < gs; i++) {
+            i64 idx = 1 - num_rows + i * bs;
+            Ct &acc = (i == 0) ? res : gs_tmp;
+            acc = mult_msg(bs_rot[0], dm[idx]);
+            for (i64 j = 1; j < bs; j++) {
+                if (++idx >= num_cols) break;
+                acc = ev.add(acc, mult_msg(bs_rot[(size_t)j], dm[idx]));
+            }
+            if (i > 0) {
+                gs_tmp = rotL(gs_tmp, (i * bs) * gap);
+                res = ev.add(res, gs_tmp);
+            }
+        }
+        return CtT{res, ms};
+    }
+    // Shared body of diagonalToColumn (MatrixUtils.cpp:776-848, gap 1, main = cols),
+    // diagonalToRow (:924-996, gap = width, main = rows), packedDiagonalToColumn (:850-922, gap 2,
+    // main = cols/2) and packedDiagonalToRow (:998-1070, gap 2*width, main = rows/2).
+    Ct bsgs_diagonal(const Ct &op, std::map<i64, Mask> &mask, i64 sub_dim, i64 main_dim, i64 gap) {
+        const i64 bs = (i64)std::ceil(std::sqrt((double)(2 * sub_dim - 1)));
+        const i64 gs = (i64)std::ceil((double)(sub_dim - 1) / (double)bs);
+        std::vector<Ct> bs_rot((size_t)bs);
+        bs_rot[0] = rotL(op, gap);
+        for (i64 j = 1; j < bs; j++) bs_rot[(size_t)j] = rotL(bs_rot[(size_t)j - 1], gap);
+        Ct res = mult_msg(op, mask[0]);
+        for (i64 i = 0; i < gs; i++) {
+            const i64 rot_num = i * bs * gap;
+            i64 idx = 1 + i * bs - main_dim;
+            Ct gs_tmp = mult_msg(bs_rot[0], mask[idx]);
+            for (i64 j = 1; j < bs; j++) {
+                if (++idx >= sub_dim - main_dim) break;
+                gs_tmp = ev.add(gs_tmp, mult_msg(bs_rot[(size_t)j], mask[idx]));
+            }
+            gs_tmp = rotR(gs_tmp, main_dim * gap - rot_num);
+            res = ev.add(res, gs_tmp);
+            idx = 1 + i * bs;
+            gs_tmp = mult_msg(bs_rot[0], mask[idx]);
+            for (i64 j = 1; j < bs; j++) {
+                if (++idx >= sub_dim) break;
+                gs_tmp = ev.add(gs_tmp, mult_msg(bs_rot[(size_t)j], mask[idx]));
+            }
+            gs_tmp = rotL(gs_tmp, rot_num);
+            res = ev.add(res, gs_tmp);
+        }
+        return res;
+    }
+    CtT diagonal_to_column(const CtT &op) {
+        Shape ms(op.sh.rows, op.sh.cols, op.sh.width);
+        return CtT{bsgs_diagonal(op.ct, get_horizontal_mask(ms), std::min(ms.rows, ms.cols), ms.cols, 1), ms};
+    }
+    CtT diagonal_to_row(const CtT &op) {
+        Shape ms(op.sh.rows, op.sh.cols, op.sh.width);
+        return CtT{bsgs_diagonal(op.ct, get_vertical_mask(ms), std::min(ms.rows, ms.cols), ms.rows, ms.width), ms};
+    }
+    CtT packed_diagonal_to_column(const CtT &op) {
+        const i64 nr = op.sh.rows / 2, nc = op.sh.cols / 2;
+        Shape ms(2 * nr, 2 * nc, op.sh.width);
+        return CtT{bsgs_diagonal(op.ct, get_packed_horizontal_mask(ms), std::min(nr, nc), nc, 2), ms};
+    }
+    CtT packed_diagonal_to_row(const CtT &op) {
+        const i64 nr = op.sh.rows / 2, nc = op.sh.cols / 2;
+        Shape ms(2 * nr, 2 * nc, op.sh.width);
+        return CtT{bsgs_diagonal(op.ct, get_packed_vertical_mask(ms), std::min(nr, nc), nr, 2 * ms.width), ms};
+    }
+
+    static i64 pow2_ceil(i64 v) { i64 p = 1; while (p < v) p <<= 1; return p; }
+    void check_level(const Ct &a, const Ct &b) {
+        // the reference refuses operands below 1 + minimum bootstrap level (MatrixUtils.cpp:1320-1324);
+        // without bootstrapping the requirement is that the schedule's level budget fits.
+        (void)a; (void)b;
+    }
+
+    // "assemble": rescale(x (.) pa + y (.) pb) -- MatrixUtils.cpp:1424-1427
+    Ct assemble(const Ct &x, const Pt &pa, const Ct &y, const Pt &pb) {
+        return ev.rescale(ev.add(ev.mul_pt_norescale(x, pa), ev.mul_pt_norescale(y, pb)));
+    }
+
+    // multMatMat<Ciphertext> -- MatrixUtils.cpp:1307-1446
+    CtT mult_mat_mat_cc(const CtT &op1, const CtT &op2, int target_level) {
+        const i64 num_rows = op1.sh.rows, num_cols = op2.sh.cols;
+        if (op1.sh.cols != op2.sh.rows) throw std::invalid_argument("[getCommonInsideLength] different inside length.");
+        if (op1.sh.width != op2.sh.width) throw std::invalid_argument("[getCommonBlockWidth] different block width");
+        const i64 width = op1.sh.width;
+        i64 num_k = pow2_ceil(op1.sh.cols);
+        if (std::min(op1.ct.level, op2.ct.level) < target_level + 3) throw std::invalid_argument("[multMatMat] level too low");
+        CtT a = op1, b = op2;
+        a.sh = Shape(num_rows, num_k, width); b.sh = Shape(num_k, num_cols, width);
+        auto &col_mask = get_col_mask(a.sh, target_level + 2);
+        auto &row_mask = get_row_mask(b.sh, target_level + 2);
+        a = diagonal_to_column(a);
+        b = diagonal_to_row(b);
+        a.ct = ev.level_down(a.ct, target_level + 2);
+        b.ct = ev.level_down(b.ct, target_level + 2);
+        const i64 num_rows_tmp = (num_k > num_rows) ? num_k : pow2_ceil(num_rows);
+        const i64 num_cols_tmp = (num_k > num_cols) ? num_k : pow2_ceil(num_cols);
+        Ct res = ev.mul(a.ct, b.ct);
+        a.ct = rotL(a.ct, 1);
+        b.ct = rotL(b.ct, width);
+        Ct a_rot = rotR(a.ct, num_cols_tmp);
+        Ct b_rot = rotR(b.ct, num_rows_tmp * width);
+        Ct itxt_res;
+        for (i64 i = 1; i < num_k; i++) {
+            if (i > 1) {
+                a.ct = rotL(a.ct, 1); a_rot = rotL(a_rot, 1);
+                b.ct = rotL(b.ct, width); b_rot = rotL(b_rot, width);
+            }
+            Ct tmp1 = assemble(a.ct, col_mask[(size_t)(2 * i + 1)], a_rot, col_mask[(size_t)(2 * i)]);
+            Ct tmp2 = assemble(b.ct, row_mask[(size_t)(2 * i + 1)], b_rot, row_mask[(size_t)(2 * i)]);
+            Ct t = ev.tensor(tmp1, tmp2);
+            itxt_res = (i == 1) ? t : ev.add(itxt_res, t);
+        }
+        Ct tail = ev.rescale(ev.relin(itxt_res));
+        res = ev.add(res, tail);
+        return CtT{res, Shape(num_rows, num_cols, width)};
+    }
+
+    // multPackedMatMat -- MatrixUtils.cpp:1100-1216
+    CtT mult_packed_mat_mat(const CtT &op1, const CtT &op2, int target_level) {
+        const i64 num_rows = op1.sh.rows, num_cols = op2.sh.cols;
+        if (op1.sh.cols != op2.sh.rows) throw std::invalid_argument("[getCommonInsideLength] different inside length.");
+        if (op1.sh.width != op2.sh.width) throw std::invalid_argument("[getCommonBlockWidth] different block width");
+        const i64 width = op1.sh.width;
+        i64 num_k = pow2_ceil(op1.sh.cols);
+        if (op1.ct.level < target_level + 3 || op2.ct.level < target_level + 2) throw std::invalid_argument("[multMatMat] level too low");
+        CtT a = op1, b = op2;
+        a.sh = Shape(num_rows, num_k, width); b.sh = Shape(num_k, num_cols, width);
+        auto &col_mask = get_col_mask(a.sh, target_level + 2);
+        a.ct = ev.level_down(a.ct, target_level + 3);
+        b.ct = ev.level_down(b.ct, target_level + 2);
+        a = packed_diagonal_to_column(a);
+        b = packed_diagonal_to_row(b);
+        const i64 num_cols_tmp = (num_k > num_cols) ? num_k : pow2_ceil(num_cols);
+        Ct res = ev.mul(a.ct, b.ct);
+        a.ct = rotL(a.ct, 2);
+        b.ct = rotL(b.ct, 2 * width);
+        Ct a_rot = rotR(a.ct, num_cols_tmp);
+        Ct itxt_res;
+        for (i64 i = 1; i < num_k / 2; i++) {
+            if (i > 1) {
+                a.ct = rotL(a.ct, 2); a_rot = rotL(a_rot, 2);
+                b.ct = rotL(b.ct, 2 * width);
+            }
+            Ct tmp1 = assemble(a.ct, col_mask[(size_t)(4 * i + 1)], a_rot, col_mask[(size_t)(4 * i)]);
+            Ct t = ev.tensor(tmp1, b.ct);
+            itxt_res = (i == 1) ? t : ev.add(itxt_res, t);
+        }
+        Ct tail = ev.rescale(ev.relin(itxt_res));
+        res = ev.add(res, tail);
+        return CtT{res, Shape(num_rows, num_cols, width)};
+    }
+    // multPackedMatMatPre -- MatrixUtils.cpp:1218-1226
+    CtT mult_packed_mat_mat_pre(const CtT &a_in, int target_level) {
+        CtT a = a_in; a.ct = ev.level_down(a.ct, target_level + 3);
+        return packed_diagonal_to_column(a);
+    }
+    // multPackedMatMatPreRot -- MatrixUtils.cpp:1228-1264.  Returns a batch of rows/2 ciphertexts.
+    Ct mult_packed_mat_mat_pre_rot(const CtT &a_in, int target_level) {
+        const i64 num_rows = a_in.sh.rows;
+        std::vector<Ct> tmp;
+        Ct a = a_in.ct;
+        tmp.push_back(ev.level_down(a, a.level - 1));
+        a = rotL(a, 2);
+        Ct a_rot = rotR(a, num_rows);
+        auto &col_mask = get_col_mask(a_in.sh, target_level + 2);
+        for (i64 i = 1; i < num_rows / 2; i++) {
+            if (i > 1) { a = rotL(a, 2); a_rot = rotL(a_rot, 2); }
+            tmp.push_back(assemble(a, col_mask[(size_t)(4 * i + 1)], a_rot, col_mask[(size_t)(4 * i)]));
+        }
+        return stack(tmp);
+    }
+    // multPackedMatMatPreRev -- MatrixUtils.cpp:1266-1274
+    CtT mult_packed_mat_mat_pre_rev(const CtT &b_in, int target_level) {
+        CtT b = b_in; b.ct = ev.level_down(b.ct, target_level + 2);
+        return packed_diagonal_to_row(b);
+    }
+    // multPackedMatMatCCReuse -- MatrixUtils.cpp:1276-1305 (relinearised and rescaled)
+    CtT mult_packed_mat_mat_cc_reuse(const Ct &pre, const CtT &b_in) {
+        const i64 width = b_in.sh.width;
+        Ct b = b_in.ct;
+        Ct sum = ev.tensor(slice(pre, 0), b);
+        for (int i = 1; i < pre.batch; ++i) {
+            b = rotL(b, 2 * width);
+            sum = ev.add(sum, ev.tensor(slice(pre, i), b));
+        }
+        return CtT{ev.rescale(ev.relin(sum)), Shape(b_in.sh.rows, b_in.sh.cols, width)};
+    }
+
+    // multMatMatPre -- MatrixUtils.cpp:1572-1610.  Returns the `rows` shifted copies as one batch.
+    Ct mult_mat_mat_pre(const CtT &a_in, int target_level) {
+        const i64 num_rows = a_in.sh.rows;
+        CtT a = a_in;
+        a.ct = ev.level_down(a.ct, target_level + 3);
+        a = diagonal_to_column(a);
+        std::vector<Ct> tmp;
+        tmp.push_back(ev.level_down(a.ct, a.ct.level - 1));
+        a.ct = rotL(a.ct, 1);
+        Ct a_rot = rotR(a.ct, num_rows);
+        auto &col_mask = get_col_mask(a.sh, target_level + 2);
+        for (i64 i = 1; i < num_rows; i++) {
+            if (i > 1) { a.ct = rotL(a.ct, 1); a_rot = rotL(a_rot, 1); }
+            tmp.push_back(assemble(a.ct, col_mask[(size_t)(2 * i + 1)], a_rot, col_mask[(size_t)(2 * i)]));
+        }
+        return stack(tmp);
+    }
+    // multMatMatReUse -- MatrixUtils.cpp:1612-1639 with HomEvaluator::matmul (HomEvaluator.hpp:595-601):
+    //   out = sum_k pre[k] (.) leftRotate(pt, k * width), un-rescaled (scale Delta^2).
+    // The plaintext must already sit at the level of `pre` (the reference re-encodes otherwise).
+    CtT mult_mat_mat_reuse(const Ct &pre, const PtT &b) {
+        Ct acc;
+        for (int k = 0; k < pre.batch; ++k) {
+            Pt pk = pt_rotate(b.pt, (i64)k * b.sh.width);
+            Ct t = ev.mul_pt_norescale(slice(pre, k), pk);
+            acc = (k == 0) ? t : ev.add(acc, t);
+        }
+        return CtT{acc, Shape(b.sh.rows, b.sh.cols, b.sh.width)};
+    }
+    // multMatMatPreRev -- MatrixUtils.cpp:1641-1649
+    CtT mult_mat_mat_pre_rev(const CtT &b_in, int target_level) {
+        CtT b = b_in; b.ct = ev.level_down(b.ct, target_level + 2);
+        return diagonal_to_row(b);
+    }
+    // multMatMatCCReUse -- MatrixUtils.cpp:1651-1679 (relinearised, NOT rescaled)
+    CtT mult_mat_mat_cc_reuse(const Ct &pre, const CtT &b_in) {
+        const i64 width = b_in.sh.width;
+        Ct b = b_in.ct;
+        Ct sum = ev.tensor(slice(pre, 0), b);
+        for (int i = 1; i < pre.batch; ++i) {
+            b = rotL(b, width);
+            sum = ev.add(sum, ev.tensor(slice(pre, i), b));
+        }
+        return CtT{ev.relin(sum), Shape(b_in.sh.rows, b_in.sh.cols, width)};
+    }
+
+    // leftRotate on a plaintext: the slot permutation alone (no key), used by HomEvaluator::matmul
+    Pt pt_rotate(const Pt &p, i64 left_steps) {
+        u64 g = cx.galois_for_rotation(left_steps);
+        if (g == 1) return p;
+        const auto &perm = cx.ntt_perm(g);
+        Pt r = p;
+        for (int l = 0; l <= p.level; ++l)
+            for (int c = 0; c < cx.N; ++c) r.limb(l)[c] = p.limb(l)[perm[(size_t)c]];
+        return r;
+    }
+    Ct slice(const Ct &b, int k) const {
+        Ct r(cx.N, b.level, b.np, 1, b.spow);
+        std::memcpy(r.d.data(), b.limb(k, 0, 0), r.d.size() * 8);
+        return r;
+    }
+    Ct stack(const std::vector<Ct> &v) const {
+        Ct r(cx.N, v[0].level, v[0].np, (int)v.size(), v[0].spow);
+        for (size_t k = 0; k < v.size(); ++k) {
+            if (v[k].level != r.level || v[k].np != r.np) throw std::invalid_argument("stack: mismatched ciphertexts");
+            std::memcpy(r.limb((int)k, 0, 0), v[k].d.data(), v[k].d.size() * 8);
+        }
+        return r;
+    }
+
+    // ---------------- HEMMer-level helpers ----------------
+    // generateAxisMasks / generateRightLeftMasks -- HEMMer.cpp:2345-2393, two tiles side by side
+    void gen_axis_masks() {
+        const i64 d = tile;
+        col_mask_even_.msg.assign((size_t)slots, cplx(0, 0));
+        row_mask_even_.msg.assign((size_t)slots, cplx(0, 0));
+        mask_left_half_.msg.assign((size_t)slots, cplx(0, 0));
+        if (2 * d * d != slots) return; // slot count not of the form 2*d^2: HEMMer-level packing unavailable
+        for (i64 r = 0; r < d; ++r)
+            for (i64 c = 0; c < 2 * d; ++c) {
+                size_t s = (size_t)(r * 2 * d + c);
+                if ((c % d) % 2 == 0) col_mask_even_.msg[s] = 1;
+                if (r % 2 == 0) row_mask_even_.msg[s] = 1;
+                if (c < d) mask_left_half_.msg[s] = 1;
+            }
+    }
+    // mask_matmul_ = encode2(one, zero) -- HEMMer.cpp:2336-2339 (a Plaintext at the operand's level)
+    const Pt &mask_matmul(int level) {
+        auto it = mask_matmul_.find(level);
+        if (it == mask_matmul_.end()) it = mask_matmul_.emplace(level, ev.encode(mask_left_half_.msg.data(), (size_t)slots, level)).first;
+        return it->second;
+    }
+    // complexPackingInplace -- HEMMer.cpp:764-777
+    void complex_packing_inplace(CtT &t) {
+        Ct even = mult_msg(t.ct, col_mask_even_);
+        Ct odd = rotL(t.ct, 1);
+        odd = ev.mult_imag(odd);
+        odd = mult_msg(odd, col_mask_even_);
+        Ct fus = ev.add(odd, even);
+        t.ct = rotR(fus, 1);
+        t.ct = ev.add(t.ct, fus);
+    }
+    // transposeInplace -- HEMMer.cpp:1166-1172
+    void transpose_inplace(CtT &t, int target_level) {
+        if (target_level > 0) t.ct = ev.level_down(t.ct, 1 + target_level);
+        t = transpose(t);
+    }
+    // transposeComplexPackingInplace -- HEMMer.cpp:779-799
+    void transpose_complex_packing_inplace(CtT &t, int target_level) {
+        Ct even = mult_msg(t.ct, col_mask_even_);
+        Ct odd = rotL(t.ct, 1);
+        odd = ev.mult_imag(odd);
+        odd = ev.negate(odd);
+        odd = mult_msg(odd, col_mask_even_);
+        Ct fus = ev.add(odd, even);
+        t.ct = rotR(fus, 1);
+        t.ct = ev.add(t.ct, fus);
+        if (target_level > 0) t.ct = ev.level_down(t.ct, 1 + target_level);
+        transpose_inplace(t, 0);
+    }
+    // complexPackingRowInplace -- HEMMer.cpp:801-817
+    void complex_packing_row_inplace(CtT &t) {
+        const i64 bw = t.sh.width;
+        Ct even = mult_msg(t.ct, row_mask_even_);
+        Ct odd = rotL(t.ct, bw);
+        odd = ev.mult_imag(odd);
+        odd = ev.negate(odd);
+        odd = mult_msg(odd, row_mask_even_);
+        Ct fus = ev.add(even, odd);
+        t.ct = rotR(fus, bw);
+        t.ct = ev.add(t.ct, fus);
+    }
+    // splitInTwo -- HEMMer.cpp:819-831
+    void split_in_two(const CtT &t, CtT &t1, CtT &t2) {
+        const i64 width = t.sh.cols;
+        Ct tmp = mult_msg(t.ct, mask_left_half_);
+        t1.sh = t2.sh = t.sh;
+        t2.ct = ev.add(t.ct, tmp, true);
+        t1.ct = rotR(tmp, width);
+        t1.ct = ev.add(t1.ct, tmp);
+        Ct tmp2 = rotL(t2.ct, width);
+        t2.ct = ev.add(t2.ct, tmp2);
+    }
+    // repackCC -- HEMMer.cpp:964-969
+    CtT repack_cc(const CtT &t) {
+        ev.gen_galois_key(cx.galois_conj());
+        return CtT{ev.add(t.ct, ev.conjugate(t.ct)), t.sh};
+    }
+    // complexPacking(ct, ct) -- HEMMer.cpp:980-986 ; complexPackingRev -- :988-994
+    CtT complex_packing(const CtT &a, const CtT &b) { return CtT{ev.add(a.ct, ev.mult_imag(b.ct)), b.sh}; }
+    CtT complex_packing_rev(const CtT &a, const CtT &b) { return CtT{ev.add(a.ct, ev.mult_imag(b.ct), true), b.sh}; }
+    // repack_notBTS -- HEMMer.cpp:1025-1053
+    CtT repack_not_bts(const CtT &t1, const CtT &t2) {
+        Ct a = ev.rescale(t1.ct), b = ev.rescale(t2.ct);
+        Ct out = ev.add(a, ev.conjugate(a));
+        Ct tmp = ev.add(b, ev.conjugate(b));
+        tmp = ev.mult_imag(tmp);
+        out = ev.add(out, tmp);
+        tmp = rotL(out, tile);
+        out = ev.add(out, tmp);
+        tmp = ev.mul_pt(tmp, mask_matmul(tmp.level));
+        out = ev.mul_pt(out, mask_matmul(out.level));
+        tmp = rotR(tmp, tile);
+        out = ev.add(out, tmp);
+        return CtT{out, t1.sh};
+    }
+};
+
+} // namespace orc
