@@ -1,0 +1,125 @@
+// HELLM::HEMMer for B200 -- the call surface of ciphertext/include/HELLM/HEMMer.hpp
+// (matmul entry points, transposes, packing helpers, encode / encrypt / decrypt) over the
+// CUDA C ABI.  Matrices cross this interface as row-major double arrays instead of
+// torch::Tensor, so the layer has no libtorch dependency.
+#pragma once
+#include "he_types.hpp"
+
+#include <map>
+#include <tuple>
+
+namespace HELLM {
+
+// include/HELLM/HETensor.hpp:16-44
+class TileTensorShape {
+  public:
+    TileTensorShape() = default;
+    TileTensorShape(i64 rows, i64 cols, i64 block_width) : rows_(rows), cols_(cols), width_(block_width) {}
+    TileTensorShape(i64 rows, i64 cols) : rows_(rows), cols_(cols), width_(1) { while (width_ < cols) width_ <<= 1; }
+    i64 getNumRows() const { return rows_; }
+    i64 getNumCols() const { return cols_; }
+    i64 getBlockWidth() const { return width_; }
+    void setShape(i64 r, i64 c) { rows_ = r; cols_ = c; }
+    void setBlockWidth(i64 w) { width_ = w; }
+    bool operator<(const TileTensorShape &o) const { return std::tie(rows_, cols_, width_) < std::tie(o.rows_, o.cols_, o.width_); }
+  private:
+    i64 rows_ = 0, cols_ = 0, width_ = 0;
+};
+
+// include/HELLM/HETensor.hpp:46-86
+template <class T> class HETensor {
+  public:
+    HETensor() = default;
+    HETensor(TileTensorShape s, T data) : shape_(s), data_(std::move(data)) {}
+    HETensor(i64 h, i64 w, T data) : shape_(h, w), data_(std::move(data)) {}
+    HETensor(i64 h, i64 w, T data, i64 block_width) : shape_(h, w, block_width), data_(std::move(data)) {}
+    i64 getHeight() const { return shape_.getNumRows(); }
+    i64 getWidth() const { return shape_.getNumCols(); }
+    i64 getBlockWidth() const { return shape_.getBlockWidth(); }
+    int getLevel() const { return data_.getLevel(); }
+    void setShape(i64 h, i64 w) { shape_.setShape(h, w); }
+    TileTensorShape getShape() const { return shape_; }
+    T &get() { return data_; }
+    const T &get() const { return data_; }
+  private:
+    TileTensorShape shape_;
+    T data_;
+};
+using CtxtTensor = HETensor<Ciphertext>;
+using PtxtTensor = HETensor<Plaintext>;
+
+// Masks of the linear transforms: cleartext slot vectors, encoded once per level and kept on the
+// device.  (The reference keeps Messages and lets HEaaN re-encode them inside every multiplication,
+// MatrixUtils.cpp:584-669; encoding is deterministic, so the ciphertexts are the same.)
+class MaskCache {
+  public:
+    using Key = std::tuple<int, TileTensorShape, i64, int>; // kind, shape, index, level
+    const Plaintext *find(const Key &k) const { auto it = enc_.find(k); return it == enc_.end() ? nullptr : &it->second; }
+    const Plaintext &put(const Key &k, Plaintext p) { return enc_.emplace(k, std::move(p)).first->second; }
+    void clear() { enc_.clear(); }
+  private:
+    std::map<Key, Plaintext> enc_;
+};
+
+class HEMMer {
+  public:
+    // Wraps an existing context (keys must have been generated with hb_keygen).
+    explicit HEMMer(hb_ctx *ctx);
+    // HEMMer::genHEMMer (HEMMer.cpp:93-112): creates the context on `device_id`, generates keys; owns the context.
+    static HEMMer *genHEMMer(int device_id, const hb_params &prm);
+    ~HEMMer();
+
+    const Evaluator &eval() const { return eval_; }
+    i64 slots() const { return slots_; }
+    i64 tile() const { return tile_; }
+    int encryptionLevel() const { return max_level_; }
+
+    // encode / encrypt / decrypt -- HEMMer.cpp:232-275, 353-416, 579-638
+    Message message2(const double *d1, const double *d2, i64 h, i64 w) const;
+    Message msgDiagonalToRow4(const double *w1, const double *w2, const double *w3, const double *w4, i64 h, i64 w) const;
+    PtxtTensor encode(const double *data, i64 h, i64 w, int level = 0) const;
+    PtxtTensor encode2(const double *d1, const double *d2, i64 h, i64 w, int level = 0) const;
+    PtxtTensor encodeDiagonalToRow4(const double *w1, const double *w2, const double *w3, const double *w4, i64 h, i64 w, int level = 0) const;
+    CtxtTensor encrypt(const double *data, i64 h, i64 w, u64 nonce) const;
+    CtxtTensor encrypt2(const double *d1, const double *d2, i64 h, i64 w, u64 nonce) const;
+    void decrypt(const CtxtTensor &t, double *out) const;  // h*w doubles
+    void decrypt2(const CtxtTensor &t, double *out) const; // [2][h][w]
+
+    void addInplace(CtxtTensor &a, const CtxtTensor &b) const;
+    // matmul family -- HEMMer.cpp:833-880, 1102-1124
+    CtxtTensor singleCCMatMul(const CtxtTensor &a, const CtxtTensor &b, int target_level = 4);
+    CtxtTensor packedMatMul(const CtxtTensor &a, const CtxtTensor &b, int target_level = 4);
+    CtxtTensor packedMatMulPre(const CtxtTensor &a, int target_level = 4);
+    Ciphertext packedMatMulPreRot(const CtxtTensor &a, int target_level = 4);
+    CtxtTensor packedMatMulPreRev(const CtxtTensor &b, int target_level = 4);
+    CtxtTensor packedMatMulCCReuse(const Ciphertext &pre, const CtxtTensor &b, int target_level = 4);
+    Ciphertext matMulPre(const CtxtTensor &a, int target_level = 4);
+    CtxtTensor matMulReUse(const Ciphertext &pre, const PtxtTensor &w, int target_level = 4);
+    CtxtTensor matMulPreRev(const CtxtTensor &b, int target_level = 4);
+    CtxtTensor matMulCCReUse(const Ciphertext &pre, const CtxtTensor &b, int target_level = 4);
+    // transposes and packing -- HEMMer.cpp:764-831, 964-1053, 1166-1172
+    void transposeInplace(CtxtTensor &t, int target_level = 0);
+    void complexPackingInplace(CtxtTensor &t);
+    void transposeComplexPackingInplace(CtxtTensor &t, int target_level = 0);
+    void complexPackingRowInplace(CtxtTensor &t);
+    void splitInTwo(const CtxtTensor &t, CtxtTensor &t1, CtxtTensor &t2);
+    CtxtTensor repackCC(const CtxtTensor &t) const;
+    CtxtTensor complexPacking(const CtxtTensor &a, const CtxtTensor &b) const;
+    CtxtTensor complexPackingRev(const CtxtTensor &a, const CtxtTensor &b) const;
+    CtxtTensor repack_notBTS(const CtxtTensor &a, const CtxtTensor &b);
+    // the two linear transforms on their own (MatrixTransformer::diagonalToColumn / diagonalToRow)
+    CtxtTensor diagonalToColumn(const CtxtTensor &t);
+    CtxtTensor diagonalToRow(const CtxtTensor &t);
+
+    MaskCache &masks() { return masks_; }
+
+  private:
+    hb_ctx *ctx_;
+    bool owns_ctx_ = false;
+    Evaluator eval_;
+    i64 slots_ = 0, tile_ = 0;
+    int max_level_ = 0;
+    MaskCache masks_;
+};
+
+} // namespace HELLM

@@ -1,0 +1,146 @@
+// Value types and the evaluator facade of the C++ HEMMer layer.
+// They stand where HEaaN::Ciphertext / Plaintext / Message / HomEvaluator stand in the reference
+// (ciphertext/external/include/HEaaN/{Ciphertext,Plaintext,Message,HomEvaluator}.hpp); every
+// operation is one call into the C ABI of include/hemmer_b200.h, i.e. one or more CUDA launches.
+#pragma once
+#include "hemmer_b200.h"
+
+#include <complex>
+#include <cstdint>
+#include <memory>
+#include <stdexcept>
+#include <string>
+#include <utility>
+#include <vector>
+
+namespace HELLM {
+
+using i64 = int64_t;
+using u64 = uint64_t;
+using Complex = std::complex<double>;
+
+// Status codes of the C ABI become the exception types the reference's callers expect:
+// std::invalid_argument for level / shape errors (MatrixUtils.cpp:27,36,680,1322),
+// std::runtime_error otherwise (utils/check_macros.hpp:49-56).
+inline void check(hb_ctx *c, int rc) {
+    if (rc == HB_OK) return;
+    std::string m = hb_last_error(c);
+    if (rc == HB_E_ARG || rc == HB_E_LEVEL || rc == HB_E_SHAPE) throw std::invalid_argument(m);
+    throw std::runtime_error(m);
+}
+
+// HEaaN::Message: one complex value per slot, kept as two real arrays (the layout hb_encode takes).
+struct Message {
+    std::vector<double> re, im;
+    Message() {}
+    explicit Message(size_t n, double v = 0.0) : re(n, v), im(n, 0.0) {}
+    size_t size() const { return re.size(); }
+    void set(size_t i, Complex v) { re[i] = v.real(); im[i] = v.imag(); }
+    // slot s of the result holds slot s - r of the input (HomEvaluator::rightRotate on a Message)
+    Message rotated_right(i64 r) const {
+        const i64 n = (i64)size();
+        r %= n; if (r < 0) r += n;
+        Message o(size());
+        for (i64 s = 0; s < n; ++s) { i64 d = s + r; if (d >= n) d -= n; o.re[(size_t)d] = re[(size_t)s]; o.im[(size_t)d] = im[(size_t)s]; }
+        return o;
+    }
+};
+
+// HEaaN::Ciphertext (Ciphertext.hpp:29-145).  Copying clones device memory, moving does not.
+class Ciphertext {
+  public:
+    Ciphertext() = default;
+    Ciphertext(hb_ctx *c, hb_ct *p) : c_(c), p_(p) {}
+    Ciphertext(const Ciphertext &o) : c_(o.c_) { if (o.p_) check(c_, hb_ct_clone(c_, o.p_, &p_)); }
+    Ciphertext(Ciphertext &&o) noexcept : c_(o.c_), p_(o.p_) { o.p_ = nullptr; }
+    Ciphertext &operator=(Ciphertext o) noexcept { std::swap(c_, o.c_); std::swap(p_, o.p_); return *this; }
+    ~Ciphertext() { if (p_) hb_ct_free(p_); }
+    hb_ct *raw() const { return p_; }
+    hb_ct *release() { hb_ct *p = p_; p_ = nullptr; return p; }
+    bool empty() const { return p_ == nullptr; }
+    int getLevel() const { int l = -1; hb_ct_meta(p_, &l, nullptr, nullptr, nullptr); return l; }
+    int getBatch() const { int b = 0; hb_ct_meta(p_, nullptr, nullptr, &b, nullptr); return b; }
+    int getRescaleCounter() const { int s = 1; hb_ct_meta(p_, nullptr, nullptr, nullptr, &s); return s - 1; }
+  private:
+    hb_ctx *c_ = nullptr;
+    hb_ct *p_ = nullptr;
+};
+
+// HEaaN::Plaintext.  Plaintexts are immutable once encoded, so copies share the device buffer.
+class Plaintext {
+  public:
+    Plaintext() = default;
+    explicit Plaintext(hb_pt *p) : p_(p, [](hb_pt *x) { hb_pt_free(x); }) {}
+    hb_pt *raw() const { return p_.get(); }
+    bool empty() const { return !p_; }
+    int getLevel() const { int l = -1; hb_pt_meta(p_.get(), &l, nullptr); return l; }
+  private:
+    std::shared_ptr<hb_pt> p_;
+};
+
+// The subset of HEaaN::HomEvaluator / EnDecoder the matmul path uses (HomEvaluator.hpp:30-616).
+class Evaluator {
+  public:
+    explicit Evaluator(hb_ctx *c) : c_(c) {}
+    hb_ctx *ctx() const { return c_; }
+
+    Plaintext encode(const Message &m, int level) const {
+        hb_pt *p = nullptr; check(c_, hb_encode(c_, m.re.data(), m.im.data(), m.size(), level, &p)); return Plaintext(p);
+    }
+    Message decode(const Plaintext &p, size_t slots) const {
+        Message m(slots); check(c_, hb_decode(c_, p.raw(), m.re.data(), m.im.data())); return m;
+    }
+#define HB_UNARY(name, fn) Ciphertext name(const Ciphertext &a) const { hb_ct *o = nullptr; check(c_, fn(c_, a.raw(), &o)); return Ciphertext(c_, o); }
+#define HB_BINARY(name, fn) Ciphertext name(const Ciphertext &a, const Ciphertext &b) const { hb_ct *o = nullptr; check(c_, fn(c_, a.raw(), b.raw(), &o)); return Ciphertext(c_, o); }
+    HB_BINARY(add, hb_add)
+    HB_BINARY(sub, hb_sub)
+    HB_BINARY(tensor, hb_tensor)
+    HB_BINARY(mult, hb_mul)
+    HB_UNARY(negate, hb_negate)
+    HB_UNARY(multImagUnit, hb_mult_imag)
+    HB_UNARY(rescale, hb_rescale)
+    HB_UNARY(relinearize, hb_relin)
+    HB_UNARY(conjugate, hb_conjugate)
+#undef HB_UNARY
+#undef HB_BINARY
+    Ciphertext mult(const Ciphertext &a, const Plaintext &p) const { hb_ct *o = nullptr; check(c_, hb_mul_pt(c_, a.raw(), p.raw(), &o)); return Ciphertext(c_, o); }
+    Ciphertext multWithoutRescale(const Ciphertext &a, const Plaintext &p) const {
+        hb_ct *o = nullptr; check(c_, hb_mul_pt_norescale(c_, a.raw(), p.raw(), &o)); return Ciphertext(c_, o);
+    }
+    Ciphertext levelDown(const Ciphertext &a, int target) const { hb_ct *o = nullptr; check(c_, hb_level_down(c_, a.raw(), target, &o)); return Ciphertext(c_, o); }
+    Ciphertext levelDownOne(const Ciphertext &a) const { return levelDown(a, a.getLevel() - 1); }
+    // one direct switching key per step, generated on first use (the reference composes power-of-two keys)
+    Ciphertext leftRotate(const Ciphertext &a, i64 steps) const {
+        check(c_, hb_gen_rot_keys(c_, &steps, 1));
+        hb_ct *o = nullptr; check(c_, hb_rotate(c_, a.raw(), steps, &o)); return Ciphertext(c_, o);
+    }
+    Ciphertext rightRotate(const Ciphertext &a, i64 steps) const { return leftRotate(a, -steps); }
+    Plaintext leftRotate(const Plaintext &p, i64 steps) const { hb_pt *o = nullptr; check(c_, hb_pt_rotate(c_, p.raw(), steps, &o)); return Plaintext(o); }
+    // rescale(a (.) pa + b (.) pb): the "assemble" step of the matmul loops in one pass
+    Ciphertext assemble(const Ciphertext &a, const Plaintext &pa, const Ciphertext &b, const Plaintext &pb) const {
+        hb_ct *o = nullptr; check(c_, hb_mul2_add_rescale(c_, a.raw(), pa.raw(), b.raw(), pb.raw(), &o)); return Ciphertext(c_, o);
+    }
+    // acc += tensor(a, b)
+    void tensorAccumulate(Ciphertext &acc, const Ciphertext &a, const Ciphertext &b) const {
+        hb_ct *p = acc.release();
+        int rc = hb_tensor_acc(c_, a.raw(), b.raw(), &p);
+        acc = Ciphertext(c_, p);
+        check(c_, rc);
+    }
+    // HomEvaluator::matmul (HomEvaluator.hpp:595-601)
+    Ciphertext matmul(const Ciphertext &pre, const Plaintext &pt, i64 row_step) const {
+        hb_ct *o = nullptr; check(c_, hb_matmul_acc(c_, pre.raw(), pt.raw(), row_step, &o)); return Ciphertext(c_, o);
+    }
+    Ciphertext stack(const std::vector<Ciphertext> &v) const {
+        int level = 0, np = 0, sp = 0; hb_ct_meta(v[0].raw(), &level, &np, nullptr, &sp);
+        hb_ct *o = nullptr; check(c_, hb_ct_create(c_, level, np, (int)v.size(), sp, &o));
+        Ciphertext out(c_, o);
+        for (size_t k = 0; k < v.size(); ++k) check(c_, hb_batch_set(c_, o, (int)k, v[k].raw()));
+        return out;
+    }
+    Ciphertext slice(const Ciphertext &b, int k) const { hb_ct *o = nullptr; check(c_, hb_batch_get(c_, b.raw(), k, &o)); return Ciphertext(c_, o); }
+  private:
+    hb_ctx *c_;
+};
+
+} // namespace HELLM

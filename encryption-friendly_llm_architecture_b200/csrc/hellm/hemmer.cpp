@@ -1,0 +1,182 @@
+// HELLM::HEMMer methods: slot layouts, encrypt / decrypt, packing helpers, and the entry points
+// that forward to the schedules (the role of ciphertext/src/HEMMer.cpp on the matmul path).
+#include "HEMMer.hpp"
+#include "schedules.hpp"
+
+namespace HELLM {
+
+namespace {
+enum HemmerMask { kColEven = 1, kRowEven = 2, kLeftHalf = 3 };
+}
+
+HEMMer::HEMMer(hb_ctx *ctx) : ctx_(ctx), eval_(ctx) {
+    int log_n = 0, L = 0;
+    hb_ctx_dims(ctx, &log_n, &L, nullptr);
+    slots_ = (i64)1 << (log_n - 1);
+    max_level_ = L;
+    tile_ = 1;
+    while (2 * tile_ * tile_ < slots_) tile_ <<= 1; // side of the tile two of which fill a ciphertext
+}
+HEMMer *HEMMer::genHEMMer(int device_id, const hb_params &prm) {
+    hb_ctx *c = nullptr;
+    if (hb_ctx_create(&prm, device_id, &c) != HB_OK) throw std::runtime_error("[genHEMMer] cannot create a context on this device");
+    int rc = hb_keygen(c);
+    if (rc != HB_OK) { std::string m = hb_last_error(c); hb_ctx_destroy(c); throw std::runtime_error(m); }
+    HEMMer *h = new HEMMer(c);
+    h->owns_ctx_ = true;
+    return h;
+}
+HEMMer::~HEMMer() {
+    masks_.clear();
+    if (owns_ctx_) hb_ctx_destroy(ctx_);
+}
+
+// ---- layouts ----
+// HEMMer::message2 (HEMMer.cpp:249-261): [A | B], row-major
+Message HEMMer::message2(const double *d1, const double *d2, i64 h, i64 w) const {
+    if (h * 2 * w > slots_) throw std::invalid_argument("[message2] matrices do not fit the slots");
+    Message m((size_t)slots_);
+    for (i64 r = 0; r < h; ++r)
+        for (i64 c = 0; c < w; ++c) {
+            m.re[(size_t)(r * 2 * w + c)] = d1[r * w + c];
+            m.re[(size_t)(r * 2 * w + w + c)] = d2[r * w + c];
+        }
+    return m;
+}
+// HEMMer::msgDiagonalToRow4 (HEMMer.cpp:353-398): left half 1/2 (W1 - i W3), right half 1/2 (W2 - i W4),
+// every column j rolled up by j rows (the cleartext tau transform)
+Message HEMMer::msgDiagonalToRow4(const double *w1, const double *w2, const double *w3, const double *w4, i64 h, i64 w) const {
+    if (h * 2 * w > slots_) throw std::invalid_argument("[msgDiagonalToRow4] matrices do not fit the slots");
+    Message m((size_t)slots_);
+    for (i64 r = 0; r < h; ++r)
+        for (i64 c = 0; c < w; ++c) {
+            const i64 src = ((r + c) % h) * w + c;
+            m.set((size_t)(r * 2 * w + c), Complex(0.5 * w1[src], -0.5 * w3[src]));
+            m.set((size_t)(r * 2 * w + w + c), Complex(0.5 * w2[src], -0.5 * w4[src]));
+        }
+    return m;
+}
+PtxtTensor HEMMer::encode(const double *data, i64 h, i64 w, int level) const {
+    if (h * w > slots_) throw std::invalid_argument("[encode] matrix does not fit the slots");
+    Message m((size_t)slots_);
+    for (i64 i = 0; i < h * w; ++i) m.re[(size_t)i] = data[i];
+    return PtxtTensor(h, w, eval_.encode(m, level ? level : max_level_));
+}
+PtxtTensor HEMMer::encode2(const double *d1, const double *d2, i64 h, i64 w, int level) const {
+    return PtxtTensor(h, w, eval_.encode(message2(d1, d2, h, w), level ? level : max_level_), 2 * w);
+}
+PtxtTensor HEMMer::encodeDiagonalToRow4(const double *w1, const double *w2, const double *w3, const double *w4, i64 h, i64 w, int level) const {
+    return PtxtTensor(h, w, eval_.encode(msgDiagonalToRow4(w1, w2, w3, w4, h, w), level ? level : max_level_), 2 * w);
+}
+CtxtTensor HEMMer::encrypt(const double *data, i64 h, i64 w, u64 nonce) const {
+    PtxtTensor p = encode(data, h, w);
+    hb_ct *ct = nullptr;
+    check(ctx_, hb_encrypt(ctx_, p.get().raw(), nonce, &ct));
+    return CtxtTensor(p.getShape(), Ciphertext(ctx_, ct));
+}
+CtxtTensor HEMMer::encrypt2(const double *d1, const double *d2, i64 h, i64 w, u64 nonce) const {
+    PtxtTensor p = encode2(d1, d2, h, w);
+    hb_ct *ct = nullptr;
+    check(ctx_, hb_encrypt(ctx_, p.get().raw(), nonce, &ct));
+    return CtxtTensor(p.getShape(), Ciphertext(ctx_, ct));
+}
+void HEMMer::decrypt(const CtxtTensor &t, double *out) const {
+    std::vector<double> re((size_t)slots_), im((size_t)slots_);
+    check(ctx_, hb_decrypt(ctx_, t.get().raw(), 0, re.data(), im.data()));
+    for (i64 i = 0; i < t.getHeight() * t.getWidth(); ++i) out[i] = re[(size_t)i];
+}
+void HEMMer::decrypt2(const CtxtTensor &t, double *out) const {
+    std::vector<double> re((size_t)slots_), im((size_t)slots_);
+    check(ctx_, hb_decrypt(ctx_, t.get().raw(), 0, re.data(), im.data()));
+    const i64 h = t.getHeight(), w = t.getWidth();
+    for (i64 r = 0; r < h; ++r)
+        for (i64 c = 0; c < w; ++c) {
+            out[r * w + c] = re[(size_t)(r * 2 * w + c)];
+            out[h * w + r * w + c] = re[(size_t)(r * 2 * w + w + c)];
+        }
+}
+void HEMMer::addInplace(CtxtTensor &a, const CtxtTensor &b) const { a.get() = eval_.add(a.get(), b.get()); }
+
+// ---- schedules ----
+#define HB_ENV sched::Env env{eval_, slots_, masks_}
+CtxtTensor HEMMer::singleCCMatMul(const CtxtTensor &a, const CtxtTensor &b, int t) { HB_ENV; return sched::multMatMatCC(env, a, b, t); }
+CtxtTensor HEMMer::packedMatMul(const CtxtTensor &a, const CtxtTensor &b, int t) { HB_ENV; return sched::multPackedMatMat(env, a, b, t); }
+CtxtTensor HEMMer::packedMatMulPre(const CtxtTensor &a, int t) { HB_ENV; return sched::multPackedMatMatPre(env, a, t); }
+Ciphertext HEMMer::packedMatMulPreRot(const CtxtTensor &a, int t) { HB_ENV; return sched::multPackedMatMatPreRot(env, a, t); }
+CtxtTensor HEMMer::packedMatMulPreRev(const CtxtTensor &b, int t) { HB_ENV; return sched::multPackedMatMatPreRev(env, b, t); }
+CtxtTensor HEMMer::packedMatMulCCReuse(const Ciphertext &pre, const CtxtTensor &b, int) { HB_ENV; return sched::multPackedMatMatCCReuse(env, pre, b); }
+Ciphertext HEMMer::matMulPre(const CtxtTensor &a, int t) { HB_ENV; return sched::multMatMatPre(env, a, t); }
+CtxtTensor HEMMer::matMulReUse(const Ciphertext &pre, const PtxtTensor &w, int) { HB_ENV; return sched::multMatMatReUse(env, pre, w); }
+CtxtTensor HEMMer::matMulPreRev(const CtxtTensor &b, int t) { HB_ENV; return sched::multMatMatPreRev(env, b, t); }
+CtxtTensor HEMMer::matMulCCReUse(const Ciphertext &pre, const CtxtTensor &b, int) { HB_ENV; return sched::multMatMatCCReUse(env, pre, b); }
+CtxtTensor HEMMer::diagonalToColumn(const CtxtTensor &t) { HB_ENV; return sched::diagonalToColumn(env, t); }
+CtxtTensor HEMMer::diagonalToRow(const CtxtTensor &t) { HB_ENV; return sched::diagonalToRow(env, t); }
+
+// HEMMer::transposeInplace -- HEMMer.cpp:1166-1172
+void HEMMer::transposeInplace(CtxtTensor &t, int target_level) {
+    HB_ENV;
+    if (target_level > 0) t.get() = eval_.levelDown(t.get(), 1 + target_level);
+    t = sched::transpose(env, t);
+}
+
+// ---- packing helpers: masks over two side-by-side tiles (generateAxisMasks / generateRightLeftMasks,
+// HEMMer.cpp:2345-2393), encoded per level on first use ----
+static const Plaintext &hemmer_mask(HEMMer &h, int which, int level) {
+    MaskCache::Key k{sched::kHemmer, TileTensorShape(h.tile(), h.tile(), 2 * h.tile()), which, level};
+    if (const Plaintext *p = h.masks().find(k)) return *p;
+    const i64 d = h.tile();
+    if (2 * d * d != h.slots()) throw std::invalid_argument("[HEMMer] slot count is not 2*d^2: tile packing unavailable");
+    Message m((size_t)h.slots());
+    for (i64 r = 0; r < d; ++r)
+        for (i64 c = 0; c < 2 * d; ++c) {
+            bool on = which == kColEven ? ((c % d) % 2 == 0) : which == kRowEven ? (r % 2 == 0) : (c < d);
+            if (on) m.re[(size_t)(r * 2 * d + c)] = 1.0;
+        }
+    return h.masks().put(k, h.eval().encode(m, level));
+}
+// shared body of complexPackingInplace (HEMMer.cpp:764-777), transposeComplexPackingInplace (:779-799, first half)
+// and complexPackingRowInplace (:801-817): fold odd columns (rows) into the imaginary part of the even ones
+static Ciphertext fold_odd(HEMMer &h, const Ciphertext &x, int mask, i64 step, bool negate, bool even_first) {
+    const Evaluator &ev = h.eval();
+    Ciphertext even = ev.mult(x, hemmer_mask(h, mask, x.getLevel()));
+    Ciphertext odd = ev.multImagUnit(ev.leftRotate(x, step));
+    if (negate) odd = ev.negate(odd);
+    odd = ev.mult(odd, hemmer_mask(h, mask, odd.getLevel()));
+    Ciphertext fus = even_first ? ev.add(even, odd) : ev.add(odd, even);
+    return ev.add(ev.rightRotate(fus, step), fus);
+}
+void HEMMer::complexPackingInplace(CtxtTensor &t) { t.get() = fold_odd(*this, t.get(), kColEven, 1, false, false); }
+void HEMMer::transposeComplexPackingInplace(CtxtTensor &t, int target_level) {
+    t.get() = fold_odd(*this, t.get(), kColEven, 1, true, false);
+    if (target_level > 0) t.get() = eval_.levelDown(t.get(), 1 + target_level);
+    transposeInplace(t, 0);
+}
+void HEMMer::complexPackingRowInplace(CtxtTensor &t) { t.get() = fold_odd(*this, t.get(), kRowEven, t.getBlockWidth(), true, true); }
+// HEMMer::splitInTwo -- HEMMer.cpp:819-831
+void HEMMer::splitInTwo(const CtxtTensor &t, CtxtTensor &t1, CtxtTensor &t2) {
+    const i64 width = t.getWidth();
+    Ciphertext left = eval_.mult(t.get(), hemmer_mask(*this, kLeftHalf, t.getLevel()));
+    Ciphertext right = eval_.sub(t.get(), left);
+    t1 = CtxtTensor(t.getShape(), eval_.add(eval_.rightRotate(left, width), left));
+    t2 = CtxtTensor(t.getShape(), eval_.add(right, eval_.leftRotate(right, width)));
+}
+// HEMMer::repackCC -- HEMMer.cpp:964-969
+CtxtTensor HEMMer::repackCC(const CtxtTensor &t) const { return CtxtTensor(t.getShape(), eval_.add(t.get(), eval_.conjugate(t.get()))); }
+// HEMMer::complexPacking(ct, ct) -- HEMMer.cpp:980-986 ; complexPackingRev -- :988-994
+CtxtTensor HEMMer::complexPacking(const CtxtTensor &a, const CtxtTensor &b) const { return CtxtTensor(b.getShape(), eval_.add(a.get(), eval_.multImagUnit(b.get()))); }
+CtxtTensor HEMMer::complexPackingRev(const CtxtTensor &a, const CtxtTensor &b) const { return CtxtTensor(b.getShape(), eval_.sub(a.get(), eval_.multImagUnit(b.get()))); }
+// HEMMer::repack_notBTS -- HEMMer.cpp:1025-1053
+CtxtTensor HEMMer::repack_notBTS(const CtxtTensor &t1, const CtxtTensor &t2) {
+    Ciphertext a = eval_.rescale(t1.get()), b = eval_.rescale(t2.get());
+    Ciphertext out = eval_.add(a, eval_.conjugate(a));
+    Ciphertext tmp = eval_.multImagUnit(eval_.add(b, eval_.conjugate(b)));
+    out = eval_.add(out, tmp);
+    tmp = eval_.leftRotate(out, tile_);
+    out = eval_.add(out, tmp);
+    tmp = eval_.mult(tmp, hemmer_mask(*this, kLeftHalf, tmp.getLevel()));
+    out = eval_.mult(out, hemmer_mask(*this, kLeftHalf, out.getLevel()));
+    out = eval_.add(out, eval_.rightRotate(tmp, tile_));
+    return CtxtTensor(t1.getShape(), std::move(out));
+}
+
+} // namespace HELLM

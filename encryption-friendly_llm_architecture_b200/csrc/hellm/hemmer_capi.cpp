@@ -1,0 +1,123 @@
+// C entry points of libhellm_b200.so: the HEMMer call surface for callers that bind through a C ABI
+// (ctypes in this repository's tests and benchmark).  Tile shapes travel as (rows, cols, block_width).
+#include "HEMMer.hpp"
+
+using namespace HELLM;
+
+struct hb_hemmer { hb_ctx *ctx; HEMMer h; explicit hb_hemmer(hb_ctx *c) : ctx(c), h(c) {} };
+
+namespace {
+// error text for failures raised above the C ABI (the CUDA library keeps its own last-error string)
+thread_local std::string g_err;
+template <class F> int guard(F &&f) {
+    try { f(); return HB_OK; }
+    catch (const std::invalid_argument &e) { g_err = e.what(); return HB_E_ARG; }
+    catch (const std::exception &e) { g_err = e.what(); return HB_E_CUDA; }
+}
+// borrow a caller-owned handle for the duration of one call
+struct Borrow {
+    Ciphertext c;
+    Borrow(hb_ctx *ctx, const hb_ct *p) : c(ctx, const_cast<hb_ct *>(p)) {}
+    ~Borrow() { c.release(); }
+};
+CtxtTensor view(Borrow &b, int r, int c, int w) { return CtxtTensor(TileTensorShape(r, c, w), Ciphertext(b.c)); }
+}
+
+extern "C" {
+const char *hb_hemmer_last_error() { return g_err.c_str(); }
+int hb_hemmer_create(hb_ctx *c, hb_hemmer **out) { return guard([&] { *out = new hb_hemmer(c); }); }
+void hb_hemmer_destroy(hb_hemmer *h) { delete h; }
+
+#define SHAPE_ARGS int rows, int cols, int width
+#define IN_TENSOR(name, p) Borrow name##_b(h->ctx, p); CtxtTensor name(TileTensorShape(rows, cols, width), Ciphertext(name##_b.c))
+
+int hb_hemmer_transpose(hb_hemmer *h, const hb_ct *a, SHAPE_ARGS, int target, hb_ct **out) {
+    return guard([&] { IN_TENSOR(t, a); h->h.transposeInplace(t, target); *out = t.get().release(); });
+}
+int hb_hemmer_sigma(hb_hemmer *h, const hb_ct *a, SHAPE_ARGS, hb_ct **out) {
+    return guard([&] { IN_TENSOR(t, a); *out = h->h.diagonalToColumn(t).get().release(); });
+}
+int hb_hemmer_tau(hb_hemmer *h, const hb_ct *a, SHAPE_ARGS, hb_ct **out) {
+    return guard([&] { IN_TENSOR(t, a); *out = h->h.diagonalToRow(t).get().release(); });
+}
+int hb_hemmer_matmul_cc(hb_hemmer *h, const hb_ct *a, int ra, int ca, int wa, const hb_ct *b, int rb, int cb, int wb, int target, hb_ct **out) {
+    return guard([&] {
+        Borrow ba(h->ctx, a), bb(h->ctx, b);
+        CtxtTensor ta = view(ba, ra, ca, wa), tb = view(bb, rb, cb, wb);
+        *out = h->h.singleCCMatMul(ta, tb, target).get().release();
+    });
+}
+int hb_hemmer_packed_matmul(hb_hemmer *h, const hb_ct *a, int ra, int ca, int wa, const hb_ct *b, int rb, int cb, int wb, int target, hb_ct **out) {
+    return guard([&] {
+        Borrow ba(h->ctx, a), bb(h->ctx, b);
+        CtxtTensor ta = view(ba, ra, ca, wa), tb = view(bb, rb, cb, wb);
+        *out = h->h.packedMatMul(ta, tb, target).get().release();
+    });
+}
+int hb_hemmer_matmul_pre(hb_hemmer *h, const hb_ct *a, SHAPE_ARGS, int target, hb_ct **out) {
+    return guard([&] { IN_TENSOR(t, a); *out = h->h.matMulPre(t, target).release(); });
+}
+int hb_hemmer_matmul_reuse(hb_hemmer *h, const hb_ct *pre, const hb_pt *p, SHAPE_ARGS, hb_ct **out) {
+    return guard([&] {
+        Borrow bp(h->ctx, pre);
+        // the plaintext stays owned by the caller: wrap it without a deleter
+        hb_ct *o = nullptr;
+        int lp = 0, lc = 0; hb_pt_meta(p, &lp, nullptr); hb_ct_meta(pre, &lc, nullptr, nullptr, nullptr);
+        if (lp != lc) throw std::invalid_argument("[multMatMatReUse] plaintext level differs from the ciphertexts'");
+        check(h->ctx, hb_matmul_acc(h->ctx, pre, p, width, &o));
+        (void)rows; (void)cols;
+        *out = o;
+    });
+}
+int hb_hemmer_matmul_pre_rev(hb_hemmer *h, const hb_ct *b, SHAPE_ARGS, int target, hb_ct **out) {
+    return guard([&] { IN_TENSOR(t, b); *out = h->h.matMulPreRev(t, target).get().release(); });
+}
+int hb_hemmer_matmul_cc_reuse(hb_hemmer *h, const hb_ct *pre, const hb_ct *b, SHAPE_ARGS, hb_ct **out) {
+    return guard([&] { Borrow bp(h->ctx, pre); IN_TENSOR(t, b); *out = h->h.matMulCCReUse(bp.c, t).get().release(); });
+}
+int hb_hemmer_packed_matmul_pre(hb_hemmer *h, const hb_ct *a, SHAPE_ARGS, int target, hb_ct **out) {
+    return guard([&] { IN_TENSOR(t, a); *out = h->h.packedMatMulPre(t, target).get().release(); });
+}
+int hb_hemmer_packed_matmul_pre_rot(hb_hemmer *h, const hb_ct *a, SHAPE_ARGS, int target, hb_ct **out) {
+    return guard([&] { IN_TENSOR(t, a); *out = h->h.packedMatMulPreRot(t, target).release(); });
+}
+int hb_hemmer_packed_matmul_pre_rev(hb_hemmer *h, const hb_ct *b, SHAPE_ARGS, int target, hb_ct **out) {
+    return guard([&] { IN_TENSOR(t, b); *out = h->h.packedMatMulPreRev(t, target).get().release(); });
+}
+int hb_hemmer_packed_matmul_cc_reuse(hb_hemmer *h, const hb_ct *pre, const hb_ct *b, SHAPE_ARGS, hb_ct **out) {
+    return guard([&] { Borrow bp(h->ctx, pre); IN_TENSOR(t, b); *out = h->h.packedMatMulCCReuse(bp.c, t).get().release(); });
+}
+int hb_hemmer_complex_packing(hb_hemmer *h, const hb_ct *a, SHAPE_ARGS, hb_ct **out) {
+    return guard([&] { IN_TENSOR(t, a); h->h.complexPackingInplace(t); *out = t.get().release(); });
+}
+int hb_hemmer_complex_packing_row(hb_hemmer *h, const hb_ct *a, SHAPE_ARGS, hb_ct **out) {
+    return guard([&] { IN_TENSOR(t, a); h->h.complexPackingRowInplace(t); *out = t.get().release(); });
+}
+int hb_hemmer_transpose_complex_packing(hb_hemmer *h, const hb_ct *a, SHAPE_ARGS, int target, hb_ct **out) {
+    return guard([&] { IN_TENSOR(t, a); h->h.transposeComplexPackingInplace(t, target); *out = t.get().release(); });
+}
+int hb_hemmer_split_in_two(hb_hemmer *h, const hb_ct *a, SHAPE_ARGS, hb_ct **out1, hb_ct **out2) {
+    return guard([&] { IN_TENSOR(t, a); CtxtTensor t1, t2; h->h.splitInTwo(t, t1, t2); *out1 = t1.get().release(); *out2 = t2.get().release(); });
+}
+int hb_hemmer_repack_cc(hb_hemmer *h, const hb_ct *a, hb_ct **out) {
+    return guard([&] { Borrow ba(h->ctx, a); *out = h->h.repackCC(CtxtTensor(TileTensorShape(), Ciphertext(ba.c))).get().release(); });
+}
+int hb_hemmer_complex_packing2(hb_hemmer *h, const hb_ct *a, const hb_ct *b, hb_ct **out) {
+    return guard([&] {
+        Borrow ba(h->ctx, a), bb(h->ctx, b);
+        *out = h->h.complexPacking(CtxtTensor(TileTensorShape(), Ciphertext(ba.c)), CtxtTensor(TileTensorShape(), Ciphertext(bb.c))).get().release();
+    });
+}
+int hb_hemmer_complex_packing_rev(hb_hemmer *h, const hb_ct *a, const hb_ct *b, hb_ct **out) {
+    return guard([&] {
+        Borrow ba(h->ctx, a), bb(h->ctx, b);
+        *out = h->h.complexPackingRev(CtxtTensor(TileTensorShape(), Ciphertext(ba.c)), CtxtTensor(TileTensorShape(), Ciphertext(bb.c))).get().release();
+    });
+}
+int hb_hemmer_repack_not_bts(hb_hemmer *h, const hb_ct *a, const hb_ct *b, hb_ct **out) {
+    return guard([&] {
+        Borrow ba(h->ctx, a), bb(h->ctx, b);
+        *out = h->h.repack_notBTS(CtxtTensor(TileTensorShape(), Ciphertext(ba.c)), CtxtTensor(TileTensorShape(), Ciphertext(bb.c))).get().release();
+    });
+}
+} // extern "C"

@@ -1,0 +1,332 @@
+// Diagonal / rotate-and-accumulate schedules for encrypted tile products.
+//
+// Algorithm (Jiang-Kim-Lauter-Song style, as scheduled by the reference in
+// ciphertext/src/MatrixUtils.cpp): with sigma(A)[r][c] = A[r][c+r] and tau(B)[r][c] = B[r+c][c],
+//     A*B = sum_k  phi^k(sigma A) (.) psi^k(tau B),
+// phi^k a column shift with wrap inside the row, psi^k a row shift.  sigma, tau and the transpose
+// are sums of masked rotations arranged as baby-step / giant-step.  The ciphertext bits depend on
+// the order of operations, so each function keeps the order of the reference function it names;
+// what differs is that masks are encoded once per level and kept on the device, and that the
+// mask-mask-add-rescale "assemble" step and the tensor accumulation are single fused launches.
+#include "schedules.hpp"
+
+#include <cmath>
+#include <functional>
+
+namespace HELLM {
+namespace sched {
+
+namespace {
+
+i64 ceil_pow2(i64 v) { i64 p = 1; while (p < v) p <<= 1; return p; }
+i64 ceil_sqrt(i64 v) { return (i64)std::ceil(std::sqrt((double)v)); }
+i64 ceil_div(i64 a, i64 b) { return (i64)std::ceil((double)a / (double)b); }
+
+// ---- mask construction -------------------------------------------------------------------
+// A mask is a 0/value indicator over (row, col) of one tile, copied to a set of tile origins in
+// the slot grid, then pre-rotated by the amount the giant step will undo.
+using Pred = std::function<bool(i64 row, i64 col)>;
+
+struct Placement { std::vector<std::pair<i64, i64>> origins; i64 row_scale = 1, col_scale = 1; };
+
+Placement all_blocks(const Env &e, const TileTensorShape &s) { // every rows x cols block of the grid
+    Placement p;
+    const i64 height = e.slots / s.getBlockWidth();
+    for (i64 rb = 0; rb < height; rb += s.getNumRows())
+        for (i64 cb = 0; cb < s.getBlockWidth(); cb += s.getNumCols()) p.origins.push_back({rb, cb});
+    return p;
+}
+Message paint(const Env &e, const TileTensorShape &s, const Placement &pl, i64 rows, i64 cols, const Pred &pred, double value) {
+    Message m((size_t)e.slots);
+    const i64 w = s.getBlockWidth();
+    for (i64 r = 0; r < rows; ++r)
+        for (i64 c = 0; c < cols; ++c) {
+            if (!pred(r, c)) continue;
+            for (const auto &o : pl.origins)
+                for (i64 dr = 0; dr < pl.row_scale; ++dr)
+                    for (i64 dc = 0; dc < pl.col_scale; ++dc)
+                        m.re[(size_t)((o.first + pl.row_scale * r + dr) * w + o.second + pl.col_scale * c + dc)] = value;
+        }
+    return m;
+}
+
+const Plaintext &cached(Env &e, int kind, const TileTensorShape &s, i64 idx, int level, const std::function<Message()> &make) {
+    MaskCache::Key k{kind, s, idx, level};
+    if (const Plaintext *p = e.cache.find(k)) return *p;
+    return e.cache.put(k, e.ev.encode(make(), level));
+}
+
+// Masks of sigma / tau and their packed forms.
+//   horizontal (MatrixUtils.cpp:129-217): idx = 0 keeps rows = 0 (mod sub); idx > 0 keeps rows = idx (mod sub),
+//   columns < cols - idx; idx < 0 keeps rows = cols + idx (mod sub), columns >= -idx.  The vertical family
+//   (:330-419) is the same with rows and columns exchanged.  Each mask is rotated by the amount its giant step
+//   undoes.  Packed families (:219-328, :421-527) work on the grid of 2x2 slot blocks; the horizontal one
+//   carries 1/2, and both are painted on the two tiles of a side-by-side pair only.
+struct DiagFamily {
+    bool vertical, packed;
+    i64 rows, cols, sub, main, bs, gs, gap;
+};
+DiagFamily family(const TileTensorShape &s, bool vertical, bool packed) {
+    DiagFamily f{};
+    f.vertical = vertical; f.packed = packed;
+    f.rows = packed ? s.getNumRows() / 2 : s.getNumRows();
+    f.cols = packed ? s.getNumCols() / 2 : s.getNumCols();
+    f.sub = std::min(f.rows, f.cols);
+    f.main = vertical ? f.rows : f.cols;
+    f.bs = ceil_sqrt(2 * f.sub - 1);
+    f.gs = ceil_div(f.sub - 1, f.bs);
+    const i64 unit = vertical ? s.getBlockWidth() : 1;
+    f.gap = packed ? 2 * unit : unit;
+    return f;
+}
+Message diag_family_mask(const Env &e, const TileTensorShape &s, const DiagFamily &f, i64 idx) {
+    const i64 sub = f.sub, main = f.main;
+    Pred pred;
+    if (idx == 0) pred = [=](i64 r, i64 c) { return ((f.vertical ? c : r) % sub) == 0; };
+    else if (idx > 0) pred = [=](i64 r, i64 c) { i64 a = f.vertical ? c : r, b = f.vertical ? r : c; return a >= idx && (a - idx) % sub == 0 && b < main - idx; };
+    else pred = [=](i64 r, i64 c) { i64 a = f.vertical ? c : r, b = f.vertical ? r : c; return a >= main + idx && (a - main - idx) % sub == 0 && b >= -idx; };
+    Placement pl;
+    if (f.packed) {
+        pl.row_scale = pl.col_scale = 2;
+        pl.origins.push_back({0, 0});
+        if (s.getBlockWidth() != f.cols) pl.origins.push_back({0, 2 * f.cols});
+    } else {
+        pl = all_blocks(e, s);
+    }
+    Message m = paint(e, s, pl, f.rows, f.cols, pred, (f.packed && !f.vertical) ? 0.5 : 1.0);
+    if (idx == 0) return m;
+    // giant-step index this mask belongs to, and the rotation applied after the baby-step sum
+    const i64 i = idx > 0 ? (idx - 1) / f.bs : (idx + main - 1) / f.bs;
+    const i64 rot_num = i * f.bs * f.gap;
+    return m.rotated_right(idx > 0 ? rot_num : rot_num - main * f.gap);
+}
+
+// Baby-step / giant-step evaluation shared by diagonalToColumn (MatrixUtils.cpp:776-848), diagonalToRow
+// (:924-996), packedDiagonalToColumn (:850-922) and packedDiagonalToRow (:998-1070).
+Ciphertext bsgs_diagonals(Env &e, const Ciphertext &op, const TileTensorShape &s, bool vertical, bool packed) {
+    const DiagFamily f = family(s, vertical, packed);
+    const int kind = packed ? (vertical ? kPackedVertical : kPackedHorizontal) : (vertical ? kVertical : kHorizontal);
+    const int level = op.getLevel();
+    auto mask = [&](i64 idx) -> const Plaintext & { return cached(e, kind, s, idx, level, [&] { return diag_family_mask(e, s, f, idx); }); };
+    std::vector<Ciphertext> baby;
+    baby.reserve((size_t)f.bs);
+    baby.push_back(e.ev.leftRotate(op, f.gap));
+    for (i64 j = 1; j < f.bs; ++j) baby.push_back(e.ev.leftRotate(baby.back(), f.gap));
+    Ciphertext res = e.ev.mult(op, mask(0));
+    for (i64 i = 0; i < f.gs; ++i) {
+        const i64 rot_num = i * f.bs * f.gap;
+        for (int sign = -1; sign <= 1; sign += 2) { // negative diagonals first, then positive
+            i64 idx = 1 + i * f.bs + (sign < 0 ? -f.main : 0);
+            const i64 limit = sign < 0 ? f.sub - f.main : f.sub;
+            Ciphertext part = e.ev.mult(baby[0], mask(idx));
+            for (i64 j = 1; j < f.bs; ++j) {
+                if (++idx >= limit) break;
+                part = e.ev.add(part, e.ev.mult(baby[(size_t)j], mask(idx)));
+            }
+            part = sign < 0 ? e.ev.rightRotate(part, f.main * f.gap - rot_num) : e.ev.leftRotate(part, rot_num);
+            res = e.ev.add(res, part);
+        }
+    }
+    return res;
+}
+
+// Column / row wrap masks of the shift loops (generateColMask / generateRowMask, MatrixUtils.cpp:529-578):
+// entry 2i is 1 where the shifted copy has wrapped (last i columns / rows), entry 2i+1 its complement.
+const Plaintext &col_wrap(Env &e, const TileTensorShape &s, i64 which, int level) {
+    return cached(e, kColWrap, s, which, level, [&] {
+        Message m((size_t)e.slots);
+        const i64 cols = s.getNumCols(), i = which / 2; const bool wrapped = (which % 2) == 0;
+        for (i64 j = 0; j < e.slots; ++j) { bool in_tail = (j % cols) >= cols - i; m.re[(size_t)j] = (in_tail == wrapped) ? 1.0 : 0.0; }
+        return m;
+    });
+}
+const Plaintext &row_wrap(Env &e, const TileTensorShape &s, i64 which, int level) {
+    return cached(e, kRowWrap, s, which, level, [&] {
+        Message m((size_t)e.slots);
+        const i64 rows = s.getNumRows(), w = s.getBlockWidth(), i = which / 2; const bool wrapped = (which % 2) == 0;
+        for (i64 j = 0; j < e.slots; ++j) { bool in_tail = ((j / w) % rows) >= rows - i; m.re[(size_t)j] = (in_tail == wrapped) ? 1.0 : 0.0; }
+        return m;
+    });
+}
+
+void require_product_shapes(const CtxtTensor &a, const CtxtTensor &b) {
+    if (a.getWidth() != b.getHeight()) throw std::invalid_argument("[getCommonInsideLength] different inside length.");
+    if (a.getBlockWidth() != b.getBlockWidth()) throw std::invalid_argument("[getCommonBlockWidth] different block width");
+}
+
+} // namespace
+
+// MatrixTransformer::transpose<Ciphertext> -- MatrixUtils.cpp:671-739, masks :90-127.
+// Diagonal delta = col - row of the result moves by (width-1)*delta slots.
+CtxtTensor transpose(Env &e, const CtxtTensor &op) {
+    const i64 num_cols = op.getHeight(), num_rows = op.getWidth(), width = op.getBlockWidth();
+    if (num_cols > width) throw std::invalid_argument("[transpose] num_cols > width.");
+    const TileTensorShape s(num_rows, num_cols, width);
+    const i64 count = num_rows + num_cols - 1, bs = ceil_sqrt(count), gs = ceil_div(count, bs), gap = width - 1;
+    const int level = op.get().getLevel();
+    auto mask = [&](i64 idx) -> const Plaintext & {
+        return cached(e, kDiagonal, s, idx, level, [&] {
+            Placement pl; pl.origins.push_back({0, 0});
+            if (width != num_cols) pl.origins.push_back({0, num_rows});
+            Message m = paint(e, s, pl, num_rows, num_cols, [=](i64 r, i64 c) { return c - r == idx; }, 1.0);
+            const i64 i = (idx - (1 - num_rows)) / bs;
+            return m.rotated_right(i * bs * gap);
+        });
+    };
+    std::vector<Ciphertext> baby;
+    baby.reserve((size_t)bs);
+    baby.push_back(e.ev.rightRotate(op.get(), (num_rows - 1) * gap));
+    for (i64 j = 1; j < bs; ++j) baby.push_back(e.ev.leftRotate(baby.back(), gap));
+    Ciphertext res;
+    for (i64 i = 0; i < gs; ++i) {
+        i64 idx = 1 - num_rows + i * bs;
+        Ciphertext part = e.ev.mult(baby[0], mask(idx));
+        for (i64 j = 1; j < bs; ++j) {
+            if (++idx >= num_cols) break;
+            part = e.ev.add(part, e.ev.mult(baby[(size_t)j], mask(idx)));
+        }
+        if (i == 0) res = std::move(part);
+        else res = e.ev.add(res, e.ev.leftRotate(part, i * bs * gap));
+    }
+    return CtxtTensor(s, std::move(res));
+}
+
+CtxtTensor diagonalToColumn(Env &e, const CtxtTensor &op) { return CtxtTensor(op.getShape(), bsgs_diagonals(e, op.get(), op.getShape(), false, false)); }
+CtxtTensor diagonalToRow(Env &e, const CtxtTensor &op) { return CtxtTensor(op.getShape(), bsgs_diagonals(e, op.get(), op.getShape(), true, false)); }
+CtxtTensor packedDiagonalToColumn(Env &e, const CtxtTensor &op) {
+    const TileTensorShape s(2 * (op.getHeight() / 2), 2 * (op.getWidth() / 2), op.getBlockWidth());
+    return CtxtTensor(s, bsgs_diagonals(e, op.get(), s, false, true));
+}
+CtxtTensor packedDiagonalToRow(Env &e, const CtxtTensor &op) {
+    const TileTensorShape s(2 * (op.getHeight() / 2), 2 * (op.getWidth() / 2), op.getBlockWidth());
+    return CtxtTensor(s, bsgs_diagonals(e, op.get(), s, true, true));
+}
+
+// multMatMat<Ciphertext> -- MatrixUtils.cpp:1307-1446
+CtxtTensor multMatMatCC(Env &e, const CtxtTensor &op1, const CtxtTensor &op2, int target_level) {
+    require_product_shapes(op1, op2);
+    const i64 num_rows = op1.getHeight(), num_cols = op2.getWidth(), width = op1.getBlockWidth();
+    const i64 num_k = ceil_pow2(op1.getWidth());
+    if (std::min(op1.getLevel(), op2.getLevel()) < target_level + 3) throw std::invalid_argument("[multMatMat] level too low");
+    const TileTensorShape sa(num_rows, num_k, width), sb(num_k, num_cols, width);
+    const int lvl = target_level + 2;
+    Ciphertext a = e.ev.levelDown(diagonalToColumn(e, CtxtTensor(sa, op1.get())).get(), lvl);
+    Ciphertext b = e.ev.levelDown(diagonalToRow(e, CtxtTensor(sb, op2.get())).get(), lvl);
+    const i64 rows_tmp = num_k > num_rows ? num_k : ceil_pow2(num_rows), cols_tmp = num_k > num_cols ? num_k : ceil_pow2(num_cols);
+    Ciphertext res = e.ev.mult(a, b);
+    a = e.ev.leftRotate(a, 1);
+    b = e.ev.leftRotate(b, width);
+    Ciphertext a_wrap = e.ev.rightRotate(a, cols_tmp), b_wrap = e.ev.rightRotate(b, rows_tmp * width);
+    Ciphertext acc;
+    for (i64 i = 1; i < num_k; ++i) {
+        if (i > 1) {
+            a = e.ev.leftRotate(a, 1); a_wrap = e.ev.leftRotate(a_wrap, 1);
+            b = e.ev.leftRotate(b, width); b_wrap = e.ev.leftRotate(b_wrap, width);
+        }
+        Ciphertext ak = e.ev.assemble(a, col_wrap(e, sa, 2 * i + 1, lvl), a_wrap, col_wrap(e, sa, 2 * i, lvl));
+        Ciphertext bk = e.ev.assemble(b, row_wrap(e, sb, 2 * i + 1, lvl), b_wrap, row_wrap(e, sb, 2 * i, lvl));
+        e.ev.tensorAccumulate(acc, ak, bk);
+    }
+    res = e.ev.add(res, e.ev.rescale(e.ev.relinearize(acc)));
+    return CtxtTensor(TileTensorShape(num_rows, num_cols, width), std::move(res));
+}
+
+// multPackedMatMat -- MatrixUtils.cpp:1100-1216
+CtxtTensor multPackedMatMat(Env &e, const CtxtTensor &op1, const CtxtTensor &op2, int target_level) {
+    require_product_shapes(op1, op2);
+    const i64 num_rows = op1.getHeight(), num_cols = op2.getWidth(), width = op1.getBlockWidth();
+    const i64 num_k = ceil_pow2(op1.getWidth());
+    if (op1.getLevel() < target_level + 3 || op2.getLevel() < target_level + 2) throw std::invalid_argument("[multMatMat] level too low");
+    const TileTensorShape sa(num_rows, num_k, width), sb(num_k, num_cols, width);
+    const int lvl = target_level + 2;
+    Ciphertext a = packedDiagonalToColumn(e, CtxtTensor(sa, e.ev.levelDown(op1.get(), target_level + 3))).get();
+    Ciphertext b = packedDiagonalToRow(e, CtxtTensor(sb, e.ev.levelDown(op2.get(), target_level + 2))).get();
+    const i64 cols_tmp = num_k > num_cols ? num_k : ceil_pow2(num_cols);
+    Ciphertext res = e.ev.mult(a, b);
+    a = e.ev.leftRotate(a, 2);
+    b = e.ev.leftRotate(b, 2 * width);
+    Ciphertext a_wrap = e.ev.rightRotate(a, cols_tmp);
+    Ciphertext acc;
+    for (i64 i = 1; i < num_k / 2; ++i) {
+        if (i > 1) {
+            a = e.ev.leftRotate(a, 2); a_wrap = e.ev.leftRotate(a_wrap, 2);
+            b = e.ev.leftRotate(b, 2 * width);
+        }
+        Ciphertext ak = e.ev.assemble(a, col_wrap(e, sa, 4 * i + 1, lvl), a_wrap, col_wrap(e, sa, 4 * i, lvl));
+        e.ev.tensorAccumulate(acc, ak, b);
+    }
+    res = e.ev.add(res, e.ev.rescale(e.ev.relinearize(acc)));
+    return CtxtTensor(TileTensorShape(num_rows, num_cols, width), std::move(res));
+}
+// multPackedMatMatPre -- MatrixUtils.cpp:1218-1226
+CtxtTensor multPackedMatMatPre(Env &e, const CtxtTensor &a, int target_level) {
+    return packedDiagonalToColumn(e, CtxtTensor(a.getShape(), e.ev.levelDown(a.get(), target_level + 3)));
+}
+// multPackedMatMatPreRot -- MatrixUtils.cpp:1228-1264; the shifted copies come back as one batch
+Ciphertext multPackedMatMatPreRot(Env &e, const CtxtTensor &in, int target_level) {
+    const i64 num_rows = in.getHeight();
+    const int lvl = target_level + 2;
+    std::vector<Ciphertext> copies;
+    copies.push_back(e.ev.levelDownOne(in.get()));
+    Ciphertext a = e.ev.leftRotate(in.get(), 2);
+    Ciphertext a_wrap = e.ev.rightRotate(a, num_rows);
+    for (i64 i = 1; i < num_rows / 2; ++i) {
+        if (i > 1) { a = e.ev.leftRotate(a, 2); a_wrap = e.ev.leftRotate(a_wrap, 2); }
+        copies.push_back(e.ev.assemble(a, col_wrap(e, in.getShape(), 4 * i + 1, lvl), a_wrap, col_wrap(e, in.getShape(), 4 * i, lvl)));
+    }
+    return e.ev.stack(copies);
+}
+// multPackedMatMatPreRev -- MatrixUtils.cpp:1266-1274
+CtxtTensor multPackedMatMatPreRev(Env &e, const CtxtTensor &b, int target_level) {
+    return packedDiagonalToRow(e, CtxtTensor(b.getShape(), e.ev.levelDown(b.get(), target_level + 2)));
+}
+// multPackedMatMatCCReuse -- MatrixUtils.cpp:1276-1305 (relinearised and rescaled)
+CtxtTensor multPackedMatMatCCReuse(Env &e, const Ciphertext &pre, const CtxtTensor &tb) {
+    const i64 width = tb.getBlockWidth();
+    Ciphertext b = tb.get(), acc;
+    const int count = pre.getBatch();
+    for (int i = 0; i < count; ++i) {
+        if (i > 0) b = e.ev.leftRotate(b, 2 * width);
+        e.ev.tensorAccumulate(acc, e.ev.slice(pre, i), b);
+    }
+    return CtxtTensor(tb.getShape(), e.ev.rescale(e.ev.relinearize(acc)));
+}
+
+// multMatMatPre -- MatrixUtils.cpp:1572-1610; the `rows` shifted copies come back as one batch
+Ciphertext multMatMatPre(Env &e, const CtxtTensor &in, int target_level) {
+    const i64 num_rows = in.getHeight();
+    const int lvl = target_level + 2;
+    CtxtTensor s = diagonalToColumn(e, CtxtTensor(in.getShape(), e.ev.levelDown(in.get(), target_level + 3)));
+    std::vector<Ciphertext> copies;
+    copies.push_back(e.ev.levelDownOne(s.get()));
+    Ciphertext a = e.ev.leftRotate(s.get(), 1);
+    Ciphertext a_wrap = e.ev.rightRotate(a, num_rows);
+    for (i64 i = 1; i < num_rows; ++i) {
+        if (i > 1) { a = e.ev.leftRotate(a, 1); a_wrap = e.ev.leftRotate(a_wrap, 1); }
+        copies.push_back(e.ev.assemble(a, col_wrap(e, s.getShape(), 2 * i + 1, lvl), a_wrap, col_wrap(e, s.getShape(), 2 * i, lvl)));
+    }
+    return e.ev.stack(copies);
+}
+// multMatMatReUse -- MatrixUtils.cpp:1612-1639: one fused pass over the shifted copies
+CtxtTensor multMatMatReUse(Env &e, const Ciphertext &pre, const PtxtTensor &w) {
+    if (w.getLevel() != pre.getLevel()) throw std::invalid_argument("[multMatMatReUse] plaintext level differs from the ciphertexts'");
+    return CtxtTensor(w.getShape(), e.ev.matmul(pre, w.get(), w.getBlockWidth()));
+}
+// multMatMatPreRev -- MatrixUtils.cpp:1641-1649
+CtxtTensor multMatMatPreRev(Env &e, const CtxtTensor &b, int target_level) {
+    return diagonalToRow(e, CtxtTensor(b.getShape(), e.ev.levelDown(b.get(), target_level + 2)));
+}
+// multMatMatCCReUse -- MatrixUtils.cpp:1651-1679 (relinearised, not rescaled)
+CtxtTensor multMatMatCCReUse(Env &e, const Ciphertext &pre, const CtxtTensor &tb) {
+    const i64 width = tb.getBlockWidth();
+    Ciphertext b = tb.get(), acc;
+    const int count = pre.getBatch();
+    for (int i = 0; i < count; ++i) {
+        if (i > 0) b = e.ev.leftRotate(b, width);
+        e.ev.tensorAccumulate(acc, e.ev.slice(pre, i), b);
+    }
+    return CtxtTensor(tb.getShape(), e.ev.relinearize(acc));
+}
+
+} // namespace sched
+} // namespace HELLM

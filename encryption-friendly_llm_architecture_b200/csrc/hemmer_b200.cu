@@ -1,0 +1,754 @@
+// libhemmer_b200.so -- implementation of the C ABI in include/hemmer_b200.h.
+// Host code here only plans launches and owns device memory; every residue is computed by the
+// sm_100a kernels in ntt.cuh / kernels.cuh.  There is no CPU fallback: without a device the
+// context cannot be created.
+#include "../../include/hemmer_b200.h"
+#include "host_ctx.hpp"
+#include "kernels.cuh"
+#include "ntt.cuh"
+
+#include <dlfcn.h>
+#include <map>
+#include <memory>
+#include <mutex>
+#include <nccl.h> // types only: the library is resolved at run time, see nccl_api()
+#include <unordered_map>
+
+using namespace hb;
+using hbhost::HostCtx;
+using hbhost::HostParams;
+
+namespace {
+
+struct CudaFail { cudaError_t e; const char *where; };
+#define CK(x) do { cudaError_t e__ = (x); if (e__ != cudaSuccess) throw CudaFail{e__, #x}; } while (0)
+struct ArgFail { int code; std::string msg; };
+[[noreturn]] void fail(int code, const std::string &m) { throw ArgFail{code, m}; }
+
+// Size-bucketed caching allocator: the matmul schedules allocate and free the same few buffer
+// sizes thousands of times; cudaMalloc is reached only the first time a size is seen.
+struct Pool {
+    std::unordered_map<size_t, std::vector<void *>> free_;
+    std::unordered_map<void *, size_t> live_;
+    size_t total = 0, in_use = 0;
+    void *get(size_t bytes) {
+        bytes = (bytes + 255) & ~(size_t)255;
+        auto &v = free_[bytes];
+        void *p = nullptr;
+        if (!v.empty()) { p = v.back(); v.pop_back(); }
+        else {
+            cudaError_t e = cudaMalloc(&p, bytes);
+            if (e != cudaSuccess) { release_cached(); e = cudaMalloc(&p, bytes); }
+            if (e != cudaSuccess) { cudaGetLastError(); fail(HB_E_OOM, "device allocation of " + std::to_string(bytes) + " bytes failed"); }
+            total += bytes;
+        }
+        live_[p] = bytes; in_use += bytes;
+        return p;
+    }
+    void put(void *p) {
+        if (!p) return;
+        auto it = live_.find(p);
+        if (it == live_.end()) return;
+        free_[it->second].push_back(p); in_use -= it->second; live_.erase(it);
+    }
+    void release_cached() {
+        for (auto &kv : free_) { for (void *p : kv.second) { cudaFree(p); total -= kv.first; } kv.second.clear(); }
+    }
+    ~Pool() { release_cached(); for (auto &kv : live_) cudaFree(kv.first); }
+};
+
+struct Evk { u64 *d = nullptr; int nd = 0; };
+
+// NCCL is bound at first use instead of at link time: a process that also loads PyTorch must use the
+// NCCL build PyTorch brought along, whichever library was loaded first.
+struct NcclApi {
+    ncclResult_t (*AllReduce)(const void *, void *, size_t, ncclDataType_t, ncclRedOp_t, ncclComm_t, cudaStream_t) = nullptr;
+    ncclResult_t (*AllGather)(const void *, void *, size_t, ncclDataType_t, ncclComm_t, cudaStream_t) = nullptr;
+    ncclResult_t (*GetUniqueId)(ncclUniqueId *) = nullptr;
+    ncclResult_t (*CommInitRank)(ncclComm_t *, int, ncclUniqueId, int) = nullptr;
+    ncclResult_t (*CommDestroy)(ncclComm_t) = nullptr;
+    const char *(*GetErrorString)(ncclResult_t) = nullptr;
+    bool ok = false;
+};
+const NcclApi &nccl_api() {
+    static NcclApi api = [] {
+        NcclApi a;
+        void *h = dlsym(RTLD_DEFAULT, "ncclAllReduce") ? RTLD_DEFAULT : dlopen("libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
+        if (!h && !dlsym(RTLD_DEFAULT, "ncclAllReduce")) return a;
+        auto sym = [&](const char *n) { void *p = dlsym(RTLD_DEFAULT, n); return p ? p : (h && h != RTLD_DEFAULT ? dlsym(h, n) : nullptr); };
+        a.AllReduce = (decltype(a.AllReduce))sym("ncclAllReduce");
+        a.AllGather = (decltype(a.AllGather))sym("ncclAllGather");
+        a.GetUniqueId = (decltype(a.GetUniqueId))sym("ncclGetUniqueId");
+        a.CommInitRank = (decltype(a.CommInitRank))sym("ncclCommInitRank");
+        a.CommDestroy = (decltype(a.CommDestroy))sym("ncclCommDestroy");
+        a.GetErrorString = (decltype(a.GetErrorString))sym("ncclGetErrorString");
+        a.ok = a.AllReduce && a.AllGather && a.GetUniqueId && a.CommInitRank && a.CommDestroy && a.GetErrorString;
+        return a;
+    }();
+    return api;
+}
+
+} // namespace
+
+struct hb_ctx {
+    std::unique_ptr<HostCtx> h;
+    int device = 0;
+    cudaStream_t st = nullptr;
+    Pool pool;
+    std::string err;
+    PrimeConst *pc = nullptr;
+    u64 *tw = nullptr; // psi | psi_sh | ipsi | ipsi_sh, each [nprimes][N]
+    NttTables tb{};
+    u64 *sk = nullptr; // [nprimes][N] NTT form
+    bool have_sk = false;
+    Evk mult_key;
+    std::map<u64, Evk> gal_keys;
+    std::map<int, KsPlan *> plans; // device copies
+    ChaChaKey ckey{};
+    int N = 0, logn = 0, L = 0, K = 0, nprimes = 0;
+
+    LimbMap qmap(int level) const { LimbMap m{}; m.n = level + 1; for (int i = 0; i <= level; ++i) m.prime[i] = (unsigned char)i; return m; }
+    LimbMap allmap() const { LimbMap m{}; m.n = nprimes; for (int i = 0; i < nprimes; ++i) m.prime[i] = (unsigned char)i; return m; }
+    dim3 egrid(int count) const { return dim3((unsigned)((N + 255) / 256), (unsigned)count); }
+    u64 *alloc_limbs(size_t limbs) { return (u64 *)pool.get(limbs * (size_t)N * 8); }
+};
+
+struct hb_ct { hb_ctx *ctx; int level, np, batch, spow; u64 *d; size_t limbs() const { return (size_t)batch * np * (level + 1); } };
+struct hb_pt { hb_ctx *ctx; int level, spow; u64 *d; };
+
+namespace {
+
+hb_ct *new_ct(hb_ctx *c, int level, int np, int batch, int spow) {
+    if (level < 0 || level > c->L || np < 1 || np > 3 || batch < 1 || spow < 1 || spow > 2) fail(HB_E_ARG, "bad ciphertext geometry");
+    hb_ct *x = new hb_ct{c, level, np, batch, spow, nullptr};
+    try { x->d = c->alloc_limbs(x->limbs()); } catch (...) { delete x; throw; }
+    return x;
+}
+hb_pt *new_pt(hb_ctx *c, int level, int spow) {
+    hb_pt *x = new hb_pt{c, level, spow, nullptr};
+    try { x->d = c->alloc_limbs((size_t)level + 1); } catch (...) { delete x; throw; }
+    return x;
+}
+struct Tmp { // pool buffer released at scope exit
+    hb_ctx *c; u64 *p;
+    Tmp(hb_ctx *cc, size_t limbs) : c(cc), p(cc->alloc_limbs(limbs)) {}
+    ~Tmp() { c->pool.put(p); }
+    Tmp(const Tmp &) = delete;
+};
+
+void ntt(hb_ctx *c, const u64 *src, size_t so, u64 *dst, size_t dof, int count, const LimbMap &m, bool inv) {
+    CK(launch_ntt(c->st, src, so, dst, dof, count, m, c->pc, c->tb, c->logn, inv));
+}
+void ntt_inplace(hb_ctx *c, u64 *d, int count, const LimbMap &m, bool inv) { ntt(c, d, (size_t)m.n * c->N, d, (size_t)m.n * c->N, count, m, inv); }
+
+// ---- key-switch plan for one level ----
+const KsPlan *get_plan(hb_ctx *c, int level) {
+    auto it = c->plans.find(level);
+    if (it != c->plans.end()) return it->second;
+    const HostCtx &h = *c->h;
+    auto P = std::make_unique<KsPlan>();
+    std::memset(P.get(), 0, sizeof(KsPlan));
+    const int n = level + 1, K = h.K, ne = n + K;
+    P->level = level; P->n = n; P->ne = ne; P->K = K; P->nd = h.digit_of(level) + 1;
+    for (int j = 0; j < ne; ++j) P->ext_prime[j] = (unsigned char)(j < n ? j : h.L + 1 + (j - n));
+    int entry = 0;
+    for (int dg = 0; dg < P->nd; ++dg) {
+        const int lo = h.digit_lo(dg), hi = h.digit_hi(dg, n), ns = hi - lo;
+        P->dig_lo[dg] = lo; P->dig_hi[dg] = hi; P->dt_start[dg] = entry;
+        for (int s = 0; s < ns; ++s) {
+            const u64 qs = h.q[lo + s];
+            u64 hat = 1;
+            for (int t = 0; t < ns; ++t) if (t != s) hat = hbhost::mulmod(hat, h.q[lo + t] % qs, qs);
+            u64 hi_ = hbhost::invmod(hat, qs);
+            P->hat_inv[dg][s] = hi_; P->hat_inv_sh[dg][s] = hbhost::shoup(hi_, qs);
+            for (int j = 0; j < ne; ++j) {
+                const u64 qt = h.q[P->ext_prime[j]];
+                u64 hm = 1;
+                for (int t = 0; t < ns; ++t) if (t != s) hm = hbhost::mulmod(hm, h.q[lo + t] % qt, qt);
+                P->hat_mod[dg][s][j] = hm;
+            }
+        }
+        for (int j = 0; j < ne; ++j) {
+            if (j >= lo && j < hi) P->dt_entry[dg][j] = -1;
+            else P->dt_entry[dg][j] = (short)entry++;
+        }
+    }
+    P->dt_count = entry;
+    for (int k = 0; k < K; ++k) {
+        const u64 pk = h.q[h.L + 1 + k];
+        u64 hat = 1;
+        for (int t = 0; t < K; ++t) if (t != k) hat = hbhost::mulmod(hat, h.q[h.L + 1 + t] % pk, pk);
+        u64 hi_ = hbhost::invmod(hat, pk);
+        P->p_hat_inv[k] = hi_; P->p_hat_inv_sh[k] = hbhost::shoup(hi_, pk);
+        for (int l = 0; l < n; ++l) {
+            const u64 ql = h.q[l];
+            u64 hm = 1;
+            for (int t = 0; t < K; ++t) if (t != k) hm = hbhost::mulmod(hm, h.q[h.L + 1 + t] % ql, ql);
+            P->p_hat_mod[k][l] = hm;
+        }
+    }
+    for (int l = 0; l < n; ++l) {
+        const u64 ql = h.q[l];
+        u64 pm = 1;
+        for (int t = 0; t < K; ++t) pm = hbhost::mulmod(pm, h.q[h.L + 1 + t] % ql, ql);
+        P->p_inv[l] = hbhost::invmod(pm, ql);
+    }
+    KsPlan *d = nullptr;
+    CK(cudaMalloc(&d, sizeof(KsPlan)));
+    CK(cudaMemcpyAsync(d, P.get(), sizeof(KsPlan), cudaMemcpyHostToDevice, c->st));
+    CK(cudaStreamSynchronize(c->st));
+    c->plans[level] = d;
+    return d;
+}
+// host mirror of the few plan fields the launcher needs
+struct PlanDims { int n, ne, nd, K, dt_count; LimbMap dtmap; };
+PlanDims plan_dims(hb_ctx *c, int level) {
+    const HostCtx &h = *c->h;
+    PlanDims p{}; p.n = level + 1; p.K = h.K; p.ne = p.n + h.K; p.nd = h.digit_of(level) + 1;
+    int e = 0;
+    for (int dg = 0; dg < p.nd; ++dg) {
+        const int lo = h.digit_lo(dg), hi = h.digit_hi(dg, p.n);
+        for (int j = 0; j < p.ne; ++j) {
+            if (j >= lo && j < hi) continue;
+            if (e >= kMaxList) fail(HB_E_LIMIT, "too many lifted limbs");
+            p.dtmap.prime[e++] = (unsigned char)(j < p.n ? j : h.L + 1 + (j - p.n));
+        }
+    }
+    p.dt_count = e; p.dtmap.n = e;
+    return p;
+}
+
+// Hybrid key switch of polynomial a (NTT form, `n` limbs, per-batch stride a_outer) with key `key`:
+//   out[b][p][l] = ModDown(sum_dg perm_g(lift_dg(a)) (.) key_dg)[p][l] + add_p[b][l] o perm_g
+void keyswitch(hb_ctx *c, const u64 *a, size_t a_outer, int level, int batch, const Evk &key, u32 g, u64 *out, size_t out_outer, const u64 *add0, const u64 *add1,
+               size_t add_outer) {
+    const KsPlan *pl = get_plan(c, level);
+    const PlanDims d = plan_dims(c, level);
+    const int N = c->N, n = d.n, ne = d.ne, K = d.K;
+    const LimbMap qm = c->qmap(level);
+    const unsigned gx = (unsigned)((N + 255) / 256);
+    Tmp acoef(c, (size_t)batch * n), dt(c, (size_t)batch * d.dt_count), acc(c, (size_t)batch * 2 * ne), pco(c, (size_t)batch * 2 * K), t(c, (size_t)batch * 2 * n);
+    ntt(c, a, a_outer, acoef.p, (size_t)n * N, batch * n, qm, true);
+    k_modup<<<dim3(gx, d.nd, batch), 256, 0, c->st>>>(dt.p, acoef.p, pl, c->pc, N);
+    ntt_inplace(c, dt.p, batch * d.dt_count, d.dtmap, false);
+    k_ks_inner<<<dim3(gx, ne, batch), 256, 0, c->st>>>(acc.p, a, a_outer, dt.p, key.d, c->nprimes, pl, c->pc, g, c->logn, N);
+    LimbMap pm{}; pm.n = K; for (int k = 0; k < K; ++k) pm.prime[k] = (unsigned char)(c->L + 1 + k);
+    ntt(c, acc.p + (size_t)n * N, (size_t)ne * N, pco.p, (size_t)K * N, batch * 2 * K, pm, true);
+    k_moddown_conv<<<dim3(gx, 1, batch * 2), 256, 0, c->st>>>(t.p, pco.p, pl, c->pc, c->L + 1, N);
+    ntt_inplace(c, t.p, batch * 2 * n, qm, false);
+    k_moddown_fin<<<dim3(gx, n, batch * 2), 256, 0, c->st>>>(out, out_outer, acc.p, t.p, add0, add1, add_outer, pl, c->pc, g, c->logn, N);
+    CK(cudaGetLastError());
+}
+
+// switching key for secret s' (g == 0: s^2, else s o perm_g); stream ids kid*64 + digit
+Evk make_key(hb_ctx *c, u64 kid, u32 g) {
+    if (!c->have_sk) fail(HB_E_NOKEY, "secret key not generated");
+    const HostCtx &h = *c->h;
+    const int N = c->N, np = c->nprimes, nd = h.digit_of(h.L) + 1;
+    Evk k; k.nd = nd; k.d = c->alloc_limbs((size_t)nd * 2 * np);
+    const LimbMap am = c->allmap();
+    Tmp e(c, (size_t)np);
+    i64 *ecoef = (i64 *)c->pool.get((size_t)N * 8);
+    Scalars pmod{};
+    for (int pi = 0; pi <= h.L; ++pi) { u64 v = 1; for (int j = 0; j < h.K; ++j) v = hbhost::mulmod(v, h.q[h.L + 1 + j] % h.q[pi], h.q[pi]); pmod.v[pi] = v; }
+    std::vector<i64> ev;
+    for (int dg = 0; dg < nd; ++dg) {
+        u64 *b = k.d + ((size_t)dg * 2) * np * N, *a = b + (size_t)np * N;
+        k_uniform<<<dim3((unsigned)((N / 4 + 255) / 256), np), 256, 0, c->st>>>(a, am, c->pc, N, c->ckey, hbhost::STREAM_KEY_A, kid * 64 + dg);
+        h.sample_gauss(hbhost::STREAM_KEY_E, kid * 64 + dg, ev);
+        CK(cudaMemcpyAsync(ecoef, ev.data(), (size_t)N * 8, cudaMemcpyHostToDevice, c->st));
+        k_reduce_i64<<<c->egrid(np), 256, 0, c->st>>>(e.p, ecoef, am, c->pc, N);
+        CK(cudaStreamSynchronize(c->st)); // ev is reused by the next digit
+        ntt_inplace(c, e.p, np, am, false);
+        k_keygen<<<c->egrid(np), 256, 0, c->st>>>(b, a, e.p, c->sk, c->pc, N, c->logn, g, h.digit_lo(dg), h.digit_hi(dg, h.L + 1), pmod);
+    }
+    CK(cudaGetLastError());
+    c->pool.put(ecoef);
+    return k;
+}
+const Evk &galois_key(hb_ctx *c, u64 g) {
+    auto it = c->gal_keys.find(g);
+    if (it == c->gal_keys.end()) fail(HB_E_NOKEY, "no switching key for galois element " + std::to_string(g));
+    return it->second;
+}
+
+void check_same(const hb_ct *a, const hb_ct *b, const char *what) {
+    if (a->level != b->level) fail(HB_E_LEVEL, std::string(what) + ": level mismatch");
+    if (a->np != b->np || a->batch != b->batch || a->spow != b->spow) fail(HB_E_SHAPE, std::string(what) + ": shape mismatch");
+}
+
+hb_ct *do_rescale(hb_ctx *c, const hb_ct *a) {
+    if (a->level < 1) fail(HB_E_LEVEL, "rescale: level 0");
+    if (a->spow != 2) fail(HB_E_SHAPE, "rescale: nothing to rescale");
+    const int l = a->level, N = c->N, nbp = a->batch * a->np;
+    hb_ct *r = new_ct(c, l - 1, a->np, a->batch, 1);
+    try {
+        Tmp last(c, (size_t)nbp), t(c, (size_t)nbp * l);
+        LimbMap lm{}; lm.n = 1; lm.prime[0] = (unsigned char)l;
+        ntt(c, a->d + (size_t)l * N, (size_t)(l + 1) * N, last.p, (size_t)N, nbp, lm, true);
+        k_rescale_prep<<<c->egrid(nbp * l), 256, 0, c->st>>>(t.p, last.p, l, c->pc, N);
+        ntt_inplace(c, t.p, nbp * l, c->qmap(l - 1), false);
+        Scalars qi{};
+        for (int i = 0; i < l; ++i) qi.v[i] = hbhost::invmod(c->h->q[l] % c->h->q[i], c->h->q[i]);
+        k_rescale_fin<<<c->egrid(nbp * l), 256, 0, c->st>>>(r->d, a->d, t.p, l, c->pc, N, qi);
+        CK(cudaGetLastError());
+    } catch (...) { hb_ct_free(r); throw; }
+    return r;
+}
+hb_ct *do_level_down(hb_ctx *c, const hb_ct *a, int target) {
+    if (target > a->level || target < 0) fail(HB_E_LEVEL, "level_down: bad target");
+    if (a->spow != 1) fail(HB_E_SHAPE, "level_down: operand not rescaled");
+    const int N = c->N, nbp = a->batch * a->np, tl = target + 1;
+    hb_ct *t = new_ct(c, tl, a->np, a->batch, 2);
+    hb_ct *r = nullptr;
+    try {
+        const double cf = c->h->scale[target] * (double)c->h->q[tl] / c->h->scale[a->level];
+        const i64 k = (i64)std::rint(cf);
+        Scalars s{};
+        for (int i = 0; i <= tl; ++i) s.v[i] = (u64)(k % (i64)c->h->q[i]);
+        k_scalar_mul<<<c->egrid(nbp * (tl + 1)), 256, 0, c->st>>>(t->d, a->d, (size_t)(a->level + 1) * N, c->qmap(tl), c->pc, N, s);
+        CK(cudaGetLastError());
+        r = do_rescale(c, t);
+    } catch (...) { hb_ct_free(t); throw; }
+    hb_ct_free(t);
+    return r;
+}
+hb_ct *do_addsub(hb_ctx *c, const hb_ct *a, const hb_ct *b, int mode) {
+    if (a->level != b->level) { // level-adjusting add: bring the higher operand down first
+        const hb_ct *hi = a->level > b->level ? a : b;
+        hb_ct *low = do_level_down(c, hi, std::min(a->level, b->level));
+        hb_ct *r = nullptr;
+        try { r = hi == a ? do_addsub(c, low, b, mode) : do_addsub(c, a, low, mode); } catch (...) { hb_ct_free(low); throw; }
+        hb_ct_free(low);
+        return r;
+    }
+    check_same(a, b, "add");
+    hb_ct *r = new_ct(c, a->level, a->np, a->batch, a->spow);
+    k_addsub<<<c->egrid((int)a->limbs()), 256, 0, c->st>>>(r->d, a->d, b->d, c->qmap(a->level), c->pc, c->N, mode);
+    return r;
+}
+hb_ct *do_tensor(hb_ctx *c, const hb_ct *a, const hb_ct *b, hb_ct *acc) {
+    check_same(a, b, "tensor");
+    if (a->np != 2 || a->spow != 1) fail(HB_E_SHAPE, "tensor: operands must be rescaled 2-poly ciphertexts");
+    hb_ct *r = acc;
+    if (r) { if (r->level != a->level || r->np != 3 || r->batch != a->batch || r->spow != 2) fail(HB_E_SHAPE, "tensor_acc: accumulator mismatch"); }
+    else r = new_ct(c, a->level, 3, a->batch, 2);
+    const int n = a->level + 1;
+    k_tensor<<<c->egrid(a->batch * n), 256, 0, c->st>>>(r->d, a->d, b->d, n, c->qmap(a->level), c->pc, c->N, acc ? 1 : 0);
+    return r;
+}
+hb_ct *do_relin(hb_ctx *c, const hb_ct *a) {
+    if (a->np != 3) fail(HB_E_SHAPE, "relin: needs 3 polys");
+    if (!c->mult_key.d) fail(HB_E_NOKEY, "multiplication key not generated");
+    const int n = a->level + 1, N = c->N;
+    hb_ct *r = new_ct(c, a->level, 2, a->batch, a->spow);
+    try {
+        keyswitch(c, a->d + (size_t)2 * n * N, (size_t)3 * n * N, a->level, a->batch, c->mult_key, 0, r->d, (size_t)2 * n * N, a->d, a->d + (size_t)n * N, (size_t)3 * n * N);
+    } catch (...) { hb_ct_free(r); throw; }
+    return r;
+}
+hb_ct *do_galois(hb_ctx *c, const hb_ct *a, u64 g) {
+    if (a->np != 2) fail(HB_E_SHAPE, "rotate: needs 2 polys");
+    const int n = a->level + 1, N = c->N;
+    if (g == 1) { hb_ct *r = new_ct(c, a->level, 2, a->batch, a->spow); CK(cudaMemcpyAsync(r->d, a->d, a->limbs() * N * 8, cudaMemcpyDeviceToDevice, c->st)); return r; }
+    const Evk &key = galois_key(c, g);
+    hb_ct *r = new_ct(c, a->level, 2, a->batch, a->spow);
+    try {
+        keyswitch(c, a->d + (size_t)n * N, (size_t)2 * n * N, a->level, a->batch, key, (u32)g, r->d, (size_t)2 * n * N, a->d, nullptr, (size_t)2 * n * N);
+    } catch (...) { hb_ct_free(r); throw; }
+    return r;
+}
+hb_ct *do_mul_pt(hb_ctx *c, const hb_ct *a, const hb_pt *p) {
+    if (a->level != p->level) fail(HB_E_LEVEL, "mul_pt: level mismatch");
+    if (a->spow != 1 || p->spow != 1) fail(HB_E_SHAPE, "mul_pt: operand not rescaled");
+    hb_ct *r = new_ct(c, a->level, a->np, a->batch, 2);
+    k_mul_pt<<<c->egrid((int)a->limbs()), 256, 0, c->st>>>(r->d, a->d, p->d, c->qmap(a->level), c->pc, c->N);
+    return r;
+}
+
+template <class F> int guard(hb_ctx *c, F &&f) {
+    try { CK(cudaSetDevice(c->device)); f(); return HB_OK; }
+    catch (const ArgFail &e) { c->err = e.msg; return e.code; }
+    catch (const CudaFail &e) { c->err = std::string(e.where) + ": " + cudaGetErrorString(e.e); return HB_E_CUDA; }
+    catch (const std::invalid_argument &e) { c->err = e.what(); return HB_E_ARG; }
+    catch (const std::exception &e) { c->err = e.what(); return HB_E_CUDA; }
+}
+
+} // namespace
+
+extern "C" {
+
+int hb_ctx_create(const hb_params *prm, int device, hb_ctx **out) {
+    if (!prm || !out) return HB_E_ARG;
+    int ndev = 0;
+    if (cudaGetDeviceCount(&ndev) != cudaSuccess || device < 0 || device >= ndev) { cudaGetLastError(); return HB_E_CUDA; }
+    hb_ctx *c = new hb_ctx();
+    try {
+        HostParams hp{prm->log_n, prm->max_level, prm->dnum, prm->num_special, prm->q0_bits, prm->q_bits, prm->p_bits, prm->hamming_weight, prm->sigma,
+                      {prm->seed[0], prm->seed[1], prm->seed[2], prm->seed[3]}};
+        c->h.reset(new HostCtx(hp));
+        if (!(c->h->logn == 16 || c->h->logn <= 12)) throw std::invalid_argument("log_n must be 16 or at most 12");
+        c->device = device; c->N = c->h->N; c->logn = c->h->logn; c->L = c->h->L; c->K = c->h->K; c->nprimes = c->h->nprimes;
+        for (int i = 0; i < 8; ++i) c->ckey.k[i] = c->h->cha.key[i];
+        CK(cudaSetDevice(device));
+        CK(cudaStreamCreateWithFlags(&c->st, cudaStreamNonBlocking));
+        const int np = c->nprimes, N = c->N;
+        std::vector<PrimeConst> pcs(np);
+        std::vector<u64> tw((size_t)4 * np * N);
+        for (int i = 0; i < np; ++i) {
+            const u64 q = c->h->q[i];
+            PrimeConst &p = pcs[i];
+            p.q = q;
+            unsigned __int128 two64 = (unsigned __int128)1 << 64;
+            p.mu_hi = (u64)(two64 / q);
+            p.mu_lo = (u64)(((two64 % q) << 64) / q);
+            p.n_inv = hbhost::invmod((u64)N, q); p.n_inv_sh = hbhost::shoup(p.n_inv, q);
+            p.iu = hbhost::powmod(c->h->psi_root[i], (u64)N / 2, q); p.iu_sh = hbhost::shoup(p.iu, q);
+            p.pad = 0;
+            std::vector<u64> f, fs, iv, ivs;
+            c->h->twiddles(i, f, fs, iv, ivs);
+            std::memcpy(&tw[((size_t)0 * np + i) * N], f.data(), (size_t)N * 8);
+            std::memcpy(&tw[((size_t)1 * np + i) * N], fs.data(), (size_t)N * 8);
+            std::memcpy(&tw[((size_t)2 * np + i) * N], iv.data(), (size_t)N * 8);
+            std::memcpy(&tw[((size_t)3 * np + i) * N], ivs.data(), (size_t)N * 8);
+        }
+        CK(cudaMalloc(&c->pc, sizeof(PrimeConst) * np));
+        CK(cudaMemcpy(c->pc, pcs.data(), sizeof(PrimeConst) * np, cudaMemcpyHostToDevice));
+        CK(cudaMalloc(&c->tw, tw.size() * 8));
+        CK(cudaMemcpy(c->tw, tw.data(), tw.size() * 8, cudaMemcpyHostToDevice));
+        c->tb.psi = c->tw; c->tb.psi_sh = c->tw + (size_t)np * N; c->tb.ipsi = c->tw + (size_t)2 * np * N; c->tb.ipsi_sh = c->tw + (size_t)3 * np * N;
+        CK(cudaMalloc(&c->sk, (size_t)np * N * 8));
+    } catch (const CudaFail &) { hb_ctx_destroy(c); return HB_E_CUDA; }
+    catch (const ArgFail &e) { int code = e.code; hb_ctx_destroy(c); return code; }
+    catch (...) { hb_ctx_destroy(c); return HB_E_ARG; }
+    *out = c;
+    return HB_OK;
+}
+void hb_ctx_destroy(hb_ctx *c) {
+    if (!c) return;
+    cudaSetDevice(c->device);
+    if (c->st) cudaStreamSynchronize(c->st);
+    for (auto &kv : c->plans) cudaFree(kv.second);
+    if (c->pc) cudaFree(c->pc);
+    if (c->tw) cudaFree(c->tw);
+    if (c->sk) cudaFree(c->sk);
+    if (c->st) cudaStreamDestroy(c->st);
+    delete c;
+}
+const char *hb_last_error(const hb_ctx *c) { return c ? c->err.c_str() : "null context"; }
+int hb_ctx_info(const hb_ctx *c, uint64_t *primes, double *scales) {
+    if (!c) return HB_E_ARG;
+    if (primes) for (int i = 0; i < c->nprimes; ++i) primes[i] = c->h->q[i];
+    if (scales) for (int i = 0; i <= c->L; ++i) scales[i] = c->h->scale[i];
+    return HB_OK;
+}
+int hb_ctx_dims(const hb_ctx *c, int *log_n, int *max_level, int *num_special) {
+    if (!c) return HB_E_ARG;
+    if (log_n) *log_n = c->logn; if (max_level) *max_level = c->L; if (num_special) *num_special = c->K;
+    return HB_OK;
+}
+int hb_sync(hb_ctx *c) { return guard(c, [&] { CK(cudaStreamSynchronize(c->st)); }); }
+int hb_mem_info(const hb_ctx *c, uint64_t *pool_bytes, uint64_t *in_use) {
+    if (pool_bytes) *pool_bytes = c->pool.total;
+    if (in_use) *in_use = c->pool.in_use;
+    return HB_OK;
+}
+void *hb_stream(const hb_ctx *c) { return (void *)c->st; }
+
+int hb_keygen(hb_ctx *c) {
+    return guard(c, [&] {
+        const HostCtx &h = *c->h;
+        std::vector<i64> s; h.sample_secret(s);
+        i64 *sc = (i64 *)c->pool.get((size_t)c->N * 8);
+        CK(cudaMemcpyAsync(sc, s.data(), (size_t)c->N * 8, cudaMemcpyHostToDevice, c->st));
+        const LimbMap am = c->allmap();
+        k_reduce_i64<<<c->egrid(c->nprimes), 256, 0, c->st>>>(c->sk, sc, am, c->pc, c->N);
+        ntt_inplace(c, c->sk, c->nprimes, am, false);
+        CK(cudaStreamSynchronize(c->st));
+        c->pool.put(sc);
+        c->have_sk = true;
+        if (!c->mult_key.d) c->mult_key = make_key(c, 0, 0);
+        const u64 gc = h.galois_conj();
+        if (!c->gal_keys.count(gc)) c->gal_keys[gc] = make_key(c, gc, (u32)gc);
+    });
+}
+int hb_gen_rot_keys(hb_ctx *c, const int64_t *steps, int n) {
+    return guard(c, [&] {
+        for (int i = 0; i < n; ++i) {
+            const u64 g = c->h->galois_rot(steps[i]);
+            if (g == 1 || c->gal_keys.count(g)) continue;
+            c->gal_keys[g] = make_key(c, g, (u32)g);
+        }
+    });
+}
+uint64_t hb_galois_for_rotation(const hb_ctx *c, int64_t s) { return c->h->galois_rot(s); }
+int hb_evk_export(hb_ctx *c, uint64_t g, uint64_t *host, int *digits) {
+    return guard(c, [&] {
+        const Evk *k = g == 0 ? &c->mult_key : &galois_key(c, g);
+        if (!k->d) fail(HB_E_NOKEY, "key not generated");
+        if (digits) *digits = k->nd;
+        if (host) { CK(cudaStreamSynchronize(c->st)); CK(cudaMemcpy(host, k->d, (size_t)k->nd * 2 * c->nprimes * c->N * 8, cudaMemcpyDeviceToHost)); }
+    });
+}
+
+int hb_encode(hb_ctx *c, const double *re, const double *im, size_t n, int level, hb_pt **out) {
+    return guard(c, [&] {
+        if (!re || !out || n > (size_t)c->h->slots) fail(HB_E_ARG, "encode: bad message");
+        if (level < 0 || level > c->L) fail(HB_E_LEVEL, "encode: bad level");
+        std::vector<i64> coef;
+        c->h->encode_coeffs(re, im, n, c->h->scale[level], coef);
+        hb_pt *p = new_pt(c, level, 1);
+        i64 *dc = (i64 *)c->pool.get((size_t)c->N * 8);
+        CK(cudaMemcpyAsync(dc, coef.data(), (size_t)c->N * 8, cudaMemcpyHostToDevice, c->st));
+        const LimbMap qm = c->qmap(level);
+        k_reduce_i64<<<c->egrid(level + 1), 256, 0, c->st>>>(p->d, dc, qm, c->pc, c->N);
+        ntt_inplace(c, p->d, level + 1, qm, false);
+        CK(cudaStreamSynchronize(c->st)); // coef goes out of scope
+        c->pool.put(dc);
+        *out = p;
+    });
+}
+static void decode_limbs(hb_ctx *c, const u64 *dev_coef, int level, int spow, double *re, double *im) {
+    const int nl = level >= 1 ? 2 : 1, N = c->N;
+    std::vector<u64> hc((size_t)nl * N);
+    CK(cudaMemcpyAsync(hc.data(), dev_coef, hc.size() * 8, cudaMemcpyDeviceToHost, c->st));
+    CK(cudaStreamSynchronize(c->st));
+    std::vector<double> val;
+    c->h->centre(hc.data(), nl == 2 ? hc.data() + N : nullptr, val);
+    const double sc = spow == 2 ? c->h->scale[level] * c->h->scale[level] : c->h->scale[level];
+    c->h->decode_values(val, sc, re, im);
+}
+int hb_decode(hb_ctx *c, const hb_pt *p, double *re, double *im) {
+    return guard(c, [&] {
+        const int nl = p->level >= 1 ? 2 : 1;
+        Tmp t(c, (size_t)nl);
+        ntt(c, p->d, (size_t)nl * c->N, t.p, (size_t)nl * c->N, nl, c->qmap(nl - 1), true);
+        decode_limbs(c, t.p, p->level, p->spow, re, im);
+    });
+}
+int hb_encrypt(hb_ctx *c, const hb_pt *p, uint64_t nonce, hb_ct **out) {
+    return guard(c, [&] {
+        if (!c->have_sk) fail(HB_E_NOKEY, "secret key not generated");
+        const int n = p->level + 1, N = c->N;
+        hb_ct *r = new_ct(c, p->level, 2, 1, p->spow);
+        try {
+            const LimbMap qm = c->qmap(p->level);
+            u64 *b = r->d, *a = r->d + (size_t)n * N;
+            k_uniform<<<dim3((unsigned)((N / 4 + 255) / 256), n), 256, 0, c->st>>>(a, qm, c->pc, N, c->ckey, hbhost::STREAM_ENC_A, nonce);
+            std::vector<i64> ev; c->h->sample_gauss(hbhost::STREAM_ENC_E, nonce, ev);
+            i64 *ec = (i64 *)c->pool.get((size_t)N * 8);
+            Tmp e(c, (size_t)n);
+            CK(cudaMemcpyAsync(ec, ev.data(), (size_t)N * 8, cudaMemcpyHostToDevice, c->st));
+            k_reduce_i64<<<c->egrid(n), 256, 0, c->st>>>(e.p, ec, qm, c->pc, N);
+            ntt_inplace(c, e.p, n, qm, false);
+            k_encrypt<<<c->egrid(n), 256, 0, c->st>>>(b, a, e.p, c->sk, p->d, qm, c->pc, N);
+            CK(cudaStreamSynchronize(c->st));
+            c->pool.put(ec);
+        } catch (...) { hb_ct_free(r); throw; }
+        *out = r;
+    });
+}
+int hb_decrypt(hb_ctx *c, const hb_ct *ct, int index, double *re, double *im) {
+    return guard(c, [&] {
+        if (!c->have_sk) fail(HB_E_NOKEY, "secret key not generated");
+        if (index < 0 || index >= ct->batch) fail(HB_E_ARG, "decrypt: bad batch index");
+        const int n = ct->level + 1, N = c->N, nl = ct->level >= 1 ? 2 : 1;
+        Tmp t(c, (size_t)nl);
+        k_decrypt<<<c->egrid(nl), 256, 0, c->st>>>(t.p, ct->d + (size_t)index * ct->np * n * N, n, ct->np, c->sk, c->pc, N);
+        ntt_inplace(c, t.p, nl, c->qmap(nl - 1), true);
+        decode_limbs(c, t.p, ct->level, ct->spow, re, im);
+    });
+}
+
+int hb_ct_create(hb_ctx *c, int level, int np, int batch, int spow, hb_ct **out) { return guard(c, [&] { *out = new_ct(c, level, np, batch, spow); }); }
+int hb_ct_clone(hb_ctx *c, const hb_ct *s, hb_ct **out) {
+    return guard(c, [&] {
+        hb_ct *r = new_ct(c, s->level, s->np, s->batch, s->spow);
+        CK(cudaMemcpyAsync(r->d, s->d, s->limbs() * c->N * 8, cudaMemcpyDeviceToDevice, c->st));
+        *out = r;
+    });
+}
+void hb_ct_free(hb_ct *x) { if (x) { x->ctx->pool.put(x->d); delete x; } }
+void hb_pt_free(hb_pt *x) { if (x) { x->ctx->pool.put(x->d); delete x; } }
+int hb_ct_meta(const hb_ct *x, int *level, int *np, int *batch, int *spow) {
+    if (!x) return HB_E_ARG;
+    if (level) *level = x->level; if (np) *np = x->np; if (batch) *batch = x->batch; if (spow) *spow = x->spow;
+    return HB_OK;
+}
+int hb_pt_meta(const hb_pt *x, int *level, int *spow) { if (!x) return HB_E_ARG; if (level) *level = x->level; if (spow) *spow = x->spow; return HB_OK; }
+int hb_ct_import(hb_ctx *c, hb_ct *x, const uint64_t *host) {
+    return guard(c, [&] { CK(cudaMemcpyAsync(x->d, host, x->limbs() * c->N * 8, cudaMemcpyHostToDevice, c->st)); CK(cudaStreamSynchronize(c->st)); });
+}
+int hb_ct_export(hb_ctx *c, const hb_ct *x, uint64_t *host) {
+    return guard(c, [&] { CK(cudaMemcpyAsync(host, x->d, x->limbs() * c->N * 8, cudaMemcpyDeviceToHost, c->st)); CK(cudaStreamSynchronize(c->st)); });
+}
+int hb_pt_export(hb_ctx *c, const hb_pt *x, uint64_t *host) {
+    return guard(c, [&] { CK(cudaMemcpyAsync(host, x->d, (size_t)(x->level + 1) * c->N * 8, cudaMemcpyDeviceToHost, c->st)); CK(cudaStreamSynchronize(c->st)); });
+}
+void *hb_ct_device_ptr(const hb_ct *x) { return x ? x->d : nullptr; }
+int hb_batch_set(hb_ctx *c, hb_ct *dst, int idx, const hb_ct *src) {
+    return guard(c, [&] {
+        if (src->batch != 1 || src->level != dst->level || src->np != dst->np || idx < 0 || idx >= dst->batch) fail(HB_E_SHAPE, "batch_set: mismatch");
+        const size_t per = (size_t)src->np * (src->level + 1) * c->N;
+        CK(cudaMemcpyAsync(dst->d + per * idx, src->d, per * 8, cudaMemcpyDeviceToDevice, c->st));
+    });
+}
+int hb_batch_get(hb_ctx *c, const hb_ct *src, int idx, hb_ct **out) {
+    return guard(c, [&] {
+        if (idx < 0 || idx >= src->batch) fail(HB_E_ARG, "batch_get: bad index");
+        hb_ct *r = new_ct(c, src->level, src->np, 1, src->spow);
+        const size_t per = (size_t)src->np * (src->level + 1) * c->N;
+        CK(cudaMemcpyAsync(r->d, src->d + per * idx, per * 8, cudaMemcpyDeviceToDevice, c->st));
+        *out = r;
+    });
+}
+
+int hb_add(hb_ctx *c, const hb_ct *a, const hb_ct *b, hb_ct **out) { return guard(c, [&] { *out = do_addsub(c, a, b, 0); }); }
+int hb_sub(hb_ctx *c, const hb_ct *a, const hb_ct *b, hb_ct **out) { return guard(c, [&] { *out = do_addsub(c, a, b, 1); }); }
+int hb_negate(hb_ctx *c, const hb_ct *a, hb_ct **out) {
+    return guard(c, [&] {
+        hb_ct *r = new_ct(c, a->level, a->np, a->batch, a->spow);
+        k_addsub<<<c->egrid((int)a->limbs()), 256, 0, c->st>>>(r->d, a->d, a->d, c->qmap(a->level), c->pc, c->N, 2);
+        *out = r;
+    });
+}
+int hb_mult_imag(hb_ctx *c, const hb_ct *a, hb_ct **out) {
+    return guard(c, [&] {
+        hb_ct *r = new_ct(c, a->level, a->np, a->batch, a->spow);
+        k_mult_imag<<<c->egrid((int)a->limbs()), 256, 0, c->st>>>(r->d, a->d, c->qmap(a->level), c->pc, c->N);
+        *out = r;
+    });
+}
+int hb_mult_int(hb_ctx *c, const hb_ct *a, int64_t k, hb_ct **out) {
+    return guard(c, [&] {
+        hb_ct *r = new_ct(c, a->level, a->np, a->batch, a->spow);
+        Scalars s{};
+        for (int i = 0; i <= a->level; ++i) { const i64 q = (i64)c->h->q[i]; i64 v = k % q; if (v < 0) v += q; s.v[i] = (u64)v; }
+        k_scalar_mul<<<c->egrid((int)a->limbs()), 256, 0, c->st>>>(r->d, a->d, (size_t)(a->level + 1) * c->N, c->qmap(a->level), c->pc, c->N, s);
+        *out = r;
+    });
+}
+int hb_mul_pt_norescale(hb_ctx *c, const hb_ct *a, const hb_pt *p, hb_ct **out) { return guard(c, [&] { *out = do_mul_pt(c, a, p); }); }
+int hb_mul_pt(hb_ctx *c, const hb_ct *a, const hb_pt *p, hb_ct **out) {
+    return guard(c, [&] {
+        hb_ct *t = do_mul_pt(c, a, p);
+        try { *out = do_rescale(c, t); } catch (...) { hb_ct_free(t); throw; }
+        hb_ct_free(t);
+    });
+}
+int hb_rescale(hb_ctx *c, const hb_ct *a, hb_ct **out) { return guard(c, [&] { *out = do_rescale(c, a); }); }
+int hb_level_down(hb_ctx *c, const hb_ct *a, int target, hb_ct **out) {
+    return guard(c, [&] {
+        if (target == a->level) { hb_ct *r = new_ct(c, a->level, a->np, a->batch, a->spow); CK(cudaMemcpyAsync(r->d, a->d, a->limbs() * c->N * 8, cudaMemcpyDeviceToDevice, c->st)); *out = r; }
+        else *out = do_level_down(c, a, target);
+    });
+}
+int hb_tensor(hb_ctx *c, const hb_ct *a, const hb_ct *b, hb_ct **out) { return guard(c, [&] { *out = do_tensor(c, a, b, nullptr); }); }
+int hb_tensor_acc(hb_ctx *c, const hb_ct *a, const hb_ct *b, hb_ct **acc) { return guard(c, [&] { *acc = do_tensor(c, a, b, *acc); }); }
+int hb_relin(hb_ctx *c, const hb_ct *a, hb_ct **out) { return guard(c, [&] { *out = do_relin(c, a); }); }
+int hb_mul(hb_ctx *c, const hb_ct *a, const hb_ct *b, hb_ct **out) {
+    return guard(c, [&] {
+        if (a->level != b->level) { // align levels: the higher operand comes down first
+            const hb_ct *hi = a->level > b->level ? a : b;
+            hb_ct *low = do_level_down(c, hi, std::min(a->level, b->level));
+            int rc = hi == a ? hb_mul(c, low, b, out) : hb_mul(c, a, low, out);
+            hb_ct_free(low);
+            if (rc != HB_OK) throw ArgFail{rc, c->err};
+            return;
+        }
+        hb_ct *t = do_tensor(c, a, b, nullptr), *r = nullptr;
+        try { r = do_relin(c, t); } catch (...) { hb_ct_free(t); throw; }
+        hb_ct_free(t);
+        try { *out = do_rescale(c, r); } catch (...) { hb_ct_free(r); throw; }
+        hb_ct_free(r);
+    });
+}
+int hb_rotate(hb_ctx *c, const hb_ct *a, int64_t steps, hb_ct **out) { return guard(c, [&] { *out = do_galois(c, a, c->h->galois_rot(steps)); }); }
+int hb_conjugate(hb_ctx *c, const hb_ct *a, hb_ct **out) { return guard(c, [&] { *out = do_galois(c, a, c->h->galois_conj()); }); }
+int hb_ntt(hb_ctx *c, hb_ct *a, int inverse) { return guard(c, [&] { ntt_inplace(c, a->d, (int)a->limbs(), c->qmap(a->level), inverse != 0); }); }
+
+int hb_mul2_add_rescale(hb_ctx *c, const hb_ct *a, const hb_pt *pa, const hb_ct *b, const hb_pt *pb, hb_ct **out) {
+    return guard(c, [&] {
+        check_same(a, b, "mul2_add_rescale");
+        if (a->level != pa->level || a->level != pb->level) fail(HB_E_LEVEL, "mul2_add_rescale: level mismatch");
+        if (a->spow != 1) fail(HB_E_SHAPE, "mul2_add_rescale: operand not rescaled");
+        hb_ct *t = new_ct(c, a->level, a->np, a->batch, 2);
+        k_mul2_add<<<c->egrid((int)a->limbs()), 256, 0, c->st>>>(t->d, a->d, pa->d, b->d, pb->d, c->qmap(a->level), c->pc, c->N);
+        try { *out = do_rescale(c, t); } catch (...) { hb_ct_free(t); throw; }
+        hb_ct_free(t);
+    });
+}
+int hb_matmul_acc(hb_ctx *c, const hb_ct *pre, const hb_pt *pt, int64_t row_step, hb_ct **out) {
+    return guard(c, [&] {
+        if (pre->level != pt->level) fail(HB_E_LEVEL, "matmul_acc: plaintext level differs from the ciphertexts'");
+        if (pre->np != 2 || pre->spow != 1 || pt->spow != 1) fail(HB_E_SHAPE, "matmul_acc: operands");
+        const int n = pre->level + 1, kc = pre->batch;
+        std::vector<u32> gal((size_t)kc);
+        for (int k = 0; k < kc; ++k) gal[(size_t)k] = (u32)c->h->galois_rot((i64)k * row_step);
+        u32 *dg = (u32 *)c->pool.get((size_t)kc * 4);
+        CK(cudaMemcpyAsync(dg, gal.data(), (size_t)kc * 4, cudaMemcpyHostToDevice, c->st));
+        hb_ct *r = new_ct(c, pre->level, 2, 1, 2);
+        k_matmul_acc<<<c->egrid(2 * n), 256, 0, c->st>>>(r->d, pre->d, kc, pt->d, dg, n, c->qmap(pre->level), c->pc, c->logn, c->N);
+        CK(cudaStreamSynchronize(c->st));
+        c->pool.put(dg);
+        *out = r;
+    });
+}
+int hb_pt_rotate(hb_ctx *c, const hb_pt *p, int64_t steps, hb_pt **out) {
+    return guard(c, [&] {
+        hb_pt *r = new_pt(c, p->level, p->spow);
+        const u64 g = c->h->galois_rot(steps);
+        if (g == 1) CK(cudaMemcpyAsync(r->d, p->d, (size_t)(p->level + 1) * c->N * 8, cudaMemcpyDeviceToDevice, c->st));
+        else k_permute<<<c->egrid(p->level + 1), 256, 0, c->st>>>(r->d, p->d, (u32)g, c->logn, c->N);
+        *out = r;
+    });
+}
+int hb_mod_reduce(hb_ctx *c, hb_ct *a) {
+    return guard(c, [&] { k_mod_reduce<<<c->egrid((int)a->limbs()), 256, 0, c->st>>>(a->d, c->qmap(a->level), c->pc, c->N); });
+}
+// Sum over ranks of residues below 2^60 cannot overflow 64 bits for up to 16 ranks; the owner
+// reduces afterwards (same order of operations as HEMMer::ncclAllReduceWrapper + modReduct).
+int hb_allreduce_sum(hb_ctx *c, hb_ct *a, void *comm) {
+    return guard(c, [&] {
+        const NcclApi &nc = nccl_api();
+        if (!nc.ok) fail(HB_E_NCCL, "NCCL library not available");
+        ncclResult_t r = nc.AllReduce(a->d, a->d, a->limbs() * c->N, ncclUint64, ncclSum, (ncclComm_t)comm, c->st);
+        if (r != ncclSuccess) fail(HB_E_NCCL, nc.GetErrorString(r));
+        k_mod_reduce<<<c->egrid((int)a->limbs()), 256, 0, c->st>>>(a->d, c->qmap(a->level), c->pc, c->N);
+    });
+}
+int hb_allgather(hb_ctx *c, const hb_ct *mine, hb_ct *all, void *comm) {
+    return guard(c, [&] {
+        if (all->level != mine->level || all->np != mine->np || all->batch % mine->batch) fail(HB_E_SHAPE, "allgather: geometry");
+        const NcclApi &nc = nccl_api();
+        if (!nc.ok) fail(HB_E_NCCL, "NCCL library not available");
+        ncclResult_t r = nc.AllGather(mine->d, all->d, mine->limbs() * c->N, ncclUint64, (ncclComm_t)comm, c->st);
+        if (r != ncclSuccess) fail(HB_E_NCCL, nc.GetErrorString(r));
+    });
+}
+int hb_nccl_unique_id(void *id128) {
+    const NcclApi &nc = nccl_api();
+    if (!nc.ok || !id128) return HB_E_NCCL;
+    ncclUniqueId id;
+    if (nc.GetUniqueId(&id) != ncclSuccess) return HB_E_NCCL;
+    std::memcpy(id128, &id, sizeof(id));
+    return HB_OK;
+}
+int hb_nccl_comm_init(hb_ctx *c, int nranks, int rank, const void *id128, void **comm) {
+    return guard(c, [&] {
+        const NcclApi &nc = nccl_api();
+        if (!nc.ok) fail(HB_E_NCCL, "NCCL library not available");
+        ncclUniqueId id; std::memcpy(&id, id128, sizeof(id));
+        ncclComm_t cm = nullptr;
+        ncclResult_t r = nc.CommInitRank(&cm, nranks, id, rank);
+        if (r != ncclSuccess) fail(HB_E_NCCL, nc.GetErrorString(r));
+        *comm = cm;
+    });
+}
+int hb_nccl_comm_destroy(void *comm) {
+    const NcclApi &nc = nccl_api();
+    if (!nc.ok) return HB_E_NCCL;
+    return nc.CommDestroy((ncclComm_t)comm) == ncclSuccess ? HB_OK : HB_E_NCCL;
+}
+
+} // extern "C"

@@ -1,0 +1,320 @@
+// Element-wise, base-conversion, automorphism, sampling and accumulate kernels (sm_100a).
+// Arrays are dense [instances][N] uint64 unless a stride is named; instance li uses prime
+// map.prime[li % map.n].  One thread handles one coefficient of one limb instance; a warp
+// touches 256 contiguous bytes per array, so every stream is fully coalesced.  Gathers through
+// ntt_perm stay inside an aligned 32-element block (the automorphism permutes aligned blocks
+// of the bit-reversed index as units), so they cost no extra sectors.
+#pragma once
+#include "modarith.cuh"
+
+namespace hb {
+
+#define HB_ELEM_IDX()                                              \
+    const int li = blockIdx.y;                                     \
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;           \
+    if (i >= N) return;                                            \
+    const PrimeConst m = pc[map.prime[li % map.n]];                \
+    const size_t off = (size_t)li * N + i;
+
+// out = a + b  (mode 0) | a - b (mode 1) | -a (mode 2)
+__global__ void k_addsub(u64 *__restrict__ out, const u64 *__restrict__ a, const u64 *__restrict__ b, LimbMap map, const PrimeConst *__restrict__ pc,
+                         int N, int mode) {
+    HB_ELEM_IDX();
+    u64 x = a[off];
+    if (mode == 0) out[off] = add_mod(x, b[off], m.q);
+    else if (mode == 1) out[off] = sub_mod(x, b[off], m.q);
+    else out[off] = x ? m.q - x : 0;
+}
+
+struct Scalars { u64 v[kMaxPrimes]; };
+// out = a * s[prime]
+__global__ void k_scalar_mul(u64 *__restrict__ out, const u64 *__restrict__ a, size_t a_outer, LimbMap map, const PrimeConst *__restrict__ pc, int N, Scalars s) {
+    const int li = blockIdx.y;
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= N) return;
+    const int pi = map.prime[li % map.n];
+    const PrimeConst m = pc[pi];
+    const size_t soff = (size_t)(li / map.n) * a_outer + (size_t)(li % map.n) * N + i;
+    out[(size_t)li * N + i] = mul_mod(a[soff], s.v[pi], m);
+}
+// multiplication by X^(N/2): +iu on the first half of an NTT-form limb, -iu on the second
+__global__ void k_mult_imag(u64 *__restrict__ out, const u64 *__restrict__ a, LimbMap map, const PrimeConst *__restrict__ pc, int N) {
+    HB_ELEM_IDX();
+    u64 r = mul_shoup(a[off], m.iu, m.iu_sh, m.q);
+    if (i >= N / 2) r = r ? m.q - r : 0;
+    out[off] = r;
+}
+// out = a (.) pt, pt limb = li % map.n
+__global__ void k_mul_pt(u64 *__restrict__ out, const u64 *__restrict__ a, const u64 *__restrict__ pt, LimbMap map, const PrimeConst *__restrict__ pc, int N) {
+    HB_ELEM_IDX();
+    out[off] = mul_mod(a[off], pt[(size_t)(li % map.n) * N + i], m);
+}
+// out = a (.) pa + b (.) pb
+__global__ void k_mul2_add(u64 *__restrict__ out, const u64 *__restrict__ a, const u64 *__restrict__ pa, const u64 *__restrict__ b, const u64 *__restrict__ pb,
+                           LimbMap map, const PrimeConst *__restrict__ pc, int N) {
+    HB_ELEM_IDX();
+    const size_t po = (size_t)(li % map.n) * N + i;
+    Acc128 s; s.zero();
+    s.mad(a[off], pa[po]); s.mad(b[off], pb[po]);
+    out[off] = barrett128(s.hi, s.lo, m);
+}
+// tensor product, optional accumulation.  grid.y = batch * n; x, y: [batch][2][n][N]; d: [batch][3][n][N]
+__global__ void k_tensor(u64 *__restrict__ d, const u64 *__restrict__ x, const u64 *__restrict__ y, int n, LimbMap map, const PrimeConst *__restrict__ pc, int N,
+                         int accumulate) {
+    const int bl = blockIdx.y, b = bl / n, l = bl % n;
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= N) return;
+    const PrimeConst m = pc[map.prime[l]];
+    const size_t x0 = ((size_t)(b * 2) * n + l) * N + i, x1 = x0 + (size_t)n * N;
+    const size_t d0 = ((size_t)(b * 3) * n + l) * N + i, d1 = d0 + (size_t)n * N, d2 = d1 + (size_t)n * N;
+    const u64 b1 = x[x0], a1 = x[x1], b2 = y[x0], a2 = y[x1];
+    u64 r0 = mul_mod(b1, b2, m), r2 = mul_mod(a1, a2, m);
+    Acc128 s; s.zero(); s.mad(a1, b2); s.mad(a2, b1);
+    u64 r1 = barrett128(s.hi, s.lo, m);
+    if (accumulate) { r0 = add_mod(r0, d[d0], m.q); r1 = add_mod(r1, d[d1], m.q); r2 = add_mod(r2, d[d2], m.q); }
+    d[d0] = r0; d[d1] = r1; d[d2] = r2;
+}
+// out[li][i] = in[li][perm_g(i)]
+__global__ void k_permute(u64 *__restrict__ out, const u64 *__restrict__ in, u32 g, int logn, int N) {
+    const int li = blockIdx.y;
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= N) return;
+    out[(size_t)li * N + i] = in[(size_t)li * N + ntt_perm((u32)i, g, logn)];
+}
+// int64 coefficients -> residues of every limb instance (coefficient form)
+__global__ void k_reduce_i64(u64 *__restrict__ out, const i64 *__restrict__ coef, LimbMap map, const PrimeConst *__restrict__ pc, int N) {
+    HB_ELEM_IDX();
+    out[off] = reduce_i64(coef[i], m);
+}
+// x mod q for lazily summed residues
+__global__ void k_mod_reduce(u64 *__restrict__ a, LimbMap map, const PrimeConst *__restrict__ pc, int N) {
+    HB_ELEM_IDX();
+    a[off] = reduce_u64(a[off], m);
+}
+
+// ---------------- rescale ----------------
+// t[bp][l][i] = centred(last[bp][i]) mod q_l, l < level.  grid.y = nbp * level
+__global__ void k_rescale_prep(u64 *__restrict__ t, const u64 *__restrict__ last, int level, const PrimeConst *__restrict__ pc, int N) {
+    const int w = blockIdx.y, bp = w / level, l = w % level;
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= N) return;
+    const PrimeConst m = pc[l];
+    const u64 ql = pc[level].q;
+    const u64 r = last[(size_t)bp * N + i];
+    u64 v = reduce_u64(r, m);
+    if (r > (ql >> 1)) v = sub_mod(v, reduce_u64(ql, m), m.q);
+    t[(size_t)w * N + i] = v;
+}
+// out[bp][l] = (x[bp][l] - t[bp][l]) * q_level^-1 ; x has level+1 limbs per poly
+__global__ void k_rescale_fin(u64 *__restrict__ out, const u64 *__restrict__ x, const u64 *__restrict__ t, int level, const PrimeConst *__restrict__ pc, int N,
+                              Scalars qlinv) {
+    const int w = blockIdx.y, bp = w / level, l = w % level;
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= N) return;
+    const PrimeConst m = pc[l];
+    const u64 xv = x[((size_t)bp * (level + 1) + l) * N + i];
+    out[(size_t)w * N + i] = mul_mod(sub_mod(xv, t[(size_t)w * N + i], m.q), qlinv.v[l], m);
+}
+
+// ---------------- key switching ----------------
+// Per-level plan held in device memory.
+struct KsPlan {
+    int level, n, ne, nd, K;
+    int dt_count;                               // lifted (non-own) limbs over all digits
+    int dig_lo[8], dig_hi[8];                   // own limb range of each digit
+    int dt_start[8];                            // first compact entry of each digit
+    short dt_entry[8][kMaxPrimes];              // [digit][ext limb j] -> compact entry or -1 (own)
+    unsigned char ext_prime[kMaxPrimes];        // ext limb j -> prime index
+    u64 hat_inv[8][kMaxDigitLimbs], hat_inv_sh[8][kMaxDigitLimbs];
+    u64 hat_mod[8][kMaxDigitLimbs][kMaxPrimes]; // [digit][source][ext limb j]
+    u64 p_hat_inv[8], p_hat_inv_sh[8];          // ModDown: per special prime
+    u64 p_hat_mod[8][kMaxPrimes];               // [special k][q limb l]
+    u64 p_inv[kMaxPrimes];                      // P^-1 mod q_l
+};
+
+// ModUp: a_coef [batch][n][N] (coefficient form) -> dt [batch][dt_count][N] (coefficient form).
+// grid = (N/256, nd, batch)
+__global__ void k_modup(u64 *__restrict__ dt, const u64 *__restrict__ a_coef, const KsPlan *__restrict__ pl, const PrimeConst *__restrict__ pc, int N) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= N) return;
+    const int dg = blockIdx.y, b = blockIdx.z;
+    const int lo = pl->dig_lo[dg], hi = pl->dig_hi[dg], ns = hi - lo, n = pl->n, ne = pl->ne;
+    u64 y[kMaxDigitLimbs];
+#pragma unroll
+    for (int s = 0; s < kMaxDigitLimbs; ++s)
+        if (s < ns) y[s] = mul_shoup(a_coef[((size_t)b * n + lo + s) * N + i], pl->hat_inv[dg][s], pl->hat_inv_sh[dg][s], pc[lo + s].q);
+    u64 *o = dt + ((size_t)b * pl->dt_count + pl->dt_start[dg]) * N + i;
+    int e = 0;
+    for (int j = 0; j < ne; ++j) {
+        if (j >= lo && j < hi) continue;
+        const PrimeConst m = pc[pl->ext_prime[j]];
+        Acc128 s; s.zero();
+#pragma unroll
+        for (int k = 0; k < kMaxDigitLimbs; ++k)
+            if (k < ns) s.mad(y[k], pl->hat_mod[dg][k][j]);
+        o[(size_t)e * N] = barrett128(s.hi, s.lo, m);
+        ++e;
+    }
+}
+
+// Inner product with the switching key over Q_level u P.
+//   acc[b][p][j][i] = sum_dg digit_dg[j][perm_g(i)] * key[dg][p][prime(j)][i]
+// digit_dg[j] is a_ntt[j] for own limbs and dt[...] otherwise.  grid = (N/256, ne, batch)
+__global__ void k_ks_inner(u64 *__restrict__ acc, const u64 *__restrict__ a_ntt, size_t a_outer, const u64 *__restrict__ dt, const u64 *__restrict__ key, int key_primes,
+                           const KsPlan *__restrict__ pl, const PrimeConst *__restrict__ pc, u32 g, int logn, int N) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= N) return;
+    const int j = blockIdx.y, b = blockIdx.z;
+    const int pj = pl->ext_prime[j], nd = pl->nd, ne = pl->ne;
+    const PrimeConst m = pc[pj];
+    const u32 s = g ? ntt_perm((u32)i, g, logn) : (u32)i;
+    Acc128 s0, s1; s0.zero(); s1.zero();
+    for (int dg = 0; dg < nd; ++dg) {
+        const int en = pl->dt_entry[dg][j];
+        const u64 v = en < 0 ? a_ntt[(size_t)b * a_outer + (size_t)j * N + s] : dt[((size_t)b * pl->dt_count + en) * N + s];
+        const u64 *k0 = key + (((size_t)dg * 2) * key_primes + pj) * N + i;
+        s0.mad(v, k0[0]);
+        s1.mad(v, k0[(size_t)key_primes * N]);
+    }
+    acc[(((size_t)b * 2) * ne + j) * N + i] = barrett128(s0.hi, s0.lo, m);
+    acc[(((size_t)b * 2 + 1) * ne + j) * N + i] = barrett128(s1.hi, s1.lo, m);
+}
+
+// ModDown conversion: pcoef [bp][K][N] (special limbs, coefficient form) -> t [bp][n][N] (coefficient form)
+// grid = (N/256, 1, nbp)
+__global__ void k_moddown_conv(u64 *__restrict__ t, const u64 *__restrict__ pcoef, const KsPlan *__restrict__ pl, const PrimeConst *__restrict__ pc, int Lp1, int N) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= N) return;
+    const int bp = blockIdx.z, K = pl->K, n = pl->n;
+    u64 y[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k)
+        if (k < K) y[k] = mul_shoup(pcoef[((size_t)bp * K + k) * N + i], pl->p_hat_inv[k], pl->p_hat_inv_sh[k], pc[Lp1 + k].q);
+    for (int l = 0; l < n; ++l) {
+        const PrimeConst m = pc[l];
+        Acc128 s; s.zero();
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+            if (k < K) s.mad(y[k], pl->p_hat_mod[k][l]);
+        t[((size_t)bp * n + l) * N + i] = barrett128(s.hi, s.lo, m);
+    }
+}
+// out[b][p][l][i] = (acc[b][p][l][i] - t[b][p][l][i]) * P^-1 + add_p[b][l][perm_g(i)]
+// add0 / add1 may be null; perm applies when g != 0.  grid = (N/256, n, batch*2)
+__global__ void k_moddown_fin(u64 *__restrict__ out, size_t out_outer, const u64 *__restrict__ acc, const u64 *__restrict__ t, const u64 *__restrict__ add0,
+                              const u64 *__restrict__ add1, size_t add_outer, const KsPlan *__restrict__ pl, const PrimeConst *__restrict__ pc, u32 g, int logn, int N) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= N) return;
+    const int l = blockIdx.y, bp = blockIdx.z, b = bp >> 1, p = bp & 1;
+    const int n = pl->n, ne = pl->ne;
+    const PrimeConst m = pc[l];
+    u64 v = sub_mod(acc[((size_t)bp * ne + l) * N + i], t[((size_t)bp * n + l) * N + i], m.q);
+    v = mul_mod(v, pl->p_inv[l], m);
+    const u64 *ad = p ? add1 : add0;
+    if (ad) {
+        const u32 s = g ? ntt_perm((u32)i, g, logn) : (u32)i;
+        v = add_mod(v, ad[(size_t)b * add_outer + (size_t)l * N + s], m.q);
+    }
+    out[(size_t)b * out_outer + ((size_t)p * n + l) * N + i] = v;
+}
+
+// ---------------- ChaCha20 ----------------
+__device__ __forceinline__ u32 rotl32(u32 v, int c) { return __funnelshift_l(v, v, c); }
+#define HB_QR(a, b, c, d)                                   \
+    a += b; d ^= a; d = rotl32(d, 16); c += d; b ^= c; b = rotl32(b, 12); \
+    a += b; d ^= a; d = rotl32(d, 8);  c += d; b ^= c; b = rotl32(b, 7);
+struct ChaChaKey { u32 k[8]; };
+__device__ __forceinline__ void chacha_block(const ChaChaKey &key, u32 domain, u64 id, u32 counter, u32 (&o)[16]) {
+    u32 in[16] = {0x61707865u, 0x3320646eu, 0x79622d32u, 0x6b206574u, key.k[0], key.k[1], key.k[2], key.k[3], key.k[4], key.k[5], key.k[6], key.k[7],
+                  counter, domain, (u32)id, (u32)(id >> 32)};
+    u32 x0 = in[0], x1 = in[1], x2 = in[2], x3 = in[3], x4 = in[4], x5 = in[5], x6 = in[6], x7 = in[7];
+    u32 x8 = in[8], x9 = in[9], x10 = in[10], x11 = in[11], x12 = in[12], x13 = in[13], x14 = in[14], x15 = in[15];
+#pragma unroll
+    for (int r = 0; r < 10; ++r) {
+        HB_QR(x0, x4, x8, x12) HB_QR(x1, x5, x9, x13) HB_QR(x2, x6, x10, x14) HB_QR(x3, x7, x11, x15)
+        HB_QR(x0, x5, x10, x15) HB_QR(x1, x6, x11, x12) HB_QR(x2, x7, x8, x13) HB_QR(x3, x4, x9, x14)
+    }
+    o[0] = x0 + in[0]; o[1] = x1 + in[1]; o[2] = x2 + in[2]; o[3] = x3 + in[3]; o[4] = x4 + in[4]; o[5] = x5 + in[5]; o[6] = x6 + in[6]; o[7] = x7 + in[7];
+    o[8] = x8 + in[8]; o[9] = x9 + in[9]; o[10] = x10 + in[10]; o[11] = x11 + in[11]; o[12] = x12 + in[12]; o[13] = x13 + in[13]; o[14] = x14 + in[14]; o[15] = x15 + in[15];
+}
+// uniform residues: limb instance li (prime pi = map.prime[li]) coefficient c = (128-bit word (pi*N + c) of the stream) mod q.
+// One thread produces the four coefficients of one ChaCha block.  grid = (N/4/256, count)
+__global__ void k_uniform(u64 *__restrict__ out, LimbMap map, const PrimeConst *__restrict__ pc, int N, ChaChaKey key, u32 domain, u64 id) {
+    const int li = blockIdx.y;
+    const int t = blockIdx.x * blockDim.x + threadIdx.x;
+    if (t * 4 >= N) return;
+    const int pi = map.prime[li % map.n];
+    const PrimeConst m = pc[pi];
+    u32 o[16];
+    chacha_block(key, domain, id, (u32)(((u64)pi * N + (u64)t * 4) >> 2), o);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        u64 lo = (u64)o[4 * k] | ((u64)o[4 * k + 1] << 32), hi = (u64)o[4 * k + 2] | ((u64)o[4 * k + 3] << 32);
+        out[(size_t)li * N + t * 4 + k] = barrett128(hi, lo, m);
+    }
+}
+
+// ---------------- encrypt / decrypt / key generation ----------------
+// b = e - a*s + msg   (all NTT form).  grid.y = n limbs
+__global__ void k_encrypt(u64 *__restrict__ b, const u64 *__restrict__ a, const u64 *__restrict__ e, const u64 *__restrict__ s, const u64 *__restrict__ msg, LimbMap map,
+                          const PrimeConst *__restrict__ pc, int N) {
+    HB_ELEM_IDX();
+    const size_t so = (size_t)map.prime[li % map.n] * N + i;
+    u64 v = sub_mod(e[off], mul_mod(a[off], s[so], m), m.q);
+    b[off] = add_mod(v, msg[off], m.q);
+}
+// out[l] = b + a*s (+ d2*s^2) for limbs l < nl of entry `index`
+__global__ void k_decrypt(u64 *__restrict__ out, const u64 *__restrict__ ct, int n, int np, const u64 *__restrict__ s, const PrimeConst *__restrict__ pc, int N) {
+    const int l = blockIdx.y;
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= N) return;
+    const PrimeConst m = pc[l];
+    const u64 sv = s[(size_t)l * N + i];
+    u64 v = add_mod(ct[(size_t)l * N + i], mul_mod(ct[((size_t)n + l) * N + i], sv, m), m.q);
+    if (np == 3) v = add_mod(v, mul_mod(ct[((size_t)2 * n + l) * N + i], mul_mod(sv, sv, m), m), m.q);
+    out[(size_t)l * N + i] = v;
+}
+// switching-key body: b = e - a*s + [prime in digit] * (P mod q) * s',  s' = s^2 (g == 0) or s o perm_g.
+// grid.y = nprimes; one digit per launch.
+__global__ void k_keygen(u64 *__restrict__ b, const u64 *__restrict__ a, const u64 *__restrict__ e, const u64 *__restrict__ s, const PrimeConst *__restrict__ pc, int N,
+                         int logn, u32 g, int dig_lo, int dig_hi, Scalars pmod) {
+    const int pi = blockIdx.y;
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= N) return;
+    const PrimeConst m = pc[pi];
+    const size_t off = (size_t)pi * N + i;
+    u64 v = sub_mod(e[off], mul_mod(a[off], s[off], m), m.q);
+    if (pi >= dig_lo && pi < dig_hi) {
+        u64 sp;
+        if (g == 0) sp = mul_mod(s[off], s[off], m);
+        else sp = s[(size_t)pi * N + ntt_perm((u32)i, g, logn)];
+        v = add_mod(v, mul_mod(sp, pmod.v[pi], m), m.q);
+    }
+    b[off] = v;
+}
+
+// ---------------- fused plaintext-matmul accumulate ----------------
+// out[p][l][i] = sum_k pre[k][p][l][i] * pt[l][perm_{g_k}(i)]     (scale Delta^2, no rescale)
+// grid = (N/256, 2*n).  The 128-bit accumulator is folded every 64 terms.
+__global__ void k_matmul_acc(u64 *__restrict__ out, const u64 *__restrict__ pre, int kcount, const u64 *__restrict__ pt, const u32 *__restrict__ gal, int n,
+                             LimbMap map, const PrimeConst *__restrict__ pc, int logn, int N) {
+    const int pl = blockIdx.y, l = pl % n;
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= N) return;
+    const PrimeConst m = pc[map.prime[l]];
+    const u64 *ptl = pt + (size_t)l * N;
+    const size_t kstride = (size_t)2 * n * N;
+    const u64 *p = pre + (size_t)pl * N + i;
+    u64 total = 0;
+    Acc128 s; s.zero();
+    for (int k = 0; k < kcount; ++k) {
+        const u32 g = __ldg(gal + k);
+        const u64 w = g == 1 ? ptl[i] : ptl[ntt_perm((u32)i, g, logn)];
+        s.mad(p[(size_t)k * kstride], w);
+        if ((k & 63) == 63) { total = add_mod(total, barrett128(s.hi, s.lo, m), m.q); s.zero(); }
+    }
+    total = add_mod(total, barrett128(s.hi, s.lo, m), m.q);
+    out[(size_t)pl * N + i] = total;
+}
+
+} // namespace hb

@@ -1,0 +1,83 @@
+// Device-side modular arithmetic for word-sized primes q < 2^61 (sm_100a).
+// All helpers are exact: whichever reduction strategy a kernel uses (Shoup with a
+// precomputed quotient, 128-bit Barrett, lazy ranges), stored results are the
+// canonical residues in [0, q).
+#pragma once
+#include <cstdint>
+#include <cuda_runtime.h>
+
+namespace hb {
+
+using u32 = uint32_t;
+using u64 = unsigned long long;
+using i64 = long long;
+
+constexpr int kMaxPrimes = 32;   // Q limbs + special limbs
+constexpr int kMaxDigitLimbs = 8; // alpha upper bound
+constexpr int kMaxList = 96;     // limb instances named by one launch
+
+// Per-prime constants, one array per context in global memory.
+struct PrimeConst {
+    u64 q;
+    u64 mu_hi, mu_lo;   // floor(2^128 / q)
+    u64 n_inv, n_inv_sh; // N^-1 mod q and its Shoup companion
+    u64 iu, iu_sh;      // psi^(N/2): the image of the imaginary unit
+    u64 pad;
+};
+
+// Limb instances of a launch: instance li (0 <= li < count) uses prime[li % n].
+struct LimbMap {
+    int n;
+    unsigned char prime[kMaxList];
+};
+
+__device__ __forceinline__ u64 mul_hi(u64 a, u64 b) { return __umul64hi(a, b); }
+
+// x*w mod q in [0, 2q) for any x < 2^64, w < q, wsh = floor(w * 2^64 / q)
+__device__ __forceinline__ u64 mul_shoup_lazy(u64 x, u64 w, u64 wsh, u64 q) {
+    return x * w - mul_hi(x, wsh) * q;
+}
+__device__ __forceinline__ u64 mul_shoup(u64 x, u64 w, u64 wsh, u64 q) {
+    u64 r = mul_shoup_lazy(x, w, wsh, q);
+    return r >= q ? r - q : r;
+}
+// (z1:z0) mod q, any 128-bit input.  The quotient estimate is low by at most 4.
+__device__ __forceinline__ u64 barrett128(u64 z1, u64 z0, const PrimeConst &m) {
+    u64 qh = z1 * m.mu_hi + mul_hi(z1, m.mu_lo) + mul_hi(z0, m.mu_hi);
+    u64 r = z0 - qh * m.q;
+    u64 q4 = m.q << 2, q2 = m.q << 1;
+    if (r >= q4) r -= q4;
+    if (r >= q2) r -= q2;
+    if (r >= m.q) r -= m.q;
+    return r;
+}
+__device__ __forceinline__ u64 mul_mod(u64 a, u64 b, const PrimeConst &m) {
+    return barrett128(mul_hi(a, b), a * b, m);
+}
+__device__ __forceinline__ u64 add_mod(u64 a, u64 b, u64 q) { u64 s = a + b; return s >= q ? s - q : s; }
+__device__ __forceinline__ u64 sub_mod(u64 a, u64 b, u64 q) { return a >= b ? a - b : a + q - b; }
+__device__ __forceinline__ u64 reduce_u64(u64 x, const PrimeConst &m) { return barrett128(0, x, m); }
+__device__ __forceinline__ u64 reduce_i64(i64 v, const PrimeConst &m) {
+    if (v >= 0) return reduce_u64((u64)v, m);
+    u64 r = reduce_u64((u64)(-(v + 1)), m);
+    return m.q - 1 - r;
+}
+// 128-bit accumulator for lazy sums of products
+struct Acc128 {
+    u64 lo, hi;
+    __device__ __forceinline__ void zero() { lo = 0; hi = 0; }
+    __device__ __forceinline__ void mad(u64 a, u64 b) {
+        u64 pl = a * b, ph = mul_hi(a, b);
+        lo += pl; hi += ph + (lo < pl);
+    }
+};
+
+// index of the source slot of the automorphism X -> X^g on an NTT-form limb:
+//   out[i] = in[ntt_perm(i)], exponents 2*bitrev(i)+1 multiply by g modulo 2N
+__device__ __forceinline__ u32 ntt_perm(u32 i, u32 g, int logn) {
+    u32 e = ((__brev(i) >> (32 - logn)) << 1) | 1u;
+    u32 ej = (g * e) & ((2u << logn) - 1u);
+    return __brev(ej >> 1) >> (32 - logn);
+}
+
+} // namespace hb

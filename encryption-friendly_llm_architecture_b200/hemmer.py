@@ -78,6 +78,10 @@ class Hemmer:
     def _call(self, name, *args, n_out=1):
         outs = [C.c_void_p() for _ in range(n_out)]
         rc = self._fn(name)(self.h, *args, *[C.byref(o) for o in outs])
+        if rc != 0 and hasattr(self.dll, self.prefix + "last_error"):
+            f = self._fn("last_error")
+            f.restype = C.c_char_p
+            raise HBError(rc, f().decode())
         self.lib._chk(rc)
         hs = [Handle(self.lib, o, "ct") for o in outs]
         return hs[0] if n_out == 1 else hs
@@ -125,13 +129,11 @@ class Hemmer:
         a.ct = self.lib.add(a.ct, b.ct)
 
     def single_cc_matmul(self, a, b, target_level=4):
-        ct = self._call("matmul_cc", a.ct.ptr, C.c_int(a.rows), C.c_int(a.cols), b.ct.ptr, C.c_int(b.rows), C.c_int(b.cols),
-                        C.c_int(a.width), C.c_int(target_level))
+        ct = self._call("matmul_cc", a.ct.ptr, *self._shp(a), b.ct.ptr, *self._shp(b), C.c_int(target_level))
         return CtxtTensor(ct, a.rows, b.cols, a.width)
 
     def packed_matmul(self, a, b, target_level=4):
-        ct = self._call("packed_matmul", a.ct.ptr, C.c_int(a.rows), C.c_int(a.cols), b.ct.ptr, C.c_int(b.rows), C.c_int(b.cols),
-                        C.c_int(a.width), C.c_int(target_level))
+        ct = self._call("packed_matmul", a.ct.ptr, *self._shp(a), b.ct.ptr, *self._shp(b), C.c_int(target_level))
         return CtxtTensor(ct, a.rows, b.cols, a.width)
 
     def transpose_inplace(self, t, target_level=0):

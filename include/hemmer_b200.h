@@ -59,6 +59,8 @@ void hb_ctx_destroy(hb_ctx *ctx);
 const char *hb_last_error(const hb_ctx *ctx);
 /* getPrimeList / scale factors -- Context.hpp:203-206.  primes[L+1+K], scales[L+1]. */
 int hb_ctx_info(const hb_ctx *ctx, uint64_t *primes, double *scales);
+/* getDegree / getEncryptionLevel -- Context.hpp:169-194 */
+int hb_ctx_dims(const hb_ctx *ctx, int *log_n, int *max_level, int *num_special);
 /* CudaTools::cudaDeviceSynchronize -- HEaaN/device/CudaTools.hpp:24 */
 int hb_sync(hb_ctx *ctx);
 /* bytes currently held by the context's device pool (cudaMemGetInfo print in bert-matmul.cpp:240-243) */
@@ -130,6 +132,11 @@ int hb_mod_reduce(hb_ctx *ctx, hb_ct *a);
 /* Multi-GPU: sum (or gather) ciphertext tiles across ranks.  The communicator is created by the
  * caller (ncclComm_t passed as void*); replaces HEMMer::ncclAllReduceWrapper (HEMMer.cpp:2625-2635)
  * and TransformerBlock::ncclReduceWrapper* (TransformerBlock.cpp:11100-11154). */
+/* communicator set-up: ncclGetUniqueId + ncclCommInitRank as in HEMMer.cpp:143-153 (the 128-byte id
+ * travels between ranks by whatever channel the launcher has; the reference uses MPI_Bcast) */
+int hb_nccl_unique_id(void *id128);
+int hb_nccl_comm_init(hb_ctx *ctx, int nranks, int rank, const void *id128, void **comm);
+int hb_nccl_comm_destroy(void *comm);
 int hb_allreduce_sum(hb_ctx *ctx, hb_ct *a, void *nccl_comm);
 int hb_allgather(hb_ctx *ctx, const hb_ct *mine, hb_ct *all, void *nccl_comm);
 

@@ -886,8 +886,13 @@ struct Evaluator {
         }
         return r;
     }
-    // HomEvaluator::mult(ct, ct) (HomEvaluator.hpp:311-312)
-    Ct mul(const Ct &x, const Ct &y) { return rescale(relin(tensor(x, y))); }
+    // HomEvaluator::mult(ct, ct) (HomEvaluator.hpp:311-312); operands of different level are aligned
+    // by bringing the higher one down first (used by multPackedMatMat, MatrixUtils.cpp:1155)
+    Ct mul(const Ct &x, const Ct &y) {
+        if (x.level > y.level) return mul(level_down(x, y.level), y);
+        if (y.level > x.level) return mul(x, level_down(y, x.level));
+        return rescale(relin(tensor(x, y)));
+    }
 
     // automorphism + key switch; g = galois element
     Ct apply_galois(const Ct &x, u64 g) {

@@ -1,0 +1,158 @@
+"""Scenarios shared by the CPU (oracle-only) and GPU (CUDA vs oracle) tests.
+
+Each scenario drives one library through the HEMMer call surface on seeded inputs and returns
+``(exports, err)``: the raw ciphertext residues of every result (for bit-exact comparison between
+libraries) and the max-abs difference between the decrypted results and the float64 computation.
+"""
+import numpy as np
+
+
+def tile_dim(lib):
+    return int(round((lib.slots // 2) ** 0.5))
+
+
+def _mats(seed, d, n, lo=-1.0, hi=1.0):
+    rng = np.random.default_rng(seed)
+    return [rng.uniform(lo, hi, (d, d)) for _ in range(n)]
+
+
+def sc_transforms(lib, H):
+    d = tile_dim(lib)
+    A, B = _mats(100, d, 2)
+    a = H.encrypt2(A, B, nonce=1)
+    s, t = H.sigma(a), H.tau(a)
+    S, T = H.decrypt2(s), H.decrypt2(t)
+    sig = lambda M: np.stack([np.roll(M[r], -r) for r in range(d)])
+    tau = lambda M: np.stack([np.roll(M[:, c], -c) for c in range(d)], axis=1)
+    err = max(np.abs(S[0] - sig(A)).max(), np.abs(S[1] - sig(B)).max(), np.abs(T[0] - tau(A)).max(), np.abs(T[1] - tau(B)).max())
+    tr = H.encrypt2(A, B, nonce=2)
+    H.transpose_inplace(tr)
+    R = H.decrypt2(tr)
+    err = max(err, np.abs(R[0] - A.T).max(), np.abs(R[1] - B.T).max())
+    return [lib.ct_export(x.ct) for x in (s, t, tr)], err
+
+
+def sc_ccmm_single_tile(lib, H, target=2):
+    """BASELINE config 1 shape: one d x d tile per ciphertext, half of the slots used."""
+    d = tile_dim(lib)
+    A, B = _mats(101, d, 2)
+    a, b = H.encrypt(A, nonce=3), H.encrypt(B, nonce=4)
+    c = H.single_cc_matmul(a, b, target)
+    assert lib.ct_meta(c.ct)[0] == target
+    return [lib.ct_export(c.ct)], np.abs(H.decrypt(c) - A @ B).max()
+
+
+def sc_ccmm_two_tiles(lib, H, target=2):
+    d = tile_dim(lib)
+    A, A2, B, B2 = _mats(102, d, 4)
+    a, b = H.encrypt2(A, A2, nonce=5), H.encrypt2(B, B2, nonce=6)
+    c = H.single_cc_matmul(a, b, target)
+    D = H.decrypt2(c)
+    return [lib.ct_export(c.ct)], max(np.abs(D[0] - A @ B).max(), np.abs(D[1] - A2 @ B2).max())
+
+
+def sc_pcmm_reuse(lib, H, target=2):
+    """matMulPre + matMulReUse + repack_notBTS on four K-tiles and two output tiles (bert-matmul.cpp:251-293)."""
+    d = tile_dim(lib)
+    X = _mats(103, d, 4)
+    rngw = np.random.default_rng(104)
+    W = [[rngw.normal(0, 0.02, (d, d)) for _ in range(4)] for _ in range(2)]
+    x01, x23 = H.encrypt2(X[0], X[1], nonce=7), H.encrypt2(X[2], X[3], nonce=8)
+    packed = H.complex_packing(x01, x23)
+    pre = H.matmul_pre(packed, target)
+    assert lib.ct_meta(pre)[:3] == (target + 1, 2, d)
+    outs = []
+    for j in range(2):
+        w = H.encode_diagonal_to_row4(*W[j], level=target + 1)
+        outs.append(H.matmul_reuse(pre, w))
+    exports = [lib.ct_export(pre)] + [lib.ct_export(o.ct) for o in outs]
+    # semantic: 2*Re(out_j) left half + right half = sum_k X_k W_jk
+    err = 0.0
+    for j in range(2):
+        z = lib.decrypt(outs[j].ct).reshape(d, 2 * d)
+        got = 2 * (z[:, :d].real + z[:, d:].real)
+        err = max(err, np.abs(got - sum(X[k] @ W[j][k] for k in range(4))).max())
+    rp = H.repack_not_bts(outs[0], outs[1])
+    exports.append(lib.ct_export(rp.ct))
+    return exports, err
+
+
+def sc_cc_reuse(lib, H, target=2):
+    """matMulPre / matMulPreRev / matMulCCReUse: encrypted right operand with shared left shifts."""
+    d = tile_dim(lib)
+    A, A2, B, B2 = _mats(105, d, 4)
+    a, b = H.encrypt2(A, A2, nonce=9), H.encrypt2(B, B2, nonce=10)
+    pre = H.matmul_pre(a, target)
+    tb = H.matmul_pre_rev(b, target)
+    c = H.matmul_cc_reuse(pre, tb)
+    assert lib.ct_meta(c.ct)[3] == 2  # relinearised, not rescaled
+    z = lib.decrypt(c.ct).real.reshape(d, 2 * d)
+    err = max(np.abs(z[:, :d] - A @ B).max(), np.abs(z[:, d:] - A2 @ B2).max())
+    return [lib.ct_export(tb.ct), lib.ct_export(c.ct)], err
+
+
+def sc_packed(lib, H, target=2):
+    """complexPacking* + packedMatMul + repackCC on a pair of tiles (TransformerBlock.cpp:2474-2482 pattern)."""
+    d = tile_dim(lib)
+    A, A2, B, B2 = _mats(106, d, 4)
+    a, b = H.encrypt2(A, A2, nonce=11), H.encrypt2(B, B2, nonce=12)
+    H.complex_packing_inplace(a)
+    H.complex_packing_row_inplace(b)
+    c = H.packed_matmul(a, b, target)
+    r = H.repack_cc(c)
+    D = H.decrypt2(r)
+    err = max(np.abs(D[0] - A @ B).max(), np.abs(D[1] - A2 @ B2).max())
+    return [lib.ct_export(a.ct), lib.ct_export(b.ct), lib.ct_export(c.ct), lib.ct_export(r.ct)], err
+
+
+def sc_packed_reuse(lib, H, target=2):
+    """packedMatMulPre / PreRot / PreRev / CCReuse and splitInTwo (bert-matmul-backward.cpp:317-384 pattern)."""
+    d = tile_dim(lib)
+    A, A2, B, B2 = _mats(107, d, 4)
+    a, b = H.encrypt2(A, A2, nonce=13), H.encrypt2(B, B2, nonce=14)
+    H.complex_packing_inplace(a)
+    H.complex_packing_row_inplace(b)
+    sa = H.packed_matmul_pre(a, target)
+    pre = H.packed_matmul_pre_rot(sa, target)
+    tb = H.packed_matmul_pre_rev(b, target)
+    c = H.packed_matmul_cc_reuse(pre, tb)
+    r = H.repack_cc(c)
+    D = H.decrypt2(r)
+    err = max(np.abs(D[0] - A @ B).max(), np.abs(D[1] - A2 @ B2).max())
+    s1, s2 = H.split_in_two(r)
+    D1, D2 = H.decrypt2(s1), H.decrypt2(s2)
+    err = max(err, np.abs(D1[0] - A @ B).max(), np.abs(D1[1] - A @ B).max(), np.abs(D2[0] - A2 @ B2).max(), np.abs(D2[1] - A2 @ B2).max())
+    return [lib.ct_export(x) for x in (pre, tb.ct, c.ct, s1.ct, s2.ct)], err
+
+
+def sc_transpose_packing(lib, H, target=0):
+    d = tile_dim(lib)
+    A, A2 = _mats(108, d, 2)
+    a = H.encrypt2(A, A2, nonce=15)
+    H.transpose_complex_packing_inplace(a, target)
+    z = lib.decrypt(a.ct).reshape(d, 2 * d)
+    # even columns keep value - i * (next column), then the transpose of each tile
+    def fold(M):
+        F = np.zeros((d, d), dtype=complex)
+        F[:, 0::2] = M[:, 0::2] - 1j * M[:, 1::2]
+        F[:, 1::2] = F[:, 0::2]
+        return F.T
+    err = max(np.abs(z[:, :d] - fold(A)).max(), np.abs(z[:, d:] - fold(A2)).max())
+    b = H.encrypt2(A, A2, nonce=16)
+    c = H.complex_packing_rev(b, b)
+    zz = lib.decrypt(c.ct)
+    base = np.concatenate([A, A2], axis=1).reshape(-1)
+    err = max(err, np.abs(zz - (base - 1j * base)).max())
+    return [lib.ct_export(a.ct), lib.ct_export(c.ct)], err
+
+
+SCENARIOS = {
+    "transforms": sc_transforms,
+    "ccmm_single_tile": sc_ccmm_single_tile,
+    "ccmm_two_tiles": sc_ccmm_two_tiles,
+    "pcmm_reuse": sc_pcmm_reuse,
+    "cc_reuse": sc_cc_reuse,
+    "packed": sc_packed,
+    "packed_reuse": sc_packed_reuse,
+    "transpose_packing": sc_transpose_packing,
+}

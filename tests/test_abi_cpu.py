@@ -1,0 +1,43 @@
+"""The C-ABI library loads without a GPU and exports every symbol the public header declares."""
+import ctypes
+import os
+import re
+
+from conftest import ROOT
+
+
+def _declared(header):
+    text = open(header).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(hb_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_library_exports_header_symbols(pkg):
+    names = _declared(os.path.join(ROOT, "include", "hemmer_b200.h"))
+    assert len(names) > 40
+    dll = ctypes.CDLL(pkg.CUDA_LIB)
+    missing = [n for n in names if not hasattr(dll, n)]
+    assert not missing, missing
+
+
+def test_hellm_layer_exports(pkg):
+    ctypes.CDLL(pkg.CUDA_LIB, mode=ctypes.RTLD_GLOBAL)
+    dll = ctypes.CDLL(pkg.HELLM_LIB)
+    for n in ("create", "destroy", "matmul_cc", "packed_matmul", "matmul_pre", "matmul_reuse", "matmul_pre_rev", "matmul_cc_reuse",
+              "packed_matmul_pre", "packed_matmul_pre_rot", "packed_matmul_pre_rev", "packed_matmul_cc_reuse", "transpose", "sigma", "tau",
+              "complex_packing", "complex_packing_row", "transpose_complex_packing", "split_in_two", "repack_cc", "complex_packing2",
+              "complex_packing_rev", "repack_not_bts"):
+        assert hasattr(dll, "hb_hemmer_" + n), n
+
+
+def test_no_gpu_means_loud_failure(pkg):
+    """Without a CUDA device the product path must refuse to run rather than fall back."""
+    import torch
+    if torch.cuda.is_available():
+        return
+    try:
+        pkg.open_gpu()
+    except pkg.HBError as e:
+        assert e.code != 0
+    else:
+        raise AssertionError("context creation succeeded without a GPU")

@@ -1,0 +1,125 @@
+"""CUDA library vs CPU oracle through the C ABI: ciphertext residues must be bit-identical."""
+import numpy as np
+import pytest
+
+import cases
+from conftest import rand_ct_residues
+
+pytestmark = pytest.mark.gpu
+TOL = 2.0 ** -14
+
+
+def _same(a, b, what=""):
+    assert a.shape == b.shape, what
+    if not np.array_equal(a, b):
+        bad = np.argwhere(a != b)
+        raise AssertionError(f"{what}: {len(bad)} of {a.size} residues differ, first at {bad[0].tolist()}")
+
+
+def _pairs(request, size):
+    return request.getfixturevalue(f"gpu_{size}"), request.getfixturevalue(f"orc_{size}")
+
+
+@pytest.mark.parametrize("size", ["small", "mid", "full"])
+def test_context_tables(request, size):
+    g, o = _pairs(request, size)
+    assert np.array_equal(g.primes, o.primes)
+    assert np.array_equal(g.scales, o.scales)
+
+
+@pytest.mark.parametrize("size", ["small", "mid", "full"])
+def test_ntt_roundtrip_and_parity(request, size):
+    g, o = _pairs(request, size)
+    lvl = g.L
+    data = rand_ct_residues(g, lvl, 2, 3, seed=1)
+    cg, co = g.ct_create(lvl, 2, 3), o.ct_create(lvl, 2, 3)
+    g.ct_import(cg, data); o.ct_import(co, data)
+    g.ntt(cg); o.ntt(co)
+    _same(g.ct_export(cg), o.ct_export(co), "forward NTT")
+    g.ntt(cg, inverse=True)
+    _same(g.ct_export(cg), data, "inverse NTT round trip")
+    g.ct_import(cg, data); g.ntt(cg, inverse=True); o.ct_import(co, data); o.ntt(co, inverse=True)
+    _same(g.ct_export(cg), o.ct_export(co), "inverse NTT")
+
+
+@pytest.mark.parametrize("size", ["small", "mid", "full"])
+def test_keys_and_encryption(request, size):
+    g, o = _pairs(request, size)
+    for lib in (g, o):
+        lib.gen_rot_keys([1, -3])
+    for gal in (0, g.galois(1), g.galois(-3), 2 * g.N - 1):
+        _same(g.evk_export(gal), o.evk_export(gal), f"switching key {gal}")
+    rng = np.random.default_rng(2)
+    z = rng.uniform(-1, 1, g.slots) + 1j * rng.uniform(-1, 1, g.slots)
+    for lvl in (g.L, 2):
+        pg, po = g.encode(z, lvl), o.encode(z, lvl)
+        _same(g.pt_export(pg), o.pt_export(po), "encode")
+        assert np.array_equal(g.decode(pg), o.decode(po))
+        cg, co = g.encrypt(pg, 77), o.encrypt(po, 77)
+        _same(g.ct_export(cg), o.ct_export(co), "encrypt")
+        dg, do = g.decrypt(cg), o.decrypt(co)
+        assert np.array_equal(dg, do) and np.abs(dg - z).max() < 1e-6
+
+
+def _primitive_sweep(g, o, lvl, batch, seed):
+    data = rand_ct_residues(g, lvl, 2, batch, seed)
+    data2 = rand_ct_residues(g, lvl, 2, batch, seed + 1)
+    cg, co = g.ct_create(lvl, 2, batch), o.ct_create(lvl, 2, batch)
+    cg2, co2 = g.ct_create(lvl, 2, batch), o.ct_create(lvl, 2, batch)
+    g.ct_import(cg, data); o.ct_import(co, data); g.ct_import(cg2, data2); o.ct_import(co2, data2)
+    z = np.random.default_rng(seed).uniform(-1, 1, g.slots)
+    pg, po = g.encode(z, lvl), o.encode(z, lvl)
+    ops = [("add", lambda L, a, b, p: L.add(a, b)), ("sub", lambda L, a, b, p: L.sub(a, b)), ("negate", lambda L, a, b, p: L.negate(a)),
+           ("mult_imag", lambda L, a, b, p: L.mult_imag(a)), ("mult_int", lambda L, a, b, p: L.mult_int(a, -12345)),
+           ("mul_pt_norescale", lambda L, a, b, p: L.mul_pt_norescale(a, p)), ("tensor", lambda L, a, b, p: L.tensor(a, b)),
+           ("conjugate", lambda L, a, b, p: L.conjugate(a))]
+    for s in (1, 128 % g.slots, 4096 % g.slots):
+        ops.append((f"rotate{s}", lambda L, a, b, p, s=s: L.rotate(a, s)))
+    if lvl >= 1:
+        ops += [("mul_pt", lambda L, a, b, p: L.mul_pt(a, p)), ("mul", lambda L, a, b, p: L.mul(a, b)),
+                ("tensor+relin", lambda L, a, b, p: L.relin(L.tensor(a, b))), ("rescale", lambda L, a, b, p: L.rescale(L.mul_pt_norescale(a, p))),
+                ("level_down", lambda L, a, b, p: L.level_down(a, max(lvl - 2, 0)))]
+    for name, f in ops:
+        rg, ro = f(g, cg, cg2, pg), f(o, co, co2, po)
+        assert g.ct_meta(rg) == o.ct_meta(ro), name
+        _same(g.ct_export(rg), o.ct_export(ro), f"{name} @ level {lvl}")
+
+
+@pytest.mark.parametrize("size,levels,batch", [("small", (8, 5, 2, 1, 0), 2), ("mid", (8, 4, 1), 2), ("full", (12, 8, 4, 1), 2)])
+def test_primitive_sweep(request, size, levels, batch):
+    g, o = _pairs(request, size)
+    for lib in (g, o):
+        lib.gen_rot_keys([1, 128 % g.slots, 4096 % g.slots])
+    for lvl in levels:
+        _primitive_sweep(g, o, lvl, batch, seed=10 + lvl)
+
+
+@pytest.mark.parametrize("size", ["small", "mid"])
+@pytest.mark.parametrize("name", sorted(cases.SCENARIOS))
+def test_schedule_parity(request, pkg, size, name):
+    g, o = _pairs(request, size)
+    Hg, Ho = pkg.open_hemmer(g), pkg.Hemmer(o)
+    eg, err_g = cases.SCENARIOS[name](g, Hg)
+    eo, err_o = cases.SCENARIOS[name](o, Ho)
+    assert len(eg) == len(eo)
+    for k, (a, b) in enumerate(zip(eg, eo)):
+        _same(a, b, f"{name}[{k}]")
+    assert err_g < TOL and err_g == err_o
+
+
+def test_error_codes(pkg, gpu_small):
+    g = gpu_small
+    a = g.ct_create(3, 2, 1)
+    b = g.ct_create(3, 3, 1)
+    with pytest.raises(pkg.HBError) as e:
+        g.sub(a, b)
+    assert e.value.code == -3
+    with pytest.raises(pkg.HBError) as e:
+        g.rotate(a, 17)  # no key for this step
+    assert e.value.code == -4
+    with pytest.raises(pkg.HBError) as e:
+        g.rescale(a)
+    assert e.value.code == -3
+    with pytest.raises(pkg.HBError) as e:
+        g.mul_pt(a, g.encode(np.zeros(4), 5))
+    assert e.value.code == -2
