@@ -106,6 +106,7 @@ struct hb_ctx {
     std::map<int, KsPlan *> plans; // device copies
     ChaChaKey ckey{};
     int N = 0, logn = 0, L = 0, K = 0, nprimes = 0;
+    unsigned long long launches = 0; // kernels launched by this context
 
     LimbMap qmap(int level) const { LimbMap m{}; m.n = level + 1; for (int i = 0; i <= level; ++i) m.prime[i] = (unsigned char)i; return m; }
     LimbMap allmap() const { LimbMap m{}; m.n = nprimes; for (int i = 0; i < nprimes; ++i) m.prime[i] = (unsigned char)i; return m; }
@@ -113,6 +114,7 @@ struct hb_ctx {
     u64 *alloc_limbs(size_t limbs) { return (u64 *)pool.get(limbs * (size_t)N * 8); }
 };
 
+#define LAUNCH(c) ((c)->launches++, 0)
 struct hb_ct { hb_ctx *ctx; int level, np, batch, spow; u64 *d; size_t limbs() const { return (size_t)batch * np * (level + 1); } };
 struct hb_pt { hb_ctx *ctx; int level, spow; u64 *d; };
 
@@ -137,6 +139,7 @@ struct Tmp { // pool buffer released at scope exit
 };
 
 void ntt(hb_ctx *c, const u64 *src, size_t so, u64 *dst, size_t dof, int count, const LimbMap &m, bool inv) {
+    c->launches += (count == 0) ? 0 : (c->logn == 16 ? 2 : 1);
     CK(launch_ntt(c->st, src, so, dst, dof, count, m, c->pc, c->tb, c->logn, inv));
 }
 void ntt_inplace(hb_ctx *c, u64 *d, int count, const LimbMap &m, bool inv) { ntt(c, d, (size_t)m.n * c->N, d, (size_t)m.n * c->N, count, m, inv); }
@@ -229,14 +232,14 @@ void keyswitch(hb_ctx *c, const u64 *a, size_t a_outer, int level, int batch, co
     const unsigned gx = (unsigned)((N + 255) / 256);
     Tmp acoef(c, (size_t)batch * n), dt(c, (size_t)batch * d.dt_count), acc(c, (size_t)batch * 2 * ne), pco(c, (size_t)batch * 2 * K), t(c, (size_t)batch * 2 * n);
     ntt(c, a, a_outer, acoef.p, (size_t)n * N, batch * n, qm, true);
-    k_modup<<<dim3(gx, d.nd, batch), 256, 0, c->st>>>(dt.p, acoef.p, pl, c->pc, N);
+    LAUNCH(c), k_modup<<<dim3(gx, d.nd, batch), 256, 0, c->st>>>(dt.p, acoef.p, pl, c->pc, N);
     ntt_inplace(c, dt.p, batch * d.dt_count, d.dtmap, false);
-    k_ks_inner<<<dim3(gx, ne, batch), 256, 0, c->st>>>(acc.p, a, a_outer, dt.p, key.d, c->nprimes, pl, c->pc, g, c->logn, N);
+    LAUNCH(c), k_ks_inner<<<dim3(gx, ne, batch), 256, 0, c->st>>>(acc.p, a, a_outer, dt.p, key.d, c->nprimes, pl, c->pc, g, c->logn, N);
     LimbMap pm{}; pm.n = K; for (int k = 0; k < K; ++k) pm.prime[k] = (unsigned char)(c->L + 1 + k);
     ntt(c, acc.p + (size_t)n * N, (size_t)ne * N, pco.p, (size_t)K * N, batch * 2 * K, pm, true);
-    k_moddown_conv<<<dim3(gx, 1, batch * 2), 256, 0, c->st>>>(t.p, pco.p, pl, c->pc, c->L + 1, N);
+    LAUNCH(c), k_moddown_conv<<<dim3(gx, 1, batch * 2), 256, 0, c->st>>>(t.p, pco.p, pl, c->pc, c->L + 1, N);
     ntt_inplace(c, t.p, batch * 2 * n, qm, false);
-    k_moddown_fin<<<dim3(gx, n, batch * 2), 256, 0, c->st>>>(out, out_outer, acc.p, t.p, add0, add1, add_outer, pl, c->pc, g, c->logn, N);
+    LAUNCH(c), k_moddown_fin<<<dim3(gx, n, batch * 2), 256, 0, c->st>>>(out, out_outer, acc.p, t.p, add0, add1, add_outer, pl, c->pc, g, c->logn, N);
     CK(cudaGetLastError());
 }
 
@@ -254,13 +257,13 @@ Evk make_key(hb_ctx *c, u64 kid, u32 g) {
     std::vector<i64> ev;
     for (int dg = 0; dg < nd; ++dg) {
         u64 *b = k.d + ((size_t)dg * 2) * np * N, *a = b + (size_t)np * N;
-        k_uniform<<<dim3((unsigned)((N / 4 + 255) / 256), np), 256, 0, c->st>>>(a, am, c->pc, N, c->ckey, hbhost::STREAM_KEY_A, kid * 64 + dg);
+        LAUNCH(c), k_uniform<<<dim3((unsigned)((N / 4 + 255) / 256), np), 256, 0, c->st>>>(a, am, c->pc, N, c->ckey, hbhost::STREAM_KEY_A, kid * 64 + dg);
         h.sample_gauss(hbhost::STREAM_KEY_E, kid * 64 + dg, ev);
         CK(cudaMemcpyAsync(ecoef, ev.data(), (size_t)N * 8, cudaMemcpyHostToDevice, c->st));
-        k_reduce_i64<<<c->egrid(np), 256, 0, c->st>>>(e.p, ecoef, am, c->pc, N);
+        LAUNCH(c), k_reduce_i64<<<c->egrid(np), 256, 0, c->st>>>(e.p, ecoef, am, c->pc, N);
         CK(cudaStreamSynchronize(c->st)); // ev is reused by the next digit
         ntt_inplace(c, e.p, np, am, false);
-        k_keygen<<<c->egrid(np), 256, 0, c->st>>>(b, a, e.p, c->sk, c->pc, N, c->logn, g, h.digit_lo(dg), h.digit_hi(dg, h.L + 1), pmod);
+        LAUNCH(c), k_keygen<<<c->egrid(np), 256, 0, c->st>>>(b, a, e.p, c->sk, c->pc, N, c->logn, g, h.digit_lo(dg), h.digit_hi(dg, h.L + 1), pmod);
     }
     CK(cudaGetLastError());
     c->pool.put(ecoef);
@@ -286,11 +289,11 @@ hb_ct *do_rescale(hb_ctx *c, const hb_ct *a) {
         Tmp last(c, (size_t)nbp), t(c, (size_t)nbp * l);
         LimbMap lm{}; lm.n = 1; lm.prime[0] = (unsigned char)l;
         ntt(c, a->d + (size_t)l * N, (size_t)(l + 1) * N, last.p, (size_t)N, nbp, lm, true);
-        k_rescale_prep<<<c->egrid(nbp * l), 256, 0, c->st>>>(t.p, last.p, l, c->pc, N);
+        LAUNCH(c), k_rescale_prep<<<c->egrid(nbp * l), 256, 0, c->st>>>(t.p, last.p, l, c->pc, N);
         ntt_inplace(c, t.p, nbp * l, c->qmap(l - 1), false);
         Scalars qi{};
         for (int i = 0; i < l; ++i) qi.v[i] = hbhost::invmod(c->h->q[l] % c->h->q[i], c->h->q[i]);
-        k_rescale_fin<<<c->egrid(nbp * l), 256, 0, c->st>>>(r->d, a->d, t.p, l, c->pc, N, qi);
+        LAUNCH(c), k_rescale_fin<<<c->egrid(nbp * l), 256, 0, c->st>>>(r->d, a->d, t.p, l, c->pc, N, qi);
         CK(cudaGetLastError());
     } catch (...) { hb_ct_free(r); throw; }
     return r;
@@ -306,7 +309,7 @@ hb_ct *do_level_down(hb_ctx *c, const hb_ct *a, int target) {
         const i64 k = (i64)std::rint(cf);
         Scalars s{};
         for (int i = 0; i <= tl; ++i) s.v[i] = (u64)(k % (i64)c->h->q[i]);
-        k_scalar_mul<<<c->egrid(nbp * (tl + 1)), 256, 0, c->st>>>(t->d, a->d, (size_t)(a->level + 1) * N, c->qmap(tl), c->pc, N, s);
+        LAUNCH(c), k_scalar_mul<<<c->egrid(nbp * (tl + 1)), 256, 0, c->st>>>(t->d, a->d, (size_t)(a->level + 1) * N, c->qmap(tl), c->pc, N, s);
         CK(cudaGetLastError());
         r = do_rescale(c, t);
     } catch (...) { hb_ct_free(t); throw; }
@@ -324,7 +327,7 @@ hb_ct *do_addsub(hb_ctx *c, const hb_ct *a, const hb_ct *b, int mode) {
     }
     check_same(a, b, "add");
     hb_ct *r = new_ct(c, a->level, a->np, a->batch, a->spow);
-    k_addsub<<<c->egrid((int)a->limbs()), 256, 0, c->st>>>(r->d, a->d, b->d, c->qmap(a->level), c->pc, c->N, mode);
+    LAUNCH(c), k_addsub<<<c->egrid((int)a->limbs()), 256, 0, c->st>>>(r->d, a->d, b->d, c->qmap(a->level), c->pc, c->N, mode);
     return r;
 }
 hb_ct *do_tensor(hb_ctx *c, const hb_ct *a, const hb_ct *b, hb_ct *acc) {
@@ -334,7 +337,7 @@ hb_ct *do_tensor(hb_ctx *c, const hb_ct *a, const hb_ct *b, hb_ct *acc) {
     if (r) { if (r->level != a->level || r->np != 3 || r->batch != a->batch || r->spow != 2) fail(HB_E_SHAPE, "tensor_acc: accumulator mismatch"); }
     else r = new_ct(c, a->level, 3, a->batch, 2);
     const int n = a->level + 1;
-    k_tensor<<<c->egrid(a->batch * n), 256, 0, c->st>>>(r->d, a->d, b->d, n, c->qmap(a->level), c->pc, c->N, acc ? 1 : 0);
+    LAUNCH(c), k_tensor<<<c->egrid(a->batch * n), 256, 0, c->st>>>(r->d, a->d, b->d, n, c->qmap(a->level), c->pc, c->N, acc ? 1 : 0);
     return r;
 }
 hb_ct *do_relin(hb_ctx *c, const hb_ct *a) {
@@ -362,7 +365,7 @@ hb_ct *do_mul_pt(hb_ctx *c, const hb_ct *a, const hb_pt *p) {
     if (a->level != p->level) fail(HB_E_LEVEL, "mul_pt: level mismatch");
     if (a->spow != 1 || p->spow != 1) fail(HB_E_SHAPE, "mul_pt: operand not rescaled");
     hb_ct *r = new_ct(c, a->level, a->np, a->batch, 2);
-    k_mul_pt<<<c->egrid((int)a->limbs()), 256, 0, c->st>>>(r->d, a->d, p->d, c->qmap(a->level), c->pc, c->N);
+    LAUNCH(c), k_mul_pt<<<c->egrid((int)a->limbs()), 256, 0, c->st>>>(r->d, a->d, p->d, c->qmap(a->level), c->pc, c->N);
     return r;
 }
 
@@ -454,6 +457,7 @@ int hb_mem_info(const hb_ctx *c, uint64_t *pool_bytes, uint64_t *in_use) {
     return HB_OK;
 }
 void *hb_stream(const hb_ctx *c) { return (void *)c->st; }
+uint64_t hb_launch_count(const hb_ctx *c) { return c ? c->launches : 0; }
 
 int hb_keygen(hb_ctx *c) {
     return guard(c, [&] {
@@ -462,7 +466,7 @@ int hb_keygen(hb_ctx *c) {
         i64 *sc = (i64 *)c->pool.get((size_t)c->N * 8);
         CK(cudaMemcpyAsync(sc, s.data(), (size_t)c->N * 8, cudaMemcpyHostToDevice, c->st));
         const LimbMap am = c->allmap();
-        k_reduce_i64<<<c->egrid(c->nprimes), 256, 0, c->st>>>(c->sk, sc, am, c->pc, c->N);
+        LAUNCH(c), k_reduce_i64<<<c->egrid(c->nprimes), 256, 0, c->st>>>(c->sk, sc, am, c->pc, c->N);
         ntt_inplace(c, c->sk, c->nprimes, am, false);
         CK(cudaStreamSynchronize(c->st));
         c->pool.put(sc);
@@ -501,7 +505,7 @@ int hb_encode(hb_ctx *c, const double *re, const double *im, size_t n, int level
         i64 *dc = (i64 *)c->pool.get((size_t)c->N * 8);
         CK(cudaMemcpyAsync(dc, coef.data(), (size_t)c->N * 8, cudaMemcpyHostToDevice, c->st));
         const LimbMap qm = c->qmap(level);
-        k_reduce_i64<<<c->egrid(level + 1), 256, 0, c->st>>>(p->d, dc, qm, c->pc, c->N);
+        LAUNCH(c), k_reduce_i64<<<c->egrid(level + 1), 256, 0, c->st>>>(p->d, dc, qm, c->pc, c->N);
         ntt_inplace(c, p->d, level + 1, qm, false);
         CK(cudaStreamSynchronize(c->st)); // coef goes out of scope
         c->pool.put(dc);
@@ -534,14 +538,14 @@ int hb_encrypt(hb_ctx *c, const hb_pt *p, uint64_t nonce, hb_ct **out) {
         try {
             const LimbMap qm = c->qmap(p->level);
             u64 *b = r->d, *a = r->d + (size_t)n * N;
-            k_uniform<<<dim3((unsigned)((N / 4 + 255) / 256), n), 256, 0, c->st>>>(a, qm, c->pc, N, c->ckey, hbhost::STREAM_ENC_A, nonce);
+            LAUNCH(c), k_uniform<<<dim3((unsigned)((N / 4 + 255) / 256), n), 256, 0, c->st>>>(a, qm, c->pc, N, c->ckey, hbhost::STREAM_ENC_A, nonce);
             std::vector<i64> ev; c->h->sample_gauss(hbhost::STREAM_ENC_E, nonce, ev);
             i64 *ec = (i64 *)c->pool.get((size_t)N * 8);
             Tmp e(c, (size_t)n);
             CK(cudaMemcpyAsync(ec, ev.data(), (size_t)N * 8, cudaMemcpyHostToDevice, c->st));
-            k_reduce_i64<<<c->egrid(n), 256, 0, c->st>>>(e.p, ec, qm, c->pc, N);
+            LAUNCH(c), k_reduce_i64<<<c->egrid(n), 256, 0, c->st>>>(e.p, ec, qm, c->pc, N);
             ntt_inplace(c, e.p, n, qm, false);
-            k_encrypt<<<c->egrid(n), 256, 0, c->st>>>(b, a, e.p, c->sk, p->d, qm, c->pc, N);
+            LAUNCH(c), k_encrypt<<<c->egrid(n), 256, 0, c->st>>>(b, a, e.p, c->sk, p->d, qm, c->pc, N);
             CK(cudaStreamSynchronize(c->st));
             c->pool.put(ec);
         } catch (...) { hb_ct_free(r); throw; }
@@ -554,7 +558,7 @@ int hb_decrypt(hb_ctx *c, const hb_ct *ct, int index, double *re, double *im) {
         if (index < 0 || index >= ct->batch) fail(HB_E_ARG, "decrypt: bad batch index");
         const int n = ct->level + 1, N = c->N, nl = ct->level >= 1 ? 2 : 1;
         Tmp t(c, (size_t)nl);
-        k_decrypt<<<c->egrid(nl), 256, 0, c->st>>>(t.p, ct->d + (size_t)index * ct->np * n * N, n, ct->np, c->sk, c->pc, N);
+        LAUNCH(c), k_decrypt<<<c->egrid(nl), 256, 0, c->st>>>(t.p, ct->d + (size_t)index * ct->np * n * N, n, ct->np, c->sk, c->pc, N);
         ntt_inplace(c, t.p, nl, c->qmap(nl - 1), true);
         decode_limbs(c, t.p, ct->level, ct->spow, re, im);
     });
@@ -608,14 +612,14 @@ int hb_sub(hb_ctx *c, const hb_ct *a, const hb_ct *b, hb_ct **out) { return guar
 int hb_negate(hb_ctx *c, const hb_ct *a, hb_ct **out) {
     return guard(c, [&] {
         hb_ct *r = new_ct(c, a->level, a->np, a->batch, a->spow);
-        k_addsub<<<c->egrid((int)a->limbs()), 256, 0, c->st>>>(r->d, a->d, a->d, c->qmap(a->level), c->pc, c->N, 2);
+        LAUNCH(c), k_addsub<<<c->egrid((int)a->limbs()), 256, 0, c->st>>>(r->d, a->d, a->d, c->qmap(a->level), c->pc, c->N, 2);
         *out = r;
     });
 }
 int hb_mult_imag(hb_ctx *c, const hb_ct *a, hb_ct **out) {
     return guard(c, [&] {
         hb_ct *r = new_ct(c, a->level, a->np, a->batch, a->spow);
-        k_mult_imag<<<c->egrid((int)a->limbs()), 256, 0, c->st>>>(r->d, a->d, c->qmap(a->level), c->pc, c->N);
+        LAUNCH(c), k_mult_imag<<<c->egrid((int)a->limbs()), 256, 0, c->st>>>(r->d, a->d, c->qmap(a->level), c->pc, c->N);
         *out = r;
     });
 }
@@ -624,7 +628,7 @@ int hb_mult_int(hb_ctx *c, const hb_ct *a, int64_t k, hb_ct **out) {
         hb_ct *r = new_ct(c, a->level, a->np, a->batch, a->spow);
         Scalars s{};
         for (int i = 0; i <= a->level; ++i) { const i64 q = (i64)c->h->q[i]; i64 v = k % q; if (v < 0) v += q; s.v[i] = (u64)v; }
-        k_scalar_mul<<<c->egrid((int)a->limbs()), 256, 0, c->st>>>(r->d, a->d, (size_t)(a->level + 1) * c->N, c->qmap(a->level), c->pc, c->N, s);
+        LAUNCH(c), k_scalar_mul<<<c->egrid((int)a->limbs()), 256, 0, c->st>>>(r->d, a->d, (size_t)(a->level + 1) * c->N, c->qmap(a->level), c->pc, c->N, s);
         *out = r;
     });
 }
@@ -673,7 +677,7 @@ int hb_mul2_add_rescale(hb_ctx *c, const hb_ct *a, const hb_pt *pa, const hb_ct 
         if (a->level != pa->level || a->level != pb->level) fail(HB_E_LEVEL, "mul2_add_rescale: level mismatch");
         if (a->spow != 1) fail(HB_E_SHAPE, "mul2_add_rescale: operand not rescaled");
         hb_ct *t = new_ct(c, a->level, a->np, a->batch, 2);
-        k_mul2_add<<<c->egrid((int)a->limbs()), 256, 0, c->st>>>(t->d, a->d, pa->d, b->d, pb->d, c->qmap(a->level), c->pc, c->N);
+        LAUNCH(c), k_mul2_add<<<c->egrid((int)a->limbs()), 256, 0, c->st>>>(t->d, a->d, pa->d, b->d, pb->d, c->qmap(a->level), c->pc, c->N);
         try { *out = do_rescale(c, t); } catch (...) { hb_ct_free(t); throw; }
         hb_ct_free(t);
     });
@@ -688,7 +692,7 @@ int hb_matmul_acc(hb_ctx *c, const hb_ct *pre, const hb_pt *pt, int64_t row_step
         u32 *dg = (u32 *)c->pool.get((size_t)kc * 4);
         CK(cudaMemcpyAsync(dg, gal.data(), (size_t)kc * 4, cudaMemcpyHostToDevice, c->st));
         hb_ct *r = new_ct(c, pre->level, 2, 1, 2);
-        k_matmul_acc<<<c->egrid(2 * n), 256, 0, c->st>>>(r->d, pre->d, kc, pt->d, dg, n, c->qmap(pre->level), c->pc, c->logn, c->N);
+        LAUNCH(c), k_matmul_acc<<<c->egrid(2 * n), 256, 0, c->st>>>(r->d, pre->d, kc, pt->d, dg, n, c->qmap(pre->level), c->pc, c->logn, c->N);
         CK(cudaStreamSynchronize(c->st));
         c->pool.put(dg);
         *out = r;
@@ -699,12 +703,12 @@ int hb_pt_rotate(hb_ctx *c, const hb_pt *p, int64_t steps, hb_pt **out) {
         hb_pt *r = new_pt(c, p->level, p->spow);
         const u64 g = c->h->galois_rot(steps);
         if (g == 1) CK(cudaMemcpyAsync(r->d, p->d, (size_t)(p->level + 1) * c->N * 8, cudaMemcpyDeviceToDevice, c->st));
-        else k_permute<<<c->egrid(p->level + 1), 256, 0, c->st>>>(r->d, p->d, (u32)g, c->logn, c->N);
+        else LAUNCH(c), k_permute<<<c->egrid(p->level + 1), 256, 0, c->st>>>(r->d, p->d, (u32)g, c->logn, c->N);
         *out = r;
     });
 }
 int hb_mod_reduce(hb_ctx *c, hb_ct *a) {
-    return guard(c, [&] { k_mod_reduce<<<c->egrid((int)a->limbs()), 256, 0, c->st>>>(a->d, c->qmap(a->level), c->pc, c->N); });
+    return guard(c, [&] { LAUNCH(c), k_mod_reduce<<<c->egrid((int)a->limbs()), 256, 0, c->st>>>(a->d, c->qmap(a->level), c->pc, c->N); });
 }
 // Sum over ranks of residues below 2^60 cannot overflow 64 bits for up to 16 ranks; the owner
 // reduces afterwards (same order of operations as HEMMer::ncclAllReduceWrapper + modReduct).
@@ -714,7 +718,7 @@ int hb_allreduce_sum(hb_ctx *c, hb_ct *a, void *comm) {
         if (!nc.ok) fail(HB_E_NCCL, "NCCL library not available");
         ncclResult_t r = nc.AllReduce(a->d, a->d, a->limbs() * c->N, ncclUint64, ncclSum, (ncclComm_t)comm, c->st);
         if (r != ncclSuccess) fail(HB_E_NCCL, nc.GetErrorString(r));
-        k_mod_reduce<<<c->egrid((int)a->limbs()), 256, 0, c->st>>>(a->d, c->qmap(a->level), c->pc, c->N);
+        LAUNCH(c), k_mod_reduce<<<c->egrid((int)a->limbs()), 256, 0, c->st>>>(a->d, c->qmap(a->level), c->pc, c->N);
     });
 }
 int hb_allgather(hb_ctx *c, const hb_ct *mine, hb_ct *all, void *comm) {

@@ -67,6 +67,8 @@ int hb_sync(hb_ctx *ctx);
 int hb_mem_info(const hb_ctx *ctx, uint64_t *pool_bytes, uint64_t *in_use_bytes);
 /* the CUDA stream all kernels of this context run on (as a void* cudaStream_t) */
 void *hb_stream(const hb_ctx *ctx);
+/* number of kernels this context has launched since creation */
+uint64_t hb_launch_count(const hb_ctx *ctx);
 
 /* KeyGenerator::genCommonKeys -- KeyGenerator.hpp:160-165: secret, multiplication and conjugation keys */
 int hb_keygen(hb_ctx *ctx);

@@ -454,8 +454,8 @@ struct Ct {
     int level = -1, np = 2, spow = 1, batch = 1, N = 0;
     std::vector<u64> d; // [batch][np][level+1][N]
     Ct() {}
-    Ct(int N_, int level_, int np_ = 2, int batch_ = 1, int spow_ = 1)
-        : level(level_), np(np_), spow(spow_), batch(batch_), N(N_), d((size_t)batch_ * np_ * (level_ + 1) * N_, 0) {}
+    Ct(int N_, int level_, int np_ = 2, int batch_ = 1, int spow_ = 1, bool meta_only = false)
+        : level(level_), np(np_), spow(spow_), batch(batch_), N(N_), d(meta_only ? 0 : (size_t)batch_ * np_ * (level_ + 1) * N_, 0) {}
     u64 *limb(int b, int p, int l) { return d.data() + (((size_t)b * np + p) * (level + 1) + l) * N; }
     const u64 *limb(int b, int p, int l) const { return d.data() + (((size_t)b * np + p) * (level + 1) + l) * N; }
 };
@@ -482,10 +482,19 @@ struct Evaluator {
     std::map<u64, Evk> gal_keys;  // galois element -> key
     explicit Evaluator(Context &c) : cx(c) {}
 
+    // Dry mode: every primitive keeps the level / shape bookkeeping but skips the arithmetic, and
+    // counts itself in `stats`.  Used to obtain exact operation counts of a full-size schedule
+    // (the cpu-baseline leg multiplies them by sampled per-operation times).
+    bool dry = false;
+    std::map<std::pair<std::string, int>, long> stats;
+    bool count(const char *op, int level) { if (dry) ++stats[{op, level}]; return dry; }
+    Ct meta(int level, int np, int batch, int spow) const { return Ct(cx.N, level, np, batch, spow, true); }
+
     // EnDecoder::encode (HEaaN/EnDecoder.hpp:51): slots -> plaintext at `level`, scale Delta_level
     Pt encode(const cplx *z, size_t n, int level) const {
         if ((int)n > cx.slots) throw std::invalid_argument("encode: too many slots");
         if (level < 0 || level > cx.L) throw std::invalid_argument("encode: bad level");
+        if (dry) { ++const_cast<Evaluator *>(this)->stats[{"encode", level}]; Pt e; e.level = level; e.N = cx.N; return e; }
         std::vector<cplx> v(cx.slots, cplx(0, 0));
         for (size_t i = 0; i < n; ++i) v[i] = z[i];
         cx.fft_special_inv(v);
@@ -542,6 +551,7 @@ struct Evaluator {
     // Encryptor::encrypt(ptxt, sk, ctxt) (HEaaN/Encryptor.hpp:84), symmetric:
     //   a uniform (stream ENC_A, nonce), e Gaussian (stream ENC_E, nonce), b = -a*s + e + m
     Ct encrypt(const Pt &pt, u64 nonce) const {
+        if (dry) { ++const_cast<Evaluator *>(this)->stats[{"encrypt", pt.level}]; return meta(pt.level, 2, 1, pt.spow); }
         Ct ct(cx.N, pt.level, 2, 1, pt.spow);
         std::vector<i64> e; cx.sample_gauss(DOM_ENC_E, nonce, e);
 #pragma omp parallel for
@@ -611,7 +621,7 @@ struct Evaluator {
         gen_galois_key(cx.galois_conj());
     }
     void gen_galois_key(u64 g) {
-        if (gal_keys.count(g)) return;
+        if (dry || gal_keys.count(g)) return;
         const auto &perm = cx.ntt_perm(g);
         std::vector<std::vector<u64>> sp(cx.nprimes, std::vector<u64>(cx.N));
         for (int pi = 0; pi < cx.nprimes; ++pi)
@@ -742,6 +752,7 @@ struct Evaluator {
             return add(x, level_down(y, x.level), subtract);
         }
         require(x.np == y.np && x.spow == y.spow && x.batch == y.batch, "add: shape mismatch");
+        if (count("add", x.level)) return meta(x.level, x.np, x.batch, x.spow);
         Ct r = x;
         const int n = x.level + 1, N = cx.N;
 #pragma omp parallel for
@@ -754,6 +765,7 @@ struct Evaluator {
         return r;
     }
     Ct negate(const Ct &x) {
+        if (count("add", x.level)) return meta(x.level, x.np, x.batch, x.spow);
         Ct r = x; const int n = x.level + 1, N = cx.N;
         for (int i = 0; i < x.batch * x.np * n; ++i) {
             const Mod &m = cx.mod[i % n]; u64 *o = r.d.data() + (size_t)i * N;
@@ -764,6 +776,7 @@ struct Evaluator {
     // HomEvaluator::multImagUnit (HomEvaluator.hpp:329-331): multiply by X^(N/2); in NTT form this is
     // +iota on the first half of the limb and -iota on the second half, iota = psi^(N/2).
     Ct mult_imag(const Ct &x) {
+        if (count("mult_imag", x.level)) return meta(x.level, x.np, x.batch, x.spow);
         Ct r = x; const int n = x.level + 1, N = cx.N;
 #pragma omp parallel for
         for (int i = 0; i < x.batch * x.np * n; ++i) {
@@ -776,6 +789,7 @@ struct Evaluator {
     }
     // HomEvaluator::multInteger (HomEvaluator.hpp:346-348)
     Ct mult_int(const Ct &x, i64 k) {
+        if (count("mult_imag", x.level)) return meta(x.level, x.np, x.batch, x.spow);
         Ct r = x; const int n = x.level + 1, N = cx.N;
 #pragma omp parallel for
         for (int i = 0; i < x.batch * x.np * n; ++i) {
@@ -788,6 +802,7 @@ struct Evaluator {
     Ct mul_pt_norescale(const Ct &x, const Pt &p) {
         require(x.level == p.level, "mul_pt: level mismatch");
         require(x.spow == 1 && p.spow == 1 && x.np == 2, "mul_pt: operand not rescaled");
+        if (count("mul_pt", x.level)) return meta(x.level, x.np, x.batch, 2);
         Ct r = x; r.spow = 2; const int n = x.level + 1, N = cx.N;
 #pragma omp parallel for
         for (int i = 0; i < x.batch * x.np * n; ++i) {
@@ -804,6 +819,7 @@ struct Evaluator {
     Ct rescale(const Ct &x) {
         require(x.level >= 1, "rescale: level 0");
         require(x.spow == 2, "rescale: nothing to rescale");
+        if (count(x.np == 3 ? "rescale3" : "rescale", x.level)) return meta(x.level - 1, x.np, x.batch, 1);
         const int l = x.level, N = cx.N; const u64 ql = cx.mod[l].q;
         Ct r(N, l - 1, x.np, x.batch, 1);
         const int nbp = x.batch * x.np;
@@ -837,6 +853,7 @@ struct Evaluator {
         if (target == x.level) return x;
         require(x.spow == 1, "level_down: operand not rescaled");
         const int N = cx.N;
+        if (count("scalar_mul", target + 1)) return rescale(meta(target + 1, x.np, x.batch, 2));
         Ct t(N, target + 1, x.np, x.batch, 2);
         double cf = cx.scale[target] * (double)cx.mod[target + 1].q / cx.scale[x.level];
         i64 k = (i64)std::rint(cf);
@@ -853,6 +870,7 @@ struct Evaluator {
     Ct tensor(const Ct &x, const Ct &y) {
         require(x.level == y.level && x.np == 2 && y.np == 2 && x.spow == 1 && y.spow == 1 && x.batch == y.batch, "tensor: operands");
         const int n = x.level + 1, N = cx.N;
+        if (count("tensor", x.level)) return meta(x.level, 3, x.batch, 2);
         Ct r(N, x.level, 3, x.batch, 2);
 #pragma omp parallel for collapse(2)
         for (int b = 0; b < x.batch; ++b)
@@ -871,6 +889,7 @@ struct Evaluator {
     // HomEvaluator::relinearize (HomEvaluator.hpp:524)
     Ct relin(const Ct &x) {
         require(x.np == 3, "relin: needs 3 polys");
+        if (count("relin", x.level)) return meta(x.level, 2, x.batch, x.spow);
         const int n = x.level + 1, N = cx.N;
         Ct r(N, x.level, 2, x.batch, x.spow);
         for (int b = 0; b < x.batch; ++b) {
@@ -898,6 +917,7 @@ struct Evaluator {
     Ct apply_galois(const Ct &x, u64 g) {
         require(x.np == 2, "rotate: needs 2 polys");
         if (g == 1) return x;
+        if (count("rotate", x.level)) return meta(x.level, 2, x.batch, x.spow);
         auto it = gal_keys.find(g);
         if (it == gal_keys.end()) throw std::runtime_error("missing galois key");
         const int n = x.level + 1, N = cx.N;

@@ -493,6 +493,7 @@ struct Hemmer {
     //   out = sum_k pre[k] (.) leftRotate(pt, k * width), un-rescaled (scale Delta^2).
     // The plaintext must already sit at the level of `pre` (the reference re-encodes otherwise).
     CtT mult_mat_mat_reuse(const Ct &pre, const PtT &b) {
+        if (b.pt.level != pre.level) throw std::invalid_argument("[multMatMatReUse] plaintext level differs from the ciphertexts'");
         Ct acc;
         for (int k = 0; k < pre.batch; ++k) {
             Pt pk = pt_rotate(b.pt, (i64)k * b.sh.width);
@@ -521,7 +522,7 @@ struct Hemmer {
     // leftRotate on a plaintext: the slot permutation alone (no key), used by HomEvaluator::matmul
     Pt pt_rotate(const Pt &p, i64 left_steps) {
         u64 g = cx.galois_for_rotation(left_steps);
-        if (g == 1) return p;
+        if (g == 1 || ev.dry) return p;
         const auto &perm = cx.ntt_perm(g);
         Pt r = p;
         for (int l = 0; l <= p.level; ++l)
@@ -529,11 +530,13 @@ struct Hemmer {
         return r;
     }
     Ct slice(const Ct &b, int k) const {
+        if (ev.dry) return ev.meta(b.level, b.np, 1, b.spow);
         Ct r(cx.N, b.level, b.np, 1, b.spow);
         std::memcpy(r.d.data(), b.limb(k, 0, 0), r.d.size() * 8);
         return r;
     }
     Ct stack(const std::vector<Ct> &v) const {
+        if (ev.dry) return ev.meta(v[0].level, v[0].np, (int)v.size(), v[0].spow);
         Ct r(cx.N, v[0].level, v[0].np, (int)v.size(), v[0].spow);
         for (size_t k = 0; k < v.size(); ++k) {
             if (v[k].level != r.level || v[k].np != r.np) throw std::invalid_argument("stack: mismatched ciphertexts");

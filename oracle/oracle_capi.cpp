@@ -71,6 +71,7 @@ int orc_decode(orc_ctx *c, const orc_pt *pt, double *re, double *im) {
 int orc_encrypt(orc_ctx *c, const orc_pt *pt, uint64_t nonce, orc_ct **out) { ORC_TRY(c, *out = new Ct(c->ev.encrypt(*pt, nonce))) }
 int orc_decrypt(orc_ctx *c, const orc_ct *ct, int idx, double *re, double *im) {
     ORC_TRY(c, {
+        if (ct->d.empty()) throw std::invalid_argument("decrypt: ciphertext produced in dry mode");
         std::vector<cplx> z(c->cx.slots); c->ev.decrypt(*ct, idx, z.data());
         for (int i = 0; i < c->cx.slots; ++i) { re[i] = z[i].real(); if (im) im[i] = z[i].imag(); }
     })
@@ -84,7 +85,7 @@ int orc_ct_meta(const orc_ct *x, int *level, int *np, int *batch, int *spow) {
 }
 int orc_pt_meta(const orc_pt *x, int *level, int *spow) { if (level) *level = x->level; if (spow) *spow = x->spow; return 0; }
 int orc_ct_import(orc_ctx *, orc_ct *x, const uint64_t *h) { std::memcpy(x->d.data(), h, x->d.size() * 8); return 0; }
-int orc_ct_export(orc_ctx *, const orc_ct *x, uint64_t *h) { std::memcpy(h, x->d.data(), x->d.size() * 8); return 0; }
+int orc_ct_export(orc_ctx *, const orc_ct *x, uint64_t *h) { if (x->d.empty()) return -3; std::memcpy(h, x->d.data(), x->d.size() * 8); return 0; }
 int orc_pt_export(orc_ctx *, const orc_pt *x, uint64_t *h) { std::memcpy(h, x->d.data(), x->d.size() * 8); return 0; }
 int orc_batch_set(orc_ctx *c, orc_ct *dst, int idx, const orc_ct *src) {
     ORC_TRY(c, {
@@ -115,6 +116,17 @@ int orc_mul(orc_ctx *c, const orc_ct *a, const orc_ct *b, orc_ct **o) { ORC_TRY(
 int orc_rotate(orc_ctx *c, const orc_ct *a, int64_t s, orc_ct **o) { ORC_TRY(c, *o = new Ct(c->ev.rotate(*a, s))) }
 int orc_conjugate(orc_ctx *c, const orc_ct *a, orc_ct **o) { ORC_TRY(c, *o = new Ct(c->ev.conjugate(*a))) }
 int orc_ntt(orc_ctx *c, orc_ct *a, int inverse) { ORC_TRY(c, c->ev.ntt_raw(*a, inverse != 0)) }
+
+// dry mode and operation counters (see Evaluator::dry)
+int orc_set_dry(orc_ctx *c, int on) { c->ev.dry = on != 0; return 0; }
+int orc_stats_clear(orc_ctx *c) { c->ev.stats.clear(); return 0; }
+// writes "op level count\n" lines; returns the needed buffer size
+int orc_stats_dump(orc_ctx *c, char *buf, int cap) {
+    std::string s;
+    for (auto &kv : c->ev.stats) s += kv.first.first + " " + std::to_string(kv.first.second) + " " + std::to_string(kv.second) + "\n";
+    if (buf && cap > 0) { int n = std::min((int)s.size(), cap - 1); std::memcpy(buf, s.data(), n); buf[n] = 0; }
+    return (int)s.size() + 1;
+}
 
 // --- small self-check helpers used only by the oracle's own unit tests ---
 int orc_chacha_block(const uint32_t key[8], uint32_t counter, const uint32_t nonce[3], uint32_t out[16]) {
