@@ -369,6 +369,30 @@ hb_ct *do_mul_pt(hb_ctx *c, const hb_ct *a, const hb_pt *p) {
     return r;
 }
 
+// ---- allocation-free rescale ---------------------------------------------------------------
+// Scratch for hb_rescale_noalloc lives in the library image instead of coming from cudaMalloc or the
+// context's pool, so the call can be made by code that is not allowed to allocate device memory
+// (for example a caller running under a fixed memory budget that was handed out in full at start-up,
+// or one that must not disturb another allocator's view of the device).  Every GPU that loads the
+// library holds these kNoAllocWords * 8 bytes (13 MiB) until the process exits.
+constexpr size_t kNoAllocLimbs = 26;                      // one 2-poly ciphertext at level 12: 2 + 2*12 limbs
+constexpr size_t kNoAllocWords = kNoAllocLimbs * 65536;   // of 2^16 words each
+static __device__ __align__(256) unsigned long long g_noalloc_scratch[kNoAllocWords];
+constexpr int kMaxDevices = 64;
+u64 *g_noalloc_ptr[kMaxDevices] = {nullptr};
+
+// Device address of the scratch array on the current device.  The array's name is only a host-side
+// stand-in here; kernels must be given the address cudaGetSymbolAddress returns for this device.
+u64 *noalloc_scratch(int device) {
+    if (device < 0 || device >= kMaxDevices) fail(HB_E_LIMIT, "device index beyond the scratch table");
+    if (!g_noalloc_ptr[device]) {
+        void *p = nullptr;
+        CK(cudaGetSymbolAddress(&p, g_noalloc_scratch));
+        g_noalloc_ptr[device] = (u64 *)p;
+    }
+    return g_noalloc_ptr[device];
+}
+
 template <class F> int guard(hb_ctx *c, F &&f) {
     try { CK(cudaSetDevice(c->device)); f(); return HB_OK; }
     catch (const ArgFail &e) { c->err = e.msg; return e.code; }
@@ -641,6 +665,30 @@ int hb_mul_pt(hb_ctx *c, const hb_ct *a, const hb_pt *p, hb_ct **out) {
     });
 }
 int hb_rescale(hb_ctx *c, const hb_ct *a, hb_ct **out) { return guard(c, [&] { *out = do_rescale(c, a); }); }
+int hb_rescale_noalloc(hb_ctx *c, const hb_ct *a, hb_ct *out) {
+    return guard(c, [&] {
+        if (!a || !out) fail(HB_E_ARG, "rescale_noalloc: null handle");
+        if (a->level < 1) fail(HB_E_LEVEL, "rescale: level 0");
+        if (a->spow != 2) fail(HB_E_SHAPE, "rescale: nothing to rescale");
+        if (out->level != a->level - 1 || out->np != a->np || out->batch != a->batch) fail(HB_E_SHAPE, "rescale_noalloc: output handle must be level-1 with the same polys and batch");
+        const int l = a->level, N = c->N, nbp = a->batch * a->np;
+        const size_t need = (size_t)nbp * (1 + (size_t)l) * N;
+        if (need > kNoAllocWords)
+            fail(HB_E_LIMIT, "rescale_noalloc: needs " + std::to_string(need * 8) + " bytes of scratch, the built-in buffer holds " + std::to_string(kNoAllocWords * 8) +
+                                 " (one 2-poly ciphertext at level 12 and N = 2^16)");
+        u64 *scratch = noalloc_scratch(c->device); // first call on a device resolves the address
+        u64 *last = scratch, *t = scratch + (size_t)nbp * N;
+        LimbMap lm{}; lm.n = 1; lm.prime[0] = (unsigned char)l;
+        ntt(c, a->d + (size_t)l * N, (size_t)(l + 1) * N, last, (size_t)N, nbp, lm, true);
+        LAUNCH(c), k_rescale_prep<<<c->egrid(nbp * l), 256, 0, c->st>>>(t, last, l, c->pc, N);
+        ntt_inplace(c, t, nbp * l, c->qmap(l - 1), false);
+        Scalars qi{};
+        for (int i = 0; i < l; ++i) qi.v[i] = hbhost::invmod(c->h->q[l] % c->h->q[i], c->h->q[i]);
+        LAUNCH(c), k_rescale_fin<<<c->egrid(nbp * l), 256, 0, c->st>>>(out->d, a->d, t, l, c->pc, N, qi);
+        CK(cudaGetLastError());
+        out->spow = 1;
+    });
+}
 int hb_level_down(hb_ctx *c, const hb_ct *a, int target, hb_ct **out) {
     return guard(c, [&] {
         if (target == a->level) { hb_ct *r = new_ct(c, a->level, a->np, a->batch, a->spow); CK(cudaMemcpyAsync(r->d, a->d, a->limbs() * c->N * 8, cudaMemcpyDeviceToDevice, c->st)); *out = r; }

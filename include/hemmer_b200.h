@@ -111,6 +111,17 @@ int hb_mul_pt(hb_ctx *ctx, const hb_ct *a, const hb_pt *p, hb_ct **out);        
 int hb_mul_pt_norescale(hb_ctx *ctx, const hb_ct *a, const hb_pt *p, hb_ct **out); /* multWithoutRescale :490-493 */
 int hb_rescale(hb_ctx *ctx, const hb_ct *a, hb_ct **out);                       /* rescale :539-540 */
 int hb_level_down(hb_ctx *ctx, const hb_ct *a, int target, hb_ct **out);        /* levelDown :574-576 */
+/* Rescale without any allocation (no counterpart in the reference).  For callers that may not obtain
+ * device memory while they run -- a service whose device budget was handed out completely at start-up, or
+ * a host that shares the GPU with an allocator it must not perturb.  Same result as hb_rescale, written
+ * into the caller's `out` (created beforehand at level-1 with the same poly count and batch).  The
+ * temporaries live in a 13 MiB buffer built into the library image, enough for one 2-poly ciphertext at
+ * level 12 with N = 2^16 (poly_count * batch * level * N * 8 + poly_count * batch * N * 8 bytes are
+ * needed); larger requests return HB_E_LIMIT.  The first call on a device looks the buffer's address up
+ * and should therefore be made before any stream capture begins.  All calls share the buffer: nothing in
+ * it has to start at zero (every word is written before it is read), but two calls that overlap on the
+ * GPU -- different contexts or streams -- would corrupt each other, so issue them one after another. */
+int hb_rescale_noalloc(hb_ctx *ctx, const hb_ct *a, hb_ct *out);
 int hb_tensor(hb_ctx *ctx, const hb_ct *a, const hb_ct *b, hb_ct **out);        /* tensor :518 */
 int hb_relin(hb_ctx *ctx, const hb_ct *a, hb_ct **out);                         /* relinearize :524 */
 int hb_mul(hb_ctx *ctx, const hb_ct *a, const hb_ct *b, hb_ct **out);           /* mult(ct,ct) :311-312 */
