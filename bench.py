@@ -78,7 +78,7 @@ class ClockSampler:
 # CPU arm: exact operation counts of the layer from a dry run of the oracle's schedules, times
 # per-operation timings sampled on the host cores.
 # ---------------------------------------------------------------------------------------------
-def cpu_layer_estimate(pkg, sample_reps=3):
+def cpu_layer_estimate(pkg, sample_reps=8):
     lib_path = os.path.join(ROOT, "oracle", "_build", "liboracle.so")
     if not os.path.exists(lib_path):
         subprocess.check_call(["make", "-s", "-C", os.path.join(ROOT, "oracle")])
@@ -218,6 +218,11 @@ def run_gpu(args):
 
     # operands resident in HBM before the clock starts
     wl.prepare()
+    if args.one_step:  # for `ncu --metrics gpu__time_duration.sum`: one pass, nothing else
+        wl.step_resident()
+        lib.sync()
+        print(json.dumps({"one_step": True, "launches": int(lib.dll.hb_launch_count(lib.ctx))}), flush=True)
+        return
     for s in range(args.warmup):
         wl.step_resident()
     lib.sync()
@@ -289,7 +294,7 @@ def run_gpu(args):
                "sample": f"sum over {info['distinct_ops_timed']} distinct (operation, level) pairs of exact count x one sampled full-size timing ({info['sample_seconds']} s of CPU work)"}
     line = {"metric": METRIC, "value": ms_step, "unit": "ms", "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,
             "higher_is_better": False, "scaling": "strong", "vs_baseline": None, "dtype": "u64", "data": "synthetic",
-            "config": {"workload": "bert_base_layer_matmuls_fwd_plus_lora_bwd", "units": len(wl.units), "ring_degree": 65536, "levels": 12, "tile": 128,
+            "config": {"workload": "bert_base_layer_matmuls_fwd_plus_lora_bwd", "units": len(wl.units), "batched_calls": True, "ring_degree": 65536, "levels": 12, "tile": 128,
                        "l2": "working set per step is tens of GB, far above the 126 MB L2", "max_abs_err_vs_float64": err},
             "roofline": roofline, "cpu_baseline": cpu,
             "e2e": {"value": ms_e2e, "unit": "ms", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
@@ -318,6 +323,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
+    ap.add_argument("--one-step", action="store_true", help="run a single pass of the layer and exit (launch-list profiling)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
     if args.impl == "reference":

@@ -120,6 +120,13 @@ class Evaluator {
     Ciphertext assemble(const Ciphertext &a, const Plaintext &pa, const Ciphertext &b, const Plaintext &pb) const {
         hb_ct *o = nullptr; check(c_, hb_mul2_add_rescale(c_, a.raw(), pa.raw(), b.raw(), pb.raw(), &o)); return Ciphertext(c_, o);
     }
+    // sum_j mult(a[j], p[j]): every product is rescaled as eval.mult(ct, mask) does, the results are added
+    Ciphertext multSum(const std::vector<const Ciphertext *> &a, const std::vector<const Plaintext *> &p) const {
+        std::vector<const hb_ct *> ra; std::vector<const hb_pt *> rp;
+        for (auto *x : a) ra.push_back(x->raw());
+        for (auto *x : p) rp.push_back(x->raw());
+        hb_ct *o = nullptr; check(c_, hb_mul_pt_sum(c_, ra.data(), rp.data(), (int)ra.size(), &o)); return Ciphertext(c_, o);
+    }
     // acc += tensor(a, b)
     void tensorAccumulate(Ciphertext &acc, const Ciphertext &a, const Ciphertext &b) const {
         hb_ct *p = acc.release();
@@ -131,9 +138,13 @@ class Evaluator {
     Ciphertext matmul(const Ciphertext &pre, const Plaintext &pt, i64 row_step) const {
         hb_ct *o = nullptr; check(c_, hb_matmul_acc(c_, pre.raw(), pt.raw(), row_step, &o)); return Ciphertext(c_, o);
     }
+    // sum over the K-groups b0 .. b0+pts.size()-1 of a batched set of shifted copies
+    Ciphertext matmulGroups(const Ciphertext &pre, int btotal, int b0, const std::vector<const hb_pt *> &pts, i64 row_step) const {
+        hb_ct *o = nullptr; check(c_, hb_matmul_acc_multi(c_, pre.raw(), btotal, b0, pts.data(), (int)pts.size(), row_step, &o)); return Ciphertext(c_, o);
+    }
     Ciphertext stack(const std::vector<Ciphertext> &v) const {
-        int level = 0, np = 0, sp = 0; hb_ct_meta(v[0].raw(), &level, &np, nullptr, &sp);
-        hb_ct *o = nullptr; check(c_, hb_ct_create(c_, level, np, (int)v.size(), sp, &o));
+        int level = 0, np = 0, sp = 0, b = 1; hb_ct_meta(v[0].raw(), &level, &np, &b, &sp);
+        hb_ct *o = nullptr; check(c_, hb_ct_create(c_, level, np, (int)v.size() * b, sp, &o)); // copy k of input j at k*b + j
         Ciphertext out(c_, o);
         for (size_t k = 0; k < v.size(); ++k) check(c_, hb_batch_set(c_, o, (int)k, v[k].raw()));
         return out;

@@ -69,6 +69,10 @@ int hb_hemmer_matmul_reuse(hb_hemmer *h, const hb_ct *pre, const hb_pt *p, SHAPE
         *out = o;
     });
 }
+// matMulReUse summed over K-groups: pre holds the copies of `btotal` inputs, groups b0..b0+bcount-1 meet pts[0..bcount-1]
+int hb_hemmer_matmul_reuse_groups(hb_hemmer *h, const hb_ct *pre, int btotal, int b0, const hb_pt *const *pts, int bcount, int width, hb_ct **out) {
+    return guard([&] { hb_ct *o = nullptr; check(h->ctx, hb_matmul_acc_multi(h->ctx, pre, btotal, b0, pts, bcount, width, &o)); *out = o; });
+}
 int hb_hemmer_matmul_pre_rev(hb_hemmer *h, const hb_ct *b, SHAPE_ARGS, int target, hb_ct **out) {
     return guard([&] { IN_TENSOR(t, b); *out = h->h.matMulPreRev(t, target).get().release(); });
 }

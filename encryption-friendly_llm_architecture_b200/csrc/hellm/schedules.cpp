@@ -118,11 +118,14 @@ Ciphertext bsgs_diagonals(Env &e, const Ciphertext &op, const TileTensorShape &s
         for (int sign = -1; sign <= 1; sign += 2) { // negative diagonals first, then positive
             i64 idx = 1 + i * f.bs + (sign < 0 ? -f.main : 0);
             const i64 limit = sign < 0 ? f.sub - f.main : f.sub;
-            Ciphertext part = e.ev.mult(baby[0], mask(idx));
+            // baby-step sum: part = sum_j mult(baby[j], mask[idx + j]), one fused call
+            std::vector<const Ciphertext *> cts{&baby[0]};
+            std::vector<const Plaintext *> pts{&mask(idx)};
             for (i64 j = 1; j < f.bs; ++j) {
                 if (++idx >= limit) break;
-                part = e.ev.add(part, e.ev.mult(baby[(size_t)j], mask(idx)));
+                cts.push_back(&baby[(size_t)j]); pts.push_back(&mask(idx));
             }
+            Ciphertext part = e.ev.multSum(cts, pts);
             part = sign < 0 ? e.ev.rightRotate(part, f.main * f.gap - rot_num) : e.ev.leftRotate(part, rot_num);
             res = e.ev.add(res, part);
         }
@@ -180,11 +183,13 @@ CtxtTensor transpose(Env &e, const CtxtTensor &op) {
     Ciphertext res;
     for (i64 i = 0; i < gs; ++i) {
         i64 idx = 1 - num_rows + i * bs;
-        Ciphertext part = e.ev.mult(baby[0], mask(idx));
+        std::vector<const Ciphertext *> cts{&baby[0]};
+        std::vector<const Plaintext *> pts{&mask(idx)};
         for (i64 j = 1; j < bs; ++j) {
             if (++idx >= num_cols) break;
-            part = e.ev.add(part, e.ev.mult(baby[(size_t)j], mask(idx)));
+            cts.push_back(&baby[(size_t)j]); pts.push_back(&mask(idx));
         }
+        Ciphertext part = e.ev.multSum(cts, pts);
         if (i == 0) res = std::move(part);
         else res = e.ev.add(res, e.ev.leftRotate(part, i * bs * gap));
     }

@@ -298,6 +298,36 @@ hb_ct *do_rescale(hb_ctx *c, const hb_ct *a) {
     } catch (...) { hb_ct_free(r); throw; }
     return r;
 }
+// sum_j rescale(a_j (.) p_j)  (separate)  or  rescale(sum_j a_j (.) p_j)
+hb_ct *do_prod_rescale(hb_ctx *c, const hb_ct *const *a, const hb_pt *const *p, int count, bool separate) {
+    if (count < 1 || count > kMaxTerms) fail(HB_E_LIMIT, "product sum: between 1 and " + std::to_string(kMaxTerms) + " terms");
+    const hb_ct *a0 = a[0];
+    if (a0->level < 1) fail(HB_E_LEVEL, "rescale: level 0");
+    TermList tl{}; tl.count = count;
+    for (int j = 0; j < count; ++j) {
+        if (a[j]->level != a0->level || p[j]->level != a0->level) fail(HB_E_LEVEL, "mul_pt: level mismatch");
+        if (a[j]->np != a0->np || a[j]->batch != a0->batch) fail(HB_E_SHAPE, "product sum: shape mismatch");
+        if (a[j]->spow != 1 || p[j]->spow != 1) fail(HB_E_SHAPE, "mul_pt: operand not rescaled");
+        tl.a[j] = a[j]->d; tl.p[j] = p[j]->d;
+    }
+    const int l = a0->level, N = c->N, nbp = a0->batch * a0->np, groups = separate ? count : 1;
+    const unsigned gx = (unsigned)((N + 255) / 256);
+    hb_ct *r = new_ct(c, l - 1, a0->np, a0->batch, 1);
+    try {
+        Tmp last(c, (size_t)groups * nbp), S(c, (size_t)nbp), t(c, (size_t)nbp * l);
+        LAUNCH(c), k_last_prod<<<dim3(gx, nbp, groups), 256, 0, c->st>>>(last.p, tl, separate ? 1 : 0, l, nbp, c->pc, N);
+        LimbMap lm{}; lm.n = 1; lm.prime[0] = (unsigned char)l;
+        ntt_inplace(c, last.p, groups * nbp, lm, true);
+        LAUNCH(c), k_centre_sum<<<dim3(gx, nbp), 256, 0, c->st>>>((i64 *)S.p, last.p, groups, nbp, l, c->pc, N);
+        LAUNCH(c), k_lift_mod<<<c->egrid(nbp * l), 256, 0, c->st>>>(t.p, (const i64 *)S.p, l, c->pc, N);
+        ntt_inplace(c, t.p, nbp * l, c->qmap(l - 1), false);
+        Scalars qi{};
+        for (int i = 0; i < l; ++i) qi.v[i] = hbhost::invmod(c->h->q[l] % c->h->q[i], c->h->q[i]);
+        LAUNCH(c), k_prod_rescale_fin<<<c->egrid(nbp * l), 256, 0, c->st>>>(r->d, tl, t.p, l, c->pc, N, qi);
+        CK(cudaGetLastError());
+    } catch (...) { hb_ct_free(r); throw; }
+    return r;
+}
 hb_ct *do_level_down(hb_ctx *c, const hb_ct *a, int target) {
     if (target > a->level || target < 0) fail(HB_E_LEVEL, "level_down: bad target");
     if (a->spow != 1) fail(HB_E_SHAPE, "level_down: operand not rescaled");
@@ -431,9 +461,19 @@ int hb_ctx_create(const hb_params *prm, int device, hb_ctx **out) {
             p.mu_lo = (u64)(((two64 % q) << 64) / q);
             p.n_inv = hbhost::invmod((u64)N, q); p.n_inv_sh = hbhost::shoup(p.n_inv, q);
             p.iu = hbhost::powmod(c->h->psi_root[i], (u64)N / 2, q); p.iu_sh = hbhost::shoup(p.iu, q);
-            p.pad = 0;
+            // the 2^16 transform takes quotients from the FP64 pipe for primes below 2^44 (mul_fp_lazy)
+            p.small = (c->logn == 16 && q < ((u64)1 << 44)) ? 1 : 0;
+            p.q_inv_f = 1.0 / (double)q;
+            p.n_inv_f = (double)p.n_inv / (double)q;
+            p.pad[0] = p.pad[1] = 0;
             std::vector<u64> f, fs, iv, ivs;
             c->h->twiddles(i, f, fs, iv, ivs);
+            if (p.small) { // companion tables hold w/q as doubles instead of Shoup quotients
+                for (int k = 0; k < N; ++k) {
+                    double a = (double)f[k] / (double)q, b = (double)iv[k] / (double)q;
+                    std::memcpy(&fs[k], &a, 8); std::memcpy(&ivs[k], &b, 8);
+                }
+            }
             std::memcpy(&tw[((size_t)0 * np + i) * N], f.data(), (size_t)N * 8);
             std::memcpy(&tw[((size_t)1 * np + i) * N], fs.data(), (size_t)N * 8);
             std::memcpy(&tw[((size_t)2 * np + i) * N], iv.data(), (size_t)N * 8);
@@ -616,8 +656,8 @@ int hb_pt_export(hb_ctx *c, const hb_pt *x, uint64_t *host) {
 void *hb_ct_device_ptr(const hb_ct *x) { return x ? x->d : nullptr; }
 int hb_batch_set(hb_ctx *c, hb_ct *dst, int idx, const hb_ct *src) {
     return guard(c, [&] {
-        if (src->batch != 1 || src->level != dst->level || src->np != dst->np || idx < 0 || idx >= dst->batch) fail(HB_E_SHAPE, "batch_set: mismatch");
-        const size_t per = (size_t)src->np * (src->level + 1) * c->N;
+        if (src->level != dst->level || src->np != dst->np || idx < 0 || (idx + 1) * src->batch > dst->batch) fail(HB_E_SHAPE, "batch_set: mismatch");
+        const size_t per = (size_t)src->batch * src->np * (src->level + 1) * c->N; // position counted in units of src's batch
         CK(cudaMemcpyAsync(dst->d + per * idx, src->d, per * 8, cudaMemcpyDeviceToDevice, c->st));
     });
 }
@@ -657,12 +697,9 @@ int hb_mult_int(hb_ctx *c, const hb_ct *a, int64_t k, hb_ct **out) {
     });
 }
 int hb_mul_pt_norescale(hb_ctx *c, const hb_ct *a, const hb_pt *p, hb_ct **out) { return guard(c, [&] { *out = do_mul_pt(c, a, p); }); }
-int hb_mul_pt(hb_ctx *c, const hb_ct *a, const hb_pt *p, hb_ct **out) {
-    return guard(c, [&] {
-        hb_ct *t = do_mul_pt(c, a, p);
-        try { *out = do_rescale(c, t); } catch (...) { hb_ct_free(t); throw; }
-        hb_ct_free(t);
-    });
+int hb_mul_pt(hb_ctx *c, const hb_ct *a, const hb_pt *p, hb_ct **out) { return guard(c, [&] { *out = do_prod_rescale(c, &a, &p, 1, true); }); }
+int hb_mul_pt_sum(hb_ctx *c, const hb_ct *const *a, const hb_pt *const *p, int count, hb_ct **out) {
+    return guard(c, [&] { *out = do_prod_rescale(c, a, p, count, true); });
 }
 int hb_rescale(hb_ctx *c, const hb_ct *a, hb_ct **out) { return guard(c, [&] { *out = do_rescale(c, a); }); }
 int hb_rescale_noalloc(hb_ctx *c, const hb_ct *a, hb_ct *out) {
@@ -721,31 +758,34 @@ int hb_ntt(hb_ctx *c, hb_ct *a, int inverse) { return guard(c, [&] { ntt_inplace
 
 int hb_mul2_add_rescale(hb_ctx *c, const hb_ct *a, const hb_pt *pa, const hb_ct *b, const hb_pt *pb, hb_ct **out) {
     return guard(c, [&] {
-        check_same(a, b, "mul2_add_rescale");
-        if (a->level != pa->level || a->level != pb->level) fail(HB_E_LEVEL, "mul2_add_rescale: level mismatch");
-        if (a->spow != 1) fail(HB_E_SHAPE, "mul2_add_rescale: operand not rescaled");
-        hb_ct *t = new_ct(c, a->level, a->np, a->batch, 2);
-        LAUNCH(c), k_mul2_add<<<c->egrid((int)a->limbs()), 256, 0, c->st>>>(t->d, a->d, pa->d, b->d, pb->d, c->qmap(a->level), c->pc, c->N);
-        try { *out = do_rescale(c, t); } catch (...) { hb_ct_free(t); throw; }
-        hb_ct_free(t);
+        const hb_ct *as[2] = {a, b};
+        const hb_pt *ps[2] = {pa, pb};
+        *out = do_prod_rescale(c, as, ps, 2, false);
     });
 }
-int hb_matmul_acc(hb_ctx *c, const hb_ct *pre, const hb_pt *pt, int64_t row_step, hb_ct **out) {
+int hb_matmul_acc_multi(hb_ctx *c, const hb_ct *pre, int btotal, int b0, const hb_pt *const *pts, int bcount, int64_t row_step, hb_ct **out) {
     return guard(c, [&] {
-        if (pre->level != pt->level) fail(HB_E_LEVEL, "matmul_acc: plaintext level differs from the ciphertexts'");
-        if (pre->np != 2 || pre->spow != 1 || pt->spow != 1) fail(HB_E_SHAPE, "matmul_acc: operands");
-        const int n = pre->level + 1, kc = pre->batch;
+        if (btotal < 1 || pre->batch % btotal || b0 < 0 || bcount < 1 || b0 + bcount > btotal || bcount > 16) fail(HB_E_SHAPE, "matmul_acc: group selection");
+        if (pre->np != 2 || pre->spow != 1) fail(HB_E_SHAPE, "matmul_acc: operands");
+        PtList pl{};
+        for (int b = 0; b < bcount; ++b) {
+            if (pre->level != pts[b]->level) fail(HB_E_LEVEL, "matmul_acc: plaintext level differs from the ciphertexts'");
+            if (pts[b]->spow != 1) fail(HB_E_SHAPE, "matmul_acc: operands");
+            pl.p[b] = pts[b]->d;
+        }
+        const int n = pre->level + 1, kc = pre->batch / btotal;
         std::vector<u32> gal((size_t)kc);
         for (int k = 0; k < kc; ++k) gal[(size_t)k] = (u32)c->h->galois_rot((i64)k * row_step);
         u32 *dg = (u32 *)c->pool.get((size_t)kc * 4);
         CK(cudaMemcpyAsync(dg, gal.data(), (size_t)kc * 4, cudaMemcpyHostToDevice, c->st));
         hb_ct *r = new_ct(c, pre->level, 2, 1, 2);
-        LAUNCH(c), k_matmul_acc<<<c->egrid(2 * n), 256, 0, c->st>>>(r->d, pre->d, kc, pt->d, dg, n, c->qmap(pre->level), c->pc, c->logn, c->N);
+        LAUNCH(c), k_matmul_acc<<<c->egrid(2 * n), 256, 0, c->st>>>(r->d, pre->d, kc, btotal, b0, bcount, pl, dg, n, c->qmap(pre->level), c->pc, c->logn, c->N);
         CK(cudaStreamSynchronize(c->st));
         c->pool.put(dg);
         *out = r;
     });
 }
+int hb_matmul_acc(hb_ctx *c, const hb_ct *pre, const hb_pt *pt, int64_t row_step, hb_ct **out) { return hb_matmul_acc_multi(c, pre, 1, 0, &pt, 1, row_step, out); }
 int hb_pt_rotate(hb_ctx *c, const hb_pt *p, int64_t steps, hb_pt **out) {
     return guard(c, [&] {
         hb_pt *r = new_pt(c, p->level, p->spow);

@@ -116,6 +116,61 @@ __global__ void k_rescale_fin(u64 *__restrict__ out, const u64 *__restrict__ x, 
     out[(size_t)w * N + i] = mul_mod(sub_mod(xv, t[(size_t)w * N + i], m.q), qlinv.v[l], m);
 }
 
+// ---------------- fused plaintext products with rescale ----------------
+// out = sum_j rescale(a_j (.) p_j)          (separate == 1: every term is rescaled on its own, as
+//                                             eval.mult(ct, mask) does, and the results are added)
+// out = rescale(sum_j a_j (.) p_j)          (separate == 0: the "assemble" step)
+// Rescale subtracts NTT_i(centred lift of the last limb) from limb i; NTT is linear modulo q_i, so the
+// centred lifts of all terms are summed as integers first and ONE transform per limb serves the whole
+// sum.  The stored residues equal those of the term-by-term sequence.
+constexpr int kMaxTerms = 24;
+struct TermList { const u64 *a[kMaxTerms]; const u64 *p[kMaxTerms]; int count; };
+// last[g][bp][x] = (sum over the terms of group g) a_j[bp][level][x] * p_j[level][x] mod q_level
+// grid = (N/256, nbp, groups)   groups = count (separate) or 1
+__global__ void k_last_prod(u64 *__restrict__ last, TermList tl, int separate, int level, int nbp, const PrimeConst *__restrict__ pc, int N) {
+    const int x = blockIdx.x * blockDim.x + threadIdx.x;
+    if (x >= N) return;
+    const int bp = blockIdx.y, g = blockIdx.z;
+    const PrimeConst m = pc[level];
+    const size_t ao = ((size_t)bp * (level + 1) + level) * N + x, po = (size_t)level * N + x;
+    const int j0 = separate ? g : 0, j1 = separate ? g + 1 : tl.count;
+    Acc128 s; s.zero();
+    for (int j = j0; j < j1; ++j) s.mad(tl.a[j][ao], tl.p[j][po]);
+    last[((size_t)g * nbp + bp) * N + x] = barrett128(s.hi, s.lo, m);
+}
+// S[bp][x] = sum_g centred(last[g][bp][x]) as a signed integer (|S| <= groups * q_level / 2)
+__global__ void k_centre_sum(i64 *__restrict__ S, const u64 *__restrict__ last, int groups, int nbp, int level, const PrimeConst *__restrict__ pc, int N) {
+    const int x = blockIdx.x * blockDim.x + threadIdx.x;
+    if (x >= N) return;
+    const int bp = blockIdx.y;
+    const u64 ql = pc[level].q, half = ql >> 1;
+    i64 acc = 0;
+    for (int g = 0; g < groups; ++g) {
+        const u64 r = last[((size_t)g * nbp + bp) * N + x];
+        acc += r > half ? (i64)r - (i64)ql : (i64)r;
+    }
+    S[(size_t)bp * N + x] = acc;
+}
+// t[bp][l][x] = S[bp][x] mod q_l.  grid.y = nbp * level
+__global__ void k_lift_mod(u64 *__restrict__ t, const i64 *__restrict__ S, int level, const PrimeConst *__restrict__ pc, int N) {
+    const int w = blockIdx.y, bp = w / level, l = w % level;
+    const int x = blockIdx.x * blockDim.x + threadIdx.x;
+    if (x >= N) return;
+    t[(size_t)w * N + x] = reduce_i64(S[(size_t)bp * N + x], pc[l]);
+}
+// out[bp][l][x] = (sum_j a_j[bp][l][x] * p_j[l][x] - t[bp][l][x]) * q_level^-1.  grid.y = nbp * level
+__global__ void k_prod_rescale_fin(u64 *__restrict__ out, TermList tl, const u64 *__restrict__ t, int level, const PrimeConst *__restrict__ pc, int N, Scalars qlinv) {
+    const int w = blockIdx.y, bp = w / level, l = w % level;
+    const int x = blockIdx.x * blockDim.x + threadIdx.x;
+    if (x >= N) return;
+    const PrimeConst m = pc[l];
+    const size_t ao = ((size_t)bp * (level + 1) + l) * N + x, po = (size_t)l * N + x;
+    Acc128 s; s.zero();
+    for (int j = 0; j < tl.count; ++j) s.mad(tl.a[j][ao], tl.p[j][po]);
+    const u64 v = barrett128(s.hi, s.lo, m);
+    out[(size_t)w * N + x] = mul_mod(sub_mod(v, t[(size_t)w * N + x], m.q), qlinv.v[l], m);
+}
+
 // ---------------- key switching ----------------
 // Per-level plan held in device memory.
 struct KsPlan {
@@ -294,24 +349,28 @@ __global__ void k_keygen(u64 *__restrict__ b, const u64 *__restrict__ a, const u
 }
 
 // ---------------- fused plaintext-matmul accumulate ----------------
-// out[p][l][i] = sum_k pre[k][p][l][i] * pt[l][perm_{g_k}(i)]     (scale Delta^2, no rescale)
-// grid = (N/256, 2*n).  The 128-bit accumulator is folded every 64 terms.
-__global__ void k_matmul_acc(u64 *__restrict__ out, const u64 *__restrict__ pre, int kcount, const u64 *__restrict__ pt, const u32 *__restrict__ gal, int n,
-                             LimbMap map, const PrimeConst *__restrict__ pc, int logn, int N) {
+// out[p][l][i] = sum_{b < bcount} sum_{k < kcount} pre[k * btotal + b0 + b][p][l][i] * pt_b[l][perm_{g_k}(i)]
+// (scale Delta^2, no rescale).  Shifted copies are stored k-major; the sum over b adds the partial products
+// of several K-groups in the same pass.  grid = (N/256, 2*n).  The 128-bit accumulator is folded every 64 terms.
+struct PtList { const u64 *p[16]; };
+__global__ void k_matmul_acc(u64 *__restrict__ out, const u64 *__restrict__ pre, int kcount, int btotal, int b0, int bcount, PtList pts, const u32 *__restrict__ gal,
+                             int n, LimbMap map, const PrimeConst *__restrict__ pc, int logn, int N) {
     const int pl = blockIdx.y, l = pl % n;
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= N) return;
     const PrimeConst m = pc[map.prime[l]];
-    const u64 *ptl = pt + (size_t)l * N;
-    const size_t kstride = (size_t)2 * n * N;
-    const u64 *p = pre + (size_t)pl * N + i;
+    const size_t estride = (size_t)2 * n * N;
     u64 total = 0;
     Acc128 s; s.zero();
+    int terms = 0;
     for (int k = 0; k < kcount; ++k) {
         const u32 g = __ldg(gal + k);
-        const u64 w = g == 1 ? ptl[i] : ptl[ntt_perm((u32)i, g, logn)];
-        s.mad(p[(size_t)k * kstride], w);
-        if ((k & 63) == 63) { total = add_mod(total, barrett128(s.hi, s.lo, m), m.q); s.zero(); }
+        const u32 src = g == 1 ? (u32)i : ntt_perm((u32)i, g, logn);
+        for (int b = 0; b < bcount; ++b) {
+            const u64 w = pts.p[b][(size_t)l * N + src];
+            s.mad(pre[((size_t)k * btotal + b0 + b) * estride + (size_t)pl * N + i], w);
+            if (++terms == 64) { total = add_mod(total, barrett128(s.hi, s.lo, m), m.q); s.zero(); terms = 0; }
+        }
     }
     total = add_mod(total, barrett128(s.hi, s.lo, m), m.q);
     out[(size_t)pl * N + i] = total;

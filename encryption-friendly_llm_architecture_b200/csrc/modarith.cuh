@@ -22,7 +22,10 @@ struct PrimeConst {
     u64 mu_hi, mu_lo;   // floor(2^128 / q)
     u64 n_inv, n_inv_sh; // N^-1 mod q and its Shoup companion
     u64 iu, iu_sh;      // psi^(N/2): the image of the imaginary unit
-    u64 pad;
+    u64 small;          // 1 when q < 2^44: the NTT uses the FP64-assisted product (see mul_fp_lazy)
+    double q_inv_f;     // 1/q
+    double n_inv_f;     // n_inv / q
+    u64 pad[2];
 };
 
 // Limb instances of a launch: instance li (0 <= li < count) uses prime[li % n].
@@ -62,6 +65,46 @@ __device__ __forceinline__ u64 reduce_i64(i64 v, const PrimeConst &m) {
     u64 r = reduce_u64((u64)(-(v + 1)), m);
     return m.q - 1 - r;
 }
+// ---- FP64-assisted product for primes below 2^44 ------------------------------------------
+// B200 issues 64-bit integer adds, compares and selects on a half-rate ALU pipe, and that pipe is
+// what bounds a Shoup butterfly (17 ALU instructions each).  For small primes the quotient
+// floor(y*w/q) is taken from the FP64 pipe instead: y < 2^52 converts exactly through the 2^52
+// magic constant, fma(y, w/q, 2^52) leaves round(y*w/q) in the mantissa (error well below 1),
+// and the remainder y*w - qh*q is exact in 64-bit integer arithmetic.  The result is congruent
+// to y*w and lies in (0.4q, 1.6q); final stores reduce to the canonical residue, so the bits
+// that reach memory are those of any other exact method.
+constexpr double kTwo52 = 4503599627370496.0;
+__device__ __forceinline__ double u52_to_double(u64 v) { return __longlong_as_double((long long)(v | 0x4330000000000000ull)) - kTwo52; }
+__device__ __forceinline__ u64 mantissa52(double d) { return (u64)__double_as_longlong(d) & 0x000FFFFFFFFFFFFFull; }
+// low 64 bits of a*b + c*d + e as one chain of integer multiply-adds (no separate add instructions)
+__device__ __forceinline__ u64 mad2_lo64(u64 a, u64 b, u64 c, u64 d, u64 e) {
+    const u32 a0 = (u32)a, a1 = (u32)(a >> 32), b0 = (u32)b, b1 = (u32)(b >> 32);
+    const u32 c0 = (u32)c, c1 = (u32)(c >> 32), d0 = (u32)d, d1 = (u32)(d >> 32);
+    u64 r;
+    asm("mad.wide.u32 %0, %1, %2, %3;" : "=l"(r) : "r"(a0), "r"(b0), "l"(e));
+    asm("mad.wide.u32 %0, %1, %2, %0;" : "+l"(r) : "r"(c0), "r"(d0));
+    u32 lo = (u32)r, hi = (u32)(r >> 32);
+    asm("mad.lo.u32 %0, %1, %2, %0;" : "+r"(hi) : "r"(a0), "r"(b1));
+    asm("mad.lo.u32 %0, %1, %2, %0;" : "+r"(hi) : "r"(a1), "r"(b0));
+    asm("mad.lo.u32 %0, %1, %2, %0;" : "+r"(hi) : "r"(c0), "r"(d1));
+    asm("mad.lo.u32 %0, %1, %2, %0;" : "+r"(hi) : "r"(c1), "r"(d0));
+    return ((u64)hi << 32) | lo;
+}
+__device__ __forceinline__ u64 mul_fp_lazy(u64 y, u64 w, double w_over_q, u64 q) {
+    const u64 qh = mantissa52(__fma_rn(u52_to_double(y), w_over_q, kTwo52));
+    return mad2_lo64(y, w, qh, 0ull - q, q); // y*w - qh*q + q
+}
+// v < 2^52 -> residue in (0.4q, 1.6q)
+__device__ __forceinline__ u64 reduce_fp_lazy(u64 v, double q_inv, u64 q) {
+    const u64 qh = mantissa52(__fma_rn(u52_to_double(v), q_inv, kTwo52));
+    return v - qh * q + q;
+}
+// v < 2^52 -> canonical residue
+__device__ __forceinline__ u64 reduce_fp(u64 v, double q_inv, u64 q) {
+    const u64 r = reduce_fp_lazy(v, q_inv, q); // (0.4q, 1.6q)
+    return r >= q ? r - q : r;
+}
+
 // 128-bit accumulator for lazy sums of products
 struct Acc128 {
     u64 lo, hi;

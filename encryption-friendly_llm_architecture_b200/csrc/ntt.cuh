@@ -70,6 +70,51 @@ __device__ __forceinline__ void inv16(u64 (&v)[16], const u64 *__restrict__ w, c
     }
 }
 
+// ---- small-prime variants: the second twiddle table holds w/q as a double ----
+// forward: values only grow by < 1.6q per stage (canonical input, 16 stages: < 27q < 2^47), no corrections
+__device__ __forceinline__ void ct_bfly_fp(u64 &x, u64 &y, u64 w, double wf, u64 q, u64 q2) {
+    const u64 t = mul_fp_lazy(y, w, wf, q);
+    y = x + q2 - t;
+    x = x + t;
+}
+// inverse: the sum path doubles per stage, so callers reduce every four stages; `off` is a multiple of q
+// above the largest y of the stage
+__device__ __forceinline__ void gs_bfly_fp(u64 &x, u64 &y, u64 w, double wf, u64 q, u64 off) {
+    const u64 s = x + y;
+    const u64 d = x + off - y;
+    x = s;
+    y = mul_fp_lazy(d, w, wf, q);
+}
+__device__ __forceinline__ void fwd16_fp(u64 (&v)[16], const u64 *__restrict__ w, const double *__restrict__ wf, u32 base, u64 q) {
+    const u64 q2 = q << 1;
+#pragma unroll
+    for (int s = 0; s < 4; ++s) {
+        const int half = 8 >> s;
+#pragma unroll
+        for (int g = 0; g < (1 << s); ++g) {
+            const u64 tw = __ldg(w + ((base << s) + g));
+            const double twf = __ldg(wf + ((base << s) + g));
+#pragma unroll
+            for (int j = 0; j < half; ++j) ct_bfly_fp(v[g * 2 * half + j], v[g * 2 * half + j + half], tw, twf, q, q2);
+        }
+    }
+}
+// inputs below 2q; outputs below 32q (sum path) -- reduce before the next round
+__device__ __forceinline__ void inv16_fp(u64 (&v)[16], const u64 *__restrict__ w, const double *__restrict__ wf, u32 base, u64 q) {
+#pragma unroll
+    for (int s = 3; s >= 0; --s) {
+        const int half = 8 >> s;
+        const u64 off = q << (4 - s); // inputs of local stage s are below 2q * 2^(3-s)
+#pragma unroll
+        for (int g = 0; g < (1 << s); ++g) {
+            const u64 tw = __ldg(w + ((base << s) + g));
+            const double twf = __ldg(wf + ((base << s) + g));
+#pragma unroll
+            for (int j = 0; j < half; ++j) gs_bfly_fp(v[g * 2 * half + j], v[g * 2 * half + j + half], tw, twf, q, off);
+        }
+    }
+}
+
 constexpr int kN16 = 65536;
 constexpr int kRowStride = 272; // 256 + one pad word per 16: conflict-free 16-consecutive reads
 
@@ -83,16 +128,18 @@ __global__ void __launch_bounds__(256) ntt16_fwd_cols(const u64 *__restrict__ sr
     const int tid = threadIdx.x, lane = tid & 15, sub = tid >> 4;
     const u64 *p = src + sa.off(li, map.n, kN16) + blockIdx.x * 16 + lane;
     u64 *o = dst + da.off(li, map.n, kN16) + blockIdx.x * 16 + lane;
+    const bool fp = pc[pi].small != 0;
+    const double *wf = reinterpret_cast<const double *>(ws);
     u64 v[16];
 #pragma unroll
     for (int e = 0; e < 16; ++e) v[e] = p[(e * 16 + sub) * 256];
-    fwd16(v, w, ws, 1u, q);
+    if (fp) fwd16_fp(v, w, wf, 1u, q); else fwd16(v, w, ws, 1u, q);
 #pragma unroll
     for (int e = 0; e < 16; ++e) sm[(e * 16 + sub) * 16 + lane] = v[e];
     __syncthreads();
 #pragma unroll
     for (int e = 0; e < 16; ++e) v[e] = sm[(sub * 16 + e) * 16 + lane];
-    fwd16(v, w, ws, 16u + sub, q);
+    if (fp) fwd16_fp(v, w, wf, 16u + sub, q); else fwd16(v, w, ws, 16u + sub, q);
 #pragma unroll
     for (int e = 0; e < 16; ++e) o[(sub * 16 + e) * 256] = v[e];
 }
@@ -109,21 +156,24 @@ __global__ void __launch_bounds__(256) ntt16_fwd_rows(const u64 *__restrict__ sr
     const u64 *p = src + sa.off(li, map.n, kN16) + (size_t)row * 256 + clo;
     u64 *o = dst + da.off(li, map.n, kN16) + (size_t)row * 256 + clo;
     u64 *smr = sm + rl * kRowStride;
+    const bool fp = pc[pi].small != 0;
+    const double *wf = reinterpret_cast<const double *>(ws);
+    const double qinv = pc[pi].q_inv_f;
     u64 v[16];
 #pragma unroll
     for (int e = 0; e < 16; ++e) v[e] = p[e * 16];
-    fwd16(v, w, ws, 256u + row, q);
+    if (fp) fwd16_fp(v, w, wf, 256u + row, q); else fwd16(v, w, ws, 256u + row, q);
 #pragma unroll
     for (int e = 0; e < 16; ++e) smr[e * 17 + clo] = v[e];
     __syncthreads();
 #pragma unroll
     for (int e = 0; e < 16; ++e) v[e] = smr[clo * 17 + e];
-    fwd16(v, w, ws, ((256u + row) << 4) + clo, q);
+    if (fp) fwd16_fp(v, w, wf, ((256u + row) << 4) + clo, q); else fwd16(v, w, ws, ((256u + row) << 4) + clo, q);
 #pragma unroll
     for (int e = 0; e < 16; ++e) {
         u64 x = v[e];
-        x = x >= q2 ? x - q2 : x;
-        x = x >= q ? x - q : x;
+        if (fp) x = reduce_fp(x, qinv, q);
+        else { x = x >= q2 ? x - q2 : x; x = x >= q ? x - q : x; }
         smr[clo * 17 + e] = x;
     }
     __syncthreads();
@@ -132,7 +182,7 @@ __global__ void __launch_bounds__(256) ntt16_fwd_rows(const u64 *__restrict__ sr
 }
 
 // ---- inverse, row pass: undoes stages 16..9.  Input canonical, output [0, 2q). ----
-__global__ void __launch_bounds__(256) ntt16_inv_rows(const u64 *__restrict__ src, LimbAddr sa, u64 *__restrict__ dst, LimbAddr da,
+__global__ void __launch_bounds__(256, 3) ntt16_inv_rows(const u64 *__restrict__ src, LimbAddr sa, u64 *__restrict__ dst, LimbAddr da,
                                                       LimbMap map, const PrimeConst *__restrict__ pc, NttTables tb) {
     __shared__ u64 sm[16 * kRowStride];
     const int li = blockIdx.y, pi = map.prime[li % map.n];
@@ -147,21 +197,32 @@ __global__ void __launch_bounds__(256) ntt16_inv_rows(const u64 *__restrict__ sr
 #pragma unroll
     for (int e = 0; e < 16; ++e) smr[e * 17 + clo] = p[e * 16];
     __syncthreads();
+    const bool fp = pc[pi].small != 0;
+    const double *wf = reinterpret_cast<const double *>(ws);
+    const double qinv = pc[pi].q_inv_f;
 #pragma unroll
     for (int e = 0; e < 16; ++e) v[e] = smr[clo * 17 + e];
-    inv16(v, w, ws, ((256u + row) << 4) + clo, q);
+    if (fp) {
+        inv16_fp(v, w, wf, ((256u + row) << 4) + clo, q);
+#pragma unroll
+        for (int e = 0; e < 16; ++e) v[e] = reduce_fp_lazy(v[e], qinv, q);
+    } else inv16(v, w, ws, ((256u + row) << 4) + clo, q);
 #pragma unroll
     for (int e = 0; e < 16; ++e) smr[clo * 17 + e] = v[e];
     __syncthreads();
 #pragma unroll
     for (int e = 0; e < 16; ++e) v[e] = smr[e * 17 + clo];
-    inv16(v, w, ws, 256u + row, q);
+    if (fp) {
+        inv16_fp(v, w, wf, 256u + row, q);
+#pragma unroll
+        for (int e = 0; e < 16; ++e) v[e] = reduce_fp_lazy(v[e], qinv, q);
+    } else inv16(v, w, ws, 256u + row, q);
 #pragma unroll
     for (int e = 0; e < 16; ++e) o[e * 16] = v[e];
 }
 
 // ---- inverse, column pass: undoes stages 8..1, scales by N^-1.  Input [0, 2q), output canonical. ----
-__global__ void __launch_bounds__(256) ntt16_inv_cols(const u64 *__restrict__ src, LimbAddr sa, u64 *__restrict__ dst, LimbAddr da,
+__global__ void __launch_bounds__(256, 3) ntt16_inv_cols(const u64 *__restrict__ src, LimbAddr sa, u64 *__restrict__ dst, LimbAddr da,
                                                       LimbMap map, const PrimeConst *__restrict__ pc, NttTables tb) {
     __shared__ u64 sm[4096];
     const int li = blockIdx.y, pi = map.prime[li % map.n];
@@ -171,18 +232,35 @@ __global__ void __launch_bounds__(256) ntt16_inv_cols(const u64 *__restrict__ sr
     const int tid = threadIdx.x, lane = tid & 15, sub = tid >> 4;
     const u64 *p = src + sa.off(li, map.n, kN16) + blockIdx.x * 16 + lane;
     u64 *o = dst + da.off(li, map.n, kN16) + blockIdx.x * 16 + lane;
+    const bool fp = pc[pi].small != 0;
+    const double *wf = reinterpret_cast<const double *>(ws);
+    const double qinv = pc[pi].q_inv_f, ninv_f = pc[pi].n_inv_f;
     u64 v[16];
 #pragma unroll
     for (int e = 0; e < 16; ++e) v[e] = p[(sub * 16 + e) * 256];
-    inv16(v, w, ws, 16u + sub, q);
+    if (fp) {
+        inv16_fp(v, w, wf, 16u + sub, q);
+#pragma unroll
+        for (int e = 0; e < 16; ++e) v[e] = reduce_fp_lazy(v[e], qinv, q);
+    } else inv16(v, w, ws, 16u + sub, q);
 #pragma unroll
     for (int e = 0; e < 16; ++e) sm[(sub * 16 + e) * 16 + lane] = v[e];
     __syncthreads();
 #pragma unroll
     for (int e = 0; e < 16; ++e) v[e] = sm[(e * 16 + sub) * 16 + lane];
-    inv16(v, w, ws, 1u, q);
+    if (fp) {
+        inv16_fp(v, w, wf, 1u, q);
 #pragma unroll
-    for (int e = 0; e < 16; ++e) o[(e * 16 + sub) * 256] = mul_shoup(v[e], ninv, ninv_sh, q);
+        for (int e = 0; e < 16; ++e) {
+            // x * N^-1: quotient from the FP64 pipe, remainder in (-0.6q, 0.6q) shifted by q, then canonical
+            u64 r = mul_fp_lazy(v[e], ninv, ninv_f, q);
+            o[(e * 16 + sub) * 256] = r >= q ? r - q : r;
+        }
+    } else {
+        inv16(v, w, ws, 1u, q);
+#pragma unroll
+        for (int e = 0; e < 16; ++e) o[(e * 16 + sub) * 256] = mul_shoup(v[e], ninv, ninv_sh, q);
+    }
 }
 
 // ---- whole limb in shared memory, N <= 4096 ----

@@ -152,6 +152,12 @@ class Hemmer:
     def matmul_reuse(self, pre, w):
         return CtxtTensor(self._call("matmul_reuse", pre.ptr, w.ct.ptr, *self._shp(w)), *w.shape)
 
+    def matmul_reuse_groups(self, pre, btotal, b0, weights):
+        """Sum over K-groups b0.. of matMulReUse(pre_b, weights[b]); `pre` holds the copies of `btotal` inputs."""
+        arr = (C.c_void_p * len(weights))(*[w.ct.ptr.value for w in weights])
+        ct = self._call("matmul_reuse_groups", pre.ptr, C.c_int(btotal), C.c_int(b0), arr, C.c_int(len(weights)), C.c_int(weights[0].width))
+        return CtxtTensor(ct, *weights[0].shape)
+
     def matmul_pre_rev(self, b, target_level=4):
         return CtxtTensor(self._call("matmul_pre_rev", b.ct.ptr, *self._shp(b), C.c_int(target_level)), *b.shape)
 

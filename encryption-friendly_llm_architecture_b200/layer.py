@@ -47,7 +47,18 @@ def tiles(m, r, c):
 
 
 class LayerWorkload:
-    """Builds the unit list once (weights encoded, masks and keys warmed by the first step)."""
+    """The layer's matmuls as a few large batched calls.
+
+    ct x pt: the K-groups of all four sublayers go through complexPacking + matMulPre as one batch
+    (groups with two ciphertexts and groups with one are separate batches, because they are packed
+    differently); every output tile is then one fused pass over the shifted copies of its sublayer's
+    groups.  ct x ct: the 42 products share one schedule, so they run as three batches (no transpose,
+    right operand transposed, left operand transposed).  Every batch entry is computed exactly as it
+    would be alone; batching only puts more ciphertexts behind each kernel launch.
+    """
+
+    PCMM = [("qkv", "x", ["wq", "wk", "wv"], HIDDEN, HIDDEN), ("wo", "x", ["wo"], HIDDEN, HIDDEN),
+            ("w1", "x", ["w1"], HIDDEN, FFN), ("w2", "h", ["w2"], FFN, HIDDEN)]
 
     def __init__(self, H: Hemmer, data, rank: int = 0, world: int = 1, target: int = 4):
         self.H, self.lib, self.data, self.rank, self.world, self.target = H, H.lib, data, rank, world, target
@@ -56,20 +67,14 @@ class LayerWorkload:
         self.h2d_bytes = 0
         self.d2h_bytes = 0
         self._weights = {}
+        self.resident = None
 
     # ---- unit construction ----
     def _build_units(self):
-        d = self.data
         units = []
-        # ct x pt: one unit per group of four K-tiles (matMulPre) with all its output tiles (matMulReUse)
-        def pcmm(name, x, weights, kt, nt):
+        for name, x, weights, kt, nt in self.PCMM:
             for g in range((kt + 3) // 4):
                 units.append(("pcmm", name, x, weights, g, kt, nt))
-        pcmm("qkv", "x", ["wq", "wk", "wv"], HIDDEN, HIDDEN)
-        pcmm("wo", "x", ["wo"], HIDDEN, HIDDEN)
-        pcmm("w1", "x", ["w1"], HIDDEN, FFN)
-        pcmm("w2", "h", ["w2"], FFN, HIDDEN)
-        # ct x ct, two tiles per ciphertext
         for ad in range(2):                      # LoRA forward: X*A (K-split over 3 pairs) and (XA)*B (3 output pairs)
             for p in range(3):
                 units.append(("ccmm", f"lora{ad}_xa{p}", ("x_pair", p), ("a_pair", ad, p), False))
@@ -114,11 +119,6 @@ class LayerWorkload:
             return d["s"][2 * spec[1]], d["s"][2 * spec[1] + 1]
         raise KeyError(kind)
 
-    def _encrypt_pair(self, spec, nonce):
-        a, b = self._pair(spec)
-        self.h2d_bytes += 2 * self.lib.N * 8
-        return self.H.encrypt2(a, b, nonce=nonce), (a, b)
-
     def _weight_pts(self, wname, g, kt, nt):
         key = (wname, g)
         if key not in self._weights:
@@ -131,48 +131,86 @@ class LayerWorkload:
             self._weights[key] = pts
         return self._weights[key]
 
-    # ---- execution ----
-    def _operands(self, u, nonce0):
-        """Encode + encrypt the unit's operands from host matrices (host -> device traffic)."""
+    def _batch(self, cts):
+        """Gather single ciphertexts into one batched handle (device-to-device copies)."""
+        lib = self.lib
+        level, npoly, _, spow = lib.ct_meta(cts[0].ct)
+        out = lib.ct_create(level, npoly, len(cts), spow)
+        for k, c in enumerate(cts):
+            lib.batch_set(out, k, c.ct)
+        return CtxtTensor(out, *cts[0].shape)
+
+    # ---- host -> device ----
+    def _encrypt_all(self, nonce0):
+        """Encode + encrypt every operand of this rank's units and group them into batches."""
         H, lib = self.H, self.lib
         per_ct = 2 * lib.N * 8  # rounded message coefficients + error polynomial uploaded per encryption
-        if u[0] == "pcmm":
-            _, name, xname, weights, g, kt, nt = u
-            x = self.data[xname]
-            pair = lambda p: (tiles(x, 0, 2 * p), tiles(x, 0, 2 * p + 1))
-            cts = [H.encrypt2(*pair(2 * g), nonce=nonce0)]
-            if 4 * g + 2 < kt:
-                cts.append(H.encrypt2(*pair(2 * g + 1), nonce=nonce0 + 1))
-            self.h2d_bytes += per_ct * len(cts)
-            for wname in weights:
-                self._weight_pts(wname, g, kt, nt)
-            return cts
-        _, name, lhs, rhs, tr = u
-        a, b = self._pair(lhs), self._pair(rhs)
-        self.h2d_bytes += 2 * per_ct
-        return [H.encrypt2(*a, nonce=nonce0), H.encrypt2(*b, nonce=nonce0 + 1)]
+        groups = {"full": [], "half": []}      # pcmm: (unit, [cts])
+        ccmm = {False: [], True: [], "left": []}
+        n = nonce0
+        for u in self.mine:
+            if u[0] == "pcmm":
+                _, name, xname, weights, g, kt, nt = u
+                x = self.data[xname]
+                pair = lambda p: (tiles(x, 0, 2 * p), tiles(x, 0, 2 * p + 1))
+                cts = [H.encrypt2(*pair(2 * g), nonce=n)]
+                if 4 * g + 2 < kt:
+                    cts.append(H.encrypt2(*pair(2 * g + 1), nonce=n + 1))
+                self.h2d_bytes += per_ct * len(cts)
+                for wname in weights:
+                    self._weight_pts(wname, g, kt, nt)
+                groups["full" if len(cts) == 2 else "half"].append((u, cts))
+            else:
+                _, name, lhs, rhs, tr = u
+                a, b = self._pair(lhs), self._pair(rhs)
+                self.h2d_bytes += 2 * per_ct
+                ccmm[tr].append((u, H.encrypt2(*a, nonce=n), H.encrypt2(*b, nonce=n + 1)))
+            n += 2
+        res = {"pcmm": {}, "ccmm": {}}
+        for kind, lst in groups.items():
+            if lst:
+                res["pcmm"][kind] = ([u for u, _ in lst], self._batch([c[0] for _, c in lst]),
+                                     self._batch([c[1] for _, c in lst]) if kind == "full" else None)
+        for tr, lst in ccmm.items():
+            if lst:
+                res["ccmm"][tr] = ([u for u, _, _ in lst], self._batch([a for _, a, _ in lst]), self._batch([b for _, _, b in lst]))
+        return res
 
-    def _compute(self, u, cts):
+    # ---- device work ----
+    def _compute(self, res):
         H, t = self.H, self.target
-        if u[0] == "pcmm":
-            _, name, xname, weights, g, kt, nt = u
-            packed = H.complex_packing(cts[0], cts[1]) if len(cts) == 2 else cts[0]
-            pre = H.matmul_pre(packed, t)
-            return [H.matmul_reuse(pre, pt) for wname in weights for pt in self._weight_pts(wname, g, kt, nt)]
-        _, name, lhs, rhs, tr = u
-        a = CtxtTensor(cts[0].ct, *cts[0].shape)
-        b = CtxtTensor(cts[1].ct, *cts[1].shape)
-        if tr is True:
-            H.transpose_inplace(b)
-        elif tr == "left":
-            H.transpose_inplace(a)
-        return [H.single_cc_matmul(a, b, t)]
+        out = {"pcmm": {}, "ccmm": {}}
+        pres = {}
+        for kind, (us, c01, c23) in res["pcmm"].items():
+            packed = H.complex_packing(c01, c23) if c23 is not None else c01
+            pres[kind] = (us, H.matmul_pre(packed, t))
+        # every (sublayer, weight, output tile): one fused pass per batch of K-groups, partial sums added
+        for name, xname, weights, kt, nt in self.PCMM:
+            for wname in weights:
+                for j in range(nt):
+                    acc = None
+                    for kind, (us, pre) in pres.items():
+                        sel = [(b, u) for b, u in enumerate(us) if u[1] == name]
+                        if not sel:
+                            continue
+                        b0 = sel[0][0]
+                        pts = [self._weight_pts(wname, u[4], kt, nt)[j] for _, u in sel]
+                        part = H.matmul_reuse_groups(pre, len(us), b0, pts)
+                        acc = part if acc is None else CtxtTensor(self.lib.add(acc.ct, part.ct), *part.shape)
+                    if acc is not None:
+                        out["pcmm"][(name, wname, j)] = acc
+        for tr, (us, a, b) in res["ccmm"].items():
+            a = CtxtTensor(a.ct, *a.shape)
+            b = CtxtTensor(b.ct, *b.shape)
+            if tr is True:
+                H.transpose_inplace(b)
+            elif tr == "left":
+                H.transpose_inplace(a)
+            out["ccmm"][tr] = (us, H.single_cc_matmul(a, b, t))
+        return out
 
-    def _expected(self, u):
-        if u[0] == "pcmm":
-            _, name, xname, weights, g, kt, nt = u
-            x, w = self.data[xname], self.data[weights[0]]
-            return sum(tiles(x, 0, 4 * g + i) @ tiles(w, 4 * g + i, 0) for i in range(4) if 4 * g + i < kt)
+    # ---- device -> host ----
+    def _expected_ccmm(self, u):
         _, name, lhs, rhs, tr = u
         (a0, a1), (b0, b1) = self._pair(lhs), self._pair(rhs)
         if tr is True:
@@ -181,45 +219,45 @@ class LayerWorkload:
             a0, a1 = a0.T, a1.T
         return np.stack([a0 @ b0, a1 @ b1])
 
-    def _decrypted(self, u, out):
-        """Device -> host: decrypt the first result of the unit into matrices."""
-        self.d2h_bytes += 2 * self.lib.N * 8
-        if u[0] == "pcmm":
-            z = self.lib.decrypt(out[0].ct).reshape(D, 2 * D)
-            return 2 * (z[:, :D].real + z[:, D:].real)
-        return self.H.decrypt2(out[0])
+    def _decrypt_all(self, out, check=False):
+        """Decrypt every result to host matrices; returns the max-abs error when `check`."""
+        err = 0.0
+        per = 2 * self.lib.N * 8
+        complete = self.world == 1  # with several ranks a ct x pt output may still miss other ranks' K-groups
+        for (name, wname, j), ct in out["pcmm"].items():
+            z = self.lib.decrypt(ct.ct).reshape(D, 2 * D)
+            self.d2h_bytes += per
+            got = 2 * (z[:, :D].real + z[:, D:].real)
+            if check and complete:
+                spec = [p for p in self.PCMM if p[0] == name][0]
+                x, w = self.data[spec[1]], self.data[wname]
+                err = max(err, float(np.abs(got - x[:, : spec[3] * D] @ w[: spec[3] * D, j * D:(j + 1) * D]).max()))
+        for tr, (us, c) in out["ccmm"].items():
+            for k, u in enumerate(us):
+                z = self.lib.decrypt(c.ct, k)[: D * 2 * D].real.reshape(D, 2 * D)
+                self.d2h_bytes += per
+                if check:
+                    exp = self._expected_ccmm(u)
+                    err = max(err, float(np.abs(z[:, :D] - exp[0]).max()), float(np.abs(z[:, D:] - exp[1]).max()))
+        return err
 
+    # ---- public steps ----
     def prepare(self):
         """Make every operand of this rank's units resident on the device."""
-        self.resident = [self._operands(u, 10_000 + 16 * i) for i, u in enumerate(self.mine)]
+        self.resident = self._encrypt_all(10_000)
 
     def step_resident(self):
-        last = None
-        for u, cts in zip(self.mine, self.resident):
-            last = self._compute(u, cts)
-        return last
+        return self._compute(self.resident)
 
     def step(self):
-        last = None
-        for i, u in enumerate(self.mine):
-            last = self._compute(u, self._operands(u, 10_000 + 16 * i))
-        return last
+        return self._compute(self._encrypt_all(10_000))
 
     def step_e2e(self):
-        """Host matrices in, decrypted host matrices out, for every unit."""
-        res = None
-        for i, u in enumerate(self.mine):
-            out = self._compute(u, self._operands(u, 30_000 + 16 * i))
-            res = self._decrypted(u, out)
-        return res
+        """Host matrices in, decrypted host matrices out."""
+        out = self._compute(self._encrypt_all(30_000))
+        self._decrypt_all(out)
+        return out
 
-    def check(self, which=(0, -1)):
-        """Max-abs error of a few units against the float64 products."""
-        err = 0.0
-        for k in which:
-            if not self.mine:
-                break
-            u = self.mine[k]
-            out = self._compute(u, self._operands(u, 20_000 + 16 * (k % 1000)))
-            err = max(err, float(np.abs(self._decrypted(u, out) - self._expected(u)).max()))
-        return err
+    def check(self):
+        """Max-abs error of every result of this rank against the float64 products."""
+        return self._decrypt_all(self._compute(self._encrypt_all(20_000)), check=True)

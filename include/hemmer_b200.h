@@ -98,6 +98,7 @@ int hb_ct_import(hb_ctx *ctx, hb_ct *ct, const uint64_t *host);
 int hb_ct_export(hb_ctx *ctx, const hb_ct *ct, uint64_t *host);
 int hb_pt_export(hb_ctx *ctx, const hb_pt *pt, uint64_t *host);
 void *hb_ct_device_ptr(const hb_ct *ct);
+/* copies all of src's entries to positions index*src_batch .. of dst */
 int hb_batch_set(hb_ctx *ctx, hb_ct *dst, int index, const hb_ct *src);
 int hb_batch_get(hb_ctx *ctx, const hb_ct *src, int index, hb_ct **out);
 
@@ -133,10 +134,17 @@ int hb_ntt(hb_ctx *ctx, hb_ct *a, int inverse);
 /* Fused forms used by the matmul schedules (bit-identical to the unfused sequences). */
 /* out = rescale(a (.) pa + b (.) pb)   -- MatrixUtils.cpp:1424-1427 "assemble" */
 int hb_mul2_add_rescale(hb_ctx *ctx, const hb_ct *a, const hb_pt *pa, const hb_ct *b, const hb_pt *pb, hb_ct **out);
+/* out = sum_j mult(a[j], p[j])  (each product rescaled, then added) -- the baby-step sums of the linear
+ * transforms, MatrixUtils.cpp:815-823, 832-840.  At most 24 terms. */
+int hb_mul_pt_sum(hb_ctx *ctx, const hb_ct *const *a, const hb_pt *const *p, int count, hb_ct **out);
 /* acc += tensor(a, b); *acc may be NULL on entry -- MatrixUtils.cpp:1434-1439 */
 int hb_tensor_acc(hb_ctx *ctx, const hb_ct *a, const hb_ct *b, hb_ct **acc);
 /* out = sum_k pre[k] (.) rot_rows(pt, k * row_step), un-rescaled -- HomEvaluator::matmul :595-601 */
 int hb_matmul_acc(hb_ctx *ctx, const hb_ct *pre, const hb_pt *pt, int64_t row_step, hb_ct **out);
+/* the same over several K-groups at once: `pre` holds the shifted copies of `btotal` independent inputs, copy k of
+ * input b at batch position k*btotal + b; the products of inputs b0 .. b0+bcount-1 with pts[0..bcount-1] are
+ * summed into one ciphertext (matMulReUse + addInplace over groups, bert-matmul.cpp:262-268) */
+int hb_matmul_acc_multi(hb_ctx *ctx, const hb_ct *pre, int btotal, int b0, const hb_pt *const *pts, int bcount, int64_t row_step, hb_ct **out);
 /* rotation of a plaintext (pure slot permutation, no key) -- leftRotate(ptxt) used at MatrixUtils.cpp:1503 */
 int hb_pt_rotate(hb_ctx *ctx, const hb_pt *p, int64_t left_steps, hb_pt **out);
 /* modReduct after a lazy sum across ranks -- HomEvaluator.hpp:602-605 */

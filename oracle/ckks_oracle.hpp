@@ -487,7 +487,7 @@ struct Evaluator {
     // (the cpu-baseline leg multiplies them by sampled per-operation times).
     bool dry = false;
     std::map<std::pair<std::string, int>, long> stats;
-    bool count(const char *op, int level) { if (dry) ++stats[{op, level}]; return dry; }
+    bool count(const char *op, int level, int batch = 1) { if (dry) stats[{op, level}] += batch; return dry; }
     Ct meta(int level, int np, int batch, int spow) const { return Ct(cx.N, level, np, batch, spow, true); }
 
     // EnDecoder::encode (HEaaN/EnDecoder.hpp:51): slots -> plaintext at `level`, scale Delta_level
@@ -752,7 +752,7 @@ struct Evaluator {
             return add(x, level_down(y, x.level), subtract);
         }
         require(x.np == y.np && x.spow == y.spow && x.batch == y.batch, "add: shape mismatch");
-        if (count("add", x.level)) return meta(x.level, x.np, x.batch, x.spow);
+        if (count("add", x.level, x.batch)) return meta(x.level, x.np, x.batch, x.spow);
         Ct r = x;
         const int n = x.level + 1, N = cx.N;
 #pragma omp parallel for
@@ -765,7 +765,7 @@ struct Evaluator {
         return r;
     }
     Ct negate(const Ct &x) {
-        if (count("add", x.level)) return meta(x.level, x.np, x.batch, x.spow);
+        if (count("add", x.level, x.batch)) return meta(x.level, x.np, x.batch, x.spow);
         Ct r = x; const int n = x.level + 1, N = cx.N;
         for (int i = 0; i < x.batch * x.np * n; ++i) {
             const Mod &m = cx.mod[i % n]; u64 *o = r.d.data() + (size_t)i * N;
@@ -776,7 +776,7 @@ struct Evaluator {
     // HomEvaluator::multImagUnit (HomEvaluator.hpp:329-331): multiply by X^(N/2); in NTT form this is
     // +iota on the first half of the limb and -iota on the second half, iota = psi^(N/2).
     Ct mult_imag(const Ct &x) {
-        if (count("mult_imag", x.level)) return meta(x.level, x.np, x.batch, x.spow);
+        if (count("mult_imag", x.level, x.batch)) return meta(x.level, x.np, x.batch, x.spow);
         Ct r = x; const int n = x.level + 1, N = cx.N;
 #pragma omp parallel for
         for (int i = 0; i < x.batch * x.np * n; ++i) {
@@ -789,7 +789,7 @@ struct Evaluator {
     }
     // HomEvaluator::multInteger (HomEvaluator.hpp:346-348)
     Ct mult_int(const Ct &x, i64 k) {
-        if (count("mult_imag", x.level)) return meta(x.level, x.np, x.batch, x.spow);
+        if (count("mult_imag", x.level, x.batch)) return meta(x.level, x.np, x.batch, x.spow);
         Ct r = x; const int n = x.level + 1, N = cx.N;
 #pragma omp parallel for
         for (int i = 0; i < x.batch * x.np * n; ++i) {
@@ -802,7 +802,7 @@ struct Evaluator {
     Ct mul_pt_norescale(const Ct &x, const Pt &p) {
         require(x.level == p.level, "mul_pt: level mismatch");
         require(x.spow == 1 && p.spow == 1 && x.np == 2, "mul_pt: operand not rescaled");
-        if (count("mul_pt", x.level)) return meta(x.level, x.np, x.batch, 2);
+        if (count("mul_pt", x.level, x.batch)) return meta(x.level, x.np, x.batch, 2);
         Ct r = x; r.spow = 2; const int n = x.level + 1, N = cx.N;
 #pragma omp parallel for
         for (int i = 0; i < x.batch * x.np * n; ++i) {
@@ -819,7 +819,7 @@ struct Evaluator {
     Ct rescale(const Ct &x) {
         require(x.level >= 1, "rescale: level 0");
         require(x.spow == 2, "rescale: nothing to rescale");
-        if (count(x.np == 3 ? "rescale3" : "rescale", x.level)) return meta(x.level - 1, x.np, x.batch, 1);
+        if (count(x.np == 3 ? "rescale3" : "rescale", x.level, x.batch)) return meta(x.level - 1, x.np, x.batch, 1);
         const int l = x.level, N = cx.N; const u64 ql = cx.mod[l].q;
         Ct r(N, l - 1, x.np, x.batch, 1);
         const int nbp = x.batch * x.np;
@@ -853,7 +853,7 @@ struct Evaluator {
         if (target == x.level) return x;
         require(x.spow == 1, "level_down: operand not rescaled");
         const int N = cx.N;
-        if (count("scalar_mul", target + 1)) return rescale(meta(target + 1, x.np, x.batch, 2));
+        if (count("scalar_mul", target + 1, x.batch)) return rescale(meta(target + 1, x.np, x.batch, 2));
         Ct t(N, target + 1, x.np, x.batch, 2);
         double cf = cx.scale[target] * (double)cx.mod[target + 1].q / cx.scale[x.level];
         i64 k = (i64)std::rint(cf);
@@ -870,7 +870,7 @@ struct Evaluator {
     Ct tensor(const Ct &x, const Ct &y) {
         require(x.level == y.level && x.np == 2 && y.np == 2 && x.spow == 1 && y.spow == 1 && x.batch == y.batch, "tensor: operands");
         const int n = x.level + 1, N = cx.N;
-        if (count("tensor", x.level)) return meta(x.level, 3, x.batch, 2);
+        if (count("tensor", x.level, x.batch)) return meta(x.level, 3, x.batch, 2);
         Ct r(N, x.level, 3, x.batch, 2);
 #pragma omp parallel for collapse(2)
         for (int b = 0; b < x.batch; ++b)
@@ -889,7 +889,7 @@ struct Evaluator {
     // HomEvaluator::relinearize (HomEvaluator.hpp:524)
     Ct relin(const Ct &x) {
         require(x.np == 3, "relin: needs 3 polys");
-        if (count("relin", x.level)) return meta(x.level, 2, x.batch, x.spow);
+        if (count("relin", x.level, x.batch)) return meta(x.level, 2, x.batch, x.spow);
         const int n = x.level + 1, N = cx.N;
         Ct r(N, x.level, 2, x.batch, x.spow);
         for (int b = 0; b < x.batch; ++b) {
@@ -917,7 +917,7 @@ struct Evaluator {
     Ct apply_galois(const Ct &x, u64 g) {
         require(x.np == 2, "rotate: needs 2 polys");
         if (g == 1) return x;
-        if (count("rotate", x.level)) return meta(x.level, 2, x.batch, x.spow);
+        if (count("rotate", x.level, x.batch)) return meta(x.level, 2, x.batch, x.spow);
         auto it = gal_keys.find(g);
         if (it == gal_keys.end()) throw std::runtime_error("missing galois key");
         const int n = x.level + 1, N = cx.N;

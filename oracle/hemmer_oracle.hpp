@@ -535,14 +535,30 @@ struct Hemmer {
         std::memcpy(r.d.data(), b.limb(k, 0, 0), r.d.size() * 8);
         return r;
     }
+    // copy k of input b lands at batch position k * B + b (B = batch of each element)
     Ct stack(const std::vector<Ct> &v) const {
-        if (ev.dry) return ev.meta(v[0].level, v[0].np, (int)v.size(), v[0].spow);
-        Ct r(cx.N, v[0].level, v[0].np, (int)v.size(), v[0].spow);
+        const int B = v[0].batch;
+        if (ev.dry) return ev.meta(v[0].level, v[0].np, (int)v.size() * B, v[0].spow);
+        Ct r(cx.N, v[0].level, v[0].np, (int)v.size() * B, v[0].spow);
         for (size_t k = 0; k < v.size(); ++k) {
-            if (v[k].level != r.level || v[k].np != r.np) throw std::invalid_argument("stack: mismatched ciphertexts");
-            std::memcpy(r.limb((int)k, 0, 0), v[k].d.data(), v[k].d.size() * 8);
+            if (v[k].level != r.level || v[k].np != r.np || v[k].batch != B) throw std::invalid_argument("stack: mismatched ciphertexts");
+            std::memcpy(r.limb((int)k * B, 0, 0), v[k].d.data(), v[k].d.size() * 8);
         }
         return r;
+    }
+    // matMulReUse summed over K-groups (addInplace over groups, bert-matmul.cpp:262-268)
+    CtT mult_mat_mat_reuse_groups(const Ct &pre, int btotal, int b0, const std::vector<const Pt *> &pts, i64 width) {
+        const int kc = pre.batch / btotal;
+        Ct acc;
+        bool first = true;
+        for (size_t b = 0; b < pts.size(); ++b)
+            for (int k = 0; k < kc; ++k) {
+                if (pts[b]->level != pre.level) throw std::invalid_argument("[multMatMatReUse] plaintext level differs from the ciphertexts'");
+                Ct t = ev.mul_pt_norescale(slice(pre, k * btotal + b0 + (int)b), pt_rotate(*pts[b], (i64)k * width));
+                acc = first ? t : ev.add(acc, t);
+                first = false;
+            }
+        return CtT{acc, Shape()};
     }
 
     // ---------------- HEMMer-level helpers ----------------

@@ -76,7 +76,7 @@ int orc_decrypt(orc_ctx *c, const orc_ct *ct, int idx, double *re, double *im) {
         for (int i = 0; i < c->cx.slots; ++i) { re[i] = z[i].real(); if (im) im[i] = z[i].imag(); }
     })
 }
-int orc_ct_create(orc_ctx *c, int level, int np, int batch, int spow, orc_ct **out) { ORC_TRY(c, *out = new Ct(c->cx.N, level, np, batch, spow)) }
+int orc_ct_create(orc_ctx *c, int level, int np, int batch, int spow, orc_ct **out) { ORC_TRY(c, *out = new Ct(c->cx.N, level, np, batch, spow, c->ev.dry)) }
 int orc_ct_clone(orc_ctx *c, const orc_ct *s, orc_ct **out) { ORC_TRY(c, *out = new Ct(*s)) }
 void orc_ct_free(orc_ct *x) { delete x; }
 void orc_pt_free(orc_pt *x) { delete x; }
@@ -89,15 +89,15 @@ int orc_ct_export(orc_ctx *, const orc_ct *x, uint64_t *h) { if (x->d.empty()) r
 int orc_pt_export(orc_ctx *, const orc_pt *x, uint64_t *h) { std::memcpy(h, x->d.data(), x->d.size() * 8); return 0; }
 int orc_batch_set(orc_ctx *c, orc_ct *dst, int idx, const orc_ct *src) {
     ORC_TRY(c, {
-        Evaluator::require(src->batch == 1 && src->level == dst->level && src->np == dst->np && idx < dst->batch, "batch_set");
-        std::memcpy(dst->limb(idx, 0, 0), src->d.data(), src->d.size() * 8);
+        Evaluator::require(src->level == dst->level && src->np == dst->np && (idx + 1) * src->batch <= dst->batch, "batch_set");
+        if (!src->d.empty() && !dst->d.empty()) std::memcpy(dst->limb(idx * src->batch, 0, 0), src->d.data(), src->d.size() * 8);
     })
 }
 int orc_batch_get(orc_ctx *c, const orc_ct *src, int idx, orc_ct **out) {
     ORC_TRY(c, {
         Evaluator::require(idx < src->batch, "batch_get");
-        Ct *r = new Ct(c->cx.N, src->level, src->np, 1, src->spow);
-        std::memcpy(r->d.data(), src->limb(idx, 0, 0), r->d.size() * 8);
+        Ct *r = new Ct(c->cx.N, src->level, src->np, 1, src->spow, src->d.empty());
+        if (!src->d.empty()) std::memcpy(r->d.data(), src->limb(idx, 0, 0), r->d.size() * 8);
         *out = r;
     })
 }

@@ -146,7 +146,49 @@ def sc_transpose_packing(lib, H, target=0):
     return [lib.ct_export(a.ct), lib.ct_export(c.ct)], err
 
 
+def sc_batched(lib, H, target=2):
+    """Batched handles: three ct x ct products and two K-groups of ct x pt behind one launch sequence must give,
+    entry by entry, the ciphertexts of the same calls made one at a time."""
+    from importlib import import_module
+    CtxtTensor = import_module("encryption-friendly_llm_architecture_b200").CtxtTensor
+    d = tile_dim(lib)
+    mats = _mats(109, d, 12)
+    As = [H.encrypt2(mats[2 * k], mats[2 * k + 1], nonce=20 + k) for k in range(3)]
+    Bs = [H.encrypt2(mats[6 + 2 * k], mats[7 + 2 * k], nonce=30 + k) for k in range(3)]
+    def batch(cts):
+        lvl, npoly, _, sp = lib.ct_meta(cts[0].ct)
+        out = lib.ct_create(lvl, npoly, len(cts), sp)
+        for k, c in enumerate(cts):
+            lib.batch_set(out, k, c.ct)
+        return CtxtTensor(out, *cts[0].shape)
+    ab, bb = batch(As), batch(Bs)
+    H.transpose_inplace(bb)
+    cb = H.single_cc_matmul(ab, bb, target)
+    exports = [lib.ct_export(cb.ct)]
+    err = 0.0
+    for k in range(3):
+        bk = CtxtTensor(Bs[k].ct, *Bs[k].shape)
+        H.transpose_inplace(bk)
+        ck = H.single_cc_matmul(As[k], bk, target)
+        assert np.array_equal(lib.ct_export(ck.ct)[0], exports[0][k]), "batched ct x ct differs from the single call"
+        z = lib.decrypt(cb.ct, k)[: 2 * d * d].real.reshape(d, 2 * d)
+        err = max(err, np.abs(z[:, :d] - mats[2 * k] @ mats[6 + 2 * k].T).max(), np.abs(z[:, d:] - mats[2 * k + 1] @ mats[7 + 2 * k].T).max())
+    # two K-groups through matMulPre as one batch, summed per output tile in one pass
+    rngw = np.random.default_rng(110)
+    W = [[rngw.normal(0, 0.02, (d, d)) for _ in range(4)] for _ in range(2)]
+    pk = [H.complex_packing(As[0], As[1]), H.complex_packing(As[1], As[2])]
+    pre_b = H.matmul_pre(batch(pk), target)
+    wts = [H.encode_diagonal_to_row4(*W[g], level=target + 1) for g in range(2)]
+    fused = H.matmul_reuse_groups(pre_b, 2, 0, wts)
+    singles = [H.matmul_reuse(H.matmul_pre(pk[g], target), wts[g]) for g in range(2)]
+    ref = lib.add(singles[0].ct, singles[1].ct)
+    assert np.array_equal(lib.ct_export(fused.ct), lib.ct_export(ref)), "fused K-group sum differs from matMulReUse + addInplace"
+    exports.append(lib.ct_export(fused.ct))
+    return exports, err
+
+
 SCENARIOS = {
+    "batched": sc_batched,
     "transforms": sc_transforms,
     "ccmm_single_tile": sc_ccmm_single_tile,
     "ccmm_two_tiles": sc_ccmm_two_tiles,
