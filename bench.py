@@ -191,6 +191,18 @@ def run_gpu(args):
     lib.dll.hb_launch_count.restype = C.c_uint64
     stream = torch.cuda.ExternalStream(lib.dll.hb_stream(lib.ctx), device=torch.device("cuda", local))
     wl = layer.LayerWorkload(H, layer.synthetic(1234), rank=rank, world=world)
+    if world > 1:   # communicator for the K-split exchange; the 128-byte id travels over torch.distributed
+        ident = torch.zeros(128, dtype=torch.uint8)
+        if rank == 0:
+            buf = (C.c_ubyte * 128)()
+            assert lib.dll.hb_nccl_unique_id(buf) == 0, "NCCL unavailable"
+            ident = torch.tensor(list(buf), dtype=torch.uint8)
+        ident = ident.cuda()
+        dist.broadcast(ident, 0)
+        raw = (C.c_ubyte * 128)(*ident.cpu().tolist())
+        comm = C.c_void_p()
+        lib._chk(lib.dll.hb_nccl_comm_init(lib.ctx, C.c_int(world), C.c_int(rank), raw, C.byref(comm)))
+        wl.comm = comm.value
 
     def barrier():
         lib.sync()

@@ -636,6 +636,7 @@ int hb_ct_clone(hb_ctx *c, const hb_ct *s, hb_ct **out) {
         *out = r;
     });
 }
+int hb_ct_zero(hb_ctx *c, hb_ct *x) { return guard(c, [&] { CK(cudaMemsetAsync(x->d, 0, x->limbs() * c->N * 8, c->st)); }); }
 void hb_ct_free(hb_ct *x) { if (x) { x->ctx->pool.put(x->d); delete x; } }
 void hb_pt_free(hb_pt *x) { if (x) { x->ctx->pool.put(x->d); delete x; } }
 int hb_ct_meta(const hb_ct *x, int *level, int *np, int *batch, int *spow) {

@@ -68,6 +68,7 @@ class LayerWorkload:
         self.d2h_bytes = 0
         self._weights = {}
         self.resident = None
+        self.comm = None   # NCCL communicator (void*) when several ranks split the K-groups of a sublayer
 
     # ---- unit construction ----
     def _build_units(self):
@@ -199,6 +200,8 @@ class LayerWorkload:
                         acc = part if acc is None else CtxtTensor(self.lib.add(acc.ct, part.ct), *part.shape)
                     if acc is not None:
                         out["pcmm"][(name, wname, j)] = acc
+        if self.world > 1:
+            self._reduce_partials(out["pcmm"])
         for tr, (us, a, b) in res["ccmm"].items():
             a = CtxtTensor(a.ct, *a.shape)
             b = CtxtTensor(b.ct, *b.shape)
@@ -208,6 +211,23 @@ class LayerWorkload:
                 H.transpose_inplace(a)
             out["ccmm"][tr] = (us, H.single_cc_matmul(a, b, t))
         return out
+
+    def _reduce_partials(self, partial):
+        """K-split exchange: every rank holds the partial products of its own K-groups; one all-reduce per sublayer
+        (sum of residues, then reduction modulo each prime) gives every rank the complete output tiles -- the pattern of
+        TransformerBlock::ncclAllReduceWrapper + modReduct (TransformerBlock.cpp:11142-11154, HEMMer.cpp:2625-2635)."""
+        import ctypes as C
+        lib = self.lib
+        for name, xname, weights, kt, nt in self.PCMM:
+            keys = [(name, wname, j) for wname in weights for j in range(nt)]
+            stacked = lib.ct_create(self.target + 1, 2, len(keys), 2)   # zero where this rank has no partial
+            lib._chk(lib.dll.hb_ct_zero(lib.ctx, stacked.ptr))
+            for k, key in enumerate(keys):
+                if key in partial:
+                    lib.batch_set(stacked, k, partial[key].ct)
+            lib._chk(lib.dll.hb_allreduce_sum(lib.ctx, stacked.ptr, C.c_void_p(self.comm)))
+            for k, key in enumerate(keys):
+                partial[key] = CtxtTensor(lib.batch_get(stacked, k), D, D, 2 * D)
 
     # ---- device -> host ----
     def _expected_ccmm(self, u):
@@ -223,7 +243,7 @@ class LayerWorkload:
         """Decrypt every result to host matrices; returns the max-abs error when `check`."""
         err = 0.0
         per = 2 * self.lib.N * 8
-        complete = self.world == 1  # with several ranks a ct x pt output may still miss other ranks' K-groups
+        complete = True
         for (name, wname, j), ct in out["pcmm"].items():
             z = self.lib.decrypt(ct.ct).reshape(D, 2 * D)
             self.d2h_bytes += per

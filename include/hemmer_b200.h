@@ -90,6 +90,7 @@ int hb_decrypt(hb_ctx *ctx, const hb_ct *ct, int index, double *re, double *im);
 /* Ciphertext construction / metadata / raw residues -- Ciphertext.hpp:83-131 */
 int hb_ct_create(hb_ctx *ctx, int level, int n_poly, int batch, int scale_pow, hb_ct **out);
 int hb_ct_clone(hb_ctx *ctx, const hb_ct *src, hb_ct **out);
+int hb_ct_zero(hb_ctx *ctx, hb_ct *ct); /* all residues 0: an encryption of zero with zero noise */
 void hb_ct_free(hb_ct *ct);
 void hb_pt_free(hb_pt *pt);
 int hb_ct_meta(const hb_ct *ct, int *level, int *n_poly, int *batch, int *scale_pow);
