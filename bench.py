@@ -79,6 +79,8 @@ class ClockSampler:
 # per-operation timings sampled on the host cores.
 # ---------------------------------------------------------------------------------------------
 def cpu_layer_estimate(pkg, sample_reps=8):
+    # launchers export OMP_NUM_THREADS=1; the CPU arm is meant to use every host core (set before libgomp loads)
+    os.environ["OMP_NUM_THREADS"] = str(os.cpu_count() or 1)
     lib_path = os.path.join(ROOT, "oracle", "_build", "liboracle.so")
     if not os.path.exists(lib_path):
         subprocess.check_call(["make", "-s", "-C", os.path.join(ROOT, "oracle")])

@@ -110,7 +110,8 @@ struct hb_ctx {
 
     LimbMap qmap(int level) const { LimbMap m{}; m.n = level + 1; for (int i = 0; i <= level; ++i) m.prime[i] = (unsigned char)i; return m; }
     LimbMap allmap() const { LimbMap m{}; m.n = nprimes; for (int i = 0; i < nprimes; ++i) m.prime[i] = (unsigned char)i; return m; }
-    dim3 egrid(int count) const { return dim3((unsigned)((N + 255) / 256), (unsigned)count); }
+    unsigned gx() const { return (unsigned)((N + 256 * kElems - 1) / (256 * kElems)); } // blocks per limb of the element-wise kernels
+    dim3 egrid(int count) const { return dim3(gx(), (unsigned)count); }
     u64 *alloc_limbs(size_t limbs) { return (u64 *)pool.get(limbs * (size_t)N * 8); }
 };
 
@@ -229,15 +230,15 @@ void keyswitch(hb_ctx *c, const u64 *a, size_t a_outer, int level, int batch, co
     const PlanDims d = plan_dims(c, level);
     const int N = c->N, n = d.n, ne = d.ne, K = d.K;
     const LimbMap qm = c->qmap(level);
-    const unsigned gx = (unsigned)((N + 255) / 256);
+    const unsigned gx1 = (unsigned)((N + 255) / 256), gx = c->gx(); // base-conversion kernels keep one coefficient per thread
     Tmp acoef(c, (size_t)batch * n), dt(c, (size_t)batch * d.dt_count), acc(c, (size_t)batch * 2 * ne), pco(c, (size_t)batch * 2 * K), t(c, (size_t)batch * 2 * n);
     ntt(c, a, a_outer, acoef.p, (size_t)n * N, batch * n, qm, true);
-    LAUNCH(c), k_modup<<<dim3(gx, d.nd, batch), 256, 0, c->st>>>(dt.p, acoef.p, pl, c->pc, N);
+    LAUNCH(c), k_modup<<<dim3(gx1, d.nd, batch), 256, 0, c->st>>>(dt.p, acoef.p, pl, c->pc, N);
     ntt_inplace(c, dt.p, batch * d.dt_count, d.dtmap, false);
     LAUNCH(c), k_ks_inner<<<dim3(gx, ne, batch), 256, 0, c->st>>>(acc.p, a, a_outer, dt.p, key.d, c->nprimes, pl, c->pc, g, c->logn, N);
     LimbMap pm{}; pm.n = K; for (int k = 0; k < K; ++k) pm.prime[k] = (unsigned char)(c->L + 1 + k);
     ntt(c, acc.p + (size_t)n * N, (size_t)ne * N, pco.p, (size_t)K * N, batch * 2 * K, pm, true);
-    LAUNCH(c), k_moddown_conv<<<dim3(gx, 1, batch * 2), 256, 0, c->st>>>(t.p, pco.p, pl, c->pc, c->L + 1, N);
+    LAUNCH(c), k_moddown_conv<<<dim3(gx1, 1, batch * 2), 256, 0, c->st>>>(t.p, pco.p, pl, c->pc, c->L + 1, N);
     ntt_inplace(c, t.p, batch * 2 * n, qm, false);
     LAUNCH(c), k_moddown_fin<<<dim3(gx, n, batch * 2), 256, 0, c->st>>>(out, out_outer, acc.p, t.p, add0, add1, add_outer, pl, c->pc, g, c->logn, N);
     CK(cudaGetLastError());
@@ -311,7 +312,7 @@ hb_ct *do_prod_rescale(hb_ctx *c, const hb_ct *const *a, const hb_pt *const *p, 
         tl.a[j] = a[j]->d; tl.p[j] = p[j]->d;
     }
     const int l = a0->level, N = c->N, nbp = a0->batch * a0->np, groups = separate ? count : 1;
-    const unsigned gx = (unsigned)((N + 255) / 256);
+    const unsigned gx = c->gx();
     hb_ct *r = new_ct(c, l - 1, a0->np, a0->batch, 1);
     try {
         Tmp last(c, (size_t)groups * nbp), S(c, (size_t)nbp), t(c, (size_t)nbp * l);
@@ -465,7 +466,8 @@ int hb_ctx_create(const hb_params *prm, int device, hb_ctx **out) {
             p.small = (c->logn == 16 && q < ((u64)1 << 44)) ? 1 : 0;
             p.q_inv_f = 1.0 / (double)q;
             p.n_inv_f = (double)p.n_inv / (double)q;
-            p.pad[0] = p.pad[1] = 0;
+            p.fp = q < ((u64)1 << 44) ? 1 : 0;
+            p.pad = 0;
             std::vector<u64> f, fs, iv, ivs;
             c->h->twiddles(i, f, fs, iv, ivs);
             if (p.small) { // companion tables hold w/q as doubles instead of Shoup quotients

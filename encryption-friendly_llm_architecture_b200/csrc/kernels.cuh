@@ -9,111 +9,173 @@
 
 namespace hb {
 
-#define HB_ELEM_IDX()                                              \
-    const int li = blockIdx.y;                                     \
-    const int i = blockIdx.x * blockDim.x + threadIdx.x;           \
-    if (i >= N) return;                                            \
-    const PrimeConst m = pc[map.prime[li % map.n]];                \
-    const size_t off = (size_t)li * N + i;
+// Every thread handles kElems coefficients, blockDim apart (each access stays a 256-byte run per warp): four
+// independent loads per array are in flight per thread and the grid has four times fewer, fatter CTAs --
+// with one coefficient per thread these kernels were bound by CTA turnover at about 2 TB/s.
+constexpr int kElems = 4;
 
 // out = a + b  (mode 0) | a - b (mode 1) | -a (mode 2)
 __global__ void k_addsub(u64 *__restrict__ out, const u64 *__restrict__ a, const u64 *__restrict__ b, LimbMap map, const PrimeConst *__restrict__ pc,
                          int N, int mode) {
-    HB_ELEM_IDX();
-    u64 x = a[off];
-    if (mode == 0) out[off] = add_mod(x, b[off], m.q);
-    else if (mode == 1) out[off] = sub_mod(x, b[off], m.q);
-    else out[off] = x ? m.q - x : 0;
+    const int li = blockIdx.y;
+#pragma unroll
+    for (int u_ = 0; u_ < kElems; ++u_) {
+        const int i = (blockIdx.x * kElems + u_) * blockDim.x + threadIdx.x;
+        if (i >= N) break;
+        const PrimeConst m = pc[map.prime[li % map.n]];
+        const size_t off = (size_t)li * N + i;
+        u64 x = a[off];
+        if (mode == 0) out[off] = add_mod(x, b[off], m.q);
+        else if (mode == 1) out[off] = sub_mod(x, b[off], m.q);
+        else out[off] = x ? m.q - x : 0;
+    }
 }
 
 struct Scalars { u64 v[kMaxPrimes]; };
 // out = a * s[prime]
 __global__ void k_scalar_mul(u64 *__restrict__ out, const u64 *__restrict__ a, size_t a_outer, LimbMap map, const PrimeConst *__restrict__ pc, int N, Scalars s) {
     const int li = blockIdx.y;
-    const int i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= N) return;
-    const int pi = map.prime[li % map.n];
-    const PrimeConst m = pc[pi];
-    const size_t soff = (size_t)(li / map.n) * a_outer + (size_t)(li % map.n) * N + i;
-    out[(size_t)li * N + i] = mul_mod(a[soff], s.v[pi], m);
+#pragma unroll
+    for (int u_ = 0; u_ < kElems; ++u_) {
+        const int i = (blockIdx.x * kElems + u_) * blockDim.x + threadIdx.x;
+        if (i >= N) break;
+        const int pi = map.prime[li % map.n];
+        const PrimeConst m = pc[pi];
+        const size_t soff = (size_t)(li / map.n) * a_outer + (size_t)(li % map.n) * N + i;
+        out[(size_t)li * N + i] = mul_mod_any(a[soff], s.v[pi], m);
+    }
 }
 // multiplication by X^(N/2): +iu on the first half of an NTT-form limb, -iu on the second
 __global__ void k_mult_imag(u64 *__restrict__ out, const u64 *__restrict__ a, LimbMap map, const PrimeConst *__restrict__ pc, int N) {
-    HB_ELEM_IDX();
-    u64 r = mul_shoup(a[off], m.iu, m.iu_sh, m.q);
-    if (i >= N / 2) r = r ? m.q - r : 0;
-    out[off] = r;
+    const int li = blockIdx.y;
+#pragma unroll
+    for (int u_ = 0; u_ < kElems; ++u_) {
+        const int i = (blockIdx.x * kElems + u_) * blockDim.x + threadIdx.x;
+        if (i >= N) break;
+        const PrimeConst m = pc[map.prime[li % map.n]];
+        const size_t off = (size_t)li * N + i;
+        u64 r = mul_shoup(a[off], m.iu, m.iu_sh, m.q);
+        if (i >= N / 2) r = r ? m.q - r : 0;
+        out[off] = r;
+    }
 }
 // out = a (.) pt, pt limb = li % map.n
 __global__ void k_mul_pt(u64 *__restrict__ out, const u64 *__restrict__ a, const u64 *__restrict__ pt, LimbMap map, const PrimeConst *__restrict__ pc, int N) {
-    HB_ELEM_IDX();
-    out[off] = mul_mod(a[off], pt[(size_t)(li % map.n) * N + i], m);
+    const int li = blockIdx.y;
+#pragma unroll
+    for (int u_ = 0; u_ < kElems; ++u_) {
+        const int i = (blockIdx.x * kElems + u_) * blockDim.x + threadIdx.x;
+        if (i >= N) break;
+        const PrimeConst m = pc[map.prime[li % map.n]];
+        const size_t off = (size_t)li * N + i;
+        out[off] = mul_mod_any(a[off], pt[(size_t)(li % map.n) * N + i], m);
+    }
 }
 // out = a (.) pa + b (.) pb
 __global__ void k_mul2_add(u64 *__restrict__ out, const u64 *__restrict__ a, const u64 *__restrict__ pa, const u64 *__restrict__ b, const u64 *__restrict__ pb,
                            LimbMap map, const PrimeConst *__restrict__ pc, int N) {
-    HB_ELEM_IDX();
-    const size_t po = (size_t)(li % map.n) * N + i;
-    Acc128 s; s.zero();
-    s.mad(a[off], pa[po]); s.mad(b[off], pb[po]);
-    out[off] = barrett128(s.hi, s.lo, m);
+    const int li = blockIdx.y;
+#pragma unroll
+    for (int u_ = 0; u_ < kElems; ++u_) {
+        const int i = (blockIdx.x * kElems + u_) * blockDim.x + threadIdx.x;
+        if (i >= N) break;
+        const PrimeConst m = pc[map.prime[li % map.n]];
+        const size_t off = (size_t)li * N + i;
+        const size_t po = (size_t)(li % map.n) * N + i;
+        Acc128 s; s.zero();
+        s.mad(a[off], pa[po]); s.mad(b[off], pb[po]);
+        out[off] = barrett128(s.hi, s.lo, m);
+    }
 }
 // tensor product, optional accumulation.  grid.y = batch * n; x, y: [batch][2][n][N]; d: [batch][3][n][N]
 __global__ void k_tensor(u64 *__restrict__ d, const u64 *__restrict__ x, const u64 *__restrict__ y, int n, LimbMap map, const PrimeConst *__restrict__ pc, int N,
                          int accumulate) {
     const int bl = blockIdx.y, b = bl / n, l = bl % n;
-    const int i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= N) return;
-    const PrimeConst m = pc[map.prime[l]];
-    const size_t x0 = ((size_t)(b * 2) * n + l) * N + i, x1 = x0 + (size_t)n * N;
-    const size_t d0 = ((size_t)(b * 3) * n + l) * N + i, d1 = d0 + (size_t)n * N, d2 = d1 + (size_t)n * N;
-    const u64 b1 = x[x0], a1 = x[x1], b2 = y[x0], a2 = y[x1];
-    u64 r0 = mul_mod(b1, b2, m), r2 = mul_mod(a1, a2, m);
-    Acc128 s; s.zero(); s.mad(a1, b2); s.mad(a2, b1);
-    u64 r1 = barrett128(s.hi, s.lo, m);
-    if (accumulate) { r0 = add_mod(r0, d[d0], m.q); r1 = add_mod(r1, d[d1], m.q); r2 = add_mod(r2, d[d2], m.q); }
-    d[d0] = r0; d[d1] = r1; d[d2] = r2;
+#pragma unroll
+    for (int u_ = 0; u_ < kElems; ++u_) {
+        const int i = (blockIdx.x * kElems + u_) * blockDim.x + threadIdx.x;
+        if (i >= N) break;
+        const PrimeConst m = pc[map.prime[l]];
+        const size_t x0 = ((size_t)(b * 2) * n + l) * N + i, x1 = x0 + (size_t)n * N;
+        const size_t d0 = ((size_t)(b * 3) * n + l) * N + i, d1 = d0 + (size_t)n * N, d2 = d1 + (size_t)n * N;
+        const u64 b1 = x[x0], a1 = x[x1], b2 = y[x0], a2 = y[x1];
+        u64 r0, r1, r2;
+        if (m.fp) {
+            const double b1d = u52_to_double(b1), a1d = u52_to_double(a1), b2d = u52_to_double(b2), a2d = u52_to_double(a2);
+            r0 = mul_small_lazy_d(b1, b1d, b2, b2d, m.q_inv_f, m.q); r0 = r0 >= m.q ? r0 - m.q : r0;
+            r2 = mul_small_lazy_d(a1, a1d, a2, a2d, m.q_inv_f, m.q); r2 = r2 >= m.q ? r2 - m.q : r2;
+            r1 = reduce_fp(mul_small_lazy_d(a1, a1d, b2, b2d, m.q_inv_f, m.q) + mul_small_lazy_d(a2, a2d, b1, b1d, m.q_inv_f, m.q), m.q_inv_f, m.q);
+        } else {
+            r0 = mul_mod(b1, b2, m); r2 = mul_mod(a1, a2, m);
+            Acc128 s; s.zero(); s.mad(a1, b2); s.mad(a2, b1);
+            r1 = barrett128(s.hi, s.lo, m);
+        }
+        if (accumulate) { r0 = add_mod(r0, d[d0], m.q); r1 = add_mod(r1, d[d1], m.q); r2 = add_mod(r2, d[d2], m.q); }
+        d[d0] = r0; d[d1] = r1; d[d2] = r2;
+    }
 }
 // out[li][i] = in[li][perm_g(i)]
 __global__ void k_permute(u64 *__restrict__ out, const u64 *__restrict__ in, u32 g, int logn, int N) {
     const int li = blockIdx.y;
-    const int i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= N) return;
-    out[(size_t)li * N + i] = in[(size_t)li * N + ntt_perm((u32)i, g, logn)];
+#pragma unroll
+    for (int u_ = 0; u_ < kElems; ++u_) {
+        const int i = (blockIdx.x * kElems + u_) * blockDim.x + threadIdx.x;
+        if (i >= N) break;
+        out[(size_t)li * N + i] = in[(size_t)li * N + ntt_perm((u32)i, g, logn)];
+    }
 }
 // int64 coefficients -> residues of every limb instance (coefficient form)
 __global__ void k_reduce_i64(u64 *__restrict__ out, const i64 *__restrict__ coef, LimbMap map, const PrimeConst *__restrict__ pc, int N) {
-    HB_ELEM_IDX();
-    out[off] = reduce_i64(coef[i], m);
+    const int li = blockIdx.y;
+#pragma unroll
+    for (int u_ = 0; u_ < kElems; ++u_) {
+        const int i = (blockIdx.x * kElems + u_) * blockDim.x + threadIdx.x;
+        if (i >= N) break;
+        const PrimeConst m = pc[map.prime[li % map.n]];
+        const size_t off = (size_t)li * N + i;
+        out[off] = reduce_i64(coef[i], m);
+    }
 }
 // x mod q for lazily summed residues
 __global__ void k_mod_reduce(u64 *__restrict__ a, LimbMap map, const PrimeConst *__restrict__ pc, int N) {
-    HB_ELEM_IDX();
-    a[off] = reduce_u64(a[off], m);
+    const int li = blockIdx.y;
+#pragma unroll
+    for (int u_ = 0; u_ < kElems; ++u_) {
+        const int i = (blockIdx.x * kElems + u_) * blockDim.x + threadIdx.x;
+        if (i >= N) break;
+        const PrimeConst m = pc[map.prime[li % map.n]];
+        const size_t off = (size_t)li * N + i;
+        a[off] = reduce_u64(a[off], m);
+    }
 }
 
 // ---------------- rescale ----------------
 // t[bp][l][i] = centred(last[bp][i]) mod q_l, l < level.  grid.y = nbp * level
 __global__ void k_rescale_prep(u64 *__restrict__ t, const u64 *__restrict__ last, int level, const PrimeConst *__restrict__ pc, int N) {
     const int w = blockIdx.y, bp = w / level, l = w % level;
-    const int i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= N) return;
-    const PrimeConst m = pc[l];
-    const u64 ql = pc[level].q;
-    const u64 r = last[(size_t)bp * N + i];
-    u64 v = reduce_u64(r, m);
-    if (r > (ql >> 1)) v = sub_mod(v, reduce_u64(ql, m), m.q);
-    t[(size_t)w * N + i] = v;
+#pragma unroll
+    for (int u_ = 0; u_ < kElems; ++u_) {
+        const int i = (blockIdx.x * kElems + u_) * blockDim.x + threadIdx.x;
+        if (i >= N) break;
+        const PrimeConst m = pc[l];
+        const u64 ql = pc[level].q;
+        const u64 r = last[(size_t)bp * N + i];
+        const i64 centred = r > (ql >> 1) ? (i64)r - (i64)ql : (i64)r;
+        t[(size_t)w * N + i] = reduce_i64_any(centred, m);
+    }
 }
 // out[bp][l] = (x[bp][l] - t[bp][l]) * q_level^-1 ; x has level+1 limbs per poly
 __global__ void k_rescale_fin(u64 *__restrict__ out, const u64 *__restrict__ x, const u64 *__restrict__ t, int level, const PrimeConst *__restrict__ pc, int N,
                               Scalars qlinv) {
     const int w = blockIdx.y, bp = w / level, l = w % level;
-    const int i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= N) return;
-    const PrimeConst m = pc[l];
-    const u64 xv = x[((size_t)bp * (level + 1) + l) * N + i];
-    out[(size_t)w * N + i] = mul_mod(sub_mod(xv, t[(size_t)w * N + i], m.q), qlinv.v[l], m);
+#pragma unroll
+    for (int u_ = 0; u_ < kElems; ++u_) {
+        const int i = (blockIdx.x * kElems + u_) * blockDim.x + threadIdx.x;
+        if (i >= N) break;
+        const PrimeConst m = pc[l];
+        const u64 xv = x[((size_t)bp * (level + 1) + l) * N + i];
+        out[(size_t)w * N + i] = mul_mod_any(sub_mod(xv, t[(size_t)w * N + i], m.q), qlinv.v[l], m);
+    }
 }
 
 // ---------------- fused plaintext products with rescale ----------------
@@ -128,47 +190,74 @@ struct TermList { const u64 *a[kMaxTerms]; const u64 *p[kMaxTerms]; int count; }
 // last[g][bp][x] = (sum over the terms of group g) a_j[bp][level][x] * p_j[level][x] mod q_level
 // grid = (N/256, nbp, groups)   groups = count (separate) or 1
 __global__ void k_last_prod(u64 *__restrict__ last, TermList tl, int separate, int level, int nbp, const PrimeConst *__restrict__ pc, int N) {
-    const int x = blockIdx.x * blockDim.x + threadIdx.x;
-    if (x >= N) return;
-    const int bp = blockIdx.y, g = blockIdx.z;
-    const PrimeConst m = pc[level];
-    const size_t ao = ((size_t)bp * (level + 1) + level) * N + x, po = (size_t)level * N + x;
-    const int j0 = separate ? g : 0, j1 = separate ? g + 1 : tl.count;
-    Acc128 s; s.zero();
-    for (int j = j0; j < j1; ++j) s.mad(tl.a[j][ao], tl.p[j][po]);
-    last[((size_t)g * nbp + bp) * N + x] = barrett128(s.hi, s.lo, m);
+#pragma unroll
+    for (int u_ = 0; u_ < kElems; ++u_) {
+        const int x = (blockIdx.x * kElems + u_) * blockDim.x + threadIdx.x;
+        if (x >= N) break;
+        const int bp = blockIdx.y, g = blockIdx.z;
+        const PrimeConst m = pc[level];
+        const size_t ao = ((size_t)bp * (level + 1) + level) * N + x, po = (size_t)level * N + x;
+        const int j0 = separate ? g : 0, j1 = separate ? g + 1 : tl.count;
+        u64 r;
+        if (m.fp) {
+            u64 acc = 0;
+            for (int j = j0; j < j1; ++j) acc += mul_small_lazy(tl.a[j][ao], tl.p[j][po], m.q_inv_f, m.q);
+            r = reduce_fp(acc, m.q_inv_f, m.q);
+        } else {
+            Acc128 s; s.zero();
+            for (int j = j0; j < j1; ++j) s.mad(tl.a[j][ao], tl.p[j][po]);
+            r = barrett128(s.hi, s.lo, m);
+        }
+        last[((size_t)g * nbp + bp) * N + x] = r;
+    }
 }
 // S[bp][x] = sum_g centred(last[g][bp][x]) as a signed integer (|S| <= groups * q_level / 2)
 __global__ void k_centre_sum(i64 *__restrict__ S, const u64 *__restrict__ last, int groups, int nbp, int level, const PrimeConst *__restrict__ pc, int N) {
-    const int x = blockIdx.x * blockDim.x + threadIdx.x;
-    if (x >= N) return;
-    const int bp = blockIdx.y;
-    const u64 ql = pc[level].q, half = ql >> 1;
-    i64 acc = 0;
-    for (int g = 0; g < groups; ++g) {
-        const u64 r = last[((size_t)g * nbp + bp) * N + x];
-        acc += r > half ? (i64)r - (i64)ql : (i64)r;
+#pragma unroll
+    for (int u_ = 0; u_ < kElems; ++u_) {
+        const int x = (blockIdx.x * kElems + u_) * blockDim.x + threadIdx.x;
+        if (x >= N) break;
+        const int bp = blockIdx.y;
+        const u64 ql = pc[level].q, half = ql >> 1;
+        i64 acc = 0;
+        for (int g = 0; g < groups; ++g) {
+            const u64 r = last[((size_t)g * nbp + bp) * N + x];
+            acc += r > half ? (i64)r - (i64)ql : (i64)r;
+        }
+        S[(size_t)bp * N + x] = acc;
     }
-    S[(size_t)bp * N + x] = acc;
 }
 // t[bp][l][x] = S[bp][x] mod q_l.  grid.y = nbp * level
 __global__ void k_lift_mod(u64 *__restrict__ t, const i64 *__restrict__ S, int level, const PrimeConst *__restrict__ pc, int N) {
     const int w = blockIdx.y, bp = w / level, l = w % level;
-    const int x = blockIdx.x * blockDim.x + threadIdx.x;
-    if (x >= N) return;
-    t[(size_t)w * N + x] = reduce_i64(S[(size_t)bp * N + x], pc[l]);
+#pragma unroll
+    for (int u_ = 0; u_ < kElems; ++u_) {
+        const int x = (blockIdx.x * kElems + u_) * blockDim.x + threadIdx.x;
+        if (x >= N) break;
+        t[(size_t)w * N + x] = reduce_i64_any(S[(size_t)bp * N + x], pc[l]);
+    }
 }
 // out[bp][l][x] = (sum_j a_j[bp][l][x] * p_j[l][x] - t[bp][l][x]) * q_level^-1.  grid.y = nbp * level
 __global__ void k_prod_rescale_fin(u64 *__restrict__ out, TermList tl, const u64 *__restrict__ t, int level, const PrimeConst *__restrict__ pc, int N, Scalars qlinv) {
     const int w = blockIdx.y, bp = w / level, l = w % level;
-    const int x = blockIdx.x * blockDim.x + threadIdx.x;
-    if (x >= N) return;
-    const PrimeConst m = pc[l];
-    const size_t ao = ((size_t)bp * (level + 1) + l) * N + x, po = (size_t)l * N + x;
-    Acc128 s; s.zero();
-    for (int j = 0; j < tl.count; ++j) s.mad(tl.a[j][ao], tl.p[j][po]);
-    const u64 v = barrett128(s.hi, s.lo, m);
-    out[(size_t)w * N + x] = mul_mod(sub_mod(v, t[(size_t)w * N + x], m.q), qlinv.v[l], m);
+#pragma unroll
+    for (int u_ = 0; u_ < kElems; ++u_) {
+        const int x = (blockIdx.x * kElems + u_) * blockDim.x + threadIdx.x;
+        if (x >= N) break;
+        const PrimeConst m = pc[l];
+        const size_t ao = ((size_t)bp * (level + 1) + l) * N + x, po = (size_t)l * N + x;
+        u64 v;
+        if (m.fp) {
+            u64 acc = 0;
+            for (int j = 0; j < tl.count; ++j) acc += mul_small_lazy(tl.a[j][ao], tl.p[j][po], m.q_inv_f, m.q);
+            v = reduce_fp(acc, m.q_inv_f, m.q);
+        } else {
+            Acc128 s; s.zero();
+            for (int j = 0; j < tl.count; ++j) s.mad(tl.a[j][ao], tl.p[j][po]);
+            v = barrett128(s.hi, s.lo, m);
+        }
+        out[(size_t)w * N + x] = mul_mod_any(sub_mod(v, t[(size_t)w * N + x], m.q), qlinv.v[l], m);
+    }
 }
 
 // ---------------- key switching ----------------
@@ -188,27 +277,40 @@ struct KsPlan {
 };
 
 // ModUp: a_coef [batch][n][N] (coefficient form) -> dt [batch][dt_count][N] (coefficient form).
-// grid = (N/256, nd, batch)
+// grid = (N/256, nd, batch).  The source count of a digit is a template parameter so that the per-target
+// contraction is fully unrolled with no predicated-off iterations.
+template <int NS>
+__device__ __forceinline__ void modup_body(u64 *__restrict__ dt, const u64 *__restrict__ a_coef, const KsPlan *__restrict__ pl, const PrimeConst *__restrict__ pc, int N,
+                                           int i, int dg, int b) {
+    const int lo = pl->dig_lo[dg], hi = lo + NS, n = pl->n, ne = pl->ne;
+    u64 y[NS];
+#pragma unroll
+    for (int s = 0; s < NS; ++s) y[s] = mul_shoup(a_coef[((size_t)b * n + lo + s) * N + i], pl->hat_inv[dg][s], pl->hat_inv_sh[dg][s], pc[lo + s].q);
+    u64 *o = dt + ((size_t)b * pl->dt_count + pl->dt_start[dg]) * N + i;
+    for (int j = 0; j < ne; ++j) {
+        if (j >= lo && j < hi) continue;
+        const PrimeConst *m = pc + pl->ext_prime[j];
+        Acc128 s; s.zero();
+#pragma unroll
+        for (int k = 0; k < NS; ++k) s.mad(y[k], pl->hat_mod[dg][k][j]);
+        PrimeConst mm; mm.q = m->q; mm.mu_hi = m->mu_hi; mm.mu_lo = m->mu_lo;
+        *o = barrett128(s.hi, s.lo, mm);
+        o += N;
+    }
+}
 __global__ void k_modup(u64 *__restrict__ dt, const u64 *__restrict__ a_coef, const KsPlan *__restrict__ pl, const PrimeConst *__restrict__ pc, int N) {
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= N) return;
     const int dg = blockIdx.y, b = blockIdx.z;
-    const int lo = pl->dig_lo[dg], hi = pl->dig_hi[dg], ns = hi - lo, n = pl->n, ne = pl->ne;
-    u64 y[kMaxDigitLimbs];
-#pragma unroll
-    for (int s = 0; s < kMaxDigitLimbs; ++s)
-        if (s < ns) y[s] = mul_shoup(a_coef[((size_t)b * n + lo + s) * N + i], pl->hat_inv[dg][s], pl->hat_inv_sh[dg][s], pc[lo + s].q);
-    u64 *o = dt + ((size_t)b * pl->dt_count + pl->dt_start[dg]) * N + i;
-    int e = 0;
-    for (int j = 0; j < ne; ++j) {
-        if (j >= lo && j < hi) continue;
-        const PrimeConst m = pc[pl->ext_prime[j]];
-        Acc128 s; s.zero();
-#pragma unroll
-        for (int k = 0; k < kMaxDigitLimbs; ++k)
-            if (k < ns) s.mad(y[k], pl->hat_mod[dg][k][j]);
-        o[(size_t)e * N] = barrett128(s.hi, s.lo, m);
-        ++e;
+    switch (pl->dig_hi[dg] - pl->dig_lo[dg]) {
+    case 1: modup_body<1>(dt, a_coef, pl, pc, N, i, dg, b); break;
+    case 2: modup_body<2>(dt, a_coef, pl, pc, N, i, dg, b); break;
+    case 3: modup_body<3>(dt, a_coef, pl, pc, N, i, dg, b); break;
+    case 4: modup_body<4>(dt, a_coef, pl, pc, N, i, dg, b); break;
+    case 5: modup_body<5>(dt, a_coef, pl, pc, N, i, dg, b); break;
+    case 6: modup_body<6>(dt, a_coef, pl, pc, N, i, dg, b); break;
+    case 7: modup_body<7>(dt, a_coef, pl, pc, N, i, dg, b); break;
+    default: modup_body<8>(dt, a_coef, pl, pc, N, i, dg, b); break;
     }
 }
 
@@ -217,60 +319,97 @@ __global__ void k_modup(u64 *__restrict__ dt, const u64 *__restrict__ a_coef, co
 // digit_dg[j] is a_ntt[j] for own limbs and dt[...] otherwise.  grid = (N/256, ne, batch)
 __global__ void k_ks_inner(u64 *__restrict__ acc, const u64 *__restrict__ a_ntt, size_t a_outer, const u64 *__restrict__ dt, const u64 *__restrict__ key, int key_primes,
                            const KsPlan *__restrict__ pl, const PrimeConst *__restrict__ pc, u32 g, int logn, int N) {
-    const int i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= N) return;
-    const int j = blockIdx.y, b = blockIdx.z;
-    const int pj = pl->ext_prime[j], nd = pl->nd, ne = pl->ne;
-    const PrimeConst m = pc[pj];
-    const u32 s = g ? ntt_perm((u32)i, g, logn) : (u32)i;
-    Acc128 s0, s1; s0.zero(); s1.zero();
-    for (int dg = 0; dg < nd; ++dg) {
-        const int en = pl->dt_entry[dg][j];
-        const u64 v = en < 0 ? a_ntt[(size_t)b * a_outer + (size_t)j * N + s] : dt[((size_t)b * pl->dt_count + en) * N + s];
-        const u64 *k0 = key + (((size_t)dg * 2) * key_primes + pj) * N + i;
-        s0.mad(v, k0[0]);
-        s1.mad(v, k0[(size_t)key_primes * N]);
+#pragma unroll
+    for (int u_ = 0; u_ < kElems; ++u_) {
+        const int i = (blockIdx.x * kElems + u_) * blockDim.x + threadIdx.x;
+        if (i >= N) break;
+        const int j = blockIdx.y, b = blockIdx.z;
+        const int pj = pl->ext_prime[j], nd = pl->nd, ne = pl->ne;
+        const PrimeConst m = pc[pj];
+        const u32 s = g ? ntt_perm((u32)i, g, logn) : (u32)i;
+        u64 r0, r1;
+        if (m.fp) {
+            u64 t0 = 0, t1 = 0;
+            for (int dg = 0; dg < nd; ++dg) {
+                const int en = pl->dt_entry[dg][j];
+                const u64 v = en < 0 ? a_ntt[(size_t)b * a_outer + (size_t)j * N + s] : dt[((size_t)b * pl->dt_count + en) * N + s];
+                const u64 *k0 = key + (((size_t)dg * 2) * key_primes + pj) * N + i;
+                const u64 ka = k0[0], kb = k0[(size_t)key_primes * N];
+                const double vd = u52_to_double(v);
+                t0 += mul_small_lazy_d(v, vd, ka, u52_to_double(ka), m.q_inv_f, m.q);
+                t1 += mul_small_lazy_d(v, vd, kb, u52_to_double(kb), m.q_inv_f, m.q);
+            }
+            r0 = reduce_fp(t0, m.q_inv_f, m.q); r1 = reduce_fp(t1, m.q_inv_f, m.q);
+        } else {
+            Acc128 s0, s1; s0.zero(); s1.zero();
+            for (int dg = 0; dg < nd; ++dg) {
+                const int en = pl->dt_entry[dg][j];
+                const u64 v = en < 0 ? a_ntt[(size_t)b * a_outer + (size_t)j * N + s] : dt[((size_t)b * pl->dt_count + en) * N + s];
+                const u64 *k0 = key + (((size_t)dg * 2) * key_primes + pj) * N + i;
+                s0.mad(v, k0[0]);
+                s1.mad(v, k0[(size_t)key_primes * N]);
+            }
+            r0 = barrett128(s0.hi, s0.lo, m); r1 = barrett128(s1.hi, s1.lo, m);
+        }
+        acc[(((size_t)b * 2) * ne + j) * N + i] = r0;
+        acc[(((size_t)b * 2 + 1) * ne + j) * N + i] = r1;
     }
-    acc[(((size_t)b * 2) * ne + j) * N + i] = barrett128(s0.hi, s0.lo, m);
-    acc[(((size_t)b * 2 + 1) * ne + j) * N + i] = barrett128(s1.hi, s1.lo, m);
 }
 
 // ModDown conversion: pcoef [bp][K][N] (special limbs, coefficient form) -> t [bp][n][N] (coefficient form)
 // grid = (N/256, 1, nbp)
+template <int K>
+__device__ __forceinline__ void moddown_conv_body(u64 *__restrict__ t, const u64 *__restrict__ pcoef, const KsPlan *__restrict__ pl, const PrimeConst *__restrict__ pc, int Lp1,
+                                                  int N, int i, int bp) {
+    const int n = pl->n;
+    u64 y[K];
+#pragma unroll
+    for (int k = 0; k < K; ++k) y[k] = mul_shoup(pcoef[((size_t)bp * K + k) * N + i], pl->p_hat_inv[k], pl->p_hat_inv_sh[k], pc[Lp1 + k].q);
+    u64 *o = t + (size_t)bp * n * N + i;
+    for (int l = 0; l < n; ++l) {
+        Acc128 s; s.zero();
+#pragma unroll
+        for (int k = 0; k < K; ++k) s.mad(y[k], pl->p_hat_mod[k][l]);
+        PrimeConst mm; mm.q = pc[l].q; mm.mu_hi = pc[l].mu_hi; mm.mu_lo = pc[l].mu_lo;
+        *o = barrett128(s.hi, s.lo, mm);
+        o += N;
+    }
+}
 __global__ void k_moddown_conv(u64 *__restrict__ t, const u64 *__restrict__ pcoef, const KsPlan *__restrict__ pl, const PrimeConst *__restrict__ pc, int Lp1, int N) {
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= N) return;
-    const int bp = blockIdx.z, K = pl->K, n = pl->n;
-    u64 y[8];
-#pragma unroll
-    for (int k = 0; k < 8; ++k)
-        if (k < K) y[k] = mul_shoup(pcoef[((size_t)bp * K + k) * N + i], pl->p_hat_inv[k], pl->p_hat_inv_sh[k], pc[Lp1 + k].q);
-    for (int l = 0; l < n; ++l) {
-        const PrimeConst m = pc[l];
-        Acc128 s; s.zero();
-#pragma unroll
-        for (int k = 0; k < 8; ++k)
-            if (k < K) s.mad(y[k], pl->p_hat_mod[k][l]);
-        t[((size_t)bp * n + l) * N + i] = barrett128(s.hi, s.lo, m);
+    const int bp = blockIdx.z;
+    switch (pl->K) {
+    case 1: moddown_conv_body<1>(t, pcoef, pl, pc, Lp1, N, i, bp); break;
+    case 2: moddown_conv_body<2>(t, pcoef, pl, pc, Lp1, N, i, bp); break;
+    case 3: moddown_conv_body<3>(t, pcoef, pl, pc, Lp1, N, i, bp); break;
+    case 4: moddown_conv_body<4>(t, pcoef, pl, pc, Lp1, N, i, bp); break;
+    case 5: moddown_conv_body<5>(t, pcoef, pl, pc, Lp1, N, i, bp); break;
+    case 6: moddown_conv_body<6>(t, pcoef, pl, pc, Lp1, N, i, bp); break;
+    case 7: moddown_conv_body<7>(t, pcoef, pl, pc, Lp1, N, i, bp); break;
+    default: moddown_conv_body<8>(t, pcoef, pl, pc, Lp1, N, i, bp); break;
     }
 }
 // out[b][p][l][i] = (acc[b][p][l][i] - t[b][p][l][i]) * P^-1 + add_p[b][l][perm_g(i)]
 // add0 / add1 may be null; perm applies when g != 0.  grid = (N/256, n, batch*2)
 __global__ void k_moddown_fin(u64 *__restrict__ out, size_t out_outer, const u64 *__restrict__ acc, const u64 *__restrict__ t, const u64 *__restrict__ add0,
                               const u64 *__restrict__ add1, size_t add_outer, const KsPlan *__restrict__ pl, const PrimeConst *__restrict__ pc, u32 g, int logn, int N) {
-    const int i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= N) return;
-    const int l = blockIdx.y, bp = blockIdx.z, b = bp >> 1, p = bp & 1;
-    const int n = pl->n, ne = pl->ne;
-    const PrimeConst m = pc[l];
-    u64 v = sub_mod(acc[((size_t)bp * ne + l) * N + i], t[((size_t)bp * n + l) * N + i], m.q);
-    v = mul_mod(v, pl->p_inv[l], m);
-    const u64 *ad = p ? add1 : add0;
-    if (ad) {
-        const u32 s = g ? ntt_perm((u32)i, g, logn) : (u32)i;
-        v = add_mod(v, ad[(size_t)b * add_outer + (size_t)l * N + s], m.q);
+#pragma unroll
+    for (int u_ = 0; u_ < kElems; ++u_) {
+        const int i = (blockIdx.x * kElems + u_) * blockDim.x + threadIdx.x;
+        if (i >= N) break;
+        const int l = blockIdx.y, bp = blockIdx.z, b = bp >> 1, p = bp & 1;
+        const int n = pl->n, ne = pl->ne;
+        const PrimeConst m = pc[l];
+        u64 v = sub_mod(acc[((size_t)bp * ne + l) * N + i], t[((size_t)bp * n + l) * N + i], m.q);
+        v = mul_mod_any(v, pl->p_inv[l], m);
+        const u64 *ad = p ? add1 : add0;
+        if (ad) {
+            const u32 s = g ? ntt_perm((u32)i, g, logn) : (u32)i;
+            v = add_mod(v, ad[(size_t)b * add_outer + (size_t)l * N + s], m.q);
+        }
+        out[(size_t)b * out_outer + ((size_t)p * n + l) * N + i] = v;
     }
-    out[(size_t)b * out_outer + ((size_t)p * n + l) * N + i] = v;
 }
 
 // ---------------- ChaCha20 ----------------
@@ -313,39 +452,52 @@ __global__ void k_uniform(u64 *__restrict__ out, LimbMap map, const PrimeConst *
 // b = e - a*s + msg   (all NTT form).  grid.y = n limbs
 __global__ void k_encrypt(u64 *__restrict__ b, const u64 *__restrict__ a, const u64 *__restrict__ e, const u64 *__restrict__ s, const u64 *__restrict__ msg, LimbMap map,
                           const PrimeConst *__restrict__ pc, int N) {
-    HB_ELEM_IDX();
-    const size_t so = (size_t)map.prime[li % map.n] * N + i;
-    u64 v = sub_mod(e[off], mul_mod(a[off], s[so], m), m.q);
-    b[off] = add_mod(v, msg[off], m.q);
+    const int li = blockIdx.y;
+#pragma unroll
+    for (int u_ = 0; u_ < kElems; ++u_) {
+        const int i = (blockIdx.x * kElems + u_) * blockDim.x + threadIdx.x;
+        if (i >= N) break;
+        const PrimeConst m = pc[map.prime[li % map.n]];
+        const size_t off = (size_t)li * N + i;
+        const size_t so = (size_t)map.prime[li % map.n] * N + i;
+        u64 v = sub_mod(e[off], mul_mod(a[off], s[so], m), m.q);
+        b[off] = add_mod(v, msg[off], m.q);
+    }
 }
 // out[l] = b + a*s (+ d2*s^2) for limbs l < nl of entry `index`
 __global__ void k_decrypt(u64 *__restrict__ out, const u64 *__restrict__ ct, int n, int np, const u64 *__restrict__ s, const PrimeConst *__restrict__ pc, int N) {
     const int l = blockIdx.y;
-    const int i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= N) return;
-    const PrimeConst m = pc[l];
-    const u64 sv = s[(size_t)l * N + i];
-    u64 v = add_mod(ct[(size_t)l * N + i], mul_mod(ct[((size_t)n + l) * N + i], sv, m), m.q);
-    if (np == 3) v = add_mod(v, mul_mod(ct[((size_t)2 * n + l) * N + i], mul_mod(sv, sv, m), m), m.q);
-    out[(size_t)l * N + i] = v;
+#pragma unroll
+    for (int u_ = 0; u_ < kElems; ++u_) {
+        const int i = (blockIdx.x * kElems + u_) * blockDim.x + threadIdx.x;
+        if (i >= N) break;
+        const PrimeConst m = pc[l];
+        const u64 sv = s[(size_t)l * N + i];
+        u64 v = add_mod(ct[(size_t)l * N + i], mul_mod(ct[((size_t)n + l) * N + i], sv, m), m.q);
+        if (np == 3) v = add_mod(v, mul_mod(ct[((size_t)2 * n + l) * N + i], mul_mod(sv, sv, m), m), m.q);
+        out[(size_t)l * N + i] = v;
+    }
 }
 // switching-key body: b = e - a*s + [prime in digit] * (P mod q) * s',  s' = s^2 (g == 0) or s o perm_g.
 // grid.y = nprimes; one digit per launch.
 __global__ void k_keygen(u64 *__restrict__ b, const u64 *__restrict__ a, const u64 *__restrict__ e, const u64 *__restrict__ s, const PrimeConst *__restrict__ pc, int N,
                          int logn, u32 g, int dig_lo, int dig_hi, Scalars pmod) {
     const int pi = blockIdx.y;
-    const int i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= N) return;
-    const PrimeConst m = pc[pi];
-    const size_t off = (size_t)pi * N + i;
-    u64 v = sub_mod(e[off], mul_mod(a[off], s[off], m), m.q);
-    if (pi >= dig_lo && pi < dig_hi) {
-        u64 sp;
-        if (g == 0) sp = mul_mod(s[off], s[off], m);
-        else sp = s[(size_t)pi * N + ntt_perm((u32)i, g, logn)];
-        v = add_mod(v, mul_mod(sp, pmod.v[pi], m), m.q);
+#pragma unroll
+    for (int u_ = 0; u_ < kElems; ++u_) {
+        const int i = (blockIdx.x * kElems + u_) * blockDim.x + threadIdx.x;
+        if (i >= N) break;
+        const PrimeConst m = pc[pi];
+        const size_t off = (size_t)pi * N + i;
+        u64 v = sub_mod(e[off], mul_mod(a[off], s[off], m), m.q);
+        if (pi >= dig_lo && pi < dig_hi) {
+            u64 sp;
+            if (g == 0) sp = mul_mod(s[off], s[off], m);
+            else sp = s[(size_t)pi * N + ntt_perm((u32)i, g, logn)];
+            v = add_mod(v, mul_mod(sp, pmod.v[pi], m), m.q);
+        }
+        b[off] = v;
     }
-    b[off] = v;
 }
 
 // ---------------- fused plaintext-matmul accumulate ----------------
@@ -356,24 +508,41 @@ struct PtList { const u64 *p[16]; };
 __global__ void k_matmul_acc(u64 *__restrict__ out, const u64 *__restrict__ pre, int kcount, int btotal, int b0, int bcount, PtList pts, const u32 *__restrict__ gal,
                              int n, LimbMap map, const PrimeConst *__restrict__ pc, int logn, int N) {
     const int pl = blockIdx.y, l = pl % n;
-    const int i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= N) return;
-    const PrimeConst m = pc[map.prime[l]];
-    const size_t estride = (size_t)2 * n * N;
-    u64 total = 0;
-    Acc128 s; s.zero();
-    int terms = 0;
-    for (int k = 0; k < kcount; ++k) {
-        const u32 g = __ldg(gal + k);
-        const u32 src = g == 1 ? (u32)i : ntt_perm((u32)i, g, logn);
-        for (int b = 0; b < bcount; ++b) {
-            const u64 w = pts.p[b][(size_t)l * N + src];
-            s.mad(pre[((size_t)k * btotal + b0 + b) * estride + (size_t)pl * N + i], w);
-            if (++terms == 64) { total = add_mod(total, barrett128(s.hi, s.lo, m), m.q); s.zero(); terms = 0; }
+#pragma unroll
+    for (int u_ = 0; u_ < kElems; ++u_) {
+        const int i = (blockIdx.x * kElems + u_) * blockDim.x + threadIdx.x;
+        if (i >= N) break;
+        const PrimeConst m = pc[map.prime[l]];
+        const size_t estride = (size_t)2 * n * N;
+        u64 total = 0;
+        if (m.fp) { // lazy terms below 1.6q: thousands fit in 64 bits
+            u64 acc = 0;
+            int terms = 0;
+            for (int k = 0; k < kcount; ++k) {
+                const u32 g = __ldg(gal + k);
+                const u32 src = g == 1 ? (u32)i : ntt_perm((u32)i, g, logn);
+                for (int b = 0; b < bcount; ++b) {
+                    acc += mul_small_lazy(pre[((size_t)k * btotal + b0 + b) * estride + (size_t)pl * N + i], pts.p[b][(size_t)l * N + src], m.q_inv_f, m.q);
+                    if (++terms == 256) { total = add_mod(total, reduce_fp(acc, m.q_inv_f, m.q), m.q); acc = 0; terms = 0; }
+                }
+            }
+            total = add_mod(total, reduce_fp(acc, m.q_inv_f, m.q), m.q);
+        } else {
+            Acc128 s; s.zero();
+            int terms = 0;
+            for (int k = 0; k < kcount; ++k) {
+                const u32 g = __ldg(gal + k);
+                const u32 src = g == 1 ? (u32)i : ntt_perm((u32)i, g, logn);
+                for (int b = 0; b < bcount; ++b) {
+                    const u64 w = pts.p[b][(size_t)l * N + src];
+                    s.mad(pre[((size_t)k * btotal + b0 + b) * estride + (size_t)pl * N + i], w);
+                    if (++terms == 64) { total = add_mod(total, barrett128(s.hi, s.lo, m), m.q); s.zero(); terms = 0; }
+                }
+            }
+            total = add_mod(total, barrett128(s.hi, s.lo, m), m.q);
         }
+        out[(size_t)pl * N + i] = total;
     }
-    total = add_mod(total, barrett128(s.hi, s.lo, m), m.q);
-    out[(size_t)pl * N + i] = total;
 }
 
 } // namespace hb

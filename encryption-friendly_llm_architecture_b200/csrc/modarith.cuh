@@ -22,10 +22,11 @@ struct PrimeConst {
     u64 mu_hi, mu_lo;   // floor(2^128 / q)
     u64 n_inv, n_inv_sh; // N^-1 mod q and its Shoup companion
     u64 iu, iu_sh;      // psi^(N/2): the image of the imaginary unit
-    u64 small;          // 1 when q < 2^44: the NTT uses the FP64-assisted product (see mul_fp_lazy)
+    u64 small;          // 1 when q < 2^44 and N = 2^16: the NTT tables hold w/q doubles (see mul_fp_lazy)
     double q_inv_f;     // 1/q
     double n_inv_f;     // n_inv / q
-    u64 pad[2];
+    u64 fp;             // 1 when q < 2^44: element-wise kernels take quotients from the FP64 pipe
+    u64 pad;
 };
 
 // Limb instances of a launch: instance li (0 <= li < count) uses prime[li % n].
@@ -103,6 +104,30 @@ __device__ __forceinline__ u64 reduce_fp_lazy(u64 v, double q_inv, u64 q) {
 __device__ __forceinline__ u64 reduce_fp(u64 v, double q_inv, u64 q) {
     const u64 r = reduce_fp_lazy(v, q_inv, q); // (0.4q, 1.6q)
     return r >= q ? r - q : r;
+}
+
+// a*b for a, b < 2^44 and q < 2^44: result congruent to a*b in (0.4q, 1.6q).  The double product is only
+// used for the quotient estimate (relative error 2^-52, far below one unit); the remainder is exact.
+__device__ __forceinline__ u64 mul_small_lazy_d(u64 a, double ad, u64 b, double bd, double q_inv, u64 q) {
+    const u64 qh = mantissa52(__fma_rn(ad * bd, q_inv, kTwo52));
+    return mad2_lo64(a, b, qh, 0ull - q, q);
+}
+__device__ __forceinline__ u64 mul_small_lazy(u64 a, u64 b, double q_inv, u64 q) {
+    return mul_small_lazy_d(a, u52_to_double(a), b, u52_to_double(b), q_inv, q);
+}
+// canonical a*b mod q, choosing the FP64-assisted form for small primes
+__device__ __forceinline__ u64 mul_mod_any(u64 a, u64 b, const PrimeConst &m) {
+    if (m.fp) { const u64 r = mul_small_lazy(a, b, m.q_inv_f, m.q); return r >= m.q ? r - m.q : r; }
+    return mul_mod(a, b, m);
+}
+// canonical residue of a signed value
+__device__ __forceinline__ u64 reduce_i64_any(i64 v, const PrimeConst &m) {
+    const u64 a = v < 0 ? (u64)(-(v + 1)) + 1 : (u64)v;
+    if (m.fp && a < (1ull << 51)) {
+        u64 r = reduce_fp(a, m.q_inv_f, m.q);
+        return (v < 0 && r) ? m.q - r : r;
+    }
+    return reduce_i64(v, m);
 }
 
 // 128-bit accumulator for lazy sums of products

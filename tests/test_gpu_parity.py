@@ -107,6 +107,34 @@ def test_schedule_parity(request, pkg, size, name):
     assert err_g < TOL and err_g == err_o
 
 
+def test_full_size_golden_fixtures(pkg, gpu_full):
+    """Full-size results against digests recorded from the oracle (no oracle run needed here):
+    the primitive sweep cases and BASELINE config 1, one 128x128 ct x ct product."""
+    import hashlib, json, os
+    from conftest import ROOT
+    gold = json.load(open(os.path.join(ROOT, "tests", "golden", "golden.json")))["full"]
+    dg = lambda a: hashlib.sha256(np.ascontiguousarray(a, dtype=np.uint64).tobytes()).hexdigest()
+    g = gpu_full
+    assert [int(q) for q in g.primes] == gold["primes"]
+    g.gen_rot_keys([1, 128, 4096])
+    for lvl in (12, 4, 1):
+        data = rand_ct_residues(g, lvl, 2, 1, seed=500 + lvl)
+        ct = g.ct_create(lvl, 2, 1)
+        g.ct_import(ct, data)
+        pt = g.encode(np.random.default_rng(600 + lvl).uniform(-1, 1, g.slots), lvl)
+        assert dg(g.ct_export(g.rotate(ct, 1))) == gold["primitives"][f"rotate1@{lvl}"]
+        assert dg(g.ct_export(g.rotate(ct, 4096))) == gold["primitives"][f"rotate4096@{lvl}"]
+        assert dg(g.ct_export(g.relin(g.tensor(ct, ct)))) == gold["primitives"][f"tensor_relin@{lvl}"]
+        assert dg(g.ct_export(g.rescale(g.mul_pt_norescale(ct, pt)))) == gold["primitives"][f"rescale@{lvl}"]
+        c2 = g.ct_create(lvl, 2, 1)
+        g.ct_import(c2, data)
+        g.ntt(c2)
+        assert dg(g.ct_export(c2)) == gold["primitives"][f"ntt@{lvl}"]
+    exports, err = cases.sc_ccmm_single_tile(g, pkg.open_hemmer(g), target=4)
+    assert dg(exports[0]) == gold["config1_ccmm_128"]["digest"]
+    assert err < TOL and err == gold["config1_ccmm_128"]["max_abs_err"]
+
+
 def test_error_codes(pkg, gpu_small):
     g = gpu_small
     a = g.ct_create(3, 2, 1)
