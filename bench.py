@@ -78,7 +78,7 @@ class ClockSampler:
 # CPU arm: exact operation counts of the layer from a dry run of the oracle's schedules, times
 # per-operation timings sampled on the host cores.
 # ---------------------------------------------------------------------------------------------
-def cpu_layer_estimate(pkg, sample_reps=8):
+def cpu_layer_estimate(pkg, sample_reps=40):
     # launchers export OMP_NUM_THREADS=1; the CPU arm is meant to use every host core (set before libgomp loads)
     os.environ["OMP_NUM_THREADS"] = str(os.cpu_count() or 1)
     lib_path = os.path.join(ROOT, "oracle", "_build", "liboracle.so")
@@ -318,6 +318,48 @@ def run_gpu(args):
         dist.destroy_process_group()
 
 
+def run_sweep(args):
+    """BASELINE config 5: primitive sweep on a batch of 256 independent ciphertexts with uniform residues, levels 12/8/4/1.
+    Prints one JSON object: per operation the time, the algorithmic bytes and the fraction of the measured HBM peak."""
+    import torch
+    pkg = importlib.import_module(PKG)
+    torch.cuda.set_device(0)
+    lib = pkg.open_gpu(pkg.make_params(), device=0)
+    lib.keygen()
+    lib.gen_rot_keys([1, 128, 4096])
+    lib.dll.hb_stream.restype = C.c_void_p
+    stream = torch.cuda.ExternalStream(lib.dll.hb_stream(lib.ctx), device=torch.device("cuda", 0))
+    hbm, which = peaks()
+    B, K = 256, 3
+    out = {"sweep": "256 ciphertexts, N=2^16", "peak_gbs": hbm, "peak_source": which, "rows": []}
+    rng = np.random.default_rng(5)
+    for lv in (12, 8, 4, 1):
+        n = lv + 1
+        beta = (lv + 1) // 4 + 1            # digits in use: limb i belongs to digit (i+1)/4
+        data = np.empty((B, 2, n, lib.N), dtype=np.uint64)
+        for l in range(n):
+            data[:, :, l, :] = rng.integers(0, int(lib.primes[l]), size=(B, 2, lib.N), dtype=np.uint64)
+        ct = lib.ct_create(lv, 2, B)
+        lib.ct_import(ct, data)
+        del data
+        pt = lib.encode(rng.uniform(-1, 1, lib.slots), lv)
+        key = 2 * beta * (n + K)
+        ops = [("ntt", lambda: lib.ntt(ct, False), B * 2 * n * 2), ("intt", lambda: lib.ntt(ct, True), B * 2 * n * 2)]
+        for st in (1, 128, 4096):
+            ops.append((f"rotate{st}", lambda st=st: lib.rotate(ct, st), B * 4 * n + key))
+        ops.append(("tensor+relin", lambda: lib.relin(lib.tensor(ct, ct)), B * 6 * n + key))
+        if lv >= 1:
+            prod = lib.mul_pt_norescale(ct, pt)
+            ops.append(("rescale", lambda: lib.rescale(prod), B * (4 * n - 2)))
+        for name, fn, limbs in ops:
+            fn(); fn()
+            ms = timed_single(torch, stream, lib, fn, 3)
+            alg = limbs * LIMB
+            out["rows"].append({"op": name, "level": lv, "ms": round(ms, 4), "algorithmic_bytes": alg, "gbs": round(alg / ms / 1e6, 1), "frac": round(alg / ms / 1e6 / hbm, 4)})
+        del ct
+    print(json.dumps(out), flush=True)
+
+
 def timed_single(torch, stream, lib, fn, reps):
     lib.sync()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -338,9 +380,12 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
     ap.add_argument("--one-step", action="store_true", help="run a single pass of the layer and exit (launch-list profiling)")
+    ap.add_argument("--sweep", action="store_true", help="primitive sweep on 256 ciphertexts (BASELINE config 5) instead of the layer")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
-    if args.impl == "reference":
+    if args.sweep:
+        run_sweep(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_gpu(args)

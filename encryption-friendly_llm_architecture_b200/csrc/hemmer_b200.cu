@@ -445,7 +445,7 @@ int hb_ctx_create(const hb_params *prm, int device, hb_ctx **out) {
         HostParams hp{prm->log_n, prm->max_level, prm->dnum, prm->num_special, prm->q0_bits, prm->q_bits, prm->p_bits, prm->hamming_weight, prm->sigma,
                       {prm->seed[0], prm->seed[1], prm->seed[2], prm->seed[3]}};
         c->h.reset(new HostCtx(hp));
-        if (!(c->h->logn == 16 || c->h->logn <= 12)) throw std::invalid_argument("log_n must be 16 or at most 12");
+        if (!(c->h->logn == 16 || (c->h->logn >= 10 && c->h->logn <= 12))) throw std::invalid_argument("log_n must be 16, or 10..12 for small test contexts");
         c->device = device; c->N = c->h->N; c->logn = c->h->logn; c->L = c->h->L; c->K = c->h->K; c->nprimes = c->h->nprimes;
         for (int i = 0; i < 8; ++i) c->ckey.k[i] = c->h->cha.key[i];
         CK(cudaSetDevice(device));

@@ -319,41 +319,56 @@ __global__ void k_modup(u64 *__restrict__ dt, const u64 *__restrict__ a_coef, co
 // digit_dg[j] is a_ntt[j] for own limbs and dt[...] otherwise.  grid = (N/256, ne, batch)
 __global__ void k_ks_inner(u64 *__restrict__ acc, const u64 *__restrict__ a_ntt, size_t a_outer, const u64 *__restrict__ dt, const u64 *__restrict__ key, int key_primes,
                            const KsPlan *__restrict__ pl, const PrimeConst *__restrict__ pc, u32 g, int logn, int N) {
+    const int j = blockIdx.y, b = blockIdx.z;
+    const int pj = pl->ext_prime[j], nd = pl->nd, ne = pl->ne;
+    const PrimeConst m = pc[pj];
+    const u32 x0 = blockIdx.x * (blockDim.x * kElems) + threadIdx.x;
+    u32 src[kElems];
 #pragma unroll
-    for (int u_ = 0; u_ < kElems; ++u_) {
-        const int i = (blockIdx.x * kElems + u_) * blockDim.x + threadIdx.x;
-        if (i >= N) break;
-        const int j = blockIdx.y, b = blockIdx.z;
-        const int pj = pl->ext_prime[j], nd = pl->nd, ne = pl->ne;
-        const PrimeConst m = pc[pj];
-        const u32 s = g ? ntt_perm((u32)i, g, logn) : (u32)i;
-        u64 r0, r1;
-        if (m.fp) {
-            u64 t0 = 0, t1 = 0;
-            for (int dg = 0; dg < nd; ++dg) {
-                const int en = pl->dt_entry[dg][j];
-                const u64 v = en < 0 ? a_ntt[(size_t)b * a_outer + (size_t)j * N + s] : dt[((size_t)b * pl->dt_count + en) * N + s];
-                const u64 *k0 = key + (((size_t)dg * 2) * key_primes + pj) * N + i;
-                const u64 ka = k0[0], kb = k0[(size_t)key_primes * N];
+    for (int u = 0; u < kElems; ++u) { const u32 i = x0 + u * blockDim.x; src[u] = g ? ntt_perm(i, g, logn) : i; }
+    const u64 *abase = a_ntt + (size_t)b * a_outer + (size_t)j * N;
+    const u64 *dbase = dt + (size_t)b * pl->dt_count * N;
+    const u64 *kbase = key + (size_t)pj * N + x0;
+    const size_t kpoly = (size_t)key_primes * N;
+    u64 r0[kElems], r1[kElems];
+    if (m.fp) {
+#pragma unroll
+        for (int u = 0; u < kElems; ++u) { r0[u] = 0; r1[u] = 0; }
+        for (int dg = 0; dg < nd; ++dg) {
+            const int en = pl->dt_entry[dg][j];
+            const u64 *sp = en < 0 ? abase : dbase + (size_t)en * N;
+            const u64 *k0 = kbase + (size_t)dg * 2 * kpoly;
+#pragma unroll
+            for (int u = 0; u < kElems; ++u) {
+                const u64 v = sp[src[u]], ka = k0[u * blockDim.x], kb = k0[kpoly + u * blockDim.x];
                 const double vd = u52_to_double(v);
-                t0 += mul_small_lazy_d(v, vd, ka, u52_to_double(ka), m.q_inv_f, m.q);
-                t1 += mul_small_lazy_d(v, vd, kb, u52_to_double(kb), m.q_inv_f, m.q);
+                r0[u] += mul_small_lazy_d(v, vd, ka, u52_to_double(ka), m.q_inv_f, m.q);
+                r1[u] += mul_small_lazy_d(v, vd, kb, u52_to_double(kb), m.q_inv_f, m.q);
             }
-            r0 = reduce_fp(t0, m.q_inv_f, m.q); r1 = reduce_fp(t1, m.q_inv_f, m.q);
-        } else {
-            Acc128 s0, s1; s0.zero(); s1.zero();
-            for (int dg = 0; dg < nd; ++dg) {
-                const int en = pl->dt_entry[dg][j];
-                const u64 v = en < 0 ? a_ntt[(size_t)b * a_outer + (size_t)j * N + s] : dt[((size_t)b * pl->dt_count + en) * N + s];
-                const u64 *k0 = key + (((size_t)dg * 2) * key_primes + pj) * N + i;
-                s0.mad(v, k0[0]);
-                s1.mad(v, k0[(size_t)key_primes * N]);
-            }
-            r0 = barrett128(s0.hi, s0.lo, m); r1 = barrett128(s1.hi, s1.lo, m);
         }
-        acc[(((size_t)b * 2) * ne + j) * N + i] = r0;
-        acc[(((size_t)b * 2 + 1) * ne + j) * N + i] = r1;
+#pragma unroll
+        for (int u = 0; u < kElems; ++u) { r0[u] = reduce_fp(r0[u], m.q_inv_f, m.q); r1[u] = reduce_fp(r1[u], m.q_inv_f, m.q); }
+    } else {
+        Acc128 s0[kElems], s1[kElems];
+#pragma unroll
+        for (int u = 0; u < kElems; ++u) { s0[u].zero(); s1[u].zero(); }
+        for (int dg = 0; dg < nd; ++dg) {
+            const int en = pl->dt_entry[dg][j];
+            const u64 *sp = en < 0 ? abase : dbase + (size_t)en * N;
+            const u64 *k0 = kbase + (size_t)dg * 2 * kpoly;
+#pragma unroll
+            for (int u = 0; u < kElems; ++u) {
+                const u64 v = sp[src[u]];
+                s0[u].mad(v, k0[u * blockDim.x]);
+                s1[u].mad(v, k0[kpoly + u * blockDim.x]);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < kElems; ++u) { r0[u] = barrett128(s0[u].hi, s0[u].lo, m); r1[u] = barrett128(s1[u].hi, s1[u].lo, m); }
     }
+    u64 *o0 = acc + (((size_t)b * 2) * ne + j) * N + x0, *o1 = o0 + (size_t)ne * N;
+#pragma unroll
+    for (int u = 0; u < kElems; ++u) { o0[u * blockDim.x] = r0[u]; o1[u * blockDim.x] = r1[u]; }
 }
 
 // ModDown conversion: pcoef [bp][K][N] (special limbs, coefficient form) -> t [bp][n][N] (coefficient form)

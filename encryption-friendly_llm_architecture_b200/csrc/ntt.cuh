@@ -119,7 +119,7 @@ constexpr int kN16 = 65536;
 constexpr int kRowStride = 272; // 256 + one pad word per 16: conflict-free 16-consecutive reads
 
 // ---- forward, column pass: stages 1..8.  Output range [0, 4q). ----
-__global__ void __launch_bounds__(256) ntt16_fwd_cols(const u64 *__restrict__ src, LimbAddr sa, u64 *__restrict__ dst, LimbAddr da,
+__global__ void __launch_bounds__(256, 4) ntt16_fwd_cols(const u64 *__restrict__ src, LimbAddr sa, u64 *__restrict__ dst, LimbAddr da,
                                                       LimbMap map, const PrimeConst *__restrict__ pc, NttTables tb) {
     __shared__ u64 sm[4096];
     const int li = blockIdx.y, pi = map.prime[li % map.n];
@@ -145,7 +145,7 @@ __global__ void __launch_bounds__(256) ntt16_fwd_cols(const u64 *__restrict__ sr
 }
 
 // ---- forward, row pass: stages 9..16.  Input [0, 4q), output canonical [0, q). ----
-__global__ void __launch_bounds__(256) ntt16_fwd_rows(const u64 *__restrict__ src, LimbAddr sa, u64 *__restrict__ dst, LimbAddr da,
+__global__ void __launch_bounds__(256, 4) ntt16_fwd_rows(const u64 *__restrict__ src, LimbAddr sa, u64 *__restrict__ dst, LimbAddr da,
                                                       LimbMap map, const PrimeConst *__restrict__ pc, NttTables tb) {
     __shared__ u64 sm[16 * kRowStride];
     const int li = blockIdx.y, pi = map.prime[li % map.n];
@@ -182,7 +182,7 @@ __global__ void __launch_bounds__(256) ntt16_fwd_rows(const u64 *__restrict__ sr
 }
 
 // ---- inverse, row pass: undoes stages 16..9.  Input canonical, output [0, 2q). ----
-__global__ void __launch_bounds__(256, 3) ntt16_inv_rows(const u64 *__restrict__ src, LimbAddr sa, u64 *__restrict__ dst, LimbAddr da,
+__global__ void __launch_bounds__(256, 4) ntt16_inv_rows(const u64 *__restrict__ src, LimbAddr sa, u64 *__restrict__ dst, LimbAddr da,
                                                       LimbMap map, const PrimeConst *__restrict__ pc, NttTables tb) {
     __shared__ u64 sm[16 * kRowStride];
     const int li = blockIdx.y, pi = map.prime[li % map.n];
@@ -222,7 +222,7 @@ __global__ void __launch_bounds__(256, 3) ntt16_inv_rows(const u64 *__restrict__
 }
 
 // ---- inverse, column pass: undoes stages 8..1, scales by N^-1.  Input [0, 2q), output canonical. ----
-__global__ void __launch_bounds__(256, 3) ntt16_inv_cols(const u64 *__restrict__ src, LimbAddr sa, u64 *__restrict__ dst, LimbAddr da,
+__global__ void __launch_bounds__(256, 4) ntt16_inv_cols(const u64 *__restrict__ src, LimbAddr sa, u64 *__restrict__ dst, LimbAddr da,
                                                       LimbMap map, const PrimeConst *__restrict__ pc, NttTables tb) {
     __shared__ u64 sm[4096];
     const int li = blockIdx.y, pi = map.prime[li % map.n];
