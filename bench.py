@@ -189,6 +189,7 @@ def run_gpu(args):
     lib = pkg.open_gpu(pkg.make_params(), device=local)
     lib.keygen()
     H = pkg.open_hemmer(lib)
+    H.set_schedule(args.schedule)
     lib.dll.hb_stream.restype = C.c_void_p
     lib.dll.hb_launch_count.restype = C.c_uint64
     stream = torch.cuda.ExternalStream(lib.dll.hb_stream(lib.ctx), device=torch.device("cuda", local))
@@ -308,7 +309,7 @@ def run_gpu(args):
                "sample": f"sum over {info['distinct_ops_timed']} distinct (operation, level) pairs of exact count x one sampled full-size timing ({info['sample_seconds']} s of CPU work)"}
     line = {"metric": METRIC, "value": ms_step, "unit": "ms", "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,
             "higher_is_better": False, "scaling": "strong", "vs_baseline": None, "dtype": "u64", "data": "synthetic",
-            "config": {"workload": "bert_base_layer_matmuls_fwd_plus_lora_bwd", "units": len(wl.units), "batched_calls": True, "ring_degree": 65536, "levels": 12, "tile": 128,
+            "config": {"workload": "bert_base_layer_matmuls_fwd_plus_lora_bwd", "units": len(wl.units), "batched_calls": True, "schedule": "direct_hoisted" if args.schedule == 1 else "reference_sequence", "ring_degree": 65536, "levels": 12, "tile": 128,
                        "l2": "working set per step is tens of GB, far above the 126 MB L2", "max_abs_err_vs_float64": err},
             "roofline": roofline, "cpu_baseline": cpu,
             "e2e": {"value": ms_e2e, "unit": "ms", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
@@ -380,6 +381,8 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
     ap.add_argument("--one-step", action="store_true", help="run a single pass of the layer and exit (launch-list profiling)")
+    ap.add_argument("--schedule", type=int, default=1, choices=[0, 1],
+                    help="0: the reference's rotation sequence; 1 (default): direct, hoisted rotations (same products, fewer chained key switches)")
     ap.add_argument("--sweep", action="store_true", help="primitive sweep on 256 ciphertexts (BASELINE config 5) instead of the layer")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup

@@ -112,6 +112,9 @@ class HEMMer {
     CtxtTensor diagonalToRow(const CtxtTensor &t);
 
     MaskCache &masks() { return masks_; }
+    // 0: the reference's rotation sequence; 1: direct (hoisted) rotations -- see sched::ScheduleMode
+    void setSchedule(int mode) { schedule_ = mode; }
+    int schedule() const { return schedule_; }
 
   private:
     hb_ctx *ctx_;
@@ -119,6 +122,7 @@ class HEMMer {
     Evaluator eval_;
     i64 slots_ = 0, tile_ = 0;
     int max_level_ = 0;
+    int schedule_ = 0;
     MaskCache masks_;
 };
 

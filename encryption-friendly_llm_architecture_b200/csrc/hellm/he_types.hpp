@@ -78,6 +78,16 @@ class Plaintext {
     std::shared_ptr<hb_pt> p_;
 };
 
+// The step-independent half of a rotation of one ciphertext (lifted key-switch digits), shared by all its rotations.
+class Hoisted {
+  public:
+    Hoisted() = default;
+    explicit Hoisted(hb_digits *d) : d_(d, [](hb_digits *x) { hb_digits_free(x); }) {}
+    hb_digits *raw() const { return d_.get(); }
+  private:
+    std::shared_ptr<hb_digits> d_;
+};
+
 // The subset of HEaaN::HomEvaluator / EnDecoder the matmul path uses (HomEvaluator.hpp:30-616).
 class Evaluator {
   public:
@@ -115,6 +125,12 @@ class Evaluator {
         hb_ct *o = nullptr; check(c_, hb_rotate(c_, a.raw(), steps, &o)); return Ciphertext(c_, o);
     }
     Ciphertext rightRotate(const Ciphertext &a, i64 steps) const { return leftRotate(a, -steps); }
+    // many rotations of one ciphertext: decompose once, then one cheap call per step (same bits as leftRotate)
+    Hoisted decompose(const Ciphertext &a) const { hb_digits *d = nullptr; check(c_, hb_decompose(c_, a.raw(), &d)); return Hoisted(d); }
+    Ciphertext leftRotate(const Ciphertext &a, const Hoisted &h, i64 steps) const {
+        check(c_, hb_gen_rot_keys(c_, &steps, 1));
+        hb_ct *o = nullptr; check(c_, hb_rotate_hoisted(c_, a.raw(), h.raw(), steps, &o)); return Ciphertext(c_, o);
+    }
     Plaintext leftRotate(const Plaintext &p, i64 steps) const { hb_pt *o = nullptr; check(c_, hb_pt_rotate(c_, p.raw(), steps, &o)); return Plaintext(o); }
     // rescale(a (.) pa + b (.) pb): the "assemble" step of the matmul loops in one pass
     Ciphertext assemble(const Ciphertext &a, const Plaintext &pa, const Ciphertext &b, const Plaintext &pb) const {

@@ -98,7 +98,7 @@ void HEMMer::decrypt2(const CtxtTensor &t, double *out) const {
 void HEMMer::addInplace(CtxtTensor &a, const CtxtTensor &b) const { a.get() = eval_.add(a.get(), b.get()); }
 
 // ---- schedules ----
-#define HB_ENV sched::Env env{eval_, slots_, masks_}
+#define HB_ENV sched::Env env{eval_, slots_, masks_, schedule_}
 CtxtTensor HEMMer::singleCCMatMul(const CtxtTensor &a, const CtxtTensor &b, int t) { HB_ENV; return sched::multMatMatCC(env, a, b, t); }
 CtxtTensor HEMMer::packedMatMul(const CtxtTensor &a, const CtxtTensor &b, int t) { HB_ENV; return sched::multPackedMatMat(env, a, b, t); }
 CtxtTensor HEMMer::packedMatMulPre(const CtxtTensor &a, int t) { HB_ENV; return sched::multPackedMatMatPre(env, a, t); }

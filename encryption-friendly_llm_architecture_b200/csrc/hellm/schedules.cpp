@@ -110,8 +110,13 @@ Ciphertext bsgs_diagonals(Env &e, const Ciphertext &op, const TileTensorShape &s
     auto mask = [&](i64 idx) -> const Plaintext & { return cached(e, kind, s, idx, level, [&] { return diag_family_mask(e, s, f, idx); }); };
     std::vector<Ciphertext> baby;
     baby.reserve((size_t)f.bs);
-    baby.push_back(e.ev.leftRotate(op, f.gap));
-    for (i64 j = 1; j < f.bs; ++j) baby.push_back(e.ev.leftRotate(baby.back(), f.gap));
+    if (e.mode == kDirect) {
+        const Hoisted h = e.ev.decompose(op);
+        for (i64 j = 0; j < f.bs; ++j) baby.push_back(e.ev.leftRotate(op, h, (j + 1) * f.gap));
+    } else {
+        baby.push_back(e.ev.leftRotate(op, f.gap));
+        for (i64 j = 1; j < f.bs; ++j) baby.push_back(e.ev.leftRotate(baby.back(), f.gap));
+    }
     Ciphertext res = e.ev.mult(op, mask(0));
     for (i64 i = 0; i < f.gs; ++i) {
         const i64 rot_num = i * f.bs * f.gap;
@@ -178,8 +183,13 @@ CtxtTensor transpose(Env &e, const CtxtTensor &op) {
     };
     std::vector<Ciphertext> baby;
     baby.reserve((size_t)bs);
-    baby.push_back(e.ev.rightRotate(op.get(), (num_rows - 1) * gap));
-    for (i64 j = 1; j < bs; ++j) baby.push_back(e.ev.leftRotate(baby.back(), gap));
+    if (e.mode == kDirect) {
+        const Hoisted h = e.ev.decompose(op.get());
+        for (i64 j = 0; j < bs; ++j) baby.push_back(e.ev.leftRotate(op.get(), h, (j - (num_rows - 1)) * gap));
+    } else {
+        baby.push_back(e.ev.rightRotate(op.get(), (num_rows - 1) * gap));
+        for (i64 j = 1; j < bs; ++j) baby.push_back(e.ev.leftRotate(baby.back(), gap));
+    }
     Ciphertext res;
     for (i64 i = 0; i < gs; ++i) {
         i64 idx = 1 - num_rows + i * bs;
@@ -219,18 +229,29 @@ CtxtTensor multMatMatCC(Env &e, const CtxtTensor &op1, const CtxtTensor &op2, in
     Ciphertext b = e.ev.levelDown(diagonalToRow(e, CtxtTensor(sb, op2.get())).get(), lvl);
     const i64 rows_tmp = num_k > num_rows ? num_k : ceil_pow2(num_rows), cols_tmp = num_k > num_cols ? num_k : ceil_pow2(num_cols);
     Ciphertext res = e.ev.mult(a, b);
-    a = e.ev.leftRotate(a, 1);
-    b = e.ev.leftRotate(b, width);
-    Ciphertext a_wrap = e.ev.rightRotate(a, cols_tmp), b_wrap = e.ev.rightRotate(b, rows_tmp * width);
     Ciphertext acc;
-    for (i64 i = 1; i < num_k; ++i) {
-        if (i > 1) {
-            a = e.ev.leftRotate(a, 1); a_wrap = e.ev.leftRotate(a_wrap, 1);
-            b = e.ev.leftRotate(b, width); b_wrap = e.ev.leftRotate(b_wrap, width);
+    if (e.mode == kDirect) {
+        const Hoisted ha = e.ev.decompose(a), hb = e.ev.decompose(b);
+        for (i64 i = 1; i < num_k; ++i) {
+            Ciphertext ai = e.ev.leftRotate(a, ha, i), aw = e.ev.leftRotate(a, ha, i - cols_tmp);
+            Ciphertext bi = e.ev.leftRotate(b, hb, i * width), bw = e.ev.leftRotate(b, hb, (i - rows_tmp) * width);
+            Ciphertext ak = e.ev.assemble(ai, col_wrap(e, sa, 2 * i + 1, lvl), aw, col_wrap(e, sa, 2 * i, lvl));
+            Ciphertext bk = e.ev.assemble(bi, row_wrap(e, sb, 2 * i + 1, lvl), bw, row_wrap(e, sb, 2 * i, lvl));
+            e.ev.tensorAccumulate(acc, ak, bk);
         }
-        Ciphertext ak = e.ev.assemble(a, col_wrap(e, sa, 2 * i + 1, lvl), a_wrap, col_wrap(e, sa, 2 * i, lvl));
-        Ciphertext bk = e.ev.assemble(b, row_wrap(e, sb, 2 * i + 1, lvl), b_wrap, row_wrap(e, sb, 2 * i, lvl));
-        e.ev.tensorAccumulate(acc, ak, bk);
+    } else {
+        a = e.ev.leftRotate(a, 1);
+        b = e.ev.leftRotate(b, width);
+        Ciphertext a_wrap = e.ev.rightRotate(a, cols_tmp), b_wrap = e.ev.rightRotate(b, rows_tmp * width);
+        for (i64 i = 1; i < num_k; ++i) {
+            if (i > 1) {
+                a = e.ev.leftRotate(a, 1); a_wrap = e.ev.leftRotate(a_wrap, 1);
+                b = e.ev.leftRotate(b, width); b_wrap = e.ev.leftRotate(b_wrap, width);
+            }
+            Ciphertext ak = e.ev.assemble(a, col_wrap(e, sa, 2 * i + 1, lvl), a_wrap, col_wrap(e, sa, 2 * i, lvl));
+            Ciphertext bk = e.ev.assemble(b, row_wrap(e, sb, 2 * i + 1, lvl), b_wrap, row_wrap(e, sb, 2 * i, lvl));
+            e.ev.tensorAccumulate(acc, ak, bk);
+        }
     }
     res = e.ev.add(res, e.ev.rescale(e.ev.relinearize(acc)));
     return CtxtTensor(TileTensorShape(num_rows, num_cols, width), std::move(res));
@@ -248,17 +269,27 @@ CtxtTensor multPackedMatMat(Env &e, const CtxtTensor &op1, const CtxtTensor &op2
     Ciphertext b = packedDiagonalToRow(e, CtxtTensor(sb, e.ev.levelDown(op2.get(), target_level + 2))).get();
     const i64 cols_tmp = num_k > num_cols ? num_k : ceil_pow2(num_cols);
     Ciphertext res = e.ev.mult(a, b);
-    a = e.ev.leftRotate(a, 2);
-    b = e.ev.leftRotate(b, 2 * width);
-    Ciphertext a_wrap = e.ev.rightRotate(a, cols_tmp);
     Ciphertext acc;
-    for (i64 i = 1; i < num_k / 2; ++i) {
-        if (i > 1) {
-            a = e.ev.leftRotate(a, 2); a_wrap = e.ev.leftRotate(a_wrap, 2);
-            b = e.ev.leftRotate(b, 2 * width);
+    if (e.mode == kDirect) {
+        const Hoisted ha = e.ev.decompose(a), hb = e.ev.decompose(b);
+        for (i64 i = 1; i < num_k / 2; ++i) {
+            Ciphertext ai = e.ev.leftRotate(a, ha, 2 * i), aw = e.ev.leftRotate(a, ha, 2 * i - cols_tmp);
+            Ciphertext bi = e.ev.leftRotate(b, hb, 2 * i * width);
+            Ciphertext ak = e.ev.assemble(ai, col_wrap(e, sa, 4 * i + 1, lvl), aw, col_wrap(e, sa, 4 * i, lvl));
+            e.ev.tensorAccumulate(acc, ak, bi);
         }
-        Ciphertext ak = e.ev.assemble(a, col_wrap(e, sa, 4 * i + 1, lvl), a_wrap, col_wrap(e, sa, 4 * i, lvl));
-        e.ev.tensorAccumulate(acc, ak, b);
+    } else {
+        a = e.ev.leftRotate(a, 2);
+        b = e.ev.leftRotate(b, 2 * width);
+        Ciphertext a_wrap = e.ev.rightRotate(a, cols_tmp);
+        for (i64 i = 1; i < num_k / 2; ++i) {
+            if (i > 1) {
+                a = e.ev.leftRotate(a, 2); a_wrap = e.ev.leftRotate(a_wrap, 2);
+                b = e.ev.leftRotate(b, 2 * width);
+            }
+            Ciphertext ak = e.ev.assemble(a, col_wrap(e, sa, 4 * i + 1, lvl), a_wrap, col_wrap(e, sa, 4 * i, lvl));
+            e.ev.tensorAccumulate(acc, ak, b);
+        }
     }
     res = e.ev.add(res, e.ev.rescale(e.ev.relinearize(acc)));
     return CtxtTensor(TileTensorShape(num_rows, num_cols, width), std::move(res));
@@ -273,6 +304,14 @@ Ciphertext multPackedMatMatPreRot(Env &e, const CtxtTensor &in, int target_level
     const int lvl = target_level + 2;
     std::vector<Ciphertext> copies;
     copies.push_back(e.ev.levelDownOne(in.get()));
+    if (e.mode == kDirect) {
+        const Hoisted h = e.ev.decompose(in.get());
+        for (i64 i = 1; i < num_rows / 2; ++i) {
+            Ciphertext ai = e.ev.leftRotate(in.get(), h, 2 * i), aw = e.ev.leftRotate(in.get(), h, 2 * i - num_rows);
+            copies.push_back(e.ev.assemble(ai, col_wrap(e, in.getShape(), 4 * i + 1, lvl), aw, col_wrap(e, in.getShape(), 4 * i, lvl)));
+        }
+        return e.ev.stack(copies);
+    }
     Ciphertext a = e.ev.leftRotate(in.get(), 2);
     Ciphertext a_wrap = e.ev.rightRotate(a, num_rows);
     for (i64 i = 1; i < num_rows / 2; ++i) {
@@ -290,8 +329,9 @@ CtxtTensor multPackedMatMatCCReuse(Env &e, const Ciphertext &pre, const CtxtTens
     const i64 width = tb.getBlockWidth();
     Ciphertext b = tb.get(), acc;
     const int count = pre.getBatch();
+    const Hoisted h = e.mode == kDirect ? e.ev.decompose(tb.get()) : Hoisted();
     for (int i = 0; i < count; ++i) {
-        if (i > 0) b = e.ev.leftRotate(b, 2 * width);
+        if (i > 0) b = e.mode == kDirect ? e.ev.leftRotate(tb.get(), h, (i64)i * 2 * width) : e.ev.leftRotate(b, 2 * width);
         e.ev.tensorAccumulate(acc, e.ev.slice(pre, i), b);
     }
     return CtxtTensor(tb.getShape(), e.ev.rescale(e.ev.relinearize(acc)));
@@ -304,6 +344,14 @@ Ciphertext multMatMatPre(Env &e, const CtxtTensor &in, int target_level) {
     CtxtTensor s = diagonalToColumn(e, CtxtTensor(in.getShape(), e.ev.levelDown(in.get(), target_level + 3)));
     std::vector<Ciphertext> copies;
     copies.push_back(e.ev.levelDownOne(s.get()));
+    if (e.mode == kDirect) {
+        const Hoisted h = e.ev.decompose(s.get());
+        for (i64 i = 1; i < num_rows; ++i) {
+            Ciphertext ai = e.ev.leftRotate(s.get(), h, i), aw = e.ev.leftRotate(s.get(), h, i - num_rows);
+            copies.push_back(e.ev.assemble(ai, col_wrap(e, s.getShape(), 2 * i + 1, lvl), aw, col_wrap(e, s.getShape(), 2 * i, lvl)));
+        }
+        return e.ev.stack(copies);
+    }
     Ciphertext a = e.ev.leftRotate(s.get(), 1);
     Ciphertext a_wrap = e.ev.rightRotate(a, num_rows);
     for (i64 i = 1; i < num_rows; ++i) {
@@ -326,8 +374,9 @@ CtxtTensor multMatMatCCReUse(Env &e, const Ciphertext &pre, const CtxtTensor &tb
     const i64 width = tb.getBlockWidth();
     Ciphertext b = tb.get(), acc;
     const int count = pre.getBatch();
+    const Hoisted h = e.mode == kDirect ? e.ev.decompose(tb.get()) : Hoisted();
     for (int i = 0; i < count; ++i) {
-        if (i > 0) b = e.ev.leftRotate(b, width);
+        if (i > 0) b = e.mode == kDirect ? e.ev.leftRotate(tb.get(), h, (i64)i * width) : e.ev.leftRotate(b, width);
         e.ev.tensorAccumulate(acc, e.ev.slice(pre, i), b);
     }
     return CtxtTensor(tb.getShape(), e.ev.relinearize(acc));

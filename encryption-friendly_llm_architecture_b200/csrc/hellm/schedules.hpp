@@ -8,10 +8,18 @@ namespace sched {
 // mask families, used as the first component of MaskCache::Key
 enum MaskKind { kDiagonal = 0, kHorizontal, kVertical, kPackedHorizontal, kPackedVertical, kColWrap, kRowWrap, kHemmer };
 
-struct Env { // what a schedule needs: evaluator, slot count, mask cache
+// Schedule variants.  kFaithful keeps the reference's sequence of rotations (each shifted copy is the previous one
+// rotated once more).  kDirect takes every shifted copy straight from the transformed operand, rot(x, k) instead of
+// rot(rot(...), 1): the same slots, fewer chained key switches (less noise), and all rotations of one ciphertext
+// share the step-independent half of the key switch (hoisting).  The two variants give different ciphertext bits;
+// the CPU oracle implements both so that each can be checked bit for bit.
+enum ScheduleMode { kFaithful = 0, kDirect = 1 };
+
+struct Env { // what a schedule needs: evaluator, slot count, mask cache, variant
     const Evaluator &ev;
     i64 slots;
     MaskCache &cache;
+    int mode = kFaithful;
 };
 
 CtxtTensor transpose(Env &e, const CtxtTensor &op);

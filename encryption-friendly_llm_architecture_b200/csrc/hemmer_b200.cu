@@ -118,6 +118,8 @@ struct hb_ctx {
 #define LAUNCH(c) ((c)->launches++, 0)
 struct hb_ct { hb_ctx *ctx; int level, np, batch, spow; u64 *d; size_t limbs() const { return (size_t)batch * np * (level + 1); } };
 struct hb_pt { hb_ctx *ctx; int level, spow; u64 *d; };
+// lifted digits of the a-part of a ciphertext batch, NTT form: what all rotations of that ciphertext share
+struct hb_digits { hb_ctx *ctx; int level, batch; u64 *d; };
 
 namespace {
 
@@ -224,24 +226,42 @@ PlanDims plan_dims(hb_ctx *c, int level) {
 
 // Hybrid key switch of polynomial a (NTT form, `n` limbs, per-batch stride a_outer) with key `key`:
 //   out[b][p][l] = ModDown(sum_dg perm_g(lift_dg(a)) (.) key_dg)[p][l] + add_p[b][l] o perm_g
-void keyswitch(hb_ctx *c, const u64 *a, size_t a_outer, int level, int batch, const Evk &key, u32 g, u64 *out, size_t out_outer, const u64 *add0, const u64 *add1,
-               size_t add_outer) {
+// Phase 1 of a key switch (shared by every rotation of the same polynomial -- "hoisting"):
+//   dt[b][entry] = NTT(lift of digit dg of a to ext limb j), for the limbs outside the digit.
+void ks_decompose(hb_ctx *c, const u64 *a, size_t a_outer, int level, int batch, u64 *dt) {
+    const KsPlan *pl = get_plan(c, level);
+    const PlanDims d = plan_dims(c, level);
+    const int N = c->N, n = d.n;
+    const unsigned gx1 = (unsigned)((N + 255) / 256); // base-conversion kernels keep one coefficient per thread
+    Tmp acoef(c, (size_t)batch * n);
+    ntt(c, a, a_outer, acoef.p, (size_t)n * N, batch * n, c->qmap(level), true);
+    LAUNCH(c), k_modup<<<dim3(gx1, d.nd, batch), 256, 0, c->st>>>(dt, acoef.p, pl, c->pc, N);
+    ntt_inplace(c, dt, batch * d.dt_count, d.dtmap, false);
+}
+// Phase 2: inner product of the (permuted) digits with the key over Q_level u P, then ModDown:
+//   out[b][p][l] = ModDown(sum_dg perm_g(digit_dg) (.) key_dg)[p][l] + add_p[b][l] o perm_g
+void ks_apply(hb_ctx *c, const u64 *a, size_t a_outer, const u64 *dt, int level, int batch, const Evk &key, u32 g, u64 *out, size_t out_outer, const u64 *add0,
+              const u64 *add1, size_t add_outer) {
     const KsPlan *pl = get_plan(c, level);
     const PlanDims d = plan_dims(c, level);
     const int N = c->N, n = d.n, ne = d.ne, K = d.K;
-    const LimbMap qm = c->qmap(level);
-    const unsigned gx1 = (unsigned)((N + 255) / 256), gx = c->gx(); // base-conversion kernels keep one coefficient per thread
-    Tmp acoef(c, (size_t)batch * n), dt(c, (size_t)batch * d.dt_count), acc(c, (size_t)batch * 2 * ne), pco(c, (size_t)batch * 2 * K), t(c, (size_t)batch * 2 * n);
-    ntt(c, a, a_outer, acoef.p, (size_t)n * N, batch * n, qm, true);
-    LAUNCH(c), k_modup<<<dim3(gx1, d.nd, batch), 256, 0, c->st>>>(dt.p, acoef.p, pl, c->pc, N);
-    ntt_inplace(c, dt.p, batch * d.dt_count, d.dtmap, false);
-    LAUNCH(c), k_ks_inner<<<dim3(gx, ne, batch), 256, 0, c->st>>>(acc.p, a, a_outer, dt.p, key.d, c->nprimes, pl, c->pc, g, c->logn, N);
+    const unsigned gx1 = (unsigned)((N + 255) / 256), gx = c->gx();
+    Tmp acc(c, (size_t)batch * 2 * ne), pco(c, (size_t)batch * 2 * K), t(c, (size_t)batch * 2 * n);
+    LAUNCH(c), k_ks_inner<<<dim3(gx, ne, batch), 256, 0, c->st>>>(acc.p, a, a_outer, dt, key.d, c->nprimes, pl, c->pc, g, c->logn, N);
     LimbMap pm{}; pm.n = K; for (int k = 0; k < K; ++k) pm.prime[k] = (unsigned char)(c->L + 1 + k);
     ntt(c, acc.p + (size_t)n * N, (size_t)ne * N, pco.p, (size_t)K * N, batch * 2 * K, pm, true);
     LAUNCH(c), k_moddown_conv<<<dim3(gx1, 1, batch * 2), 256, 0, c->st>>>(t.p, pco.p, pl, c->pc, c->L + 1, N);
-    ntt_inplace(c, t.p, batch * 2 * n, qm, false);
+    ntt_inplace(c, t.p, batch * 2 * n, c->qmap(level), false);
     LAUNCH(c), k_moddown_fin<<<dim3(gx, n, batch * 2), 256, 0, c->st>>>(out, out_outer, acc.p, t.p, add0, add1, add_outer, pl, c->pc, g, c->logn, N);
     CK(cudaGetLastError());
+}
+// Hybrid key switch of polynomial a (NTT form, `n` limbs, per-batch stride a_outer) with key `key`
+void keyswitch(hb_ctx *c, const u64 *a, size_t a_outer, int level, int batch, const Evk &key, u32 g, u64 *out, size_t out_outer, const u64 *add0, const u64 *add1,
+               size_t add_outer) {
+    const PlanDims d = plan_dims(c, level);
+    Tmp dt(c, (size_t)batch * d.dt_count);
+    ks_decompose(c, a, a_outer, level, batch, dt.p);
+    ks_apply(c, a, a_outer, dt.p, level, batch, key, g, out, out_outer, add0, add1, add_outer);
 }
 
 // switching key for secret s' (g == 0: s^2, else s o perm_g); stream ids kid*64 + digit
@@ -753,6 +773,34 @@ int hb_mul(hb_ctx *c, const hb_ct *a, const hb_ct *b, hb_ct **out) {
         hb_ct_free(t);
         try { *out = do_rescale(c, r); } catch (...) { hb_ct_free(r); throw; }
         hb_ct_free(r);
+    });
+}
+int hb_decompose(hb_ctx *c, const hb_ct *a, hb_digits **out) {
+    return guard(c, [&] {
+        if (a->np != 2) fail(HB_E_SHAPE, "decompose: needs 2 polys");
+        const PlanDims d = plan_dims(c, a->level);
+        const int n = a->level + 1, N = c->N;
+        hb_digits *h = new hb_digits{c, a->level, a->batch, nullptr};
+        try {
+            h->d = c->alloc_limbs((size_t)a->batch * d.dt_count);
+            ks_decompose(c, a->d + (size_t)n * N, (size_t)2 * n * N, a->level, a->batch, h->d);
+        } catch (...) { c->pool.put(h->d); delete h; throw; }
+        *out = h;
+    });
+}
+void hb_digits_free(hb_digits *h) { if (h) { h->ctx->pool.put(h->d); delete h; } }
+int hb_rotate_hoisted(hb_ctx *c, const hb_ct *a, const hb_digits *dg, int64_t steps, hb_ct **out) {
+    return guard(c, [&] {
+        if (a->np != 2 || dg->level != a->level || dg->batch != a->batch) fail(HB_E_SHAPE, "rotate_hoisted: digits do not belong to this ciphertext");
+        const u64 g = c->h->galois_rot(steps);
+        const int n = a->level + 1, N = c->N;
+        hb_ct *r = new_ct(c, a->level, 2, a->batch, a->spow);
+        if (g == 1) { CK(cudaMemcpyAsync(r->d, a->d, a->limbs() * N * 8, cudaMemcpyDeviceToDevice, c->st)); *out = r; return; }
+        try {
+            const Evk &key = galois_key(c, g);
+            ks_apply(c, a->d + (size_t)n * N, (size_t)2 * n * N, dg->d, a->level, a->batch, key, (u32)g, r->d, (size_t)2 * n * N, a->d, nullptr, (size_t)2 * n * N);
+        } catch (...) { hb_ct_free(r); throw; }
+        *out = r;
     });
 }
 int hb_rotate(hb_ctx *c, const hb_ct *a, int64_t steps, hb_ct **out) { return guard(c, [&] { *out = do_galois(c, a, c->h->galois_rot(steps)); }); }

@@ -66,9 +66,15 @@ class Hemmer:
         if rc != 0:
             raise HBError(rc, "hemmer_create failed")
         self._nonce = 1000
+        self.schedule = 0
 
     def _fn(self, name):
         return getattr(self.dll, self.prefix + name)
+
+    def set_schedule(self, mode: int):
+        """0: the reference's rotation sequence (default); 1: direct rotations of the transformed operand, hoisted."""
+        self.lib._chk(self._fn("set_schedule")(self.h, C.c_int(mode)))
+        self.schedule = mode
 
     def close(self):
         if self.h:

@@ -27,6 +27,7 @@ extern "C" {
 typedef struct hb_ctx hb_ctx;
 typedef struct hb_ct hb_ct;
 typedef struct hb_pt hb_pt;
+typedef struct hb_digits hb_digits;
 
 enum {
     HB_OK = 0,
@@ -129,6 +130,13 @@ int hb_relin(hb_ctx *ctx, const hb_ct *a, hb_ct **out);                         
 int hb_mul(hb_ctx *ctx, const hb_ct *a, const hb_ct *b, hb_ct **out);           /* mult(ct,ct) :311-312 */
 int hb_rotate(hb_ctx *ctx, const hb_ct *a, int64_t left_steps, hb_ct **out);    /* leftRotate :383 / rightRotate :403 */
 int hb_conjugate(hb_ctx *ctx, const hb_ct *a, hb_ct **out);                     /* conjugate :465 */
+/* Hoisted rotations: hb_decompose does the part of leftRotate that does not depend on the step (inverse NTT,
+ * lift of every key-switch digit, forward NTT); hb_rotate_hoisted finishes one rotation from it.  The result is bit
+ * for bit hb_rotate(a, left_steps): rotation is defined as decompose-then-permute.  (HEaaN exposes no such split;
+ * the reference's loops call leftRotate once per step, MatrixUtils.cpp:1416-1420.) */
+int hb_decompose(hb_ctx *ctx, const hb_ct *a, hb_digits **out);
+int hb_rotate_hoisted(hb_ctx *ctx, const hb_ct *a, const hb_digits *digits, int64_t left_steps, hb_ct **out);
+void hb_digits_free(hb_digits *digits);
 /* raw forward / inverse NTT of every limb of the batch, in place (primitive sweep) */
 int hb_ntt(hb_ctx *ctx, hb_ct *a, int inverse);
 

@@ -51,6 +51,12 @@ struct Hemmer {
     Mask col_mask_even_, row_mask_even_, mask_left_half_;
     std::map<int, Pt> mask_matmul_;
 
+    // 0: the reference's rotation sequence (each shifted copy is the previous one rotated once more).
+    // 1: "direct" variant -- every shifted copy is one rotation of the transformed operand itself, rot(x, k).
+    //    Same slots, different ciphertext bits (fewer chained key switches).  The CUDA library implements the
+    //    same variant with hoisting; both variants are compared bit for bit.
+    int mode = 0;
+
     Hemmer(Context &c, Evaluator &e) : cx(c), ev(e), slots(c.slots) {
         tile = 1; while (2 * tile * tile < slots) tile <<= 1;
         gen_axis_masks();
@@ -282,8 +288,12 @@ struct Hemmer {
         const i64 gs = (i64)std::ceil((double)(num_rows + num_cols - 1) / (double)bs);
         const i64 gap = width - 1;
         std::vector<Ct> bs_rot((size_t)bs);
-        bs_rot[0] = rotR(op.ct, (num_rows - 1) * gap);
-        for (i64 j = 1; j < bs; j++) bs_rot[(size_t)j] = rotL(bs_rot[(size_t)j - 1], gap);
+        if (mode == 1) {
+            for (i64 j = 0; j < bs; j++) bs_rot[(size_t)j] = rotL(op.ct, (j - (num_rows - 1)) * gap);
+        } else {
+            bs_rot[0] = rotR(op.ct, (num_rows - 1) * gap);
+            for (i64 j = 1; j < bs; j++) bs_rot[(size_t)j] = rotL(bs_rot[(size_t)j - 1], gap);
+        }
         Ct res, gs_tmp;
         for (i64 i = 0; i < gs; i++) {
             i64 idx = 1 - num_rows + i * bs;
@@ -307,8 +317,12 @@ struct Hemmer {
         const i64 bs = (i64)std::ceil(std::sqrt((double)(2 * sub_dim - 1)));
         const i64 gs = (i64)std::ceil((double)(sub_dim - 1) / (double)bs);
         std::vector<Ct> bs_rot((size_t)bs);
-        bs_rot[0] = rotL(op, gap);
-        for (i64 j = 1; j < bs; j++) bs_rot[(size_t)j] = rotL(bs_rot[(size_t)j - 1], gap);
+        if (mode == 1) {
+            for (i64 j = 0; j < bs; j++) bs_rot[(size_t)j] = rotL(op, (j + 1) * gap);
+        } else {
+            bs_rot[0] = rotL(op, gap);
+            for (i64 j = 1; j < bs; j++) bs_rot[(size_t)j] = rotL(bs_rot[(size_t)j - 1], gap);
+        }
         Ct res = mult_msg(op, mask[0]);
         for (i64 i = 0; i < gs; i++) {
             const i64 rot_num = i * bs * gap;
@@ -381,20 +395,29 @@ struct Hemmer {
         const i64 num_rows_tmp = (num_k > num_rows) ? num_k : pow2_ceil(num_rows);
         const i64 num_cols_tmp = (num_k > num_cols) ? num_k : pow2_ceil(num_cols);
         Ct res = ev.mul(a.ct, b.ct);
-        a.ct = rotL(a.ct, 1);
-        b.ct = rotL(b.ct, width);
-        Ct a_rot = rotR(a.ct, num_cols_tmp);
-        Ct b_rot = rotR(b.ct, num_rows_tmp * width);
         Ct itxt_res;
-        for (i64 i = 1; i < num_k; i++) {
-            if (i > 1) {
-                a.ct = rotL(a.ct, 1); a_rot = rotL(a_rot, 1);
-                b.ct = rotL(b.ct, width); b_rot = rotL(b_rot, width);
+        if (mode == 1) {
+            for (i64 i = 1; i < num_k; i++) {
+                Ct tmp1 = assemble(rotL(a.ct, i), col_mask[(size_t)(2 * i + 1)], rotL(a.ct, i - num_cols_tmp), col_mask[(size_t)(2 * i)]);
+                Ct tmp2 = assemble(rotL(b.ct, i * width), row_mask[(size_t)(2 * i + 1)], rotL(b.ct, (i - num_rows_tmp) * width), row_mask[(size_t)(2 * i)]);
+                Ct t = ev.tensor(tmp1, tmp2);
+                itxt_res = (i == 1) ? t : ev.add(itxt_res, t);
             }
-            Ct tmp1 = assemble(a.ct, col_mask[(size_t)(2 * i + 1)], a_rot, col_mask[(size_t)(2 * i)]);
-            Ct tmp2 = assemble(b.ct, row_mask[(size_t)(2 * i + 1)], b_rot, row_mask[(size_t)(2 * i)]);
-            Ct t = ev.tensor(tmp1, tmp2);
-            itxt_res = (i == 1) ? t : ev.add(itxt_res, t);
+        } else {
+            a.ct = rotL(a.ct, 1);
+            b.ct = rotL(b.ct, width);
+            Ct a_rot = rotR(a.ct, num_cols_tmp);
+            Ct b_rot = rotR(b.ct, num_rows_tmp * width);
+            for (i64 i = 1; i < num_k; i++) {
+                if (i > 1) {
+                    a.ct = rotL(a.ct, 1); a_rot = rotL(a_rot, 1);
+                    b.ct = rotL(b.ct, width); b_rot = rotL(b_rot, width);
+                }
+                Ct tmp1 = assemble(a.ct, col_mask[(size_t)(2 * i + 1)], a_rot, col_mask[(size_t)(2 * i)]);
+                Ct tmp2 = assemble(b.ct, row_mask[(size_t)(2 * i + 1)], b_rot, row_mask[(size_t)(2 * i)]);
+                Ct t = ev.tensor(tmp1, tmp2);
+                itxt_res = (i == 1) ? t : ev.add(itxt_res, t);
+            }
         }
         Ct tail = ev.rescale(ev.relin(itxt_res));
         res = ev.add(res, tail);
@@ -418,18 +441,26 @@ struct Hemmer {
         b = packed_diagonal_to_row(b);
         const i64 num_cols_tmp = (num_k > num_cols) ? num_k : pow2_ceil(num_cols);
         Ct res = ev.mul(a.ct, b.ct);
-        a.ct = rotL(a.ct, 2);
-        b.ct = rotL(b.ct, 2 * width);
-        Ct a_rot = rotR(a.ct, num_cols_tmp);
         Ct itxt_res;
-        for (i64 i = 1; i < num_k / 2; i++) {
-            if (i > 1) {
-                a.ct = rotL(a.ct, 2); a_rot = rotL(a_rot, 2);
-                b.ct = rotL(b.ct, 2 * width);
+        if (mode == 1) {
+            for (i64 i = 1; i < num_k / 2; i++) {
+                Ct tmp1 = assemble(rotL(a.ct, 2 * i), col_mask[(size_t)(4 * i + 1)], rotL(a.ct, 2 * i - num_cols_tmp), col_mask[(size_t)(4 * i)]);
+                Ct t = ev.tensor(tmp1, rotL(b.ct, 2 * i * width));
+                itxt_res = (i == 1) ? t : ev.add(itxt_res, t);
             }
-            Ct tmp1 = assemble(a.ct, col_mask[(size_t)(4 * i + 1)], a_rot, col_mask[(size_t)(4 * i)]);
-            Ct t = ev.tensor(tmp1, b.ct);
-            itxt_res = (i == 1) ? t : ev.add(itxt_res, t);
+        } else {
+            a.ct = rotL(a.ct, 2);
+            b.ct = rotL(b.ct, 2 * width);
+            Ct a_rot = rotR(a.ct, num_cols_tmp);
+            for (i64 i = 1; i < num_k / 2; i++) {
+                if (i > 1) {
+                    a.ct = rotL(a.ct, 2); a_rot = rotL(a_rot, 2);
+                    b.ct = rotL(b.ct, 2 * width);
+                }
+                Ct tmp1 = assemble(a.ct, col_mask[(size_t)(4 * i + 1)], a_rot, col_mask[(size_t)(4 * i)]);
+                Ct t = ev.tensor(tmp1, b.ct);
+                itxt_res = (i == 1) ? t : ev.add(itxt_res, t);
+            }
         }
         Ct tail = ev.rescale(ev.relin(itxt_res));
         res = ev.add(res, tail);
@@ -446,9 +477,14 @@ struct Hemmer {
         std::vector<Ct> tmp;
         Ct a = a_in.ct;
         tmp.push_back(ev.level_down(a, a.level - 1));
+        auto &col_mask = get_col_mask(a_in.sh, target_level + 2);
+        if (mode == 1) {
+            for (i64 i = 1; i < num_rows / 2; i++)
+                tmp.push_back(assemble(rotL(a_in.ct, 2 * i), col_mask[(size_t)(4 * i + 1)], rotL(a_in.ct, 2 * i - num_rows), col_mask[(size_t)(4 * i)]));
+            return stack(tmp);
+        }
         a = rotL(a, 2);
         Ct a_rot = rotR(a, num_rows);
-        auto &col_mask = get_col_mask(a_in.sh, target_level + 2);
         for (i64 i = 1; i < num_rows / 2; i++) {
             if (i > 1) { a = rotL(a, 2); a_rot = rotL(a_rot, 2); }
             tmp.push_back(assemble(a, col_mask[(size_t)(4 * i + 1)], a_rot, col_mask[(size_t)(4 * i)]));
@@ -466,7 +502,7 @@ struct Hemmer {
         Ct b = b_in.ct;
         Ct sum = ev.tensor(slice(pre, 0), b);
         for (int i = 1; i < pre.batch; ++i) {
-            b = rotL(b, 2 * width);
+            b = mode == 1 ? rotL(b_in.ct, (i64)i * 2 * width) : rotL(b, 2 * width);
             sum = ev.add(sum, ev.tensor(slice(pre, i), b));
         }
         return CtT{ev.rescale(ev.relin(sum)), Shape(b_in.sh.rows, b_in.sh.cols, width)};
@@ -480,9 +516,14 @@ struct Hemmer {
         a = diagonal_to_column(a);
         std::vector<Ct> tmp;
         tmp.push_back(ev.level_down(a.ct, a.ct.level - 1));
+        auto &col_mask = get_col_mask(a.sh, target_level + 2);
+        if (mode == 1) {
+            for (i64 i = 1; i < num_rows; i++)
+                tmp.push_back(assemble(rotL(a.ct, i), col_mask[(size_t)(2 * i + 1)], rotL(a.ct, i - num_rows), col_mask[(size_t)(2 * i)]));
+            return stack(tmp);
+        }
         a.ct = rotL(a.ct, 1);
         Ct a_rot = rotR(a.ct, num_rows);
-        auto &col_mask = get_col_mask(a.sh, target_level + 2);
         for (i64 i = 1; i < num_rows; i++) {
             if (i > 1) { a.ct = rotL(a.ct, 1); a_rot = rotL(a_rot, 1); }
             tmp.push_back(assemble(a.ct, col_mask[(size_t)(2 * i + 1)], a_rot, col_mask[(size_t)(2 * i)]));
@@ -513,7 +554,7 @@ struct Hemmer {
         Ct b = b_in.ct;
         Ct sum = ev.tensor(slice(pre, 0), b);
         for (int i = 1; i < pre.batch; ++i) {
-            b = rotL(b, width);
+            b = mode == 1 ? rotL(b_in.ct, (i64)i * width) : rotL(b, width);
             sum = ev.add(sum, ev.tensor(slice(pre, i), b));
         }
         return CtT{ev.relin(sum), Shape(b_in.sh.rows, b_in.sh.cols, width)};

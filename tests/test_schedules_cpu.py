@@ -27,3 +27,19 @@ def test_shape_and_level_errors(pkg, orc_small, H):
     low = pkg.CtxtTensor(orc_small.level_down(a.ct, 3), d, d)
     with pytest.raises(pkg.HBError):  # level guard (MatrixUtils.cpp:1320-1324)
         H.single_cc_matmul(low, low, 2)
+
+
+DIRECT = ["transforms", "ccmm_two_tiles", "pcmm_reuse", "cc_reuse", "packed", "packed_reuse"]
+
+
+@pytest.mark.parametrize("name", DIRECT)
+def test_direct_schedule_semantics(name, pkg, orc_small):
+    """The direct-rotation variant (every shifted copy is one rotation of the transformed operand) computes the same products."""
+    Hd = pkg.Hemmer(orc_small)
+    Hd.set_schedule(1)
+    exports_d, err = cases.SCENARIOS[name](orc_small, Hd)
+    assert err < TOL, (name, err)
+    Hf = pkg.Hemmer(orc_small)
+    exports_f, _ = cases.SCENARIOS[name](orc_small, Hf)
+    import numpy as np
+    assert any(not np.array_equal(a, b) for a, b in zip(exports_d, exports_f)), "variants are expected to differ in bits"
