@@ -249,6 +249,13 @@ def run_gpu(args):
     launches = (lib.dll.hb_launch_count(lib.ctx) - l0) // max(args.steps, 1)
     clocks = sampler.stop()
     ms_step = ms_total / args.steps
+    # the same layer with the reference's own rotation sequence (no hoisting), for comparison
+    ms_faithful = None
+    if args.schedule == 1 and not args.no_compare:
+        H.set_schedule(0)
+        wl.step_resident()
+        ms_faithful = timed_region(lambda s: wl.step_resident(), 1)
+        H.set_schedule(1)
 
     # end to end: host matrices in, decrypted host results out, every step
     wl.h2d_bytes = wl.d2h_bytes = 0
@@ -302,6 +309,9 @@ def run_gpu(args):
                 "traffic_source": "ncu dram bytes of a 32-ciphertext capture, scaled by limbs: each of the two passes reads and writes every limb once",
                 "intt_gbs": roof["intt"]["gbs"], "keyswitch": ks}
 
+    pb, iu = C.c_uint64(), C.c_uint64()
+    lib.dll.hb_mem_info(lib.ctx, C.byref(pb), C.byref(iu))
+    pool_gb = round(pb.value / 2 ** 30, 1)
     cpu_ms, info = cpu_layer_estimate(pkg) if world == 1 and not args.no_cpu else (None, {})
     cpu = None
     if cpu_ms is not None:
@@ -310,7 +320,8 @@ def run_gpu(args):
     line = {"metric": METRIC, "value": ms_step, "unit": "ms", "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,
             "higher_is_better": False, "scaling": "strong", "vs_baseline": None, "dtype": "u64", "data": "synthetic",
             "config": {"workload": "bert_base_layer_matmuls_fwd_plus_lora_bwd", "units": len(wl.units), "batched_calls": True, "schedule": "direct_hoisted" if args.schedule == 1 else "reference_sequence", "ring_degree": 65536, "levels": 12, "tile": 128,
-                       "l2": "working set per step is tens of GB, far above the 126 MB L2", "max_abs_err_vs_float64": err},
+                       "l2": "working set per step is tens of GB, far above the 126 MB L2", "max_abs_err_vs_float64": err,
+                       "reference_sequence_ms": ms_faithful, "device_pool_gb": pool_gb},
             "roofline": roofline, "cpu_baseline": cpu,
             "e2e": {"value": ms_e2e, "unit": "ms", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
             "gpu_launches": launches, "clocks": clocks}
@@ -331,10 +342,10 @@ def run_sweep(args):
     lib.dll.hb_stream.restype = C.c_void_p
     stream = torch.cuda.ExternalStream(lib.dll.hb_stream(lib.ctx), device=torch.device("cuda", 0))
     hbm, which = peaks()
-    B, K = 256, 3
-    out = {"sweep": "256 ciphertexts, N=2^16", "peak_gbs": hbm, "peak_source": which, "rows": []}
+    B, K = args.sweep_batch, 3
+    out = {"sweep": f"{B} ciphertexts, N=2^16", "peak_gbs": hbm, "peak_source": which, "rows": []}
     rng = np.random.default_rng(5)
-    for lv in (12, 8, 4, 1):
+    for lv in [int(x) for x in args.sweep_levels.split(",")]:
         n = lv + 1
         beta = (lv + 1) // 4 + 1            # digits in use: limb i belongs to digit (i+1)/4
         data = np.empty((B, 2, n, lib.N), dtype=np.uint64)
@@ -383,6 +394,9 @@ def main():
     ap.add_argument("--one-step", action="store_true", help="run a single pass of the layer and exit (launch-list profiling)")
     ap.add_argument("--schedule", type=int, default=1, choices=[0, 1],
                     help="0: the reference's rotation sequence; 1 (default): direct, hoisted rotations (same products, fewer chained key switches)")
+    ap.add_argument("--no-compare", action="store_true", help="skip the extra timed pass with the reference's rotation sequence")
+    ap.add_argument("--sweep-batch", type=int, default=256)
+    ap.add_argument("--sweep-levels", type=str, default="12,8,4,1")
     ap.add_argument("--sweep", action="store_true", help="primitive sweep on 256 ciphertexts (BASELINE config 5) instead of the layer")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
