@@ -179,6 +179,17 @@ class Lib:
         self._chk(self._fn("batch_get")(self.ctx, src.ptr, C.c_int(idx), C.byref(out)))
         return Handle(self, out, "ct")
 
+    def batch_concat(self, parts):
+        arr = (C.c_void_p * len(parts))(*[p.ptr.value for p in parts])
+        out = C.c_void_p()
+        self._chk(self._fn("batch_concat")(self.ctx, arr, C.c_int(len(parts)), C.byref(out)))
+        return Handle(self, out, "ct")
+
+    def batch_slice(self, src, start, count):
+        out = C.c_void_p()
+        self._chk(self._fn("batch_slice")(self.ctx, src.ptr, C.c_int(start), C.c_int(count), C.byref(out)))
+        return Handle(self, out, "ct")
+
     def sync(self):
         self._chk(self._fn("sync")(self.ctx))
 

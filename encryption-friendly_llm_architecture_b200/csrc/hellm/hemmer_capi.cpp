@@ -49,6 +49,21 @@ int hb_hemmer_matmul_cc(hb_hemmer *h, const hb_ct *a, int ra, int ca, int wa, co
         *out = h->h.singleCCMatMul(ta, tb, target).get().release();
     });
 }
+int hb_hemmer_matmul_cc_prepare(hb_hemmer *h, const hb_ct *a, int ra, int ca, int wa, const hb_ct *b, int rb, int cb, int wb, int target, hb_ct **out_a, hb_ct **out_b) {
+    return guard([&] {
+        Borrow ba(h->ctx, a), bb(h->ctx, b);
+        CtxtTensor ta = view(ba, ra, ca, wa), tb = view(bb, rb, cb, wb);
+        Ciphertext sa, sb;
+        h->h.ccMatMulPrepare(ta, tb, target, sa, sb);
+        *out_a = sa.release(); *out_b = sb.release();
+    });
+}
+int hb_hemmer_matmul_cc_core(hb_hemmer *h, const hb_ct *sa, const hb_ct *tb, int rows, int inner, int cols, int width, int target, hb_ct **out) {
+    return guard([&] {
+        Borrow ba(h->ctx, sa), bb(h->ctx, tb);
+        *out = h->h.ccMatMulCore(Ciphertext(ba.c), Ciphertext(bb.c), rows, inner, cols, width, target).get().release();
+    });
+}
 int hb_hemmer_packed_matmul(hb_hemmer *h, const hb_ct *a, int ra, int ca, int wa, const hb_ct *b, int rb, int cb, int wb, int target, hb_ct **out) {
     return guard([&] {
         Borrow ba(h->ctx, a), bb(h->ctx, b);

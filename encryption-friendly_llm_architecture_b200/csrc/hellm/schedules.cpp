@@ -217,16 +217,25 @@ CtxtTensor packedDiagonalToRow(Env &e, const CtxtTensor &op) {
     return CtxtTensor(s, bsgs_diagonals(e, op.get(), s, true, true));
 }
 
-// multMatMat<Ciphertext> -- MatrixUtils.cpp:1307-1446
-CtxtTensor multMatMatCC(Env &e, const CtxtTensor &op1, const CtxtTensor &op2, int target_level) {
+// multMatMat<Ciphertext> -- MatrixUtils.cpp:1307-1446, in two halves so that callers holding operands of different
+// levels (a transposed tile sits one level lower) can run the transforms per group and the product loop on all of
+// them together.  First half: sigma(A), tau(B), both brought to target + 2 (:1346-1361).
+void ccmmPrepare(Env &e, const CtxtTensor &op1, const CtxtTensor &op2, int target_level, Ciphertext &sa_out, Ciphertext &tb_out) {
     require_product_shapes(op1, op2);
     const i64 num_rows = op1.getHeight(), num_cols = op2.getWidth(), width = op1.getBlockWidth();
     const i64 num_k = ceil_pow2(op1.getWidth());
     if (std::min(op1.getLevel(), op2.getLevel()) < target_level + 3) throw std::invalid_argument("[multMatMat] level too low");
     const TileTensorShape sa(num_rows, num_k, width), sb(num_k, num_cols, width);
     const int lvl = target_level + 2;
-    Ciphertext a = e.ev.levelDown(diagonalToColumn(e, CtxtTensor(sa, op1.get())).get(), lvl);
-    Ciphertext b = e.ev.levelDown(diagonalToRow(e, CtxtTensor(sb, op2.get())).get(), lvl);
+    sa_out = e.ev.levelDown(diagonalToColumn(e, CtxtTensor(sa, op1.get())).get(), lvl);
+    tb_out = e.ev.levelDown(diagonalToRow(e, CtxtTensor(sb, op2.get())).get(), lvl);
+}
+// Second half: the k = 0 term, the shift-mask-tensor loop, relinearise, rescale, add (:1376-1443).
+CtxtTensor ccmmCore(Env &e, Ciphertext a, Ciphertext b, i64 num_rows, i64 inner, i64 num_cols, i64 width, int target_level) {
+    const i64 num_k = ceil_pow2(inner);
+    const TileTensorShape sa(num_rows, num_k, width), sb(num_k, num_cols, width);
+    const int lvl = target_level + 2;
+    if (a.getLevel() != lvl || b.getLevel() != lvl) throw std::invalid_argument("[multMatMat] operands of the product loop must sit at target + 2");
     const i64 rows_tmp = num_k > num_rows ? num_k : ceil_pow2(num_rows), cols_tmp = num_k > num_cols ? num_k : ceil_pow2(num_cols);
     Ciphertext res = e.ev.mult(a, b);
     Ciphertext acc;
@@ -255,6 +264,11 @@ CtxtTensor multMatMatCC(Env &e, const CtxtTensor &op1, const CtxtTensor &op2, in
     }
     res = e.ev.add(res, e.ev.rescale(e.ev.relinearize(acc)));
     return CtxtTensor(TileTensorShape(num_rows, num_cols, width), std::move(res));
+}
+CtxtTensor multMatMatCC(Env &e, const CtxtTensor &op1, const CtxtTensor &op2, int target_level) {
+    Ciphertext a, b;
+    ccmmPrepare(e, op1, op2, target_level, a, b);
+    return ccmmCore(e, std::move(a), std::move(b), op1.getHeight(), op1.getWidth(), op2.getWidth(), op1.getBlockWidth(), target_level);
 }
 
 // multPackedMatMat -- MatrixUtils.cpp:1100-1216

@@ -694,6 +694,33 @@ int hb_batch_get(hb_ctx *c, const hb_ct *src, int idx, hb_ct **out) {
     });
 }
 
+int hb_batch_concat(hb_ctx *c, const hb_ct *const *parts, int n, hb_ct **out) {
+    return guard(c, [&] {
+        if (n < 1) fail(HB_E_ARG, "batch_concat: nothing to join");
+        int total = 0;
+        for (int k = 0; k < n; ++k) {
+            if (parts[k]->level != parts[0]->level || parts[k]->np != parts[0]->np || parts[k]->spow != parts[0]->spow) fail(HB_E_SHAPE, "batch_concat: mismatch");
+            total += parts[k]->batch;
+        }
+        hb_ct *r = new_ct(c, parts[0]->level, parts[0]->np, total, parts[0]->spow);
+        size_t off = 0;
+        for (int k = 0; k < n; ++k) {
+            const size_t words = parts[k]->limbs() * c->N;
+            CK(cudaMemcpyAsync(r->d + off, parts[k]->d, words * 8, cudaMemcpyDeviceToDevice, c->st));
+            off += words;
+        }
+        *out = r;
+    });
+}
+int hb_batch_slice(hb_ctx *c, const hb_ct *src, int start, int count, hb_ct **out) {
+    return guard(c, [&] {
+        if (start < 0 || count < 1 || start + count > src->batch) fail(HB_E_ARG, "batch_slice: bad range");
+        hb_ct *r = new_ct(c, src->level, src->np, count, src->spow);
+        const size_t per = (size_t)src->np * (src->level + 1) * c->N;
+        CK(cudaMemcpyAsync(r->d, src->d + per * start, per * count * 8, cudaMemcpyDeviceToDevice, c->st));
+        *out = r;
+    });
+}
 int hb_add(hb_ctx *c, const hb_ct *a, const hb_ct *b, hb_ct **out) { return guard(c, [&] { *out = do_addsub(c, a, b, 0); }); }
 int hb_sub(hb_ctx *c, const hb_ct *a, const hb_ct *b, hb_ct **out) { return guard(c, [&] { *out = do_addsub(c, a, b, 1); }); }
 int hb_negate(hb_ctx *c, const hb_ct *a, hb_ct **out) {

@@ -138,6 +138,16 @@ class Hemmer:
         ct = self._call("matmul_cc", a.ct.ptr, *self._shp(a), b.ct.ptr, *self._shp(b), C.c_int(target_level))
         return CtxtTensor(ct, a.rows, b.cols, a.width)
 
+    def cc_matmul_prepare(self, a, b, target_level=4):
+        """First half of singleCCMatMul: sigma(A), tau(B), both at target + 2."""
+        sa, tb = self._call("matmul_cc_prepare", a.ct.ptr, *self._shp(a), b.ct.ptr, *self._shp(b), C.c_int(target_level), n_out=2)
+        return sa, tb
+
+    def cc_matmul_core(self, sa, tb, rows, inner, cols, width, target_level=4):
+        """Second half: the product loop on operands already transformed (any batch)."""
+        ct = self._call("matmul_cc_core", sa.ptr, tb.ptr, C.c_int(rows), C.c_int(inner), C.c_int(cols), C.c_int(width), C.c_int(target_level))
+        return CtxtTensor(ct, rows, cols, width)
+
     def packed_matmul(self, a, b, target_level=4):
         ct = self._call("packed_matmul", a.ct.ptr, *self._shp(a), b.ct.ptr, *self._shp(b), C.c_int(target_level))
         return CtxtTensor(ct, a.rows, b.cols, a.width)

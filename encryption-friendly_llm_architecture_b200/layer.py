@@ -202,32 +202,34 @@ class LayerWorkload:
                         out["pcmm"][(name, wname, j)] = acc
         if self.world > 1:
             self._reduce_partials(out["pcmm"])
-        for tr, (us, a, b) in res["ccmm"].items():
-            a = CtxtTensor(a.ct, *a.shape)
-            b = CtxtTensor(b.ct, *b.shape)
-            if tr is True:
-                H.transpose_inplace(b)
-            elif tr == "left":
-                H.transpose_inplace(a)
-            out["ccmm"][tr] = (us, H.single_cc_matmul(a, b, t))
+        # ct x ct: one batched transpose for every operand that needs it; the transforms sigma / tau run per group
+        # (a transposed tile sits one level lower), then ONE product loop serves all units of this rank
+        cc = res["ccmm"]
+        if cc:
+            lib = self.lib
+            order = [tr for tr in (False, True, "left") if tr in cc]
+            need = [cc[tr][2] if tr is True else cc[tr][1] for tr in order if tr is not False]
+            transposed = {}
+            if need:
+                joined = CtxtTensor(lib.batch_concat([x.ct for x in need]) if len(need) > 1 else need[0].ct, D, D, 2 * D)
+                H.transpose_inplace(joined)
+                pos = 0
+                for tr in order:
+                    if tr is False:
+                        continue
+                    cnt = len(cc[tr][0])
+                    transposed[tr] = lib.batch_slice(joined.ct, pos, cnt) if len(need) > 1 else joined.ct
+                    pos += cnt
+            sas, tbs = [], []
+            for tr in order:
+                a = CtxtTensor(transposed[tr] if tr == "left" else cc[tr][1].ct, D, D, 2 * D)
+                b = CtxtTensor(transposed[tr] if tr is True else cc[tr][2].ct, D, D, 2 * D)
+                sa, tb = H.cc_matmul_prepare(a, b, t)
+                sas.append(sa); tbs.append(tb)
+            sa = lib.batch_concat(sas) if len(sas) > 1 else sas[0]
+            tb = lib.batch_concat(tbs) if len(tbs) > 1 else tbs[0]
+            out["ccmm"]["all"] = ([u for tr in order for u in cc[tr][0]], H.cc_matmul_core(sa, tb, D, D, D, 2 * D, t))
         return out
-
-    def _reduce_partials(self, partial):
-        """K-split exchange: every rank holds the partial products of its own K-groups; one all-reduce per sublayer
-        (sum of residues, then reduction modulo each prime) gives every rank the complete output tiles -- the pattern of
-        TransformerBlock::ncclAllReduceWrapper + modReduct (TransformerBlock.cpp:11142-11154, HEMMer.cpp:2625-2635)."""
-        import ctypes as C
-        lib = self.lib
-        for name, xname, weights, kt, nt in self.PCMM:
-            keys = [(name, wname, j) for wname in weights for j in range(nt)]
-            stacked = lib.ct_create(self.target + 1, 2, len(keys), 2)   # zero where this rank has no partial
-            lib._chk(lib.dll.hb_ct_zero(lib.ctx, stacked.ptr))
-            for k, key in enumerate(keys):
-                if key in partial:
-                    lib.batch_set(stacked, k, partial[key].ct)
-            lib._chk(lib.dll.hb_allreduce_sum(lib.ctx, stacked.ptr, C.c_void_p(self.comm)))
-            for k, key in enumerate(keys):
-                partial[key] = CtxtTensor(lib.batch_get(stacked, k), D, D, 2 * D)
 
     # ---- device -> host ----
     def _expected_ccmm(self, u):

@@ -103,6 +103,9 @@ void *hb_ct_device_ptr(const hb_ct *ct);
 /* copies all of src's entries to positions index*src_batch .. of dst */
 int hb_batch_set(hb_ctx *ctx, hb_ct *dst, int index, const hb_ct *src);
 int hb_batch_get(hb_ctx *ctx, const hb_ct *src, int index, hb_ct **out);
+/* join batches end to end / copy out a run of entries (device-to-device copies) */
+int hb_batch_concat(hb_ctx *ctx, const hb_ct *const *parts, int n, hb_ct **out);
+int hb_batch_slice(hb_ctx *ctx, const hb_ct *src, int start, int count, hb_ct **out);
 
 /* HomEvaluator primitives; `out` receives a new handle unless stated otherwise. */
 int hb_add(hb_ctx *ctx, const hb_ct *a, const hb_ct *b, hb_ct **out);           /* HomEvaluator.hpp:143-146 */

@@ -376,8 +376,9 @@ struct Hemmer {
         return ev.rescale(ev.add(ev.mul_pt_norescale(x, pa), ev.mul_pt_norescale(y, pb)));
     }
 
-    // multMatMat<Ciphertext> -- MatrixUtils.cpp:1307-1446
-    CtT mult_mat_mat_cc(const CtT &op1, const CtT &op2, int target_level) {
+    // multMatMat<Ciphertext> -- MatrixUtils.cpp:1307-1446, in two halves (the split only exposes the point where
+    // both operands have reached target + 2; the operations and their order are those of the reference function).
+    void ccmm_prepare(const CtT &op1, const CtT &op2, int target_level, Ct &sa, Ct &tb) {
         const i64 num_rows = op1.sh.rows, num_cols = op2.sh.cols;
         if (op1.sh.cols != op2.sh.rows) throw std::invalid_argument("[getCommonInsideLength] different inside length.");
         if (op1.sh.width != op2.sh.width) throw std::invalid_argument("[getCommonBlockWidth] different block width");
@@ -386,35 +387,40 @@ struct Hemmer {
         if (std::min(op1.ct.level, op2.ct.level) < target_level + 3) throw std::invalid_argument("[multMatMat] level too low");
         CtT a = op1, b = op2;
         a.sh = Shape(num_rows, num_k, width); b.sh = Shape(num_k, num_cols, width);
-        auto &col_mask = get_col_mask(a.sh, target_level + 2);
-        auto &row_mask = get_row_mask(b.sh, target_level + 2);
         a = diagonal_to_column(a);
         b = diagonal_to_row(b);
-        a.ct = ev.level_down(a.ct, target_level + 2);
-        b.ct = ev.level_down(b.ct, target_level + 2);
+        sa = ev.level_down(a.ct, target_level + 2);
+        tb = ev.level_down(b.ct, target_level + 2);
+    }
+    CtT ccmm_core(Ct a, Ct b, i64 num_rows, i64 inner, i64 num_cols, i64 width, int target_level) {
+        const i64 num_k = pow2_ceil(inner);
+        if (a.level != target_level + 2 || b.level != target_level + 2) throw std::invalid_argument("[multMatMat] operands of the product loop must sit at target + 2");
+        const Shape sha(num_rows, num_k, width), shb(num_k, num_cols, width);
+        auto &col_mask = get_col_mask(sha, target_level + 2);
+        auto &row_mask = get_row_mask(shb, target_level + 2);
         const i64 num_rows_tmp = (num_k > num_rows) ? num_k : pow2_ceil(num_rows);
         const i64 num_cols_tmp = (num_k > num_cols) ? num_k : pow2_ceil(num_cols);
-        Ct res = ev.mul(a.ct, b.ct);
+        Ct res = ev.mul(a, b);
         Ct itxt_res;
         if (mode == 1) {
             for (i64 i = 1; i < num_k; i++) {
-                Ct tmp1 = assemble(rotL(a.ct, i), col_mask[(size_t)(2 * i + 1)], rotL(a.ct, i - num_cols_tmp), col_mask[(size_t)(2 * i)]);
-                Ct tmp2 = assemble(rotL(b.ct, i * width), row_mask[(size_t)(2 * i + 1)], rotL(b.ct, (i - num_rows_tmp) * width), row_mask[(size_t)(2 * i)]);
+                Ct tmp1 = assemble(rotL(a, i), col_mask[(size_t)(2 * i + 1)], rotL(a, i - num_cols_tmp), col_mask[(size_t)(2 * i)]);
+                Ct tmp2 = assemble(rotL(b, i * width), row_mask[(size_t)(2 * i + 1)], rotL(b, (i - num_rows_tmp) * width), row_mask[(size_t)(2 * i)]);
                 Ct t = ev.tensor(tmp1, tmp2);
                 itxt_res = (i == 1) ? t : ev.add(itxt_res, t);
             }
         } else {
-            a.ct = rotL(a.ct, 1);
-            b.ct = rotL(b.ct, width);
-            Ct a_rot = rotR(a.ct, num_cols_tmp);
-            Ct b_rot = rotR(b.ct, num_rows_tmp * width);
+            a = rotL(a, 1);
+            b = rotL(b, width);
+            Ct a_rot = rotR(a, num_cols_tmp);
+            Ct b_rot = rotR(b, num_rows_tmp * width);
             for (i64 i = 1; i < num_k; i++) {
                 if (i > 1) {
-                    a.ct = rotL(a.ct, 1); a_rot = rotL(a_rot, 1);
-                    b.ct = rotL(b.ct, width); b_rot = rotL(b_rot, width);
+                    a = rotL(a, 1); a_rot = rotL(a_rot, 1);
+                    b = rotL(b, width); b_rot = rotL(b_rot, width);
                 }
-                Ct tmp1 = assemble(a.ct, col_mask[(size_t)(2 * i + 1)], a_rot, col_mask[(size_t)(2 * i)]);
-                Ct tmp2 = assemble(b.ct, row_mask[(size_t)(2 * i + 1)], b_rot, row_mask[(size_t)(2 * i)]);
+                Ct tmp1 = assemble(a, col_mask[(size_t)(2 * i + 1)], a_rot, col_mask[(size_t)(2 * i)]);
+                Ct tmp2 = assemble(b, row_mask[(size_t)(2 * i + 1)], b_rot, row_mask[(size_t)(2 * i)]);
                 Ct t = ev.tensor(tmp1, tmp2);
                 itxt_res = (i == 1) ? t : ev.add(itxt_res, t);
             }
@@ -422,6 +428,11 @@ struct Hemmer {
         Ct tail = ev.rescale(ev.relin(itxt_res));
         res = ev.add(res, tail);
         return CtT{res, Shape(num_rows, num_cols, width)};
+    }
+    CtT mult_mat_mat_cc(const CtT &op1, const CtT &op2, int target_level) {
+        Ct a, b;
+        ccmm_prepare(op1, op2, target_level, a, b);
+        return ccmm_core(std::move(a), std::move(b), op1.sh.rows, op1.sh.cols, op2.sh.cols, op1.sh.width, target_level);
     }
 
     // multPackedMatMat -- MatrixUtils.cpp:1100-1216

@@ -101,6 +101,26 @@ int orc_batch_get(orc_ctx *c, const orc_ct *src, int idx, orc_ct **out) {
         *out = r;
     })
 }
+int orc_batch_concat(orc_ctx *c, const orc_ct *const *parts, int n, orc_ct **out) {
+    ORC_TRY(c, {
+        int total = 0;
+        for (int k = 0; k < n; ++k) total += parts[k]->batch;
+        const bool dry = parts[0]->d.empty();
+        Ct *r = new Ct(c->cx.N, parts[0]->level, parts[0]->np, total, parts[0]->spow, dry);
+        size_t off = 0;
+        if (!dry) for (int k = 0; k < n; ++k) { std::memcpy(r->d.data() + off, parts[k]->d.data(), parts[k]->d.size() * 8); off += parts[k]->d.size(); }
+        *out = r;
+    })
+}
+int orc_batch_slice(orc_ctx *c, const orc_ct *src, int start, int count, orc_ct **out) {
+    ORC_TRY(c, {
+        Evaluator::require(start >= 0 && count >= 1 && start + count <= src->batch, "batch_slice");
+        const bool dry = src->d.empty();
+        Ct *r = new Ct(c->cx.N, src->level, src->np, count, src->spow, dry);
+        if (!dry) std::memcpy(r->d.data(), src->limb(start, 0, 0), r->d.size() * 8);
+        *out = r;
+    })
+}
 int orc_add(orc_ctx *c, const orc_ct *a, const orc_ct *b, orc_ct **o) { ORC_TRY(c, *o = new Ct(c->ev.add(*a, *b))) }
 int orc_sub(orc_ctx *c, const orc_ct *a, const orc_ct *b, orc_ct **o) { ORC_TRY(c, *o = new Ct(c->ev.add(*a, *b, true))) }
 int orc_negate(orc_ctx *c, const orc_ct *a, orc_ct **o) { ORC_TRY(c, *o = new Ct(c->ev.negate(*a))) }

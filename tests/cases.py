@@ -173,6 +173,10 @@ def sc_batched(lib, H, target=2):
         assert np.array_equal(lib.ct_export(ck.ct)[0], exports[0][k]), "batched ct x ct differs from the single call"
         z = lib.decrypt(cb.ct, k)[: 2 * d * d].real.reshape(d, 2 * d)
         err = max(err, np.abs(z[:, :d] - mats[2 * k] @ mats[6 + 2 * k].T).max(), np.abs(z[:, d:] - mats[2 * k + 1] @ mats[7 + 2 * k].T).max())
+    # the two-half form of the product (transforms per group, one product loop) gives the same ciphertexts
+    sa, tb = H.cc_matmul_prepare(ab, bb, target)
+    split = H.cc_matmul_core(sa, tb, d, d, d, 2 * d, target)
+    assert np.array_equal(lib.ct_export(split.ct), exports[0]), "prepare + core differs from singleCCMatMul"
     # two K-groups through matMulPre as one batch, summed per output tile in one pass
     rngw = np.random.default_rng(110)
     W = [[rngw.normal(0, 0.02, (d, d)) for _ in range(4)] for _ in range(2)]
