@@ -305,8 +305,10 @@ struct HostCtx {
         e.resize(N);
         HostChaCha::Reader rd(&cha, domain, id);
         for (int c = 0; c < N; ++c) {
+            // magnitude = number of table entries <= u; the table is increasing, so stop at the first larger one
             u64 r = rd.next(), u = r >> 1; i64 mag = 0;
-            for (u64 t : gauss_cdt) mag += t <= u ? 1 : 0;
+            const size_t J = gauss_cdt.size();
+            while ((size_t)mag < J && gauss_cdt[(size_t)mag] <= u) ++mag;
             e[c] = (r & 1) ? -mag : mag;
         }
     }
