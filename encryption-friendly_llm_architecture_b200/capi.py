@@ -214,5 +214,14 @@ class Lib:
     def rotate(self, a, s): return self._op("rotate", a.ptr, C.c_int64(s))
     def conjugate(self, a): return self._op("conjugate", a.ptr)
 
+    def _pt_op(self, name, *args):
+        out = C.c_void_p()
+        self._chk(self._fn(name)(self.ctx, *args, C.byref(out)))
+        return Handle(self, out, "pt")
+
+    def pt_mul(self, a, b): return self._pt_op("pt_mul", a.ptr, b.ptr)
+    def pt_add(self, a, b): return self._pt_op("pt_add", a.ptr, b.ptr)
+    def pt_rotate(self, a, s): return self._pt_op("pt_rotate", a.ptr, C.c_int64(s))
+
     def ntt(self, a, inverse=False):
         self._chk(self._fn("ntt")(self.ctx, a.ptr, C.c_int(1 if inverse else 0)))

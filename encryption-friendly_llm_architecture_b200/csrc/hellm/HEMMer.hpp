@@ -88,6 +88,7 @@ class HEMMer {
     void addInplace(CtxtTensor &a, const CtxtTensor &b) const;
     // matmul family -- HEMMer.cpp:833-880, 1102-1124
     CtxtTensor singleCCMatMul(const CtxtTensor &a, const CtxtTensor &b, int target_level = 4);
+    CtxtTensor singleMatMul(const CtxtTensor &a, const PtxtTensor &b, int target_level = 4);
     // singleCCMatMul in two halves (transforms, then the product loop), for batching operands of different levels
     void ccMatMulPrepare(const CtxtTensor &a, const CtxtTensor &b, int target_level, Ciphertext &sigma_a, Ciphertext &tau_b);
     CtxtTensor ccMatMulCore(Ciphertext sigma_a, Ciphertext tau_b, i64 rows, i64 inner, i64 cols, i64 width, int target_level);

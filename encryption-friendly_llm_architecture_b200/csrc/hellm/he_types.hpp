@@ -71,6 +71,8 @@ class Plaintext {
   public:
     Plaintext() = default;
     explicit Plaintext(hb_pt *p) : p_(p, [](hb_pt *x) { hb_pt_free(x); }) {}
+    // a handle owned by someone else (kept alive by the caller for the duration of the call)
+    static Plaintext borrowed(const hb_pt *p) { Plaintext r; r.p_ = std::shared_ptr<hb_pt>(const_cast<hb_pt *>(p), [](hb_pt *) {}); return r; }
     hb_pt *raw() const { return p_.get(); }
     bool empty() const { return !p_; }
     int getLevel() const { int l = -1; hb_pt_meta(p_.get(), &l, nullptr); return l; }
@@ -131,6 +133,8 @@ class Evaluator {
         check(c_, hb_gen_rot_keys(c_, &steps, 1));
         hb_ct *o = nullptr; check(c_, hb_rotate_hoisted(c_, a.raw(), h.raw(), steps, &o)); return Ciphertext(c_, o);
     }
+    Plaintext mult(const Plaintext &a, const Plaintext &b) const { hb_pt *o = nullptr; check(c_, hb_pt_mul(c_, a.raw(), b.raw(), &o)); return Plaintext(o); }
+    Plaintext add(const Plaintext &a, const Plaintext &b) const { hb_pt *o = nullptr; check(c_, hb_pt_add(c_, a.raw(), b.raw(), &o)); return Plaintext(o); }
     Plaintext leftRotate(const Plaintext &p, i64 steps) const { hb_pt *o = nullptr; check(c_, hb_pt_rotate(c_, p.raw(), steps, &o)); return Plaintext(o); }
     // rescale(a (.) pa + b (.) pb): the "assemble" step of the matmul loops in one pass
     Ciphertext assemble(const Ciphertext &a, const Plaintext &pa, const Ciphertext &b, const Plaintext &pb) const {

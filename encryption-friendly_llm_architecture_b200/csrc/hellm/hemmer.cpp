@@ -100,6 +100,7 @@ void HEMMer::addInplace(CtxtTensor &a, const CtxtTensor &b) const { a.get() = ev
 // ---- schedules ----
 #define HB_ENV sched::Env env{eval_, slots_, masks_, schedule_}
 CtxtTensor HEMMer::singleCCMatMul(const CtxtTensor &a, const CtxtTensor &b, int t) { HB_ENV; return sched::multMatMatCC(env, a, b, t); }
+CtxtTensor HEMMer::singleMatMul(const CtxtTensor &a, const PtxtTensor &b, int t) { HB_ENV; return sched::multMatMatCP(env, a, b, t); }
 void HEMMer::ccMatMulPrepare(const CtxtTensor &a, const CtxtTensor &b, int t, Ciphertext &sa, Ciphertext &tb) { HB_ENV; sched::ccmmPrepare(env, a, b, t, sa, tb); }
 CtxtTensor HEMMer::ccMatMulCore(Ciphertext sa, Ciphertext tb, i64 rows, i64 inner, i64 cols, i64 width, int t) {
     HB_ENV; return sched::ccmmCore(env, std::move(sa), std::move(tb), rows, inner, cols, width, t);

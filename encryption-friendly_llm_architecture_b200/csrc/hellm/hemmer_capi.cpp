@@ -49,6 +49,14 @@ int hb_hemmer_matmul_cc(hb_hemmer *h, const hb_ct *a, int ra, int ca, int wa, co
         *out = h->h.singleCCMatMul(ta, tb, target).get().release();
     });
 }
+int hb_hemmer_matmul_cp(hb_hemmer *h, const hb_ct *a, int ra, int ca, int wa, const hb_pt *b, int rb, int cb, int wb, int target, hb_ct **out) {
+    return guard([&] {
+        Borrow ba(h->ctx, a);
+        CtxtTensor ta = view(ba, ra, ca, wa);
+        PtxtTensor tb(TileTensorShape(rb, cb, wb), Plaintext::borrowed(b));
+        *out = h->h.singleMatMul(ta, tb, target).get().release();
+    });
+}
 int hb_hemmer_matmul_cc_prepare(hb_hemmer *h, const hb_ct *a, int ra, int ca, int wa, const hb_ct *b, int rb, int cb, int wb, int target, hb_ct **out_a, hb_ct **out_b) {
     return guard([&] {
         Borrow ba(h->ctx, a), bb(h->ctx, b);

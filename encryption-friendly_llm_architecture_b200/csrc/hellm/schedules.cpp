@@ -271,6 +271,47 @@ CtxtTensor multMatMatCC(Env &e, const CtxtTensor &op1, const CtxtTensor &op2, in
     return ccmmCore(e, std::move(a), std::move(b), op1.getHeight(), op1.getWidth(), op2.getWidth(), op1.getBlockWidth(), target_level);
 }
 
+// multMatMat<Plaintext> (HEMMer::singleMatMul) -- MatrixUtils.cpp:1448-1570: ciphertext x plaintext without reuse.  The right
+// operand is decoded, tau-transformed in the clear (diagonalToRow<Plaintext>, :1072-1098), encoded at target + 2 and then
+// shifted by slot rotations of the plaintext; its row wrap uses plaintext x mask products as the reference does.
+CtxtTensor multMatMatCP(Env &e, const CtxtTensor &op1, const PtxtTensor &op2, int target_level) {
+    if (op1.getWidth() != op2.getHeight()) throw std::invalid_argument("[getCommonInsideLength] different inside length.");
+    if (op1.getBlockWidth() != op2.getBlockWidth()) throw std::invalid_argument("[getCommonBlockWidth] different block width");
+    const i64 num_rows = op1.getHeight(), num_cols = op2.getWidth(), width = op1.getBlockWidth();
+    const i64 num_k = ceil_pow2(op1.getWidth());
+    if (op1.getLevel() < target_level + 3) throw std::invalid_argument("[multMatMat] level too low");
+    const TileTensorShape sa(num_rows, num_k, width), sb(num_k, num_cols, width);
+    const int lvl = target_level + 2;
+    Ciphertext a = e.ev.levelDown(diagonalToColumn(e, CtxtTensor(sa, op1.get())).get(), lvl);
+    const Message msg = e.ev.decode(op2.get(), (size_t)e.slots);
+    Message tau((size_t)e.slots);
+    for (i64 i = 0; i < sb.getNumRows(); ++i)
+        for (i64 j = 0; j < sb.getNumCols(); ++j) {
+            const size_t dst = (size_t)(((i - j + sb.getNumRows()) % sb.getNumRows()) * width + j), src = (size_t)(i * width + j);
+            tau.re[dst] = msg.re[src]; tau.im[dst] = msg.im[src];
+            if (width != sb.getNumCols()) { tau.re[dst + sb.getNumCols()] = msg.re[src + sb.getNumCols()]; tau.im[dst + sb.getNumCols()] = msg.im[src + sb.getNumCols()]; }
+        }
+    Plaintext b = e.ev.encode(tau, lvl);
+    const i64 rows_tmp = num_k > num_rows ? num_k : ceil_pow2(num_rows), cols_tmp = num_k > num_cols ? num_k : ceil_pow2(num_cols);
+    Ciphertext res = e.ev.mult(a, b);
+    a = e.ev.leftRotate(a, 1);
+    b = e.ev.leftRotate(b, width);
+    Ciphertext a_wrap = e.ev.rightRotate(a, cols_tmp);
+    Plaintext b_wrap = e.ev.leftRotate(b, -rows_tmp * width);
+    Ciphertext acc;
+    for (i64 i = 1; i < num_k; ++i) {
+        if (i > 1) {
+            a = e.ev.leftRotate(a, 1); a_wrap = e.ev.leftRotate(a_wrap, 1);
+            b = e.ev.leftRotate(b, width); b_wrap = e.ev.leftRotate(b_wrap, width);
+        }
+        Ciphertext ak = e.ev.assemble(a, col_wrap(e, sa, 2 * i + 1, lvl), a_wrap, col_wrap(e, sa, 2 * i, lvl));
+        Plaintext bk = e.ev.add(e.ev.mult(b, row_wrap(e, sb, 2 * i + 1, lvl)), e.ev.mult(b_wrap, row_wrap(e, sb, 2 * i, lvl)));
+        Ciphertext term = e.ev.mult(ak, bk);
+        acc = acc.empty() ? std::move(term) : e.ev.add(acc, term);
+    }
+    return CtxtTensor(TileTensorShape(num_rows, num_cols, width), e.ev.add(res, acc));
+}
+
 // multPackedMatMat -- MatrixUtils.cpp:1100-1216
 CtxtTensor multPackedMatMat(Env &e, const CtxtTensor &op1, const CtxtTensor &op2, int target_level) {
     require_product_shapes(op1, op2);

@@ -31,6 +31,7 @@ CtxtTensor packedDiagonalToRow(Env &e, const CtxtTensor &op);
 CtxtTensor multMatMatCC(Env &e, const CtxtTensor &a, const CtxtTensor &b, int target_level);
 void ccmmPrepare(Env &e, const CtxtTensor &a, const CtxtTensor &b, int target_level, Ciphertext &sigma_a, Ciphertext &tau_b);
 CtxtTensor ccmmCore(Env &e, Ciphertext sigma_a, Ciphertext tau_b, i64 rows, i64 inner, i64 cols, i64 width, int target_level);
+CtxtTensor multMatMatCP(Env &e, const CtxtTensor &a, const PtxtTensor &b, int target_level);
 CtxtTensor multPackedMatMat(Env &e, const CtxtTensor &a, const CtxtTensor &b, int target_level);
 CtxtTensor multPackedMatMatPre(Env &e, const CtxtTensor &a, int target_level);
 Ciphertext multPackedMatMatPreRot(Env &e, const CtxtTensor &a, int target_level);

@@ -873,6 +873,26 @@ int hb_pt_rotate(hb_ctx *c, const hb_pt *p, int64_t steps, hb_pt **out) {
         *out = r;
     });
 }
+// plaintext x plaintext with rescale, and plaintext + plaintext: a plaintext is handled as a one-polynomial ciphertext
+int hb_pt_mul(hb_ctx *c, const hb_pt *a, const hb_pt *b, hb_pt **out) {
+    return guard(c, [&] {
+        hb_ct view{c, a->level, 1, 1, a->spow, a->d};
+        const hb_ct *vp = &view;
+        hb_ct *r = do_prod_rescale(c, &vp, &b, 1, true);
+        hb_pt *p = new hb_pt{c, r->level, 1, r->d};
+        delete r; // the buffer now belongs to the plaintext handle
+        *out = p;
+    });
+}
+int hb_pt_add(hb_ctx *c, const hb_pt *a, const hb_pt *b, hb_pt **out) {
+    return guard(c, [&] {
+        if (a->level != b->level) fail(HB_E_LEVEL, "pt_add: level mismatch");
+        if (a->spow != b->spow) fail(HB_E_SHAPE, "pt_add: scale mismatch");
+        hb_pt *r = new_pt(c, a->level, a->spow);
+        LAUNCH(c), k_addsub<<<c->egrid(a->level + 1), 256, 0, c->st>>>(r->d, a->d, b->d, c->qmap(a->level), c->pc, c->N, 0);
+        *out = r;
+    });
+}
 int hb_mod_reduce(hb_ctx *c, hb_ct *a) {
     return guard(c, [&] { LAUNCH(c), k_mod_reduce<<<c->egrid((int)a->limbs()), 256, 0, c->st>>>(a->d, c->qmap(a->level), c->pc, c->N); });
 }

@@ -138,6 +138,11 @@ class Hemmer:
         ct = self._call("matmul_cc", a.ct.ptr, *self._shp(a), b.ct.ptr, *self._shp(b), C.c_int(target_level))
         return CtxtTensor(ct, a.rows, b.cols, a.width)
 
+    def single_matmul(self, a, b, target_level=4):
+        """HEMMer::singleMatMul: ciphertext x plaintext without reuse."""
+        ct = self._call("matmul_cp", a.ct.ptr, *self._shp(a), b.ct.ptr, *self._shp(b), C.c_int(target_level))
+        return CtxtTensor(ct, a.rows, b.cols, a.width)
+
     def cc_matmul_prepare(self, a, b, target_level=4):
         """First half of singleCCMatMul: sigma(A), tau(B), both at target + 2."""
         sa, tb = self._call("matmul_cc_prepare", a.ct.ptr, *self._shp(a), b.ct.ptr, *self._shp(b), C.c_int(target_level), n_out=2)

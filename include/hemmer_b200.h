@@ -159,6 +159,9 @@ int hb_matmul_acc(hb_ctx *ctx, const hb_ct *pre, const hb_pt *pt, int64_t row_st
 int hb_matmul_acc_multi(hb_ctx *ctx, const hb_ct *pre, int btotal, int b0, const hb_pt *const *pts, int bcount, int64_t row_step, hb_ct **out);
 /* rotation of a plaintext (pure slot permutation, no key) -- leftRotate(ptxt) used at MatrixUtils.cpp:1503 */
 int hb_pt_rotate(hb_ctx *ctx, const hb_pt *p, int64_t left_steps, hb_pt **out);
+/* mult(ptxt, ptxt) with rescale and add(ptxt, ptxt), as multMatMat<Plaintext> uses them -- MatrixUtils.cpp:1556-1558 */
+int hb_pt_mul(hb_ctx *ctx, const hb_pt *a, const hb_pt *b, hb_pt **out);
+int hb_pt_add(hb_ctx *ctx, const hb_pt *a, const hb_pt *b, hb_pt **out);
 /* modReduct after a lazy sum across ranks -- HomEvaluator.hpp:602-605 */
 int hb_mod_reduce(hb_ctx *ctx, hb_ct *a);
 

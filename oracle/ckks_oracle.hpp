@@ -801,7 +801,7 @@ struct Evaluator {
     // HomEvaluator::multWithoutRescale(ct, ptxt) (HomEvaluator.hpp:490-493)
     Ct mul_pt_norescale(const Ct &x, const Pt &p) {
         require(x.level == p.level, "mul_pt: level mismatch");
-        require(x.spow == 1 && p.spow == 1 && x.np == 2, "mul_pt: operand not rescaled");
+        require(x.spow == 1 && p.spow == 1, "mul_pt: operand not rescaled");
         if (count("mul_pt", x.level, x.batch)) return meta(x.level, x.np, x.batch, 2);
         Ct r = x; r.spow = 2; const int n = x.level + 1, N = cx.N;
 #pragma omp parallel for

@@ -571,6 +571,56 @@ struct Hemmer {
         return CtT{ev.relin(sum), Shape(b_in.sh.rows, b_in.sh.cols, width)};
     }
 
+    // Plaintext arithmetic used by multMatMat<Plaintext>: a plaintext is a one-polynomial ciphertext without key material,
+    // so product (with rescale) and sum are the ciphertext operations on one polynomial.
+    static Ct pt_as_ct(const Pt &p) { Ct c(p.N, p.level, 1, 1, p.spow, p.d.empty()); c.d = p.d; return c; }
+    static Pt ct_as_pt(const Ct &c) { Pt p; p.level = c.level; p.spow = c.spow; p.N = c.N; p.d = c.d; return p; }
+    Pt pt_mul(const Pt &a, const Pt &b) { return ct_as_pt(ev.rescale(ev.mul_pt_norescale(pt_as_ct(a), b))); }
+    Pt pt_add(const Pt &a, const Pt &b) { return ct_as_pt(ev.add(pt_as_ct(a), pt_as_ct(b))); }
+
+    // multMatMat<Plaintext> -- MatrixUtils.cpp:1448-1570 (HEMMer::singleMatMul), with the cleartext tau of
+    // diagonalToRow<Plaintext> (:1072-1098).  `msg` is the decoded right operand (the reference decodes the Plaintext).
+    CtT mult_mat_mat_cp(const CtT &op1, const Message &msg, const Shape &shb, int target_level) {
+        const i64 num_rows = op1.sh.rows, num_cols = shb.cols, width = op1.sh.width;
+        if (op1.sh.cols != shb.rows) throw std::invalid_argument("[getCommonInsideLength] different inside length.");
+        if (width != shb.width) throw std::invalid_argument("[getCommonBlockWidth] different block width");
+        const i64 num_k = pow2_ceil(op1.sh.cols);
+        if (op1.ct.level < target_level + 3) throw std::invalid_argument("[multMatMat] level too low");
+        CtT a = op1; a.sh = Shape(num_rows, num_k, width);
+        const Shape sb(num_k, num_cols, width);
+        a = diagonal_to_column(a);
+        Message m2((size_t)slots, cplx(0, 0));
+        for (i64 i = 0; i < sb.rows; i++)
+            for (i64 j = 0; j < sb.cols; j++) {
+                m2[(size_t)(((i - j + sb.rows) % sb.rows) * width + j)] = msg[(size_t)(i * width + j)];
+                if (width != sb.cols) m2[(size_t)(((i - j + sb.rows) % sb.rows) * width + sb.cols + j)] = msg[(size_t)(i * width + j + sb.cols)];
+            }
+        a.ct = ev.level_down(a.ct, target_level + 2);
+        Pt b = ev.encode(m2.data(), m2.size(), target_level + 2);
+        const i64 num_rows_tmp = (num_k > num_rows) ? num_k : pow2_ceil(num_rows);
+        const i64 num_cols_tmp = (num_k > num_cols) ? num_k : pow2_ceil(num_cols);
+        Ct res = ev.mul_pt(a.ct, b);
+        a.ct = rotL(a.ct, 1);
+        b = pt_rotate(b, width);
+        Ct a_rot = rotR(a.ct, num_cols_tmp);
+        Pt b_rot = pt_rotate(b, -num_rows_tmp * width);
+        auto &col_mask = get_col_mask(a.sh, target_level + 2);
+        auto &row_mask = get_row_mask(sb, target_level + 2);
+        Ct itxt_res;
+        for (i64 i = 1; i < num_k; i++) {
+            if (i > 1) {
+                a.ct = rotL(a.ct, 1); a_rot = rotL(a_rot, 1);
+                b = pt_rotate(b, width); b_rot = pt_rotate(b_rot, width);
+            }
+            Ct tmp1 = assemble(a.ct, col_mask[(size_t)(2 * i + 1)], a_rot, col_mask[(size_t)(2 * i)]);
+            Pt tmp3 = pt_add(pt_mul(b, row_mask[(size_t)(2 * i + 1)]), pt_mul(b_rot, row_mask[(size_t)(2 * i)]));
+            Ct t = ev.mul_pt(tmp1, tmp3);
+            itxt_res = (i == 1) ? t : ev.add(itxt_res, t);
+        }
+        res = ev.add(res, itxt_res);
+        return CtT{res, Shape(num_rows, num_cols, width)};
+    }
+
     // leftRotate on a plaintext: the slot permutation alone (no key), used by HomEvaluator::matmul
     Pt pt_rotate(const Pt &p, i64 left_steps) {
         u64 g = cx.galois_for_rotation(left_steps);

@@ -137,6 +137,17 @@ int orc_rotate(orc_ctx *c, const orc_ct *a, int64_t s, orc_ct **o) { ORC_TRY(c, 
 int orc_conjugate(orc_ctx *c, const orc_ct *a, orc_ct **o) { ORC_TRY(c, *o = new Ct(c->ev.conjugate(*a))) }
 int orc_ntt(orc_ctx *c, orc_ct *a, int inverse) { ORC_TRY(c, c->ev.ntt_raw(*a, inverse != 0)) }
 
+// plaintext arithmetic (one-polynomial objects)
+int orc_pt_mul(orc_ctx *c, const orc_pt *a, const orc_pt *b, orc_pt **o) {
+    ORC_TRY(c, { Hemmer h(c->cx, c->ev); *o = new Pt(h.pt_mul(*a, *b)); })
+}
+int orc_pt_add(orc_ctx *c, const orc_pt *a, const orc_pt *b, orc_pt **o) {
+    ORC_TRY(c, { Hemmer h(c->cx, c->ev); *o = new Pt(h.pt_add(*a, *b)); })
+}
+int orc_pt_rotate(orc_ctx *c, const orc_pt *a, int64_t s, orc_pt **o) {
+    ORC_TRY(c, { Hemmer h(c->cx, c->ev); *o = new Pt(h.pt_rotate(*a, s)); })
+}
+
 // dry mode and operation counters (see Evaluator::dry)
 int orc_set_dry(orc_ctx *c, int on) { c->ev.dry = on != 0; return 0; }
 int orc_stats_clear(orc_ctx *c) { c->ev.stats.clear(); return 0; }

@@ -191,7 +191,28 @@ def sc_batched(lib, H, target=2):
     return exports, err
 
 
+def sc_single_matmul(lib, H, target=2):
+    """HEMMer::singleMatMul (ct x pt without reuse) on two side-by-side tiles, plus the plaintext primitives it uses."""
+    d = tile_dim(lib)
+    A, A2 = _mats(111, d, 2)
+    rngw = np.random.default_rng(112)
+    W, W2 = rngw.normal(0, 0.02, (d, d)), rngw.normal(0, 0.02, (d, d))
+    a = H.encrypt2(A, A2, nonce=40)
+    w = H.encode2(W, W2, level=target + 3)
+    c = H.single_matmul(a, w, target)
+    assert lib.ct_meta(c.ct)[0] == target
+    D = H.decrypt2(c)
+    err = max(np.abs(D[0] - A @ W).max(), np.abs(D[1] - A2 @ W2).max())
+    z = np.random.default_rng(113).uniform(-1, 1, lib.slots)
+    p1, p2 = lib.encode(z, 4), lib.encode(z[::-1].copy(), 4)
+    prod, summ, rot = lib.pt_mul(p1, p2), lib.pt_add(p1, p2), lib.pt_rotate(p1, 5)
+    err = max(err, np.abs(lib.decode(prod).real - z * z[::-1]).max(), np.abs(lib.decode(summ).real - (z + z[::-1])).max(),
+              np.abs(lib.decode(rot).real - np.roll(z, -5)).max())
+    return [lib.ct_export(c.ct), lib.pt_export(prod)[None, None], lib.pt_export(summ)[None, None], lib.pt_export(rot)[None, None]], err
+
+
 SCENARIOS = {
+    "single_matmul": sc_single_matmul,
     "batched": sc_batched,
     "transforms": sc_transforms,
     "ccmm_single_tile": sc_ccmm_single_tile,
