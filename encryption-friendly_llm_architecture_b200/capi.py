@@ -179,6 +179,13 @@ class Lib:
         self._chk(self._fn("batch_get")(self.ctx, src.ptr, C.c_int(idx), C.byref(out)))
         return Handle(self, out, "ct")
 
+    def ct_zero(self, ct):
+        self._chk(self._fn("ct_zero")(self.ctx, ct.ptr))
+
+    def allreduce_sum(self, ct, comm):
+        """Sum over the ranks of `comm` (an NCCL communicator as an integer address), then reduce modulo each prime."""
+        self._chk(self._fn("allreduce_sum")(self.ctx, ct.ptr, C.c_void_p(comm)))
+
     def batch_concat(self, parts):
         arr = (C.c_void_p * len(parts))(*[p.ptr.value for p in parts])
         out = C.c_void_p()

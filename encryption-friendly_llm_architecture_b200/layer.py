@@ -231,6 +231,22 @@ class LayerWorkload:
             out["ccmm"]["all"] = ([u for tr in order for u in cc[tr][0]], H.cc_matmul_core(sa, tb, D, D, D, 2 * D, t))
         return out
 
+    def _reduce_partials(self, partial):
+        """K-split exchange: every rank holds the partial products of its own K-groups; one all-reduce per sublayer
+        (sum of residues, then reduction modulo each prime) gives every rank the complete output tiles -- the pattern of
+        TransformerBlock::ncclAllReduceWrapper + modReduct (TransformerBlock.cpp:11142-11154, HEMMer.cpp:2625-2635)."""
+        lib = self.lib
+        for name, xname, weights, kt, nt in self.PCMM:
+            keys = [(name, wname, j) for wname in weights for j in range(nt)]
+            stacked = lib.ct_create(self.target + 1, 2, len(keys), 2)   # zero where this rank has no partial
+            lib.ct_zero(stacked)
+            for k, key in enumerate(keys):
+                if key in partial:
+                    lib.batch_set(stacked, k, partial[key].ct)
+            lib.allreduce_sum(stacked, self.comm)
+            for k, key in enumerate(keys):
+                partial[key] = CtxtTensor(lib.batch_get(stacked, k), D, D, 2 * D)
+
     # ---- device -> host ----
     def _expected_ccmm(self, u):
         _, name, lhs, rhs, tr = u

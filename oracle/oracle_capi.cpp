@@ -101,6 +101,9 @@ int orc_batch_get(orc_ctx *c, const orc_ct *src, int idx, orc_ct **out) {
         *out = r;
     })
 }
+int orc_ct_zero(orc_ctx *, orc_ct *x) { std::fill(x->d.begin(), x->d.end(), 0); return 0; }
+// single-process stand-in for the collective: one rank, so the sum is the operand itself
+int orc_allreduce_sum(orc_ctx *, orc_ct *, void *) { return 0; }
 int orc_batch_concat(orc_ctx *c, const orc_ct *const *parts, int n, orc_ct **out) {
     ORC_TRY(c, {
         int total = 0;

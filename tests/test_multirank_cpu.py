@@ -63,3 +63,30 @@ def test_two_ranks_cover_all_units_and_ksplit_sum_is_exact():
     assert len(flat) == total == 54 and len(set(flat)) == total
     assert abs(len(gathered[0]) - len(gathered[1])) <= 1
     assert ok
+
+
+def test_rank_local_step_runs_the_ksplit_exchange(pkg, oracle_so):
+    """Each rank's pass over its share of the layer, including the K-split exchange code path, on the oracle in dry mode
+    (operation bookkeeping only): the operation counts of the two ranks add up to those of the single-rank pass."""
+    import ctypes as C
+    layer = importlib.import_module(PKG + ".layer")
+
+    def counts(rank, world):
+        o = pkg.capi.Lib(oracle_so, "orc_", pkg.make_params())
+        o.dll.orc_set_dry(o.ctx, 1)
+        wl = layer.LayerWorkload(pkg.Hemmer(o), layer.synthetic(3), rank=rank, world=world)
+        wl.comm = 0
+        wl.step()
+        need = o.dll.orc_stats_dump(o.ctx, None, 0)
+        buf = C.create_string_buffer(need)
+        o.dll.orc_stats_dump(o.ctx, buf, need)
+        out = {}
+        for line in buf.value.decode().splitlines():
+            op, lvl, n = line.split()
+            if op in ("rotate", "tensor", "relin", "mul_pt"):
+                out[(op, int(lvl))] = int(n)
+        return out
+
+    whole, parts = counts(0, 1), [counts(r, 2) for r in range(2)]
+    for key, n in whole.items():
+        assert sum(p.get(key, 0) for p in parts) == n, key
