@@ -111,6 +111,19 @@ class HEMMer {
     CtxtTensor complexPacking(const CtxtTensor &a, const CtxtTensor &b) const;
     CtxtTensor complexPackingRev(const CtxtTensor &a, const CtxtTensor &b) const;
     CtxtTensor repack_notBTS(const CtxtTensor &a, const CtxtTensor &b);
+    // LoRA low-rank products and their repacking -- HEMMer.cpp:2108-2332.  The thin factor has lowDim() columns or
+    // rows (ModelArgs::LOW_DIM, ModelArgs.hpp:67) and sits in block `in_*_block` of its tile.
+    CtxtTensor matMulHighLow(const CtxtTensor &a, const CtxtTensor &b, u64 in_col_block, int target_level = 4);
+    CtxtTensor matMulLowHigh(const CtxtTensor &a, const CtxtTensor &b, u64 in_row_block, int target_level = 4);
+    CtxtTensor matMulLowLow(const CtxtTensor &a, const CtxtTensor &b, u64 in_col_block, u64 in_row_block, int target_level = 4);
+    CtxtTensor repackToOneCol(const CtxtTensor &t, u64 out_col_block);
+    CtxtTensor repackToMultiCol(const CtxtTensor &t, u64 out_col_block);
+    CtxtTensor repackToOneRow(const CtxtTensor &t, u64 out_row_block);
+    CtxtTensor repackToMultiRow(const CtxtTensor &t, u64 out_row_block);
+    CtxtTensor getLowColBlock(const CtxtTensor &t, u64 col_block);
+    CtxtTensor getLowRowBlock(const CtxtTensor &t, u64 row_block);
+    void setLowDim(i64 low_dim) { low_dim_ = low_dim; }
+    i64 lowDim() const { return low_dim_; }
     // the two linear transforms on their own (MatrixTransformer::diagonalToColumn / diagonalToRow)
     CtxtTensor diagonalToColumn(const CtxtTensor &t);
     CtxtTensor diagonalToRow(const CtxtTensor &t);
@@ -127,6 +140,7 @@ class HEMMer {
     i64 slots_ = 0, tile_ = 0;
     int max_level_ = 0;
     int schedule_ = 0;
+    i64 low_dim_ = 2;
     MaskCache masks_;
 };
 

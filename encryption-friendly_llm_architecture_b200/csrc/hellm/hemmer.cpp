@@ -184,4 +184,74 @@ CtxtTensor HEMMer::repack_notBTS(const CtxtTensor &t1, const CtxtTensor &t2) {
     return CtxtTensor(t1.getShape(), std::move(out));
 }
 
+// ---- LoRA low-rank products and repacking -- HEMMer.cpp:2108-2332 ----
+CtxtTensor HEMMer::matMulHighLow(const CtxtTensor &a, const CtxtTensor &b, u64 in_col_block, int t) { HB_ENV; return sched::multMatMatHighLow(env, a, b, (i64)in_col_block, t, low_dim_); }
+CtxtTensor HEMMer::matMulLowHigh(const CtxtTensor &a, const CtxtTensor &b, u64 in_row_block, int t) { HB_ENV; return sched::multMatMatLowHigh(env, a, b, (i64)in_row_block, t, low_dim_); }
+CtxtTensor HEMMer::matMulLowLow(const CtxtTensor &a, const CtxtTensor &b, u64 in_col_block, u64 in_row_block, int t) {
+    HB_ENV; return sched::multMatMatLowLow(env, a, b, (i64)in_col_block, (i64)in_row_block, t, low_dim_);
+}
+namespace {
+enum LowMask { kOneCol = 0, kOneRow, kMultiRow, kColBlock, kRowBlock };
+// 0/1 masks that keep one low_dim-wide block: of the first tile only (kOneCol, kOneRow), of every tile across
+// the block width (kColBlock, kRowBlock), or a whole row band (kMultiRow)
+const Plaintext &low_mask(HEMMer &h, LowMask kind, const TileTensorShape &s, i64 block, int level) {
+    const i64 low = h.lowDim();
+    MaskCache::Key k{sched::kLowRank, s, ((i64)kind << 40) | (block << 20) | low, level};
+    if (const Plaintext *p = h.masks().find(k)) return *p;
+    const i64 rows = s.getNumRows(), cols = s.getNumCols(), width = s.getBlockWidth();
+    if (rows * width > h.slots() || (block + 1) * low > std::max(rows, width)) throw std::invalid_argument("[lowRank] block outside the tile");
+    Message m((size_t)h.slots());
+    auto on = [&](i64 r, i64 c) { m.re[(size_t)(r * width + c)] = 1.0; };
+    const i64 lo = block * low, hi = (block + 1) * low;
+    switch (kind) {
+    case kOneCol:   for (i64 r = 0; r < rows; ++r) for (i64 c = lo; c < hi; ++c) on(r, c); break;
+    case kOneRow:   for (i64 r = lo; r < hi; ++r) for (i64 c = 0; c < cols; ++c) on(r, c); break;
+    case kMultiRow: for (i64 r = lo; r < hi; ++r) for (i64 c = 0; c < width; ++c) on(r, c); break;
+    case kColBlock: for (i64 r = 0; r < rows; ++r) for (i64 t = 0; t < width; t += cols) for (i64 c = lo; c < hi; ++c) on(r, t + c); break;
+    case kRowBlock: for (i64 r = lo; r < hi; ++r) for (i64 t = 0; t < width; t += cols) for (i64 c = 0; c < cols; ++c) on(r, t + c); break;
+    }
+    return h.masks().put(k, h.eval().encode(m, level));
+}
+// x + rot(x, i * step) for i = low, 2 low, ... < end: left when bit j of `pos` is 0, right otherwise.  After the
+// tree, block `pos` holds the sum over all blocks.
+Ciphertext sum_into_block(const Evaluator &ev, Ciphertext x, i64 low, i64 end, i64 step, i64 pos) {
+    for (i64 i = low; i < end; i <<= 1, pos /= 2) x = ev.add(x, pos % 2 == 0 ? ev.leftRotate(x, i * step) : ev.rightRotate(x, i * step));
+    return x;
+}
+}
+// HEMMer::repackToOneCol -- HEMMer.cpp:2131-2172
+CtxtTensor HEMMer::repackToOneCol(const CtxtTensor &t, u64 out_col_block) {
+    const i64 cols = t.getWidth(), width = t.getBlockWidth();
+    Ciphertext x = sum_into_block(eval_, t.get(), low_dim_, width, 1, (i64)out_col_block);
+    x = eval_.mult(x, low_mask(*this, kOneCol, t.getShape(), (i64)out_col_block, x.getLevel()));
+    for (i64 i = cols; i < width; i <<= 1) x = eval_.add(x, eval_.rightRotate(x, cols));
+    return CtxtTensor(t.getShape(), std::move(x));
+}
+// HEMMer::repackToMultiCol -- HEMMer.cpp:2174-2209
+CtxtTensor HEMMer::repackToMultiCol(const CtxtTensor &t, u64 out_col_block) {
+    Ciphertext x = sum_into_block(eval_, t.get(), low_dim_, t.getBlockWidth() / 2, 1, (i64)out_col_block);
+    return CtxtTensor(t.getShape(), eval_.mult(x, low_mask(*this, kColBlock, t.getShape(), (i64)out_col_block, x.getLevel())));
+}
+// HEMMer::repackToOneRow -- HEMMer.cpp:2211-2255
+CtxtTensor HEMMer::repackToOneRow(const CtxtTensor &t, u64 out_row_block) {
+    const i64 cols = t.getWidth(), width = t.getBlockWidth();
+    Ciphertext x = sum_into_block(eval_, t.get(), low_dim_, t.getHeight(), width, (i64)out_row_block);
+    for (i64 i = cols; i < width; i <<= 1) x = eval_.add(x, eval_.leftRotate(x, cols));
+    x = eval_.mult(x, low_mask(*this, kOneRow, t.getShape(), (i64)out_row_block, x.getLevel()));
+    for (i64 i = cols; i < width; i += cols) x = eval_.add(x, eval_.rightRotate(x, cols));
+    return CtxtTensor(t.getShape(), std::move(x));
+}
+// HEMMer::repackToMultiRow -- HEMMer.cpp:2257-2290
+CtxtTensor HEMMer::repackToMultiRow(const CtxtTensor &t, u64 out_row_block) {
+    Ciphertext x = sum_into_block(eval_, t.get(), low_dim_, t.getHeight(), t.getBlockWidth(), (i64)out_row_block);
+    return CtxtTensor(t.getShape(), eval_.mult(x, low_mask(*this, kMultiRow, t.getShape(), (i64)out_row_block, x.getLevel())));
+}
+// HEMMer::getLowColBlock -- HEMMer.cpp:2292-2311 ; getLowRowBlock -- :2313-2332
+CtxtTensor HEMMer::getLowColBlock(const CtxtTensor &t, u64 col_block) {
+    return CtxtTensor(t.getShape(), eval_.mult(t.get(), low_mask(*this, kColBlock, t.getShape(), (i64)col_block, t.getLevel())));
+}
+CtxtTensor HEMMer::getLowRowBlock(const CtxtTensor &t, u64 row_block) {
+    return CtxtTensor(t.getShape(), eval_.mult(t.get(), low_mask(*this, kRowBlock, t.getShape(), (i64)row_block, t.getLevel())));
+}
+
 } // namespace HELLM

@@ -1,6 +1,7 @@
 // C entry points of libhellm_b200.so: the HEMMer call surface for callers that bind through a C ABI
 // (ctypes in this repository's tests and benchmark).  Tile shapes travel as (rows, cols, block_width).
 #include "HEMMer.hpp"
+#include "hellm_b200.h"
 
 using namespace HELLM;
 
@@ -149,4 +150,36 @@ int hb_hemmer_repack_not_bts(hb_hemmer *h, const hb_ct *a, const hb_ct *b, hb_ct
         *out = h->h.repack_notBTS(CtxtTensor(TileTensorShape(), Ciphertext(ba.c)), CtxtTensor(TileTensorShape(), Ciphertext(bb.c))).get().release();
     });
 }
+// LoRA low-rank family (HEMMer.cpp:2108-2332); low_dim replaces the compile-time ModelArgs::LOW_DIM
+int hb_hemmer_matmul_high_low(hb_hemmer *h, const hb_ct *a, int ra, int ca, int wa, const hb_ct *b, int rb, int cb, int wb, int in_col_block, int target, int low_dim, hb_ct **out) {
+    return guard([&] {
+        Borrow ba(h->ctx, a), bb(h->ctx, b);
+        h->h.setLowDim(low_dim);
+        *out = h->h.matMulHighLow(view(ba, ra, ca, wa), view(bb, rb, cb, wb), (u64)in_col_block, target).get().release();
+    });
+}
+int hb_hemmer_matmul_low_high(hb_hemmer *h, const hb_ct *a, int ra, int ca, int wa, const hb_ct *b, int rb, int cb, int wb, int in_row_block, int target, int low_dim, hb_ct **out) {
+    return guard([&] {
+        Borrow ba(h->ctx, a), bb(h->ctx, b);
+        h->h.setLowDim(low_dim);
+        *out = h->h.matMulLowHigh(view(ba, ra, ca, wa), view(bb, rb, cb, wb), (u64)in_row_block, target).get().release();
+    });
+}
+int hb_hemmer_matmul_low_low(hb_hemmer *h, const hb_ct *a, int ra, int ca, int wa, const hb_ct *b, int rb, int cb, int wb, int in_col_block, int in_row_block, int target, int low_dim, hb_ct **out) {
+    return guard([&] {
+        Borrow ba(h->ctx, a), bb(h->ctx, b);
+        h->h.setLowDim(low_dim);
+        *out = h->h.matMulLowLow(view(ba, ra, ca, wa), view(bb, rb, cb, wb), (u64)in_col_block, (u64)in_row_block, target).get().release();
+    });
+}
+#define LOW_REPACK(name, method) \
+    int hb_hemmer_##name(hb_hemmer *h, const hb_ct *a, SHAPE_ARGS, int block, int low_dim, hb_ct **out) { \
+        return guard([&] { if (block < 0) throw std::invalid_argument("[lowRank] negative block"); IN_TENSOR(t, a); h->h.setLowDim(low_dim); *out = h->h.method(t, (u64)block).get().release(); }); \
+    }
+LOW_REPACK(repack_to_one_col, repackToOneCol)
+LOW_REPACK(repack_to_multi_col, repackToMultiCol)
+LOW_REPACK(repack_to_one_row, repackToOneRow)
+LOW_REPACK(repack_to_multi_row, repackToMultiRow)
+LOW_REPACK(low_col_block, getLowColBlock)
+LOW_REPACK(low_row_block, getLowRowBlock)
 } // extern "C"

@@ -437,5 +437,89 @@ CtxtTensor multMatMatCCReUse(Env &e, const Ciphertext &pre, const CtxtTensor &tb
     return CtxtTensor(tb.getShape(), e.ev.relinearize(acc));
 }
 
+// ---- LoRA low-rank products -- MatrixUtils.cpp:1681-1996 --------------------------------------------------
+// One factor has only low_dim columns (or rows).  Its transform then has low_dim diagonals and the product loop
+// low_dim terms; the other terms of the inner sum are folded by doubling trees of rotate-and-add, here on the
+// thin operand (so that every low_dim-wide block of it carries the term it meets in the loop) and, afterwards,
+// in HEMMer::repackTo*.  The operation order is that of the reference functions.
+namespace {
+void require_low_rank(const CtxtTensor &a, const CtxtTensor &b, int target_level, i64 low_dim) {
+    if (low_dim < 1 || (low_dim & (low_dim - 1))) throw std::invalid_argument("[lowRank] low_dim must be a power of two");
+    if (std::min(a.getLevel(), b.getLevel()) < target_level + 3) throw std::invalid_argument("[lowRank] level too low");
+}
+// x + rot(x, +-step * i) for i = low_dim, 2 low_dim, ... < end; bit j of `pos` picks the direction of round j
+Ciphertext fold_tree(Env &e, Ciphertext x, i64 low_dim, i64 end, i64 step, i64 pos, bool even_goes_right) {
+    for (i64 i = low_dim; i < end; i <<= 1, pos /= 2) {
+        const bool right = (pos % 2 == 0) == even_goes_right;
+        x = e.ev.add(x, right ? e.ev.rightRotate(x, i * step) : e.ev.leftRotate(x, i * step));
+    }
+    return x;
+}
+// k = 0 term plus the low_dim - 1 shifted terms (the common tail of the three reference functions)
+CtxtTensor low_rank_tail(Env &e, Ciphertext a, Ciphertext b, const TileTensorShape &s1, const TileTensorShape &s2, i64 width, i64 low_dim, int target_level) {
+    const int lvl = target_level + 2;
+    const i64 num_rows = s1.getNumRows();
+    Ciphertext res = e.ev.mult(a, b);
+    if (low_dim > 1) {
+        a = e.ev.leftRotate(a, 1);
+        b = e.ev.leftRotate(b, width);
+        Ciphertext a_wrap = e.ev.rightRotate(a, width / 2), b_wrap = e.ev.rightRotate(b, num_rows * width);
+        Ciphertext acc;
+        for (i64 i = 1; i < low_dim; ++i) {
+            if (i > 1) {
+                a = e.ev.leftRotate(a, 1); a_wrap = e.ev.leftRotate(a_wrap, 1);
+                b = e.ev.leftRotate(b, width); b_wrap = e.ev.leftRotate(b_wrap, width);
+            }
+            Ciphertext ak = e.ev.assemble(a, col_wrap(e, s1, 2 * i + 1, lvl), a_wrap, col_wrap(e, s1, 2 * i, lvl));
+            Ciphertext bk = e.ev.assemble(b, row_wrap(e, s2, 2 * i + 1, lvl), b_wrap, row_wrap(e, s2, 2 * i, lvl));
+            e.ev.tensorAccumulate(acc, ak, bk);
+        }
+        res = e.ev.add(res, e.ev.rescale(e.ev.relinearize(acc)));
+    }
+    return CtxtTensor(TileTensorShape(s1.getNumRows(), s2.getNumCols(), s2.getBlockWidth()), std::move(res));
+}
+} // namespace
+
+// multMatMatHighLow -- MatrixUtils.cpp:1681-1771
+CtxtTensor multMatMatHighLow(Env &e, const CtxtTensor &op1, const CtxtTensor &op2, i64 in_col_block, int target_level, i64 low_dim) {
+    require_low_rank(op1, op2, target_level, low_dim);
+    const i64 width = op2.getBlockWidth();
+    Ciphertext a = diagonalToColumn(e, CtxtTensor(op1.getShape(), e.ev.levelDown(op1.get(), target_level + 3))).get();
+    Ciphertext b = diagonalToRow(e, CtxtTensor(TileTensorShape(op2.getHeight(), low_dim, width), e.ev.levelDown(op2.get(), target_level + 3))).get();
+    i64 col_pos = in_col_block;
+    for (i64 i = low_dim; i < width / 2; i <<= 1, col_pos /= 2) {
+        if (col_pos % 2 == 0) {
+            b = e.ev.add(b, e.ev.rightRotate(e.ev.leftRotate(b, i * width), i));
+        } else {
+            Ciphertext side = e.ev.leftRotate(b, i);
+            b = e.ev.add(e.ev.leftRotate(b, i * width), side);
+        }
+    }
+    return low_rank_tail(e, std::move(a), std::move(b), op1.getShape(), op2.getShape(), width, low_dim, target_level);
+}
+// multMatMatLowHigh -- MatrixUtils.cpp:1773-1879
+CtxtTensor multMatMatLowHigh(Env &e, const CtxtTensor &op1, const CtxtTensor &op2, i64 in_row_block, int target_level, i64 low_dim) {
+    require_low_rank(op1, op2, target_level, low_dim);
+    if (op1.getBlockWidth() != op2.getBlockWidth()) throw std::invalid_argument("[getCommonBlockWidth] different block width");
+    const i64 width = op1.getBlockWidth();
+    Ciphertext a = fold_tree(e, e.ev.levelDown(op1.get(), target_level + 3), low_dim, width / 2, width, in_row_block, true);
+    a = diagonalToColumn(e, CtxtTensor(op1.getShape(), std::move(a))).get();
+    Ciphertext b = diagonalToRow(e, CtxtTensor(op2.getShape(), e.ev.levelDown(op2.get(), target_level + 3))).get();
+    return low_rank_tail(e, std::move(a), std::move(b), op1.getShape(), op2.getShape(), width, low_dim, target_level);
+}
+// multMatMatLowLow -- MatrixUtils.cpp:1881-1996
+CtxtTensor multMatMatLowLow(Env &e, const CtxtTensor &op1, const CtxtTensor &op2, i64 in_col_block, i64 in_row_block, int target_level, i64 low_dim) {
+    require_low_rank(op1, op2, target_level, low_dim);
+    if (op1.getBlockWidth() != op2.getBlockWidth()) throw std::invalid_argument("[getCommonBlockWidth] different block width");
+    const i64 width = op1.getBlockWidth();
+    Ciphertext a = diagonalToColumn(e, CtxtTensor(TileTensorShape(op1.getHeight(), low_dim, width), e.ev.levelDown(op1.get(), target_level + 3))).get();
+    Ciphertext b = diagonalToRow(e, CtxtTensor(TileTensorShape(low_dim, op2.getWidth(), width), e.ev.levelDown(op2.get(), target_level + 3))).get();
+    // the reference interleaves the two trees round by round; they touch different ciphertexts, so running one
+    // after the other leaves every bit as it was
+    a = fold_tree(e, std::move(a), low_dim, width / 2, 1, in_col_block, true);
+    b = fold_tree(e, std::move(b), low_dim, width / 2, width, in_row_block, true);
+    return low_rank_tail(e, std::move(a), std::move(b), op1.getShape(), op2.getShape(), width, low_dim, target_level);
+}
+
 } // namespace sched
 } // namespace HELLM

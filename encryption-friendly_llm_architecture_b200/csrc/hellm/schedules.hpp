@@ -6,7 +6,7 @@ namespace HELLM {
 namespace sched {
 
 // mask families, used as the first component of MaskCache::Key
-enum MaskKind { kDiagonal = 0, kHorizontal, kVertical, kPackedHorizontal, kPackedVertical, kColWrap, kRowWrap, kHemmer };
+enum MaskKind { kDiagonal = 0, kHorizontal, kVertical, kPackedHorizontal, kPackedVertical, kColWrap, kRowWrap, kHemmer, kLowRank };
 
 // Schedule variants.  kFaithful keeps the reference's sequence of rotations (each shifted copy is the previous one
 // rotated once more).  kDirect takes every shifted copy straight from the transformed operand, rot(x, k) instead of
@@ -41,6 +41,10 @@ Ciphertext multMatMatPre(Env &e, const CtxtTensor &a, int target_level);
 CtxtTensor multMatMatReUse(Env &e, const Ciphertext &pre, const PtxtTensor &w);
 CtxtTensor multMatMatPreRev(Env &e, const CtxtTensor &b, int target_level);
 CtxtTensor multMatMatCCReUse(Env &e, const Ciphertext &pre, const CtxtTensor &b);
+// LoRA low-rank products (MatrixUtils.cpp:1681-1996); low_dim stands for ModelArgs::LOW_DIM
+CtxtTensor multMatMatHighLow(Env &e, const CtxtTensor &a, const CtxtTensor &b, i64 in_col_block, int target_level, i64 low_dim);
+CtxtTensor multMatMatLowHigh(Env &e, const CtxtTensor &a, const CtxtTensor &b, i64 in_row_block, int target_level, i64 low_dim);
+CtxtTensor multMatMatLowLow(Env &e, const CtxtTensor &a, const CtxtTensor &b, i64 in_col_block, i64 in_row_block, int target_level, i64 low_dim);
 
 } // namespace sched
 } // namespace HELLM

@@ -223,3 +223,43 @@ class Hemmer:
 
     def repack_not_bts(self, a, b):
         return CtxtTensor(self._call("repack_not_bts", a.ct.ptr, b.ct.ptr), *a.shape)
+
+    # ---- LoRA low-rank products (HEMMer.hpp:326-346) ----
+    def matmul_high_low(self, a, b, in_col_block, target_level=4, low_dim=2):
+        """HEMMer::matMulHighLow: full tile x thin block that sits in column block `in_col_block`."""
+        ct = self._call("matmul_high_low", a.ct.ptr, *self._shp(a), b.ct.ptr, *self._shp(b),
+                        C.c_int(in_col_block), C.c_int(target_level), C.c_int(low_dim))
+        return CtxtTensor(ct, a.rows, b.cols, b.width)
+
+    def matmul_low_high(self, a, b, in_row_block, target_level=4, low_dim=2):
+        """HEMMer::matMulLowHigh: thin block in row block `in_row_block` x full tile."""
+        ct = self._call("matmul_low_high", a.ct.ptr, *self._shp(a), b.ct.ptr, *self._shp(b),
+                        C.c_int(in_row_block), C.c_int(target_level), C.c_int(low_dim))
+        return CtxtTensor(ct, a.rows, b.cols, b.width)
+
+    def matmul_low_low(self, a, b, in_col_block, in_row_block, target_level=4, low_dim=2):
+        """HEMMer::matMulLowLow: thin column block x thin row block."""
+        ct = self._call("matmul_low_low", a.ct.ptr, *self._shp(a), b.ct.ptr, *self._shp(b),
+                        C.c_int(in_col_block), C.c_int(in_row_block), C.c_int(target_level), C.c_int(low_dim))
+        return CtxtTensor(ct, a.rows, b.cols, b.width)
+
+    def _low(self, name, t, block, low_dim):
+        return CtxtTensor(self._call(name, t.ct.ptr, *self._shp(t), C.c_int(block), C.c_int(low_dim)), *t.shape)
+
+    def repack_to_one_col(self, t, out_col_block, low_dim=2):
+        return self._low("repack_to_one_col", t, out_col_block, low_dim)
+
+    def repack_to_multi_col(self, t, out_col_block, low_dim=2):
+        return self._low("repack_to_multi_col", t, out_col_block, low_dim)
+
+    def repack_to_one_row(self, t, out_row_block, low_dim=2):
+        return self._low("repack_to_one_row", t, out_row_block, low_dim)
+
+    def repack_to_multi_row(self, t, out_row_block, low_dim=2):
+        return self._low("repack_to_multi_row", t, out_row_block, low_dim)
+
+    def get_low_col_block(self, t, col_block, low_dim=2):
+        return self._low("low_col_block", t, col_block, low_dim)
+
+    def get_low_row_block(self, t, row_block, low_dim=2):
+        return self._low("low_row_block", t, row_block, low_dim)

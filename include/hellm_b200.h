@@ -1,0 +1,117 @@
+/* hellm_b200.h -- C entry points of libhellm_b200.so: the HELLM::HEMMer call surface on one B200.
+ *
+ * The reference exposes this surface as the C++ class HELLM::HEMMer
+ * (ciphertext/include/HELLM/HEMMer.hpp:33-438) over HETensor values (HETensor.hpp:46-86); it
+ * has no C ABI.  The same class, with the reference's method names, is in this repository's
+ * csrc/hellm/HEMMer.hpp for C++ callers; the functions below are that class for callers that
+ * bind through C.  Each one names the HEMMer method (header line) and the schedule it runs
+ * (ciphertext/src/MatrixUtils.cpp or HEMMer.cpp lines).
+ *
+ * Conventions
+ *   - a tile tensor travels as a ciphertext handle plus (rows, cols, block_width), the
+ *     TileTensorShape of the reference (HETensor.hpp:16-44);
+ *   - inputs are borrowed for the call, outputs are new caller-owned handles (hb_ct_free);
+ *   - every function returns 0 or a negative HB_E_* code (hemmer_b200.h); the reference throws
+ *     std::invalid_argument for shape and level violations (MatrixUtils.cpp:27,36,680,1113,1322),
+ *     reported here as HB_E_ARG with the same message through hb_hemmer_last_error();
+ *   - all ciphertext handles may hold a batch: every function applies the schedule to all batch
+ *     members with one set of launches.
+ */
+#ifndef HELLM_B200_H
+#define HELLM_B200_H
+
+#include "hemmer_b200.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct hb_hemmer hb_hemmer;
+
+/* HEMMer::HEMMer over an existing context with keys (HEMMer.cpp:93-209); masks are cached per object */
+int hb_hemmer_create(hb_ctx *ctx, hb_hemmer **out);
+void hb_hemmer_destroy(hb_hemmer *h);
+/* message of the last failure raised above the primitive layer (thread-local) */
+const char *hb_hemmer_last_error(void);
+/* 0: the reference's rotation sequence, each shifted copy rotated from the previous one (default);
+ * 1: every shifted copy is one rotation of the transformed operand, sharing its decomposition.
+ * The two give the same slots and different ciphertext bits; no counterpart in the reference. */
+int hb_hemmer_set_schedule(hb_hemmer *h, int mode);
+
+/* HEMMer::transposeInplace (HEMMer.hpp:129; HEMMer.cpp:1166-1172; MatrixUtils.cpp:671-739) */
+int hb_hemmer_transpose(hb_hemmer *h, const hb_ct *a, int rows, int cols, int width, int target_level, hb_ct **out);
+/* MatrixTransformer::diagonalToColumn / diagonalToRow (MatrixUtils.cpp:776-848, 924-996) */
+int hb_hemmer_sigma(hb_hemmer *h, const hb_ct *a, int rows, int cols, int width, hb_ct **out);
+int hb_hemmer_tau(hb_hemmer *h, const hb_ct *a, int rows, int cols, int width, hb_ct **out);
+
+/* HEMMer::singleCCMatMul (HEMMer.hpp:164-166; MatrixUtils.cpp:1307-1446) */
+int hb_hemmer_matmul_cc(hb_hemmer *h, const hb_ct *a, int ra, int ca, int wa, const hb_ct *b, int rb, int cb, int wb,
+                        int target_level, hb_ct **out);
+/* the same product in two halves: the transforms (both results at target_level + 2), then the product loop.
+ * Operands of different input levels can be transformed one by one and multiplied as one batch. */
+int hb_hemmer_matmul_cc_prepare(hb_hemmer *h, const hb_ct *a, int ra, int ca, int wa, const hb_ct *b, int rb, int cb, int wb,
+                                int target_level, hb_ct **sigma_a, hb_ct **tau_b);
+int hb_hemmer_matmul_cc_core(hb_hemmer *h, const hb_ct *sigma_a, const hb_ct *tau_b, int rows, int inner, int cols, int width,
+                             int target_level, hb_ct **out);
+/* HEMMer::singleMatMul (HEMMer.hpp:160-162; MatrixUtils.cpp:1448-1570) */
+int hb_hemmer_matmul_cp(hb_hemmer *h, const hb_ct *a, int ra, int ca, int wa, const hb_pt *b, int rb, int cb, int wb,
+                        int target_level, hb_ct **out);
+/* HEMMer::packedMatMul (HEMMer.cpp:833-838; MatrixUtils.cpp:1100-1216) */
+int hb_hemmer_packed_matmul(hb_hemmer *h, const hb_ct *a, int ra, int ca, int wa, const hb_ct *b, int rb, int cb, int wb,
+                            int target_level, hb_ct **out);
+
+/* HEMMer::matMulPre (HEMMer.hpp:190-191; MatrixUtils.cpp:1572-1610): `out` is ONE handle whose batch holds the
+ * shifted copies, copy k of input b at index k * batch(a) + b */
+int hb_hemmer_matmul_pre(hb_hemmer *h, const hb_ct *a, int rows, int cols, int width, int target_level, hb_ct **out);
+/* HEMMer::matMulReUse (HEMMer.hpp:192-194; MatrixUtils.cpp:1612-1639; HEaaN matmul, HomEvaluator.hpp:595-601) */
+int hb_hemmer_matmul_reuse(hb_hemmer *h, const hb_ct *pre, const hb_pt *w, int rows, int cols, int width, hb_ct **out);
+/* sum over `bcount` inputs b0.. of matMulReUse(copies of input b, pts[b - b0]) in one pass; `pre` holds the copies
+ * of `btotal` inputs.  The sum the reference takes with addInplace over K tiles (bert-matmul.cpp:268-287). */
+int hb_hemmer_matmul_reuse_groups(hb_hemmer *h, const hb_ct *pre, int btotal, int b0, const hb_pt *const *pts, int bcount,
+                                  int width, hb_ct **out);
+/* HEMMer::matMulPreRev, matMulCCReUse (HEMMer.cpp:1114-1124; MatrixUtils.cpp:1641-1679) */
+int hb_hemmer_matmul_pre_rev(hb_hemmer *h, const hb_ct *b, int rows, int cols, int width, int target_level, hb_ct **out);
+int hb_hemmer_matmul_cc_reuse(hb_hemmer *h, const hb_ct *pre, const hb_ct *b, int rows, int cols, int width, hb_ct **out);
+/* HEMMer::packedMatMulPre, PreRot, PreRev, CCReuse (HEMMer.cpp:840-864; MatrixUtils.cpp:1218-1305) */
+int hb_hemmer_packed_matmul_pre(hb_hemmer *h, const hb_ct *a, int rows, int cols, int width, int target_level, hb_ct **out);
+int hb_hemmer_packed_matmul_pre_rot(hb_hemmer *h, const hb_ct *a, int rows, int cols, int width, int target_level, hb_ct **out);
+int hb_hemmer_packed_matmul_pre_rev(hb_hemmer *h, const hb_ct *b, int rows, int cols, int width, int target_level, hb_ct **out);
+int hb_hemmer_packed_matmul_cc_reuse(hb_hemmer *h, const hb_ct *pre, const hb_ct *b, int rows, int cols, int width, hb_ct **out);
+
+/* HEMMer::complexPackingInplace, complexPackingRowInplace, transposeComplexPackingInplace (HEMMer.cpp:764-817) */
+int hb_hemmer_complex_packing(hb_hemmer *h, const hb_ct *a, int rows, int cols, int width, hb_ct **out);
+int hb_hemmer_complex_packing_row(hb_hemmer *h, const hb_ct *a, int rows, int cols, int width, hb_ct **out);
+int hb_hemmer_transpose_complex_packing(hb_hemmer *h, const hb_ct *a, int rows, int cols, int width, int target_level, hb_ct **out);
+/* HEMMer::splitInTwo (HEMMer.cpp:819-831) */
+int hb_hemmer_split_in_two(hb_hemmer *h, const hb_ct *a, int rows, int cols, int width, hb_ct **out1, hb_ct **out2);
+/* HEMMer::repackCC (HEMMer.cpp:964-969), complexPacking(ct, ct) (:980-986), complexPackingRev (:988-994),
+ * repack_notBTS (:1025-1053) */
+int hb_hemmer_repack_cc(hb_hemmer *h, const hb_ct *a, hb_ct **out);
+int hb_hemmer_complex_packing2(hb_hemmer *h, const hb_ct *a, const hb_ct *b, hb_ct **out);
+int hb_hemmer_complex_packing_rev(hb_hemmer *h, const hb_ct *a, const hb_ct *b, hb_ct **out);
+int hb_hemmer_repack_not_bts(hb_hemmer *h, const hb_ct *a, const hb_ct *b, hb_ct **out);
+
+/* LoRA low-rank family.  `low_dim` is the width of the thin factor, ModelArgs::LOW_DIM in the reference
+ * (ModelArgs.hpp:67, a compile-time 2 there); `in_*_block` / `block` is the index of the low_dim-wide column
+ * (row) block the thin factor occupies inside its tile.
+ * HEMMer::matMulHighLow / matMulLowHigh / matMulLowLow (HEMMer.hpp:326-334; MatrixUtils.cpp:1681-1996) */
+int hb_hemmer_matmul_high_low(hb_hemmer *h, const hb_ct *a, int ra, int ca, int wa, const hb_ct *b, int rb, int cb, int wb,
+                              int in_col_block, int target_level, int low_dim, hb_ct **out);
+int hb_hemmer_matmul_low_high(hb_hemmer *h, const hb_ct *a, int ra, int ca, int wa, const hb_ct *b, int rb, int cb, int wb,
+                              int in_row_block, int target_level, int low_dim, hb_ct **out);
+int hb_hemmer_matmul_low_low(hb_hemmer *h, const hb_ct *a, int ra, int ca, int wa, const hb_ct *b, int rb, int cb, int wb,
+                             int in_col_block, int in_row_block, int target_level, int low_dim, hb_ct **out);
+/* HEMMer::repackToOneCol / MultiCol / OneRow / MultiRow (HEMMer.hpp:336-343; HEMMer.cpp:2131-2290): fold the
+ * partial sums the products above leave spread over the blocks into block `block` */
+int hb_hemmer_repack_to_one_col(hb_hemmer *h, const hb_ct *a, int rows, int cols, int width, int block, int low_dim, hb_ct **out);
+int hb_hemmer_repack_to_multi_col(hb_hemmer *h, const hb_ct *a, int rows, int cols, int width, int block, int low_dim, hb_ct **out);
+int hb_hemmer_repack_to_one_row(hb_hemmer *h, const hb_ct *a, int rows, int cols, int width, int block, int low_dim, hb_ct **out);
+int hb_hemmer_repack_to_multi_row(hb_hemmer *h, const hb_ct *a, int rows, int cols, int width, int block, int low_dim, hb_ct **out);
+/* HEMMer::getLowColBlock / getLowRowBlock (HEMMer.hpp:345-346; HEMMer.cpp:2292-2332): keep one block of every tile */
+int hb_hemmer_low_col_block(hb_hemmer *h, const hb_ct *a, int rows, int cols, int width, int block, int low_dim, hb_ct **out);
+int hb_hemmer_low_row_block(hb_hemmer *h, const hb_ct *a, int rows, int cols, int width, int block, int low_dim, hb_ct **out);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* HELLM_B200_H */

@@ -759,6 +759,208 @@ struct Hemmer {
         out = ev.add(out, tmp);
         return CtT{out, t1.sh};
     }
+    // ---------------- LoRA low-rank products ----------------
+    // A thin factor (low_dim columns or rows) needs only low_dim terms of the product loop; the remaining terms
+    // of the inner sum are folded by the log-step rotate-and-add trees below and in the repackTo* helpers.
+    // low_dim is ModelArgs::LOW_DIM in the reference (ModelArgs.hpp:67); here it is an argument.
+    std::map<std::tuple<int, Shape, i64, i64>, Mask> low_mask_;
+    Mask &low_mask(int kind, const Shape &s, i64 block, i64 low_dim) { return low_mask_[std::make_tuple(kind, s, block, low_dim)]; }
+
+    // the k = 0 term and the low_dim - 1 shifted terms -- shared tail of MatrixUtils.cpp:1716-1768, 1809-1876, 1929-1996
+    CtT low_rank_tail(Ct a, Ct b, const Shape &sh1, const Shape &sh2, i64 width, i64 low_dim, int target_level) {
+        const i64 num_rows = sh1.rows;
+        Ct res = ev.mul(a, b);
+        a = rotL(a, 1);
+        b = rotL(b, width);
+        Ct a_rot = rotR(a, width / 2);
+        Ct b_rot = rotR(b, num_rows * width);
+        auto &col_mask = get_col_mask(sh1, target_level + 2);
+        auto &row_mask = get_row_mask(sh2, target_level + 2);
+        Ct itxt_res;
+        for (i64 i = 1; i < low_dim; i++) {
+            if (i > 1) {
+                a = rotL(a, 1); a_rot = rotL(a_rot, 1);
+                b = rotL(b, width); b_rot = rotL(b_rot, width);
+            }
+            Ct tmp1 = assemble(a, col_mask[(size_t)(2 * i + 1)], a_rot, col_mask[(size_t)(2 * i)]);
+            Ct tmp2 = assemble(b, row_mask[(size_t)(2 * i + 1)], b_rot, row_mask[(size_t)(2 * i)]);
+            Ct t = ev.tensor(tmp1, tmp2);
+            itxt_res = (i == 1) ? t : ev.add(itxt_res, t);
+        }
+        if (low_dim > 1) res = ev.add(res, ev.rescale(ev.relin(itxt_res)));
+        return CtT{res, Shape(sh1.rows, sh2.cols, sh2.width)};
+    }
+    void low_rank_check(const CtT &op1, const CtT &op2, int target_level, i64 low_dim) {
+        if (low_dim < 1 || (low_dim & (low_dim - 1))) throw std::invalid_argument("[lowRank] low_dim must be a power of two");
+        if (std::min(op1.ct.level, op2.ct.level) < target_level + 3) throw std::invalid_argument("[lowRank] level too low");
+    }
+    // multMatMatHighLow -- MatrixUtils.cpp:1681-1771
+    CtT mult_mat_mat_high_low(const CtT &op1, const CtT &op2, i64 in_col_block, int target_level, i64 low_dim) {
+        low_rank_check(op1, op2, target_level, low_dim);
+        const i64 width = op2.sh.width;
+        CtT a = op1, b = op2;
+        b.sh = Shape(op2.sh.rows, low_dim, op2.sh.width);
+        a.ct = ev.level_down(a.ct, target_level + 3);
+        b.ct = ev.level_down(b.ct, target_level + 3);
+        a = diagonal_to_column(a);
+        b = diagonal_to_row(b);
+        i64 col_pos = in_col_block;
+        for (i64 i = low_dim; i < width / 2; i <<= 1) {
+            Ct tmp;
+            if (col_pos % 2 == 0) {
+                tmp = rotL(b.ct, i * width);
+                tmp = rotR(tmp, i);
+            } else {
+                tmp = rotL(b.ct, i);
+                b.ct = rotL(b.ct, i * width);
+            }
+            b.ct = ev.add(b.ct, tmp);
+            col_pos /= 2;
+        }
+        return low_rank_tail(a.ct, b.ct, op1.sh, op2.sh, width, low_dim, target_level);
+    }
+    // multMatMatLowHigh -- MatrixUtils.cpp:1773-1879
+    CtT mult_mat_mat_low_high(const CtT &op1, const CtT &op2, i64 in_row_block, int target_level, i64 low_dim) {
+        low_rank_check(op1, op2, target_level, low_dim);
+        if (op1.sh.width != op2.sh.width) throw std::invalid_argument("[getCommonBlockWidth] different block width");
+        const i64 width = op1.sh.width;
+        CtT a = op1, b = op2;
+        a.ct = ev.level_down(a.ct, target_level + 3);
+        b.ct = ev.level_down(b.ct, target_level + 3);
+        i64 row_pos = in_row_block;
+        for (i64 i = low_dim; i < width / 2; i <<= 1) {
+            Ct tmp = (row_pos % 2 == 0) ? rotR(a.ct, i * width) : rotL(a.ct, i * width);
+            a.ct = ev.add(a.ct, tmp);
+            row_pos /= 2;
+        }
+        a = diagonal_to_column(a);
+        b = diagonal_to_row(b);
+        return low_rank_tail(a.ct, b.ct, op1.sh, op2.sh, width, low_dim, target_level);
+    }
+    // multMatMatLowLow -- MatrixUtils.cpp:1881-1996
+    CtT mult_mat_mat_low_low(const CtT &op1, const CtT &op2, i64 in_col_block, i64 in_row_block, int target_level, i64 low_dim) {
+        low_rank_check(op1, op2, target_level, low_dim);
+        if (op1.sh.width != op2.sh.width) throw std::invalid_argument("[getCommonBlockWidth] different block width");
+        const i64 width = op1.sh.width;
+        CtT a = op1, b = op2;
+        a.sh = Shape(op1.sh.rows, low_dim, op1.sh.width);
+        b.sh = Shape(low_dim, op2.sh.cols, op2.sh.width);
+        a.ct = ev.level_down(a.ct, target_level + 3);
+        b.ct = ev.level_down(b.ct, target_level + 3);
+        a = diagonal_to_column(a);
+        b = diagonal_to_row(b);
+        i64 col_pos = in_col_block, row_pos = in_row_block;
+        for (i64 i = low_dim; i < width / 2; i <<= 1) {
+            Ct tmp = (col_pos % 2 == 0) ? rotR(a.ct, i) : rotL(a.ct, i);
+            a.ct = ev.add(a.ct, tmp);
+            col_pos /= 2;
+            tmp = (row_pos % 2 == 0) ? rotR(b.ct, i * width) : rotL(b.ct, i * width);
+            b.ct = ev.add(b.ct, tmp);
+            row_pos /= 2;
+        }
+        return low_rank_tail(a.ct, b.ct, op1.sh, op2.sh, width, low_dim, target_level);
+    }
+    // repackToOneCol -- HEMMer.cpp:2131-2172
+    CtT repack_to_one_col(const CtT &t, i64 out_col_block, i64 low_dim) {
+        const i64 num_rows = t.sh.rows, num_cols = t.sh.cols, width = t.sh.width;
+        CtT ret = t;
+        i64 col_pos = out_col_block;
+        for (i64 i = low_dim; i < width; i <<= 1) {
+            Ct tmp = (col_pos % 2 == 0) ? rotL(ret.ct, i) : rotR(ret.ct, i);
+            ret.ct = ev.add(ret.ct, tmp);
+            col_pos /= 2;
+        }
+        Mask &m = low_mask(0, t.sh, out_col_block, low_dim);
+        if (m.msg.empty()) {
+            m.msg.assign((size_t)slots, cplx(0, 0));
+            for (i64 i = 0; i < num_rows; i++)
+                for (i64 j = out_col_block * low_dim; j < (1 + out_col_block) * low_dim; j++) m.msg[(size_t)(i * width + j)] = 1;
+        }
+        ret.ct = mult_msg(ret.ct, m);
+        for (i64 i = num_cols; i < width; i <<= 1) ret.ct = ev.add(ret.ct, rotR(ret.ct, num_cols));
+        return ret;
+    }
+    // repackToMultiCol -- HEMMer.cpp:2174-2209
+    CtT repack_to_multi_col(const CtT &t, i64 out_col_block, i64 low_dim) {
+        const i64 num_rows = t.sh.rows, num_cols = t.sh.cols, width = t.sh.width;
+        CtT ret = t;
+        i64 col_pos = out_col_block;
+        for (i64 i = low_dim; i < width / 2; i <<= 1) {
+            Ct tmp = (col_pos % 2 == 0) ? rotL(ret.ct, i) : rotR(ret.ct, i);
+            ret.ct = ev.add(ret.ct, tmp);
+            col_pos /= 2;
+        }
+        ret.ct = mult_msg(ret.ct, low_col_block_mask(t.sh, out_col_block, low_dim));
+        (void)num_rows; (void)num_cols;
+        return ret;
+    }
+    // repackToOneRow -- HEMMer.cpp:2211-2255
+    CtT repack_to_one_row(const CtT &t, i64 out_row_block, i64 low_dim) {
+        const i64 num_rows = t.sh.rows, num_cols = t.sh.cols, width = t.sh.width;
+        CtT ret = t;
+        i64 row_pos = out_row_block;
+        for (i64 i = low_dim; i < num_rows; i <<= 1) {
+            Ct tmp = (row_pos % 2 == 0) ? rotL(ret.ct, i * width) : rotR(ret.ct, i * width);
+            ret.ct = ev.add(ret.ct, tmp);
+            row_pos /= 2;
+        }
+        for (i64 i = num_cols; i < width; i <<= 1) ret.ct = ev.add(ret.ct, rotL(ret.ct, num_cols));
+        Mask &m = low_mask(1, t.sh, out_row_block, low_dim);
+        if (m.msg.empty()) {
+            m.msg.assign((size_t)slots, cplx(0, 0));
+            for (i64 i = out_row_block * low_dim; i < (1 + out_row_block) * low_dim; ++i)
+                for (i64 j = 0; j < num_cols; j++) m.msg[(size_t)(i * width + j)] = 1;
+        }
+        ret.ct = mult_msg(ret.ct, m);
+        for (i64 i = num_cols; i < width; i += num_cols) ret.ct = ev.add(ret.ct, rotR(ret.ct, num_cols));
+        return ret;
+    }
+    // repackToMultiRow -- HEMMer.cpp:2257-2290
+    CtT repack_to_multi_row(const CtT &t, i64 out_row_block, i64 low_dim) {
+        const i64 num_rows = t.sh.rows, width = t.sh.width;
+        CtT ret = t;
+        i64 row_pos = out_row_block;
+        for (i64 i = low_dim; i < num_rows; i <<= 1) {
+            Ct tmp = (row_pos % 2 == 0) ? rotL(ret.ct, i * width) : rotR(ret.ct, i * width);
+            ret.ct = ev.add(ret.ct, tmp);
+            row_pos /= 2;
+        }
+        Mask &m = low_mask(2, t.sh, out_row_block, low_dim);
+        if (m.msg.empty()) {
+            m.msg.assign((size_t)slots, cplx(0, 0));
+            for (i64 i = out_row_block * low_dim; i < (1 + out_row_block) * low_dim; ++i)
+                for (i64 j = 0; j < width; j++) m.msg[(size_t)(i * width + j)] = 1;
+        }
+        ret.ct = mult_msg(ret.ct, m);
+        return ret;
+    }
+    // the mask of getLowColBlock and repackToMultiCol: columns [block*low_dim, (block+1)*low_dim) of every
+    // num_cols-wide tile of the first num_rows rows
+    Mask &low_col_block_mask(const Shape &s, i64 block, i64 low_dim) {
+        Mask &m = low_mask(3, s, block, low_dim);
+        if (m.msg.empty()) {
+            m.msg.assign((size_t)slots, cplx(0, 0));
+            for (i64 i = 0; i < s.rows; i++)
+                for (i64 k = 0; k < s.width; k += s.cols)
+                    for (i64 j = block * low_dim; j < (1 + block) * low_dim; j++) m.msg[(size_t)(i * s.width + k + j)] = 1;
+        }
+        return m;
+    }
+    // getLowColBlock -- HEMMer.cpp:2292-2311
+    CtT get_low_col_block(const CtT &t, i64 col_block, i64 low_dim) {
+        return CtT{mult_msg(t.ct, low_col_block_mask(t.sh, col_block, low_dim)), t.sh};
+    }
+    // getLowRowBlock -- HEMMer.cpp:2313-2332
+    CtT get_low_row_block(const CtT &t, i64 row_block, i64 low_dim) {
+        Mask &m = low_mask(4, t.sh, row_block, low_dim);
+        if (m.msg.empty()) {
+            m.msg.assign((size_t)slots, cplx(0, 0));
+            for (i64 i = row_block * low_dim; i < (1 + row_block) * low_dim; i++)
+                for (i64 k = 0; k < t.sh.width; k += t.sh.cols)
+                    for (i64 j = 0; j < t.sh.cols; j++) m.msg[(size_t)(i * t.sh.width + k + j)] = 1;
+        }
+        return CtT{mult_msg(t.ct, m), t.sh};
+    }
 };
 
 } // namespace orc

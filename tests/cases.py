@@ -211,7 +211,100 @@ def sc_single_matmul(lib, H, target=2):
     return [lib.ct_export(c.ct), lib.pt_export(prod)[None, None], lib.pt_export(summ)[None, None], lib.pt_export(rot)[None, None]], err
 
 
+def _thin_cols(M, d, r):
+    """[T0 | T1]: the d x r row block k of M sits in columns [r (k // 2), r (k // 2) + r) of tile k % 2."""
+    T = [np.zeros((d, d)), np.zeros((d, d))]
+    for k in range(M.shape[0] // d):
+        T[k % 2][:, r * (k // 2):r * (k // 2) + r] = M[k * d:(k + 1) * d]
+    return T
+
+
+def _thin_rows(M, d, r):
+    """[T0 | T1]: the r x d column block k of M sits in rows [r (k // 2), r (k // 2) + r) of tile k % 2."""
+    T = [np.zeros((d, d)), np.zeros((d, d))]
+    for k in range(M.shape[1] // d):
+        T[k % 2][r * (k // 2):r * (k // 2) + r, :] = M[:, k * d:(k + 1) * d]
+    return T
+
+
+def _pairs(H, M, d, nonce):
+    return [H.encrypt2(M[:, 2 * i * d:(2 * i + 1) * d].copy(), M[:, (2 * i + 1) * d:(2 * i + 2) * d].copy(), nonce=nonce + i) for i in range(M.shape[1] // (2 * d))]
+
+
+def sc_lora_forward(lib, H, target=4, r=2):
+    """The LoRA branch of a projection as the reference runs it (TransformerBlock.cpp:1787-1835, without the
+    bootstraps): X Wa by matMulHighLow on three tile pairs, repackToOneCol, then (X Wa) Wb by matMulLowLow."""
+    d = tile_dim(lib)
+    rng = np.random.default_rng(120)
+    X, Wa, Wb = rng.uniform(-1, 1, (d, 6 * d)), rng.normal(0, 0.2, (6 * d, r)), rng.normal(0, 0.2, (r, 6 * d))
+    cur = _pairs(H, X, d, 50)
+    lora_wa, lora_wb = H.encrypt2(*_thin_cols(Wa, d, r), nonce=56), H.encrypt2(*_thin_rows(Wb, d, r), nonce=57)
+    acc = None
+    for i in range(3):
+        part = H.matmul_high_low(cur[i], H.get_low_col_block(lora_wa, i, r), i, target, r)
+        if acc is None:
+            acc = part
+        else:
+            H.add_inplace(acc, part)
+    assert lib.ct_meta(acc.ct)[0] == target
+    xa = H.repack_to_one_col(acc, 0, r)
+    z = lib.decrypt(xa.ct).real.reshape(d, 2 * d)
+    want = np.zeros((d, 2 * d))
+    want[:, :r] = want[:, d:d + r] = X @ Wa
+    err = np.abs(z - want).max()
+    exports = [lib.ct_export(acc.ct), lib.ct_export(xa.ct)]
+    t2 = lib.ct_meta(xa.ct)[0] - 3
+    for i in range(3):
+        out = H.matmul_low_low(xa, H.get_low_row_block(lora_wb, i, r), 0, i, t2, r)
+        z = lib.decrypt(out.ct).real.reshape(d, 2 * d)
+        err = max(err, np.abs(z - (X @ Wa @ Wb)[:, 2 * i * d:(2 * i + 2) * d]).max())
+        exports.append(lib.ct_export(out.ct))
+    return exports, err
+
+
+def sc_lora_backward(lib, H, target=4, r=2):
+    """Gradients of the two LoRA factors (TransformerBlock.cpp:10500-10535): (X Wa)^T dY by matMulLowHigh +
+    repackToMultiRow, X^T (dY Wb^T) by matMulHighLow + repackToMultiCol; and repackToOneRow on its own."""
+    d = tile_dim(lib)
+    rng = np.random.default_rng(121)
+    X, dY = rng.uniform(-1, 1, (d, 6 * d)), rng.uniform(-1, 1, (d, 6 * d))
+    XA, G = rng.uniform(-1, 1, (d, r)), rng.uniform(-1, 1, (d, r))  # stand-ins for X Wa and dY Wb^T
+    dYc = _pairs(H, dY, d, 60)
+    P = np.zeros((d, d)); P[:r, :] = XA.T
+    Q = np.zeros((d, d)); Q[:, :r] = G
+    in_b, gb = H.encrypt2(P, P, nonce=66), H.encrypt2(Q, Q, nonce=67)
+    grad_wb = grad_wa = None
+    for i in range(3):
+        m = H.repack_to_multi_row(H.matmul_low_high(in_b, dYc[i], 0, target, r), i, r)
+        if grad_wb is None:
+            grad_wb = m
+        else:
+            H.add_inplace(grad_wb, m)
+        xt = H.encrypt2(X[:, 2 * i * d:(2 * i + 1) * d].T.copy(), X[:, (2 * i + 1) * d:(2 * i + 2) * d].T.copy(), nonce=70 + i)
+        m = H.repack_to_multi_col(H.matmul_high_low(xt, gb, 0, target, r), i, r)
+        if grad_wa is None:
+            grad_wa = m
+        else:
+            H.add_inplace(grad_wa, m)
+    z = lib.decrypt(grad_wb.ct).real.reshape(d, 2 * d)
+    err = np.abs(z - np.concatenate(_thin_rows(XA.T @ dY, d, r), axis=1)).max()
+    z = lib.decrypt(grad_wa.ct).real.reshape(d, 2 * d)
+    want = np.concatenate(_thin_cols(np.concatenate([X[:, k * d:(k + 1) * d].T @ G for k in range(6)]), d, r), axis=1)
+    err = max(err, np.abs(z - want).max())
+    # repackToOneRow: every r-row band of both tiles summed into band `block` of both tiles
+    M = rng.uniform(-1, 1, (d, 2 * d))
+    blk = 1
+    one = H.repack_to_one_row(H.encrypt2(M[:, :d].copy(), M[:, d:].copy(), nonce=75), blk, r)
+    band = sum(M[j:j + r, :d] + M[j:j + r, d:] for j in range(0, d, r))
+    want = np.zeros((d, 2 * d))
+    want[blk * r:(blk + 1) * r, :d] = want[blk * r:(blk + 1) * r, d:] = band
+    err = max(err, np.abs(lib.decrypt(one.ct).real.reshape(d, 2 * d) - want).max())
+    return [lib.ct_export(grad_wb.ct), lib.ct_export(grad_wa.ct), lib.ct_export(one.ct)], err
+
+
 SCENARIOS = {
+    "lora_forward": sc_lora_forward,
+    "lora_backward": sc_lora_backward,
     "single_matmul": sc_single_matmul,
     "batched": sc_batched,
     "transforms": sc_transforms,
