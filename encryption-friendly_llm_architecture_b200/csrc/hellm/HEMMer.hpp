@@ -111,6 +111,7 @@ class HEMMer {
     CtxtTensor complexPacking(const CtxtTensor &a, const CtxtTensor &b) const;
     CtxtTensor complexPackingRev(const CtxtTensor &a, const CtxtTensor &b) const;
     CtxtTensor repack_notBTS(const CtxtTensor &a, const CtxtTensor &b);
+    CtxtTensor repack_loraOpti(const CtxtTensor &a, const CtxtTensor &b);
     // LoRA low-rank products and their repacking -- HEMMer.cpp:2108-2332.  The thin factor has lowDim() columns or
     // rows (ModelArgs::LOW_DIM, ModelArgs.hpp:67) and sits in block `in_*_block` of its tile.
     CtxtTensor matMulHighLow(const CtxtTensor &a, const CtxtTensor &b, u64 in_col_block, int target_level = 4);

@@ -6,7 +6,7 @@
 namespace HELLM {
 
 namespace {
-enum HemmerMask { kColEven = 1, kRowEven = 2, kLeftHalf = 3 };
+enum HemmerMask { kColEven = 1, kRowEven = 2, kLeftHalf = 3, kLeftHalfScaled = 4 };
 }
 
 HEMMer::HEMMer(hb_ctx *ctx) : ctx_(ctx), eval_(ctx) {
@@ -135,7 +135,7 @@ static const Plaintext &hemmer_mask(HEMMer &h, int which, int level) {
     for (i64 r = 0; r < d; ++r)
         for (i64 c = 0; c < 2 * d; ++c) {
             bool on = which == kColEven ? ((c % d) % 2 == 0) : which == kRowEven ? (r % 2 == 0) : (c < d);
-            if (on) m.re[(size_t)(r * 2 * d + c)] = 1.0;
+            if (on) m.re[(size_t)(r * 2 * d + c)] = which == kLeftHalfScaled ? 0.5 : 1.0;
         }
     return h.masks().put(k, h.eval().encode(m, level));
 }
@@ -180,6 +180,22 @@ CtxtTensor HEMMer::repack_notBTS(const CtxtTensor &t1, const CtxtTensor &t2) {
     out = eval_.add(out, tmp);
     tmp = eval_.mult(tmp, hemmer_mask(*this, kLeftHalf, tmp.getLevel()));
     out = eval_.mult(out, hemmer_mask(*this, kLeftHalf, out.getLevel()));
+    out = eval_.add(out, eval_.rightRotate(tmp, tile_));
+    return CtxtTensor(t1.getShape(), std::move(out));
+}
+// HEMMer::repack_loraOpti -- HEMMer.cpp:1055-1091; its mask is 0.5 on the left tile (mask_matmul_half_, HEMMer.cpp:2341-2342)
+CtxtTensor HEMMer::repack_loraOpti(const CtxtTensor &t1, const CtxtTensor &t2) {
+    Ciphertext a = eval_.rescale(t1.get()), b = eval_.rescale(t2.get());
+    Ciphertext out = eval_.add(a, eval_.conjugate(a));
+    Ciphertext tmp = eval_.multImagUnit(eval_.add(b, eval_.conjugate(b)));
+    out = eval_.add(out, tmp);
+    tmp = eval_.leftRotate(out, tile_);
+    out = eval_.add(out, tmp);
+    Ciphertext conj = eval_.conjugate(out);
+    out = eval_.add(out, conj);
+    tmp = eval_.multImagUnit(eval_.sub(conj, tmp));
+    tmp = eval_.mult(tmp, hemmer_mask(*this, kLeftHalfScaled, tmp.getLevel()));
+    out = eval_.mult(out, hemmer_mask(*this, kLeftHalfScaled, out.getLevel()));
     out = eval_.add(out, eval_.rightRotate(tmp, tile_));
     return CtxtTensor(t1.getShape(), std::move(out));
 }

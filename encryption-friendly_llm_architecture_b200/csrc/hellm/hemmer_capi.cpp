@@ -150,6 +150,12 @@ int hb_hemmer_repack_not_bts(hb_hemmer *h, const hb_ct *a, const hb_ct *b, hb_ct
         *out = h->h.repack_notBTS(CtxtTensor(TileTensorShape(), Ciphertext(ba.c)), CtxtTensor(TileTensorShape(), Ciphertext(bb.c))).get().release();
     });
 }
+int hb_hemmer_repack_lora_opti(hb_hemmer *h, const hb_ct *a, const hb_ct *b, hb_ct **out) {
+    return guard([&] {
+        Borrow ba(h->ctx, a), bb(h->ctx, b);
+        *out = h->h.repack_loraOpti(CtxtTensor(TileTensorShape(), Ciphertext(ba.c)), CtxtTensor(TileTensorShape(), Ciphertext(bb.c))).get().release();
+    });
+}
 // LoRA low-rank family (HEMMer.cpp:2108-2332); low_dim replaces the compile-time ModelArgs::LOW_DIM
 int hb_hemmer_matmul_high_low(hb_hemmer *h, const hb_ct *a, int ra, int ca, int wa, const hb_ct *b, int rb, int cb, int wb, int in_col_block, int target, int low_dim, hb_ct **out) {
     return guard([&] {

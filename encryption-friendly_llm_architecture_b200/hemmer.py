@@ -224,6 +224,9 @@ class Hemmer:
     def repack_not_bts(self, a, b):
         return CtxtTensor(self._call("repack_not_bts", a.ct.ptr, b.ct.ptr), *a.shape)
 
+    def repack_lora_opti(self, a, b):
+        return CtxtTensor(self._call("repack_lora_opti", a.ct.ptr, b.ct.ptr), *a.shape)
+
     # ---- LoRA low-rank products (HEMMer.hpp:326-346) ----
     def matmul_high_low(self, a, b, in_col_block, target_level=4, low_dim=2):
         """HEMMer::matMulHighLow: full tile x thin block that sits in column block `in_col_block`."""

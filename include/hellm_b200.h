@@ -90,6 +90,9 @@ int hb_hemmer_repack_cc(hb_hemmer *h, const hb_ct *a, hb_ct **out);
 int hb_hemmer_complex_packing2(hb_hemmer *h, const hb_ct *a, const hb_ct *b, hb_ct **out);
 int hb_hemmer_complex_packing_rev(hb_hemmer *h, const hb_ct *a, const hb_ct *b, hb_ct **out);
 int hb_hemmer_repack_not_bts(hb_hemmer *h, const hb_ct *a, const hb_ct *b, hb_ct **out);
+/* HEMMer::repack_loraOpti (HEMMer.cpp:1055-1091): repack_notBTS followed by the split of real and imaginary part
+ * that the reference otherwise gets from bootstrapExtended */
+int hb_hemmer_repack_lora_opti(hb_hemmer *h, const hb_ct *a, const hb_ct *b, hb_ct **out);
 
 /* LoRA low-rank family.  `low_dim` is the width of the thin factor, ModelArgs::LOW_DIM in the reference
  * (ModelArgs.hpp:67, a compile-time 2 there); `in_*_block` / `block` is the index of the low_dim-wide column

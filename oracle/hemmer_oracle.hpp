@@ -759,6 +759,32 @@ struct Hemmer {
         out = ev.add(out, tmp);
         return CtT{out, t1.sh};
     }
+    // repack_loraOpti -- HEMMer.cpp:1055-1091 (mask_matmul_half_ = encode2(0.5, 0), HEMMer.cpp:2341-2342)
+    Mask mask_left_half_scaled_;
+    CtT repack_lora_opti(const CtT &t1, const CtT &t2) {
+        if (mask_left_half_scaled_.msg.empty()) {
+            mask_left_half_scaled_.msg = mask_left_half_.msg;
+            for (auto &v : mask_left_half_scaled_.msg) v *= 0.5;
+        }
+        ev.gen_galois_key(cx.galois_conj());
+        Ct a = ev.rescale(t1.ct), b = ev.rescale(t2.ct);
+        Ct out = ev.add(a, ev.conjugate(a));
+        Ct tmp = ev.add(b, ev.conjugate(b));
+        tmp = ev.mult_imag(tmp);
+        out = ev.add(out, tmp);
+        tmp = rotL(out, tile);
+        out = ev.add(out, tmp);
+        Ct conj_tmp = ev.conjugate(out);
+        out = ev.add(out, conj_tmp);
+        tmp = ev.add(conj_tmp, tmp, true);
+        tmp = ev.mult_imag(tmp);
+        tmp = mult_msg(tmp, mask_left_half_scaled_);
+        out = mult_msg(out, mask_left_half_scaled_);
+        tmp = rotR(tmp, tile);
+        out = ev.add(out, tmp);
+        return CtT{out, t1.sh};
+    }
+
     // ---------------- LoRA low-rank products ----------------
     // A thin factor (low_dim columns or rows) needs only low_dim terms of the product loop; the remaining terms
     // of the inner sum are folded by the log-step rotate-and-add trees below and in the repackTo* helpers.

@@ -302,7 +302,30 @@ def sc_lora_backward(lib, H, target=4, r=2):
     return [lib.ct_export(grad_wb.ct), lib.ct_export(grad_wa.ct), lib.ct_export(one.ct)], err
 
 
+def sc_repack_lora_opti(lib, H, target=2):
+    """repack_loraOpti on two un-rescaled matMulReUse results, against the same slot arithmetic in the clear."""
+    d = tile_dim(lib)
+    X = _mats(122, d, 4)
+    rngw = np.random.default_rng(123)
+    x01, x23 = H.encrypt2(X[0], X[1], nonce=80), H.encrypt2(X[2], X[3], nonce=81)
+    pre = H.matmul_pre(H.complex_packing(x01, x23), target)
+    outs = [H.matmul_reuse(pre, H.encode_diagonal_to_row4(*[rngw.normal(0, 0.05, (d, d)) for _ in range(4)], level=target + 1)) for _ in range(2)]
+    rp = H.repack_lora_opti(outs[0], outs[1])
+    u, v = lib.decrypt(outs[0].ct), lib.decrypt(outs[1].ct)
+    out = 2 * u.real + 2j * v.real
+    tmp = np.roll(out, -d)
+    out = out + tmp
+    conj = np.conj(out)
+    out = out + conj
+    tmp = 1j * (conj - tmp)
+    m = np.zeros(lib.slots)
+    m.reshape(-1, 2 * d)[:d, :d] = 0.5
+    want = m * out + np.roll(m * tmp, d)
+    return [lib.ct_export(rp.ct)], np.abs(lib.decrypt(rp.ct) - want).max()
+
+
 SCENARIOS = {
+    "repack_lora_opti": sc_repack_lora_opti,
     "lora_forward": sc_lora_forward,
     "lora_backward": sc_lora_backward,
     "single_matmul": sc_single_matmul,
