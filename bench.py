@@ -255,18 +255,20 @@ def run_gpu(args):
     ms_step = ms_total / args.steps
     # the same layer with the reference's own rotation sequence (no hoisting), for comparison
     ms_faithful = None
-    if args.schedule == 1 and not args.no_compare:
+    if args.schedule != 0 and not args.no_compare:
         H.set_schedule(0)
         wl.step_resident()
         ms_faithful = timed_region(lambda s: wl.step_resident(), 1)
-        H.set_schedule(1)
+        H.set_schedule(args.schedule)
 
     # end to end: host matrices in, decrypted host results out, every step
     wl.h2d_bytes = wl.d2h_bytes = 0
     wl.step_e2e()
     wl.h2d_bytes = wl.d2h_bytes = 0
+    wl.phases_ms = {}
     e2e_steps = max(1, min(args.steps, 2))
     ms_e2e = timed_region(lambda s: wl.step_e2e(), e2e_steps) / e2e_steps
+    e2e_phases = {k: round(v / e2e_steps, 1) for k, v in wl.phases_ms.items()}
     h2d, d2h = wl.h2d_bytes // e2e_steps, wl.d2h_bytes // e2e_steps
     if world > 1:
         t = torch.tensor([h2d, d2h, launches], device="cuda", dtype=torch.float64)
@@ -323,11 +325,11 @@ def run_gpu(args):
                "sample": f"sum over {info['distinct_ops_timed']} distinct (operation, level) pairs of exact count x one sampled full-size timing ({info['sample_seconds']} s of CPU work)"}
     line = {"metric": METRIC, "value": ms_step, "unit": "ms", "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,
             "higher_is_better": False, "scaling": "strong", "vs_baseline": None, "dtype": "u64", "data": "synthetic",
-            "config": {"workload": "bert_base_layer_matmuls_fwd_plus_lora_bwd", "units": len(wl.units), "batched_calls": True, "schedule": "direct_hoisted" if args.schedule == 1 else "reference_sequence", "ring_degree": 65536, "levels": 12, "tile": 128,
+            "config": {"workload": "bert_base_layer_matmuls_fwd_plus_lora_bwd", "units": len(wl.units), "batched_calls": True, "schedule": {0: "reference_sequence", 1: "direct_hoisted", 2: "direct_hoisted_one_division_per_copy"}[args.schedule], "ring_degree": 65536, "levels": 12, "tile": 128,
                        "l2": "working set per step is tens of GB, far above the 126 MB L2", "max_abs_err_vs_float64": err,
                        "reference_sequence_ms": ms_faithful, "device_pool_gb": pool_gb},
             "roofline": roofline, "cpu_baseline": cpu,
-            "e2e": {"value": ms_e2e, "unit": "ms", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+            "e2e": {"value": ms_e2e, "unit": "ms", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "phases_ms_rank0": e2e_phases},
             "gpu_launches": launches, "clocks": clocks}
     print(json.dumps(line), flush=True)
     if world > 1:
@@ -396,8 +398,9 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
     ap.add_argument("--one-step", action="store_true", help="run a single pass of the layer and exit (launch-list profiling)")
-    ap.add_argument("--schedule", type=int, default=1, choices=[0, 1],
-                    help="0: the reference's rotation sequence; 1 (default): direct, hoisted rotations (same products, fewer chained key switches)")
+    ap.add_argument("--schedule", type=int, default=2, choices=[0, 1, 2],
+                    help="0: the reference's rotation sequence; 1: direct, hoisted rotations (same products, fewer chained key switches); "
+                         "2 (default): as 1, each wrapped copy of the shift loops made with one division by P*q_level instead of two ModDowns and a rescale")
     ap.add_argument("--no-compare", action="store_true", help="skip the extra timed pass with the reference's rotation sequence")
     ap.add_argument("--sweep-batch", type=int, default=256)
     ap.add_argument("--sweep-levels", type=str, default="12,8,4,1")

@@ -124,6 +124,15 @@ class Lib:
         self._chk(self._fn("encode")(self.ctx, _f64(re), _f64(im), C.c_size_t(re.size), C.c_int(level), C.byref(out)))
         return Handle(self, out, "pt")
 
+    def encode_ext(self, z, level):
+        """encode() with K further limbs modulo the special primes: the plaintext operand of assemble_rot."""
+        z = np.asarray(z)
+        re = np.ascontiguousarray(z.real, dtype=np.float64)
+        im = np.ascontiguousarray(z.imag, dtype=np.float64) if np.iscomplexobj(z) else None
+        out = C.c_void_p()
+        self._chk(self._fn("encode_ext")(self.ctx, _f64(re), _f64(im), C.c_size_t(re.size), C.c_int(level), C.byref(out)))
+        return Handle(self, out, "pt")
+
     def decode(self, pt):
         re = np.zeros(self.slots); im = np.zeros(self.slots)
         self._chk(self._fn("decode")(self.ctx, pt.ptr, _f64(re), _f64(im)))
@@ -137,6 +146,30 @@ class Lib:
     def decrypt(self, ct, index=0):
         re = np.zeros(self.slots); im = np.zeros(self.slots)
         self._chk(self._fn("decrypt")(self.ctx, ct.ptr, C.c_int(index), _f64(re), _f64(im)))
+        return re + 1j * im
+
+    def encrypt_many(self, msgs, level, nonces):
+        """Encode + encrypt the rows of `msgs` ([count][slots], real or complex) into one batched handle."""
+        msgs = np.asarray(msgs)
+        n = msgs.shape[0]
+        if not self.has("encrypt_many"):  # a library without the batched entry point: one call per member
+            return self.batch_concat([self.encrypt(self.encode(m, level), k) for m, k in zip(msgs, nonces)])
+        re = np.ascontiguousarray(msgs.real, dtype=np.float64)
+        im = np.ascontiguousarray(msgs.imag, dtype=np.float64) if np.iscomplexobj(msgs) else None
+        nn = (C.c_uint64 * n)(*[int(k) for k in nonces])
+        out = C.c_void_p()
+        self._chk(self._fn("encrypt_many")(self.ctx, _f64(re), _f64(im), C.c_size_t(msgs.shape[1]), C.c_int(n), C.c_int(level), nn, C.byref(out)))
+        return Handle(self, out, "ct")
+
+    def decrypt_many(self, items):
+        """Decrypt a list of (ciphertext handle, batch index) pairs in one call; returns complex [len(items)][slots]."""
+        n = len(items)
+        if not self.has("decrypt_many"):  # a library without the batched entry point: one call per member
+            return np.stack([self.decrypt(ct, k) for ct, k in items])
+        re = np.zeros((n, self.slots)); im = np.zeros((n, self.slots))
+        cts = (C.c_void_p * n)(*[ct.ptr.value for ct, _ in items])
+        idx = (C.c_int * n)(*[int(k) for _, k in items])
+        self._chk(self._fn("decrypt_many")(self.ctx, cts, idx, C.c_int(n), _f64(re), _f64(im)))
         return re + 1j * im
 
     # ---- raw ----
@@ -220,6 +253,10 @@ class Lib:
     def mul(self, a, b): return self._op("mul", a.ptr, b.ptr)
     def rotate(self, a, s): return self._op("rotate", a.ptr, C.c_int64(s))
     def conjugate(self, a): return self._op("conjugate", a.ptr)
+
+    def assemble_rot(self, a, s1, p1, s2, p2):
+        """rescale(p1 (.) rot(a, s1) + p2 (.) rot(a, s2)) with one division by P * q_level for the sum."""
+        return self._op("assemble_rot", a.ptr, C.c_int64(s1), p1.ptr, C.c_int64(s2), p2.ptr)
 
     def _pt_op(self, name, *args):
         out = C.c_void_p()

@@ -99,6 +99,9 @@ class Evaluator {
     Plaintext encode(const Message &m, int level) const {
         hb_pt *p = nullptr; check(c_, hb_encode(c_, m.re.data(), m.im.data(), m.size(), level, &p)); return Plaintext(p);
     }
+    Plaintext encodeExtended(const Message &m, int level) const {
+        hb_pt *p = nullptr; check(c_, hb_encode_ext(c_, m.re.data(), m.im.data(), m.size(), level, &p)); return Plaintext(p);
+    }
     Message decode(const Plaintext &p, size_t slots) const {
         Message m(slots); check(c_, hb_decode(c_, p.raw(), m.re.data(), m.im.data())); return m;
     }
@@ -139,6 +142,13 @@ class Evaluator {
     // rescale(a (.) pa + b (.) pb): the "assemble" step of the matmul loops in one pass
     Ciphertext assemble(const Ciphertext &a, const Plaintext &pa, const Ciphertext &b, const Plaintext &pb) const {
         hb_ct *o = nullptr; check(c_, hb_mul2_add_rescale(c_, a.raw(), pa.raw(), b.raw(), pb.raw(), &o)); return Ciphertext(c_, o);
+    }
+    // pa (.) rot(a, sa) + pb (.) rot(a, sb), one level down: both key switches stay in the extended basis and share
+    // one division by P * q_level (pa, pb from encodeExtended)
+    Ciphertext assembleRotations(const Ciphertext &a, const Hoisted &h, i64 sa, const Plaintext &pa, i64 sb, const Plaintext &pb) const {
+        const i64 steps[2] = {sa, sb};
+        check(c_, hb_gen_rot_keys(c_, steps, 2));
+        hb_ct *o = nullptr; check(c_, hb_assemble_hoisted(c_, a.raw(), h.raw(), sa, pa.raw(), sb, pb.raw(), &o)); return Ciphertext(c_, o);
     }
     // sum_j mult(a[j], p[j]): every product is rescaled as eval.mult(ct, mask) does, the results are added
     Ciphertext multSum(const std::vector<const Ciphertext *> &a, const std::vector<const Plaintext *> &p) const {

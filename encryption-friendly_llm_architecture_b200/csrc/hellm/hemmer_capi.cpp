@@ -28,8 +28,8 @@ extern "C" {
 const char *hb_hemmer_last_error() { return g_err.c_str(); }
 int hb_hemmer_create(hb_ctx *c, hb_hemmer **out) { return guard([&] { *out = new hb_hemmer(c); }); }
 void hb_hemmer_destroy(hb_hemmer *h) { delete h; }
-// 0 = the reference's rotation sequence (default), 1 = direct, hoisted rotations
-int hb_hemmer_set_schedule(hb_hemmer *h, int mode) { if (mode < 0 || mode > 1) return HB_E_ARG; h->h.setSchedule(mode); return HB_OK; }
+// 0 = the reference's rotation sequence (default), 1 = direct, hoisted rotations, 2 = 1 with one division per wrapped copy
+int hb_hemmer_set_schedule(hb_hemmer *h, int mode) { if (mode < 0 || mode > 2) return HB_E_ARG; h->h.setSchedule(mode); return HB_OK; }
 
 #define SHAPE_ARGS int rows, int cols, int width
 #define IN_TENSOR(name, p) Borrow name##_b(h->ctx, p); CtxtTensor name(TileTensorShape(rows, cols, width), Ciphertext(name##_b.c))

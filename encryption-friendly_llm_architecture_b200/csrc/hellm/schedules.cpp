@@ -50,10 +50,10 @@ Message paint(const Env &e, const TileTensorShape &s, const Placement &pl, i64 r
     return m;
 }
 
-const Plaintext &cached(Env &e, int kind, const TileTensorShape &s, i64 idx, int level, const std::function<Message()> &make) {
+const Plaintext &cached(Env &e, int kind, const TileTensorShape &s, i64 idx, int level, const std::function<Message()> &make, bool extended = false) {
     MaskCache::Key k{kind, s, idx, level};
     if (const Plaintext *p = e.cache.find(k)) return *p;
-    return e.cache.put(k, e.ev.encode(make(), level));
+    return e.cache.put(k, extended ? e.ev.encodeExtended(make(), level) : e.ev.encode(make(), level));
 }
 
 // Masks of sigma / tau and their packed forms.
@@ -110,7 +110,7 @@ Ciphertext bsgs_diagonals(Env &e, const Ciphertext &op, const TileTensorShape &s
     auto mask = [&](i64 idx) -> const Plaintext & { return cached(e, kind, s, idx, level, [&] { return diag_family_mask(e, s, f, idx); }); };
     std::vector<Ciphertext> baby;
     baby.reserve((size_t)f.bs);
-    if (e.mode == kDirect) {
+    if (e.mode >= kDirect) {
         const Hoisted h = e.ev.decompose(op);
         for (i64 j = 0; j < f.bs; ++j) baby.push_back(e.ev.leftRotate(op, h, (j + 1) * f.gap));
     } else {
@@ -139,14 +139,16 @@ Ciphertext bsgs_diagonals(Env &e, const Ciphertext &op, const TileTensorShape &s
 }
 
 // Column / row wrap masks of the shift loops (generateColMask / generateRowMask, MatrixUtils.cpp:529-578):
-// entry 2i is 1 where the shifted copy has wrapped (last i columns / rows), entry 2i+1 its complement.
+// entry 2i is 1 where the shifted copy has wrapped (last i columns / rows), entry 2i+1 its complement.  They are
+// encoded with the extra special-prime limbs so that the kLazy schedule can apply them to a key-switch result that
+// is still in the extended basis; the first level + 1 limbs are those of a plain encoding.
 const Plaintext &col_wrap(Env &e, const TileTensorShape &s, i64 which, int level) {
     return cached(e, kColWrap, s, which, level, [&] {
         Message m((size_t)e.slots);
         const i64 cols = s.getNumCols(), i = which / 2; const bool wrapped = (which % 2) == 0;
         for (i64 j = 0; j < e.slots; ++j) { bool in_tail = (j % cols) >= cols - i; m.re[(size_t)j] = (in_tail == wrapped) ? 1.0 : 0.0; }
         return m;
-    });
+    }, true);
 }
 const Plaintext &row_wrap(Env &e, const TileTensorShape &s, i64 which, int level) {
     return cached(e, kRowWrap, s, which, level, [&] {
@@ -154,7 +156,7 @@ const Plaintext &row_wrap(Env &e, const TileTensorShape &s, i64 which, int level
         const i64 rows = s.getNumRows(), w = s.getBlockWidth(), i = which / 2; const bool wrapped = (which % 2) == 0;
         for (i64 j = 0; j < e.slots; ++j) { bool in_tail = ((j / w) % rows) >= rows - i; m.re[(size_t)j] = (in_tail == wrapped) ? 1.0 : 0.0; }
         return m;
-    });
+    }, true);
 }
 
 void require_product_shapes(const CtxtTensor &a, const CtxtTensor &b) {
@@ -183,7 +185,7 @@ CtxtTensor transpose(Env &e, const CtxtTensor &op) {
     };
     std::vector<Ciphertext> baby;
     baby.reserve((size_t)bs);
-    if (e.mode == kDirect) {
+    if (e.mode >= kDirect) {
         const Hoisted h = e.ev.decompose(op.get());
         for (i64 j = 0; j < bs; ++j) baby.push_back(e.ev.leftRotate(op.get(), h, (j - (num_rows - 1)) * gap));
     } else {
@@ -239,7 +241,14 @@ CtxtTensor ccmmCore(Env &e, Ciphertext a, Ciphertext b, i64 num_rows, i64 inner,
     const i64 rows_tmp = num_k > num_rows ? num_k : ceil_pow2(num_rows), cols_tmp = num_k > num_cols ? num_k : ceil_pow2(num_cols);
     Ciphertext res = e.ev.mult(a, b);
     Ciphertext acc;
-    if (e.mode == kDirect) {
+    if (e.mode == kLazy) {
+        const Hoisted ha = e.ev.decompose(a), hb = e.ev.decompose(b);
+        for (i64 i = 1; i < num_k; ++i) {
+            Ciphertext ak = e.ev.assembleRotations(a, ha, i, col_wrap(e, sa, 2 * i + 1, lvl), i - cols_tmp, col_wrap(e, sa, 2 * i, lvl));
+            Ciphertext bk = e.ev.assembleRotations(b, hb, i * width, row_wrap(e, sb, 2 * i + 1, lvl), (i - rows_tmp) * width, row_wrap(e, sb, 2 * i, lvl));
+            e.ev.tensorAccumulate(acc, ak, bk);
+        }
+    } else if (e.mode >= kDirect) {
         const Hoisted ha = e.ev.decompose(a), hb = e.ev.decompose(b);
         for (i64 i = 1; i < num_k; ++i) {
             Ciphertext ai = e.ev.leftRotate(a, ha, i), aw = e.ev.leftRotate(a, ha, i - cols_tmp);
@@ -325,7 +334,7 @@ CtxtTensor multPackedMatMat(Env &e, const CtxtTensor &op1, const CtxtTensor &op2
     const i64 cols_tmp = num_k > num_cols ? num_k : ceil_pow2(num_cols);
     Ciphertext res = e.ev.mult(a, b);
     Ciphertext acc;
-    if (e.mode == kDirect) {
+    if (e.mode >= kDirect) {
         const Hoisted ha = e.ev.decompose(a), hb = e.ev.decompose(b);
         for (i64 i = 1; i < num_k / 2; ++i) {
             Ciphertext ai = e.ev.leftRotate(a, ha, 2 * i), aw = e.ev.leftRotate(a, ha, 2 * i - cols_tmp);
@@ -359,7 +368,7 @@ Ciphertext multPackedMatMatPreRot(Env &e, const CtxtTensor &in, int target_level
     const int lvl = target_level + 2;
     std::vector<Ciphertext> copies;
     copies.push_back(e.ev.levelDownOne(in.get()));
-    if (e.mode == kDirect) {
+    if (e.mode >= kDirect) {
         const Hoisted h = e.ev.decompose(in.get());
         for (i64 i = 1; i < num_rows / 2; ++i) {
             Ciphertext ai = e.ev.leftRotate(in.get(), h, 2 * i), aw = e.ev.leftRotate(in.get(), h, 2 * i - num_rows);
@@ -384,9 +393,9 @@ CtxtTensor multPackedMatMatCCReuse(Env &e, const Ciphertext &pre, const CtxtTens
     const i64 width = tb.getBlockWidth();
     Ciphertext b = tb.get(), acc;
     const int count = pre.getBatch();
-    const Hoisted h = e.mode == kDirect ? e.ev.decompose(tb.get()) : Hoisted();
+    const Hoisted h = e.mode >= kDirect ? e.ev.decompose(tb.get()) : Hoisted();
     for (int i = 0; i < count; ++i) {
-        if (i > 0) b = e.mode == kDirect ? e.ev.leftRotate(tb.get(), h, (i64)i * 2 * width) : e.ev.leftRotate(b, 2 * width);
+        if (i > 0) b = e.mode >= kDirect ? e.ev.leftRotate(tb.get(), h, (i64)i * 2 * width) : e.ev.leftRotate(b, 2 * width);
         e.ev.tensorAccumulate(acc, e.ev.slice(pre, i), b);
     }
     return CtxtTensor(tb.getShape(), e.ev.rescale(e.ev.relinearize(acc)));
@@ -399,7 +408,13 @@ Ciphertext multMatMatPre(Env &e, const CtxtTensor &in, int target_level) {
     CtxtTensor s = diagonalToColumn(e, CtxtTensor(in.getShape(), e.ev.levelDown(in.get(), target_level + 3)));
     std::vector<Ciphertext> copies;
     copies.push_back(e.ev.levelDownOne(s.get()));
-    if (e.mode == kDirect) {
+    if (e.mode == kLazy) {
+        const Hoisted h = e.ev.decompose(s.get());
+        for (i64 i = 1; i < num_rows; ++i)
+            copies.push_back(e.ev.assembleRotations(s.get(), h, i, col_wrap(e, s.getShape(), 2 * i + 1, lvl), i - num_rows, col_wrap(e, s.getShape(), 2 * i, lvl)));
+        return e.ev.stack(copies);
+    }
+    if (e.mode >= kDirect) {
         const Hoisted h = e.ev.decompose(s.get());
         for (i64 i = 1; i < num_rows; ++i) {
             Ciphertext ai = e.ev.leftRotate(s.get(), h, i), aw = e.ev.leftRotate(s.get(), h, i - num_rows);
@@ -429,9 +444,9 @@ CtxtTensor multMatMatCCReUse(Env &e, const Ciphertext &pre, const CtxtTensor &tb
     const i64 width = tb.getBlockWidth();
     Ciphertext b = tb.get(), acc;
     const int count = pre.getBatch();
-    const Hoisted h = e.mode == kDirect ? e.ev.decompose(tb.get()) : Hoisted();
+    const Hoisted h = e.mode >= kDirect ? e.ev.decompose(tb.get()) : Hoisted();
     for (int i = 0; i < count; ++i) {
-        if (i > 0) b = e.mode == kDirect ? e.ev.leftRotate(tb.get(), h, (i64)i * width) : e.ev.leftRotate(b, width);
+        if (i > 0) b = e.mode >= kDirect ? e.ev.leftRotate(tb.get(), h, (i64)i * width) : e.ev.leftRotate(b, width);
         e.ev.tensorAccumulate(acc, e.ev.slice(pre, i), b);
     }
     return CtxtTensor(tb.getShape(), e.ev.relinearize(acc));

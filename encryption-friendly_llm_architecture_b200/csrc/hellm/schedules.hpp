@@ -13,7 +13,10 @@ enum MaskKind { kDiagonal = 0, kHorizontal, kVertical, kPackedHorizontal, kPacke
 // rot(rot(...), 1): the same slots, fewer chained key switches (less noise), and all rotations of one ciphertext
 // share the step-independent half of the key switch (hoisting).  The two variants give different ciphertext bits;
 // the CPU oracle implements both so that each can be checked bit for bit.
-enum ScheduleMode { kFaithful = 0, kDirect = 1 };
+// kLazy is kDirect with the masked pair of rotations that makes a wrapped copy done as one operation
+// (Evaluator::assembleRotations): the two key switches stay in the extended basis, the masks are applied there, and
+// one division by P * q_level replaces two ModDowns and a rescale -- in the product loop and in multMatMatPre.
+enum ScheduleMode { kFaithful = 0, kDirect = 1, kLazy = 2 };
 
 struct Env { // what a schedule needs: evaluator, slot count, mask cache, variant
     const Evaluator &ev;

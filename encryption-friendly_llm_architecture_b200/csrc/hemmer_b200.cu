@@ -9,6 +9,7 @@
 
 #include <dlfcn.h>
 #include <map>
+#include <thread>
 #include <memory>
 #include <mutex>
 #include <nccl.h> // types only: the library is resolved at run time, see nccl_api()
@@ -104,6 +105,8 @@ struct hb_ctx {
     Evk mult_key;
     std::map<u64, Evk> gal_keys;
     std::map<int, KsPlan *> plans; // device copies
+    std::map<int, DivPlan *> div_plans;
+    u64 *pinned = nullptr; size_t pinned_bytes = 0; // host staging buffer of hb_decrypt_many
     ChaChaKey ckey{};
     int N = 0, logn = 0, L = 0, K = 0, nprimes = 0;
     unsigned long long launches = 0; // kernels launched by this context
@@ -117,7 +120,7 @@ struct hb_ctx {
 
 #define LAUNCH(c) ((c)->launches++, 0)
 struct hb_ct { hb_ctx *ctx; int level, np, batch, spow; u64 *d; size_t limbs() const { return (size_t)batch * np * (level + 1); } };
-struct hb_pt { hb_ctx *ctx; int level, spow; u64 *d; };
+struct hb_pt { hb_ctx *ctx; int level, spow; u64 *d; int ext = 0; }; // ext: K further limbs modulo the special primes follow the level+1 limbs
 // lifted digits of the a-part of a ciphertext batch, NTT form: what all rotations of that ciphertext share
 struct hb_digits { hb_ctx *ctx; int level, batch; u64 *d; };
 
@@ -294,6 +297,79 @@ const Evk &galois_key(hb_ctx *c, u64 g) {
     auto it = c->gal_keys.find(g);
     if (it == c->gal_keys.end()) fail(HB_E_NOKEY, "no switching key for galois element " + std::to_string(g));
     return it->second;
+}
+
+// ---- division of a Q_level u P polynomial by P * q_level (masked pair of rotations) ----
+const DivPlan *get_div_plan(hb_ctx *c, int level) {
+    auto it = c->div_plans.find(level);
+    if (it != c->div_plans.end()) return it->second;
+    const HostCtx &h = *c->h;
+    auto P = std::make_unique<DivPlan>();
+    std::memset(P.get(), 0, sizeof(DivPlan));
+    const int K = h.K, ns = K + 1;
+    if (ns > 8) fail(HB_E_LIMIT, "too many special primes");
+    P->level = level; P->ns = ns;
+    P->src_prime[0] = (unsigned char)level;
+    for (int k = 0; k < K; ++k) P->src_prime[1 + k] = (unsigned char)(h.L + 1 + k);
+    for (int s = 0; s < ns; ++s) {
+        const u64 ds = h.q[P->src_prime[s]];
+        u64 hat = 1;
+        for (int t = 0; t < ns; ++t) if (t != s) hat = hbhost::mulmod(hat, h.q[P->src_prime[t]] % ds, ds);
+        const u64 hi_ = hbhost::invmod(hat, ds);
+        P->hat_inv[s] = hi_; P->hat_inv_sh[s] = hbhost::shoup(hi_, ds);
+        for (int l = 0; l < level; ++l) {
+            const u64 ql = h.q[l];
+            u64 hm = 1;
+            for (int t = 0; t < ns; ++t) if (t != s) hm = hbhost::mulmod(hm, h.q[P->src_prime[t]] % ql, ql);
+            P->hat_mod[s][l] = hm;
+        }
+    }
+    for (int l = 0; l <= level; ++l) {
+        const u64 ql = h.q[l];
+        u64 pm = 1;
+        for (int k = 0; k < K; ++k) pm = hbhost::mulmod(pm, h.q[h.L + 1 + k] % ql, ql);
+        P->p_mod[l] = pm;
+        if (l < level) P->d_inv[l] = hbhost::invmod(hbhost::mulmod(pm, h.q[level] % ql, ql), ql);
+    }
+    DivPlan *d = nullptr;
+    CK(cudaMalloc(&d, sizeof(DivPlan)));
+    CK(cudaMemcpyAsync(d, P.get(), sizeof(DivPlan), cudaMemcpyHostToDevice, c->st));
+    CK(cudaStreamSynchronize(c->st));
+    c->div_plans[level] = d;
+    return d;
+}
+// rescale(p1 (.) rot(a, s1) + p2 (.) rot(a, s2)) from the lifted digits `dt` of a: both inner products stay in
+// Q_level u P, are multiplied there by the extended plaintexts and summed; one division by P * q_level follows.
+hb_ct *do_assemble_rot(hb_ctx *c, const hb_ct *a, const u64 *dt, int64_t s1, const hb_pt *p1, int64_t s2, const hb_pt *p2) {
+    if (a->np != 2 || a->spow != 1) fail(HB_E_SHAPE, "assemble_rot: needs a rescaled 2-poly ciphertext");
+    if (a->level < 1) fail(HB_E_LEVEL, "assemble_rot: level 0");
+    if (!p1->ext || !p2->ext || p1->level != a->level || p2->level != a->level || p1->spow != 1 || p2->spow != 1)
+        fail(HB_E_LEVEL, "assemble_rot: plaintexts must be extended and at the ciphertext's level");
+    const u64 g1 = c->h->galois_rot(s1), g2 = c->h->galois_rot(s2);
+    if (g1 == 1 || g2 == 1) fail(HB_E_ARG, "assemble_rot: zero rotation");
+    const int level = a->level, batch = a->batch, N = c->N;
+    const KsPlan *pl = get_plan(c, level);
+    const DivPlan *dv = get_div_plan(c, level);
+    const PlanDims d = plan_dims(c, level);
+    const int n = d.n, ne = d.ne, ns = d.K + 1;
+    RotPair rp{};
+    rp.key[0] = galois_key(c, g1).d; rp.key[1] = galois_key(c, g2).d;
+    rp.mask[0] = p1->d; rp.mask[1] = p2->d;
+    rp.g[0] = (u32)g1; rp.g[1] = (u32)g2;
+    hb_ct *r = new_ct(c, level - 1, 2, batch, 1);
+    try {
+        const unsigned gx1 = (unsigned)((N + 255) / 256), gx = c->gx();
+        Tmp E(c, (size_t)batch * 2 * ne), sc(c, (size_t)batch * 2 * ns), t(c, (size_t)batch * 2 * level);
+        const size_t a_outer = (size_t)2 * n * N;
+        LAUNCH(c), k_ks_inner_pair<<<dim3(gx, ne, batch), 256, 0, c->st>>>(E.p, a->d, a->d + (size_t)n * N, a_outer, dt, rp, c->nprimes, pl, dv, c->pc, c->logn, N);
+        LimbMap sm{}; sm.n = ns; sm.prime[0] = (unsigned char)level; for (int k = 0; k < d.K; ++k) sm.prime[1 + k] = (unsigned char)(c->L + 1 + k);
+        ntt(c, E.p + (size_t)(n - 1) * N, (size_t)ne * N, sc.p, (size_t)ns * N, batch * 2 * ns, sm, true);
+        LAUNCH(c), k_div_conv<<<dim3(gx1, 1, batch * 2), 256, 0, c->st>>>(t.p, sc.p, dv, c->pc, N);
+        ntt_inplace(c, t.p, batch * 2 * level, c->qmap(level - 1), false);
+        LAUNCH(c), k_div_fin<<<dim3(gx, level, batch * 2), 256, 0, c->st>>>(r->d, E.p, t.p, ne, dv, c->pc, N);
+        CK(cudaGetLastError());
+    } catch (...) { hb_ct_free(r); throw; }
+    return r;
 }
 
 void check_same(const hb_ct *a, const hb_ct *b, const char *what) {
@@ -518,6 +594,8 @@ void hb_ctx_destroy(hb_ctx *c) {
     cudaSetDevice(c->device);
     if (c->st) cudaStreamSynchronize(c->st);
     for (auto &kv : c->plans) cudaFree(kv.second);
+    for (auto &kv : c->div_plans) cudaFree(kv.second);
+    if (c->pinned) cudaFreeHost(c->pinned);
     if (c->pc) cudaFree(c->pc);
     if (c->tw) cudaFree(c->tw);
     if (c->sk) cudaFree(c->sk);
@@ -598,6 +676,27 @@ int hb_encode(hb_ctx *c, const double *re, const double *im, size_t n, int level
         *out = p;
     });
 }
+int hb_encode_ext(hb_ctx *c, const double *re, const double *im, size_t n, int level, hb_pt **out) {
+    return guard(c, [&] {
+        if (!re || !out || n > (size_t)c->h->slots) fail(HB_E_ARG, "encode: bad message");
+        if (level < 0 || level > c->L) fail(HB_E_LEVEL, "encode: bad level");
+        std::vector<i64> coef;
+        c->h->encode_coeffs(re, im, n, c->h->scale[level], coef);
+        const int ne = level + 1 + c->K;
+        hb_pt *p = new hb_pt{c, level, 1, nullptr};
+        p->ext = 1;
+        try { p->d = c->alloc_limbs((size_t)ne); } catch (...) { delete p; throw; }
+        i64 *dc = (i64 *)c->pool.get((size_t)c->N * 8);
+        CK(cudaMemcpyAsync(dc, coef.data(), (size_t)c->N * 8, cudaMemcpyHostToDevice, c->st));
+        LimbMap em{}; em.n = ne;
+        for (int j = 0; j < ne; ++j) em.prime[j] = (unsigned char)(j <= level ? j : c->L + 1 + (j - level - 1));
+        LAUNCH(c), k_reduce_i64<<<c->egrid(ne), 256, 0, c->st>>>(p->d, dc, em, c->pc, c->N);
+        ntt_inplace(c, p->d, ne, em, false);
+        CK(cudaStreamSynchronize(c->st)); // coef goes out of scope
+        c->pool.put(dc);
+        *out = p;
+    });
+}
 static void decode_limbs(hb_ctx *c, const u64 *dev_coef, int level, int spow, double *re, double *im) {
     const int nl = level >= 1 ? 2 : 1, N = c->N;
     std::vector<u64> hc((size_t)nl * N);
@@ -638,6 +737,57 @@ int hb_encrypt(hb_ctx *c, const hb_pt *p, uint64_t nonce, hb_ct **out) {
         *out = r;
     });
 }
+// encode + encrypt `count` messages into one batched handle; member i is bit for bit hb_encrypt(hb_encode(message i), nonces[i])
+int hb_encrypt_many(hb_ctx *c, const double *re, const double *im, size_t n_slots, int count, int level, const uint64_t *nonces, hb_ct **out) {
+    return guard(c, [&] {
+        if (!c->have_sk) fail(HB_E_NOKEY, "secret key not generated");
+        if (!re || !nonces || !out || count < 1 || n_slots > (size_t)c->h->slots) fail(HB_E_ARG, "encrypt_many: bad message");
+        if (level < 0 || level > c->L) fail(HB_E_LEVEL, "encrypt_many: bad level");
+        const int n = level + 1, N = c->N;
+        const HostCtx &h = *c->h;
+        // host part, one member per task: inverse embedding + rounding, and the error polynomial
+        const size_t words = (size_t)count * 2 * N;
+        if (c->pinned_bytes < words * 8) {
+            if (c->pinned) CK(cudaFreeHost(c->pinned));
+            c->pinned = nullptr; c->pinned_bytes = 0;
+            CK(cudaMallocHost(&c->pinned, words * 8));
+            c->pinned_bytes = words * 8;
+        }
+        i64 *host = (i64 *)c->pinned; // [count][2][N]: message coefficients, error coefficients
+        const int workers = std::max(1, std::min({count, (int)std::thread::hardware_concurrency(), 32}));
+        std::vector<std::thread> pool;
+        for (int w = 0; w < workers; ++w)
+            pool.emplace_back([&, w] {
+                std::vector<i64> v;
+                for (int i = w; i < count; i += workers) {
+                    h.encode_coeffs(re + (size_t)i * n_slots, im ? im + (size_t)i * n_slots : nullptr, n_slots, h.scale[level], v);
+                    std::memcpy(host + (size_t)i * 2 * N, v.data(), (size_t)N * 8);
+                    h.sample_gauss(hbhost::STREAM_ENC_E, nonces[i], v);
+                    std::memcpy(host + ((size_t)i * 2 + 1) * N, v.data(), (size_t)N * 8);
+                }
+            });
+        for (auto &th : pool) th.join();
+        hb_ct *r = new_ct(c, level, 2, count, 1);
+        try {
+            const LimbMap qm = c->qmap(level);
+            i64 *dc = (i64 *)c->pool.get(words * 8);
+            Tmp me(c, (size_t)count * 2 * n); // [count][message | error][n][N]
+            CK(cudaMemcpyAsync(dc, host, words * 8, cudaMemcpyHostToDevice, c->st));
+            for (int i = 0; i < count * 2; ++i)
+                LAUNCH(c), k_reduce_i64<<<c->egrid(n), 256, 0, c->st>>>(me.p + (size_t)i * n * N, dc + (size_t)i * N, qm, c->pc, N);
+            ntt_inplace(c, me.p, count * 2 * n, qm, false);
+            for (int i = 0; i < count; ++i) {
+                u64 *b = r->d + (size_t)i * 2 * n * N, *a = b + (size_t)n * N;
+                LAUNCH(c), k_uniform<<<dim3((unsigned)((N / 4 + 255) / 256), n), 256, 0, c->st>>>(a, qm, c->pc, N, c->ckey, hbhost::STREAM_ENC_A, nonces[i]);
+                LAUNCH(c), k_encrypt<<<c->egrid(n), 256, 0, c->st>>>(b, a, me.p + ((size_t)i * 2 + 1) * n * N, c->sk, me.p + (size_t)i * 2 * n * N, qm, c->pc, N);
+            }
+            CK(cudaGetLastError());
+            CK(cudaStreamSynchronize(c->st)); // the staging buffer is reused by the next call
+            c->pool.put(dc);
+        } catch (...) { hb_ct_free(r); throw; }
+        *out = r;
+    });
+}
 int hb_decrypt(hb_ctx *c, const hb_ct *ct, int index, double *re, double *im) {
     return guard(c, [&] {
         if (!c->have_sk) fail(HB_E_NOKEY, "secret key not generated");
@@ -647,6 +797,63 @@ int hb_decrypt(hb_ctx *c, const hb_ct *ct, int index, double *re, double *im) {
         LAUNCH(c), k_decrypt<<<c->egrid(nl), 256, 0, c->st>>>(t.p, ct->d + (size_t)index * ct->np * n * N, n, ct->np, c->sk, c->pc, N);
         ntt_inplace(c, t.p, nl, c->qmap(nl - 1), true);
         decode_limbs(c, t.p, ct->level, ct->spow, re, im);
+    });
+}
+
+int hb_decrypt_many(hb_ctx *c, const hb_ct *const *cts, const int *index, int count, double *re, double *im) {
+    return guard(c, [&] {
+        if (!c->have_sk) fail(HB_E_NOKEY, "secret key not generated");
+        if (count < 1 || !cts || !re) fail(HB_E_ARG, "decrypt_many: nothing to decrypt");
+        const int N = c->N, slots = c->h->slots;
+        bool two = true;
+        for (int i = 0; i < count; ++i) {
+            const int idx = index ? index[i] : 0;
+            if (!cts[i] || idx < 0 || idx >= cts[i]->batch) fail(HB_E_ARG, "decrypt_many: bad batch index");
+            if (cts[i]->level < 1) two = false;
+        }
+        if (!two) { // a level-0 member has one limb only: take the members one by one
+            for (int i = 0; i < count; ++i) {
+                const hb_ct *ct = cts[i];
+                const int n = ct->level + 1, nl = ct->level >= 1 ? 2 : 1;
+                Tmp t(c, (size_t)nl);
+                LAUNCH(c), k_decrypt<<<c->egrid(nl), 256, 0, c->st>>>(t.p, ct->d + (size_t)(index ? index[i] : 0) * ct->np * n * N, n, ct->np, c->sk, c->pc, N);
+                ntt_inplace(c, t.p, nl, c->qmap(nl - 1), true);
+                decode_limbs(c, t.p, ct->level, ct->spow, re + (size_t)i * slots, im ? im + (size_t)i * slots : nullptr);
+            }
+            return;
+        }
+        const size_t bytes = (size_t)count * 2 * N * 8;
+        if (c->pinned_bytes < bytes) {
+            if (c->pinned) CK(cudaFreeHost(c->pinned));
+            c->pinned = nullptr; c->pinned_bytes = 0;
+            CK(cudaMallocHost(&c->pinned, bytes));
+            c->pinned_bytes = bytes;
+        }
+        Tmp t(c, (size_t)count * 2);
+        for (int i = 0; i < count; ++i) {
+            const hb_ct *ct = cts[i];
+            const int n = ct->level + 1;
+            LAUNCH(c), k_decrypt<<<c->egrid(2), 256, 0, c->st>>>(t.p + (size_t)i * 2 * N, ct->d + (size_t)(index ? index[i] : 0) * ct->np * n * N, n, ct->np, c->sk, c->pc, N);
+        }
+        ntt_inplace(c, t.p, count * 2, c->qmap(1), true);
+        CK(cudaMemcpyAsync(c->pinned, t.p, bytes, cudaMemcpyDeviceToHost, c->st));
+        CK(cudaStreamSynchronize(c->st));
+        // CRT lift and inverse embedding on the host cores, one member per task
+        const int workers = std::max(1, std::min({count, (int)std::thread::hardware_concurrency(), 32}));
+        std::vector<std::thread> pool;
+        const HostCtx &h = *c->h;
+        const u64 *host = c->pinned;
+        for (int w = 0; w < workers; ++w)
+            pool.emplace_back([&, w] {
+                std::vector<double> val;
+                for (int i = w; i < count; i += workers) {
+                    const hb_ct *ct = cts[i];
+                    h.centre(host + (size_t)i * 2 * N, host + ((size_t)i * 2 + 1) * N, val);
+                    const double sc = ct->spow == 2 ? h.scale[ct->level] * h.scale[ct->level] : h.scale[ct->level];
+                    h.decode_values(val, sc, re + (size_t)i * slots, im ? im + (size_t)i * slots : nullptr);
+                }
+            });
+        for (auto &th : pool) th.join();
     });
 }
 
@@ -828,6 +1035,22 @@ int hb_rotate_hoisted(hb_ctx *c, const hb_ct *a, const hb_digits *dg, int64_t st
             ks_apply(c, a->d + (size_t)n * N, (size_t)2 * n * N, dg->d, a->level, a->batch, key, (u32)g, r->d, (size_t)2 * n * N, a->d, nullptr, (size_t)2 * n * N);
         } catch (...) { hb_ct_free(r); throw; }
         *out = r;
+    });
+}
+int hb_assemble_hoisted(hb_ctx *c, const hb_ct *a, const hb_digits *dg, int64_t s1, const hb_pt *p1, int64_t s2, const hb_pt *p2, hb_ct **out) {
+    return guard(c, [&] {
+        if (a->np != 2 || dg->level != a->level || dg->batch != a->batch) fail(HB_E_SHAPE, "assemble_hoisted: digits do not belong to this ciphertext");
+        *out = do_assemble_rot(c, a, dg->d, s1, p1, s2, p2);
+    });
+}
+int hb_assemble_rot(hb_ctx *c, const hb_ct *a, int64_t s1, const hb_pt *p1, int64_t s2, const hb_pt *p2, hb_ct **out) {
+    return guard(c, [&] {
+        if (a->np != 2) fail(HB_E_SHAPE, "assemble_rot: needs 2 polys");
+        const PlanDims d = plan_dims(c, a->level);
+        const int n = a->level + 1, N = c->N;
+        Tmp dt(c, (size_t)a->batch * d.dt_count);
+        ks_decompose(c, a->d + (size_t)n * N, (size_t)2 * n * N, a->level, a->batch, dt.p);
+        *out = do_assemble_rot(c, a, dt.p, s1, p1, s2, p2);
     });
 }
 int hb_rotate(hb_ctx *c, const hb_ct *a, int64_t steps, hb_ct **out) { return guard(c, [&] { *out = do_galois(c, a, c->h->galois_rot(steps)); }); }

@@ -427,6 +427,148 @@ __global__ void k_moddown_fin(u64 *__restrict__ out, size_t out_outer, const u64
     }
 }
 
+// ---------------- masked pair of rotations with one division by P * q_level ----------------
+// Constants of the division of a Q_level u P polynomial by D = P * q_level (sources: q_level, p_1 .. p_K).
+struct DivPlan {
+    int level, ns;                     // ns = K + 1 source limbs
+    unsigned char src_prime[8];
+    u64 hat_inv[8], hat_inv_sh[8];     // (D / d_s)^-1 mod d_s
+    u64 hat_mod[8][kMaxPrimes];        // (D / d_s) mod q_i, i < level
+    u64 d_inv[kMaxPrimes];             // D^-1 mod q_i
+    u64 p_mod[kMaxPrimes];             // P mod q_j, j <= level
+};
+struct RotPair {                       // the two rotations of one call
+    const u64 *key[2];                 // switching keys
+    const u64 *mask[2];                // extended plaintexts [ne][N]
+    u32 g[2];
+};
+// E[b][p][j][i] = sum_r mask_r[j][i] * (sum_dg digit_dg[j][perm_r(i)] * key_r[dg][p][prime(j)][i])
+//               + (p == 0 and j < n)  P * sum_r mask_r[j][i] * c0[b][j][perm_r(i)]
+// Every term is reduced to its canonical residue before the next operation uses it.  grid = (N/(256*kElems), ne, batch)
+__global__ void k_ks_inner_pair(u64 *__restrict__ E, const u64 *__restrict__ c0, const u64 *__restrict__ a_ntt, size_t a_outer, const u64 *__restrict__ dt, RotPair rp,
+                                int key_primes, const KsPlan *__restrict__ pl, const DivPlan *__restrict__ dv, const PrimeConst *__restrict__ pc, int logn, int N) {
+    const int j = blockIdx.y, b = blockIdx.z;
+    const int pj = pl->ext_prime[j], nd = pl->nd, ne = pl->ne, n = pl->n;
+    const PrimeConst m = pc[pj];
+    const u32 x0 = blockIdx.x * (blockDim.x * kElems) + threadIdx.x;
+    const u64 *abase = a_ntt + (size_t)b * a_outer + (size_t)j * N;
+    const u64 *cbase = c0 + (size_t)b * a_outer + (size_t)j * N;
+    const u64 *dbase = dt + (size_t)b * pl->dt_count * N;
+    const size_t kpoly = (size_t)key_primes * N;
+    u64 e0[kElems], e1[kElems], f[kElems];
+#pragma unroll
+    for (int u = 0; u < kElems; ++u) { e0[u] = 0; e1[u] = 0; f[u] = 0; }
+    // When both steps are the same rotation (a row shift by a whole tile height on a full slot grid) the two inner
+    // products are the same polynomial: it is computed once and multiplied by mask_0 + mask_1, which gives the same
+    // residues as the two-term sum.
+    const int nrot = rp.g[0] == rp.g[1] ? 1 : 2;
+    for (int r = 0; r < nrot; ++r) {
+        u32 src[kElems];
+#pragma unroll
+        for (int u = 0; u < kElems; ++u) src[u] = ntt_perm(x0 + u * blockDim.x, rp.g[r], logn);
+        const u64 *kbase = rp.key[r] + (size_t)pj * N + x0;
+        u64 r0[kElems], r1[kElems];
+        if (m.fp) {
+#pragma unroll
+            for (int u = 0; u < kElems; ++u) { r0[u] = 0; r1[u] = 0; }
+            for (int dg = 0; dg < nd; ++dg) {
+                const int en = pl->dt_entry[dg][j];
+                const u64 *sp = en < 0 ? abase : dbase + (size_t)en * N;
+                const u64 *k0 = kbase + (size_t)dg * 2 * kpoly;
+#pragma unroll
+                for (int u = 0; u < kElems; ++u) {
+                    const u64 v = sp[src[u]], ka = k0[u * blockDim.x], kb = k0[kpoly + u * blockDim.x];
+                    const double vd = u52_to_double(v);
+                    r0[u] += mul_small_lazy_d(v, vd, ka, u52_to_double(ka), m.q_inv_f, m.q);
+                    r1[u] += mul_small_lazy_d(v, vd, kb, u52_to_double(kb), m.q_inv_f, m.q);
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < kElems; ++u) { r0[u] = reduce_fp(r0[u], m.q_inv_f, m.q); r1[u] = reduce_fp(r1[u], m.q_inv_f, m.q); }
+        } else {
+            Acc128 s0[kElems], s1[kElems];
+#pragma unroll
+            for (int u = 0; u < kElems; ++u) { s0[u].zero(); s1[u].zero(); }
+            for (int dg = 0; dg < nd; ++dg) {
+                const int en = pl->dt_entry[dg][j];
+                const u64 *sp = en < 0 ? abase : dbase + (size_t)en * N;
+                const u64 *k0 = kbase + (size_t)dg * 2 * kpoly;
+#pragma unroll
+                for (int u = 0; u < kElems; ++u) {
+                    const u64 v = sp[src[u]];
+                    s0[u].mad(v, k0[u * blockDim.x]);
+                    s1[u].mad(v, k0[kpoly + u * blockDim.x]);
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < kElems; ++u) { r0[u] = barrett128(s0[u].hi, s0[u].lo, m); r1[u] = barrett128(s1[u].hi, s1[u].lo, m); }
+        }
+        const u64 *mk = rp.mask[r] + (size_t)j * N + x0, *mk2 = rp.mask[1] + (size_t)j * N + x0;
+#pragma unroll
+        for (int u = 0; u < kElems; ++u) {
+            u64 w = mk[u * blockDim.x];
+            if (nrot == 1) w = add_mod(w, mk2[u * blockDim.x], m.q);
+            e0[u] = add_mod(e0[u], mul_mod_any(w, r0[u], m), m.q);
+            e1[u] = add_mod(e1[u], mul_mod_any(w, r1[u], m), m.q);
+            if (j < n) f[u] = add_mod(f[u], mul_mod_any(w, cbase[src[u]], m), m.q);
+        }
+    }
+    if (j < n) {
+        const u64 pm = dv->p_mod[j];
+#pragma unroll
+        for (int u = 0; u < kElems; ++u) e0[u] = add_mod(e0[u], mul_mod_any(pm, f[u], m), m.q);
+    }
+    u64 *o0 = E + (((size_t)b * 2) * ne + j) * N + x0, *o1 = o0 + (size_t)ne * N;
+#pragma unroll
+    for (int u = 0; u < kElems; ++u) { o0[u * blockDim.x] = e0[u]; o1[u * blockDim.x] = e1[u]; }
+}
+// Base conversion of the division: src [bp][ns][N] (limbs q_level, P; coefficient form) -> t [bp][level][N]
+// grid = (N/256, 1, nbp)
+template <int NS>
+__device__ __forceinline__ void div_conv_body(u64 *__restrict__ t, const u64 *__restrict__ src, const DivPlan *__restrict__ dv, const PrimeConst *__restrict__ pc, int N, int i, int bp) {
+    const int nl = dv->level;
+    u64 y[NS];
+#pragma unroll
+    for (int k = 0; k < NS; ++k) y[k] = mul_shoup(src[((size_t)bp * NS + k) * N + i], dv->hat_inv[k], dv->hat_inv_sh[k], pc[dv->src_prime[k]].q);
+    u64 *o = t + (size_t)bp * nl * N + i;
+    for (int l = 0; l < nl; ++l) {
+        Acc128 s; s.zero();
+#pragma unroll
+        for (int k = 0; k < NS; ++k) s.mad(y[k], dv->hat_mod[k][l]);
+        PrimeConst mm; mm.q = pc[l].q; mm.mu_hi = pc[l].mu_hi; mm.mu_lo = pc[l].mu_lo;
+        *o = barrett128(s.hi, s.lo, mm);
+        o += N;
+    }
+}
+__global__ void k_div_conv(u64 *__restrict__ t, const u64 *__restrict__ src, const DivPlan *__restrict__ dv, const PrimeConst *__restrict__ pc, int N) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= N) return;
+    const int bp = blockIdx.z;
+    switch (dv->ns) {
+    case 2: div_conv_body<2>(t, src, dv, pc, N, i, bp); break;
+    case 3: div_conv_body<3>(t, src, dv, pc, N, i, bp); break;
+    case 4: div_conv_body<4>(t, src, dv, pc, N, i, bp); break;
+    case 5: div_conv_body<5>(t, src, dv, pc, N, i, bp); break;
+    case 6: div_conv_body<6>(t, src, dv, pc, N, i, bp); break;
+    case 7: div_conv_body<7>(t, src, dv, pc, N, i, bp); break;
+    default: div_conv_body<8>(t, src, dv, pc, N, i, bp); break;
+    }
+}
+// out[bp][l][i] = (E[bp][l][i] - t[bp][l][i]) * D^-1 for l < level.  grid = (N/(256*kElems), level, batch*2)
+__global__ void k_div_fin(u64 *__restrict__ out, const u64 *__restrict__ E, const u64 *__restrict__ t, int ne, const DivPlan *__restrict__ dv,
+                          const PrimeConst *__restrict__ pc, int N) {
+    const int l = blockIdx.y, bp = blockIdx.z, nl = dv->level;
+    const PrimeConst m = pc[l];
+    const u64 dinv = dv->d_inv[l];
+#pragma unroll
+    for (int u_ = 0; u_ < kElems; ++u_) {
+        const int i = (blockIdx.x * kElems + u_) * blockDim.x + threadIdx.x;
+        if (i >= N) break;
+        const u64 v = sub_mod(E[((size_t)bp * ne + l) * N + i], t[((size_t)bp * nl + l) * N + i], m.q);
+        out[((size_t)bp * nl + l) * N + i] = mul_mod_any(v, dinv, m);
+    }
+}
+
 // ---------------- ChaCha20 ----------------
 __device__ __forceinline__ u32 rotl32(u32 v, int c) { return __funnelshift_l(v, v, c); }
 #define HB_QR(a, b, c, d)                                   \

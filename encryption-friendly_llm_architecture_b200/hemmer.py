@@ -72,7 +72,8 @@ class Hemmer:
         return getattr(self.dll, self.prefix + name)
 
     def set_schedule(self, mode: int):
-        """0: the reference's rotation sequence (default); 1: direct rotations of the transformed operand, hoisted."""
+        """0: the reference's rotation sequence (default); 1: direct rotations of the transformed operand, hoisted;
+        2: as 1, with each wrapped copy of the shift loops made by one assemble_rot (one division by P * q_level)."""
         self.lib._chk(self._fn("set_schedule")(self.h, C.c_int(mode)))
         self.schedule = mode
 
@@ -121,6 +122,12 @@ class Hemmer:
     def encrypt2(self, d1, d2, nonce=None):
         pt = self.encode2(d1, d2)
         return CtxtTensor(self.lib.encrypt(pt.ct, self.next_nonce() if nonce is None else nonce), pt.rows, pt.cols, pt.width)
+
+    def encrypt2_many(self, pairs, nonces):
+        """encrypt2 for a list of (left, right) tile pairs: one batched CtxtTensor, member i = encrypt2(*pairs[i], nonces[i])."""
+        msgs = np.stack([layout2(a, b, self.lib.slots).real for a, b in pairs])
+        d = pairs[0][0].shape
+        return CtxtTensor(self.lib.encrypt_many(msgs, self.lib.L, nonces), d[0], d[1], 2 * d[1])
 
     def decrypt(self, t):
         z = self.lib.decrypt(t.ct)

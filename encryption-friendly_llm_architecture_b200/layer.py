@@ -12,6 +12,8 @@ two-tile ct x ct product); rank r of R executes units r, r+R, ... so the same co
 """
 from __future__ import annotations
 
+import time
+
 import numpy as np
 
 from .hemmer import CtxtTensor, Hemmer
@@ -65,6 +67,7 @@ class LayerWorkload:
         self.units = self._build_units()
         self.mine = [u for i, u in enumerate(self.units) if i % world == rank]
         self.h2d_bytes = 0
+        self.phases_ms = {}
         self.d2h_bytes = 0
         self._weights = {}
         self.resident = None
@@ -143,10 +146,10 @@ class LayerWorkload:
 
     # ---- host -> device ----
     def _encrypt_all(self, nonce0):
-        """Encode + encrypt every operand of this rank's units and group them into batches."""
+        """Encode + encrypt every operand of this rank's units, one batched call per group of operands."""
         H, lib = self.H, self.lib
         per_ct = 2 * lib.N * 8  # rounded message coefficients + error polynomial uploaded per encryption
-        groups = {"full": [], "half": []}      # pcmm: (unit, [cts])
+        groups = {"full": [], "half": []}      # pcmm: (unit, [(pair, nonce)])
         ccmm = {False: [], True: [], "left": []}
         n = nonce0
         for u in self.mine:
@@ -154,27 +157,27 @@ class LayerWorkload:
                 _, name, xname, weights, g, kt, nt = u
                 x = self.data[xname]
                 pair = lambda p: (tiles(x, 0, 2 * p), tiles(x, 0, 2 * p + 1))
-                cts = [H.encrypt2(*pair(2 * g), nonce=n)]
+                ops = [(pair(2 * g), n)]
                 if 4 * g + 2 < kt:
-                    cts.append(H.encrypt2(*pair(2 * g + 1), nonce=n + 1))
-                self.h2d_bytes += per_ct * len(cts)
+                    ops.append((pair(2 * g + 1), n + 1))
+                self.h2d_bytes += per_ct * len(ops)
                 for wname in weights:
                     self._weight_pts(wname, g, kt, nt)
-                groups["full" if len(cts) == 2 else "half"].append((u, cts))
+                groups["full" if len(ops) == 2 else "half"].append((u, ops))
             else:
                 _, name, lhs, rhs, tr = u
-                a, b = self._pair(lhs), self._pair(rhs)
                 self.h2d_bytes += 2 * per_ct
-                ccmm[tr].append((u, H.encrypt2(*a, nonce=n), H.encrypt2(*b, nonce=n + 1)))
+                ccmm[tr].append((u, (self._pair(lhs), n), (self._pair(rhs), n + 1)))
             n += 2
+        many = lambda ops: H.encrypt2_many([p for p, _ in ops], [k for _, k in ops])
         res = {"pcmm": {}, "ccmm": {}}
         for kind, lst in groups.items():
             if lst:
-                res["pcmm"][kind] = ([u for u, _ in lst], self._batch([c[0] for _, c in lst]),
-                                     self._batch([c[1] for _, c in lst]) if kind == "full" else None)
+                res["pcmm"][kind] = ([u for u, _ in lst], many([o[0] for _, o in lst]),
+                                     many([o[1] for _, o in lst]) if kind == "full" else None)
         for tr, lst in ccmm.items():
             if lst:
-                res["ccmm"][tr] = ([u for u, _, _ in lst], self._batch([a for _, a, _ in lst]), self._batch([b for _, _, b in lst]))
+                res["ccmm"][tr] = ([u for u, _, _ in lst], many([a for _, a, _ in lst]), many([b for _, _, b in lst]))
         return res
 
     # ---- device work ----
@@ -258,27 +261,37 @@ class LayerWorkload:
         return np.stack([a0 @ b0, a1 @ b1])
 
     def _decrypt_all(self, out, check=False):
-        """Decrypt every result to host matrices; returns the max-abs error when `check`."""
+        """Decrypt every result to host matrices (one batched call); returns the max-abs error when `check`."""
         err = 0.0
         per = 2 * self.lib.N * 8
-        complete = True
+        items, tags = [], []
         for k, ((name, wname, j), ct) in enumerate(out["pcmm"].items()):
             if k % self.world != self.rank:
                 continue   # after the exchange every rank holds every output tile; each one is read back by one rank
-            z = self.lib.decrypt(ct.ct).reshape(D, 2 * D)
-            self.d2h_bytes += per
-            got = 2 * (z[:, :D].real + z[:, D:].real)
-            if check and complete:
-                spec = [p for p in self.PCMM if p[0] == name][0]
-                x, w = self.data[spec[1]], self.data[wname]
-                err = max(err, float(np.abs(got - x[:, : spec[3] * D] @ w[: spec[3] * D, j * D:(j + 1) * D]).max()))
+            items.append((ct.ct, 0)); tags.append(("p", name, wname, j))
         for tr, (us, c) in out["ccmm"].items():
             for k, u in enumerate(us):
-                z = self.lib.decrypt(c.ct, k)[: D * 2 * D].real.reshape(D, 2 * D)
-                self.d2h_bytes += per
+                items.append((c.ct, k)); tags.append(("c", u))
+        if not items:
+            return err
+        zs = self.lib.decrypt_many(items)
+        self.d2h_bytes += per * len(items)
+        self.results = []
+        for tag, z in zip(tags, zs):
+            z = z[: D * 2 * D].reshape(D, 2 * D)
+            if tag[0] == "p":
+                got = 2 * (z[:, :D].real + z[:, D:].real)
+                self.results.append(got)
                 if check:
-                    exp = self._expected_ccmm(u)
-                    err = max(err, float(np.abs(z[:, :D] - exp[0]).max()), float(np.abs(z[:, D:] - exp[1]).max()))
+                    _, name, wname, j = tag
+                    spec = [p for p in self.PCMM if p[0] == name][0]
+                    x, w = self.data[spec[1]], self.data[wname]
+                    err = max(err, float(np.abs(got - x[:, : spec[3] * D] @ w[: spec[3] * D, j * D:(j + 1) * D]).max()))
+            else:
+                self.results.append(z.real)
+                if check:
+                    exp = self._expected_ccmm(tag[1])
+                    err = max(err, float(np.abs(z[:, :D].real - exp[0]).max()), float(np.abs(z[:, D:].real - exp[1]).max()))
         return err
 
     # ---- public steps ----
@@ -293,9 +306,18 @@ class LayerWorkload:
         return self._compute(self._encrypt_all(10_000))
 
     def step_e2e(self):
-        """Host matrices in, decrypted host matrices out."""
-        out = self._compute(self._encrypt_all(30_000))
+        """Host matrices in, decrypted host matrices out.  `phases_ms` accumulates the host-clock time of the three parts."""
+        t0 = time.perf_counter()
+        enc = self._encrypt_all(30_000)
+        self.lib.sync()
+        t1 = time.perf_counter()
+        out = self._compute(enc)
+        self.lib.sync()
+        t2 = time.perf_counter()
         self._decrypt_all(out)
+        t3 = time.perf_counter()
+        for k, v in (("encode_encrypt", t1 - t0), ("compute", t2 - t1), ("decrypt_decode", t3 - t2)):
+            self.phases_ms[k] = self.phases_ms.get(k, 0.0) + 1e3 * v
         return out
 
     def check(self):

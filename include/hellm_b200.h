@@ -34,8 +34,9 @@ void hb_hemmer_destroy(hb_hemmer *h);
 /* message of the last failure raised above the primitive layer (thread-local) */
 const char *hb_hemmer_last_error(void);
 /* 0: the reference's rotation sequence, each shifted copy rotated from the previous one (default);
- * 1: every shifted copy is one rotation of the transformed operand, sharing its decomposition.
- * The two give the same slots and different ciphertext bits; no counterpart in the reference. */
+ * 1: every shifted copy is one rotation of the transformed operand, sharing its decomposition;
+ * 2: as 1, and each wrapped copy (two rotations, two masks, add, rescale) is one hb_assemble_hoisted.
+ * All give the same slots and different ciphertext bits; no counterpart in the reference. */
 int hb_hemmer_set_schedule(hb_hemmer *h, int mode);
 
 /* HEMMer::transposeInplace (HEMMer.hpp:129; HEMMer.cpp:1166-1172; MatrixUtils.cpp:671-739) */

@@ -83,10 +83,23 @@ uint64_t hb_galois_for_rotation(const hb_ctx *ctx, int64_t left_steps);
 /* EnDecoder::encode / decode -- EnDecoder.hpp:51,66.  im may be NULL (real message). */
 int hb_encode(hb_ctx *ctx, const double *re, const double *im, size_t n_slots, int level, hb_pt **out);
 int hb_decode(hb_ctx *ctx, const hb_pt *pt, double *re, double *im);
+/* hb_encode with K further limbs modulo the special primes after the level + 1 usual ones: the plaintext operand of
+ * hb_assemble_rot.  Usable wherever a plaintext of that level is.  No counterpart in the reference. */
+int hb_encode_ext(hb_ctx *ctx, const double *re, const double *im, size_t n_slots, int level, hb_pt **out);
 /* Encryptor::encrypt(ptxt, sk, ctxt) -- Encryptor.hpp:84; `nonce` selects the random streams */
 int hb_encrypt(hb_ctx *ctx, const hb_pt *pt, uint64_t nonce, hb_ct **out);
+/* encode + encrypt `count` messages (message i at re + i * n_slots, im likewise or NULL) into ONE handle of batch
+ * `count`: the inverse embeddings and error polynomials are made on the host cores in parallel, uploaded in one
+ * copy, and the device part runs over the whole batch.  Member i is bit for bit hb_encrypt(hb_encode(message i,
+ * level), nonces[i]). */
+int hb_encrypt_many(hb_ctx *ctx, const double *re, const double *im, size_t n_slots, int count, int level, const uint64_t *nonces,
+                    hb_ct **out);
 /* Decryptor::decrypt -- Decryptor.hpp:36; decrypts entry `index` of the batch */
 int hb_decrypt(hb_ctx *ctx, const hb_ct *ct, int index, double *re, double *im);
+/* the same for `count` ciphertexts at once (member index[i] of batch handle cts[i]; index may be NULL for all zero):
+ * one device pass and one copy for all, the CRT lift and the inverse embedding spread over the host cores.
+ * re / im receive count * slots doubles; each member's values are exactly those hb_decrypt gives. */
+int hb_decrypt_many(hb_ctx *ctx, const hb_ct *const *cts, const int *index, int count, double *re, double *im);
 
 /* Ciphertext construction / metadata / raw residues -- Ciphertext.hpp:83-131 */
 int hb_ct_create(hb_ctx *ctx, int level, int n_poly, int batch, int scale_pow, hb_ct **out);
@@ -140,6 +153,17 @@ int hb_conjugate(hb_ctx *ctx, const hb_ct *a, hb_ct **out);                     
 int hb_decompose(hb_ctx *ctx, const hb_ct *a, hb_digits **out);
 int hb_rotate_hoisted(hb_ctx *ctx, const hb_ct *a, const hb_digits *digits, int64_t left_steps, hb_ct **out);
 void hb_digits_free(hb_digits *digits);
+/* The masked pair of rotations that makes one wrapped copy in the shift loops (MatrixUtils.cpp:1416-1427:
+ * two leftRotate, two multWithoutRescale, add, rescale) as one operation:
+ *     out = p1 (.) rot(a, s1) + p2 (.) rot(a, s2),   at level(a) - 1.
+ * Both key-switch inner products stay in the extended basis Q_level u P, are multiplied there by the extended
+ * plaintexts (hb_encode_ext) and summed, and the sum is divided once by P * q_level -- instead of a ModDown per
+ * rotation and a rescale of the sum.  Same slots as the unfused sequence, different ciphertext bits (one rounding
+ * instead of three); the CPU oracle implements the same arithmetic (Evaluator::assemble_rot).  s1, s2 must be
+ * non-zero rotations.  hb_assemble_hoisted takes the digits of `a` from hb_decompose.  No counterpart in HEaaN. */
+int hb_assemble_rot(hb_ctx *ctx, const hb_ct *a, int64_t s1, const hb_pt *p1, int64_t s2, const hb_pt *p2, hb_ct **out);
+int hb_assemble_hoisted(hb_ctx *ctx, const hb_ct *a, const hb_digits *digits, int64_t s1, const hb_pt *p1, int64_t s2, const hb_pt *p2,
+                        hb_ct **out);
 /* raw forward / inverse NTT of every limb of the batch, in place (primitive sweep) */
 int hb_ntt(hb_ctx *ctx, hb_ct *a, int inverse);
 

@@ -461,7 +461,8 @@ struct Ct {
 };
 struct Pt {
     int level = -1, spow = 1, N = 0;
-    std::vector<u64> d; // [level+1][N] NTT form
+    bool ext = false;   // K more limbs follow, modulo the special primes (operand of assemble_rot)
+    std::vector<u64> d; // [level+1 (+K)][N] NTT form
     u64 *limb(int l) { return d.data() + (size_t)l * N; }
     const u64 *limb(int l) const { return d.data() + (size_t)l * N; }
 };
@@ -510,6 +511,32 @@ struct Evaluator {
             u64 *p = pt.limb(l);
             for (int c = 0; c < cx.N; ++c) p[c] = cx.mod[l].from_i64(coef[c]);
             cx.ntt(p, l);
+        }
+        return pt;
+    }
+    // The same plaintext with K further limbs modulo the special primes, so that it can multiply a key-switch
+    // result that is still in the basis Q_level u P.  The first level+1 limbs are those of encode().
+    Pt encode_ext(const cplx *z, size_t n, int level) const {
+        if ((int)n > cx.slots) throw std::invalid_argument("encode: too many slots");
+        if (level < 0 || level > cx.L) throw std::invalid_argument("encode: bad level");
+        if (dry) { ++const_cast<Evaluator *>(this)->stats[{"encode", level}]; Pt e; e.level = level; e.N = cx.N; e.ext = true; return e; }
+        std::vector<cplx> v(cx.slots, cplx(0, 0));
+        for (size_t i = 0; i < n; ++i) v[i] = z[i];
+        cx.fft_special_inv(v);
+        const double sc = cx.scale[level];
+        std::vector<i64> coef(cx.N);
+        for (int i = 0; i < cx.slots; ++i) {
+            coef[i] = (i64)std::rint(v[i].real() * sc);
+            coef[i + cx.slots] = (i64)std::rint(v[i].imag() * sc);
+        }
+        const int ne = level + 1 + cx.K;
+        Pt pt; pt.level = level; pt.N = cx.N; pt.ext = true; pt.d.resize((size_t)ne * cx.N);
+#pragma omp parallel for
+        for (int j = 0; j < ne; ++j) {
+            const int pi = cx.prime_index_ext(level, j);
+            u64 *p = pt.limb(j);
+            for (int c = 0; c < cx.N; ++c) p[c] = cx.mod[pi].from_i64(coef[c]);
+            cx.ntt(p, pi);
         }
         return pt;
     }
@@ -741,6 +768,37 @@ struct Evaluator {
         }
     }
 
+    // Steps 1-2 of keyswitch on their own: the digits of `a` lifted to Q_level u P, NTT form, [digit][ext limb][N].
+    std::vector<u64> lifted_digits(const u64 *a, int level) {
+        const int N = cx.N, n = level + 1, ne = n + cx.K, nd = cx.num_digits(level);
+        std::vector<u64> ac((size_t)n * N), out((size_t)nd * ne * N);
+#pragma omp parallel for
+        for (int l = 0; l < n; ++l) { std::memcpy(&ac[(size_t)l * N], a + (size_t)l * N, N * 8); cx.intt(&ac[(size_t)l * N], l); }
+        for (int dg = 0; dg < nd; ++dg) {
+            const int lo = cx.digit_lo(dg), hi = cx.digit_hi(dg, n);
+            std::vector<int> src; for (int l = lo; l < hi; ++l) src.push_back(l);
+            BConv bc = make_bconv(src);
+            const size_t ns = src.size();
+            std::vector<u64> y(ns * N);
+            for (size_t i = 0; i < ns; ++i)
+                for (int c = 0; c < N; ++c) y[i * N + c] = Mod::mul_shoup(ac[(size_t)src[i] * N + c], bc.hat_inv[i], bc.hat_inv_sh[i], cx.mod[src[i]].q);
+#pragma omp parallel for
+            for (int j = 0; j < ne; ++j) {
+                const int pi = cx.prime_index_ext(level, j);
+                const Mod &m = cx.mod[pi];
+                u64 *d = &out[((size_t)dg * ne + j) * N];
+                if (pi >= lo && pi < hi) { std::memcpy(d, a + (size_t)pi * N, N * 8); continue; }
+                for (int c = 0; c < N; ++c) {
+                    u128 s = 0;
+                    for (size_t i = 0; i < ns; ++i) s += (u128)y[i * N + c] * bc.hat_mod[pi][i];
+                    d[c] = m.red128(s);
+                }
+                cx.ntt(d, pi);
+            }
+        }
+        return out;
+    }
+
     // ----- homomorphic primitives -----
     static void require(bool c, const char *msg) { if (!c) throw std::invalid_argument(msg); }
 
@@ -935,6 +993,90 @@ struct Evaluator {
             }
         }
         return r;
+    }
+    // The masked sum of two rotations of one ciphertext, rescaled:
+    //     p1 (.) rot(x, s1) + p2 (.) rot(x, s2)   ->   level - 1
+    // computed with the two key-switch inner products left in the basis Q_level u P, multiplied there by the
+    // (extended) plaintexts and summed, and ONE division by D = P * q_level for the sum instead of a ModDown per
+    // rotation and a rescale afterwards:
+    //   E_p = sum_r p_r (.) (sum_dg perm_r(digit_dg) (.) key_r,dg,p)            over Q_level u P,  p = 0, 1
+    //   E_0 += P * sum_r p_r (.) perm_r(c0)                                      on the Q limbs
+    //   out_p = (E_p - lift_{D -> Q_{level-1}}(iNTT(E_p | {q_level, P}))) * D^-1  on limbs 0 .. level-1
+    // Same slots as rescale(p1 (.) rot + p2 (.) rot); the ciphertext bits differ (one rounding instead of three).
+    Ct assemble_rot(const Ct &x, i64 s1, const Pt &p1, i64 s2, const Pt &p2) {
+        require(x.np == 2 && x.spow == 1, "assemble_rot: needs a rescaled 2-poly ciphertext");
+        require(x.level >= 1, "assemble_rot: level 0");
+        require(p1.ext && p2.ext && p1.level == x.level && p2.level == x.level && p1.spow == 1 && p2.spow == 1, "assemble_rot: plaintexts must be extended and at the ciphertext's level");
+        const u64 g[2] = {cx.galois_for_rotation(s1), cx.galois_for_rotation(s2)};
+        require(g[0] != 1 && g[1] != 1, "assemble_rot: zero rotation");
+        if (count("assemble_rot", x.level, x.batch)) return meta(x.level - 1, 2, x.batch, 1);
+        const Pt *pp[2] = {&p1, &p2};
+        const Evk *key[2]; const std::vector<u32> *perm[2];
+        for (int r = 0; r < 2; ++r) {
+            auto it = gal_keys.find(g[r]);
+            if (it == gal_keys.end()) throw std::runtime_error("missing galois key");
+            key[r] = &it->second; perm[r] = &cx.ntt_perm(g[r]);
+        }
+        const int N = cx.N, level = x.level, n = level + 1, K = cx.K, ne = n + K, nd = cx.num_digits(level);
+        std::vector<int> src; src.push_back(level); for (int j = 0; j < K; ++j) src.push_back(cx.L + 1 + j);
+        const BConv bc = make_bconv(src);
+        const int ns = K + 1;
+        Ct out(N, level - 1, 2, x.batch, 1);
+        for (int b = 0; b < x.batch; ++b) {
+            const std::vector<u64> dg = lifted_digits(x.limb(b, 1, 0), level);
+            std::vector<u64> E((size_t)2 * ne * N, 0);
+#pragma omp parallel for
+            for (int j = 0; j < ne; ++j) {
+                const int pi = cx.prime_index_ext(level, j);
+                const Mod &m = cx.mod[pi];
+                u64 *e0 = &E[(size_t)j * N], *e1 = &E[((size_t)ne + j) * N];
+                u64 pmod = 1;
+                for (int t = 0; t < K; ++t) pmod = m.mul(pmod, cx.mod[cx.L + 1 + t].q % m.q);
+                for (int c = 0; c < N; ++c) {
+                    u64 f = 0;
+                    for (int r = 0; r < 2; ++r) {
+                        const u32 sc = (*perm[r])[c];
+                        u64 i0 = 0, i1 = 0;
+                        for (int d = 0; d < nd; ++d) {
+                            const u64 v = dg[((size_t)d * ne + j) * N + sc];
+                            i0 = m.add(i0, m.mul(v, key[r]->limb(d, 0, pi)[c]));
+                            i1 = m.add(i1, m.mul(v, key[r]->limb(d, 1, pi)[c]));
+                        }
+                        const u64 mk = pp[r]->limb(j)[c];
+                        e0[c] = m.add(e0[c], m.mul(mk, i0));
+                        e1[c] = m.add(e1[c], m.mul(mk, i1));
+                        if (j < n) f = m.add(f, m.mul(mk, x.limb(b, 0, j)[sc]));
+                    }
+                    if (j < n) e0[c] = m.add(e0[c], m.mul(pmod, f));
+                }
+            }
+            for (int p = 0; p < 2; ++p) {
+                std::vector<u64> y((size_t)ns * N);
+#pragma omp parallel for
+                for (int s = 0; s < ns; ++s) {
+                    u64 *pl = &E[((size_t)p * ne + (n - 1 + s)) * N];
+                    cx.intt(pl, src[s]);
+                    for (int c = 0; c < N; ++c) y[(size_t)s * N + c] = Mod::mul_shoup(pl[c], bc.hat_inv[s], bc.hat_inv_sh[s], cx.mod[src[s]].q);
+                }
+#pragma omp parallel for
+                for (int i = 0; i < level; ++i) {
+                    const Mod &m = cx.mod[i];
+                    u64 dinv = 1;
+                    for (int s = 0; s < ns; ++s) dinv = m.mul(dinv, cx.mod[src[s]].q % m.q);
+                    dinv = m.inv(dinv);
+                    std::vector<u64> t(N);
+                    for (int c = 0; c < N; ++c) {
+                        u128 acc = 0;
+                        for (int s = 0; s < ns; ++s) acc += (u128)y[(size_t)s * N + c] * bc.hat_mod[i][s];
+                        t[c] = m.red128(acc);
+                    }
+                    cx.ntt(t.data(), i);
+                    const u64 *e = &E[((size_t)p * ne + i) * N]; u64 *o = out.limb(b, p, i);
+                    for (int c = 0; c < N; ++c) o[c] = m.mul(m.sub(e[c], t[c]), dinv);
+                }
+            }
+        }
+        return out;
     }
     // HomEvaluator::leftRotate / rightRotate (HomEvaluator.hpp:383, 403): slot p+t moves to slot p
     Ct rotate(const Ct &x, i64 left_steps) { return apply_galois(x, cx.galois_for_rotation(left_steps)); }

@@ -55,6 +55,8 @@ struct Hemmer {
     // 1: "direct" variant -- every shifted copy is one rotation of the transformed operand itself, rot(x, k).
     //    Same slots, different ciphertext bits (fewer chained key switches).  The CUDA library implements the
     //    same variant with hoisting; both variants are compared bit for bit.
+    // 2: as 1, and the masked pair of rotations that makes a wrapped copy is one Evaluator::assemble_rot (one
+    //    division by P * q_level for the pair) in the product loop and in multMatMatPre.
     int mode = 0;
 
     Hemmer(Context &c, Evaluator &e) : cx(c), ev(e), slots(c.slots) {
@@ -250,7 +252,9 @@ struct Hemmer {
         }
         return mp;
     }
-    // generateRowMask -- MatrixUtils.cpp:529-552 (plaintexts at target_level, two per shift)
+    // generateRowMask -- MatrixUtils.cpp:529-552 (plaintexts at target_level, two per shift).  The wrap masks carry
+    // the extra limbs of encode_ext so that schedule 2 can use them; their first target_level + 1 limbs are those
+    // of encode().
     std::vector<Pt> &get_row_mask(const Shape &s, int target_level) {
         auto &v = row_mask_[{target_level, s}];
         if (!v.empty()) return v;
@@ -258,8 +262,8 @@ struct Hemmer {
             Message msg((size_t)slots, cplx(1, 0)), rev((size_t)slots, cplx(0, 0));
             for (i64 j = 0; j < slots; j++)
                 if ((j / s.width) % s.rows < s.rows - i) { msg[(size_t)j] = 0; rev[(size_t)j] = 1; }
-            v.push_back(ev.encode(msg.data(), msg.size(), target_level));
-            v.push_back(ev.encode(rev.data(), rev.size(), target_level));
+            v.push_back(ev.encode_ext(msg.data(), msg.size(), target_level));
+            v.push_back(ev.encode_ext(rev.data(), rev.size(), target_level));
         }
         return v;
     }
@@ -271,8 +275,8 @@ struct Hemmer {
             Message msg((size_t)slots, cplx(1, 0)), rev((size_t)slots, cplx(0, 0));
             for (i64 j = 0; j < slots; j++)
                 if (j % s.cols < s.cols - i) { msg[(size_t)j] = 0; rev[(size_t)j] = 1; }
-            v.push_back(ev.encode(msg.data(), msg.size(), target_level));
-            v.push_back(ev.encode(rev.data(), rev.size(), target_level));
+            v.push_back(ev.encode_ext(msg.data(), msg.size(), target_level));
+            v.push_back(ev.encode_ext(rev.data(), rev.size(), target_level));
         }
         return v;
     }
@@ -288,7 +292,7 @@ struct Hemmer {
         const i64 gs = (i64)std::ceil((double)(num_rows + num_cols - 1) / (double)bs);
         const i64 gap = width - 1;
         std::vector<Ct> bs_rot((size_t)bs);
-        if (mode == 1) {
+        if (mode >= 1) {
             for (i64 j = 0; j < bs; j++) bs_rot[(size_t)j] = rotL(op.ct, (j - (num_rows - 1)) * gap);
         } else {
             bs_rot[0] = rotR(op.ct, (num_rows - 1) * gap);
@@ -317,7 +321,7 @@ struct Hemmer {
         const i64 bs = (i64)std::ceil(std::sqrt((double)(2 * sub_dim - 1)));
         const i64 gs = (i64)std::ceil((double)(sub_dim - 1) / (double)bs);
         std::vector<Ct> bs_rot((size_t)bs);
-        if (mode == 1) {
+        if (mode >= 1) {
             for (i64 j = 0; j < bs; j++) bs_rot[(size_t)j] = rotL(op, (j + 1) * gap);
         } else {
             bs_rot[0] = rotL(op, gap);
@@ -402,7 +406,15 @@ struct Hemmer {
         const i64 num_cols_tmp = (num_k > num_cols) ? num_k : pow2_ceil(num_cols);
         Ct res = ev.mul(a, b);
         Ct itxt_res;
-        if (mode == 1) {
+        if (mode == 2) {
+            for (i64 i = 1; i < num_k; i++) {
+                ev.gen_rot_key(i); ev.gen_rot_key(i - num_cols_tmp); ev.gen_rot_key(i * width); ev.gen_rot_key((i - num_rows_tmp) * width);
+                Ct tmp1 = ev.assemble_rot(a, i, col_mask[(size_t)(2 * i + 1)], i - num_cols_tmp, col_mask[(size_t)(2 * i)]);
+                Ct tmp2 = ev.assemble_rot(b, i * width, row_mask[(size_t)(2 * i + 1)], (i - num_rows_tmp) * width, row_mask[(size_t)(2 * i)]);
+                Ct t = ev.tensor(tmp1, tmp2);
+                itxt_res = (i == 1) ? t : ev.add(itxt_res, t);
+            }
+        } else if (mode >= 1) {
             for (i64 i = 1; i < num_k; i++) {
                 Ct tmp1 = assemble(rotL(a, i), col_mask[(size_t)(2 * i + 1)], rotL(a, i - num_cols_tmp), col_mask[(size_t)(2 * i)]);
                 Ct tmp2 = assemble(rotL(b, i * width), row_mask[(size_t)(2 * i + 1)], rotL(b, (i - num_rows_tmp) * width), row_mask[(size_t)(2 * i)]);
@@ -453,7 +465,7 @@ struct Hemmer {
         const i64 num_cols_tmp = (num_k > num_cols) ? num_k : pow2_ceil(num_cols);
         Ct res = ev.mul(a.ct, b.ct);
         Ct itxt_res;
-        if (mode == 1) {
+        if (mode >= 1) {
             for (i64 i = 1; i < num_k / 2; i++) {
                 Ct tmp1 = assemble(rotL(a.ct, 2 * i), col_mask[(size_t)(4 * i + 1)], rotL(a.ct, 2 * i - num_cols_tmp), col_mask[(size_t)(4 * i)]);
                 Ct t = ev.tensor(tmp1, rotL(b.ct, 2 * i * width));
@@ -489,7 +501,7 @@ struct Hemmer {
         Ct a = a_in.ct;
         tmp.push_back(ev.level_down(a, a.level - 1));
         auto &col_mask = get_col_mask(a_in.sh, target_level + 2);
-        if (mode == 1) {
+        if (mode >= 1) {
             for (i64 i = 1; i < num_rows / 2; i++)
                 tmp.push_back(assemble(rotL(a_in.ct, 2 * i), col_mask[(size_t)(4 * i + 1)], rotL(a_in.ct, 2 * i - num_rows), col_mask[(size_t)(4 * i)]));
             return stack(tmp);
@@ -513,7 +525,7 @@ struct Hemmer {
         Ct b = b_in.ct;
         Ct sum = ev.tensor(slice(pre, 0), b);
         for (int i = 1; i < pre.batch; ++i) {
-            b = mode == 1 ? rotL(b_in.ct, (i64)i * 2 * width) : rotL(b, 2 * width);
+            b = mode >= 1 ? rotL(b_in.ct, (i64)i * 2 * width) : rotL(b, 2 * width);
             sum = ev.add(sum, ev.tensor(slice(pre, i), b));
         }
         return CtT{ev.rescale(ev.relin(sum)), Shape(b_in.sh.rows, b_in.sh.cols, width)};
@@ -528,7 +540,14 @@ struct Hemmer {
         std::vector<Ct> tmp;
         tmp.push_back(ev.level_down(a.ct, a.ct.level - 1));
         auto &col_mask = get_col_mask(a.sh, target_level + 2);
-        if (mode == 1) {
+        if (mode == 2) {
+            for (i64 i = 1; i < num_rows; i++) {
+                ev.gen_rot_key(i); ev.gen_rot_key(i - num_rows);
+                tmp.push_back(ev.assemble_rot(a.ct, i, col_mask[(size_t)(2 * i + 1)], i - num_rows, col_mask[(size_t)(2 * i)]));
+            }
+            return stack(tmp);
+        }
+        if (mode >= 1) {
             for (i64 i = 1; i < num_rows; i++)
                 tmp.push_back(assemble(rotL(a.ct, i), col_mask[(size_t)(2 * i + 1)], rotL(a.ct, i - num_rows), col_mask[(size_t)(2 * i)]));
             return stack(tmp);
@@ -565,7 +584,7 @@ struct Hemmer {
         Ct b = b_in.ct;
         Ct sum = ev.tensor(slice(pre, 0), b);
         for (int i = 1; i < pre.batch; ++i) {
-            b = mode == 1 ? rotL(b_in.ct, (i64)i * width) : rotL(b, width);
+            b = mode >= 1 ? rotL(b_in.ct, (i64)i * width) : rotL(b, width);
             sum = ev.add(sum, ev.tensor(slice(pre, i), b));
         }
         return CtT{ev.relin(sum), Shape(b_in.sh.rows, b_in.sh.cols, width)};

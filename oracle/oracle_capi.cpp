@@ -62,6 +62,13 @@ int orc_encode(orc_ctx *c, const double *re, const double *im, size_t n, int lev
         *out = new Pt(c->ev.encode(z.data(), n, level));
     })
 }
+int orc_encode_ext(orc_ctx *c, const double *re, const double *im, size_t n, int level, orc_pt **out) {
+    ORC_TRY(c, {
+        std::vector<cplx> z(n);
+        for (size_t i = 0; i < n; ++i) z[i] = cplx(re[i], im ? im[i] : 0.0);
+        *out = new Pt(c->ev.encode_ext(z.data(), n, level));
+    })
+}
 int orc_decode(orc_ctx *c, const orc_pt *pt, double *re, double *im) {
     ORC_TRY(c, {
         std::vector<cplx> z(c->cx.slots); c->ev.decode(*pt, z.data());
@@ -137,6 +144,9 @@ int orc_tensor(orc_ctx *c, const orc_ct *a, const orc_ct *b, orc_ct **o) { ORC_T
 int orc_relin(orc_ctx *c, const orc_ct *a, orc_ct **o) { ORC_TRY(c, *o = new Ct(c->ev.relin(*a))) }
 int orc_mul(orc_ctx *c, const orc_ct *a, const orc_ct *b, orc_ct **o) { ORC_TRY(c, *o = new Ct(c->ev.mul(*a, *b))) }
 int orc_rotate(orc_ctx *c, const orc_ct *a, int64_t s, orc_ct **o) { ORC_TRY(c, *o = new Ct(c->ev.rotate(*a, s))) }
+int orc_assemble_rot(orc_ctx *c, const orc_ct *a, int64_t s1, const orc_pt *p1, int64_t s2, const orc_pt *p2, orc_ct **o) {
+    ORC_TRY(c, *o = new Ct(c->ev.assemble_rot(*a, s1, *p1, s2, *p2)))
+}
 int orc_conjugate(orc_ctx *c, const orc_ct *a, orc_ct **o) { ORC_TRY(c, *o = new Ct(c->ev.conjugate(*a))) }
 int orc_ntt(orc_ctx *c, orc_ct *a, int inverse) { ORC_TRY(c, c->ev.ntt_raw(*a, inverse != 0)) }
 

@@ -121,6 +121,92 @@ def test_direct_schedule_parity(request, pkg, size, name):
     assert err_g < TOL and err_g == err_o
 
 
+@pytest.mark.parametrize("size", ["small", "mid"])
+@pytest.mark.parametrize("name", ["ccmm_single_tile", "ccmm_two_tiles", "pcmm_reuse", "batched", "lora_forward"])
+def test_lazy_schedule_parity(request, pkg, size, name):
+    """Schedule 2 (one division by P * q_level per wrapped copy) on the GPU against the oracle's assemble_rot: bit-identical."""
+    g, o = _pairs(request, size)
+    Hg, Ho = pkg.open_hemmer(g), pkg.Hemmer(o)
+    Hg.set_schedule(2); Ho.set_schedule(2)
+    eg, err_g = cases.SCENARIOS[name](g, Hg)
+    eo, err_o = cases.SCENARIOS[name](o, Ho)
+    for k, (a, b) in enumerate(zip(eg, eo)):
+        _same(a, b, f"lazy {name}[{k}]")
+    assert err_g < TOL and err_g == err_o
+
+
+@pytest.mark.parametrize("size", ["small", "mid", "full"])
+def test_assemble_rot_parity(request, size):
+    """The masked pair of rotations with one division, at every digit count, on random residues and a batch of 2."""
+    g, o = _pairs(request, size)
+    steps = (3, -5)
+    for lib in (g, o):
+        lib.gen_rot_keys(list(steps))
+    rng = np.random.default_rng(31)
+    m1 = (rng.uniform(0, 1, g.slots) > 0.5).astype(np.float64)
+    levels = (g.L, 7, 4, 2, 1) if size != "full" else (g.L, 6, 1)
+    for lvl in levels:
+        data = rand_ct_residues(g, lvl, 2, 2, seed=40 + lvl)
+        outs = []
+        for lib in (g, o):
+            ct = lib.ct_create(lvl, 2, 2)
+            lib.ct_import(ct, data)
+            r = lib.assemble_rot(ct, steps[0], lib.encode_ext(m1, lvl), steps[1], lib.encode_ext(1.0 - m1, lvl))
+            assert lib.ct_meta(r) == (lvl - 1, 2, 2, 1)
+            outs.append(lib.ct_export(r))
+        _same(outs[0], outs[1], f"assemble_rot@{lvl}")
+
+
+def test_assemble_rot_argument_errors(pkg, gpu_small):
+    g = gpu_small
+    g.gen_rot_keys([1, 2])
+    ct = g.ct_create(3, 2, 1)
+    g.ct_zero(ct)
+    ones = np.ones(g.slots)
+    with pytest.raises(pkg.HBError):  # plain (not extended) plaintext
+        g.assemble_rot(ct, 1, g.encode(ones, 3), 2, g.encode_ext(ones, 3))
+    with pytest.raises(pkg.HBError):  # plaintext of another level
+        g.assemble_rot(ct, 1, g.encode_ext(ones, 4), 2, g.encode_ext(ones, 3))
+    with pytest.raises(pkg.HBError):  # zero rotation
+        g.assemble_rot(ct, 0, g.encode_ext(ones, 3), 2, g.encode_ext(ones, 3))
+
+
+@pytest.mark.parametrize("size", ["mid", "full"])
+def test_encrypt_many_equals_encrypt(request, size):
+    """The batched encode + encrypt gives, member by member, the residues of hb_encode + hb_encrypt (and of the oracle)."""
+    g, o = _pairs(request, size)
+    rng = np.random.default_rng(56)
+    msgs = rng.uniform(-1, 1, (3, g.slots))
+    nonces = [901, 77, 4242]
+    many = g.ct_export(g.encrypt_many(msgs, g.L, nonces))
+    for i in range(3):
+        _same(many[i:i + 1], g.ct_export(g.encrypt(g.encode(msgs[i], g.L), nonces[i])), f"encrypt_many[{i}]")
+    _same(many[2:3], o.ct_export(o.encrypt(o.encode(msgs[2], o.L), nonces[2])), "encrypt_many vs oracle")
+    cplx = msgs[:2] + 1j * msgs[1:3]
+    many = g.ct_export(g.encrypt_many(cplx, 5, nonces[:2]))
+    _same(many[1:2], g.ct_export(g.encrypt(g.encode(cplx[1], 5), nonces[1])), "encrypt_many complex, level 5")
+
+
+def test_decrypt_many_equals_decrypt(gpu_mid):
+    """One batched call gives, member by member, exactly the values of hb_decrypt (also with a level-0 member)."""
+    g = gpu_mid
+    rng = np.random.default_rng(55)
+    zs = [rng.uniform(-1, 1, g.slots) + 1j * rng.uniform(-1, 1, g.slots) for _ in range(5)]
+    cts = [g.encrypt(g.encode(z, g.L), 300 + i) for i, z in enumerate(zs)]
+    cts[1] = g.level_down(cts[1], 3)
+    cts[2] = g.mul_pt_norescale(cts[2], g.encode(np.ones(g.slots), g.L))   # scale Delta^2
+    both = g.batch_concat([cts[3], cts[4]])
+    items = [(cts[0], 0), (cts[1], 0), (cts[2], 0), (both, 1), (both, 0)]
+    many = g.decrypt_many(items)
+    for (ct, k), row in zip(items, many):
+        assert np.array_equal(row, g.decrypt(ct, k))
+    assert np.abs(many[3] - zs[4]).max() < 1e-6
+    items.append((g.level_down(cts[0], 0), 0))
+    many = g.decrypt_many(items)
+    for (ct, k), row in zip(items, many):
+        assert np.array_equal(row, g.decrypt(ct, k))
+
+
 def test_hoisted_rotation_equals_rotation(gpu_mid):
     g = gpu_mid
     import ctypes as C

@@ -43,3 +43,37 @@ def test_direct_schedule_semantics(name, pkg, orc_small):
     exports_f, _ = cases.SCENARIOS[name](orc_small, Hf)
     import numpy as np
     assert any(not np.array_equal(a, b) for a, b in zip(exports_d, exports_f)), "variants are expected to differ in bits"
+
+
+@pytest.mark.parametrize("name", ["ccmm_single_tile", "ccmm_two_tiles", "pcmm_reuse", "batched"])
+def test_lazy_schedule_semantics(name, pkg, orc_small):
+    """Schedule 2: each wrapped copy is one assemble_rot (one division by P * q_level); same products, other bits."""
+    Hl = pkg.Hemmer(orc_small)
+    Hl.set_schedule(2)
+    exports_l, err = cases.SCENARIOS[name](orc_small, Hl)
+    assert err < TOL, (name, err)
+    Hd = pkg.Hemmer(orc_small)
+    Hd.set_schedule(1)
+    exports_d, _ = cases.SCENARIOS[name](orc_small, Hd)
+    import numpy as np
+    assert any(not np.array_equal(a, b) for a, b in zip(exports_l, exports_d))
+
+
+def test_assemble_rot_semantics(orc_small):
+    """p1 (.) rot(x, s1) + p2 (.) rot(x, s2) at every level, against the slot arithmetic and the unfused sequence."""
+    import numpy as np
+    o = orc_small
+    rng = np.random.default_rng(3)
+    z = rng.uniform(-1, 1, o.slots) + 1j * rng.uniform(-1, 1, o.slots)
+    m1 = (rng.uniform(0, 1, o.slots) > 0.5).astype(float)
+    o.gen_rot_keys([3, -13])
+    want = m1 * np.roll(z, -3) + (1 - m1) * np.roll(z, 13)
+    for lvl in range(o.L, 0, -1):
+        ct = o.encrypt(o.encode(z, o.L), 5)
+        if lvl < o.L:
+            ct = o.level_down(ct, lvl)
+        a = o.assemble_rot(ct, 3, o.encode_ext(m1, lvl), -13, o.encode_ext(1 - m1, lvl))
+        assert o.ct_meta(a) == (lvl - 1, 2, 1, 1)
+        ref = o.rescale(o.add(o.mul_pt_norescale(o.rotate(ct, 3), o.encode(m1, lvl)), o.mul_pt_norescale(o.rotate(ct, -13), o.encode(1 - m1, lvl))))
+        err, err_ref = np.abs(o.decrypt(a) - want).max(), np.abs(o.decrypt(ref) - want).max()
+        assert err < 4 * err_ref + 1e-9, (lvl, err, err_ref)
