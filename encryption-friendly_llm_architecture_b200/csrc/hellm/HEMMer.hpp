@@ -56,9 +56,13 @@ class MaskCache {
     using Key = std::tuple<int, TileTensorShape, i64, int>; // kind, shape, index, level
     const Plaintext *find(const Key &k) const { auto it = enc_.find(k); return it == enc_.end() ? nullptr : &it->second; }
     const Plaintext &put(const Key &k, Plaintext p) { return enc_.emplace(k, std::move(p)).first->second; }
-    void clear() { enc_.clear(); }
+    // rotation keys that carry a wrap mask (schedule 2), per (kind, shape, shift index, level)
+    const MaskedKey *findKey(const Key &k) const { auto it = keys_.find(k); return it == keys_.end() ? nullptr : &it->second; }
+    const MaskedKey &putKey(const Key &k, MaskedKey m) { return keys_.emplace(k, std::move(m)).first->second; }
+    void clear() { enc_.clear(); keys_.clear(); }
   private:
     std::map<Key, Plaintext> enc_;
+    std::map<Key, MaskedKey> keys_;
 };
 
 class HEMMer {

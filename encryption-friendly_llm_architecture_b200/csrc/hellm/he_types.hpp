@@ -90,6 +90,17 @@ class Hoisted {
     std::shared_ptr<hb_digits> d_;
 };
 
+// A rotation key multiplied once by a mask (or the sum of two), for one level: see hb_masked_key_create.
+class MaskedKey {
+  public:
+    MaskedKey() = default;
+    explicit MaskedKey(hb_mkey *k) : k_(k, [](hb_mkey *x) { hb_masked_key_free(x); }) {}
+    hb_mkey *raw() const { return k_.get(); }
+    bool empty() const { return !k_; }
+  private:
+    std::shared_ptr<hb_mkey> k_;
+};
+
 // The subset of HEaaN::HomEvaluator / EnDecoder the matmul path uses (HomEvaluator.hpp:30-616).
 class Evaluator {
   public:
@@ -149,6 +160,14 @@ class Evaluator {
         const i64 steps[2] = {sa, sb};
         check(c_, hb_gen_rot_keys(c_, steps, 2));
         hb_ct *o = nullptr; check(c_, hb_assemble_hoisted(c_, a.raw(), h.raw(), sa, pa.raw(), sb, pb.raw(), &o)); return Ciphertext(c_, o);
+    }
+    // the same from rotation keys that already carry the masks; kb may be empty (one masked rotation)
+    MaskedKey maskedKey(i64 steps, const Plaintext &m1, const Plaintext *m2 = nullptr) const {
+        check(c_, hb_gen_rot_keys(c_, &steps, 1));
+        hb_mkey *k = nullptr; check(c_, hb_masked_key_create(c_, steps, m1.raw(), m2 ? m2->raw() : nullptr, &k)); return MaskedKey(k);
+    }
+    Ciphertext assembleRotations(const Ciphertext &a, const Hoisted &h, const MaskedKey &ka, const MaskedKey &kb) const {
+        hb_ct *o = nullptr; check(c_, hb_assemble_masked(c_, a.raw(), h.raw(), ka.raw(), kb.raw(), &o)); return Ciphertext(c_, o);
     }
     // sum_j mult(a[j], p[j]): every product is rescaled as eval.mult(ct, mask) does, the results are added
     Ciphertext multSum(const std::vector<const Ciphertext *> &a, const std::vector<const Plaintext *> &p) const {

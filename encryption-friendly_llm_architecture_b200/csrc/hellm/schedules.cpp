@@ -159,6 +159,31 @@ const Plaintext &row_wrap(Env &e, const TileTensorShape &s, i64 which, int level
     }, true);
 }
 
+// The wrapped copy number i of a shift loop, rescale(wrap[2i+1] (.) rot(x, s) + wrap[2i] (.) rot(x, s_wrapped)), in the kLazy
+// schedule: the two masks are folded into their rotation keys once (cached per shape, shift and level).  When both
+// steps are the same rotation (a row shift by the whole tile height on a full slot grid) one key carries both masks.
+struct WrappedCopy { const MaskedKey *main; const MaskedKey *wrapped; };
+WrappedCopy wrapped_copy(Env &e, bool rows, const TileTensorShape &s, i64 i, int level, i64 step, i64 step_wrapped) {
+    const int kind = rows ? kRowWrapKey : kColWrapKey;
+    const i64 norm = e.slots;
+    const bool same = ((step - step_wrapped) % norm) == 0;
+    // the steps are part of the key: the wrapped step depends on the other operand's width as well as on the shape
+    const i64 st = ((step % norm) + norm) % norm, sw = ((step_wrapped % norm) + norm) % norm, tag = (st << 20) | (sw << 40);
+    MaskCache::Key k1{kind, s, tag | (2 * i + 1), level}, k0{kind, s, tag | (2 * i), level};
+    const MaskedKey *main = e.cache.findKey(k1);
+    if (!main) {
+        const Plaintext &m1 = rows ? row_wrap(e, s, 2 * i + 1, level) : col_wrap(e, s, 2 * i + 1, level);
+        const Plaintext &m0 = rows ? row_wrap(e, s, 2 * i, level) : col_wrap(e, s, 2 * i, level);
+        main = &e.cache.putKey(k1, same ? e.ev.maskedKey(step, m1, &m0) : e.ev.maskedKey(step, m1));
+        if (!same) e.cache.putKey(k0, e.ev.maskedKey(step_wrapped, m0));
+    }
+    return WrappedCopy{main, same ? nullptr : e.cache.findKey(k0)};
+}
+Ciphertext assemble_lazy(Env &e, const Ciphertext &x, const Hoisted &h, const WrappedCopy &w) {
+    static const MaskedKey none;
+    return e.ev.assembleRotations(x, h, *w.main, w.wrapped ? *w.wrapped : none);
+}
+
 void require_product_shapes(const CtxtTensor &a, const CtxtTensor &b) {
     if (a.getWidth() != b.getHeight()) throw std::invalid_argument("[getCommonInsideLength] different inside length.");
     if (a.getBlockWidth() != b.getBlockWidth()) throw std::invalid_argument("[getCommonBlockWidth] different block width");
@@ -244,8 +269,8 @@ CtxtTensor ccmmCore(Env &e, Ciphertext a, Ciphertext b, i64 num_rows, i64 inner,
     if (e.mode == kLazy) {
         const Hoisted ha = e.ev.decompose(a), hb = e.ev.decompose(b);
         for (i64 i = 1; i < num_k; ++i) {
-            Ciphertext ak = e.ev.assembleRotations(a, ha, i, col_wrap(e, sa, 2 * i + 1, lvl), i - cols_tmp, col_wrap(e, sa, 2 * i, lvl));
-            Ciphertext bk = e.ev.assembleRotations(b, hb, i * width, row_wrap(e, sb, 2 * i + 1, lvl), (i - rows_tmp) * width, row_wrap(e, sb, 2 * i, lvl));
+            Ciphertext ak = assemble_lazy(e, a, ha, wrapped_copy(e, false, sa, i, lvl, i, i - cols_tmp));
+            Ciphertext bk = assemble_lazy(e, b, hb, wrapped_copy(e, true, sb, i, lvl, i * width, (i - rows_tmp) * width));
             e.ev.tensorAccumulate(acc, ak, bk);
         }
     } else if (e.mode >= kDirect) {
@@ -411,7 +436,7 @@ Ciphertext multMatMatPre(Env &e, const CtxtTensor &in, int target_level) {
     if (e.mode == kLazy) {
         const Hoisted h = e.ev.decompose(s.get());
         for (i64 i = 1; i < num_rows; ++i)
-            copies.push_back(e.ev.assembleRotations(s.get(), h, i, col_wrap(e, s.getShape(), 2 * i + 1, lvl), i - num_rows, col_wrap(e, s.getShape(), 2 * i, lvl)));
+            copies.push_back(assemble_lazy(e, s.get(), h, wrapped_copy(e, false, s.getShape(), i, lvl, i, i - num_rows)));
         return e.ev.stack(copies);
     }
     if (e.mode >= kDirect) {

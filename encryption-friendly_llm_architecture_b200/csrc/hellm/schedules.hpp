@@ -6,7 +6,7 @@ namespace HELLM {
 namespace sched {
 
 // mask families, used as the first component of MaskCache::Key
-enum MaskKind { kDiagonal = 0, kHorizontal, kVertical, kPackedHorizontal, kPackedVertical, kColWrap, kRowWrap, kHemmer, kLowRank };
+enum MaskKind { kDiagonal = 0, kHorizontal, kVertical, kPackedHorizontal, kPackedVertical, kColWrap, kRowWrap, kHemmer, kLowRank, kColWrapKey, kRowWrapKey };
 
 // Schedule variants.  kFaithful keeps the reference's sequence of rotations (each shifted copy is the previous one
 // rotated once more).  kDirect takes every shifted copy straight from the transformed operand, rot(x, k) instead of

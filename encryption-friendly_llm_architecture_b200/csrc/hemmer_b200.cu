@@ -123,6 +123,8 @@ struct hb_ct { hb_ctx *ctx; int level, np, batch, spow; u64 *d; size_t limbs() c
 struct hb_pt { hb_ctx *ctx; int level, spow; u64 *d; int ext = 0; }; // ext: K further limbs modulo the special primes follow the level+1 limbs
 // lifted digits of the a-part of a ciphertext batch, NTT form: what all rotations of that ciphertext share
 struct hb_digits { hb_ctx *ctx; int level, batch; u64 *d; };
+// a switching key multiplied by a plaintext mask, restricted to one level: key [nd][2][ne][N], pm = P * mask on the Q limbs [n][N]
+struct hb_mkey { hb_ctx *ctx; int level; u32 g; u64 *key, *pm; };
 
 namespace {
 
@@ -338,6 +340,24 @@ const DivPlan *get_div_plan(hb_ctx *c, int level) {
     c->div_plans[level] = d;
     return d;
 }
+// E [batch][2][ne][N] over Q_level u P  ->  new ciphertext at level - 1:  (E - lift(E mod P*q_level)) / (P*q_level)
+hb_ct *divide_by_p_ql(hb_ctx *c, const u64 *E, int level, int batch) {
+    const DivPlan *dv = get_div_plan(c, level);
+    const PlanDims d = plan_dims(c, level);
+    const int N = c->N, n = d.n, ne = d.ne, ns = d.K + 1;
+    hb_ct *r = new_ct(c, level - 1, 2, batch, 1);
+    try {
+        const unsigned gx1 = (unsigned)((N + 255) / 256), gx = c->gx();
+        Tmp sc(c, (size_t)batch * 2 * ns), t(c, (size_t)batch * 2 * level);
+        LimbMap sm{}; sm.n = ns; sm.prime[0] = (unsigned char)level; for (int k = 0; k < d.K; ++k) sm.prime[1 + k] = (unsigned char)(c->L + 1 + k);
+        ntt(c, E + (size_t)(n - 1) * N, (size_t)ne * N, sc.p, (size_t)ns * N, batch * 2 * ns, sm, true);
+        LAUNCH(c), k_div_conv<<<dim3(gx1, 1, batch * 2), 256, 0, c->st>>>(t.p, sc.p, dv, c->pc, N);
+        ntt_inplace(c, t.p, batch * 2 * level, c->qmap(level - 1), false);
+        LAUNCH(c), k_div_fin<<<dim3(gx, level, batch * 2), 256, 0, c->st>>>(r->d, E, t.p, ne, dv, c->pc, N);
+        CK(cudaGetLastError());
+    } catch (...) { hb_ct_free(r); throw; }
+    return r;
+}
 // rescale(p1 (.) rot(a, s1) + p2 (.) rot(a, s2)) from the lifted digits `dt` of a: both inner products stay in
 // Q_level u P, are multiplied there by the extended plaintexts and summed; one division by P * q_level follows.
 hb_ct *do_assemble_rot(hb_ctx *c, const hb_ct *a, const u64 *dt, int64_t s1, const hb_pt *p1, int64_t s2, const hb_pt *p2) {
@@ -351,25 +371,34 @@ hb_ct *do_assemble_rot(hb_ctx *c, const hb_ct *a, const u64 *dt, int64_t s1, con
     const KsPlan *pl = get_plan(c, level);
     const DivPlan *dv = get_div_plan(c, level);
     const PlanDims d = plan_dims(c, level);
-    const int n = d.n, ne = d.ne, ns = d.K + 1;
+    const int n = d.n, ne = d.ne;
     RotPair rp{};
     rp.key[0] = galois_key(c, g1).d; rp.key[1] = galois_key(c, g2).d;
     rp.mask[0] = p1->d; rp.mask[1] = p2->d;
     rp.g[0] = (u32)g1; rp.g[1] = (u32)g2;
-    hb_ct *r = new_ct(c, level - 1, 2, batch, 1);
-    try {
-        const unsigned gx1 = (unsigned)((N + 255) / 256), gx = c->gx();
-        Tmp E(c, (size_t)batch * 2 * ne), sc(c, (size_t)batch * 2 * ns), t(c, (size_t)batch * 2 * level);
-        const size_t a_outer = (size_t)2 * n * N;
-        LAUNCH(c), k_ks_inner_pair<<<dim3(gx, ne, batch), 256, 0, c->st>>>(E.p, a->d, a->d + (size_t)n * N, a_outer, dt, rp, c->nprimes, pl, dv, c->pc, c->logn, N);
-        LimbMap sm{}; sm.n = ns; sm.prime[0] = (unsigned char)level; for (int k = 0; k < d.K; ++k) sm.prime[1 + k] = (unsigned char)(c->L + 1 + k);
-        ntt(c, E.p + (size_t)(n - 1) * N, (size_t)ne * N, sc.p, (size_t)ns * N, batch * 2 * ns, sm, true);
-        LAUNCH(c), k_div_conv<<<dim3(gx1, 1, batch * 2), 256, 0, c->st>>>(t.p, sc.p, dv, c->pc, N);
-        ntt_inplace(c, t.p, batch * 2 * level, c->qmap(level - 1), false);
-        LAUNCH(c), k_div_fin<<<dim3(gx, level, batch * 2), 256, 0, c->st>>>(r->d, E.p, t.p, ne, dv, c->pc, N);
-        CK(cudaGetLastError());
-    } catch (...) { hb_ct_free(r); throw; }
-    return r;
+    Tmp E(c, (size_t)batch * 2 * ne);
+    const size_t a_outer = (size_t)2 * n * N;
+    LAUNCH(c), k_ks_inner_pair<<<dim3(c->gx(), ne, batch), 256, 0, c->st>>>(E.p, a->d, a->d + (size_t)n * N, a_outer, dt, rp, c->nprimes, pl, dv, c->pc, c->logn, N);
+    return divide_by_p_ql(c, E.p, level, batch);
+}
+// the same from keys that already carry the masks (hb_masked_key_create)
+hb_ct *do_assemble_mk(hb_ctx *c, const hb_ct *a, const u64 *dt, const hb_mkey *const *keys, int count) {
+    if (a->np != 2 || a->spow != 1) fail(HB_E_SHAPE, "assemble: needs a rescaled 2-poly ciphertext");
+    if (a->level < 1) fail(HB_E_LEVEL, "assemble: level 0");
+    if (count < 1 || count > 2) fail(HB_E_ARG, "assemble: one or two masked keys");
+    MaskedRot mr{};
+    mr.count = count;
+    for (int r = 0; r < count; ++r) {
+        if (!keys[r] || keys[r]->level != a->level) fail(HB_E_LEVEL, "assemble: masked key of another level");
+        mr.mkey[r] = keys[r]->key; mr.pm[r] = keys[r]->pm; mr.g[r] = keys[r]->g;
+    }
+    const int level = a->level, batch = a->batch, N = c->N;
+    const KsPlan *pl = get_plan(c, level);
+    const PlanDims d = plan_dims(c, level);
+    const int n = d.n, ne = d.ne;
+    Tmp E(c, (size_t)batch * 2 * ne);
+    LAUNCH(c), k_ks_inner_mk<<<dim3(c->gx(), ne, batch), 256, 0, c->st>>>(E.p, a->d, a->d + (size_t)n * N, (size_t)2 * n * N, dt, mr, pl, c->pc, c->logn, N);
+    return divide_by_p_ql(c, E.p, level, batch);
 }
 
 void check_same(const hb_ct *a, const hb_ct *b, const char *what) {
@@ -1051,6 +1080,36 @@ int hb_assemble_rot(hb_ctx *c, const hb_ct *a, int64_t s1, const hb_pt *p1, int6
         Tmp dt(c, (size_t)a->batch * d.dt_count);
         ks_decompose(c, a->d + (size_t)n * N, (size_t)2 * n * N, a->level, a->batch, dt.p);
         *out = do_assemble_rot(c, a, dt.p, s1, p1, s2, p2);
+    });
+}
+int hb_masked_key_create(hb_ctx *c, int64_t steps, const hb_pt *m1, const hb_pt *m2, hb_mkey **out) {
+    return guard(c, [&] {
+        if (!m1 || !m1->ext || m1->spow != 1 || (m2 && (!m2->ext || m2->level != m1->level || m2->spow != 1))) fail(HB_E_ARG, "masked_key: extended plaintexts of one level needed");
+        const u64 g = c->h->galois_rot(steps);
+        if (g == 1) fail(HB_E_ARG, "masked_key: zero rotation");
+        const int level = m1->level, N = c->N;
+        if (level < 1) fail(HB_E_LEVEL, "masked_key: level 0");
+        const Evk &key = galois_key(c, g);
+        const KsPlan *pl = get_plan(c, level);
+        const DivPlan *dv = get_div_plan(c, level);
+        const PlanDims d = plan_dims(c, level);
+        hb_mkey *k = new hb_mkey{c, level, (u32)g, nullptr, nullptr};
+        try {
+            k->key = c->alloc_limbs((size_t)d.nd * 2 * d.ne);
+            k->pm = c->alloc_limbs((size_t)d.n);
+            LAUNCH(c), k_mask_key<<<dim3(c->gx(), d.ne, d.nd * 2), 256, 0, c->st>>>(k->key, key.d, c->nprimes, m1->d, m2 ? m2->d : nullptr, pl, c->pc, N);
+            LAUNCH(c), k_mask_p<<<dim3(c->gx(), d.n), 256, 0, c->st>>>(k->pm, m1->d, m2 ? m2->d : nullptr, dv, c->pc, N);
+            CK(cudaGetLastError());
+        } catch (...) { if (k->key) c->pool.put(k->key); if (k->pm) c->pool.put(k->pm); delete k; throw; }
+        *out = k;
+    });
+}
+void hb_masked_key_free(hb_mkey *k) { if (k) { k->ctx->pool.put(k->key); k->ctx->pool.put(k->pm); delete k; } }
+int hb_assemble_masked(hb_ctx *c, const hb_ct *a, const hb_digits *dg, const hb_mkey *k1, const hb_mkey *k2, hb_ct **out) {
+    return guard(c, [&] {
+        if (a->np != 2 || dg->level != a->level || dg->batch != a->batch) fail(HB_E_SHAPE, "assemble_masked: digits do not belong to this ciphertext");
+        const hb_mkey *ks[2] = {k1, k2};
+        *out = do_assemble_mk(c, a, dg->d, ks, k2 ? 2 : 1);
     });
 }
 int hb_rotate(hb_ctx *c, const hb_ct *a, int64_t steps, hb_ct **out) { return guard(c, [&] { *out = do_galois(c, a, c->h->galois_rot(steps)); }); }

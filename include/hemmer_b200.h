@@ -28,6 +28,7 @@ typedef struct hb_ctx hb_ctx;
 typedef struct hb_ct hb_ct;
 typedef struct hb_pt hb_pt;
 typedef struct hb_digits hb_digits;
+typedef struct hb_mkey hb_mkey;
 
 enum {
     HB_OK = 0,
@@ -164,6 +165,15 @@ void hb_digits_free(hb_digits *digits);
 int hb_assemble_rot(hb_ctx *ctx, const hb_ct *a, int64_t s1, const hb_pt *p1, int64_t s2, const hb_pt *p2, hb_ct **out);
 int hb_assemble_hoisted(hb_ctx *ctx, const hb_ct *a, const hb_digits *digits, int64_t s1, const hb_pt *p1, int64_t s2, const hb_pt *p2,
                         hb_ct **out);
+/* The same with the masks folded into the switching keys once.  mask (.) sum_dg digit_dg (.) key_dg equals
+ * sum_dg digit_dg (.) (mask (.) key_dg) modulo every prime, so hb_masked_key_create(steps, m1, m2) stores
+ * (m1 + m2) (.) key_steps restricted to the masks' level (m2 may be NULL), and hb_assemble_masked(a, digits, k1, k2)
+ * gives exactly the residues of hb_assemble_hoisted(a, digits, s1, m1, s2, m2) with one inner product and one
+ * reduction per residue (k2 may be NULL: a single masked rotation, e.g. when both steps are the same rotation and
+ * the key carries m1 + m2).  A masked key is as large as nd * 2 * (level + 1 + K) limbs.  No counterpart in HEaaN. */
+int hb_masked_key_create(hb_ctx *ctx, int64_t left_steps, const hb_pt *m1, const hb_pt *m2, hb_mkey **out);
+void hb_masked_key_free(hb_mkey *key);
+int hb_assemble_masked(hb_ctx *ctx, const hb_ct *a, const hb_digits *digits, const hb_mkey *k1, const hb_mkey *k2, hb_ct **out);
 /* raw forward / inverse NTT of every limb of the batch, in place (primitive sweep) */
 int hb_ntt(hb_ctx *ctx, hb_ct *a, int inverse);
 

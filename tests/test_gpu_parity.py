@@ -275,3 +275,35 @@ def test_error_codes(pkg, gpu_small):
     with pytest.raises(pkg.HBError) as e:
         g.mul_pt(a, g.encode(np.zeros(4), 5))
     assert e.value.code == -2
+
+
+def test_masked_keys_give_the_residues_of_assemble_rot(gpu_mid):
+    """hb_assemble_masked (masks folded into the keys) against hb_assemble_hoisted, two rotations and one."""
+    import ctypes as C
+    g = gpu_mid
+    g.gen_rot_keys([3, -5])
+    rng = np.random.default_rng(32)
+    m1 = (rng.uniform(0, 1, g.slots) > 0.5).astype(np.float64)
+    dll = g.dll
+    dll.hb_digits_free.restype = None
+    dll.hb_masked_key_free.restype = None
+    for lvl in (g.L, 5, 1):
+        ct = g.ct_create(lvl, 2, 2)
+        g.ct_import(ct, rand_ct_residues(g, lvl, 2, 2, seed=60 + lvl))
+        p1, p2 = g.encode_ext(m1, lvl), g.encode_ext(1.0 - m1, lvl)
+        dg, k1, k2, k12 = C.c_void_p(), C.c_void_p(), C.c_void_p(), C.c_void_p()
+        g._chk(dll.hb_decompose(g.ctx, ct.ptr, C.byref(dg)))
+        g._chk(dll.hb_masked_key_create(g.ctx, C.c_int64(3), p1.ptr, None, C.byref(k1)))
+        g._chk(dll.hb_masked_key_create(g.ctx, C.c_int64(-5), p2.ptr, None, C.byref(k2)))
+        g._chk(dll.hb_masked_key_create(g.ctx, C.c_int64(3), p1.ptr, p2.ptr, C.byref(k12)))
+        try:
+            out = C.c_void_p()
+            g._chk(dll.hb_assemble_masked(g.ctx, ct.ptr, dg, k1, k2, C.byref(out)))
+            _same(g.ct_export(pkg_handle(g, out)), g.ct_export(g.assemble_rot(ct, 3, p1, -5, p2)), f"masked pair@{lvl}")
+            out = C.c_void_p()
+            g._chk(dll.hb_assemble_masked(g.ctx, ct.ptr, dg, k12, None, C.byref(out)))
+            _same(g.ct_export(pkg_handle(g, out)), g.ct_export(g.assemble_rot(ct, 3, p1, 3, p2)), f"masked single@{lvl}")
+        finally:
+            for k in (k1, k2, k12):
+                dll.hb_masked_key_free(k)
+            dll.hb_digits_free(dg)
