@@ -369,6 +369,17 @@ def run_sweep(args):
         if lv >= 1:
             prod = lib.mul_pt_norescale(ct, pt)
             ops.append(("rescale", lambda: lib.rescale(prod), B * (4 * n - 2)))
+        if lv >= 1:
+            # one wrapped copy of a shift loop: two masked rotations of the batch + one division by P*q_l.  Reads the
+            # ciphertexts (2n), writes them one level down (2(n-1)); the lifted digits are made once per operand and
+            # shared by all 127 copies, so they and the two masked keys count once per batch.
+            lib.gen_rot_keys([1, -127])
+            m = (rng.uniform(0, 1, lib.slots) > 0.5).astype(np.float64)
+            k1, k2 = lib.masked_key(1, lib.encode_ext(m, lv)), lib.masked_key(-127, lib.encode_ext(1.0 - m, lv))
+            dg = lib.decompose(ct)
+            ops.append(("wrapped_copy", lambda: lib.assemble_masked(ct, dg, k1, k2), B * (4 * n - 2) + 2 * key))
+        if args.sweep_ops:
+            ops = [o for o in ops if o[0] in args.sweep_ops.split(",")]
         for name, fn, limbs in ops:
             fn(); fn()
             ms = timed_single(torch, stream, lib, fn, 3)
@@ -402,6 +413,7 @@ def main():
                     help="0: the reference's rotation sequence; 1: direct, hoisted rotations (same products, fewer chained key switches); "
                          "2 (default): as 1, each wrapped copy of the shift loops made with one division by P*q_level instead of two ModDowns and a rescale")
     ap.add_argument("--no-compare", action="store_true", help="skip the extra timed pass with the reference's rotation sequence")
+    ap.add_argument("--sweep-ops", type=str, default="", help="comma-separated subset of the sweep's operations (profiling one kernel family)")
     ap.add_argument("--sweep-batch", type=int, default=256)
     ap.add_argument("--sweep-levels", type=str, default="12,8,4,1")
     ap.add_argument("--sweep", action="store_true", help="primitive sweep on 256 ciphertexts (BASELINE config 5) instead of the layer")

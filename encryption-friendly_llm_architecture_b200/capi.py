@@ -258,6 +258,23 @@ class Lib:
         """rescale(p1 (.) rot(a, s1) + p2 (.) rot(a, s2)) with one division by P * q_level for the sum."""
         return self._op("assemble_rot", a.ptr, C.c_int64(s1), p1.ptr, C.c_int64(s2), p2.ptr)
 
+    # ---- hoisting (CUDA library only: the oracle defines rotation as decompose-then-permute and has no split) ----
+    def decompose(self, a):
+        out = C.c_void_p()
+        self._chk(self._fn("decompose")(self.ctx, a.ptr, C.byref(out)))
+        return Handle(self, out, "digits")
+
+    def rotate_hoisted(self, a, digits, s): return self._op("rotate_hoisted", a.ptr, digits.ptr, C.c_int64(s))
+
+    def masked_key(self, steps, m1, m2=None):
+        """Rotation key of `steps` multiplied by the extended plaintext m1 (+ m2), for the plaintexts' level."""
+        out = C.c_void_p()
+        self._chk(self._fn("masked_key_create")(self.ctx, C.c_int64(steps), m1.ptr, m2.ptr if m2 is not None else None, C.byref(out)))
+        return Handle(self, out, "masked_key")
+
+    def assemble_masked(self, a, digits, k1, k2=None):
+        return self._op("assemble_masked", a.ptr, digits.ptr, k1.ptr, k2.ptr if k2 is not None else None)
+
     def _pt_op(self, name, *args):
         out = C.c_void_p()
         self._chk(self._fn(name)(self.ctx, *args, C.byref(out)))

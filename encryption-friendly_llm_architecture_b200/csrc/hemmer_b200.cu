@@ -397,7 +397,8 @@ hb_ct *do_assemble_mk(hb_ctx *c, const hb_ct *a, const u64 *dt, const hb_mkey *c
     const PlanDims d = plan_dims(c, level);
     const int n = d.n, ne = d.ne;
     Tmp E(c, (size_t)batch * 2 * ne);
-    LAUNCH(c), k_ks_inner_mk<<<dim3(c->gx(), ne, batch), 256, 0, c->st>>>(E.p, a->d, a->d + (size_t)n * N, (size_t)2 * n * N, dt, mr, pl, c->pc, c->logn, N);
+    constexpr int kEl = 4; // coefficients per thread (2, with three CTAs resident per SM, measured no faster)
+    LAUNCH(c), k_ks_inner_mk<kEl><<<dim3((unsigned)((N + 256 * kEl - 1) / (256 * kEl)), ne, batch), 256, 0, c->st>>>(E.p, a->d, a->d + (size_t)n * N, (size_t)2 * n * N, dt, mr, pl, c->pc, c->logn, N);
     return divide_by_p_ql(c, E.p, level, batch);
 }
 

@@ -561,32 +561,33 @@ struct MaskedRot {
     int count;            // 1 or 2 rotations
 };
 // E[b][p][j][i] = sum_r sum_dg digit_dg[j][perm_r(i)] * mkey_r[dg][p][j][i]  +  (p == 0, j < n) sum_r c0[b][j][perm_r(i)] * pm_r[j][i]
-// grid = (N/(256*kElems), ne, batch)
-__global__ void k_ks_inner_mk(u64 *__restrict__ E, const u64 *__restrict__ c0, const u64 *__restrict__ a_ntt, size_t a_outer, const u64 *__restrict__ dt, MaskedRot mr,
+// grid = (N/(256*EL), ne, batch); EL coefficients per thread
+template <int EL>
+__global__ void __launch_bounds__(256, EL == 2 ? 3 : 2) k_ks_inner_mk(u64 *__restrict__ E, const u64 *__restrict__ c0, const u64 *__restrict__ a_ntt, size_t a_outer, const u64 *__restrict__ dt, MaskedRot mr,
                               const KsPlan *__restrict__ pl, const PrimeConst *__restrict__ pc, int logn, int N) {
     const int j = blockIdx.y, b = blockIdx.z;
     const int pj = pl->ext_prime[j], nd = pl->nd, ne = pl->ne, n = pl->n;
     const PrimeConst m = pc[pj];
-    const u32 x0 = blockIdx.x * (blockDim.x * kElems) + threadIdx.x;
+    const u32 x0 = blockIdx.x * (blockDim.x * EL) + threadIdx.x;
     const u64 *abase = a_ntt + (size_t)b * a_outer + (size_t)j * N;
     const u64 *cbase = c0 + (size_t)b * a_outer + (size_t)j * N;
     const u64 *dbase = dt + (size_t)b * pl->dt_count * N;
     const size_t kpoly = (size_t)ne * N;
-    u64 r0[kElems], r1[kElems];
+    u64 r0[EL], r1[EL];
     if (m.fp) {
 #pragma unroll
-        for (int u = 0; u < kElems; ++u) { r0[u] = 0; r1[u] = 0; }
+        for (int u = 0; u < EL; ++u) { r0[u] = 0; r1[u] = 0; }
         for (int r = 0; r < mr.count; ++r) {
-            u32 src[kElems];
+            u32 src[EL];
 #pragma unroll
-            for (int u = 0; u < kElems; ++u) src[u] = ntt_perm(x0 + u * blockDim.x, mr.g[r], logn);
+            for (int u = 0; u < EL; ++u) src[u] = ntt_perm(x0 + u * blockDim.x, mr.g[r], logn);
             const u64 *kbase = mr.mkey[r] + (size_t)j * N + x0;
             for (int dg = 0; dg < nd; ++dg) {
                 const int en = pl->dt_entry[dg][j];
                 const u64 *sp = en < 0 ? abase : dbase + (size_t)en * N;
                 const u64 *k0 = kbase + (size_t)dg * 2 * kpoly;
 #pragma unroll
-                for (int u = 0; u < kElems; ++u) {
+                for (int u = 0; u < EL; ++u) {
                     const u64 v = sp[src[u]], ka = k0[u * blockDim.x], kb = k0[kpoly + u * blockDim.x];
                     const double vd = u52_to_double(v);
                     r0[u] += mul_small_lazy_d(v, vd, ka, u52_to_double(ka), m.q_inv_f, m.q);
@@ -596,26 +597,26 @@ __global__ void k_ks_inner_mk(u64 *__restrict__ E, const u64 *__restrict__ c0, c
             if (j < n) {
                 const u64 *pmb = mr.pm[r] + (size_t)j * N + x0;
 #pragma unroll
-                for (int u = 0; u < kElems; ++u) r0[u] += mul_small_lazy(cbase[src[u]], pmb[u * blockDim.x], m.q_inv_f, m.q);
+                for (int u = 0; u < EL; ++u) r0[u] += mul_small_lazy(cbase[src[u]], pmb[u * blockDim.x], m.q_inv_f, m.q);
             }
         }
 #pragma unroll
-        for (int u = 0; u < kElems; ++u) { r0[u] = reduce_fp(r0[u], m.q_inv_f, m.q); r1[u] = reduce_fp(r1[u], m.q_inv_f, m.q); }
+        for (int u = 0; u < EL; ++u) { r0[u] = reduce_fp(r0[u], m.q_inv_f, m.q); r1[u] = reduce_fp(r1[u], m.q_inv_f, m.q); }
     } else {
-        Acc128 s0[kElems], s1[kElems];
+        Acc128 s0[EL], s1[EL];
 #pragma unroll
-        for (int u = 0; u < kElems; ++u) { s0[u].zero(); s1[u].zero(); }
+        for (int u = 0; u < EL; ++u) { s0[u].zero(); s1[u].zero(); }
         for (int r = 0; r < mr.count; ++r) {
-            u32 src[kElems];
+            u32 src[EL];
 #pragma unroll
-            for (int u = 0; u < kElems; ++u) src[u] = ntt_perm(x0 + u * blockDim.x, mr.g[r], logn);
+            for (int u = 0; u < EL; ++u) src[u] = ntt_perm(x0 + u * blockDim.x, mr.g[r], logn);
             const u64 *kbase = mr.mkey[r] + (size_t)j * N + x0;
             for (int dg = 0; dg < nd; ++dg) {
                 const int en = pl->dt_entry[dg][j];
                 const u64 *sp = en < 0 ? abase : dbase + (size_t)en * N;
                 const u64 *k0 = kbase + (size_t)dg * 2 * kpoly;
 #pragma unroll
-                for (int u = 0; u < kElems; ++u) {
+                for (int u = 0; u < EL; ++u) {
                     const u64 v = sp[src[u]];
                     s0[u].mad(v, k0[u * blockDim.x]);
                     s1[u].mad(v, k0[kpoly + u * blockDim.x]);
@@ -624,15 +625,15 @@ __global__ void k_ks_inner_mk(u64 *__restrict__ E, const u64 *__restrict__ c0, c
             if (j < n) {
                 const u64 *pmb = mr.pm[r] + (size_t)j * N + x0;
 #pragma unroll
-                for (int u = 0; u < kElems; ++u) s0[u].mad(cbase[src[u]], pmb[u * blockDim.x]);
+                for (int u = 0; u < EL; ++u) s0[u].mad(cbase[src[u]], pmb[u * blockDim.x]);
             }
         }
 #pragma unroll
-        for (int u = 0; u < kElems; ++u) { r0[u] = barrett128(s0[u].hi, s0[u].lo, m); r1[u] = barrett128(s1[u].hi, s1[u].lo, m); }
+        for (int u = 0; u < EL; ++u) { r0[u] = barrett128(s0[u].hi, s0[u].lo, m); r1[u] = barrett128(s1[u].hi, s1[u].lo, m); }
     }
     u64 *o0 = E + (((size_t)b * 2) * ne + j) * N + x0, *o1 = o0 + (size_t)ne * N;
 #pragma unroll
-    for (int u = 0; u < kElems; ++u) { o0[u * blockDim.x] = r0[u]; o1[u * blockDim.x] = r1[u]; }
+    for (int u = 0; u < EL; ++u) { o0[u * blockDim.x] = r0[u]; o1[u * blockDim.x] = r1[u]; }
 }
 // Base conversion of the division: src [bp][ns][N] (limbs q_level, P; coefficient form) -> t [bp][level][N]
 // grid = (N/256, 1, nbp)
