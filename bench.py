@@ -41,16 +41,43 @@ def peaks():
 
 
 class ClockSampler:
-    """nvidia-smi clocks and throttle reasons during the timed region."""
+    """SM clock and throttle reasons sampled DURING the timed region: NVML reads from a thread of this process
+    (two light queries every 250 ms; a looping nvidia-smi process was measured to disturb the timed kernels),
+    nvidia-smi only if NVML cannot be loaded."""
 
-    Q = "clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
+    Q = "clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
+    NAMES = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
 
     def __init__(self, index):
-        self.index, self.rows, self.proc = index, [], None
+        self.index, self.sm, self.max, self.reasons, self.proc, self.stop_flag, self.thread = index, [], None, set(), None, threading.Event(), None
 
     def start(self):
         try:
-            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "200"],
+            import pynvml
+            pynvml.nvmlInit()
+            vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+            phys = int(vis.split(",")[self.index]) if vis and all(v.strip().isdigit() for v in vis.split(",")) else self.index
+            h = pynvml.nvmlDeviceGetHandleByIndex(phys)
+            self.max = float(pynvml.nvmlDeviceGetMaxClockInfo(h, pynvml.NVML_CLOCK_SM))
+            bits = [(pynvml.nvmlClocksEventReasonHwSlowdown, "hw_slowdown"), (pynvml.nvmlClocksEventReasonHwThermalSlowdown, "hw_thermal_slowdown"),
+                    (pynvml.nvmlClocksEventReasonSwThermalSlowdown, "sw_thermal_slowdown"), (pynvml.nvmlClocksEventReasonSwPowerCap, "sw_power_cap")]
+
+            def loop():
+                while not self.stop_flag.is_set():
+                    try:
+                        self.sm.append(float(pynvml.nvmlDeviceGetClockInfo(h, pynvml.NVML_CLOCK_SM)))
+                        r = pynvml.nvmlDeviceGetCurrentClocksEventReasons(h)
+                        self.reasons.update(name for bit, name in bits if r & bit)
+                    except Exception:
+                        pass
+                    self.stop_flag.wait(0.25)
+            self.thread = threading.Thread(target=loop, daemon=True)
+            self.thread.start()
+            return
+        except Exception:
+            self.thread = None
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "500"],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             threading.Thread(target=self._read, daemon=True).start()
         except OSError:
@@ -58,20 +85,25 @@ class ClockSampler:
 
     def _read(self):
         for line in self.proc.stdout:
-            self.rows.append([x.strip() for x in line.split(",")])
+            r = [x.strip() for x in line.split(",")]
+            if r and r[0].replace(".", "").isdigit():
+                self.sm.append(float(r[0]))
+            if len(r) > 1 and r[1].replace(".", "").isdigit():
+                self.max = max(self.max or 0.0, float(r[1]))
+            if len(r) >= 6:
+                self.reasons.update(self.NAMES[k] for k in range(4) if r[2 + k].lower().startswith("active"))
 
     def stop(self):
+        self.stop_flag.set()
+        if self.thread:
+            self.thread.join(timeout=2)
         if self.proc:
             self.proc.terminate()
             try:
                 self.proc.wait(timeout=2)
             except Exception:
                 pass
-        sm = [float(r[0]) for r in self.rows if r and r[0].replace(".", "").isdigit()]
-        mx = [float(r[1]) for r in self.rows if len(r) > 1 and r[1].replace(".", "").isdigit()]
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        reasons = sorted({names[k] for r in self.rows if len(r) >= 7 for k in range(4) if r[3 + k].lower().startswith("active")})
-        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None, "reasons": reasons, "samples": len(sm)}
+        return {"sm_mhz": statistics.median(self.sm) if self.sm else None, "sm_max_mhz": self.max, "reasons": sorted(self.reasons), "samples": len(self.sm)}
 
 
 # ---------------------------------------------------------------------------------------------
@@ -219,7 +251,7 @@ def run_gpu(args):
         with torch.cuda.stream(stream):
             e0.record(stream)
             for s in range(steps):
-                keep = fn(s)
+                fn(s)   # the result handles are dropped at once, as in the warm-up passes: the pool sees the same allocation pattern
             e1.record(stream)
         lib.sync()
         torch.cuda.synchronize()

@@ -169,6 +169,24 @@ class Evaluator {
     Ciphertext assembleRotations(const Ciphertext &a, const Hoisted &h, const MaskedKey &ka, const MaskedKey &kb) const {
         hb_ct *o = nullptr; check(c_, hb_assemble_masked(c_, a.raw(), h.raw(), ka.raw(), kb.raw(), &o)); return Ciphertext(c_, o);
     }
+    // several wrapped copies of the same input in one launch sequence; member g * batch + b of the result is copy g of input b
+    Ciphertext assembleRotationsMulti(const Ciphertext &a, const Hoisted &h, const std::vector<const MaskedKey *> &ka, const std::vector<const MaskedKey *> &kb) const {
+        std::vector<const hb_mkey *> k1, k2;
+        for (size_t g = 0; g < ka.size(); ++g) { k1.push_back(ka[g]->raw()); k2.push_back(kb[g] ? kb[g]->raw() : nullptr); }
+        hb_ct *o = nullptr; check(c_, hb_assemble_masked_multi(c_, a.raw(), h.raw(), k1.data(), k2.data(), (int)k1.size(), &o)); return Ciphertext(c_, o);
+    }
+    // acc += sum_g tensor(a[g], b[g]) for group-major batches of `groups` groups
+    void tensorAccumulateGroups(Ciphertext &acc, const Ciphertext &a, const Ciphertext &b, int groups) const {
+        hb_ct *p = acc.release();
+        int rc = hb_tensor_acc_groups(c_, a.raw(), b.raw(), groups, &p);
+        acc = Ciphertext(c_, p);
+        check(c_, rc);
+    }
+    Ciphertext concat(const std::vector<Ciphertext> &parts) const {
+        std::vector<const hb_ct *> raw;
+        for (const auto &x : parts) raw.push_back(x.raw());
+        hb_ct *o = nullptr; check(c_, hb_batch_concat(c_, raw.data(), (int)raw.size(), &o)); return Ciphertext(c_, o);
+    }
     // sum_j mult(a[j], p[j]): every product is rescaled as eval.mult(ct, mask) does, the results are added
     Ciphertext multSum(const std::vector<const Ciphertext *> &a, const std::vector<const Plaintext *> &p) const {
         std::vector<const hb_ct *> ra; std::vector<const hb_pt *> rp;

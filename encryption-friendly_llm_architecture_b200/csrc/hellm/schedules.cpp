@@ -179,10 +179,15 @@ WrappedCopy wrapped_copy(Env &e, bool rows, const TileTensorShape &s, i64 i, int
     }
     return WrappedCopy{main, same ? nullptr : e.cache.findKey(k0)};
 }
-Ciphertext assemble_lazy(Env &e, const Ciphertext &x, const Hoisted &h, const WrappedCopy &w) {
-    static const MaskedKey none;
-    return e.ev.assembleRotations(x, h, *w.main, w.wrapped ? *w.wrapped : none);
+// Wrapped copies first .. first + count - 1 of one operand in one launch sequence (group-major batch).
+Ciphertext assemble_lazy(Env &e, const Ciphertext &x, const Hoisted &h, const std::vector<WrappedCopy> &w) {
+    std::vector<const MaskedKey *> ka, kb;
+    for (const auto &c : w) { ka.push_back(c.main); kb.push_back(c.wrapped); }
+    return e.ev.assembleRotationsMulti(x, h, ka, kb);
 }
+// Iterations of a shift loop handled by one launch sequence: small batches are stacked until about 40 ciphertexts
+// are in flight (a batch that large fills the GPU on its own).  The stored residues do not depend on the grouping.
+i64 loop_group(const Ciphertext &x) { return std::max<i64>(1, std::min<i64>(16, 40 / std::max(1, x.getBatch()))); }
 
 void require_product_shapes(const CtxtTensor &a, const CtxtTensor &b) {
     if (a.getWidth() != b.getHeight()) throw std::invalid_argument("[getCommonInsideLength] different inside length.");
@@ -268,10 +273,15 @@ CtxtTensor ccmmCore(Env &e, Ciphertext a, Ciphertext b, i64 num_rows, i64 inner,
     Ciphertext acc;
     if (e.mode == kLazy) {
         const Hoisted ha = e.ev.decompose(a), hb = e.ev.decompose(b);
-        for (i64 i = 1; i < num_k; ++i) {
-            Ciphertext ak = assemble_lazy(e, a, ha, wrapped_copy(e, false, sa, i, lvl, i, i - cols_tmp));
-            Ciphertext bk = assemble_lazy(e, b, hb, wrapped_copy(e, true, sb, i, lvl, i * width, (i - rows_tmp) * width));
-            e.ev.tensorAccumulate(acc, ak, bk);
+        const i64 group = loop_group(a);
+        for (i64 i0 = 1; i0 < num_k; i0 += group) {
+            std::vector<WrappedCopy> wa, wb;
+            for (i64 i = i0; i < std::min(num_k, i0 + group); ++i) {
+                wa.push_back(wrapped_copy(e, false, sa, i, lvl, i, i - cols_tmp));
+                wb.push_back(wrapped_copy(e, true, sb, i, lvl, i * width, (i - rows_tmp) * width));
+            }
+            Ciphertext ak = assemble_lazy(e, a, ha, wa), bk = assemble_lazy(e, b, hb, wb);
+            e.ev.tensorAccumulateGroups(acc, ak, bk, (int)wa.size());
         }
     } else if (e.mode >= kDirect) {
         const Hoisted ha = e.ev.decompose(a), hb = e.ev.decompose(b);
@@ -435,9 +445,13 @@ Ciphertext multMatMatPre(Env &e, const CtxtTensor &in, int target_level) {
     copies.push_back(e.ev.levelDownOne(s.get()));
     if (e.mode == kLazy) {
         const Hoisted h = e.ev.decompose(s.get());
-        for (i64 i = 1; i < num_rows; ++i)
-            copies.push_back(assemble_lazy(e, s.get(), h, wrapped_copy(e, false, s.getShape(), i, lvl, i, i - num_rows)));
-        return e.ev.stack(copies);
+        const i64 group = loop_group(s.get());
+        for (i64 i0 = 1; i0 < num_rows; i0 += group) { // a group of copies is already laid out copy-major, as stack() lays them
+            std::vector<WrappedCopy> w;
+            for (i64 i = i0; i < std::min(num_rows, i0 + group); ++i) w.push_back(wrapped_copy(e, false, s.getShape(), i, lvl, i, i - num_rows));
+            copies.push_back(assemble_lazy(e, s.get(), h, w));
+        }
+        return e.ev.concat(copies);
     }
     if (e.mode >= kDirect) {
         const Hoisted h = e.ev.decompose(s.get());

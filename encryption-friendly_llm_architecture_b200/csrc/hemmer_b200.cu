@@ -381,25 +381,32 @@ hb_ct *do_assemble_rot(hb_ctx *c, const hb_ct *a, const u64 *dt, int64_t s1, con
     LAUNCH(c), k_ks_inner_pair<<<dim3(c->gx(), ne, batch), 256, 0, c->st>>>(E.p, a->d, a->d + (size_t)n * N, a_outer, dt, rp, c->nprimes, pl, dv, c->pc, c->logn, N);
     return divide_by_p_ql(c, E.p, level, batch);
 }
-// the same from keys that already carry the masks (hb_masked_key_create)
-hb_ct *do_assemble_mk(hb_ctx *c, const hb_ct *a, const u64 *dt, const hb_mkey *const *keys, int count) {
+// the same from keys that already carry the masks (hb_masked_key_create).  `groups` wrapped copies of the same input
+// (each with its own one or two keys: k1s[g], k2s[g] or null) come out of one launch sequence, group-major.
+hb_ct *do_assemble_mk(hb_ctx *c, const hb_ct *a, const u64 *dt, const hb_mkey *const *k1s, const hb_mkey *const *k2s, int groups) {
     if (a->np != 2 || a->spow != 1) fail(HB_E_SHAPE, "assemble: needs a rescaled 2-poly ciphertext");
     if (a->level < 1) fail(HB_E_LEVEL, "assemble: level 0");
-    if (count < 1 || count > 2) fail(HB_E_ARG, "assemble: one or two masked keys");
-    MaskedRot mr{};
-    mr.count = count;
-    for (int r = 0; r < count; ++r) {
-        if (!keys[r] || keys[r]->level != a->level) fail(HB_E_LEVEL, "assemble: masked key of another level");
-        mr.mkey[r] = keys[r]->key; mr.pm[r] = keys[r]->pm; mr.g[r] = keys[r]->g;
+    if (groups < 1 || groups > kMaxRotGroups) fail(HB_E_LIMIT, "assemble: 1 to 16 wrapped copies per call");
+    MaskedRotList mrl{};
+    for (int g = 0; g < groups; ++g) {
+        MaskedRot &mr = mrl.r[g];
+        const hb_mkey *ks[2] = {k1s[g], k2s ? k2s[g] : nullptr};
+        if (!ks[0]) fail(HB_E_ARG, "assemble: missing masked key");
+        mr.count = ks[1] ? 2 : 1;
+        for (int r = 0; r < mr.count; ++r) {
+            if (ks[r]->level != a->level) fail(HB_E_LEVEL, "assemble: masked key of another level");
+            mr.mkey[r] = ks[r]->key; mr.pm[r] = ks[r]->pm; mr.g[r] = ks[r]->g;
+        }
     }
     const int level = a->level, batch = a->batch, N = c->N;
     const KsPlan *pl = get_plan(c, level);
     const PlanDims d = plan_dims(c, level);
     const int n = d.n, ne = d.ne;
-    Tmp E(c, (size_t)batch * 2 * ne);
+    Tmp E(c, (size_t)groups * batch * 2 * ne);
     constexpr int kEl = 4; // coefficients per thread (2, with three CTAs resident per SM, measured no faster)
-    LAUNCH(c), k_ks_inner_mk<kEl><<<dim3((unsigned)((N + 256 * kEl - 1) / (256 * kEl)), ne, batch), 256, 0, c->st>>>(E.p, a->d, a->d + (size_t)n * N, (size_t)2 * n * N, dt, mr, pl, c->pc, c->logn, N);
-    return divide_by_p_ql(c, E.p, level, batch);
+    LAUNCH(c), k_ks_inner_mk<kEl><<<dim3((unsigned)((N + 256 * kEl - 1) / (256 * kEl)), ne, groups * batch), 256, 0, c->st>>>(E.p, a->d, a->d + (size_t)n * N, (size_t)2 * n * N, dt, mrl, batch, pl, c->pc,
+                                                                                                                        c->logn, N);
+    return divide_by_p_ql(c, E.p, level, groups * batch);
 }
 
 void check_same(const hb_ct *a, const hb_ct *b, const char *what) {
@@ -487,14 +494,17 @@ hb_ct *do_addsub(hb_ctx *c, const hb_ct *a, const hb_ct *b, int mode) {
     LAUNCH(c), k_addsub<<<c->egrid((int)a->limbs()), 256, 0, c->st>>>(r->d, a->d, b->d, c->qmap(a->level), c->pc, c->N, mode);
     return r;
 }
-hb_ct *do_tensor(hb_ctx *c, const hb_ct *a, const hb_ct *b, hb_ct *acc) {
+// acc (+)= sum over `groups` of tensor(a[g], b[g]); a, b hold groups * batch members, group-major
+hb_ct *do_tensor(hb_ctx *c, const hb_ct *a, const hb_ct *b, hb_ct *acc, int groups = 1) {
     check_same(a, b, "tensor");
     if (a->np != 2 || a->spow != 1) fail(HB_E_SHAPE, "tensor: operands must be rescaled 2-poly ciphertexts");
+    if (groups < 1 || groups > kMaxRotGroups || a->batch % groups) fail(HB_E_SHAPE, "tensor: the batch does not split into that many groups");
+    const int batch = a->batch / groups;
     hb_ct *r = acc;
-    if (r) { if (r->level != a->level || r->np != 3 || r->batch != a->batch || r->spow != 2) fail(HB_E_SHAPE, "tensor_acc: accumulator mismatch"); }
-    else r = new_ct(c, a->level, 3, a->batch, 2);
+    if (r) { if (r->level != a->level || r->np != 3 || r->batch != batch || r->spow != 2) fail(HB_E_SHAPE, "tensor_acc: accumulator mismatch"); }
+    else r = new_ct(c, a->level, 3, batch, 2);
     const int n = a->level + 1;
-    LAUNCH(c), k_tensor<<<c->egrid(a->batch * n), 256, 0, c->st>>>(r->d, a->d, b->d, n, c->qmap(a->level), c->pc, c->N, acc ? 1 : 0);
+    LAUNCH(c), k_tensor<<<c->egrid(batch * n), 256, 0, c->st>>>(r->d, a->d, b->d, n, c->qmap(a->level), c->pc, c->N, acc ? 1 : 0, groups, batch);
     return r;
 }
 hb_ct *do_relin(hb_ctx *c, const hb_ct *a) {
@@ -1109,10 +1119,17 @@ void hb_masked_key_free(hb_mkey *k) { if (k) { k->ctx->pool.put(k->key); k->ctx-
 int hb_assemble_masked(hb_ctx *c, const hb_ct *a, const hb_digits *dg, const hb_mkey *k1, const hb_mkey *k2, hb_ct **out) {
     return guard(c, [&] {
         if (a->np != 2 || dg->level != a->level || dg->batch != a->batch) fail(HB_E_SHAPE, "assemble_masked: digits do not belong to this ciphertext");
-        const hb_mkey *ks[2] = {k1, k2};
-        *out = do_assemble_mk(c, a, dg->d, ks, k2 ? 2 : 1);
+        *out = do_assemble_mk(c, a, dg->d, &k1, k2 ? &k2 : nullptr, 1);
     });
 }
+int hb_assemble_masked_multi(hb_ctx *c, const hb_ct *a, const hb_digits *dg, const hb_mkey *const *k1s, const hb_mkey *const *k2s, int groups, hb_ct **out) {
+    return guard(c, [&] {
+        if (a->np != 2 || dg->level != a->level || dg->batch != a->batch) fail(HB_E_SHAPE, "assemble_masked: digits do not belong to this ciphertext");
+        if (!k1s) fail(HB_E_ARG, "assemble_masked: no keys");
+        *out = do_assemble_mk(c, a, dg->d, k1s, k2s, groups);
+    });
+}
+int hb_tensor_acc_groups(hb_ctx *c, const hb_ct *a, const hb_ct *b, int groups, hb_ct **acc) { return guard(c, [&] { *acc = do_tensor(c, a, b, *acc, groups); }); }
 int hb_rotate(hb_ctx *c, const hb_ct *a, int64_t steps, hb_ct **out) { return guard(c, [&] { *out = do_galois(c, a, c->h->galois_rot(steps)); }); }
 int hb_conjugate(hb_ctx *c, const hb_ct *a, hb_ct **out) { return guard(c, [&] { *out = do_galois(c, a, c->h->galois_conj()); }); }
 int hb_ntt(hb_ctx *c, hb_ct *a, int inverse) { return guard(c, [&] { ntt_inplace(c, a->d, (int)a->limbs(), c->qmap(a->level), inverse != 0); }); }

@@ -87,10 +87,13 @@ __global__ void k_mul2_add(u64 *__restrict__ out, const u64 *__restrict__ a, con
         out[off] = barrett128(s.hi, s.lo, m);
     }
 }
-// tensor product, optional accumulation.  grid.y = batch * n; x, y: [batch][2][n][N]; d: [batch][3][n][N]
+// tensor product, optional accumulation.  grid.y = batch * n; x, y: [groups][batch][2][n][N]; d: [batch][3][n][N]
+//   d[b] (+)= sum over the groups g of tensor(x[g][b], y[g][b])
+// (groups = 1 is the plain tensor product; several groups are several iterations of a product loop in one launch).
 __global__ void k_tensor(u64 *__restrict__ d, const u64 *__restrict__ x, const u64 *__restrict__ y, int n, LimbMap map, const PrimeConst *__restrict__ pc, int N,
-                         int accumulate) {
+                         int accumulate, int groups, int batch) {
     const int bl = blockIdx.y, b = bl / n, l = bl % n;
+    const size_t gstride = (size_t)batch * 2 * n * N;
 #pragma unroll
     for (int u_ = 0; u_ < kElems; ++u_) {
         const int i = (blockIdx.x * kElems + u_) * blockDim.x + threadIdx.x;
@@ -98,17 +101,24 @@ __global__ void k_tensor(u64 *__restrict__ d, const u64 *__restrict__ x, const u
         const PrimeConst m = pc[map.prime[l]];
         const size_t x0 = ((size_t)(b * 2) * n + l) * N + i, x1 = x0 + (size_t)n * N;
         const size_t d0 = ((size_t)(b * 3) * n + l) * N + i, d1 = d0 + (size_t)n * N, d2 = d1 + (size_t)n * N;
-        const u64 b1 = x[x0], a1 = x[x1], b2 = y[x0], a2 = y[x1];
         u64 r0, r1, r2;
-        if (m.fp) {
-            const double b1d = u52_to_double(b1), a1d = u52_to_double(a1), b2d = u52_to_double(b2), a2d = u52_to_double(a2);
-            r0 = mul_small_lazy_d(b1, b1d, b2, b2d, m.q_inv_f, m.q); r0 = r0 >= m.q ? r0 - m.q : r0;
-            r2 = mul_small_lazy_d(a1, a1d, a2, a2d, m.q_inv_f, m.q); r2 = r2 >= m.q ? r2 - m.q : r2;
-            r1 = reduce_fp(mul_small_lazy_d(a1, a1d, b2, b2d, m.q_inv_f, m.q) + mul_small_lazy_d(a2, a2d, b1, b1d, m.q_inv_f, m.q), m.q_inv_f, m.q);
+        if (m.fp) { // lazy products below 1.6q; the group count is bounded by the launcher so that the sums stay below 2^52
+            u64 s0 = 0, s1 = 0, s2 = 0;
+            for (int g = 0; g < groups; ++g) {
+                const u64 b1 = x[g * gstride + x0], a1 = x[g * gstride + x1], b2 = y[g * gstride + x0], a2 = y[g * gstride + x1];
+                const double b1d = u52_to_double(b1), a1d = u52_to_double(a1), b2d = u52_to_double(b2), a2d = u52_to_double(a2);
+                s0 += mul_small_lazy_d(b1, b1d, b2, b2d, m.q_inv_f, m.q);
+                s2 += mul_small_lazy_d(a1, a1d, a2, a2d, m.q_inv_f, m.q);
+                s1 += mul_small_lazy_d(a1, a1d, b2, b2d, m.q_inv_f, m.q) + mul_small_lazy_d(a2, a2d, b1, b1d, m.q_inv_f, m.q);
+            }
+            r0 = reduce_fp(s0, m.q_inv_f, m.q); r1 = reduce_fp(s1, m.q_inv_f, m.q); r2 = reduce_fp(s2, m.q_inv_f, m.q);
         } else {
-            r0 = mul_mod(b1, b2, m); r2 = mul_mod(a1, a2, m);
-            Acc128 s; s.zero(); s.mad(a1, b2); s.mad(a2, b1);
-            r1 = barrett128(s.hi, s.lo, m);
+            Acc128 s0, s1, s2; s0.zero(); s1.zero(); s2.zero();
+            for (int g = 0; g < groups; ++g) {
+                const u64 b1 = x[g * gstride + x0], a1 = x[g * gstride + x1], b2 = y[g * gstride + x0], a2 = y[g * gstride + x1];
+                s0.mad(b1, b2); s2.mad(a1, a2); s1.mad(a1, b2); s1.mad(a2, b1);
+            }
+            r0 = barrett128(s0.hi, s0.lo, m); r1 = barrett128(s1.hi, s1.lo, m); r2 = barrett128(s2.hi, s2.lo, m);
         }
         if (accumulate) { r0 = add_mod(r0, d[d0], m.q); r1 = add_mod(r1, d[d1], m.q); r2 = add_mod(r2, d[d2], m.q); }
         d[d0] = r0; d[d1] = r1; d[d2] = r2;
@@ -237,27 +247,44 @@ __global__ void k_lift_mod(u64 *__restrict__ t, const i64 *__restrict__ S, int l
         t[(size_t)w * N + x] = reduce_i64_any(S[(size_t)bp * N + x], pc[l]);
     }
 }
-// out[bp][l][x] = (sum_j a_j[bp][l][x] * p_j[l][x] - t[bp][l][x]) * q_level^-1.  grid.y = nbp * level
+// out[bp][l][x] = (sum_j a_j[bp][l][x] * p_j[l][x] - t[bp][l][x]) * q_level^-1.  grid = (N/(256*kElems), nbp * level).
+// The four coefficients of a thread sit in the inner loop so that eight loads of one term (and, unrolled, of the
+// next) are in flight together: the kernel streams `count` ciphertexts per output and lives on memory parallelism.
 __global__ void k_prod_rescale_fin(u64 *__restrict__ out, TermList tl, const u64 *__restrict__ t, int level, const PrimeConst *__restrict__ pc, int N, Scalars qlinv) {
     const int w = blockIdx.y, bp = w / level, l = w % level;
+    const PrimeConst m = pc[l];
+    const u32 x0 = blockIdx.x * (blockDim.x * kElems) + threadIdx.x;
+    const size_t ao = ((size_t)bp * (level + 1) + l) * N + x0, po = (size_t)l * N + x0;
+    u64 v[kElems];
+    if (m.fp) {
+        u64 acc[kElems];
 #pragma unroll
-    for (int u_ = 0; u_ < kElems; ++u_) {
-        const int x = (blockIdx.x * kElems + u_) * blockDim.x + threadIdx.x;
-        if (x >= N) break;
-        const PrimeConst m = pc[l];
-        const size_t ao = ((size_t)bp * (level + 1) + l) * N + x, po = (size_t)l * N + x;
-        u64 v;
-        if (m.fp) {
-            u64 acc = 0;
-            for (int j = 0; j < tl.count; ++j) acc += mul_small_lazy(tl.a[j][ao], tl.p[j][po], m.q_inv_f, m.q);
-            v = reduce_fp(acc, m.q_inv_f, m.q);
-        } else {
-            Acc128 s; s.zero();
-            for (int j = 0; j < tl.count; ++j) s.mad(tl.a[j][ao], tl.p[j][po]);
-            v = barrett128(s.hi, s.lo, m);
+        for (int u = 0; u < kElems; ++u) acc[u] = 0;
+#pragma unroll 2
+        for (int j = 0; j < tl.count; ++j) {
+            const u64 *a = tl.a[j] + ao, *p = tl.p[j] + po;
+#pragma unroll
+            for (int u = 0; u < kElems; ++u) acc[u] += mul_small_lazy(a[u * blockDim.x], p[u * blockDim.x], m.q_inv_f, m.q);
         }
-        out[(size_t)w * N + x] = mul_mod_any(sub_mod(v, t[(size_t)w * N + x], m.q), qlinv.v[l], m);
+#pragma unroll
+        for (int u = 0; u < kElems; ++u) v[u] = reduce_fp(acc[u], m.q_inv_f, m.q);
+    } else {
+        Acc128 s[kElems];
+#pragma unroll
+        for (int u = 0; u < kElems; ++u) s[u].zero();
+#pragma unroll 2
+        for (int j = 0; j < tl.count; ++j) {
+            const u64 *a = tl.a[j] + ao, *p = tl.p[j] + po;
+#pragma unroll
+            for (int u = 0; u < kElems; ++u) s[u].mad(a[u * blockDim.x], p[u * blockDim.x]);
+        }
+#pragma unroll
+        for (int u = 0; u < kElems; ++u) v[u] = barrett128(s[u].hi, s[u].lo, m);
     }
+    const u64 *tp = t + (size_t)w * N + x0;
+    u64 *op = out + (size_t)w * N + x0;
+#pragma unroll
+    for (int u = 0; u < kElems; ++u) op[u * blockDim.x] = mul_mod_any(sub_mod(v[u], tp[u * blockDim.x], m.q), qlinv.v[l], m);
 }
 
 // ---------------- key switching ----------------
@@ -560,12 +587,16 @@ struct MaskedRot {
     u32 g[2];
     int count;            // 1 or 2 rotations
 };
+constexpr int kMaxRotGroups = 16;
+struct MaskedRotList { MaskedRot r[kMaxRotGroups]; }; // one entry per wrapped copy made by the same launch
 // E[b][p][j][i] = sum_r sum_dg digit_dg[j][perm_r(i)] * mkey_r[dg][p][j][i]  +  (p == 0, j < n) sum_r c0[b][j][perm_r(i)] * pm_r[j][i]
-// grid = (N/(256*EL), ne, batch); EL coefficients per thread
+// grid = (N/(256*EL), ne, groups * batch); EL coefficients per thread.  Output member g * batch + b is wrapped copy
+// number g (its own pair of masked keys) of input member b: several iterations of a shift loop in one launch.
 template <int EL>
-__global__ void __launch_bounds__(256, EL == 2 ? 3 : 2) k_ks_inner_mk(u64 *__restrict__ E, const u64 *__restrict__ c0, const u64 *__restrict__ a_ntt, size_t a_outer, const u64 *__restrict__ dt, MaskedRot mr,
-                              const KsPlan *__restrict__ pl, const PrimeConst *__restrict__ pc, int logn, int N) {
-    const int j = blockIdx.y, b = blockIdx.z;
+__global__ void __launch_bounds__(256, EL == 2 ? 3 : 2) k_ks_inner_mk(u64 *__restrict__ E, const u64 *__restrict__ c0, const u64 *__restrict__ a_ntt, size_t a_outer, const u64 *__restrict__ dt, MaskedRotList mrl,
+                              int batch, const KsPlan *__restrict__ pl, const PrimeConst *__restrict__ pc, int logn, int N) {
+    const int j = blockIdx.y, ob = blockIdx.z, b = ob % batch;
+    const MaskedRot &mr = mrl.r[ob / batch];
     const int pj = pl->ext_prime[j], nd = pl->nd, ne = pl->ne, n = pl->n;
     const PrimeConst m = pc[pj];
     const u32 x0 = blockIdx.x * (blockDim.x * EL) + threadIdx.x;
@@ -631,7 +662,7 @@ __global__ void __launch_bounds__(256, EL == 2 ? 3 : 2) k_ks_inner_mk(u64 *__res
 #pragma unroll
         for (int u = 0; u < EL; ++u) { r0[u] = barrett128(s0[u].hi, s0[u].lo, m); r1[u] = barrett128(s1[u].hi, s1[u].lo, m); }
     }
-    u64 *o0 = E + (((size_t)b * 2) * ne + j) * N + x0, *o1 = o0 + (size_t)ne * N;
+    u64 *o0 = E + (((size_t)ob * 2) * ne + j) * N + x0, *o1 = o0 + (size_t)ne * N;
 #pragma unroll
     for (int u = 0; u < EL; ++u) { o0[u * blockDim.x] = r0[u]; o1[u * blockDim.x] = r1[u]; }
 }
@@ -778,41 +809,68 @@ struct PtList { const u64 *p[16]; };
 __global__ void k_matmul_acc(u64 *__restrict__ out, const u64 *__restrict__ pre, int kcount, int btotal, int b0, int bcount, PtList pts, const u32 *__restrict__ gal,
                              int n, LimbMap map, const PrimeConst *__restrict__ pc, int logn, int N) {
     const int pl = blockIdx.y, l = pl % n;
+    const PrimeConst m = pc[map.prime[l]];
+    const size_t estride = (size_t)2 * n * N;
+    const u32 x0 = blockIdx.x * (blockDim.x * kElems) + threadIdx.x;
+    const u64 *pbase = pre + (size_t)pl * N + x0;
+    u64 total[kElems];
 #pragma unroll
-    for (int u_ = 0; u_ < kElems; ++u_) {
-        const int i = (blockIdx.x * kElems + u_) * blockDim.x + threadIdx.x;
-        if (i >= N) break;
-        const PrimeConst m = pc[map.prime[l]];
-        const size_t estride = (size_t)2 * n * N;
-        u64 total = 0;
-        if (m.fp) { // lazy terms below 1.6q: thousands fit in 64 bits
-            u64 acc = 0;
-            int terms = 0;
-            for (int k = 0; k < kcount; ++k) {
-                const u32 g = __ldg(gal + k);
-                const u32 src = g == 1 ? (u32)i : ntt_perm((u32)i, g, logn);
-                for (int b = 0; b < bcount; ++b) {
-                    acc += mul_small_lazy(pre[((size_t)k * btotal + b0 + b) * estride + (size_t)pl * N + i], pts.p[b][(size_t)l * N + src], m.q_inv_f, m.q);
-                    if (++terms == 256) { total = add_mod(total, reduce_fp(acc, m.q_inv_f, m.q), m.q); acc = 0; terms = 0; }
-                }
+    for (int u = 0; u < kElems; ++u) total[u] = 0;
+    // the four coefficients of a thread sit in the inner loop: their loads (and those of the next K-group) overlap
+    if (m.fp) { // lazy terms below 1.6q: thousands fit in 64 bits
+        u64 acc[kElems];
+#pragma unroll
+        for (int u = 0; u < kElems; ++u) acc[u] = 0;
+        int terms = 0;
+        for (int k = 0; k < kcount; ++k) {
+            const u32 g = __ldg(gal + k);
+            u32 src[kElems];
+#pragma unroll
+            for (int u = 0; u < kElems; ++u) src[u] = g == 1 ? x0 + u * blockDim.x : ntt_perm(x0 + u * blockDim.x, g, logn);
+#pragma unroll 2
+            for (int b = 0; b < bcount; ++b) {
+                const u64 *a = pbase + ((size_t)k * btotal + b0 + b) * estride, *w = pts.p[b] + (size_t)l * N;
+#pragma unroll
+                for (int u = 0; u < kElems; ++u) acc[u] += mul_small_lazy(a[u * blockDim.x], w[src[u]], m.q_inv_f, m.q);
             }
-            total = add_mod(total, reduce_fp(acc, m.q_inv_f, m.q), m.q);
-        } else {
-            Acc128 s; s.zero();
-            int terms = 0;
-            for (int k = 0; k < kcount; ++k) {
-                const u32 g = __ldg(gal + k);
-                const u32 src = g == 1 ? (u32)i : ntt_perm((u32)i, g, logn);
-                for (int b = 0; b < bcount; ++b) {
-                    const u64 w = pts.p[b][(size_t)l * N + src];
-                    s.mad(pre[((size_t)k * btotal + b0 + b) * estride + (size_t)pl * N + i], w);
-                    if (++terms == 64) { total = add_mod(total, barrett128(s.hi, s.lo, m), m.q); s.zero(); terms = 0; }
-                }
+            terms += bcount;
+            if (terms >= 256) {
+#pragma unroll
+                for (int u = 0; u < kElems; ++u) { total[u] = add_mod(total[u], reduce_fp(acc[u], m.q_inv_f, m.q), m.q); acc[u] = 0; }
+                terms = 0;
             }
-            total = add_mod(total, barrett128(s.hi, s.lo, m), m.q);
         }
-        out[(size_t)pl * N + i] = total;
+#pragma unroll
+        for (int u = 0; u < kElems; ++u) total[u] = add_mod(total[u], reduce_fp(acc[u], m.q_inv_f, m.q), m.q);
+    } else {
+        Acc128 s[kElems];
+#pragma unroll
+        for (int u = 0; u < kElems; ++u) s[u].zero();
+        int terms = 0;
+        for (int k = 0; k < kcount; ++k) {
+            const u32 g = __ldg(gal + k);
+            u32 src[kElems];
+#pragma unroll
+            for (int u = 0; u < kElems; ++u) src[u] = g == 1 ? x0 + u * blockDim.x : ntt_perm(x0 + u * blockDim.x, g, logn);
+#pragma unroll 2
+            for (int b = 0; b < bcount; ++b) {
+                const u64 *a = pbase + ((size_t)k * btotal + b0 + b) * estride, *w = pts.p[b] + (size_t)l * N;
+#pragma unroll
+                for (int u = 0; u < kElems; ++u) s[u].mad(a[u * blockDim.x], w[src[u]]);
+            }
+            terms += bcount;
+            if (terms >= 48) { // products below 2^120: the 128-bit accumulator holds 256 of them
+#pragma unroll
+                for (int u = 0; u < kElems; ++u) { total[u] = add_mod(total[u], barrett128(s[u].hi, s[u].lo, m), m.q); s[u].zero(); }
+                terms = 0;
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < kElems; ++u) total[u] = add_mod(total[u], barrett128(s[u].hi, s[u].lo, m), m.q);
     }
+    u64 *op = out + (size_t)pl * N + x0;
+#pragma unroll
+    for (int u = 0; u < kElems; ++u) op[u * blockDim.x] = total[u];
 }
 
 } // namespace hb

@@ -174,6 +174,12 @@ int hb_assemble_hoisted(hb_ctx *ctx, const hb_ct *a, const hb_digits *digits, in
 int hb_masked_key_create(hb_ctx *ctx, int64_t left_steps, const hb_pt *m1, const hb_pt *m2, hb_mkey **out);
 void hb_masked_key_free(hb_mkey *key);
 int hb_assemble_masked(hb_ctx *ctx, const hb_ct *a, const hb_digits *digits, const hb_mkey *k1, const hb_mkey *k2, hb_ct **out);
+/* `groups` wrapped copies of the same input in one launch sequence: copy g uses k1s[g] and k2s[g] (k2s, or single
+ * entries of it, may be NULL).  `out` holds groups * batch(a) members, member g * batch(a) + b = copy g of input b,
+ * each bit for bit what hb_assemble_masked gives.  At most 16 groups.  Several iterations of a shift loop at once,
+ * for batches too small to fill the GPU on their own. */
+int hb_assemble_masked_multi(hb_ctx *ctx, const hb_ct *a, const hb_digits *digits, const hb_mkey *const *k1s, const hb_mkey *const *k2s,
+                             int groups, hb_ct **out);
 /* raw forward / inverse NTT of every limb of the batch, in place (primitive sweep) */
 int hb_ntt(hb_ctx *ctx, hb_ct *a, int inverse);
 
@@ -185,6 +191,9 @@ int hb_mul2_add_rescale(hb_ctx *ctx, const hb_ct *a, const hb_pt *pa, const hb_c
 int hb_mul_pt_sum(hb_ctx *ctx, const hb_ct *const *a, const hb_pt *const *p, int count, hb_ct **out);
 /* acc += tensor(a, b); *acc may be NULL on entry -- MatrixUtils.cpp:1434-1439 */
 int hb_tensor_acc(hb_ctx *ctx, const hb_ct *a, const hb_ct *b, hb_ct **acc);
+/* *acc (+)= sum over g < groups of tensor(a[g], b[g]); a and b hold groups * batch members (group-major), *acc holds
+ * batch members (NULL: created).  Same residues as `groups` calls of hb_tensor_acc. */
+int hb_tensor_acc_groups(hb_ctx *ctx, const hb_ct *a, const hb_ct *b, int groups, hb_ct **acc);
 /* out = sum_k pre[k] (.) rot_rows(pt, k * row_step), un-rescaled -- HomEvaluator::matmul :595-601 */
 int hb_matmul_acc(hb_ctx *ctx, const hb_ct *pre, const hb_pt *pt, int64_t row_step, hb_ct **out);
 /* the same over several K-groups at once: `pre` holds the shifted copies of `btotal` independent inputs, copy k of
