@@ -340,6 +340,21 @@ def run_gpu(args):
         alg = (nbk * 4 * n + 2 * beta * (n + 3)) * LIMB
         ks[f"rotate_l{lv}"] = {"algorithmic_bytes": alg, "ms": ms, "gbs": alg / ms / 1e6, "frac": alg / ms / 1e6 / hbm}
         del cb
+    # one wrapped copy of a shift loop (schedule 2) at the level of the layer's product loops: two masked rotations of
+    # the batch and one division by P*q_l.  Ciphertexts in (2n) and out (2(n-1)); the two masked keys once per batch.
+    lv, nbk = 6, 32
+    cb = lib.ct_create(lv, 2, nbk)
+    lib.ct_zero(cb)
+    lib.gen_rot_keys([1, -127])
+    ones = np.ones(lib.slots)
+    k1, k2 = lib.masked_key(1, lib.encode_ext(ones, lv)), lib.masked_key(-127, lib.encode_ext(ones, lv))
+    dgt = lib.decompose(cb)
+    for _ in range(2):
+        lib.assemble_masked(cb, dgt, k1, k2)
+    ms = timed_single(torch, stream, lib, lambda: lib.assemble_masked(cb, dgt, k1, k2), 5)
+    alg = (nbk * (4 * (lv + 1) - 2) + 2 * 2 * 2 * (lv + 4)) * LIMB
+    ks["wrapped_copy_l6"] = {"algorithmic_bytes": alg, "ms": ms, "gbs": alg / ms / 1e6, "frac": alg / ms / 1e6 / hbm}
+    del cb, dgt, k1, k2
     top = roof["ntt"]
     # two launches (column pass, row pass) make one transform: per-launch algorithmic bytes are half of the transform's
     roofline = {"bound": "hbm", "kernel": "ntt16_fwd_cols+ntt16_fwd_rows (one forward NTT of 64 ciphertexts, level 12)", "achieved": top["gbs"], "peak": hbm,

@@ -259,6 +259,11 @@ void ccmmPrepare(Env &e, const CtxtTensor &op1, const CtxtTensor &op2, int targe
     if (std::min(op1.getLevel(), op2.getLevel()) < target_level + 3) throw std::invalid_argument("[multMatMat] level too low");
     const TileTensorShape sa(num_rows, num_k, width), sb(num_k, num_cols, width);
     const int lvl = target_level + 2;
+    if (e.mode == kLazy) { // transforms at the lowest level that still leaves target + 2: far fewer limbs to transform
+        sa_out = diagonalToColumn(e, CtxtTensor(sa, e.ev.levelDown(op1.get(), target_level + 3))).get();
+        tb_out = diagonalToRow(e, CtxtTensor(sb, e.ev.levelDown(op2.get(), target_level + 3))).get();
+        return;
+    }
     sa_out = e.ev.levelDown(diagonalToColumn(e, CtxtTensor(sa, op1.get())).get(), lvl);
     tb_out = e.ev.levelDown(diagonalToRow(e, CtxtTensor(sb, op2.get())).get(), lvl);
 }

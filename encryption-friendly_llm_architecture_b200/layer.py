@@ -215,7 +215,9 @@ class LayerWorkload:
             transposed = {}
             if need:
                 joined = CtxtTensor(lib.batch_concat([x.ct for x in need]) if len(need) > 1 else need[0].ct, D, D, 2 * D)
-                H.transpose_inplace(joined)
+                # schedule 2 transposes at the lowest level that leaves target + 3 for sigma / tau (transposeInplace's
+                # own target_level argument, HEMMer.cpp:1166-1172); the other schedules transpose at the input level
+                H.transpose_inplace(joined, t + 3 if getattr(H, "schedule", 0) == 2 else 0)
                 pos = 0
                 for tr in order:
                     if tr is False:

@@ -56,7 +56,9 @@ struct Hemmer {
     //    Same slots, different ciphertext bits (fewer chained key switches).  The CUDA library implements the
     //    same variant with hoisting; both variants are compared bit for bit.
     // 2: as 1, and the masked pair of rotations that makes a wrapped copy is one Evaluator::assemble_rot (one
-    //    division by P * q_level for the pair) in the product loop and in multMatMatPre.
+    //    division by P * q_level for the pair) in the product loop and in multMatMatPre; multMatMat brings its operands
+    //    down to target + 3 BEFORE sigma / tau instead of after (MatrixUtils.cpp:1346-1361 transforms at the operands'
+    //    level), the order multMatMatPre (:1583) and the low-rank products (:1692) use.
     int mode = 0;
 
     Hemmer(Context &c, Evaluator &e) : cx(c), ev(e), slots(c.slots) {
@@ -391,6 +393,10 @@ struct Hemmer {
         if (std::min(op1.ct.level, op2.ct.level) < target_level + 3) throw std::invalid_argument("[multMatMat] level too low");
         CtT a = op1, b = op2;
         a.sh = Shape(num_rows, num_k, width); b.sh = Shape(num_k, num_cols, width);
+        if (mode == 2) { // transforms at the lowest level that still leaves target + 2 (as multMatMatPre and the low-rank products do)
+            a.ct = ev.level_down(a.ct, target_level + 3);
+            b.ct = ev.level_down(b.ct, target_level + 3);
+        }
         a = diagonal_to_column(a);
         b = diagonal_to_row(b);
         sa = ev.level_down(a.ct, target_level + 2);
