@@ -252,7 +252,7 @@ void ks_apply(hb_ctx *c, const u64 *a, size_t a_outer, const u64 *dt, int level,
     const int N = c->N, n = d.n, ne = d.ne, K = d.K;
     const unsigned gx1 = (unsigned)((N + 255) / 256), gx = c->gx();
     Tmp acc(c, (size_t)batch * 2 * ne), pco(c, (size_t)batch * 2 * K), t(c, (size_t)batch * 2 * n);
-    LAUNCH(c), k_ks_inner<<<dim3(gx, ne, batch), 256, 0, c->st>>>(acc.p, a, a_outer, dt, key.d, c->nprimes, pl, c->pc, g, c->logn, N);
+    LAUNCH(c), k_ks_inner<<<dim3(gx, batch, ne), 256, 0, c->st>>>(acc.p, a, a_outer, dt, key.d, c->nprimes, pl, c->pc, g, c->logn, N);
     LimbMap pm{}; pm.n = K; for (int k = 0; k < K; ++k) pm.prime[k] = (unsigned char)(c->L + 1 + k);
     ntt(c, acc.p + (size_t)n * N, (size_t)ne * N, pco.p, (size_t)K * N, batch * 2 * K, pm, true);
     LAUNCH(c), k_moddown_conv<<<dim3(gx1, 1, batch * 2), 256, 0, c->st>>>(t.p, pco.p, pl, c->pc, c->L + 1, N);
@@ -404,7 +404,7 @@ hb_ct *do_assemble_mk(hb_ctx *c, const hb_ct *a, const u64 *dt, const hb_mkey *c
     const int n = d.n, ne = d.ne;
     Tmp E(c, (size_t)groups * batch * 2 * ne);
     constexpr int kEl = 4; // coefficients per thread (2, with three CTAs resident per SM, measured no faster)
-    LAUNCH(c), k_ks_inner_mk<kEl><<<dim3((unsigned)((N + 256 * kEl - 1) / (256 * kEl)), ne, groups * batch), 256, 0, c->st>>>(E.p, a->d, a->d + (size_t)n * N, (size_t)2 * n * N, dt, mrl, batch, pl, c->pc,
+    LAUNCH(c), k_ks_inner_mk<kEl><<<dim3((unsigned)((N + 256 * kEl - 1) / (256 * kEl)), groups * batch, ne), 256, 0, c->st>>>(E.p, a->d, a->d + (size_t)n * N, (size_t)2 * n * N, dt, mrl, batch, pl, c->pc,
                                                                                                                         c->logn, N);
     return divide_by_p_ql(c, E.p, level, groups * batch);
 }
@@ -457,7 +457,7 @@ hb_ct *do_prod_rescale(hb_ctx *c, const hb_ct *const *a, const hb_pt *const *p, 
         ntt_inplace(c, t.p, nbp * l, c->qmap(l - 1), false);
         Scalars qi{};
         for (int i = 0; i < l; ++i) qi.v[i] = hbhost::invmod(c->h->q[l] % c->h->q[i], c->h->q[i]);
-        LAUNCH(c), k_prod_rescale_fin<<<c->egrid(nbp * l), 256, 0, c->st>>>(r->d, tl, t.p, l, c->pc, N, qi);
+        LAUNCH(c), k_prod_rescale_fin<<<c->egrid(nbp * l), 256, 0, c->st>>>(r->d, tl, t.p, l, nbp, c->pc, N, qi);
         CK(cudaGetLastError());
     } catch (...) { hb_ct_free(r); throw; }
     return r;

@@ -250,8 +250,10 @@ __global__ void k_lift_mod(u64 *__restrict__ t, const i64 *__restrict__ S, int l
 // out[bp][l][x] = (sum_j a_j[bp][l][x] * p_j[l][x] - t[bp][l][x]) * q_level^-1.  grid = (N/(256*kElems), nbp * level).
 // The four coefficients of a thread sit in the inner loop so that eight loads of one term (and, unrolled, of the
 // next) are in flight together: the kernel streams `count` ciphertexts per output and lives on memory parallelism.
-__global__ void k_prod_rescale_fin(u64 *__restrict__ out, TermList tl, const u64 *__restrict__ t, int level, const PrimeConst *__restrict__ pc, int N, Scalars qlinv) {
-    const int w = blockIdx.y, bp = w / level, l = w % level;
+// Blocks are ordered limb-major (all batch members of limb 0, then of limb 1, ...): the plaintext limbs of a sum are
+// shared by every member, and in this order they stay in L2 while the members stream past.
+__global__ void k_prod_rescale_fin(u64 *__restrict__ out, TermList tl, const u64 *__restrict__ t, int level, int nbp, const PrimeConst *__restrict__ pc, int N, Scalars qlinv) {
+    const int l = blockIdx.y / nbp, bp = blockIdx.y % nbp, w = bp * level + l;
     const PrimeConst m = pc[l];
     const u32 x0 = blockIdx.x * (blockDim.x * kElems) + threadIdx.x;
     const size_t ao = ((size_t)bp * (level + 1) + l) * N + x0, po = (size_t)l * N + x0;
@@ -343,10 +345,10 @@ __global__ void k_modup(u64 *__restrict__ dt, const u64 *__restrict__ a_coef, co
 
 // Inner product with the switching key over Q_level u P.
 //   acc[b][p][j][i] = sum_dg digit_dg[j][perm_g(i)] * key[dg][p][prime(j)][i]
-// digit_dg[j] is a_ntt[j] for own limbs and dt[...] otherwise.  grid = (N/256, ne, batch)
+// digit_dg[j] is a_ntt[j] for own limbs and dt[...] otherwise.  grid = (N/(256*kElems), batch, ne)
 __global__ void k_ks_inner(u64 *__restrict__ acc, const u64 *__restrict__ a_ntt, size_t a_outer, const u64 *__restrict__ dt, const u64 *__restrict__ key, int key_primes,
                            const KsPlan *__restrict__ pl, const PrimeConst *__restrict__ pc, u32 g, int logn, int N) {
-    const int j = blockIdx.y, b = blockIdx.z;
+    const int j = blockIdx.z, b = blockIdx.y; // limb-major block order: the key limbs stay in L2 across the members
     const int pj = pl->ext_prime[j], nd = pl->nd, ne = pl->ne;
     const PrimeConst m = pc[pj];
     const u32 x0 = blockIdx.x * (blockDim.x * kElems) + threadIdx.x;
@@ -590,12 +592,12 @@ struct MaskedRot {
 constexpr int kMaxRotGroups = 16;
 struct MaskedRotList { MaskedRot r[kMaxRotGroups]; }; // one entry per wrapped copy made by the same launch
 // E[b][p][j][i] = sum_r sum_dg digit_dg[j][perm_r(i)] * mkey_r[dg][p][j][i]  +  (p == 0, j < n) sum_r c0[b][j][perm_r(i)] * pm_r[j][i]
-// grid = (N/(256*EL), ne, groups * batch); EL coefficients per thread.  Output member g * batch + b is wrapped copy
+// grid = (N/(256*EL), groups * batch, ne); EL coefficients per thread.  Output member g * batch + b is wrapped copy
 // number g (its own pair of masked keys) of input member b: several iterations of a shift loop in one launch.
 template <int EL>
 __global__ void __launch_bounds__(256, EL == 2 ? 3 : 2) k_ks_inner_mk(u64 *__restrict__ E, const u64 *__restrict__ c0, const u64 *__restrict__ a_ntt, size_t a_outer, const u64 *__restrict__ dt, MaskedRotList mrl,
                               int batch, const KsPlan *__restrict__ pl, const PrimeConst *__restrict__ pc, int logn, int N) {
-    const int j = blockIdx.y, ob = blockIdx.z, b = ob % batch;
+    const int j = blockIdx.z, ob = blockIdx.y, b = ob % batch; // limb-major block order: the key limbs stay in L2 across the members
     const MaskedRot &mr = mrl.r[ob / batch];
     const int pj = pl->ext_prime[j], nd = pl->nd, ne = pl->ne, n = pl->n;
     const PrimeConst m = pc[pj];
