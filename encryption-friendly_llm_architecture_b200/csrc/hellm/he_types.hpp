@@ -194,6 +194,13 @@ class Evaluator {
         for (auto *x : p) rp.push_back(x->raw());
         hb_ct *o = nullptr; check(c_, hb_mul_pt_sum(c_, ra.data(), rp.data(), (int)ra.size(), &o)); return Ciphertext(c_, o);
     }
+    // rescale(sum_j multWithoutRescale(a[j], p[j])): one rescale for the whole sum
+    Ciphertext multSumRescaledOnce(const std::vector<const Ciphertext *> &a, const std::vector<const Plaintext *> &p) const {
+        std::vector<const hb_ct *> ra; std::vector<const hb_pt *> rp;
+        for (auto *x : a) ra.push_back(x->raw());
+        for (auto *x : p) rp.push_back(x->raw());
+        hb_ct *o = nullptr; check(c_, hb_sum_mul_pt_rescale(c_, ra.data(), rp.data(), (int)ra.size(), &o)); return Ciphertext(c_, o);
+    }
     // acc += tensor(a, b)
     void tensorAccumulate(Ciphertext &acc, const Ciphertext &a, const Ciphertext &b) const {
         hb_ct *p = acc.release();

@@ -130,7 +130,7 @@ Ciphertext bsgs_diagonals(Env &e, const Ciphertext &op, const TileTensorShape &s
                 if (++idx >= limit) break;
                 cts.push_back(&baby[(size_t)j]); pts.push_back(&mask(idx));
             }
-            Ciphertext part = e.ev.multSum(cts, pts);
+            Ciphertext part = e.mode == kLazy ? e.ev.multSumRescaledOnce(cts, pts) : e.ev.multSum(cts, pts);
             part = sign < 0 ? e.ev.rightRotate(part, f.main * f.gap - rot_num) : e.ev.leftRotate(part, rot_num);
             res = e.ev.add(res, part);
         }
@@ -231,7 +231,7 @@ CtxtTensor transpose(Env &e, const CtxtTensor &op) {
             if (++idx >= num_cols) break;
             cts.push_back(&baby[(size_t)j]); pts.push_back(&mask(idx));
         }
-        Ciphertext part = e.ev.multSum(cts, pts);
+        Ciphertext part = e.mode == kLazy ? e.ev.multSumRescaledOnce(cts, pts) : e.ev.multSum(cts, pts);
         if (i == 0) res = std::move(part);
         else res = e.ev.add(res, e.ev.leftRotate(part, i * bs * gap));
     }

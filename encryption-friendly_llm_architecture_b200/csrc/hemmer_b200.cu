@@ -998,6 +998,9 @@ int hb_mul_pt(hb_ctx *c, const hb_ct *a, const hb_pt *p, hb_ct **out) { return g
 int hb_mul_pt_sum(hb_ctx *c, const hb_ct *const *a, const hb_pt *const *p, int count, hb_ct **out) {
     return guard(c, [&] { *out = do_prod_rescale(c, a, p, count, true); });
 }
+int hb_sum_mul_pt_rescale(hb_ctx *c, const hb_ct *const *a, const hb_pt *const *p, int count, hb_ct **out) {
+    return guard(c, [&] { *out = do_prod_rescale(c, a, p, count, false); });
+}
 int hb_rescale(hb_ctx *c, const hb_ct *a, hb_ct **out) { return guard(c, [&] { *out = do_rescale(c, a); }); }
 int hb_rescale_noalloc(hb_ctx *c, const hb_ct *a, hb_ct *out) {
     return guard(c, [&] {

@@ -189,6 +189,9 @@ int hb_mul2_add_rescale(hb_ctx *ctx, const hb_ct *a, const hb_pt *pa, const hb_c
 /* out = sum_j mult(a[j], p[j])  (each product rescaled, then added) -- the baby-step sums of the linear
  * transforms, MatrixUtils.cpp:815-823, 832-840.  At most 24 terms. */
 int hb_mul_pt_sum(hb_ctx *ctx, const hb_ct *const *a, const hb_pt *const *p, int count, hb_ct **out);
+/* out = rescale(sum_j a[j] (.) p[j]): the products are added un-rescaled and the sum is rescaled once (one inverse
+ * transform of the last limb instead of one per term).  The masked sums of the linear transforms in schedule 2. */
+int hb_sum_mul_pt_rescale(hb_ctx *ctx, const hb_ct *const *a, const hb_pt *const *p, int count, hb_ct **out);
 /* acc += tensor(a, b); *acc may be NULL on entry -- MatrixUtils.cpp:1434-1439 */
 int hb_tensor_acc(hb_ctx *ctx, const hb_ct *a, const hb_ct *b, hb_ct **acc);
 /* *acc (+)= sum over g < groups of tensor(a[g], b[g]); a and b hold groups * batch members (group-major), *acc holds

@@ -58,7 +58,8 @@ struct Hemmer {
     // 2: as 1, and the masked pair of rotations that makes a wrapped copy is one Evaluator::assemble_rot (one
     //    division by P * q_level for the pair) in the product loop and in multMatMatPre; multMatMat brings its operands
     //    down to target + 3 BEFORE sigma / tau instead of after (MatrixUtils.cpp:1346-1361 transforms at the operands'
-    //    level), the order multMatMatPre (:1583) and the low-rank products (:1692) use.
+    //    level), the order multMatMatPre (:1583) and the low-rank products (:1692) use; the masked sums of the
+    //    baby-step / giant-step transforms are rescaled once per sum instead of once per term (MaskedSum).
     int mode = 0;
 
     Hemmer(Context &c, Evaluator &e) : cx(c), ev(e), slots(c.slots) {
@@ -76,6 +77,18 @@ struct Hemmer {
     }
     // eval.mult(ct, Message) -- HomEvaluator.hpp:287-289
     Ct mult_msg(const Ct &x, Mask &m) { return ev.mul_pt(x, enc_mask(m, x.level)); }
+    // One masked sum of a baby-step / giant-step transform.  The reference rescales every product and adds the
+    // results (eval.mult(ct, Message) per term); schedule 2 adds the un-rescaled products and rescales the sum once.
+    struct MaskedSum {
+        Hemmer &h; Ct acc; bool any = false;
+        explicit MaskedSum(Hemmer &hh) : h(hh) {}
+        void add(const Ct &x, Mask &m) {
+            Ct t = h.mode == 2 ? h.ev.mul_pt_norescale(x, h.enc_mask(m, x.level)) : h.mult_msg(x, m);
+            acc = any ? h.ev.add(acc, t) : t;
+            any = true;
+        }
+        Ct result() { return h.mode == 2 ? h.ev.rescale(acc) : acc; }
+    };
 
     // ---------------- TransformMask generators ----------------
     // generateDiagoanlMask -- MatrixUtils.cpp:90-127
@@ -303,12 +316,13 @@ struct Hemmer {
         Ct res, gs_tmp;
         for (i64 i = 0; i < gs; i++) {
             i64 idx = 1 - num_rows + i * bs;
-            Ct &acc = (i == 0) ? res : gs_tmp;
-            acc = mult_msg(bs_rot[0], dm[idx]);
+            MaskedSum sum(*this);
+            sum.add(bs_rot[0], dm[idx]);
             for (i64 j = 1; j < bs; j++) {
                 if (++idx >= num_cols) break;
-                acc = ev.add(acc, mult_msg(bs_rot[(size_t)j], dm[idx]));
+                sum.add(bs_rot[(size_t)j], dm[idx]);
             }
+            ((i == 0) ? res : gs_tmp) = sum.result();
             if (i > 0) {
                 gs_tmp = rotL(gs_tmp, (i * bs) * gap);
                 res = ev.add(res, gs_tmp);
@@ -333,20 +347,22 @@ struct Hemmer {
         for (i64 i = 0; i < gs; i++) {
             const i64 rot_num = i * bs * gap;
             i64 idx = 1 + i * bs - main_dim;
-            Ct gs_tmp = mult_msg(bs_rot[0], mask[idx]);
+            MaskedSum neg(*this);
+            neg.add(bs_rot[0], mask[idx]);
             for (i64 j = 1; j < bs; j++) {
                 if (++idx >= sub_dim - main_dim) break;
-                gs_tmp = ev.add(gs_tmp, mult_msg(bs_rot[(size_t)j], mask[idx]));
+                neg.add(bs_rot[(size_t)j], mask[idx]);
             }
-            gs_tmp = rotR(gs_tmp, main_dim * gap - rot_num);
+            Ct gs_tmp = rotR(neg.result(), main_dim * gap - rot_num);
             res = ev.add(res, gs_tmp);
             idx = 1 + i * bs;
-            gs_tmp = mult_msg(bs_rot[0], mask[idx]);
+            MaskedSum pos(*this);
+            pos.add(bs_rot[0], mask[idx]);
             for (i64 j = 1; j < bs; j++) {
                 if (++idx >= sub_dim) break;
-                gs_tmp = ev.add(gs_tmp, mult_msg(bs_rot[(size_t)j], mask[idx]));
+                pos.add(bs_rot[(size_t)j], mask[idx]);
             }
-            gs_tmp = rotL(gs_tmp, rot_num);
+            gs_tmp = rotL(pos.result(), rot_num);
             res = ev.add(res, gs_tmp);
         }
         return res;
