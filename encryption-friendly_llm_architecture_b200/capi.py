@@ -254,6 +254,13 @@ class Lib:
     def rotate(self, a, s): return self._op("rotate", a.ptr, C.c_int64(s))
     def conjugate(self, a): return self._op("conjugate", a.ptr)
 
+    def rotate_sum(self, xs, steps):
+        """sum_t rot(xs[t], steps[t]) with one ModDown for the whole sum."""
+        n = len(xs)
+        arr = (C.c_void_p * n)(*[x.ptr.value for x in xs])
+        st = (C.c_int64 * n)(*[int(v) for v in steps])
+        return self._op("rotate_sum", arr, st, C.c_int(n))
+
     def assemble_rot(self, a, s1, p1, s2, p2):
         """rescale(p1 (.) rot(a, s1) + p2 (.) rot(a, s2)) with one division by P * q_level for the sum."""
         return self._op("assemble_rot", a.ptr, C.c_int64(s1), p1.ptr, C.c_int64(s2), p2.ptr)

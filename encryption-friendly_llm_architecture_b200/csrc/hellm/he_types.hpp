@@ -147,6 +147,13 @@ class Evaluator {
         check(c_, hb_gen_rot_keys(c_, &steps, 1));
         hb_ct *o = nullptr; check(c_, hb_rotate_hoisted(c_, a.raw(), h.raw(), steps, &o)); return Ciphertext(c_, o);
     }
+    // sum_t leftRotate(x[t], steps[t]) with one ModDown for the whole sum
+    Ciphertext rotateSum(const std::vector<Ciphertext> &x, const std::vector<i64> &steps) const {
+        check(c_, hb_gen_rot_keys(c_, steps.data(), (int)steps.size()));
+        std::vector<const hb_ct *> raw;
+        for (const auto &v : x) raw.push_back(v.raw());
+        hb_ct *o = nullptr; check(c_, hb_rotate_sum(c_, raw.data(), steps.data(), (int)raw.size(), &o)); return Ciphertext(c_, o);
+    }
     Plaintext mult(const Plaintext &a, const Plaintext &b) const { hb_pt *o = nullptr; check(c_, hb_pt_mul(c_, a.raw(), b.raw(), &o)); return Plaintext(o); }
     Plaintext add(const Plaintext &a, const Plaintext &b) const { hb_pt *o = nullptr; check(c_, hb_pt_add(c_, a.raw(), b.raw(), &o)); return Plaintext(o); }
     Plaintext leftRotate(const Plaintext &p, i64 steps) const { hb_pt *o = nullptr; check(c_, hb_pt_rotate(c_, p.raw(), steps, &o)); return Plaintext(o); }

@@ -117,7 +117,10 @@ Ciphertext bsgs_diagonals(Env &e, const Ciphertext &op, const TileTensorShape &s
         baby.push_back(e.ev.leftRotate(op, f.gap));
         for (i64 j = 1; j < f.bs; ++j) baby.push_back(e.ev.leftRotate(baby.back(), f.gap));
     }
+    // kLazy: the parts and their giant steps are collected and rotated by ONE call that shares the ModDown
+    std::vector<Ciphertext> parts; std::vector<i64> part_steps;
     Ciphertext res = e.ev.mult(op, mask(0));
+    if (e.mode == kLazy) { parts.push_back(std::move(res)); part_steps.push_back(0); }
     for (i64 i = 0; i < f.gs; ++i) {
         const i64 rot_num = i * f.bs * f.gap;
         for (int sign = -1; sign <= 1; sign += 2) { // negative diagonals first, then positive
@@ -130,11 +133,17 @@ Ciphertext bsgs_diagonals(Env &e, const Ciphertext &op, const TileTensorShape &s
                 if (++idx >= limit) break;
                 cts.push_back(&baby[(size_t)j]); pts.push_back(&mask(idx));
             }
-            Ciphertext part = e.mode == kLazy ? e.ev.multSumRescaledOnce(cts, pts) : e.ev.multSum(cts, pts);
+            if (e.mode == kLazy) {
+                parts.push_back(e.ev.multSumRescaledOnce(cts, pts));
+                part_steps.push_back(sign < 0 ? -(f.main * f.gap - rot_num) : rot_num);
+                continue;
+            }
+            Ciphertext part = e.ev.multSum(cts, pts);
             part = sign < 0 ? e.ev.rightRotate(part, f.main * f.gap - rot_num) : e.ev.leftRotate(part, rot_num);
             res = e.ev.add(res, part);
         }
     }
+    if (e.mode == kLazy) return e.ev.rotateSum(parts, part_steps);
     return res;
 }
 
@@ -223,6 +232,7 @@ CtxtTensor transpose(Env &e, const CtxtTensor &op) {
         for (i64 j = 1; j < bs; ++j) baby.push_back(e.ev.leftRotate(baby.back(), gap));
     }
     Ciphertext res;
+    std::vector<Ciphertext> parts; std::vector<i64> part_steps; // kLazy: all giant steps in one call
     for (i64 i = 0; i < gs; ++i) {
         i64 idx = 1 - num_rows + i * bs;
         std::vector<const Ciphertext *> cts{&baby[0]};
@@ -231,10 +241,12 @@ CtxtTensor transpose(Env &e, const CtxtTensor &op) {
             if (++idx >= num_cols) break;
             cts.push_back(&baby[(size_t)j]); pts.push_back(&mask(idx));
         }
-        Ciphertext part = e.mode == kLazy ? e.ev.multSumRescaledOnce(cts, pts) : e.ev.multSum(cts, pts);
+        if (e.mode == kLazy) { parts.push_back(e.ev.multSumRescaledOnce(cts, pts)); part_steps.push_back(i * bs * gap); continue; }
+        Ciphertext part = e.ev.multSum(cts, pts);
         if (i == 0) res = std::move(part);
         else res = e.ev.add(res, e.ev.leftRotate(part, i * bs * gap));
     }
+    if (e.mode == kLazy) res = e.ev.rotateSum(parts, part_steps);
     return CtxtTensor(s, std::move(res));
 }
 

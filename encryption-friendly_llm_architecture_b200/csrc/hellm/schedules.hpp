@@ -18,7 +18,8 @@ enum MaskKind { kDiagonal = 0, kHorizontal, kVertical, kPackedHorizontal, kPacke
 // one division by P * q_level replaces two ModDowns and a rescale -- in the product loop and in multMatMatPre.
 // multMatMat also brings its operands down to target + 3 before sigma / tau (the reference transforms at the
 // operands' level and levels down afterwards): the same slots from transforms on far fewer limbs.  The masked sums of
-// the baby-step / giant-step transforms are rescaled once per sum (the reference rescales every term).
+// the baby-step / giant-step transforms are rescaled once per sum (the reference rescales every term), and their
+// giant-step rotations are summed in the extended basis before ONE ModDown (Evaluator::rotateSum).
 enum ScheduleMode { kFaithful = 0, kDirect = 1, kLazy = 2 };
 
 struct Env { // what a schedule needs: evaluator, slot count, mask cache, variant

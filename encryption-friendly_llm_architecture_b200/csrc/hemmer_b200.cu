@@ -1133,6 +1133,57 @@ int hb_assemble_masked_multi(hb_ctx *c, const hb_ct *a, const hb_digits *dg, con
     });
 }
 int hb_tensor_acc_groups(hb_ctx *c, const hb_ct *a, const hb_ct *b, int groups, hb_ct **acc) { return guard(c, [&] { *acc = do_tensor(c, a, b, *acc, groups); }); }
+// sum_t rot(xs[t], steps[t]): every term is decomposed, the inner products of all terms are added up in Q_level u P by
+// one kernel, and one ModDown serves the sum; unrotated terms (step 0) are added as they are.
+int hb_rotate_sum(hb_ctx *c, const hb_ct *const *xs, const int64_t *steps, int count, hb_ct **out) {
+    return guard(c, [&] {
+        if (count < 1 || count > 32 || !xs || !steps) fail(HB_E_LIMIT, "rotate_sum: 1 to 32 terms");
+        const hb_ct *x0 = xs[0];
+        for (int t = 0; t < count; ++t)
+            if (!xs[t] || xs[t]->np != 2 || xs[t]->level != x0->level || xs[t]->batch != x0->batch || xs[t]->spow != x0->spow) fail(HB_E_SHAPE, "rotate_sum: operands differ in shape");
+        const int level = x0->level, batch = x0->batch, N = c->N;
+        const KsPlan *pl = get_plan(c, level);
+        const PlanDims d = plan_dims(c, level);
+        const int n = d.n, ne = d.ne, K = d.K;
+        const size_t ct_outer = (size_t)2 * n * N;
+        RotTermList rot{}; PlainTermList plain{};
+        std::vector<u64 *> dts;
+        hb_ct *r = new_ct(c, level, 2, batch, x0->spow);
+        try {
+            for (int t = 0; t < count; ++t) {
+                const u64 g = c->h->galois_rot(steps[t]);
+                if (g == 1) {
+                    if (plain.count == 16) fail(HB_E_LIMIT, "rotate_sum: at most 16 unrotated terms");
+                    plain.x[plain.count++] = xs[t]->d;
+                    continue;
+                }
+                if (rot.count == 16) fail(HB_E_LIMIT, "rotate_sum: at most 16 rotated terms");
+                const Evk &key = galois_key(c, g);
+                u64 *dt = c->alloc_limbs((size_t)batch * d.dt_count);
+                dts.push_back(dt);
+                ks_decompose(c, xs[t]->d + (size_t)n * N, ct_outer, level, batch, dt);
+                rot.t[rot.count++] = RotTerm{xs[t]->d + (size_t)n * N, dt, key.d, (u32)g, 0u};
+            }
+            const unsigned gx1 = (unsigned)((N + 255) / 256), gx = c->gx();
+            Tmp add(c, (size_t)batch * 2 * n);
+            LAUNCH(c), k_rot_sum_addend<<<dim3(gx, n, batch * 2), 256, 0, c->st>>>(add.p, rot, plain, n, c->qmap(level), c->pc, c->logn, N);
+            if (rot.count == 0) {
+                CK(cudaMemcpyAsync(r->d, add.p, r->limbs() * N * 8, cudaMemcpyDeviceToDevice, c->st));
+            } else {
+                Tmp acc(c, (size_t)batch * 2 * ne), pco(c, (size_t)batch * 2 * K), t(c, (size_t)batch * 2 * n);
+                LAUNCH(c), k_ks_inner_sum<<<dim3(gx, batch, ne), 256, 0, c->st>>>(acc.p, rot, ct_outer, c->nprimes, pl, c->pc, c->logn, N);
+                LimbMap pm{}; pm.n = K; for (int k = 0; k < K; ++k) pm.prime[k] = (unsigned char)(c->L + 1 + k);
+                ntt(c, acc.p + (size_t)n * N, (size_t)ne * N, pco.p, (size_t)K * N, batch * 2 * K, pm, true);
+                LAUNCH(c), k_moddown_conv<<<dim3(gx1, 1, batch * 2), 256, 0, c->st>>>(t.p, pco.p, pl, c->pc, c->L + 1, N);
+                ntt_inplace(c, t.p, batch * 2 * n, c->qmap(level), false);
+                LAUNCH(c), k_moddown_fin<<<dim3(gx, n, batch * 2), 256, 0, c->st>>>(r->d, ct_outer, acc.p, t.p, add.p, add.p + (size_t)n * N, ct_outer, pl, c->pc, 0u, c->logn, N);
+            }
+            CK(cudaGetLastError());
+        } catch (...) { for (u64 *p : dts) c->pool.put(p); hb_ct_free(r); throw; }
+        for (u64 *p : dts) c->pool.put(p);
+        *out = r;
+    });
+}
 int hb_rotate(hb_ctx *c, const hb_ct *a, int64_t steps, hb_ct **out) { return guard(c, [&] { *out = do_galois(c, a, c->h->galois_rot(steps)); }); }
 int hb_conjugate(hb_ctx *c, const hb_ct *a, hb_ct **out) { return guard(c, [&] { *out = do_galois(c, a, c->h->galois_conj()); }); }
 int hb_ntt(hb_ctx *c, hb_ct *a, int inverse) { return guard(c, [&] { ntt_inplace(c, a->d, (int)a->limbs(), c->qmap(a->level), inverse != 0); }); }

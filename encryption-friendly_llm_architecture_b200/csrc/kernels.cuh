@@ -456,6 +456,94 @@ __global__ void k_moddown_fin(u64 *__restrict__ out, size_t out_outer, const u64
     }
 }
 
+// ---------------- sum of rotations with one ModDown ----------------
+// Up to 16 terms (ciphertext batch x_t rotated by g_t): the inner products of all terms are added up in Q_level u P.
+struct RotTerm { const u64 *a_ntt; const u64 *dt; const u64 *key; u32 g; u32 pad; };
+struct RotTermList { RotTerm t[16]; int count; };
+//   acc[b][p][j][i] = sum_t sum_dg digit_t,dg[j][perm_t(i)] * key_t[dg][p][prime(j)][i]      grid = (N/(256*kElems), batch, ne)
+__global__ void k_ks_inner_sum(u64 *__restrict__ acc, RotTermList tl, size_t a_outer, int key_primes, const KsPlan *__restrict__ pl, const PrimeConst *__restrict__ pc,
+                               int logn, int N) {
+    const int j = blockIdx.z, b = blockIdx.y;
+    const int pj = pl->ext_prime[j], nd = pl->nd, ne = pl->ne;
+    const PrimeConst m = pc[pj];
+    const u32 x0 = blockIdx.x * (blockDim.x * kElems) + threadIdx.x;
+    const size_t kpoly = (size_t)key_primes * N;
+    u64 r0[kElems], r1[kElems];
+    if (m.fp) { // at most 16 terms x 4 digits lazy products below 1.6q: the sums stay below 2^49
+#pragma unroll
+        for (int u = 0; u < kElems; ++u) { r0[u] = 0; r1[u] = 0; }
+        for (int t = 0; t < tl.count; ++t) {
+            u32 src[kElems];
+#pragma unroll
+            for (int u = 0; u < kElems; ++u) src[u] = ntt_perm(x0 + u * blockDim.x, tl.t[t].g, logn);
+            const u64 *abase = tl.t[t].a_ntt + (size_t)b * a_outer + (size_t)j * N;
+            const u64 *dbase = tl.t[t].dt + (size_t)b * pl->dt_count * N;
+            const u64 *kbase = tl.t[t].key + (size_t)pj * N + x0;
+            for (int dg = 0; dg < nd; ++dg) {
+                const int en = pl->dt_entry[dg][j];
+                const u64 *sp = en < 0 ? abase : dbase + (size_t)en * N;
+                const u64 *k0 = kbase + (size_t)dg * 2 * kpoly;
+#pragma unroll
+                for (int u = 0; u < kElems; ++u) {
+                    const u64 v = sp[src[u]], ka = k0[u * blockDim.x], kb = k0[kpoly + u * blockDim.x];
+                    const double vd = u52_to_double(v);
+                    r0[u] += mul_small_lazy_d(v, vd, ka, u52_to_double(ka), m.q_inv_f, m.q);
+                    r1[u] += mul_small_lazy_d(v, vd, kb, u52_to_double(kb), m.q_inv_f, m.q);
+                }
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < kElems; ++u) { r0[u] = reduce_fp(r0[u], m.q_inv_f, m.q); r1[u] = reduce_fp(r1[u], m.q_inv_f, m.q); }
+    } else {   // 64 products below 2^120 fit the 128-bit accumulator
+        Acc128 s0[kElems], s1[kElems];
+#pragma unroll
+        for (int u = 0; u < kElems; ++u) { s0[u].zero(); s1[u].zero(); }
+        for (int t = 0; t < tl.count; ++t) {
+            u32 src[kElems];
+#pragma unroll
+            for (int u = 0; u < kElems; ++u) src[u] = ntt_perm(x0 + u * blockDim.x, tl.t[t].g, logn);
+            const u64 *abase = tl.t[t].a_ntt + (size_t)b * a_outer + (size_t)j * N;
+            const u64 *dbase = tl.t[t].dt + (size_t)b * pl->dt_count * N;
+            const u64 *kbase = tl.t[t].key + (size_t)pj * N + x0;
+            for (int dg = 0; dg < nd; ++dg) {
+                const int en = pl->dt_entry[dg][j];
+                const u64 *sp = en < 0 ? abase : dbase + (size_t)en * N;
+                const u64 *k0 = kbase + (size_t)dg * 2 * kpoly;
+#pragma unroll
+                for (int u = 0; u < kElems; ++u) {
+                    const u64 v = sp[src[u]];
+                    s0[u].mad(v, k0[u * blockDim.x]);
+                    s1[u].mad(v, k0[kpoly + u * blockDim.x]);
+                }
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < kElems; ++u) { r0[u] = barrett128(s0[u].hi, s0[u].lo, m); r1[u] = barrett128(s1[u].hi, s1[u].lo, m); }
+    }
+    u64 *o0 = acc + (((size_t)b * 2) * ne + j) * N + x0, *o1 = o0 + (size_t)ne * N;
+#pragma unroll
+    for (int u = 0; u < kElems; ++u) { o0[u * blockDim.x] = r0[u]; o1[u * blockDim.x] = r1[u]; }
+}
+// add[b][p][l][i] = sum over the rotated terms of (p == 0) c0_t[b][l][perm_t(i)]  +  sum over the unrotated terms of x_t[b][p][l][i]
+// rot: terms with g != 1 (a_ntt - n limbs = c0); plain: terms added as they are.  grid = (N/(256*kElems), n, batch*2)
+struct PlainTermList { const u64 *x[16]; int count; };
+__global__ void k_rot_sum_addend(u64 *__restrict__ add, RotTermList rot, PlainTermList plain, int n, LimbMap map, const PrimeConst *__restrict__ pc, int logn, int N) {
+    const int l = blockIdx.y, bp = blockIdx.z, b = bp >> 1, p = bp & 1;
+    const u64 q = pc[map.prime[l]].q;
+    const size_t ct_outer = (size_t)2 * n * N;
+#pragma unroll
+    for (int u_ = 0; u_ < kElems; ++u_) {
+        const int i = (blockIdx.x * kElems + u_) * blockDim.x + threadIdx.x;
+        if (i >= N) break;
+        u64 v = 0;
+        if (p == 0)
+            for (int t = 0; t < rot.count; ++t) // a_ntt points at the second polynomial; the first sits n limbs before it
+                v = add_mod(v, (rot.t[t].a_ntt - (size_t)n * N)[(size_t)b * ct_outer + (size_t)l * N + ntt_perm((u32)i, rot.t[t].g, logn)], q);
+        for (int t = 0; t < plain.count; ++t) v = add_mod(v, plain.x[t][(size_t)b * ct_outer + ((size_t)p * n + l) * N + i], q);
+        add[((size_t)bp * n + l) * N + i] = v;
+    }
+}
+
 // ---------------- masked pair of rotations with one division by P * q_level ----------------
 // Constants of the division of a Q_level u P polynomial by D = P * q_level (sources: q_level, p_1 .. p_K).
 struct DivPlan {

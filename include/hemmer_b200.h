@@ -154,6 +154,12 @@ int hb_conjugate(hb_ctx *ctx, const hb_ct *a, hb_ct **out);                     
 int hb_decompose(hb_ctx *ctx, const hb_ct *a, hb_digits **out);
 int hb_rotate_hoisted(hb_ctx *ctx, const hb_ct *a, const hb_digits *digits, int64_t left_steps, hb_ct **out);
 void hb_digits_free(hb_digits *digits);
+/* out = sum_t rot(xs[t], left_steps[t]) for ciphertexts of equal level (at most 16 rotated and 16 unrotated terms): the key-switch inner products of
+ * all terms are added up in the extended basis and ONE ModDown serves the sum (a step of 0 adds its operand as it is).
+ * The giant-step half of a baby-step / giant-step transform in schedule 2.  Same slots as the sum of hb_rotate
+ * results, different bits (one rounding instead of one per term); the oracle's Evaluator::rotate_sum is the same
+ * arithmetic.  No counterpart in HEaaN. */
+int hb_rotate_sum(hb_ctx *ctx, const hb_ct *const *xs, const int64_t *left_steps, int count, hb_ct **out);
 /* The masked pair of rotations that makes one wrapped copy in the shift loops (MatrixUtils.cpp:1416-1427:
  * two leftRotate, two multWithoutRescale, add, rescale) as one operation:
  *     out = p1 (.) rot(a, s1) + p2 (.) rot(a, s2),   at level(a) - 1.

@@ -1078,6 +1078,104 @@ struct Evaluator {
         }
         return out;
     }
+    // Steps 3-4 of keyswitch accumulated into (acc0, acc1) over Q_level u P: acc_p += sum_dg perm_g(digit_dg) (.) key_dg,p
+    void ks_inner_acc(const u64 *a, int level, const Evk &key, u64 g, std::vector<u64> &acc0, std::vector<u64> &acc1) {
+        const int N = cx.N, n = level + 1, ne = n + cx.K, nd = cx.num_digits(level);
+        const std::vector<u64> dg = lifted_digits(a, level);
+        const std::vector<u32> *perm = g ? &cx.ntt_perm(g) : nullptr;
+#pragma omp parallel for
+        for (int j = 0; j < ne; ++j) {
+            const int pi = cx.prime_index_ext(level, j);
+            const Mod &m = cx.mod[pi];
+            u64 *o0 = &acc0[(size_t)j * N], *o1 = &acc1[(size_t)j * N];
+            for (int d = 0; d < nd; ++d) {
+                const u64 *dv = &dg[((size_t)d * ne + j) * N];
+                const u64 *k0 = key.limb(d, 0, pi), *k1 = key.limb(d, 1, pi);
+                for (int c = 0; c < N; ++c) {
+                    const u64 v = perm ? dv[(*perm)[c]] : dv[c];
+                    o0[c] = m.add(o0[c], m.mul(v, k0[c]));
+                    o1[c] = m.add(o1[c], m.mul(v, k1[c]));
+                }
+            }
+        }
+    }
+    // Step 5 of keyswitch on its own: out = (acc - lift_{P->Q}(iNTT(acc|P))) * P^-1 on the Q limbs (acc is consumed)
+    void mod_down(std::vector<u64> &acc, int level, u64 *out) {
+        const int N = cx.N, n = level + 1, K = cx.K;
+        std::vector<int> psrc; for (int j = 0; j < K; ++j) psrc.push_back(cx.L + 1 + j);
+        const BConv pb = make_bconv(psrc);
+        std::vector<u64> y((size_t)K * N);
+#pragma omp parallel for
+        for (int j = 0; j < K; ++j) {
+            u64 *pl = &acc[(size_t)(n + j) * N];
+            cx.intt(pl, cx.L + 1 + j);
+            for (int c = 0; c < N; ++c) y[(size_t)j * N + c] = Mod::mul_shoup(pl[c], pb.hat_inv[j], pb.hat_inv_sh[j], cx.mod[cx.L + 1 + j].q);
+        }
+#pragma omp parallel for
+        for (int l = 0; l < n; ++l) {
+            const Mod &m = cx.mod[l];
+            u64 pinv = 1;
+            for (int j = 0; j < K; ++j) pinv = m.mul(pinv, cx.mod[cx.L + 1 + j].q % m.q);
+            pinv = m.inv(pinv);
+            std::vector<u64> t(N);
+            for (int c = 0; c < N; ++c) {
+                u128 s = 0;
+                for (int j = 0; j < K; ++j) s += (u128)y[(size_t)j * N + c] * pb.hat_mod[l][j];
+                t[c] = m.red128(s);
+            }
+            cx.ntt(t.data(), l);
+            const u64 *al = &acc[(size_t)l * N]; u64 *o = out + (size_t)l * N;
+            for (int c = 0; c < N; ++c) o[c] = m.mul(m.sub(al[c], t[c]), pinv);
+        }
+    }
+    // sum_i rot(x_i, s_i) with the key-switch inner products of all terms added up in Q_level u P and ONE ModDown
+    // for the sum (a rotation by zero adds its operand as it is).  Same slots as the sum of the rotations; the
+    // ciphertext bits differ (one rounding instead of one per term).
+    Ct rotate_sum(const std::vector<const Ct *> &xs, const std::vector<i64> &steps) {
+        require(!xs.empty() && xs.size() == steps.size(), "rotate_sum: nothing to add");
+        const Ct &x0 = *xs[0];
+        for (const Ct *x : xs) require(x->np == 2 && x->level == x0.level && x->batch == x0.batch && x->spow == x0.spow, "rotate_sum: operands differ in shape");
+        if (count("rotate_sum", x0.level, x0.batch * (int)xs.size())) return meta(x0.level, 2, x0.batch, x0.spow);
+        const int N = cx.N, level = x0.level, n = level + 1, ne = n + cx.K;
+        Ct r(N, level, 2, x0.batch, x0.spow);
+        for (int b = 0; b < x0.batch; ++b) {
+            std::vector<u64> acc0((size_t)ne * N, 0), acc1((size_t)ne * N, 0), add0((size_t)n * N, 0), add1((size_t)n * N, 0);
+            bool switched = false;
+            for (size_t i = 0; i < xs.size(); ++i) {
+                const u64 g = cx.galois_for_rotation(steps[i]);
+                const Ct &x = *xs[i];
+                if (g == 1) {
+                    for (int l = 0; l < n; ++l) {
+                        const Mod &m = cx.mod[l];
+                        for (int c = 0; c < N; ++c) {
+                            add0[(size_t)l * N + c] = m.add(add0[(size_t)l * N + c], x.limb(b, 0, l)[c]);
+                            add1[(size_t)l * N + c] = m.add(add1[(size_t)l * N + c], x.limb(b, 1, l)[c]);
+                        }
+                    }
+                    continue;
+                }
+                auto it = gal_keys.find(g);
+                if (it == gal_keys.end()) throw std::runtime_error("missing galois key");
+                ks_inner_acc(x.limb(b, 1, 0), level, it->second, g, acc0, acc1);
+                const auto &perm = cx.ntt_perm(g);
+                for (int l = 0; l < n; ++l) {
+                    const Mod &m = cx.mod[l];
+                    for (int c = 0; c < N; ++c) add0[(size_t)l * N + c] = m.add(add0[(size_t)l * N + c], x.limb(b, 0, l)[perm[c]]);
+                }
+                switched = true;
+            }
+            std::vector<u64> k0((size_t)n * N, 0), k1((size_t)n * N, 0);
+            if (switched) { mod_down(acc0, level, k0.data()); mod_down(acc1, level, k1.data()); }
+            for (int l = 0; l < n; ++l) {
+                const Mod &m = cx.mod[l];
+                for (int c = 0; c < N; ++c) {
+                    r.limb(b, 0, l)[c] = m.add(k0[(size_t)l * N + c], add0[(size_t)l * N + c]);
+                    r.limb(b, 1, l)[c] = m.add(k1[(size_t)l * N + c], add1[(size_t)l * N + c]);
+                }
+            }
+        }
+        return r;
+    }
     // HomEvaluator::leftRotate / rightRotate (HomEvaluator.hpp:383, 403): slot p+t moves to slot p
     Ct rotate(const Ct &x, i64 left_steps) { return apply_galois(x, cx.galois_for_rotation(left_steps)); }
     // HomEvaluator::conjugate (HomEvaluator.hpp:465)

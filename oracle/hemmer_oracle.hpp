@@ -59,7 +59,8 @@ struct Hemmer {
     //    division by P * q_level for the pair) in the product loop and in multMatMatPre; multMatMat brings its operands
     //    down to target + 3 BEFORE sigma / tau instead of after (MatrixUtils.cpp:1346-1361 transforms at the operands'
     //    level), the order multMatMatPre (:1583) and the low-rank products (:1692) use; the masked sums of the
-    //    baby-step / giant-step transforms are rescaled once per sum instead of once per term (MaskedSum).
+    //    baby-step / giant-step transforms are rescaled once per sum instead of once per term (MaskedSum), and their
+    //    giant-step rotations share one ModDown (GiantSum).
     int mode = 0;
 
     Hemmer(Context &c, Evaluator &e) : cx(c), ev(e), slots(c.slots) {
@@ -88,6 +89,26 @@ struct Hemmer {
             any = true;
         }
         Ct result() { return h.mode == 2 ? h.ev.rescale(acc) : acc; }
+    };
+
+    // The giant-step rotations of a transform and their sum.  Schedule 2 adds the key-switch inner products of all
+    // giant steps in the extended basis and applies ONE ModDown (Evaluator::rotate_sum); the other schedules rotate
+    // every part on its own and add, in the order the reference does.
+    struct GiantSum {
+        Hemmer &h; std::vector<Ct> parts; std::vector<i64> steps; Ct res; bool any = false;
+        explicit GiantSum(Hemmer &hh) : h(hh) {}
+        void add(Ct part, i64 left_steps) {
+            if (h.mode == 2) { parts.push_back(std::move(part)); steps.push_back(left_steps); return; }
+            Ct t = (left_steps % h.slots) ? h.rotL(part, left_steps) : part;
+            res = any ? h.ev.add(res, t) : t;
+            any = true;
+        }
+        Ct result() {
+            if (h.mode != 2) return res;
+            std::vector<const Ct *> ptr;
+            for (size_t i = 0; i < parts.size(); ++i) { h.ev.gen_rot_key(steps[i]); ptr.push_back(&parts[i]); }
+            return h.ev.rotate_sum(ptr, steps);
+        }
     };
 
     // ---------------- TransformMask generators ----------------
@@ -313,7 +334,7 @@ struct Hemmer {
             bs_rot[0] = rotR(op.ct, (num_rows - 1) * gap);
             for (i64 j = 1; j < bs; j++) bs_rot[(size_t)j] = rotL(bs_rot[(size_t)j - 1], gap);
         }
-        Ct res, gs_tmp;
+        GiantSum giant(*this);
         for (i64 i = 0; i < gs; i++) {
             i64 idx = 1 - num_rows + i * bs;
             MaskedSum sum(*this);
@@ -322,13 +343,9 @@ struct Hemmer {
                 if (++idx >= num_cols) break;
                 sum.add(bs_rot[(size_t)j], dm[idx]);
             }
-            ((i == 0) ? res : gs_tmp) = sum.result();
-            if (i > 0) {
-                gs_tmp = rotL(gs_tmp, (i * bs) * gap);
-                res = ev.add(res, gs_tmp);
-            }
+            giant.add(sum.result(), (i * bs) * gap);
         }
-        return CtT{res, ms};
+        return CtT{giant.result(), ms};
     }
     // Shared body of diagonalToColumn (MatrixUtils.cpp:776-848, gap 1, main = cols),
     // diagonalToRow (:924-996, gap = width, main = rows), packedDiagonalToColumn (:850-922, gap 2,
@@ -343,7 +360,8 @@ struct Hemmer {
             bs_rot[0] = rotL(op, gap);
             for (i64 j = 1; j < bs; j++) bs_rot[(size_t)j] = rotL(bs_rot[(size_t)j - 1], gap);
         }
-        Ct res = mult_msg(op, mask[0]);
+        GiantSum giant(*this);
+        giant.add(mult_msg(op, mask[0]), 0);
         for (i64 i = 0; i < gs; i++) {
             const i64 rot_num = i * bs * gap;
             i64 idx = 1 + i * bs - main_dim;
@@ -353,8 +371,7 @@ struct Hemmer {
                 if (++idx >= sub_dim - main_dim) break;
                 neg.add(bs_rot[(size_t)j], mask[idx]);
             }
-            Ct gs_tmp = rotR(neg.result(), main_dim * gap - rot_num);
-            res = ev.add(res, gs_tmp);
+            giant.add(neg.result(), -(main_dim * gap - rot_num));
             idx = 1 + i * bs;
             MaskedSum pos(*this);
             pos.add(bs_rot[0], mask[idx]);
@@ -362,10 +379,9 @@ struct Hemmer {
                 if (++idx >= sub_dim) break;
                 pos.add(bs_rot[(size_t)j], mask[idx]);
             }
-            gs_tmp = rotL(pos.result(), rot_num);
-            res = ev.add(res, gs_tmp);
+            giant.add(pos.result(), rot_num);
         }
-        return res;
+        return giant.result();
     }
     CtT diagonal_to_column(const CtT &op) {
         Shape ms(op.sh.rows, op.sh.cols, op.sh.width);

@@ -147,6 +147,9 @@ int orc_rotate(orc_ctx *c, const orc_ct *a, int64_t s, orc_ct **o) { ORC_TRY(c, 
 int orc_assemble_rot(orc_ctx *c, const orc_ct *a, int64_t s1, const orc_pt *p1, int64_t s2, const orc_pt *p2, orc_ct **o) {
     ORC_TRY(c, *o = new Ct(c->ev.assemble_rot(*a, s1, *p1, s2, *p2)))
 }
+int orc_rotate_sum(orc_ctx *c, const orc_ct *const *xs, const int64_t *steps, int count, orc_ct **o) {
+    ORC_TRY(c, { std::vector<const Ct *> v(xs, xs + count); std::vector<i64> s(steps, steps + count); *o = new Ct(c->ev.rotate_sum(v, s)); })
+}
 int orc_conjugate(orc_ctx *c, const orc_ct *a, orc_ct **o) { ORC_TRY(c, *o = new Ct(c->ev.conjugate(*a))) }
 int orc_ntt(orc_ctx *c, orc_ct *a, int inverse) { ORC_TRY(c, c->ev.ntt_raw(*a, inverse != 0)) }
 

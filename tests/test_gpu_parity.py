@@ -307,3 +307,25 @@ def test_masked_keys_give_the_residues_of_assemble_rot(gpu_mid):
             for k in (k1, k2, k12):
                 dll.hb_masked_key_free(k)
             dll.hb_digits_free(dg)
+
+
+@pytest.mark.parametrize("size", ["small", "mid", "full"])
+def test_rotate_sum_parity(request, size):
+    """Sum of rotations with one ModDown: rotated and unrotated terms, every digit count, batch of 2."""
+    g, o = _pairs(request, size)
+    steps = [0, 3, -5, 0, 17]
+    for lib in (g, o):
+        lib.gen_rot_keys(steps)
+    levels = (g.L, 6, 3, 0) if size != "full" else (g.L, 5)
+    for lvl in levels:
+        outs = []
+        for lib in (g, o):
+            xs = []
+            for t in range(len(steps)):
+                ct = lib.ct_create(lvl, 2, 2)
+                lib.ct_import(ct, rand_ct_residues(g, lvl, 2, 2, seed=70 + 10 * lvl + t))
+                xs.append(ct)
+            outs.append(lib.ct_export(lib.rotate_sum(xs, steps)))
+            if lib is g and lvl == levels[0]:   # unrotated terms only: the plain sum
+                _same(lib.ct_export(lib.rotate_sum([xs[0], xs[3]], [0, 0])), lib.ct_export(lib.add(xs[0], xs[3])), "rotate_sum of unrotated terms")
+        _same(outs[0], outs[1], f"rotate_sum@{lvl}")

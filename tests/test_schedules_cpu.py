@@ -77,3 +77,21 @@ def test_assemble_rot_semantics(orc_small):
         ref = o.rescale(o.add(o.mul_pt_norescale(o.rotate(ct, 3), o.encode(m1, lvl)), o.mul_pt_norescale(o.rotate(ct, -13), o.encode(1 - m1, lvl))))
         err, err_ref = np.abs(o.decrypt(a) - want).max(), np.abs(o.decrypt(ref) - want).max()
         assert err < 4 * err_ref + 1e-9, (lvl, err, err_ref)
+
+
+def test_rotate_sum_semantics(orc_small):
+    """sum_t rot(x_t, s_t) with one ModDown decrypts to the sum of the rotated messages."""
+    import numpy as np
+    o = orc_small
+    rng = np.random.default_rng(4)
+    steps = [0, 3, -13, 40]
+    o.gen_rot_keys(steps)
+    zs = [rng.uniform(-1, 1, o.slots) + 1j * rng.uniform(-1, 1, o.slots) for _ in steps]
+    for lvl in (o.L, 4, 1):
+        xs = [o.encrypt(o.encode(z, o.L), 50 + i) for i, z in enumerate(zs)]
+        if lvl < o.L:
+            xs = [o.level_down(x, lvl) for x in xs]
+        want = sum(np.roll(z, -s) for z, s in zip(zs, steps))
+        got = o.decrypt(o.rotate_sum(xs, steps))
+        ref = o.decrypt(o.add(o.add(xs[0], o.rotate(xs[1], 3)), o.add(o.rotate(xs[2], -13), o.rotate(xs[3], 40))))
+        assert np.abs(got - want).max() < 2 * np.abs(ref - want).max() + 1e-9
