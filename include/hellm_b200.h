@@ -35,7 +35,9 @@ void hb_hemmer_destroy(hb_hemmer *h);
 const char *hb_hemmer_last_error(void);
 /* 0: the reference's rotation sequence, each shifted copy rotated from the previous one (default);
  * 1: every shifted copy is one rotation of the transformed operand, sharing its decomposition;
- * 2: as 1, and each wrapped copy (two rotations, two masks, add, rescale) is one hb_assemble_hoisted.
+ * 2: as 1, and each wrapped copy (two rotations, two masks, add, rescale) is one hb_assemble_masked; the operands
+ *    of singleCCMatMul are levelled down before sigma / tau; inside the transforms every masked sum is rescaled
+ *    once (hb_sum_mul_pt_rescale) and the giant-step rotations share one ModDown (hb_rotate_sum).
  * All give the same slots and different ciphertext bits; no counterpart in the reference. */
 int hb_hemmer_set_schedule(hb_hemmer *h, int mode);
 
