@@ -6,8 +6,9 @@
 
 A step is one pass over the layer's matmul units (12 ct x pt groups with 132 fused plaintext products,
 42 two-tile ct x ct products = 84 tile products, 18 of them with a transpose).  Units are independent
-and are dealt round-robin to the ranks; no data-path collective is needed ("weak" scaling is not the
-right word here: total work is fixed, so the line says "strong").
+and are dealt to the ranks by estimated cost; the K-groups of a ct x pt sublayer that land on different ranks
+exchange their partial output tiles (point to point, to one owner per tile).  Total work is fixed, so the line
+says "strong".  The timed passes replay a CUDA graph of one pass over operands resident in HBM.
 
 Prints one JSON line on rank 0.
 """
@@ -164,8 +165,12 @@ def cpu_layer_estimate(pkg, sample_reps=40):
         elif op == "mul_pt":
             pt = o.encode(z, lvl)
             times[(op, lvl)] = timed(lambda: o.mul_pt_norescale(ct, pt))
-        elif op in ("add", "mult_imag", "scalar_mul"):
+        elif op == "add":
             times[(op, lvl)] = timed(lambda: o.add(ct, ct))
+        elif op == "mult_imag":
+            times[(op, lvl)] = timed(lambda: o.mult_imag(ct))
+        elif op == "scalar_mul":
+            times[(op, lvl)] = timed(lambda: o.mult_int(ct, 12345))
         elif op == "encode":
             times[(op, lvl)] = 0.0   # masks and weights are encoded outside the timed region
         elif op == "encrypt":
@@ -204,7 +209,16 @@ def run_reference(args):
 # ---------------------------------------------------------------------------------------------
 # GPU arm
 # ---------------------------------------------------------------------------------------------
+def golden_units(schedule):
+    """Digests recorded from the CPU oracle for one unit of every kind of the layer (tests/golden/golden.json)."""
+    path = os.path.join(ROOT, "tests", "golden", "golden.json")
+    if not os.path.exists(path):
+        return {}
+    return json.load(open(path)).get("layer_units", {}).get(f"schedule{schedule}", {})
+
+
 def run_gpu(args):
+    import hashlib
     import torch
     import torch.distributed as dist
 
@@ -219,11 +233,13 @@ def run_gpu(args):
     pkg = importlib.import_module(PKG)
     layer = importlib.import_module(PKG + ".layer")
     lib = pkg.open_gpu(pkg.make_params(), device=local)
+    lib.set_host_threads(max(1, (os.cpu_count() or 1) // int(os.environ.get("LOCAL_WORLD_SIZE", world))))
     lib.keygen()
     H = pkg.open_hemmer(lib)
     H.set_schedule(args.schedule)
     lib.dll.hb_stream.restype = C.c_void_p
     lib.dll.hb_launch_count.restype = C.c_uint64
+    lib.dll.hb_algorithmic_bytes.restype = C.c_uint64
     stream = torch.cuda.ExternalStream(lib.dll.hb_stream(lib.ctx), device=torch.device("cuda", local))
     wl = layer.LayerWorkload(H, layer.synthetic(1234), rank=rank, world=world)
     if world > 1:   # communicator for the K-split exchange; the 128-byte id travels over torch.distributed
@@ -245,23 +261,32 @@ def run_gpu(args):
         if world > 1:
             dist.barrier()
 
+    def gather(obj):
+        if world == 1:
+            return [obj]
+        out = [None] * world
+        dist.all_gather_object(out, obj)
+        return out
+
     def timed_region(fn, steps):
+        """(max over ranks, this rank's own) device time of `steps` calls of fn, CUDA events on the library's stream."""
         barrier()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         with torch.cuda.stream(stream):
             e0.record(stream)
             for s in range(steps):
-                fn(s)   # the result handles are dropped at once, as in the warm-up passes: the pool sees the same allocation pattern
+                fn(s)   # result handles are dropped at once, as in the warm-up passes: the pool sees the same allocation pattern
             e1.record(stream)
         lib.sync()
         torch.cuda.synchronize()
-        ms = e0.elapsed_time(e1)
+        own = e0.elapsed_time(e1)
+        ms = own
         if world > 1:
             t = torch.tensor([ms], device="cuda", dtype=torch.float64)
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             ms = float(t.item())
         barrier()
-        return ms
+        return ms, own
 
     # operands resident in HBM before the clock starts
     wl.prepare()
@@ -277,20 +302,84 @@ def run_gpu(args):
     for s in range(args.warmup):
         wl.step_resident()
     lib.sync()
-    err = wl.check()
+    # correctness of this run: every result against the float64 products (max over the ranks), every result hashed
+    # (one digest over all tiles in canonical order: the same at every rank count), and the units whose residues the
+    # CPU oracle recorded compared bit for bit
+    err, digests = wl.check(with_digests=True)
+    err = max(gather(err))
+    all_digests = {}
+    for d in gather({repr(k): v for k, v in digests.items()}):
+        all_digests.update(d)
+    canon = [repr(("p",) + k) for k in wl.tile_keys] + [repr(("c", i)) for i, u in enumerate(wl.units) if u[0] == "ccmm"]
+    missing = [k for k in canon if k not in all_digests]
+    outputs_sha = hashlib.sha256("".join(all_digests.get(k, "-") for k in canon).encode()).hexdigest()
+    gold = golden_units(args.schedule)
+    hits = 0
+    for name, want in gold.items():
+        tag = ("p", *name.split("/")[:2], int(name.split("/")[2])) if "/" in name else ("c", wl.unit_index(name))
+        hits += int(all_digests.get(repr(tag)) == want)
+    bit_exact = f"{hits}/{len(gold)}"
+
+    # the timed pass: a CUDA graph of one resident pass, replayed (`--no-graph`: launched from the host every time)
+    graph = graph_out = None
+    if not args.no_graph:
+        graph, graph_out = wl.record_graph()
+        lib.graph_launch(graph)
+        lib.sync()
+    step_fn = (lambda s: lib.graph_launch(graph)) if graph is not None else (lambda s: wl.step_resident())
     sampler = ClockSampler(local)
     sampler.start()
     l0 = lib.dll.hb_launch_count(lib.ctx)
-    ms_total = timed_region(lambda s: wl.step_resident(), args.steps)
+    a0 = lib.dll.hb_algorithmic_bytes(lib.ctx)
+    ms_total, own_total = timed_region(step_fn, args.steps)
     launches = (lib.dll.hb_launch_count(lib.ctx) - l0) // max(args.steps, 1)
+    alg_bytes = (lib.dll.hb_algorithmic_bytes(lib.ctx) - a0) // max(args.steps, 1)
     clocks = sampler.stop()
     ms_step = ms_total / args.steps
+    per_rank = gather({"ms": own_total / args.steps, "alg_bytes": alg_bytes, "units": len(wl.mine), "launches": launches})
+    if graph is not None:   # the replayed pass must leave exactly the bits of an ordinary pass
+        replay = wl.output_digests(graph_out)
+        eager = wl.output_digests(wl.step_resident())
+        assert replay == eager, "graph replay and host-launched pass differ"
+    ms_eager = None
+    if graph is not None and not args.no_compare:
+        ms_eager = timed_region(lambda s: wl.step_resident(), 1)[0]
+    # exchange time: one host-launched pass with CUDA events around the K-split exchange (nothing overlaps it: the
+    # library runs on one stream, so all of it is exposed)
+    comm_ms = 0.0
+    if world > 1:
+        evs = []
+        def hook(phase):
+            e = torch.cuda.Event(enable_timing=True)
+            e.record(stream)
+            evs.append(e)
+        wl.on_comm = hook
+        barrier()
+        wl.step_resident()
+        lib.sync()
+        wl.on_comm = None
+        own_comm = sum(evs[k].elapsed_time(evs[k + 1]) for k in range(0, len(evs) - 1, 2))
+        t = torch.tensor([own_comm], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        comm_ms = float(t.item())
     # the same layer with the reference's own rotation sequence (no hoisting), for comparison
     ms_faithful = None
+    faithful_exact = None
     if args.schedule != 0 and not args.no_compare:
         H.set_schedule(0)
         wl.step_resident()
-        ms_faithful = timed_region(lambda s: wl.step_resident(), 1)
+        ms_faithful = timed_region(lambda s: wl.step_resident(), 1)[0]
+        gold0 = golden_units(0)
+        if gold0:
+            _, dg0 = wl.check(with_digests=True)
+            merged = {}
+            for d in gather({repr(k): v for k, v in dg0.items()}):
+                merged.update(d)
+            ok = 0
+            for name, want in gold0.items():
+                tag = ("p", *name.split("/")[:2], int(name.split("/")[2])) if "/" in name else ("c", wl.unit_index(name))
+                ok += int(merged.get(repr(tag)) == want)
+            faithful_exact = f"{ok}/{len(gold0)}"
         H.set_schedule(args.schedule)
 
     # end to end: host matrices in, decrypted host results out, every step
@@ -298,14 +387,14 @@ def run_gpu(args):
     wl.step_e2e()
     wl.h2d_bytes = wl.d2h_bytes = 0
     wl.phases_ms = {}
-    e2e_steps = max(1, min(args.steps, 2))
-    ms_e2e = timed_region(lambda s: wl.step_e2e(), e2e_steps) / e2e_steps
+    e2e_steps = max(1, args.steps)
+    ms_e2e = timed_region(lambda s: wl.step_e2e(), e2e_steps)[0] / e2e_steps
     e2e_phases = {k: round(v / e2e_steps, 1) for k, v in wl.phases_ms.items()}
     h2d, d2h = wl.h2d_bytes // e2e_steps, wl.d2h_bytes // e2e_steps
     if world > 1:
-        t = torch.tensor([h2d, d2h, launches], device="cuda", dtype=torch.float64)
+        t = torch.tensor([h2d, d2h, launches, alg_bytes], device="cuda", dtype=torch.float64)
         dist.all_reduce(t)
-        h2d, d2h, launches = int(t[0].item()), int(t[1].item()), int(t[2].item())
+        h2d, d2h, launches, alg_bytes = int(t[0].item()), int(t[1].item()), int(t[2].item()), int(t[3].item())
 
     if rank != 0:
         if world > 1:
@@ -356,10 +445,20 @@ def run_gpu(args):
     ks["wrapped_copy_l6"] = {"algorithmic_bytes": alg, "ms": ms, "gbs": alg / ms / 1e6, "frac": alg / ms / 1e6 / hbm}
     del cb, dgt, k1, k2
     top = roof["ntt"]
+    # Instruction roofline of the same transform: a radix-2 butterfly on a prime below 2^44 needs at least six 32-bit
+    # multiply-adds (the exact low words of y*w and of quotient*q) on a pipe that issues 64 of them per SM per clock,
+    # plus two FP64 operations (quotient estimate) and about six adds / logic operations for the conversions and the
+    # two 64-bit sums: 14 issue slots of the 128 per SM per clock.  The four 60-bit limbs of the 26 cost at least as much.
+    mhz = clocks.get("sm_mhz") or clocks.get("sm_max_mhz") or 1965.0
+    bfly = nb * 2 * (lvl + 1) * (65536 // 2) * 16
+    issue_ms = bfly * 14 / (148 * 128 * mhz * 1e6) * 1e3
+    imad_ms = bfly * 6 / (148 * 64 * mhz * 1e6) * 1e3
     # two launches (column pass, row pass) make one transform: per-launch algorithmic bytes are half of the transform's
-    roofline = {"bound": "hbm", "kernel": "ntt16_fwd_cols+ntt16_fwd_rows (one forward NTT of 64 ciphertexts, level 12)", "achieved": top["gbs"], "peak": hbm,
-                "unit": "GB/s", "frac": top["gbs"] / hbm, "peak_source": which, "traffic": 2 * top["algorithmic_bytes"],
-                "traffic_source": "ncu dram bytes of a 32-ciphertext capture, scaled by limbs: each of the two passes reads and writes every limb once",
+    roofline = {"bound": "hbm", "kernel": NTT_KERNELS, "achieved": top["gbs"], "peak": hbm,
+                "unit": "GB/s", "frac": top["gbs"] / hbm, "peak_source": which, "traffic": NTT_TRAFFIC_FACTOR * top["algorithmic_bytes"],
+                "traffic_source": NTT_TRAFFIC_NOTE,
+                "issue_bound_ms": issue_ms, "imad_pipe_bound_ms": imad_ms, "measured_ms": top["ms"],
+                "issue_note": "butterflies x 14 issue slots / (148 SMs x 128 lanes x sampled SM clock); multiply-add pipe: butterflies x 6 / (148 x 64 x clock)",
                 "intt_gbs": roof["intt"]["gbs"], "keyswitch": ks}
 
     pb, iu = C.c_uint64(), C.c_uint64()
@@ -374,7 +473,13 @@ def run_gpu(args):
             "higher_is_better": False, "scaling": "strong", "vs_baseline": None, "dtype": "u64", "data": "synthetic",
             "config": {"workload": "bert_base_layer_matmuls_fwd_plus_lora_bwd", "units": len(wl.units), "batched_calls": True, "schedule": {0: "reference_sequence", 1: "direct_hoisted", 2: "direct_hoisted_one_division_per_copy"}[args.schedule], "ring_degree": 65536, "levels": 12, "tile": 128,
                        "l2": "working set per step is tens of GB, far above the 126 MB L2", "max_abs_err_vs_float64": err,
+                       "bit_exact_units": bit_exact, "bit_exact_units_reference_sequence": faithful_exact, "outputs_sha256": outputs_sha, "outputs_missing": len(missing),
+                       "timed_as": "cuda_graph_replay" if graph is not None else "host_launched", "host_launched_ms": ms_eager,
                        "reference_sequence_ms": ms_faithful, "device_pool_gb": pool_gb},
+            "schedule_roofline_ms": alg_bytes / (hbm * 1e6), "algorithmic_bytes_per_step": alg_bytes,
+            "comm_ms": comm_ms, "exposed_comm_frac": comm_ms / ms_step if ms_step else None,
+            "compute_ms_per_rank": {"min": min(p["ms"] for p in per_rank), "max": max(p["ms"] for p in per_rank), "all": [round(p["ms"], 2) for p in per_rank],
+                                    "units": [p["units"] for p in per_rank]},
             "roofline": roofline, "cpu_baseline": cpu,
             "e2e": {"value": ms_e2e, "unit": "ms", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "phases_ms_rank0": e2e_phases},
             "gpu_launches": launches, "clocks": clocks}
@@ -383,8 +488,14 @@ def run_gpu(args):
         dist.destroy_process_group()
 
 
+# which kernels the roofline object describes, and how their DRAM traffic relates to the algorithmic bytes
+NTT_KERNELS = "ntt16_fwd_cols+ntt16_fwd_rows (one forward NTT of 64 ciphertexts, level 12)"
+NTT_TRAFFIC_FACTOR = 2
+NTT_TRAFFIC_NOTE = "ncu dram bytes of a 32-ciphertext capture, scaled by limbs: each of the two passes reads and writes every limb once"
+
+
 def run_sweep(args):
-    """BASELINE config 5: primitive sweep on a batch of 256 independent ciphertexts with uniform residues, levels 12/8/4/1.
+    """Primitive sweep on a batch of 256 independent ciphertexts with uniform residues, levels 12/8/4/1.
     Prints one JSON object: per operation the time, the algorithmic bytes and the fraction of the measured HBM peak."""
     import torch
     pkg = importlib.import_module(PKG)
@@ -459,11 +570,12 @@ def main():
     ap.add_argument("--schedule", type=int, default=2, choices=[0, 1, 2],
                     help="0: the reference's rotation sequence; 1: direct, hoisted rotations (same products, fewer chained key switches); "
                          "2 (default): as 1, each wrapped copy of the shift loops made with one division by P*q_level instead of two ModDowns and a rescale")
-    ap.add_argument("--no-compare", action="store_true", help="skip the extra timed pass with the reference's rotation sequence")
+    ap.add_argument("--no-compare", action="store_true", help="skip the extra timed passes (host-launched, and the reference's rotation sequence)")
+    ap.add_argument("--no-graph", action="store_true", help="launch every kernel of the timed passes from the host instead of replaying a CUDA graph")
     ap.add_argument("--sweep-ops", type=str, default="", help="comma-separated subset of the sweep's operations (profiling one kernel family)")
     ap.add_argument("--sweep-batch", type=int, default=256)
     ap.add_argument("--sweep-levels", type=str, default="12,8,4,1")
-    ap.add_argument("--sweep", action="store_true", help="primitive sweep on 256 ciphertexts (BASELINE config 5) instead of the layer")
+    ap.add_argument("--sweep", action="store_true", help="primitive sweep on 256 ciphertexts instead of the layer")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
     if args.sweep:

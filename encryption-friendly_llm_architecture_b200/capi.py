@@ -51,7 +51,9 @@ class Handle:
 
     def __del__(self):
         if getattr(self, "ptr", None) and self.lib is not None and self.lib.alive:
-            getattr(self.lib.dll, f"{self.lib.prefix}{self.kind}_free")(self.ptr)
+            f = getattr(self.lib.dll, f"{self.lib.prefix}{self.kind}_free")
+            f.restype = None
+            f(self.ptr)
             self.ptr = None
 
 
@@ -218,6 +220,58 @@ class Lib:
     def allreduce_sum(self, ct, comm):
         """Sum over the ranks of `comm` (an NCCL communicator as an integer address), then reduce modulo each prime."""
         self._chk(self._fn("allreduce_sum")(self.ctx, ct.ptr, C.c_void_p(comm)))
+
+    def reduce_sum(self, ct, root, my_rank, comm):
+        """Sum over the ranks to `root`, which then reduces modulo each prime; other ranks keep their buffer."""
+        self._chk(self._fn("reduce_sum")(self.ctx, ct.ptr, C.c_int(root), C.c_int(my_rank), C.c_void_p(comm)))
+
+    def allgather(self, mine, all_, comm):
+        """`all_` (batch = ranks x batch of `mine`) receives every rank's `mine`, rank-major."""
+        self._chk(self._fn("allgather")(self.ctx, mine.ptr, all_.ptr, C.c_void_p(comm)))
+
+    def nccl_group_start(self):
+        rc = self._fn("nccl_group_start")()
+        if rc != 0:
+            raise HBError(rc, "ncclGroupStart failed")
+
+    def nccl_group_end(self):
+        rc = self._fn("nccl_group_end")()
+        if rc != 0:
+            raise HBError(rc, "ncclGroupEnd failed")
+
+    def send(self, ct, peer, comm):
+        self._chk(self._fn("send")(self.ctx, ct.ptr, C.c_int(peer), C.c_void_p(comm)))
+
+    def recv(self, ct, peer, comm):
+        self._chk(self._fn("recv")(self.ctx, ct.ptr, C.c_int(peer), C.c_void_p(comm)))
+
+    def sum_mod_reduce(self, parts):
+        """(sum of the parts) mod q in one pass: the owner's half of a K-split exchange."""
+        arr = (C.c_void_p * len(parts))(*[p.ptr.value for p in parts])
+        return self._op("sum_mod_reduce", arr, C.c_int(len(parts)))
+
+    def mod_reduce(self, ct):
+        self._chk(self._fn("mod_reduce")(self.ctx, ct.ptr))
+
+    def set_host_threads(self, n):
+        self._chk(self._fn("set_host_threads")(self.ctx, C.c_int(n)))
+
+    # ---- CUDA graph of a fixed call sequence ----
+    def graph_begin(self):
+        self._chk(self._fn("graph_begin")(self.ctx))
+
+    def graph_end(self):
+        out = C.c_void_p()
+        self._chk(self._fn("graph_end")(self.ctx, C.byref(out)))
+        return Handle(self, out, "graph")
+
+    def graph_launch(self, g):
+        self._chk(self._fn("graph_launch")(self.ctx, g.ptr))
+
+    def graph_kernels(self, g):
+        f = self._fn("graph_kernels")
+        f.restype = C.c_uint64
+        return int(f(g.ptr))
 
     def batch_concat(self, parts):
         arr = (C.c_void_p * len(parts))(*[p.ptr.value for p in parts])

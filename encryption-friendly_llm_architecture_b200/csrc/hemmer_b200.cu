@@ -65,6 +65,11 @@ struct Evk { u64 *d = nullptr; int nd = 0; };
 struct NcclApi {
     ncclResult_t (*AllReduce)(const void *, void *, size_t, ncclDataType_t, ncclRedOp_t, ncclComm_t, cudaStream_t) = nullptr;
     ncclResult_t (*AllGather)(const void *, void *, size_t, ncclDataType_t, ncclComm_t, cudaStream_t) = nullptr;
+    ncclResult_t (*Reduce)(const void *, void *, size_t, ncclDataType_t, ncclRedOp_t, int, ncclComm_t, cudaStream_t) = nullptr;
+    ncclResult_t (*Send)(const void *, size_t, ncclDataType_t, int, ncclComm_t, cudaStream_t) = nullptr;
+    ncclResult_t (*Recv)(void *, size_t, ncclDataType_t, int, ncclComm_t, cudaStream_t) = nullptr;
+    ncclResult_t (*GroupStart)() = nullptr;
+    ncclResult_t (*GroupEnd)() = nullptr;
     ncclResult_t (*GetUniqueId)(ncclUniqueId *) = nullptr;
     ncclResult_t (*CommInitRank)(ncclComm_t *, int, ncclUniqueId, int) = nullptr;
     ncclResult_t (*CommDestroy)(ncclComm_t) = nullptr;
@@ -79,11 +84,17 @@ const NcclApi &nccl_api() {
         auto sym = [&](const char *n) { void *p = dlsym(RTLD_DEFAULT, n); return p ? p : (h && h != RTLD_DEFAULT ? dlsym(h, n) : nullptr); };
         a.AllReduce = (decltype(a.AllReduce))sym("ncclAllReduce");
         a.AllGather = (decltype(a.AllGather))sym("ncclAllGather");
+        a.Reduce = (decltype(a.Reduce))sym("ncclReduce");
+        a.Send = (decltype(a.Send))sym("ncclSend");
+        a.Recv = (decltype(a.Recv))sym("ncclRecv");
+        a.GroupStart = (decltype(a.GroupStart))sym("ncclGroupStart");
+        a.GroupEnd = (decltype(a.GroupEnd))sym("ncclGroupEnd");
         a.GetUniqueId = (decltype(a.GetUniqueId))sym("ncclGetUniqueId");
         a.CommInitRank = (decltype(a.CommInitRank))sym("ncclCommInitRank");
         a.CommDestroy = (decltype(a.CommDestroy))sym("ncclCommDestroy");
         a.GetErrorString = (decltype(a.GetErrorString))sym("ncclGetErrorString");
-        a.ok = a.AllReduce && a.AllGather && a.GetUniqueId && a.CommInitRank && a.CommDestroy && a.GetErrorString;
+        a.ok = a.AllReduce && a.AllGather && a.Reduce && a.Send && a.Recv && a.GroupStart && a.GroupEnd && a.GetUniqueId && a.CommInitRank && a.CommDestroy &&
+               a.GetErrorString;
         return a;
     }();
     return api;
@@ -108,8 +119,16 @@ struct hb_ctx {
     std::map<int, DivPlan *> div_plans;
     u64 *pinned = nullptr; size_t pinned_bytes = 0; // host staging buffer of hb_decrypt_many
     ChaChaKey ckey{};
+    std::map<std::pair<int, long long>, u32 *> gal_tables; // (copies, row_step) -> Galois elements of hb_matmul_acc, on the device
+    int host_threads = 0;                                 // cap for the host-side encode / decode workers (0: all cores, at most 32)
+    bool capturing = false;                               // between hb_graph_begin and hb_graph_end
+    unsigned long long launches_at_capture = 0, alg_at_capture = 0;
     int N = 0, logn = 0, L = 0, K = 0, nprimes = 0;
     unsigned long long launches = 0; // kernels launched by this context
+    // Compulsory HBM traffic of the primitives called so far, in limbs of N words: every input of a primitive read once,
+    // every output written once, a switching key or plaintext once per batch (temporaries and transforms inside a
+    // primitive do not count).  Divided by the HBM peak this is the time the call sequence cannot go below.
+    unsigned long long alg_limbs = 0;
 
     LimbMap qmap(int level) const { LimbMap m{}; m.n = level + 1; for (int i = 0; i <= level; ++i) m.prime[i] = (unsigned char)i; return m; }
     LimbMap allmap() const { LimbMap m{}; m.n = nprimes; for (int i = 0; i < nprimes; ++i) m.prime[i] = (unsigned char)i; return m; }
@@ -119,6 +138,7 @@ struct hb_ctx {
 };
 
 #define LAUNCH(c) ((c)->launches++, 0)
+#define ALG(c, limbs) ((c)->alg_limbs += (unsigned long long)(limbs))
 struct hb_ct { hb_ctx *ctx; int level, np, batch, spow; u64 *d; size_t limbs() const { return (size_t)batch * np * (level + 1); } };
 struct hb_pt { hb_ctx *ctx; int level, spow; u64 *d; int ext = 0; }; // ext: K further limbs modulo the special primes follow the level+1 limbs
 // lifted digits of the a-part of a ciphertext batch, NTT form: what all rotations of that ciphertext share
@@ -127,6 +147,13 @@ struct hb_digits { hb_ctx *ctx; int level, batch; u64 *d; };
 struct hb_mkey { hb_ctx *ctx; int level; u32 g; u64 *key, *pm; };
 
 namespace {
+
+// entry points that wait for the stream or copy to / from the host cannot be part of a recorded graph
+void no_capture(const hb_ctx *c, const char *what) { if (c->capturing) fail(HB_E_ARG, std::string(what) + ": not available while a graph is being recorded"); }
+// A handle is only valid with the context that made it: its buffer lives in that context's pool, on that
+// context's device.
+template <class H> void own1(const hb_ctx *c, const H *h) { if (h && h->ctx != c) fail(HB_E_ARG, "handle belongs to another context"); }
+template <class... H> void own(const hb_ctx *c, const H *...h) { (own1(c, h), ...); }
 
 hb_ct *new_ct(hb_ctx *c, int level, int np, int batch, int spow) {
     if (level < 0 || level > c->L || np < 1 || np > 3 || batch < 1 || spow < 1 || spow > 2) fail(HB_E_ARG, "bad ciphertext geometry");
@@ -146,6 +173,13 @@ struct Tmp { // pool buffer released at scope exit
     Tmp(const Tmp &) = delete;
 };
 
+struct TmpBytes { // the same for a byte count (staging buffers of int64 coefficients)
+    hb_ctx *c; void *p;
+    TmpBytes(hb_ctx *cc, size_t bytes) : c(cc), p(cc->pool.get(bytes)) {}
+    ~TmpBytes() { c->pool.put(p); }
+    TmpBytes(const TmpBytes &) = delete;
+};
+
 void ntt(hb_ctx *c, const u64 *src, size_t so, u64 *dst, size_t dof, int count, const LimbMap &m, bool inv) {
     c->launches += (count == 0) ? 0 : (c->logn == 16 ? 2 : 1);
     CK(launch_ntt(c->st, src, so, dst, dof, count, m, c->pc, c->tb, c->logn, inv));
@@ -156,6 +190,7 @@ void ntt_inplace(hb_ctx *c, u64 *d, int count, const LimbMap &m, bool inv) { ntt
 const KsPlan *get_plan(hb_ctx *c, int level) {
     auto it = c->plans.find(level);
     if (it != c->plans.end()) return it->second;
+    no_capture(c, "first key switch at this level");
     const HostCtx &h = *c->h;
     auto P = std::make_unique<KsPlan>();
     std::memset(P.get(), 0, sizeof(KsPlan));
@@ -229,6 +264,8 @@ PlanDims plan_dims(hb_ctx *c, int level) {
     return p;
 }
 
+size_t key_limbs(hb_ctx *c, int level) { const PlanDims d = plan_dims(c, level); return (size_t)2 * d.nd * d.ne; } // the part of a switching key one key switch reads
+
 // Hybrid key switch of polynomial a (NTT form, `n` limbs, per-batch stride a_outer) with key `key`:
 //   out[b][p][l] = ModDown(sum_dg perm_g(lift_dg(a)) (.) key_dg)[p][l] + add_p[b][l] o perm_g
 // Phase 1 of a key switch (shared by every rotation of the same polynomial -- "hoisting"):
@@ -269,15 +306,35 @@ void keyswitch(hb_ctx *c, const u64 *a, size_t a_outer, int level, int batch, co
     ks_apply(c, a, a_outer, dt.p, level, batch, key, g, out, out_outer, add0, add1, add_outer);
 }
 
+// Galois elements of the row shifts k * row_step, k < copies, kept on the device per (copies, row_step): the fused
+// plaintext-matmul accumulate reads them on every call, and a per-call upload would need a host synchronisation.
+const u32 *galois_table(hb_ctx *c, int copies, i64 row_step) {
+    const auto key = std::make_pair(copies, (long long)row_step);
+    auto it = c->gal_tables.find(key);
+    if (it != c->gal_tables.end()) return it->second;
+    if (c->capturing) fail(HB_E_ARG, "matmul_acc: first use of this (copies, row_step) pair inside a graph capture; run the step once before capturing");
+    std::vector<u32> gal((size_t)copies);
+    for (int k = 0; k < copies; ++k) gal[(size_t)k] = (u32)c->h->galois_rot((i64)k * row_step);
+    u32 *d = nullptr;
+    CK(cudaMalloc(&d, (size_t)copies * 4));
+    cudaError_t e = cudaMemcpyAsync(d, gal.data(), (size_t)copies * 4, cudaMemcpyHostToDevice, c->st);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(c->st); // gal goes out of scope
+    if (e != cudaSuccess) { cudaFree(d); throw CudaFail{e, "galois_table upload"}; }
+    c->gal_tables[key] = d;
+    return d;
+}
+
 // switching key for secret s' (g == 0: s^2, else s o perm_g); stream ids kid*64 + digit
 Evk make_key(hb_ctx *c, u64 kid, u32 g) {
     if (!c->have_sk) fail(HB_E_NOKEY, "secret key not generated");
+    no_capture(c, "key generation");
     const HostCtx &h = *c->h;
     const int N = c->N, np = c->nprimes, nd = h.digit_of(h.L) + 1;
     Evk k; k.nd = nd; k.d = c->alloc_limbs((size_t)nd * 2 * np);
     const LimbMap am = c->allmap();
     Tmp e(c, (size_t)np);
-    i64 *ecoef = (i64 *)c->pool.get((size_t)N * 8);
+    TmpBytes ecoef_buf(c, (size_t)N * 8);
+    i64 *ecoef = (i64 *)ecoef_buf.p;
     Scalars pmod{};
     for (int pi = 0; pi <= h.L; ++pi) { u64 v = 1; for (int j = 0; j < h.K; ++j) v = hbhost::mulmod(v, h.q[h.L + 1 + j] % h.q[pi], h.q[pi]); pmod.v[pi] = v; }
     std::vector<i64> ev;
@@ -292,7 +349,6 @@ Evk make_key(hb_ctx *c, u64 kid, u32 g) {
         LAUNCH(c), k_keygen<<<c->egrid(np), 256, 0, c->st>>>(b, a, e.p, c->sk, c->pc, N, c->logn, g, h.digit_lo(dg), h.digit_hi(dg, h.L + 1), pmod);
     }
     CK(cudaGetLastError());
-    c->pool.put(ecoef);
     return k;
 }
 const Evk &galois_key(hb_ctx *c, u64 g) {
@@ -305,6 +361,7 @@ const Evk &galois_key(hb_ctx *c, u64 g) {
 const DivPlan *get_div_plan(hb_ctx *c, int level) {
     auto it = c->div_plans.find(level);
     if (it != c->div_plans.end()) return it->second;
+    no_capture(c, "first masked rotation at this level");
     const HostCtx &h = *c->h;
     auto P = std::make_unique<DivPlan>();
     std::memset(P.get(), 0, sizeof(DivPlan));
@@ -361,6 +418,7 @@ hb_ct *divide_by_p_ql(hb_ctx *c, const u64 *E, int level, int batch) {
 // rescale(p1 (.) rot(a, s1) + p2 (.) rot(a, s2)) from the lifted digits `dt` of a: both inner products stay in
 // Q_level u P, are multiplied there by the extended plaintexts and summed; one division by P * q_level follows.
 hb_ct *do_assemble_rot(hb_ctx *c, const hb_ct *a, const u64 *dt, int64_t s1, const hb_pt *p1, int64_t s2, const hb_pt *p2) {
+    own(c, a); own(c, p1, p2);
     if (a->np != 2 || a->spow != 1) fail(HB_E_SHAPE, "assemble_rot: needs a rescaled 2-poly ciphertext");
     if (a->level < 1) fail(HB_E_LEVEL, "assemble_rot: level 0");
     if (!p1->ext || !p2->ext || p1->level != a->level || p2->level != a->level || p1->spow != 1 || p2->spow != 1)
@@ -377,6 +435,7 @@ hb_ct *do_assemble_rot(hb_ctx *c, const hb_ct *a, const u64 *dt, int64_t s1, con
     rp.mask[0] = p1->d; rp.mask[1] = p2->d;
     rp.g[0] = (u32)g1; rp.g[1] = (u32)g2;
     Tmp E(c, (size_t)batch * 2 * ne);
+    ALG(c, (size_t)batch * (2 * n + d.dt_count + 2 * (n - 1)) + 2 * ((size_t)d.nd * 2 * ne + ne));
     const size_t a_outer = (size_t)2 * n * N;
     LAUNCH(c), k_ks_inner_pair<<<dim3(c->gx(), ne, batch), 256, 0, c->st>>>(E.p, a->d, a->d + (size_t)n * N, a_outer, dt, rp, c->nprimes, pl, dv, c->pc, c->logn, N);
     return divide_by_p_ql(c, E.p, level, batch);
@@ -384,6 +443,7 @@ hb_ct *do_assemble_rot(hb_ctx *c, const hb_ct *a, const u64 *dt, int64_t s1, con
 // the same from keys that already carry the masks (hb_masked_key_create).  `groups` wrapped copies of the same input
 // (each with its own one or two keys: k1s[g], k2s[g] or null) come out of one launch sequence, group-major.
 hb_ct *do_assemble_mk(hb_ctx *c, const hb_ct *a, const u64 *dt, const hb_mkey *const *k1s, const hb_mkey *const *k2s, int groups) {
+    own(c, a);
     if (a->np != 2 || a->spow != 1) fail(HB_E_SHAPE, "assemble: needs a rescaled 2-poly ciphertext");
     if (a->level < 1) fail(HB_E_LEVEL, "assemble: level 0");
     if (groups < 1 || groups > kMaxRotGroups) fail(HB_E_LIMIT, "assemble: 1 to 16 wrapped copies per call");
@@ -395,6 +455,7 @@ hb_ct *do_assemble_mk(hb_ctx *c, const hb_ct *a, const u64 *dt, const hb_mkey *c
         mr.count = ks[1] ? 2 : 1;
         for (int r = 0; r < mr.count; ++r) {
             if (ks[r]->level != a->level) fail(HB_E_LEVEL, "assemble: masked key of another level");
+            own(c, ks[r]);
             mr.mkey[r] = ks[r]->key; mr.pm[r] = ks[r]->pm; mr.g[r] = ks[r]->g;
         }
     }
@@ -403,6 +464,8 @@ hb_ct *do_assemble_mk(hb_ctx *c, const hb_ct *a, const u64 *dt, const hb_mkey *c
     const PlanDims d = plan_dims(c, level);
     const int n = d.n, ne = d.ne;
     Tmp E(c, (size_t)groups * batch * 2 * ne);
+    for (int g = 0; g < groups; ++g) ALG(c, (size_t)mrl.r[g].count * ((size_t)d.nd * 2 * ne + n) + (size_t)batch * 2 * (n - 1));
+    ALG(c, (size_t)batch * (2 * n + d.dt_count));
     constexpr int kEl = 4; // coefficients per thread (2, with three CTAs resident per SM, measured no faster)
     LAUNCH(c), k_ks_inner_mk<kEl><<<dim3((unsigned)((N + 256 * kEl - 1) / (256 * kEl)), groups * batch, ne), 256, 0, c->st>>>(E.p, a->d, a->d + (size_t)n * N, (size_t)2 * n * N, dt, mrl, batch, pl, c->pc,
                                                                                                                         c->logn, N);
@@ -415,10 +478,12 @@ void check_same(const hb_ct *a, const hb_ct *b, const char *what) {
 }
 
 hb_ct *do_rescale(hb_ctx *c, const hb_ct *a) {
+    own(c, a);
     if (a->level < 1) fail(HB_E_LEVEL, "rescale: level 0");
     if (a->spow != 2) fail(HB_E_SHAPE, "rescale: nothing to rescale");
     const int l = a->level, N = c->N, nbp = a->batch * a->np;
     hb_ct *r = new_ct(c, l - 1, a->np, a->batch, 1);
+    ALG(c, (size_t)nbp * (2 * l + 1));
     try {
         Tmp last(c, (size_t)nbp), t(c, (size_t)nbp * l);
         LimbMap lm{}; lm.n = 1; lm.prime[0] = (unsigned char)l;
@@ -440,6 +505,7 @@ hb_ct *do_prod_rescale(hb_ctx *c, const hb_ct *const *a, const hb_pt *const *p, 
     TermList tl{}; tl.count = count;
     for (int j = 0; j < count; ++j) {
         if (a[j]->level != a0->level || p[j]->level != a0->level) fail(HB_E_LEVEL, "mul_pt: level mismatch");
+        own(c, a[j]); own(c, p[j]);
         if (a[j]->np != a0->np || a[j]->batch != a0->batch) fail(HB_E_SHAPE, "product sum: shape mismatch");
         if (a[j]->spow != 1 || p[j]->spow != 1) fail(HB_E_SHAPE, "mul_pt: operand not rescaled");
         tl.a[j] = a[j]->d; tl.p[j] = p[j]->d;
@@ -447,6 +513,7 @@ hb_ct *do_prod_rescale(hb_ctx *c, const hb_ct *const *a, const hb_pt *const *p, 
     const int l = a0->level, N = c->N, nbp = a0->batch * a0->np, groups = separate ? count : 1;
     const unsigned gx = c->gx();
     hb_ct *r = new_ct(c, l - 1, a0->np, a0->batch, 1);
+    ALG(c, (size_t)count * ((size_t)nbp * (l + 1) + (l + 1)) + (size_t)nbp * l);
     try {
         Tmp last(c, (size_t)groups * nbp), S(c, (size_t)nbp), t(c, (size_t)nbp * l);
         LAUNCH(c), k_last_prod<<<dim3(gx, nbp, groups), 256, 0, c->st>>>(last.p, tl, separate ? 1 : 0, l, nbp, c->pc, N);
@@ -463,6 +530,7 @@ hb_ct *do_prod_rescale(hb_ctx *c, const hb_ct *const *a, const hb_pt *const *p, 
     return r;
 }
 hb_ct *do_level_down(hb_ctx *c, const hb_ct *a, int target) {
+    own(c, a);
     if (target > a->level || target < 0) fail(HB_E_LEVEL, "level_down: bad target");
     if (a->spow != 1) fail(HB_E_SHAPE, "level_down: operand not rescaled");
     const int N = c->N, nbp = a->batch * a->np, tl = target + 1;
@@ -473,6 +541,7 @@ hb_ct *do_level_down(hb_ctx *c, const hb_ct *a, int target) {
         const i64 k = (i64)std::rint(cf);
         Scalars s{};
         for (int i = 0; i <= tl; ++i) s.v[i] = (u64)(k % (i64)c->h->q[i]);
+        ALG(c, (size_t)nbp * (tl + 1)); // the input limbs that survive; do_rescale counts the rest
         LAUNCH(c), k_scalar_mul<<<c->egrid(nbp * (tl + 1)), 256, 0, c->st>>>(t->d, a->d, (size_t)(a->level + 1) * N, c->qmap(tl), c->pc, N, s);
         CK(cudaGetLastError());
         r = do_rescale(c, t);
@@ -481,6 +550,7 @@ hb_ct *do_level_down(hb_ctx *c, const hb_ct *a, int target) {
     return r;
 }
 hb_ct *do_addsub(hb_ctx *c, const hb_ct *a, const hb_ct *b, int mode) {
+    own(c, a, b);
     if (a->level != b->level) { // level-adjusting add: bring the higher operand down first
         const hb_ct *hi = a->level > b->level ? a : b;
         hb_ct *low = do_level_down(c, hi, std::min(a->level, b->level));
@@ -491,11 +561,13 @@ hb_ct *do_addsub(hb_ctx *c, const hb_ct *a, const hb_ct *b, int mode) {
     }
     check_same(a, b, "add");
     hb_ct *r = new_ct(c, a->level, a->np, a->batch, a->spow);
+    ALG(c, 3 * a->limbs());
     LAUNCH(c), k_addsub<<<c->egrid((int)a->limbs()), 256, 0, c->st>>>(r->d, a->d, b->d, c->qmap(a->level), c->pc, c->N, mode);
     return r;
 }
 // acc (+)= sum over `groups` of tensor(a[g], b[g]); a, b hold groups * batch members, group-major
 hb_ct *do_tensor(hb_ctx *c, const hb_ct *a, const hb_ct *b, hb_ct *acc, int groups = 1) {
+    own(c, a, b, acc);
     check_same(a, b, "tensor");
     if (a->np != 2 || a->spow != 1) fail(HB_E_SHAPE, "tensor: operands must be rescaled 2-poly ciphertexts");
     if (groups < 1 || groups > kMaxRotGroups || a->batch % groups) fail(HB_E_SHAPE, "tensor: the batch does not split into that many groups");
@@ -504,34 +576,41 @@ hb_ct *do_tensor(hb_ctx *c, const hb_ct *a, const hb_ct *b, hb_ct *acc, int grou
     if (r) { if (r->level != a->level || r->np != 3 || r->batch != batch || r->spow != 2) fail(HB_E_SHAPE, "tensor_acc: accumulator mismatch"); }
     else r = new_ct(c, a->level, 3, batch, 2);
     const int n = a->level + 1;
+    ALG(c, 2 * a->limbs() + (size_t)(acc ? 2 : 1) * batch * 3 * n);
     LAUNCH(c), k_tensor<<<c->egrid(batch * n), 256, 0, c->st>>>(r->d, a->d, b->d, n, c->qmap(a->level), c->pc, c->N, acc ? 1 : 0, groups, batch);
     return r;
 }
 hb_ct *do_relin(hb_ctx *c, const hb_ct *a) {
+    own(c, a);
     if (a->np != 3) fail(HB_E_SHAPE, "relin: needs 3 polys");
     if (!c->mult_key.d) fail(HB_E_NOKEY, "multiplication key not generated");
     const int n = a->level + 1, N = c->N;
     hb_ct *r = new_ct(c, a->level, 2, a->batch, a->spow);
+    ALG(c, (size_t)a->batch * 5 * n + key_limbs(c, a->level));
     try {
         keyswitch(c, a->d + (size_t)2 * n * N, (size_t)3 * n * N, a->level, a->batch, c->mult_key, 0, r->d, (size_t)2 * n * N, a->d, a->d + (size_t)n * N, (size_t)3 * n * N);
     } catch (...) { hb_ct_free(r); throw; }
     return r;
 }
 hb_ct *do_galois(hb_ctx *c, const hb_ct *a, u64 g) {
+    own(c, a);
     if (a->np != 2) fail(HB_E_SHAPE, "rotate: needs 2 polys");
     const int n = a->level + 1, N = c->N;
     if (g == 1) { hb_ct *r = new_ct(c, a->level, 2, a->batch, a->spow); CK(cudaMemcpyAsync(r->d, a->d, a->limbs() * N * 8, cudaMemcpyDeviceToDevice, c->st)); return r; }
     const Evk &key = galois_key(c, g);
     hb_ct *r = new_ct(c, a->level, 2, a->batch, a->spow);
+    ALG(c, (size_t)a->batch * 4 * n + key_limbs(c, a->level));
     try {
         keyswitch(c, a->d + (size_t)n * N, (size_t)2 * n * N, a->level, a->batch, key, (u32)g, r->d, (size_t)2 * n * N, a->d, nullptr, (size_t)2 * n * N);
     } catch (...) { hb_ct_free(r); throw; }
     return r;
 }
 hb_ct *do_mul_pt(hb_ctx *c, const hb_ct *a, const hb_pt *p) {
+    own(c, a); own(c, p);
     if (a->level != p->level) fail(HB_E_LEVEL, "mul_pt: level mismatch");
     if (a->spow != 1 || p->spow != 1) fail(HB_E_SHAPE, "mul_pt: operand not rescaled");
     hb_ct *r = new_ct(c, a->level, a->np, a->batch, 2);
+    ALG(c, 2 * a->limbs() + a->level + 1);
     LAUNCH(c), k_mul_pt<<<c->egrid((int)a->limbs()), 256, 0, c->st>>>(r->d, a->d, p->d, c->qmap(a->level), c->pc, c->N);
     return r;
 }
@@ -560,6 +639,12 @@ u64 *noalloc_scratch(int device) {
     return g_noalloc_ptr[device];
 }
 
+// host threads for the encode / decode halves of hb_encrypt_many / hb_decrypt_many
+int host_workers(const hb_ctx *c, int tasks) {
+    const int cap = c->host_threads > 0 ? c->host_threads : std::min(32, std::max(1, (int)std::thread::hardware_concurrency()));
+    return std::max(1, std::min(tasks, cap));
+}
+
 template <class F> int guard(hb_ctx *c, F &&f) {
     try { CK(cudaSetDevice(c->device)); f(); return HB_OK; }
     catch (const ArgFail &e) { c->err = e.msg; return e.code; }
@@ -582,6 +667,7 @@ int hb_ctx_create(const hb_params *prm, int device, hb_ctx **out) {
                       {prm->seed[0], prm->seed[1], prm->seed[2], prm->seed[3]}};
         c->h.reset(new HostCtx(hp));
         if (!(c->h->logn == 16 || (c->h->logn >= 10 && c->h->logn <= 12))) throw std::invalid_argument("log_n must be 16, or 10..12 for small test contexts");
+        if (c->h->digit_of(c->h->L) + 1 > 8) throw std::invalid_argument("more than 8 key-switch digits");
         c->device = device; c->N = c->h->N; c->logn = c->h->logn; c->L = c->h->L; c->K = c->h->K; c->nprimes = c->h->nprimes;
         for (int i = 0; i < 8; ++i) c->ckey.k[i] = c->h->cha.key[i];
         CK(cudaSetDevice(device));
@@ -603,7 +689,11 @@ int hb_ctx_create(const hb_params *prm, int device, hb_ctx **out) {
             p.q_inv_f = 1.0 / (double)q;
             p.n_inv_f = (double)p.n_inv / (double)q;
             p.fp = q < ((u64)1 << 44) ? 1 : 0;
-            p.pad = 0;
+            // lazy FP64-assisted products are below 1.6 q; reduce_fp takes sums below 2^52.  Every fixed-length lazy sum in
+            // the kernels has at most 128 terms (16 rotated terms x 8 digits), which any prime below 2^44 allows (>= 160);
+            // the open-ended sum of k_matmul_acc folds at this count.
+            p.lazy_terms = (u64)((((unsigned __int128)1 << 52) * 5) / ((unsigned __int128)q * 8));
+            if (p.fp && p.lazy_terms < 160) throw std::invalid_argument("prime too large for the lazy FP64-assisted sums");
             std::vector<u64> f, fs, iv, ivs;
             c->h->twiddles(i, f, fs, iv, ivs);
             if (p.small) { // companion tables hold w/q as doubles instead of Shoup quotients
@@ -635,6 +725,7 @@ void hb_ctx_destroy(hb_ctx *c) {
     if (c->st) cudaStreamSynchronize(c->st);
     for (auto &kv : c->plans) cudaFree(kv.second);
     for (auto &kv : c->div_plans) cudaFree(kv.second);
+    for (auto &kv : c->gal_tables) cudaFree(kv.second);
     if (c->pinned) cudaFreeHost(c->pinned);
     if (c->pc) cudaFree(c->pc);
     if (c->tw) cudaFree(c->tw);
@@ -654,7 +745,7 @@ int hb_ctx_dims(const hb_ctx *c, int *log_n, int *max_level, int *num_special) {
     if (log_n) *log_n = c->logn; if (max_level) *max_level = c->L; if (num_special) *num_special = c->K;
     return HB_OK;
 }
-int hb_sync(hb_ctx *c) { return guard(c, [&] { CK(cudaStreamSynchronize(c->st)); }); }
+int hb_sync(hb_ctx *c) { return guard(c, [&] { no_capture(c, "sync"); CK(cudaStreamSynchronize(c->st)); }); }
 int hb_mem_info(const hb_ctx *c, uint64_t *pool_bytes, uint64_t *in_use) {
     if (pool_bytes) *pool_bytes = c->pool.total;
     if (in_use) *in_use = c->pool.in_use;
@@ -662,18 +753,20 @@ int hb_mem_info(const hb_ctx *c, uint64_t *pool_bytes, uint64_t *in_use) {
 }
 void *hb_stream(const hb_ctx *c) { return (void *)c->st; }
 uint64_t hb_launch_count(const hb_ctx *c) { return c ? c->launches : 0; }
+uint64_t hb_algorithmic_bytes(const hb_ctx *c) { return c ? c->alg_limbs * (uint64_t)c->N * 8 : 0; }
 
 int hb_keygen(hb_ctx *c) {
     return guard(c, [&] {
+        no_capture(c, "keygen");
         const HostCtx &h = *c->h;
         std::vector<i64> s; h.sample_secret(s);
-        i64 *sc = (i64 *)c->pool.get((size_t)c->N * 8);
+        TmpBytes sc_buf(c, (size_t)c->N * 8);
+        i64 *sc = (i64 *)sc_buf.p;
         CK(cudaMemcpyAsync(sc, s.data(), (size_t)c->N * 8, cudaMemcpyHostToDevice, c->st));
         const LimbMap am = c->allmap();
         LAUNCH(c), k_reduce_i64<<<c->egrid(c->nprimes), 256, 0, c->st>>>(c->sk, sc, am, c->pc, c->N);
         ntt_inplace(c, c->sk, c->nprimes, am, false);
         CK(cudaStreamSynchronize(c->st));
-        c->pool.put(sc);
         c->have_sk = true;
         if (!c->mult_key.d) c->mult_key = make_key(c, 0, 0);
         const u64 gc = h.galois_conj();
@@ -692,6 +785,7 @@ int hb_gen_rot_keys(hb_ctx *c, const int64_t *steps, int n) {
 uint64_t hb_galois_for_rotation(const hb_ctx *c, int64_t s) { return c->h->galois_rot(s); }
 int hb_evk_export(hb_ctx *c, uint64_t g, uint64_t *host, int *digits) {
     return guard(c, [&] {
+        no_capture(c, "evk_export");
         const Evk *k = g == 0 ? &c->mult_key : &galois_key(c, g);
         if (!k->d) fail(HB_E_NOKEY, "key not generated");
         if (digits) *digits = k->nd;
@@ -701,23 +795,27 @@ int hb_evk_export(hb_ctx *c, uint64_t g, uint64_t *host, int *digits) {
 
 int hb_encode(hb_ctx *c, const double *re, const double *im, size_t n, int level, hb_pt **out) {
     return guard(c, [&] {
+        no_capture(c, "encode");
         if (!re || !out || n > (size_t)c->h->slots) fail(HB_E_ARG, "encode: bad message");
         if (level < 0 || level > c->L) fail(HB_E_LEVEL, "encode: bad level");
         std::vector<i64> coef;
         c->h->encode_coeffs(re, im, n, c->h->scale[level], coef);
         hb_pt *p = new_pt(c, level, 1);
-        i64 *dc = (i64 *)c->pool.get((size_t)c->N * 8);
-        CK(cudaMemcpyAsync(dc, coef.data(), (size_t)c->N * 8, cudaMemcpyHostToDevice, c->st));
-        const LimbMap qm = c->qmap(level);
-        LAUNCH(c), k_reduce_i64<<<c->egrid(level + 1), 256, 0, c->st>>>(p->d, dc, qm, c->pc, c->N);
-        ntt_inplace(c, p->d, level + 1, qm, false);
-        CK(cudaStreamSynchronize(c->st)); // coef goes out of scope
-        c->pool.put(dc);
+        try {
+            TmpBytes dcb(c, (size_t)c->N * 8);
+            i64 *dc = (i64 *)dcb.p;
+            CK(cudaMemcpyAsync(dc, coef.data(), (size_t)c->N * 8, cudaMemcpyHostToDevice, c->st));
+            const LimbMap qm = c->qmap(level);
+            LAUNCH(c), k_reduce_i64<<<c->egrid(level + 1), 256, 0, c->st>>>(p->d, dc, qm, c->pc, c->N);
+            ntt_inplace(c, p->d, level + 1, qm, false);
+            CK(cudaStreamSynchronize(c->st)); // coef goes out of scope
+        } catch (...) { hb_pt_free(p); throw; }
         *out = p;
     });
 }
 int hb_encode_ext(hb_ctx *c, const double *re, const double *im, size_t n, int level, hb_pt **out) {
     return guard(c, [&] {
+        no_capture(c, "encode_ext");
         if (!re || !out || n > (size_t)c->h->slots) fail(HB_E_ARG, "encode: bad message");
         if (level < 0 || level > c->L) fail(HB_E_LEVEL, "encode: bad level");
         std::vector<i64> coef;
@@ -726,14 +824,16 @@ int hb_encode_ext(hb_ctx *c, const double *re, const double *im, size_t n, int l
         hb_pt *p = new hb_pt{c, level, 1, nullptr};
         p->ext = 1;
         try { p->d = c->alloc_limbs((size_t)ne); } catch (...) { delete p; throw; }
-        i64 *dc = (i64 *)c->pool.get((size_t)c->N * 8);
-        CK(cudaMemcpyAsync(dc, coef.data(), (size_t)c->N * 8, cudaMemcpyHostToDevice, c->st));
-        LimbMap em{}; em.n = ne;
-        for (int j = 0; j < ne; ++j) em.prime[j] = (unsigned char)(j <= level ? j : c->L + 1 + (j - level - 1));
-        LAUNCH(c), k_reduce_i64<<<c->egrid(ne), 256, 0, c->st>>>(p->d, dc, em, c->pc, c->N);
-        ntt_inplace(c, p->d, ne, em, false);
-        CK(cudaStreamSynchronize(c->st)); // coef goes out of scope
-        c->pool.put(dc);
+        try {
+            TmpBytes dcb(c, (size_t)c->N * 8);
+            i64 *dc = (i64 *)dcb.p;
+            CK(cudaMemcpyAsync(dc, coef.data(), (size_t)c->N * 8, cudaMemcpyHostToDevice, c->st));
+            LimbMap em{}; em.n = ne;
+            for (int j = 0; j < ne; ++j) em.prime[j] = (unsigned char)(j <= level ? j : c->L + 1 + (j - level - 1));
+            LAUNCH(c), k_reduce_i64<<<c->egrid(ne), 256, 0, c->st>>>(p->d, dc, em, c->pc, c->N);
+            ntt_inplace(c, p->d, ne, em, false);
+            CK(cudaStreamSynchronize(c->st)); // coef goes out of scope
+        } catch (...) { hb_pt_free(p); throw; }
         *out = p;
     });
 }
@@ -749,6 +849,7 @@ static void decode_limbs(hb_ctx *c, const u64 *dev_coef, int level, int spow, do
 }
 int hb_decode(hb_ctx *c, const hb_pt *p, double *re, double *im) {
     return guard(c, [&] {
+        no_capture(c, "decode");
         const int nl = p->level >= 1 ? 2 : 1;
         Tmp t(c, (size_t)nl);
         ntt(c, p->d, (size_t)nl * c->N, t.p, (size_t)nl * c->N, nl, c->qmap(nl - 1), true);
@@ -757,6 +858,7 @@ int hb_decode(hb_ctx *c, const hb_pt *p, double *re, double *im) {
 }
 int hb_encrypt(hb_ctx *c, const hb_pt *p, uint64_t nonce, hb_ct **out) {
     return guard(c, [&] {
+        no_capture(c, "encrypt");
         if (!c->have_sk) fail(HB_E_NOKEY, "secret key not generated");
         const int n = p->level + 1, N = c->N;
         hb_ct *r = new_ct(c, p->level, 2, 1, p->spow);
@@ -765,14 +867,14 @@ int hb_encrypt(hb_ctx *c, const hb_pt *p, uint64_t nonce, hb_ct **out) {
             u64 *b = r->d, *a = r->d + (size_t)n * N;
             LAUNCH(c), k_uniform<<<dim3((unsigned)((N / 4 + 255) / 256), n), 256, 0, c->st>>>(a, qm, c->pc, N, c->ckey, hbhost::STREAM_ENC_A, nonce);
             std::vector<i64> ev; c->h->sample_gauss(hbhost::STREAM_ENC_E, nonce, ev);
-            i64 *ec = (i64 *)c->pool.get((size_t)N * 8);
+            TmpBytes ecb(c, (size_t)N * 8);
+            i64 *ec = (i64 *)ecb.p;
             Tmp e(c, (size_t)n);
             CK(cudaMemcpyAsync(ec, ev.data(), (size_t)N * 8, cudaMemcpyHostToDevice, c->st));
             LAUNCH(c), k_reduce_i64<<<c->egrid(n), 256, 0, c->st>>>(e.p, ec, qm, c->pc, N);
             ntt_inplace(c, e.p, n, qm, false);
             LAUNCH(c), k_encrypt<<<c->egrid(n), 256, 0, c->st>>>(b, a, e.p, c->sk, p->d, qm, c->pc, N);
             CK(cudaStreamSynchronize(c->st));
-            c->pool.put(ec);
         } catch (...) { hb_ct_free(r); throw; }
         *out = r;
     });
@@ -780,6 +882,7 @@ int hb_encrypt(hb_ctx *c, const hb_pt *p, uint64_t nonce, hb_ct **out) {
 // encode + encrypt `count` messages into one batched handle; member i is bit for bit hb_encrypt(hb_encode(message i), nonces[i])
 int hb_encrypt_many(hb_ctx *c, const double *re, const double *im, size_t n_slots, int count, int level, const uint64_t *nonces, hb_ct **out) {
     return guard(c, [&] {
+        no_capture(c, "encrypt_many");
         if (!c->have_sk) fail(HB_E_NOKEY, "secret key not generated");
         if (!re || !nonces || !out || count < 1 || n_slots > (size_t)c->h->slots) fail(HB_E_ARG, "encrypt_many: bad message");
         if (level < 0 || level > c->L) fail(HB_E_LEVEL, "encrypt_many: bad level");
@@ -794,7 +897,7 @@ int hb_encrypt_many(hb_ctx *c, const double *re, const double *im, size_t n_slot
             c->pinned_bytes = words * 8;
         }
         i64 *host = (i64 *)c->pinned; // [count][2][N]: message coefficients, error coefficients
-        const int workers = std::max(1, std::min({count, (int)std::thread::hardware_concurrency(), 32}));
+        const int workers = host_workers(c, count);
         std::vector<std::thread> pool;
         for (int w = 0; w < workers; ++w)
             pool.emplace_back([&, w] {
@@ -810,7 +913,8 @@ int hb_encrypt_many(hb_ctx *c, const double *re, const double *im, size_t n_slot
         hb_ct *r = new_ct(c, level, 2, count, 1);
         try {
             const LimbMap qm = c->qmap(level);
-            i64 *dc = (i64 *)c->pool.get(words * 8);
+            TmpBytes dcb(c, words * 8);
+            i64 *dc = (i64 *)dcb.p;
             Tmp me(c, (size_t)count * 2 * n); // [count][message | error][n][N]
             CK(cudaMemcpyAsync(dc, host, words * 8, cudaMemcpyHostToDevice, c->st));
             for (int i = 0; i < count * 2; ++i)
@@ -823,13 +927,13 @@ int hb_encrypt_many(hb_ctx *c, const double *re, const double *im, size_t n_slot
             }
             CK(cudaGetLastError());
             CK(cudaStreamSynchronize(c->st)); // the staging buffer is reused by the next call
-            c->pool.put(dc);
         } catch (...) { hb_ct_free(r); throw; }
         *out = r;
     });
 }
 int hb_decrypt(hb_ctx *c, const hb_ct *ct, int index, double *re, double *im) {
     return guard(c, [&] {
+        no_capture(c, "decrypt");
         if (!c->have_sk) fail(HB_E_NOKEY, "secret key not generated");
         if (index < 0 || index >= ct->batch) fail(HB_E_ARG, "decrypt: bad batch index");
         const int n = ct->level + 1, N = c->N, nl = ct->level >= 1 ? 2 : 1;
@@ -842,6 +946,7 @@ int hb_decrypt(hb_ctx *c, const hb_ct *ct, int index, double *re, double *im) {
 
 int hb_decrypt_many(hb_ctx *c, const hb_ct *const *cts, const int *index, int count, double *re, double *im) {
     return guard(c, [&] {
+        no_capture(c, "decrypt_many");
         if (!c->have_sk) fail(HB_E_NOKEY, "secret key not generated");
         if (count < 1 || !cts || !re) fail(HB_E_ARG, "decrypt_many: nothing to decrypt");
         const int N = c->N, slots = c->h->slots;
@@ -879,7 +984,7 @@ int hb_decrypt_many(hb_ctx *c, const hb_ct *const *cts, const int *index, int co
         CK(cudaMemcpyAsync(c->pinned, t.p, bytes, cudaMemcpyDeviceToHost, c->st));
         CK(cudaStreamSynchronize(c->st));
         // CRT lift and inverse embedding on the host cores, one member per task
-        const int workers = std::max(1, std::min({count, (int)std::thread::hardware_concurrency(), 32}));
+        const int workers = host_workers(c, count);
         std::vector<std::thread> pool;
         const HostCtx &h = *c->h;
         const u64 *host = c->pinned;
@@ -905,7 +1010,7 @@ int hb_ct_clone(hb_ctx *c, const hb_ct *s, hb_ct **out) {
         *out = r;
     });
 }
-int hb_ct_zero(hb_ctx *c, hb_ct *x) { return guard(c, [&] { CK(cudaMemsetAsync(x->d, 0, x->limbs() * c->N * 8, c->st)); }); }
+int hb_ct_zero(hb_ctx *c, hb_ct *x) { return guard(c, [&] { own(c, x); CK(cudaMemsetAsync(x->d, 0, x->limbs() * c->N * 8, c->st)); }); }
 void hb_ct_free(hb_ct *x) { if (x) { x->ctx->pool.put(x->d); delete x; } }
 void hb_pt_free(hb_pt *x) { if (x) { x->ctx->pool.put(x->d); delete x; } }
 int hb_ct_meta(const hb_ct *x, int *level, int *np, int *batch, int *spow) {
@@ -915,17 +1020,18 @@ int hb_ct_meta(const hb_ct *x, int *level, int *np, int *batch, int *spow) {
 }
 int hb_pt_meta(const hb_pt *x, int *level, int *spow) { if (!x) return HB_E_ARG; if (level) *level = x->level; if (spow) *spow = x->spow; return HB_OK; }
 int hb_ct_import(hb_ctx *c, hb_ct *x, const uint64_t *host) {
-    return guard(c, [&] { CK(cudaMemcpyAsync(x->d, host, x->limbs() * c->N * 8, cudaMemcpyHostToDevice, c->st)); CK(cudaStreamSynchronize(c->st)); });
+    return guard(c, [&] { no_capture(c, "ct_import"); own(c, x); CK(cudaMemcpyAsync(x->d, host, x->limbs() * c->N * 8, cudaMemcpyHostToDevice, c->st)); CK(cudaStreamSynchronize(c->st)); });
 }
 int hb_ct_export(hb_ctx *c, const hb_ct *x, uint64_t *host) {
-    return guard(c, [&] { CK(cudaMemcpyAsync(host, x->d, x->limbs() * c->N * 8, cudaMemcpyDeviceToHost, c->st)); CK(cudaStreamSynchronize(c->st)); });
+    return guard(c, [&] { no_capture(c, "ct_export"); own(c, x); CK(cudaMemcpyAsync(host, x->d, x->limbs() * c->N * 8, cudaMemcpyDeviceToHost, c->st)); CK(cudaStreamSynchronize(c->st)); });
 }
 int hb_pt_export(hb_ctx *c, const hb_pt *x, uint64_t *host) {
-    return guard(c, [&] { CK(cudaMemcpyAsync(host, x->d, (size_t)(x->level + 1) * c->N * 8, cudaMemcpyDeviceToHost, c->st)); CK(cudaStreamSynchronize(c->st)); });
+    return guard(c, [&] { no_capture(c, "pt_export"); own(c, x); CK(cudaMemcpyAsync(host, x->d, (size_t)(x->level + 1) * c->N * 8, cudaMemcpyDeviceToHost, c->st)); CK(cudaStreamSynchronize(c->st)); });
 }
 void *hb_ct_device_ptr(const hb_ct *x) { return x ? x->d : nullptr; }
 int hb_batch_set(hb_ctx *c, hb_ct *dst, int idx, const hb_ct *src) {
     return guard(c, [&] {
+        own(c, dst, src);
         if (src->level != dst->level || src->np != dst->np || idx < 0 || (idx + 1) * src->batch > dst->batch) fail(HB_E_SHAPE, "batch_set: mismatch");
         const size_t per = (size_t)src->batch * src->np * (src->level + 1) * c->N; // position counted in units of src's batch
         CK(cudaMemcpyAsync(dst->d + per * idx, src->d, per * 8, cudaMemcpyDeviceToDevice, c->st));
@@ -973,6 +1079,7 @@ int hb_sub(hb_ctx *c, const hb_ct *a, const hb_ct *b, hb_ct **out) { return guar
 int hb_negate(hb_ctx *c, const hb_ct *a, hb_ct **out) {
     return guard(c, [&] {
         hb_ct *r = new_ct(c, a->level, a->np, a->batch, a->spow);
+        ALG(c, 2 * a->limbs());
         LAUNCH(c), k_addsub<<<c->egrid((int)a->limbs()), 256, 0, c->st>>>(r->d, a->d, a->d, c->qmap(a->level), c->pc, c->N, 2);
         *out = r;
     });
@@ -980,6 +1087,7 @@ int hb_negate(hb_ctx *c, const hb_ct *a, hb_ct **out) {
 int hb_mult_imag(hb_ctx *c, const hb_ct *a, hb_ct **out) {
     return guard(c, [&] {
         hb_ct *r = new_ct(c, a->level, a->np, a->batch, a->spow);
+        ALG(c, 2 * a->limbs());
         LAUNCH(c), k_mult_imag<<<c->egrid((int)a->limbs()), 256, 0, c->st>>>(r->d, a->d, c->qmap(a->level), c->pc, c->N);
         *out = r;
     });
@@ -989,6 +1097,7 @@ int hb_mult_int(hb_ctx *c, const hb_ct *a, int64_t k, hb_ct **out) {
         hb_ct *r = new_ct(c, a->level, a->np, a->batch, a->spow);
         Scalars s{};
         for (int i = 0; i <= a->level; ++i) { const i64 q = (i64)c->h->q[i]; i64 v = k % q; if (v < 0) v += q; s.v[i] = (u64)v; }
+        ALG(c, 2 * a->limbs());
         LAUNCH(c), k_scalar_mul<<<c->egrid((int)a->limbs()), 256, 0, c->st>>>(r->d, a->d, (size_t)(a->level + 1) * c->N, c->qmap(a->level), c->pc, c->N, s);
         *out = r;
     });
@@ -1005,6 +1114,7 @@ int hb_rescale(hb_ctx *c, const hb_ct *a, hb_ct **out) { return guard(c, [&] { *
 int hb_rescale_noalloc(hb_ctx *c, const hb_ct *a, hb_ct *out) {
     return guard(c, [&] {
         if (!a || !out) fail(HB_E_ARG, "rescale_noalloc: null handle");
+        own(c, a, out);
         if (a->level < 1) fail(HB_E_LEVEL, "rescale: level 0");
         if (a->spow != 2) fail(HB_E_SHAPE, "rescale: nothing to rescale");
         if (out->level != a->level - 1 || out->np != a->np || out->batch != a->batch) fail(HB_E_SHAPE, "rescale_noalloc: output handle must be level-1 with the same polys and batch");
@@ -1055,11 +1165,13 @@ int hb_mul(hb_ctx *c, const hb_ct *a, const hb_ct *b, hb_ct **out) {
 int hb_decompose(hb_ctx *c, const hb_ct *a, hb_digits **out) {
     return guard(c, [&] {
         if (a->np != 2) fail(HB_E_SHAPE, "decompose: needs 2 polys");
+        own(c, a);
         const PlanDims d = plan_dims(c, a->level);
         const int n = a->level + 1, N = c->N;
         hb_digits *h = new hb_digits{c, a->level, a->batch, nullptr};
         try {
             h->d = c->alloc_limbs((size_t)a->batch * d.dt_count);
+            ALG(c, (size_t)a->batch * (n + d.dt_count));
             ks_decompose(c, a->d + (size_t)n * N, (size_t)2 * n * N, a->level, a->batch, h->d);
         } catch (...) { c->pool.put(h->d); delete h; throw; }
         *out = h;
@@ -1069,12 +1181,14 @@ void hb_digits_free(hb_digits *h) { if (h) { h->ctx->pool.put(h->d); delete h; }
 int hb_rotate_hoisted(hb_ctx *c, const hb_ct *a, const hb_digits *dg, int64_t steps, hb_ct **out) {
     return guard(c, [&] {
         if (a->np != 2 || dg->level != a->level || dg->batch != a->batch) fail(HB_E_SHAPE, "rotate_hoisted: digits do not belong to this ciphertext");
+        own(c, a); own(c, dg);
         const u64 g = c->h->galois_rot(steps);
         const int n = a->level + 1, N = c->N;
         hb_ct *r = new_ct(c, a->level, 2, a->batch, a->spow);
         if (g == 1) { CK(cudaMemcpyAsync(r->d, a->d, a->limbs() * N * 8, cudaMemcpyDeviceToDevice, c->st)); *out = r; return; }
         try {
             const Evk &key = galois_key(c, g);
+            ALG(c, (size_t)a->batch * (4 * n + plan_dims(c, a->level).dt_count) + key_limbs(c, a->level));
             ks_apply(c, a->d + (size_t)n * N, (size_t)2 * n * N, dg->d, a->level, a->batch, key, (u32)g, r->d, (size_t)2 * n * N, a->d, nullptr, (size_t)2 * n * N);
         } catch (...) { hb_ct_free(r); throw; }
         *out = r;
@@ -1141,6 +1255,7 @@ int hb_rotate_sum(hb_ctx *c, const hb_ct *const *xs, const int64_t *steps, int c
         const hb_ct *x0 = xs[0];
         for (int t = 0; t < count; ++t)
             if (!xs[t] || xs[t]->np != 2 || xs[t]->level != x0->level || xs[t]->batch != x0->batch || xs[t]->spow != x0->spow) fail(HB_E_SHAPE, "rotate_sum: operands differ in shape");
+        for (int t = 0; t < count; ++t) own(c, xs[t]);
         const int level = x0->level, batch = x0->batch, N = c->N;
         const KsPlan *pl = get_plan(c, level);
         const PlanDims d = plan_dims(c, level);
@@ -1165,6 +1280,7 @@ int hb_rotate_sum(hb_ctx *c, const hb_ct *const *xs, const int64_t *steps, int c
                 rot.t[rot.count++] = RotTerm{xs[t]->d + (size_t)n * N, dt, key.d, (u32)g, 0u};
             }
             const unsigned gx1 = (unsigned)((N + 255) / 256), gx = c->gx();
+            ALG(c, (size_t)(count + 1) * batch * 2 * n + (size_t)rot.count * key_limbs(c, level));
             Tmp add(c, (size_t)batch * 2 * n);
             LAUNCH(c), k_rot_sum_addend<<<dim3(gx, n, batch * 2), 256, 0, c->st>>>(add.p, rot, plain, n, c->qmap(level), c->pc, c->logn, N);
             if (rot.count == 0) {
@@ -1186,7 +1302,7 @@ int hb_rotate_sum(hb_ctx *c, const hb_ct *const *xs, const int64_t *steps, int c
 }
 int hb_rotate(hb_ctx *c, const hb_ct *a, int64_t steps, hb_ct **out) { return guard(c, [&] { *out = do_galois(c, a, c->h->galois_rot(steps)); }); }
 int hb_conjugate(hb_ctx *c, const hb_ct *a, hb_ct **out) { return guard(c, [&] { *out = do_galois(c, a, c->h->galois_conj()); }); }
-int hb_ntt(hb_ctx *c, hb_ct *a, int inverse) { return guard(c, [&] { ntt_inplace(c, a->d, (int)a->limbs(), c->qmap(a->level), inverse != 0); }); }
+int hb_ntt(hb_ctx *c, hb_ct *a, int inverse) { return guard(c, [&] { own(c, a); ntt_inplace(c, a->d, (int)a->limbs(), c->qmap(a->level), inverse != 0); }); }
 
 int hb_mul2_add_rescale(hb_ctx *c, const hb_ct *a, const hb_pt *pa, const hb_ct *b, const hb_pt *pb, hb_ct **out) {
     return guard(c, [&] {
@@ -1199,21 +1315,19 @@ int hb_matmul_acc_multi(hb_ctx *c, const hb_ct *pre, int btotal, int b0, const h
     return guard(c, [&] {
         if (btotal < 1 || pre->batch % btotal || b0 < 0 || bcount < 1 || b0 + bcount > btotal || bcount > 16) fail(HB_E_SHAPE, "matmul_acc: group selection");
         if (pre->np != 2 || pre->spow != 1) fail(HB_E_SHAPE, "matmul_acc: operands");
+        own(c, pre);
         PtList pl{};
         for (int b = 0; b < bcount; ++b) {
             if (pre->level != pts[b]->level) fail(HB_E_LEVEL, "matmul_acc: plaintext level differs from the ciphertexts'");
+            own(c, pts[b]);
             if (pts[b]->spow != 1) fail(HB_E_SHAPE, "matmul_acc: operands");
             pl.p[b] = pts[b]->d;
         }
         const int n = pre->level + 1, kc = pre->batch / btotal;
-        std::vector<u32> gal((size_t)kc);
-        for (int k = 0; k < kc; ++k) gal[(size_t)k] = (u32)c->h->galois_rot((i64)k * row_step);
-        u32 *dg = (u32 *)c->pool.get((size_t)kc * 4);
-        CK(cudaMemcpyAsync(dg, gal.data(), (size_t)kc * 4, cudaMemcpyHostToDevice, c->st));
+        const u32 *dg = galois_table(c, kc, row_step);
         hb_ct *r = new_ct(c, pre->level, 2, 1, 2);
+        ALG(c, (size_t)kc * bcount * 2 * n + (size_t)bcount * n + 2 * n);
         LAUNCH(c), k_matmul_acc<<<c->egrid(2 * n), 256, 0, c->st>>>(r->d, pre->d, kc, btotal, b0, bcount, pl, dg, n, c->qmap(pre->level), c->pc, c->logn, c->N);
-        CK(cudaStreamSynchronize(c->st));
-        c->pool.put(dg);
         *out = r;
     });
 }
@@ -1248,12 +1362,33 @@ int hb_pt_add(hb_ctx *c, const hb_pt *a, const hb_pt *b, hb_pt **out) {
     });
 }
 int hb_mod_reduce(hb_ctx *c, hb_ct *a) {
-    return guard(c, [&] { LAUNCH(c), k_mod_reduce<<<c->egrid((int)a->limbs()), 256, 0, c->st>>>(a->d, c->qmap(a->level), c->pc, c->N); });
+    return guard(c, [&] {
+        own(c, a);
+        LAUNCH(c), k_mod_reduce<<<c->egrid((int)a->limbs()), 256, 0, c->st>>>(a->d, c->qmap(a->level), c->pc, c->N);
+    });
+}
+// out = (sum of the parts) mod q, one pass: the owner's half of a K-split exchange (its own partial product plus the
+// ones received from the other ranks).  Parts hold canonical residues; at most 16 of them.
+int hb_sum_mod_reduce(hb_ctx *c, const hb_ct *const *parts, int count, hb_ct **out) {
+    return guard(c, [&] {
+        if (!parts || count < 1 || count > 16) fail(HB_E_LIMIT, "sum_mod_reduce: 1 to 16 parts");
+        SumList sl{}; sl.count = count;
+        for (int t = 0; t < count; ++t) {
+            own(c, parts[t]);
+            check_same(parts[0], parts[t], "sum_mod_reduce");
+            sl.x[t] = parts[t]->d;
+        }
+        hb_ct *r = new_ct(c, parts[0]->level, parts[0]->np, parts[0]->batch, parts[0]->spow);
+        ALG(c, (size_t)(count + 1) * r->limbs());
+        LAUNCH(c), k_sum_mod<<<c->egrid((int)r->limbs()), 256, 0, c->st>>>(r->d, sl, c->qmap(r->level), c->pc, c->N);
+        *out = r;
+    });
 }
 // Sum over ranks of residues below 2^60 cannot overflow 64 bits for up to 16 ranks; the owner
 // reduces afterwards (same order of operations as HEMMer::ncclAllReduceWrapper + modReduct).
 int hb_allreduce_sum(hb_ctx *c, hb_ct *a, void *comm) {
     return guard(c, [&] {
+        own(c, a);
         const NcclApi &nc = nccl_api();
         if (!nc.ok) fail(HB_E_NCCL, "NCCL library not available");
         ncclResult_t r = nc.AllReduce(a->d, a->d, a->limbs() * c->N, ncclUint64, ncclSum, (ncclComm_t)comm, c->st);
@@ -1261,12 +1396,47 @@ int hb_allreduce_sum(hb_ctx *c, hb_ct *a, void *comm) {
         LAUNCH(c), k_mod_reduce<<<c->egrid((int)a->limbs()), 256, 0, c->st>>>(a->d, c->qmap(a->level), c->pc, c->N);
     });
 }
+// Sum to one owner: TransformerBlock::ncclReduceWrapper / ncclReduceWrapperHidden (ncclReduce to `root`), followed on
+// the root by the reduction modulo each prime.  The other ranks' buffers are left as they were.
+int hb_reduce_sum(hb_ctx *c, hb_ct *a, int root, int my_rank, void *comm) {
+    return guard(c, [&] {
+        own(c, a);
+        const NcclApi &nc = nccl_api();
+        if (!nc.ok) fail(HB_E_NCCL, "NCCL library not available");
+        ncclResult_t r = nc.Reduce(a->d, a->d, a->limbs() * c->N, ncclUint64, ncclSum, root, (ncclComm_t)comm, c->st);
+        if (r != ncclSuccess) fail(HB_E_NCCL, nc.GetErrorString(r));
+        if (my_rank == root) LAUNCH(c), k_mod_reduce<<<c->egrid((int)a->limbs()), 256, 0, c->st>>>(a->d, c->qmap(a->level), c->pc, c->N);
+    });
+}
 int hb_allgather(hb_ctx *c, const hb_ct *mine, hb_ct *all, void *comm) {
     return guard(c, [&] {
+        own(c, mine, all);
         if (all->level != mine->level || all->np != mine->np || all->batch % mine->batch) fail(HB_E_SHAPE, "allgather: geometry");
         const NcclApi &nc = nccl_api();
         if (!nc.ok) fail(HB_E_NCCL, "NCCL library not available");
         ncclResult_t r = nc.AllGather(mine->d, all->d, mine->limbs() * c->N, ncclUint64, (ncclComm_t)comm, c->st);
+        if (r != ncclSuccess) fail(HB_E_NCCL, nc.GetErrorString(r));
+    });
+}
+// Point-to-point moves of whole handles, to be issued between hb_nccl_group_start and hb_nccl_group_end on both sides
+// (every send needs its receive in the same group, as NCCL requires).
+int hb_nccl_group_start() { const NcclApi &nc = nccl_api(); return nc.ok && nc.GroupStart() == ncclSuccess ? HB_OK : HB_E_NCCL; }
+int hb_nccl_group_end() { const NcclApi &nc = nccl_api(); return nc.ok && nc.GroupEnd() == ncclSuccess ? HB_OK : HB_E_NCCL; }
+int hb_send(hb_ctx *c, const hb_ct *a, int peer, void *comm) {
+    return guard(c, [&] {
+        own(c, a);
+        const NcclApi &nc = nccl_api();
+        if (!nc.ok) fail(HB_E_NCCL, "NCCL library not available");
+        ncclResult_t r = nc.Send(a->d, a->limbs() * c->N, ncclUint64, peer, (ncclComm_t)comm, c->st);
+        if (r != ncclSuccess) fail(HB_E_NCCL, nc.GetErrorString(r));
+    });
+}
+int hb_recv(hb_ctx *c, hb_ct *a, int peer, void *comm) {
+    return guard(c, [&] {
+        own(c, a);
+        const NcclApi &nc = nccl_api();
+        if (!nc.ok) fail(HB_E_NCCL, "NCCL library not available");
+        ncclResult_t r = nc.Recv(a->d, a->limbs() * c->N, ncclUint64, peer, (ncclComm_t)comm, c->st);
         if (r != ncclSuccess) fail(HB_E_NCCL, nc.GetErrorString(r));
     });
 }
@@ -1293,6 +1463,54 @@ int hb_nccl_comm_destroy(void *comm) {
     const NcclApi &nc = nccl_api();
     if (!nc.ok) return HB_E_NCCL;
     return nc.CommDestroy((ncclComm_t)comm) == ncclSuccess ? HB_OK : HB_E_NCCL;
+}
+
+
+int hb_set_host_threads(hb_ctx *c, int n) { if (!c || n < 0) return HB_E_ARG; c->host_threads = n; return HB_OK; }
+
+// ---- CUDA graph of a fixed launch sequence -------------------------------------------------------------------
+// Between hb_graph_begin and hb_graph_end the calls made on this context are recorded instead of run.  The pool hands
+// out the same buffers as in any other pass, so the recorded kernels read and write fixed addresses: the caller keeps
+// the operand handles alive and unchanged in place, and keeps the result handles of the recorded pass for as long as
+// it replays the graph (every replay writes the results into those same buffers).  Everything the pass needs that is
+// made on first use -- rotation keys, plans, masks, masked keys, Galois tables, pool buffers -- must exist already:
+// run the pass once before recording it.  Calls that copy to or from the host are refused while recording.
+struct hb_graph { hb_ctx *ctx; cudaGraph_t g; cudaGraphExec_t e; unsigned long long kernels, alg_limbs; };
+int hb_graph_begin(hb_ctx *c) {
+    return guard(c, [&] {
+        if (c->capturing) fail(HB_E_ARG, "graph: already recording");
+        CK(cudaStreamBeginCapture(c->st, cudaStreamCaptureModeRelaxed));
+        c->capturing = true;
+        c->launches_at_capture = c->launches;
+        c->alg_at_capture = c->alg_limbs;
+    });
+}
+int hb_graph_end(hb_ctx *c, hb_graph **out) {
+    return guard(c, [&] {
+        if (!c->capturing) fail(HB_E_ARG, "graph: not recording");
+        c->capturing = false;
+        cudaGraph_t g = nullptr;
+        CK(cudaStreamEndCapture(c->st, &g));
+        cudaGraphExec_t e = nullptr;
+        cudaError_t rc = cudaGraphInstantiate(&e, g, 0);
+        if (rc != cudaSuccess) { cudaGraphDestroy(g); throw CudaFail{rc, "cudaGraphInstantiate"}; }
+        *out = new hb_graph{c, g, e, c->launches - c->launches_at_capture, c->alg_limbs - c->alg_at_capture};
+    });
+}
+int hb_graph_launch(hb_ctx *c, hb_graph *g) {
+    return guard(c, [&] {
+        if (!g || g->ctx != c) fail(HB_E_ARG, "graph belongs to another context");
+        CK(cudaGraphLaunch(g->e, c->st));
+        c->launches += g->kernels;
+        c->alg_limbs += g->alg_limbs;
+    });
+}
+uint64_t hb_graph_kernels(const hb_graph *g) { return g ? g->kernels : 0; }
+void hb_graph_free(hb_graph *g) {
+    if (!g) return;
+    cudaSetDevice(g->ctx->device);
+    cudaGraphExecDestroy(g->e); cudaGraphDestroy(g->g);
+    delete g;
 }
 
 } // extern "C"

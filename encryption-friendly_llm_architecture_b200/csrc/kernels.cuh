@@ -158,6 +158,21 @@ __global__ void k_mod_reduce(u64 *__restrict__ a, LimbMap map, const PrimeConst 
         a[off] = reduce_u64(a[off], m);
     }
 }
+// out = (x_0 + ... + x_{count-1}) mod q for canonical residues (count <= 16: the sum stays below 2^64)
+struct SumList { const u64 *x[16]; int count; };
+__global__ void k_sum_mod(u64 *__restrict__ out, SumList sl, LimbMap map, const PrimeConst *__restrict__ pc, int N) {
+    const int li = blockIdx.y;
+#pragma unroll
+    for (int u_ = 0; u_ < kElems; ++u_) {
+        const int i = (blockIdx.x * kElems + u_) * blockDim.x + threadIdx.x;
+        if (i >= N) break;
+        const PrimeConst m = pc[map.prime[li % map.n]];
+        const size_t off = (size_t)li * N + i;
+        u64 v = 0;
+        for (int t = 0; t < sl.count; ++t) v += sl.x[t][off];
+        out[off] = reduce_u64(v, m);
+    }
+}
 
 // ---------------- rescale ----------------
 // t[bp][l][i] = centred(last[bp][i]) mod q_l, l < level.  grid.y = nbp * level
@@ -907,11 +922,12 @@ __global__ void k_matmul_acc(u64 *__restrict__ out, const u64 *__restrict__ pre,
 #pragma unroll
     for (int u = 0; u < kElems; ++u) total[u] = 0;
     // the four coefficients of a thread sit in the inner loop: their loads (and those of the next K-group) overlap
-    if (m.fp) { // lazy terms below 1.6q: thousands fit in 64 bits
+    if (m.fp) { // lazy terms below 1.6q: the running sum is folded before it can reach 2^52 (reduce_fp's input range)
         u64 acc[kElems];
 #pragma unroll
         for (int u = 0; u < kElems; ++u) acc[u] = 0;
         int terms = 0;
+        const int fold_at = (int)m.lazy_terms - 16; // a round of the inner loop adds at most 16 terms (bcount <= 16)
         for (int k = 0; k < kcount; ++k) {
             const u32 g = __ldg(gal + k);
             u32 src[kElems];
@@ -924,7 +940,7 @@ __global__ void k_matmul_acc(u64 *__restrict__ out, const u64 *__restrict__ pre,
                 for (int u = 0; u < kElems; ++u) acc[u] += mul_small_lazy(a[u * blockDim.x], w[src[u]], m.q_inv_f, m.q);
             }
             terms += bcount;
-            if (terms >= 256) {
+            if (terms > fold_at) {
 #pragma unroll
                 for (int u = 0; u < kElems; ++u) { total[u] = add_mod(total[u], reduce_fp(acc[u], m.q_inv_f, m.q), m.q); acc[u] = 0; }
                 terms = 0;

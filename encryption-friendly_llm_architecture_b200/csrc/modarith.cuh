@@ -26,7 +26,7 @@ struct PrimeConst {
     double q_inv_f;     // 1/q
     double n_inv_f;     // n_inv / q
     u64 fp;             // 1 when q < 2^44: element-wise kernels take quotients from the FP64 pipe
-    u64 pad;
+    u64 lazy_terms;     // how many lazy products (each below 1.6 q) may be summed before the sum reaches 2^52
 };
 
 // Limb instances of a launch: instance li (0 <= li < count) uses prime[li % n].

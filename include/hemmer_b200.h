@@ -71,6 +71,11 @@ int hb_mem_info(const hb_ctx *ctx, uint64_t *pool_bytes, uint64_t *in_use_bytes)
 void *hb_stream(const hb_ctx *ctx);
 /* number of kernels this context has launched since creation */
 uint64_t hb_launch_count(const hb_ctx *ctx);
+/* Compulsory HBM traffic, in bytes, of the primitives this context has run since creation: every input of a primitive
+ * (rotation, rescale, tensor, relinearise, plaintext product, fused accumulate ...) read once, every output written
+ * once, a switching key or plaintext once per batch; the transforms and temporaries inside a primitive do not count.
+ * Divided by the HBM bandwidth it is the time a call sequence cannot go below ("schedule roofline"). */
+uint64_t hb_algorithmic_bytes(const hb_ctx *ctx);
 
 /* KeyGenerator::genCommonKeys -- KeyGenerator.hpp:160-165: secret, multiplication and conjugation keys */
 int hb_keygen(hb_ctx *ctx);
@@ -225,8 +230,41 @@ int hb_mod_reduce(hb_ctx *ctx, hb_ct *a);
 int hb_nccl_unique_id(void *id128);
 int hb_nccl_comm_init(hb_ctx *ctx, int nranks, int rank, const void *id128, void **comm);
 int hb_nccl_comm_destroy(void *comm);
+/* in place: a <- (sum over ranks of a) mod q on every rank -- HEMMer::ncclAllReduceWrapper (HEMMer.cpp:2625-2635) + modReduct */
 int hb_allreduce_sum(hb_ctx *ctx, hb_ct *a, void *nccl_comm);
+/* sum to one owner: on `root`, a <- (sum over ranks of a) mod q; elsewhere a is left as it was --
+ * TransformerBlock::ncclReduceWrapper / ncclReduceWrapperHidden (TransformerBlock.cpp:11100-11140) + modReduct */
+int hb_reduce_sum(hb_ctx *ctx, hb_ct *a, int root, int my_rank, void *nccl_comm);
+/* `all` (batch = ranks * batch(mine)) receives every rank's `mine`, rank-major: tiles of a sublayer replicated for the next one */
 int hb_allgather(hb_ctx *ctx, const hb_ct *mine, hb_ct *all, void *nccl_comm);
+/* Point-to-point moves of whole handles for a K-split exchange in which only the ranks that hold partial products of
+ * a tile talk to its owner.  Sends and receives are issued between hb_nccl_group_start() and hb_nccl_group_end() on
+ * both sides (ncclGroupStart / ncclGroupEnd as in TransformerBlock.cpp:11106-11119); hb_sum_mod_reduce then adds the
+ * owner's own partial product and the received ones and reduces modulo every prime in one pass (at most 16 parts). */
+int hb_nccl_group_start(void);
+int hb_nccl_group_end(void);
+int hb_send(hb_ctx *ctx, const hb_ct *a, int peer, void *nccl_comm);
+int hb_recv(hb_ctx *ctx, hb_ct *a, int peer, void *nccl_comm);
+int hb_sum_mod_reduce(hb_ctx *ctx, const hb_ct *const *parts, int count, hb_ct **out);
+
+/* Host threads used by the encode / decode halves of hb_encrypt_many / hb_decrypt_many (0: every core, at most 32).
+ * Several ranks on one host each take cores / ranks.  No counterpart in the reference (one process per GPU under mpirun). */
+int hb_set_host_threads(hb_ctx *ctx, int n);
+
+/* CUDA graph of a fixed sequence of calls on this context (no counterpart in the reference, which launches every
+ * kernel from the host each time).  Calls made between hb_graph_begin and hb_graph_end are recorded instead of run;
+ * hb_graph_launch replays them on the context's stream.  Device buffers come from the context's pool exactly as in
+ * an unrecorded pass, so the recorded kernels use fixed addresses: keep the operand handles alive and update them
+ * in place only, and keep the result handles of the recorded pass while the graph is in use -- every replay writes
+ * its results there.  Whatever is made on first use (rotation keys, masks, masked keys, per-level plans) must exist
+ * before recording: run the sequence once first.  Calls that wait for the stream or copy to / from the host
+ * (encode, encrypt, decrypt, import, export, sync) return HB_E_ARG while recording. */
+typedef struct hb_graph hb_graph;
+int hb_graph_begin(hb_ctx *ctx);
+int hb_graph_end(hb_ctx *ctx, hb_graph **out);
+int hb_graph_launch(hb_ctx *ctx, hb_graph *graph);
+uint64_t hb_graph_kernels(const hb_graph *graph); /* kernels recorded in the graph */
+void hb_graph_free(hb_graph *graph);
 
 #ifdef __cplusplus
 }

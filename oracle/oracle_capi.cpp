@@ -109,8 +109,29 @@ int orc_batch_get(orc_ctx *c, const orc_ct *src, int idx, orc_ct **out) {
     })
 }
 int orc_ct_zero(orc_ctx *, orc_ct *x) { std::fill(x->d.begin(), x->d.end(), 0); return 0; }
-// single-process stand-in for the collective: one rank, so the sum is the operand itself
+// single-process stand-ins for the collectives, so that the host-side logic of the multi-rank layer driver can be
+// walked through on the CPU (operation bookkeeping in dry mode): nothing is exchanged
 int orc_allreduce_sum(orc_ctx *, orc_ct *, void *) { return 0; }
+int orc_nccl_group_start() { return 0; }
+int orc_nccl_group_end() { return 0; }
+int orc_send(orc_ctx *, const orc_ct *, int, void *) { return 0; }
+int orc_recv(orc_ctx *, orc_ct *, int, void *) { return 0; }
+// exact modular sum of canonical residues (what the owner of a tile computes from the partial products)
+int orc_sum_mod_reduce(orc_ctx *c, const orc_ct *const *parts, int count, orc_ct **out) {
+    ORC_TRY(c, {
+        Evaluator::require(count >= 1 && count <= 16, "sum_mod_reduce");
+        Ct *r = new Ct(*parts[0]);
+        for (int t = 1; t < count && !r->d.empty(); ++t) {
+            Evaluator::require(parts[t]->d.size() == r->d.size(), "sum_mod_reduce: shape");
+            const size_t per = (size_t)c->cx.N, limbs = r->d.size() / per, n = (size_t)r->level + 1;
+            for (size_t l = 0; l < limbs; ++l) {
+                const uint64_t q = c->cx.mod[l % n].q;
+                for (size_t i = 0; i < per; ++i) { uint64_t v = r->d[l * per + i] + parts[t]->d[l * per + i]; r->d[l * per + i] = v >= q ? v - q : v; }
+            }
+        }
+        *out = r;
+    })
+}
 int orc_batch_concat(orc_ctx *c, const orc_ct *const *parts, int n, orc_ct **out) {
     ORC_TRY(c, {
         int total = 0;

@@ -33,7 +33,7 @@ def sc_transforms(lib, H):
 
 
 def sc_ccmm_single_tile(lib, H, target=2):
-    """BASELINE config 1 shape: one d x d tile per ciphertext, half of the slots used."""
+    """Single ct x ct product: one d x d tile per ciphertext, half of the slots used."""
     d = tile_dim(lib)
     A, B = _mats(101, d, 2)
     a, b = H.encrypt(A, nonce=3), H.encrypt(B, nonce=4)

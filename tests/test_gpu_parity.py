@@ -233,7 +233,7 @@ def pkg_handle(lib, ptr):
 
 def test_full_size_golden_fixtures(pkg, gpu_full):
     """Full-size results against digests recorded from the oracle (no oracle run needed here):
-    the primitive sweep cases and BASELINE config 1, one 128x128 ct x ct product."""
+    the primitive sweep cases and a single 128x128 ct x ct product with one tile per ciphertext."""
     import hashlib, json, os
     from conftest import ROOT
     gold = json.load(open(os.path.join(ROOT, "tests", "golden", "golden.json")))["full"]
