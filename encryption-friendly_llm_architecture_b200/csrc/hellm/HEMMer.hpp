@@ -90,6 +90,19 @@ class HEMMer {
     void decrypt2(const CtxtTensor &t, double *out) const; // [2][h][w]
 
     void addInplace(CtxtTensor &a, const CtxtTensor &b) const;
+    // HEMMer::hadamardMultInplace (HEMMer.hpp:107-115; HEMMer.cpp:702-713): slot-wise product, ciphertext or plaintext operand
+    void hadamardMultInplace(CtxtTensor &a, const CtxtTensor &b) const;
+    void hadamardMultInplace(CtxtTensor &a, const PtxtTensor &b) const;
+    // HEMMer::oneMatRotSumInplace (HEMMer.cpp:882-919): row sums of the left half of a's tiles and of the right half of
+    // b's tiles, spread over every column -- the norm terms of the Gaussian-kernel attention scores
+    void oneMatRotSumInplace(CtxtTensor &a, CtxtTensor &b);
+    // HEMMer::getRank / getMaxRank (HEMMer.hpp:56-57): this process's GPU among the GPUs of the job
+    int getRank() const { return rank_; }
+    int getMaxRank() const { return max_rank_; }
+    void setRank(int rank, int max_rank) { rank_ = rank; max_rank_ = max_rank; }
+    // HEMMer::save (HEMMer.cpp:225-230): secret key and switching keys to `keys_path` (hb_keys_save)
+    void save(const std::string &keys_path) const;
+    hb_ctx *context() const { return ctx_; }
     // matmul family -- HEMMer.cpp:833-880, 1102-1124
     CtxtTensor singleCCMatMul(const CtxtTensor &a, const CtxtTensor &b, int target_level = 4);
     CtxtTensor singleMatMul(const CtxtTensor &a, const PtxtTensor &b, int target_level = 4);
@@ -146,6 +159,7 @@ class HEMMer {
     int max_level_ = 0;
     int schedule_ = 0;
     i64 low_dim_ = 2;
+    int rank_ = 0, max_rank_ = 1;
     MaskCache masks_;
 };
 

@@ -70,14 +70,21 @@ class Ciphertext {
 class Plaintext {
   public:
     Plaintext() = default;
-    explicit Plaintext(hb_pt *p) : p_(p, [](hb_pt *x) { hb_pt_free(x); }) {}
+    explicit Plaintext(hb_pt *p) : p_(std::make_shared<Holder>(p, true)) {}
     // a handle owned by someone else (kept alive by the caller for the duration of the call)
-    static Plaintext borrowed(const hb_pt *p) { Plaintext r; r.p_ = std::shared_ptr<hb_pt>(const_cast<hb_pt *>(p), [](hb_pt *) {}); return r; }
-    hb_pt *raw() const { return p_.get(); }
+    static Plaintext borrowed(const hb_pt *p) { Plaintext r; r.p_ = std::make_shared<Holder>(const_cast<hb_pt *>(p), false); return r; }
+    hb_pt *raw() const { return p_ ? p_->p : nullptr; }
+    // hands the handle to the caller (C entry points); every copy of this Plaintext stops owning it
+    hb_pt *release() { if (!p_) return nullptr; p_->owned = false; return p_->p; }
     bool empty() const { return !p_; }
-    int getLevel() const { int l = -1; hb_pt_meta(p_.get(), &l, nullptr); return l; }
+    int getLevel() const { int l = -1; hb_pt_meta(raw(), &l, nullptr); return l; }
   private:
-    std::shared_ptr<hb_pt> p_;
+    struct Holder {
+        hb_pt *p; bool owned;
+        Holder(hb_pt *pp, bool o) : p(pp), owned(o) {}
+        ~Holder() { if (owned && p) hb_pt_free(p); }
+    };
+    std::shared_ptr<Holder> p_;
 };
 
 // The step-independent half of a rotation of one ciphertext (lifted key-switch digits), shared by all its rotations.

@@ -6,7 +6,7 @@
 namespace HELLM {
 
 namespace {
-enum HemmerMask { kColEven = 1, kRowEven = 2, kLeftHalf = 3, kLeftHalfScaled = 4 };
+enum HemmerMask { kColEven = 1, kRowEven = 2, kLeftHalf = 3, kLeftHalfScaled = 4, kFirstCol = 5, kLastCol = 6 };
 }
 
 HEMMer::HEMMer(hb_ctx *ctx) : ctx_(ctx), eval_(ctx) {
@@ -96,6 +96,9 @@ void HEMMer::decrypt2(const CtxtTensor &t, double *out) const {
         }
 }
 void HEMMer::addInplace(CtxtTensor &a, const CtxtTensor &b) const { a.get() = eval_.add(a.get(), b.get()); }
+void HEMMer::hadamardMultInplace(CtxtTensor &a, const CtxtTensor &b) const { a.get() = eval_.mult(a.get(), b.get()); }
+void HEMMer::hadamardMultInplace(CtxtTensor &a, const PtxtTensor &b) const { a.get() = eval_.mult(a.get(), b.get()); }
+void HEMMer::save(const std::string &keys_path) const { check(ctx_, hb_keys_save(ctx_, keys_path.c_str())); }
 
 // ---- schedules ----
 #define HB_ENV sched::Env env{eval_, slots_, masks_, schedule_}
@@ -134,7 +137,7 @@ static const Plaintext &hemmer_mask(HEMMer &h, int which, int level) {
     Message m((size_t)h.slots());
     for (i64 r = 0; r < d; ++r)
         for (i64 c = 0; c < 2 * d; ++c) {
-            bool on = which == kColEven ? ((c % d) % 2 == 0) : which == kRowEven ? (r % 2 == 0) : (c < d);
+            bool on = which == kColEven ? ((c % d) % 2 == 0) : which == kRowEven ? (r % 2 == 0) : which == kFirstCol ? (c % d == 0) : which == kLastCol ? (c % d == d - 1) : (c < d);
             if (on) m.re[(size_t)(r * 2 * d + c)] = which == kLeftHalfScaled ? 0.5 : 1.0;
         }
     return h.masks().put(k, h.eval().encode(m, level));
@@ -157,6 +160,20 @@ void HEMMer::transposeComplexPackingInplace(CtxtTensor &t, int target_level) {
     transposeInplace(t, 0);
 }
 void HEMMer::complexPackingRowInplace(CtxtTensor &t) { t.get() = fold_odd(*this, t.get(), kRowEven, t.getBlockWidth(), true, true); }
+// HEMMer::oneMatRotSumInplace -- HEMMer.cpp:882-919 with ModelArgs::HEAD_DIM equal to the tile side
+void HEMMer::oneMatRotSumInplace(CtxtTensor &a, CtxtTensor &b) {
+    const i64 d = tile_;
+    for (i64 rot = 1; rot < d / 2; rot <<= 1) {
+        a.get() = eval_.add(a.get(), eval_.leftRotate(a.get(), rot));
+        b.get() = eval_.add(b.get(), eval_.rightRotate(b.get(), rot));
+    }
+    a.get() = eval_.mult(a.get(), hemmer_mask(*this, kFirstCol, a.getLevel()));
+    b.get() = eval_.mult(b.get(), hemmer_mask(*this, kLastCol, b.getLevel()));
+    for (i64 rot = 1; rot < d; rot <<= 1) {
+        a.get() = eval_.add(a.get(), eval_.rightRotate(a.get(), rot));
+        b.get() = eval_.add(b.get(), eval_.leftRotate(b.get(), rot));
+    }
+}
 // HEMMer::splitInTwo -- HEMMer.cpp:819-831
 void HEMMer::splitInTwo(const CtxtTensor &t, CtxtTensor &t1, CtxtTensor &t2) {
     const i64 width = t.getWidth();

@@ -5,7 +5,11 @@
 
 using namespace HELLM;
 
-struct hb_hemmer { hb_ctx *ctx; HEMMer h; explicit hb_hemmer(hb_ctx *c) : ctx(c), h(c) {} };
+struct hb_hemmer {
+    hb_ctx *ctx; HEMMer h; bool owns_ctx = false;
+    explicit hb_hemmer(hb_ctx *c) : ctx(c), h(c) {}
+    ~hb_hemmer() { h.masks().clear(); if (owns_ctx) hb_ctx_destroy(ctx); }
+};
 
 namespace {
 // error text for failures raised above the C ABI (the CUDA library keeps its own last-error string)
@@ -30,6 +34,80 @@ int hb_hemmer_create(hb_ctx *c, hb_hemmer **out) { return guard([&] { *out = new
 void hb_hemmer_destroy(hb_hemmer *h) { delete h; }
 // 0 = the reference's rotation sequence (default), 1 = direct, hoisted rotations, 2 = 1 with one division per wrapped copy
 int hb_hemmer_set_schedule(hb_hemmer *h, int mode) { if (mode < 0 || mode > 2) return HB_E_ARG; h->h.setSchedule(mode); return HB_OK; }
+
+// HEMMer::genHEMMer (HEMMer.cpp:93-112): context + keys + HEMMer in one call; the object owns the context
+int hb_hemmer_gen(int device, const hb_params *prm, hb_hemmer **out) {
+    return guard([&] {
+        if (!prm || !out) throw std::invalid_argument("[genHEMMer] null argument");
+        hb_ctx *c = nullptr;
+        if (hb_ctx_create(prm, device, &c) != HB_OK) throw std::runtime_error("[genHEMMer] cannot create a context on this device");
+        int rc = hb_keygen(c);
+        if (rc != HB_OK) { std::string m = hb_last_error(c); hb_ctx_destroy(c); throw std::runtime_error(m); }
+        hb_hemmer *h = new hb_hemmer(c);
+        h->owns_ctx = true;
+        *out = h;
+    });
+}
+hb_ctx *hb_hemmer_context(const hb_hemmer *h) { return h ? h->ctx : nullptr; }
+int hb_hemmer_set_rank(hb_hemmer *h, int rank, int max_rank) { if (!h || rank < 0 || max_rank < 1 || rank >= max_rank) return HB_E_ARG; h->h.setRank(rank, max_rank); return HB_OK; }
+int hb_hemmer_get_rank(const hb_hemmer *h) { return h->h.getRank(); }
+int hb_hemmer_get_max_rank(const hb_hemmer *h) { return h->h.getMaxRank(); }
+int hb_hemmer_save(hb_hemmer *h, const char *keys_path) { return guard([&] { h->h.save(keys_path); }); }
+
+// encode / encrypt / decrypt of row-major matrices (HEMMer.hpp:65-100)
+int hb_hemmer_encode(hb_hemmer *h, const double *data, int rows, int cols, int level, hb_pt **out) {
+    return guard([&] { *out = h->h.encode(data, rows, cols, level).get().release(); });
+}
+int hb_hemmer_encode2(hb_hemmer *h, const double *d1, const double *d2, int rows, int cols, int level, hb_pt **out) {
+    return guard([&] { *out = h->h.encode2(d1, d2, rows, cols, level).get().release(); });
+}
+int hb_hemmer_encode_diagonal_to_row4(hb_hemmer *h, const double *w1, const double *w2, const double *w3, const double *w4, int rows, int cols, int level, hb_pt **out) {
+    return guard([&] { *out = h->h.encodeDiagonalToRow4(w1, w2, w3, w4, rows, cols, level).get().release(); });
+}
+int hb_hemmer_encrypt(hb_hemmer *h, const double *data, int rows, int cols, uint64_t nonce, hb_ct **out) {
+    return guard([&] { *out = h->h.encrypt(data, rows, cols, nonce).get().release(); });
+}
+int hb_hemmer_encrypt2(hb_hemmer *h, const double *d1, const double *d2, int rows, int cols, uint64_t nonce, hb_ct **out) {
+    return guard([&] { *out = h->h.encrypt2(d1, d2, rows, cols, nonce).get().release(); });
+}
+int hb_hemmer_decrypt(hb_hemmer *h, const hb_ct *a, int rows, int cols, int width, double *out) {
+    return guard([&] { Borrow b(h->ctx, a); h->h.decrypt(view(b, rows, cols, width), out); });
+}
+int hb_hemmer_decrypt2(hb_hemmer *h, const hb_ct *a, int rows, int cols, int width, double *out) {
+    return guard([&] { Borrow b(h->ctx, a); h->h.decrypt2(view(b, rows, cols, width), out); });
+}
+int hb_hemmer_add(hb_hemmer *h, const hb_ct *a, const hb_ct *b, hb_ct **out) {
+    return guard([&] {
+        Borrow ba(h->ctx, a), bb(h->ctx, b);
+        CtxtTensor ta(TileTensorShape(), Ciphertext(ba.c));
+        h->h.addInplace(ta, CtxtTensor(TileTensorShape(), Ciphertext(bb.c)));
+        *out = ta.get().release();
+    });
+}
+int hb_hemmer_hadamard_mult(hb_hemmer *h, const hb_ct *a, const hb_ct *b, hb_ct **out) {
+    return guard([&] {
+        Borrow ba(h->ctx, a), bb(h->ctx, b);
+        CtxtTensor ta(TileTensorShape(), Ciphertext(ba.c));
+        h->h.hadamardMultInplace(ta, CtxtTensor(TileTensorShape(), Ciphertext(bb.c)));
+        *out = ta.get().release();
+    });
+}
+int hb_hemmer_hadamard_mult_pt(hb_hemmer *h, const hb_ct *a, const hb_pt *p, hb_ct **out) {
+    return guard([&] {
+        Borrow ba(h->ctx, a);
+        CtxtTensor ta(TileTensorShape(), Ciphertext(ba.c));
+        h->h.hadamardMultInplace(ta, PtxtTensor(TileTensorShape(), Plaintext::borrowed(p)));
+        *out = ta.get().release();
+    });
+}
+int hb_hemmer_one_mat_rot_sum(hb_hemmer *h, const hb_ct *a, const hb_ct *b, hb_ct **out_a, hb_ct **out_b) {
+    return guard([&] {
+        Borrow ba(h->ctx, a), bb(h->ctx, b);
+        CtxtTensor ta(TileTensorShape(), Ciphertext(ba.c)), tb(TileTensorShape(), Ciphertext(bb.c));
+        h->h.oneMatRotSumInplace(ta, tb);
+        *out_a = ta.get().release(); *out_b = tb.get().release();
+    });
+}
 
 #define SHAPE_ARGS int rows, int cols, int width
 #define IN_TENSOR(name, p) Borrow name##_b(h->ctx, p); CtxtTensor name(TileTensorShape(rows, cols, width), Ciphertext(name##_b.c))

@@ -7,6 +7,7 @@
 #include "kernels.cuh"
 #include "ntt.cuh"
 
+#include <cstdio>
 #include <dlfcn.h>
 #include <map>
 #include <thread>
@@ -109,7 +110,7 @@ struct hb_ctx {
     Pool pool;
     std::string err;
     PrimeConst *pc = nullptr;
-    u64 *tw = nullptr; // psi | psi_sh | ipsi | ipsi_sh, each [nprimes][N]
+    u64 *tw = nullptr; // twiddle tables: psi | psi_sh | ipsi | ipsi_sh, each [nprimes][N], or the 2^16 layout of ntt16.cuh
     NttTables tb{};
     u64 *sk = nullptr; // [nprimes][N] NTT form
     bool have_sk = false;
@@ -348,6 +349,8 @@ Evk make_key(hb_ctx *c, u64 kid, u32 g) {
         ntt_inplace(c, e.p, np, am, false);
         LAUNCH(c), k_keygen<<<c->egrid(np), 256, 0, c->st>>>(b, a, e.p, c->sk, c->pc, N, c->logn, g, h.digit_lo(dg), h.digit_hi(dg, h.L + 1), pmod);
     }
+    // the inner-product kernels take keys with every residue cut in two pieces (split_word)
+    LAUNCH(c), k_split_key<<<c->egrid(nd * 2 * np), 256, 0, c->st>>>(k.d, am, c->pc, N, 0);
     CK(cudaGetLastError());
     return k;
 }
@@ -674,7 +677,9 @@ int hb_ctx_create(const hb_params *prm, int device, hb_ctx **out) {
         CK(cudaStreamCreateWithFlags(&c->st, cudaStreamNonBlocking));
         const int np = c->nprimes, N = c->N;
         std::vector<PrimeConst> pcs(np);
-        std::vector<u64> tw((size_t)4 * np * N);
+        const bool big = c->logn == 16;   // 2^16 coefficients: tables in the order the two-pass kernels read them
+        std::vector<u64> tw(big ? 0 : (size_t)4 * np * N);
+        std::vector<ulonglong2> t16(big ? (size_t)2 * np * Ntt16Layout::kEntries : 0);
         for (int i = 0; i < np; ++i) {
             const u64 q = c->h->q[i];
             PrimeConst &p = pcs[i];
@@ -684,8 +689,8 @@ int hb_ctx_create(const hb_params *prm, int device, hb_ctx **out) {
             p.mu_lo = (u64)(((two64 % q) << 64) / q);
             p.n_inv = hbhost::invmod((u64)N, q); p.n_inv_sh = hbhost::shoup(p.n_inv, q);
             p.iu = hbhost::powmod(c->h->psi_root[i], (u64)N / 2, q); p.iu_sh = hbhost::shoup(p.iu, q);
-            // the 2^16 transform takes quotients from the FP64 pipe for primes below 2^44 (mul_fp_lazy)
-            p.small = (c->logn == 16 && q < ((u64)1 << 44)) ? 1 : 0;
+            // the 2^16 transform carries the residues of primes below 2^44 as integer-valued doubles (ntt16.cuh)
+            p.small = (big && q < ((u64)1 << 44)) ? 1 : 0;
             p.q_inv_f = 1.0 / (double)q;
             p.n_inv_f = (double)p.n_inv / (double)q;
             p.fp = q < ((u64)1 << 44) ? 1 : 0;
@@ -696,22 +701,34 @@ int hb_ctx_create(const hb_params *prm, int device, hb_ctx **out) {
             if (p.fp && p.lazy_terms < 160) throw std::invalid_argument("prime too large for the lazy FP64-assisted sums");
             std::vector<u64> f, fs, iv, ivs;
             c->h->twiddles(i, f, fs, iv, ivs);
-            if (p.small) { // companion tables hold w/q as doubles instead of Shoup quotients
+            if (p.small) { // companion words hold w/q as doubles instead of Shoup quotients
                 for (int k = 0; k < N; ++k) {
                     double a = (double)f[k] / (double)q, b = (double)iv[k] / (double)q;
                     std::memcpy(&fs[k], &a, 8); std::memcpy(&ivs[k], &b, 8);
                 }
             }
-            std::memcpy(&tw[((size_t)0 * np + i) * N], f.data(), (size_t)N * 8);
-            std::memcpy(&tw[((size_t)1 * np + i) * N], fs.data(), (size_t)N * 8);
-            std::memcpy(&tw[((size_t)2 * np + i) * N], iv.data(), (size_t)N * 8);
-            std::memcpy(&tw[((size_t)3 * np + i) * N], ivs.data(), (size_t)N * 8);
+            if (big) {
+                ntt16_fill_table(&t16[(size_t)i * Ntt16Layout::kEntries], [&](unsigned k) { return make_ulonglong2(f[k], fs[k]); });
+                ntt16_fill_table(&t16[((size_t)np + i) * Ntt16Layout::kEntries], [&](unsigned k) { return make_ulonglong2(iv[k], ivs[k]); });
+            } else {
+                std::memcpy(&tw[((size_t)0 * np + i) * N], f.data(), (size_t)N * 8);
+                std::memcpy(&tw[((size_t)1 * np + i) * N], fs.data(), (size_t)N * 8);
+                std::memcpy(&tw[((size_t)2 * np + i) * N], iv.data(), (size_t)N * 8);
+                std::memcpy(&tw[((size_t)3 * np + i) * N], ivs.data(), (size_t)N * 8);
+            }
         }
         CK(cudaMalloc(&c->pc, sizeof(PrimeConst) * np));
         CK(cudaMemcpy(c->pc, pcs.data(), sizeof(PrimeConst) * np, cudaMemcpyHostToDevice));
-        CK(cudaMalloc(&c->tw, tw.size() * 8));
-        CK(cudaMemcpy(c->tw, tw.data(), tw.size() * 8, cudaMemcpyHostToDevice));
-        c->tb.psi = c->tw; c->tb.psi_sh = c->tw + (size_t)np * N; c->tb.ipsi = c->tw + (size_t)2 * np * N; c->tb.ipsi_sh = c->tw + (size_t)3 * np * N;
+        if (big) {
+            CK(cudaMalloc(&c->tw, t16.size() * sizeof(ulonglong2)));
+            CK(cudaMemcpy(c->tw, t16.data(), t16.size() * sizeof(ulonglong2), cudaMemcpyHostToDevice));
+            const ulonglong2 *t = reinterpret_cast<const ulonglong2 *>(c->tw);
+            c->tb.t16 = Ntt16Tables{t, t + (size_t)np * Ntt16Layout::kEntries};
+        } else {
+            CK(cudaMalloc(&c->tw, tw.size() * 8));
+            CK(cudaMemcpy(c->tw, tw.data(), tw.size() * 8, cudaMemcpyHostToDevice));
+            c->tb.psi = c->tw; c->tb.psi_sh = c->tw + (size_t)np * N; c->tb.ipsi = c->tw + (size_t)2 * np * N; c->tb.ipsi_sh = c->tw + (size_t)3 * np * N;
+        }
         CK(cudaMalloc(&c->sk, (size_t)np * N * 8));
     } catch (const CudaFail &) { hb_ctx_destroy(c); return HB_E_CUDA; }
     catch (const ArgFail &e) { int code = e.code; hb_ctx_destroy(c); return code; }
@@ -789,7 +806,14 @@ int hb_evk_export(hb_ctx *c, uint64_t g, uint64_t *host, int *digits) {
         const Evk *k = g == 0 ? &c->mult_key : &galois_key(c, g);
         if (!k->d) fail(HB_E_NOKEY, "key not generated");
         if (digits) *digits = k->nd;
-        if (host) { CK(cudaStreamSynchronize(c->st)); CK(cudaMemcpy(host, k->d, (size_t)k->nd * 2 * c->nprimes * c->N * 8, cudaMemcpyDeviceToHost)); }
+        if (host) { // the stored key is in split form: export the plain residues
+            const size_t limbs = (size_t)k->nd * 2 * c->nprimes;
+            Tmp plain(c, limbs);
+            CK(cudaMemcpyAsync(plain.p, k->d, limbs * c->N * 8, cudaMemcpyDeviceToDevice, c->st));
+            LAUNCH(c), k_split_key<<<c->egrid((int)limbs), 256, 0, c->st>>>(plain.p, c->allmap(), c->pc, c->N, 1);
+            CK(cudaMemcpyAsync(host, plain.p, limbs * c->N * 8, cudaMemcpyDeviceToHost, c->st));
+            CK(cudaStreamSynchronize(c->st));
+        }
     });
 }
 
@@ -1465,6 +1489,158 @@ int hb_nccl_comm_destroy(void *comm) {
     return nc.CommDestroy((ncclComm_t)comm) == ncclSuccess ? HB_OK : HB_E_NCCL;
 }
 
+
+// ---- files ---------------------------------------------------------------------------------------------------
+// One self-describing container for ciphertexts, plaintexts and keys (HEaaN's own binary format is not published, so
+// files of the reference cannot be read; these take their place for the same calls: Ciphertext::save / load,
+// HEMMer::save).  Layout, little-endian:
+//     FileHeader (96 bytes) | payload: plain residues, uint64, in the device layout of the object | FNV-1a-64 of the payload
+// A file is only accepted by a context with the same ring degree and the same primes (prime_hash).
+namespace {
+enum FileKind : uint32_t { kFileCt = 1, kFilePt = 2, kFileEvk = 3, kFileSecret = 4 };
+struct FileHeader {
+    char magic[8];          // "HB200F1\0"
+    uint32_t kind, log_n, level, n_poly, batch, scale_pow, ext, digits, nprimes, reserved;
+    uint64_t galois;        // switching keys: Galois element (0: multiplication key)
+    uint64_t prime_hash;    // FNV-1a over the context's primes
+    uint64_t payload_words;
+    uint64_t reserved2[3];
+};
+static_assert(sizeof(FileHeader) == 96, "file header layout");
+uint64_t fnv1a(const void *data, size_t bytes, uint64_t h = 1469598103934665603ull) {
+    const unsigned char *p = (const unsigned char *)data;
+    for (size_t i = 0; i < bytes; ++i) { h ^= p[i]; h *= 1099511628211ull; }
+    return h;
+}
+uint64_t prime_hash(const hb_ctx *c) { return fnv1a(c->h->q.data(), c->h->q.size() * 8); }
+struct File {
+    FILE *f;
+    File(const char *path, const char *mode) : f(path ? std::fopen(path, mode) : nullptr) { if (!f) fail(HB_E_ARG, std::string("cannot open ") + (path ? path : "(null)")); }
+    ~File() { if (f) std::fclose(f); }
+};
+void write_file(hb_ctx *c, const char *path, FileHeader h, const u64 *dev, size_t words) {
+    no_capture(c, "save");
+    std::vector<u64> host(words);
+    CK(cudaMemcpyAsync(host.data(), dev, words * 8, cudaMemcpyDeviceToHost, c->st));
+    CK(cudaStreamSynchronize(c->st));
+    std::memcpy(h.magic, "HB200F1", 8);
+    h.log_n = (uint32_t)c->logn; h.nprimes = (uint32_t)c->nprimes; h.prime_hash = prime_hash(c); h.payload_words = words;
+    const uint64_t sum = fnv1a(host.data(), words * 8);
+    File out(path, "wb");
+    if (std::fwrite(&h, sizeof(h), 1, out.f) != 1 || std::fwrite(host.data(), 8, words, out.f) != words || std::fwrite(&sum, 8, 1, out.f) != 1)
+        fail(HB_E_ARG, std::string("short write to ") + path);
+}
+// reads header + payload; checks magic, kind, context and checksum
+std::vector<u64> read_file(hb_ctx *c, const char *path, uint32_t kind, FileHeader &h) {
+    File in(path, "rb");
+    if (std::fread(&h, sizeof(h), 1, in.f) != 1 || std::memcmp(h.magic, "HB200F1", 8) != 0) fail(HB_E_ARG, std::string(path) + ": not a file of this library");
+    if (h.kind != kind) fail(HB_E_ARG, std::string(path) + ": holds another kind of object");
+    if (h.log_n != (uint32_t)c->logn || h.nprimes != (uint32_t)c->nprimes || h.prime_hash != prime_hash(c)) fail(HB_E_ARG, std::string(path) + ": written under other parameters");
+    if (h.payload_words > ((uint64_t)1 << 34)) fail(HB_E_LIMIT, std::string(path) + ": implausible size");
+    std::vector<u64> host((size_t)h.payload_words);
+    uint64_t sum = 0;
+    if (std::fread(host.data(), 8, host.size(), in.f) != host.size() || std::fread(&sum, 8, 1, in.f) != 1) fail(HB_E_ARG, std::string(path) + ": truncated");
+    if (sum != fnv1a(host.data(), host.size() * 8)) fail(HB_E_ARG, std::string(path) + ": checksum mismatch");
+    return host;
+}
+void upload(hb_ctx *c, u64 *dev, const std::vector<u64> &host) {
+    CK(cudaMemcpyAsync(dev, host.data(), host.size() * 8, cudaMemcpyHostToDevice, c->st));
+    CK(cudaStreamSynchronize(c->st));
+}
+// switching key -> file: the stored split form is joined into plain residues first
+void save_evk(hb_ctx *c, const Evk &k, uint64_t g, const std::string &path) {
+    const size_t limbs = (size_t)k.nd * 2 * c->nprimes;
+    Tmp plain(c, limbs);
+    CK(cudaMemcpyAsync(plain.p, k.d, limbs * c->N * 8, cudaMemcpyDeviceToDevice, c->st));
+    LAUNCH(c), k_split_key<<<c->egrid((int)limbs), 256, 0, c->st>>>(plain.p, c->allmap(), c->pc, c->N, 1);
+    FileHeader h{}; h.kind = kFileEvk; h.level = (uint32_t)c->L; h.digits = (uint32_t)k.nd; h.galois = g; h.n_poly = 2;
+    write_file(c, path.c_str(), h, plain.p, limbs * c->N);
+}
+} // namespace
+
+// Ciphertext::save / load (Ciphertext.hpp:89-98), used by the reference to carry activations from the forward to the
+// backward pass (HEMMer.cpp:1403-1405, TransformerBlock.cpp:11059-11079)
+int hb_ct_save(hb_ctx *c, const hb_ct *x, const char *path) {
+    return guard(c, [&] {
+        own(c, x);
+        FileHeader h{}; h.kind = kFileCt; h.level = (uint32_t)x->level; h.n_poly = (uint32_t)x->np; h.batch = (uint32_t)x->batch; h.scale_pow = (uint32_t)x->spow;
+        write_file(c, path, h, x->d, x->limbs() * c->N);
+    });
+}
+int hb_ct_load(hb_ctx *c, const char *path, hb_ct **out) {
+    return guard(c, [&] {
+        no_capture(c, "load");
+        FileHeader h;
+        const std::vector<u64> host = read_file(c, path, kFileCt, h);
+        hb_ct *r = new_ct(c, (int)h.level, (int)h.n_poly, (int)h.batch, (int)h.scale_pow);
+        if (r->limbs() * c->N != host.size()) { hb_ct_free(r); fail(HB_E_ARG, std::string(path) + ": size does not match its header"); }
+        try { upload(c, r->d, host); } catch (...) { hb_ct_free(r); throw; }
+        *out = r;
+    });
+}
+// Plaintext::save / load (Plaintext.hpp), e.g. the encoded weights the reference writes once and reloads (HEMMer::encodeWeight)
+int hb_pt_save(hb_ctx *c, const hb_pt *x, const char *path) {
+    return guard(c, [&] {
+        own(c, x);
+        FileHeader h{}; h.kind = kFilePt; h.level = (uint32_t)x->level; h.scale_pow = (uint32_t)x->spow; h.ext = (uint32_t)x->ext; h.n_poly = 1; h.batch = 1;
+        write_file(c, path, h, x->d, (size_t)(x->level + 1 + (x->ext ? c->K : 0)) * c->N);
+    });
+}
+int hb_pt_load(hb_ctx *c, const char *path, hb_pt **out) {
+    return guard(c, [&] {
+        no_capture(c, "load");
+        FileHeader h;
+        const std::vector<u64> host = read_file(c, path, kFilePt, h);
+        const size_t limbs = (size_t)h.level + 1 + (h.ext ? c->K : 0);
+        if ((int)h.level > c->L || limbs * c->N != host.size()) fail(HB_E_ARG, std::string(path) + ": size does not match its header");
+        hb_pt *r = new hb_pt{c, (int)h.level, (int)h.scale_pow, nullptr};
+        r->ext = h.ext ? 1 : 0;
+        try { r->d = c->alloc_limbs(limbs); upload(c, r->d, host); } catch (...) { if (r->d) c->pool.put(r->d); delete r; throw; }
+        *out = r;
+    });
+}
+// HEMMer::save (HEMMer.cpp:225-230): SecretKey.bin plus the key pack -- here MultKey.bin and one GaloisKey_<g>.bin per
+// generated rotation / conjugation key -- under an existing directory
+int hb_keys_save(hb_ctx *c, const char *dir) {
+    return guard(c, [&] {
+        if (!dir) fail(HB_E_ARG, "keys_save: null path");
+        if (!c->have_sk) fail(HB_E_NOKEY, "secret key not generated");
+        const std::string d(dir);
+        FileHeader h{}; h.kind = kFileSecret; h.level = (uint32_t)c->L; h.n_poly = 1;
+        write_file(c, (d + "/SecretKey.bin").c_str(), h, c->sk, (size_t)c->nprimes * c->N);
+        if (c->mult_key.d) save_evk(c, c->mult_key, 0, d + "/MultKey.bin");
+        for (const auto &kv : c->gal_keys) save_evk(c, kv.second, kv.first, d + "/GaloisKey_" + std::to_string(kv.first) + ".bin");
+    });
+}
+// the reverse: secret key, multiplication key and the Galois keys named by `galois` (count entries) from `dir`
+int hb_keys_load(hb_ctx *c, const char *dir, const uint64_t *galois, int count) {
+    return guard(c, [&] {
+        no_capture(c, "load");
+        if (!dir || count < 0 || (count && !galois)) fail(HB_E_ARG, "keys_load: bad arguments");
+        const std::string d(dir);
+        FileHeader h;
+        std::vector<u64> host = read_file(c, (d + "/SecretKey.bin").c_str(), kFileSecret, h);
+        if (host.size() != (size_t)c->nprimes * c->N) fail(HB_E_ARG, "SecretKey.bin: size does not match the context");
+        upload(c, c->sk, host);
+        c->have_sk = true;
+        auto load_evk = [&](const std::string &path, uint64_t g) {
+            std::vector<u64> w = read_file(c, path.c_str(), kFileEvk, h);
+            const int nd = c->h->digit_of(c->h->L) + 1;
+            const size_t limbs = (size_t)nd * 2 * c->nprimes;
+            if ((int)h.digits != nd || h.galois != g || w.size() != limbs * c->N) fail(HB_E_ARG, path + ": does not fit this context");
+            Evk k; k.nd = nd; k.d = c->alloc_limbs(limbs);
+            try {
+                upload(c, k.d, w);
+                LAUNCH(c), k_split_key<<<c->egrid((int)limbs), 256, 0, c->st>>>(k.d, c->allmap(), c->pc, c->N, 0);
+                CK(cudaGetLastError());
+            } catch (...) { c->pool.put(k.d); throw; }
+            return k;
+        };
+        auto replace = [&](Evk &slot, Evk k) { if (slot.d) c->pool.put(slot.d); slot = k; };
+        replace(c->mult_key, load_evk(d + "/MultKey.bin", 0));
+        for (int i = 0; i < count; ++i) replace(c->gal_keys[galois[i]], load_evk(d + "/GaloisKey_" + std::to_string(galois[i]) + ".bin", galois[i]));
+    });
+}
 
 int hb_set_host_threads(hb_ctx *c, int n) { if (!c || n < 0) return HB_E_ARG; c->host_threads = n; return HB_OK; }
 

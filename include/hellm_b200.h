@@ -41,6 +41,40 @@ const char *hb_hemmer_last_error(void);
  * All give the same slots and different ciphertext bits; no counterpart in the reference. */
 int hb_hemmer_set_schedule(hb_hemmer *h, int mode);
 
+/* HEMMer::genHEMMer (HEMMer.hpp:38-44; HEMMer.cpp:93-112): creates the context on `device`, generates the keys and
+ * builds the HEMMer in one call; hb_hemmer_destroy then releases the context too.  hb_hemmer_context gives the
+ * primitive-layer handle of either kind of HEMMer. */
+int hb_hemmer_gen(int device, const hb_params *prm, hb_hemmer **out);
+hb_ctx *hb_hemmer_context(const hb_hemmer *h);
+/* HEMMer::getRank / getMaxRank (HEMMer.hpp:56-57): this process's GPU among the GPUs of the job (set by the launcher) */
+int hb_hemmer_set_rank(hb_hemmer *h, int rank, int max_rank);
+int hb_hemmer_get_rank(const hb_hemmer *h);
+int hb_hemmer_get_max_rank(const hb_hemmer *h);
+/* HEMMer::save (HEMMer.hpp:61; HEMMer.cpp:225-230): secret key and switching keys to files under keys_path */
+int hb_hemmer_save(hb_hemmer *h, const char *keys_path);
+
+/* HEMMer::encode / encode2 / encodeDiagonalToRow4 (HEMMer.hpp:65-86; HEMMer.cpp:232-275, 353-416): row-major rows x cols
+ * matrices of doubles instead of torch::Tensor; level 0 means the encryption level, as in the reference.  encode2 lays
+ * [d1 | d2] side by side (block width 2 * cols); encodeDiagonalToRow4 packs 1/2 (w1 - i w3) | 1/2 (w2 - i w4) with
+ * column j rolled up by j rows. */
+int hb_hemmer_encode(hb_hemmer *h, const double *data, int rows, int cols, int level, hb_pt **out);
+int hb_hemmer_encode2(hb_hemmer *h, const double *d1, const double *d2, int rows, int cols, int level, hb_pt **out);
+int hb_hemmer_encode_diagonal_to_row4(hb_hemmer *h, const double *w1, const double *w2, const double *w3, const double *w4, int rows, int cols,
+                                      int level, hb_pt **out);
+/* HEMMer::encrypt / encrypt2 (HEMMer.hpp:93-94; HEMMer.cpp:579-594); `nonce` selects the random streams (the reference
+ * draws unseeded randomness) */
+int hb_hemmer_encrypt(hb_hemmer *h, const double *data, int rows, int cols, uint64_t nonce, hb_ct **out);
+int hb_hemmer_encrypt2(hb_hemmer *h, const double *d1, const double *d2, int rows, int cols, uint64_t nonce, hb_ct **out);
+/* HEMMer::decrypt / decrypt2 (HEMMer.hpp:98-100; HEMMer.cpp:603-638): rows * cols doubles, or [2][rows][cols] */
+int hb_hemmer_decrypt(hb_hemmer *h, const hb_ct *a, int rows, int cols, int width, double *out);
+int hb_hemmer_decrypt2(hb_hemmer *h, const hb_ct *a, int rows, int cols, int width, double *out);
+/* HEMMer::addInplace / hadamardMultInplace (HEMMer.hpp:102-115; HEMMer.cpp:683-713), returning a new handle */
+int hb_hemmer_add(hb_hemmer *h, const hb_ct *a, const hb_ct *b, hb_ct **out);
+int hb_hemmer_hadamard_mult(hb_hemmer *h, const hb_ct *a, const hb_ct *b, hb_ct **out);
+int hb_hemmer_hadamard_mult_pt(hb_hemmer *h, const hb_ct *a, const hb_pt *p, hb_ct **out);
+/* HEMMer::oneMatRotSumInplace (HEMMer.hpp:168; HEMMer.cpp:882-919) on two-tile ciphertexts */
+int hb_hemmer_one_mat_rot_sum(hb_hemmer *h, const hb_ct *a, const hb_ct *b, hb_ct **out_a, hb_ct **out_b);
+
 /* HEMMer::transposeInplace (HEMMer.hpp:129; HEMMer.cpp:1166-1172; MatrixUtils.cpp:671-739) */
 int hb_hemmer_transpose(hb_hemmer *h, const hb_ct *a, int rows, int cols, int width, int target_level, hb_ct **out);
 /* MatrixTransformer::diagonalToColumn / diagonalToRow (MatrixUtils.cpp:776-848, 924-996) */

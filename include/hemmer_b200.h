@@ -119,6 +119,20 @@ int hb_ct_import(hb_ctx *ctx, hb_ct *ct, const uint64_t *host);
 int hb_ct_export(hb_ctx *ctx, const hb_ct *ct, uint64_t *host);
 int hb_pt_export(hb_ctx *ctx, const hb_pt *pt, uint64_t *host);
 void *hb_ct_device_ptr(const hb_ct *ct);
+/* Files.  HEaaN's binary format is not published, so these calls write and read this library's own container:
+ * a 96-byte header (magic, kind, ring degree, level, polynomial count, batch, scale power, a hash of the primes),
+ * the plain residues in device layout, and a checksum.  A file is accepted only under the parameters it was
+ * written with.  hb_ct_save / hb_ct_load stand for Ciphertext::save / load (Ciphertext.hpp:89-98; the reference keeps
+ * forward-pass activations for the backward pass this way, HEMMer.cpp:1403-1405, TransformerBlock.cpp:11059-11079);
+ * hb_pt_save / hb_pt_load for Plaintext::save / load (encoded weights, HEMMer::encodeWeight); hb_keys_save for
+ * HEMMer::save (HEMMer.cpp:225-230): SecretKey.bin, MultKey.bin and one GaloisKey_<galois>.bin per generated key under
+ * an existing directory; hb_keys_load reads them back (the Galois keys named in `galois`). */
+int hb_ct_save(hb_ctx *ctx, const hb_ct *ct, const char *path);
+int hb_ct_load(hb_ctx *ctx, const char *path, hb_ct **out);
+int hb_pt_save(hb_ctx *ctx, const hb_pt *pt, const char *path);
+int hb_pt_load(hb_ctx *ctx, const char *path, hb_pt **out);
+int hb_keys_save(hb_ctx *ctx, const char *dir);
+int hb_keys_load(hb_ctx *ctx, const char *dir, const uint64_t *galois, int count);
 /* copies all of src's entries to positions index*src_batch .. of dst */
 int hb_batch_set(hb_ctx *ctx, hb_ct *dst, int index, const hb_ct *src);
 int hb_batch_get(hb_ctx *ctx, const hb_ct *src, int index, hb_ct **out);

@@ -793,6 +793,29 @@ struct Hemmer {
         Ct tmp2 = rotL(t2.ct, width);
         t2.ct = ev.add(t2.ct, tmp2);
     }
+    // oneMatRotSumInplace -- HEMMer.cpp:882-919, ModelArgs::HEAD_DIM = tile side: the row sums of the left halves of the
+    // tiles of a (first column) and of the right halves of the tiles of b (last column), spread over the whole row
+    void one_mat_rot_sum_inplace(CtT &a, CtT &b) {
+        const i64 d = tile;
+        for (i64 rot = 1; rot < d / 2; rot <<= 1) {
+            a.ct = ev.add(a.ct, rotL(a.ct, rot));
+            b.ct = ev.add(b.ct, rotR(b.ct, rot));
+        }
+        Mask first, last;
+        first.msg.assign((size_t)slots, cplx(0, 0));
+        last.msg.assign((size_t)slots, cplx(0, 0));
+        for (i64 r = 0; r < d; ++r)
+            for (i64 t = 0; t < 2; ++t) {
+                first.msg[(size_t)(r * 2 * d + t * d)] = 1;
+                last.msg[(size_t)(r * 2 * d + t * d + d - 1)] = 1;
+            }
+        a.ct = mult_msg(a.ct, first);
+        b.ct = mult_msg(b.ct, last);
+        for (i64 rot = 1; rot < d; rot <<= 1) {
+            a.ct = ev.add(a.ct, rotR(a.ct, rot));
+            b.ct = ev.add(b.ct, rotL(b.ct, rot));
+        }
+    }
     // repackCC -- HEMMer.cpp:964-969
     CtT repack_cc(const CtT &t) {
         ev.gen_galois_key(cx.galois_conj());

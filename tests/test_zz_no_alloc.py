@@ -32,6 +32,24 @@ def test_noalloc_rescale_matches_rescale_twice(request, size):
         got = _rescale_noalloc(g, src, level)
         assert g.ct_meta(got) == (level - 1, 2, 1, 1)
         assert np.array_equal(g.ct_export(got), want), f"call {call} at level {level}"
+        # the property the entry point exists for: with the output handle in place and the scratch address resolved,
+        # a further call obtains no device memory, neither from the context's pool nor from the driver
+        import torch
+        pool, used = C.c_uint64(), C.c_uint64()
+        g.dll.hb_mem_info(g.ctx, C.byref(pool), C.byref(used))
+        before = (pool.value, used.value, torch.cuda.mem_get_info()[0])
+        g._chk(g.dll.hb_rescale_noalloc(g.ctx, src.ptr, got.ptr))
+        g.sync()
+        g.dll.hb_mem_info(g.ctx, C.byref(pool), C.byref(used))
+        assert (pool.value, used.value, torch.cuda.mem_get_info()[0]) == before, "hb_rescale_noalloc obtained device memory"
+        assert np.array_equal(g.ct_export(got), want)
+
+
+def test_noalloc_rejects_a_foreign_output_handle(pkg, gpu_full, gpu_small):
+    src = gpu_small.ct_create(3, 2, 1, 2)
+    gpu_small.ct_zero(src)
+    out = gpu_full.ct_create(2, 2, 1, 1)
+    assert gpu_small.dll.hb_rescale_noalloc(gpu_small.ctx, src.ptr, out.ptr) == -1
 
 
 def test_noalloc_rejects_oversized_request(pkg, gpu_full):
