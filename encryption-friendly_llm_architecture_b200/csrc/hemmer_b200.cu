@@ -349,8 +349,6 @@ Evk make_key(hb_ctx *c, u64 kid, u32 g) {
         ntt_inplace(c, e.p, np, am, false);
         LAUNCH(c), k_keygen<<<c->egrid(np), 256, 0, c->st>>>(b, a, e.p, c->sk, c->pc, N, c->logn, g, h.digit_lo(dg), h.digit_hi(dg, h.L + 1), pmod);
     }
-    // the inner-product kernels take keys with every residue cut in two pieces (split_word)
-    LAUNCH(c), k_split_key<<<c->egrid(nd * 2 * np), 256, 0, c->st>>>(k.d, am, c->pc, N, 0);
     CK(cudaGetLastError());
     return k;
 }
@@ -806,14 +804,7 @@ int hb_evk_export(hb_ctx *c, uint64_t g, uint64_t *host, int *digits) {
         const Evk *k = g == 0 ? &c->mult_key : &galois_key(c, g);
         if (!k->d) fail(HB_E_NOKEY, "key not generated");
         if (digits) *digits = k->nd;
-        if (host) { // the stored key is in split form: export the plain residues
-            const size_t limbs = (size_t)k->nd * 2 * c->nprimes;
-            Tmp plain(c, limbs);
-            CK(cudaMemcpyAsync(plain.p, k->d, limbs * c->N * 8, cudaMemcpyDeviceToDevice, c->st));
-            LAUNCH(c), k_split_key<<<c->egrid((int)limbs), 256, 0, c->st>>>(plain.p, c->allmap(), c->pc, c->N, 1);
-            CK(cudaMemcpyAsync(host, plain.p, limbs * c->N * 8, cudaMemcpyDeviceToHost, c->st));
-            CK(cudaStreamSynchronize(c->st));
-        }
+        if (host) { CK(cudaStreamSynchronize(c->st)); CK(cudaMemcpy(host, k->d, (size_t)k->nd * 2 * c->nprimes * c->N * 8, cudaMemcpyDeviceToHost)); }
     });
 }
 
@@ -1547,14 +1538,10 @@ void upload(hb_ctx *c, u64 *dev, const std::vector<u64> &host) {
     CK(cudaMemcpyAsync(dev, host.data(), host.size() * 8, cudaMemcpyHostToDevice, c->st));
     CK(cudaStreamSynchronize(c->st));
 }
-// switching key -> file: the stored split form is joined into plain residues first
 void save_evk(hb_ctx *c, const Evk &k, uint64_t g, const std::string &path) {
     const size_t limbs = (size_t)k.nd * 2 * c->nprimes;
-    Tmp plain(c, limbs);
-    CK(cudaMemcpyAsync(plain.p, k.d, limbs * c->N * 8, cudaMemcpyDeviceToDevice, c->st));
-    LAUNCH(c), k_split_key<<<c->egrid((int)limbs), 256, 0, c->st>>>(plain.p, c->allmap(), c->pc, c->N, 1);
     FileHeader h{}; h.kind = kFileEvk; h.level = (uint32_t)c->L; h.digits = (uint32_t)k.nd; h.galois = g; h.n_poly = 2;
-    write_file(c, path.c_str(), h, plain.p, limbs * c->N);
+    write_file(c, path.c_str(), h, k.d, limbs * c->N);
 }
 } // namespace
 
@@ -1629,11 +1616,7 @@ int hb_keys_load(hb_ctx *c, const char *dir, const uint64_t *galois, int count) 
             const size_t limbs = (size_t)nd * 2 * c->nprimes;
             if ((int)h.digits != nd || h.galois != g || w.size() != limbs * c->N) fail(HB_E_ARG, path + ": does not fit this context");
             Evk k; k.nd = nd; k.d = c->alloc_limbs(limbs);
-            try {
-                upload(c, k.d, w);
-                LAUNCH(c), k_split_key<<<c->egrid((int)limbs), 256, 0, c->st>>>(k.d, c->allmap(), c->pc, c->N, 0);
-                CK(cudaGetLastError());
-            } catch (...) { c->pool.put(k.d); throw; }
+            try { upload(c, k.d, w); } catch (...) { c->pool.put(k.d); throw; }
             return k;
         };
         auto replace = [&](Evk &slot, Evk k) { if (slot.d) c->pool.put(slot.d); slot = k; };

@@ -334,11 +334,11 @@ __device__ __forceinline__ void modup_body(u64 *__restrict__ dt, const u64 *__re
     for (int j = 0; j < ne; ++j) {
         if (j >= lo && j < hi) continue;
         const PrimeConst *m = pc + pl->ext_prime[j];
-        Acc128 s; s.zero();
+        PieceAcc s; s.zero(); // at most 8 sources
 #pragma unroll
-        for (int k = 0; k < NS; ++k) s.mad(y[k], pl->hat_mod[dg][k][j]);
+        for (int k = 0; k < NS; ++k) s.mac(y[k], pl->hat_mod[dg][k][j]);
         PrimeConst mm; mm.q = m->q; mm.mu_hi = m->mu_hi; mm.mu_lo = m->mu_lo;
-        *o = barrett128(s.hi, s.lo, mm);
+        *o = s.finish(mm);
         o += N;
     }
 }
@@ -358,29 +358,14 @@ __global__ void k_modup(u64 *__restrict__ dt, const u64 *__restrict__ a_coef, co
     }
 }
 
-// Switching keys live on the device in split form (split_word: the two pieces of every residue in the two halves of
-// the word).  k_split_key converts a freshly generated key in place, k_join_key gives the plain residues back.
-// grid = (N/(256*kElems), limbs); limb li uses prime map.prime[li % map.n]
-__global__ void k_split_key(u64 *__restrict__ key, LimbMap map, const PrimeConst *__restrict__ pc, int N, int join) {
-    const int li = blockIdx.y;
-    const bool small = pc[map.prime[li % map.n]].fp != 0;
-#pragma unroll
-    for (int u_ = 0; u_ < kElems; ++u_) {
-        const int i = (blockIdx.x * kElems + u_) * blockDim.x + threadIdx.x;
-        if (i >= N) break;
-        const size_t off = (size_t)li * N + i;
-        const u64 v = key[off];
-        key[off] = join ? (small ? join_word<kSplitSmall>(v) : join_word<kSplitBig>(v)) : (small ? split_word<kSplitSmall>(v) : split_word<kSplitBig>(v));
-    }
-}
-
 // Inner product with the switching key over Q_level u P.
 //   acc[b][p][j][i] = sum_dg digit_dg[j][perm_g(i)] * key[dg][p][prime(j)][i]
 // digit_dg[j] is a_ntt[j] for own limbs and dt[...] otherwise.  grid = (N/(256*kElems), batch, ne)
-template <int SH>
-__device__ __forceinline__ void ks_inner_body(u64 *__restrict__ acc, const u64 *__restrict__ a_ntt, size_t a_outer, const u64 *__restrict__ dt, const u64 *__restrict__ key,
-                                              int key_primes, const KsPlan *__restrict__ pl, const PrimeConst &m, int pj, int j, int b, u32 g, int logn, int N) {
-    const int nd = pl->nd, ne = pl->ne;
+__global__ void k_ks_inner(u64 *__restrict__ acc, const u64 *__restrict__ a_ntt, size_t a_outer, const u64 *__restrict__ dt, const u64 *__restrict__ key, int key_primes,
+                           const KsPlan *__restrict__ pl, const PrimeConst *__restrict__ pc, u32 g, int logn, int N) {
+    const int j = blockIdx.z, b = blockIdx.y; // limb-major block order: the key limbs stay in L2 across the members
+    const int pj = pl->ext_prime[j], nd = pl->nd, ne = pl->ne;
+    const PrimeConst m = pc[pj];
     const u32 x0 = blockIdx.x * (blockDim.x * kElems) + threadIdx.x;
     u32 src[kElems];
 #pragma unroll
@@ -389,31 +374,45 @@ __device__ __forceinline__ void ks_inner_body(u64 *__restrict__ acc, const u64 *
     const u64 *dbase = dt + (size_t)b * pl->dt_count * N;
     const u64 *kbase = key + (size_t)pj * N + x0;
     const size_t kpoly = (size_t)key_primes * N;
-    SplitAcc<SH> s0[kElems], s1[kElems];
+    u64 r0[kElems], r1[kElems];
+    if (m.fp) {
 #pragma unroll
-    for (int u = 0; u < kElems; ++u) { s0[u].zero(); s1[u].zero(); }
-    for (int dg = 0; dg < nd; ++dg) { // at most 8 digits: the accumulators hold 16 terms
-        const int en = pl->dt_entry[dg][j];
-        const u64 *sp = en < 0 ? abase : dbase + (size_t)en * N;
-        const u64 *k0 = kbase + (size_t)dg * 2 * kpoly;
+        for (int u = 0; u < kElems; ++u) { r0[u] = 0; r1[u] = 0; }
+        for (int dg = 0; dg < nd; ++dg) {
+            const int en = pl->dt_entry[dg][j];
+            const u64 *sp = en < 0 ? abase : dbase + (size_t)en * N;
+            const u64 *k0 = kbase + (size_t)dg * 2 * kpoly;
 #pragma unroll
-        for (int u = 0; u < kElems; ++u) {
-            const u64 v = sp[src[u]];
-            s0[u].mac(v, k0[u * blockDim.x]);
-            s1[u].mac(v, k0[kpoly + u * blockDim.x]);
+            for (int u = 0; u < kElems; ++u) {
+                const u64 v = sp[src[u]], ka = k0[u * blockDim.x], kb = k0[kpoly + u * blockDim.x];
+                const double vd = u52_to_double(v);
+                r0[u] += mul_small_lazy_d(v, vd, ka, u52_to_double(ka), m.q_inv_f, m.q);
+                r1[u] += mul_small_lazy_d(v, vd, kb, u52_to_double(kb), m.q_inv_f, m.q);
+            }
         }
+#pragma unroll
+        for (int u = 0; u < kElems; ++u) { r0[u] = reduce_fp(r0[u], m.q_inv_f, m.q); r1[u] = reduce_fp(r1[u], m.q_inv_f, m.q); }
+    } else {
+        Acc128 s0[kElems], s1[kElems];
+#pragma unroll
+        for (int u = 0; u < kElems; ++u) { s0[u].zero(); s1[u].zero(); }
+        for (int dg = 0; dg < nd; ++dg) {
+            const int en = pl->dt_entry[dg][j];
+            const u64 *sp = en < 0 ? abase : dbase + (size_t)en * N;
+            const u64 *k0 = kbase + (size_t)dg * 2 * kpoly;
+#pragma unroll
+            for (int u = 0; u < kElems; ++u) {
+                const u64 v = sp[src[u]];
+                s0[u].mad(v, k0[u * blockDim.x]);
+                s1[u].mad(v, k0[kpoly + u * blockDim.x]);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < kElems; ++u) { r0[u] = barrett128(s0[u].hi, s0[u].lo, m); r1[u] = barrett128(s1[u].hi, s1[u].lo, m); }
     }
     u64 *o0 = acc + (((size_t)b * 2) * ne + j) * N + x0, *o1 = o0 + (size_t)ne * N;
 #pragma unroll
-    for (int u = 0; u < kElems; ++u) { o0[u * blockDim.x] = s0[u].finish(m); o1[u * blockDim.x] = s1[u].finish(m); }
-}
-__global__ void k_ks_inner(u64 *__restrict__ acc, const u64 *__restrict__ a_ntt, size_t a_outer, const u64 *__restrict__ dt, const u64 *__restrict__ key, int key_primes,
-                           const KsPlan *__restrict__ pl, const PrimeConst *__restrict__ pc, u32 g, int logn, int N) {
-    const int j = blockIdx.z, b = blockIdx.y; // limb-major block order: the key limbs stay in L2 across the members
-    const int pj = pl->ext_prime[j];
-    const PrimeConst m = pc[pj];
-    if (m.fp) ks_inner_body<kSplitSmall>(acc, a_ntt, a_outer, dt, key, key_primes, pl, m, pj, j, b, g, logn, N);
-    else ks_inner_body<kSplitBig>(acc, a_ntt, a_outer, dt, key, key_primes, pl, m, pj, j, b, g, logn, N);
+    for (int u = 0; u < kElems; ++u) { o0[u * blockDim.x] = r0[u]; o1[u * blockDim.x] = r1[u]; }
 }
 
 // ModDown conversion: pcoef [bp][K][N] (special limbs, coefficient form) -> t [bp][n][N] (coefficient form)
@@ -427,11 +426,11 @@ __device__ __forceinline__ void moddown_conv_body(u64 *__restrict__ t, const u64
     for (int k = 0; k < K; ++k) y[k] = mul_shoup(pcoef[((size_t)bp * K + k) * N + i], pl->p_hat_inv[k], pl->p_hat_inv_sh[k], pc[Lp1 + k].q);
     u64 *o = t + (size_t)bp * n * N + i;
     for (int l = 0; l < n; ++l) {
-        Acc128 s; s.zero();
+        PieceAcc s; s.zero();
 #pragma unroll
-        for (int k = 0; k < K; ++k) s.mad(y[k], pl->p_hat_mod[k][l]);
+        for (int k = 0; k < K; ++k) s.mac(y[k], pl->p_hat_mod[k][l]);
         PrimeConst mm; mm.q = pc[l].q; mm.mu_hi = pc[l].mu_hi; mm.mu_lo = pc[l].mu_lo;
-        *o = barrett128(s.hi, s.lo, mm);
+        *o = s.finish(mm);
         o += N;
     }
 }
@@ -477,52 +476,68 @@ __global__ void k_moddown_fin(u64 *__restrict__ out, size_t out_outer, const u64
 struct RotTerm { const u64 *a_ntt; const u64 *dt; const u64 *key; u32 g; u32 pad; };
 struct RotTermList { RotTerm t[16]; int count; };
 //   acc[b][p][j][i] = sum_t sum_dg digit_t,dg[j][perm_t(i)] * key_t[dg][p][prime(j)][i]      grid = (N/(256*kElems), batch, ne)
-template <int SH>
-__device__ __forceinline__ void ks_inner_sum_body(u64 *__restrict__ acc, const RotTermList &tl, size_t a_outer, int key_primes, const KsPlan *__restrict__ pl,
-                                                  const PrimeConst &m, int pj, int j, int b, int logn, int N) {
-    const int nd = pl->nd, ne = pl->ne;
-    const u32 x0 = blockIdx.x * (blockDim.x * kElems) + threadIdx.x;
-    const size_t kpoly = (size_t)key_primes * N;
-    SplitAcc<SH> s0[kElems], s1[kElems];
-#pragma unroll
-    for (int u = 0; u < kElems; ++u) { s0[u].zero(); s1[u].zero(); }
-    int held = 0; // terms in the piece accumulators since the last flush
-    for (int t = 0; t < tl.count; ++t) {
-        u32 src[kElems];
-#pragma unroll
-        for (int u = 0; u < kElems; ++u) src[u] = ntt_perm(x0 + u * blockDim.x, tl.t[t].g, logn);
-        const u64 *abase = tl.t[t].a_ntt + (size_t)b * a_outer + (size_t)j * N;
-        const u64 *dbase = tl.t[t].dt + (size_t)b * pl->dt_count * N;
-        const u64 *kbase = tl.t[t].key + (size_t)pj * N + x0;
-        if (SH == kSplitBig && held + nd > 16) {
-#pragma unroll
-            for (int u = 0; u < kElems; ++u) { s0[u].flush(); s1[u].flush(); }
-            held = 0;
-        }
-        held += nd;
-        for (int dg = 0; dg < nd; ++dg) {
-            const int en = pl->dt_entry[dg][j];
-            const u64 *sp = en < 0 ? abase : dbase + (size_t)en * N;
-            const u64 *k0 = kbase + (size_t)dg * 2 * kpoly;
-#pragma unroll
-            for (int u = 0; u < kElems; ++u) {
-                const u64 v = sp[src[u]];
-                s0[u].mac(v, k0[u * blockDim.x]);
-                s1[u].mac(v, k0[kpoly + u * blockDim.x]);
-            }
-        }
-    }
-    u64 *o0 = acc + (((size_t)b * 2) * ne + j) * N + x0, *o1 = o0 + (size_t)ne * N;
-#pragma unroll
-    for (int u = 0; u < kElems; ++u) { o0[u * blockDim.x] = s0[u].finish(m); o1[u * blockDim.x] = s1[u].finish(m); }
-}
 __global__ void k_ks_inner_sum(u64 *__restrict__ acc, RotTermList tl, size_t a_outer, int key_primes, const KsPlan *__restrict__ pl, const PrimeConst *__restrict__ pc,
                                int logn, int N) {
     const int j = blockIdx.z, b = blockIdx.y;
-    const int pj = pl->ext_prime[j];
+    const int pj = pl->ext_prime[j], nd = pl->nd, ne = pl->ne;
     const PrimeConst m = pc[pj];
-    if (m.fp) ks_inner_sum_body<kSplitSmall>(acc, tl, a_outer, key_primes, pl, m, pj, j, b, logn, N);
-    else ks_inner_sum_body<kSplitBig>(acc, tl, a_outer, key_primes, pl, m, pj, j, b, logn, N);
+    const u32 x0 = blockIdx.x * (blockDim.x * kElems) + threadIdx.x;
+    const size_t kpoly = (size_t)key_primes * N;
+    u64 r0[kElems], r1[kElems];
+    if (m.fp) { // at most 16 terms x 4 digits lazy products below 1.6q: the sums stay below 2^49
+#pragma unroll
+        for (int u = 0; u < kElems; ++u) { r0[u] = 0; r1[u] = 0; }
+        for (int t = 0; t < tl.count; ++t) {
+            u32 src[kElems];
+#pragma unroll
+            for (int u = 0; u < kElems; ++u) src[u] = ntt_perm(x0 + u * blockDim.x, tl.t[t].g, logn);
+            const u64 *abase = tl.t[t].a_ntt + (size_t)b * a_outer + (size_t)j * N;
+            const u64 *dbase = tl.t[t].dt + (size_t)b * pl->dt_count * N;
+            const u64 *kbase = tl.t[t].key + (size_t)pj * N + x0;
+            for (int dg = 0; dg < nd; ++dg) {
+                const int en = pl->dt_entry[dg][j];
+                const u64 *sp = en < 0 ? abase : dbase + (size_t)en * N;
+                const u64 *k0 = kbase + (size_t)dg * 2 * kpoly;
+#pragma unroll
+                for (int u = 0; u < kElems; ++u) {
+                    const u64 v = sp[src[u]], ka = k0[u * blockDim.x], kb = k0[kpoly + u * blockDim.x];
+                    const double vd = u52_to_double(v);
+                    r0[u] += mul_small_lazy_d(v, vd, ka, u52_to_double(ka), m.q_inv_f, m.q);
+                    r1[u] += mul_small_lazy_d(v, vd, kb, u52_to_double(kb), m.q_inv_f, m.q);
+                }
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < kElems; ++u) { r0[u] = reduce_fp(r0[u], m.q_inv_f, m.q); r1[u] = reduce_fp(r1[u], m.q_inv_f, m.q); }
+    } else {   // 64 products below 2^120 fit the 128-bit accumulator
+        Acc128 s0[kElems], s1[kElems];
+#pragma unroll
+        for (int u = 0; u < kElems; ++u) { s0[u].zero(); s1[u].zero(); }
+        for (int t = 0; t < tl.count; ++t) {
+            u32 src[kElems];
+#pragma unroll
+            for (int u = 0; u < kElems; ++u) src[u] = ntt_perm(x0 + u * blockDim.x, tl.t[t].g, logn);
+            const u64 *abase = tl.t[t].a_ntt + (size_t)b * a_outer + (size_t)j * N;
+            const u64 *dbase = tl.t[t].dt + (size_t)b * pl->dt_count * N;
+            const u64 *kbase = tl.t[t].key + (size_t)pj * N + x0;
+            for (int dg = 0; dg < nd; ++dg) {
+                const int en = pl->dt_entry[dg][j];
+                const u64 *sp = en < 0 ? abase : dbase + (size_t)en * N;
+                const u64 *k0 = kbase + (size_t)dg * 2 * kpoly;
+#pragma unroll
+                for (int u = 0; u < kElems; ++u) {
+                    const u64 v = sp[src[u]];
+                    s0[u].mad(v, k0[u * blockDim.x]);
+                    s1[u].mad(v, k0[kpoly + u * blockDim.x]);
+                }
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < kElems; ++u) { r0[u] = barrett128(s0[u].hi, s0[u].lo, m); r1[u] = barrett128(s1[u].hi, s1[u].lo, m); }
+    }
+    u64 *o0 = acc + (((size_t)b * 2) * ne + j) * N + x0, *o1 = o0 + (size_t)ne * N;
+#pragma unroll
+    for (int u = 0; u < kElems; ++u) { o0[u * blockDim.x] = r0[u]; o1[u * blockDim.x] = r1[u]; }
 }
 // add[b][p][l][i] = sum over the rotated terms of (p == 0) c0_t[b][l][perm_t(i)]  +  sum over the unrotated terms of x_t[b][p][l][i]
 // rot: terms with g != 1 (a_ntt - n limbs = c0); plain: terms added as they are.  grid = (N/(256*kElems), n, batch*2)
@@ -585,7 +600,7 @@ __global__ void k_ks_inner_pair(u64 *__restrict__ E, const u64 *__restrict__ c0,
         for (int u = 0; u < kElems; ++u) src[u] = ntt_perm(x0 + u * blockDim.x, rp.g[r], logn);
         const u64 *kbase = rp.key[r] + (size_t)pj * N + x0;
         u64 r0[kElems], r1[kElems];
-        if (m.fp) { // the keys are stored in split form: join_word gives the residue back
+        if (m.fp) {
 #pragma unroll
             for (int u = 0; u < kElems; ++u) { r0[u] = 0; r1[u] = 0; }
             for (int dg = 0; dg < nd; ++dg) {
@@ -594,7 +609,7 @@ __global__ void k_ks_inner_pair(u64 *__restrict__ E, const u64 *__restrict__ c0,
                 const u64 *k0 = kbase + (size_t)dg * 2 * kpoly;
 #pragma unroll
                 for (int u = 0; u < kElems; ++u) {
-                    const u64 v = sp[src[u]], ka = join_word<kSplitSmall>(k0[u * blockDim.x]), kb = join_word<kSplitSmall>(k0[kpoly + u * blockDim.x]);
+                    const u64 v = sp[src[u]], ka = k0[u * blockDim.x], kb = k0[kpoly + u * blockDim.x];
                     const double vd = u52_to_double(v);
                     r0[u] += mul_small_lazy_d(v, vd, ka, u52_to_double(ka), m.q_inv_f, m.q);
                     r1[u] += mul_small_lazy_d(v, vd, kb, u52_to_double(kb), m.q_inv_f, m.q);
@@ -613,8 +628,8 @@ __global__ void k_ks_inner_pair(u64 *__restrict__ E, const u64 *__restrict__ c0,
 #pragma unroll
                 for (int u = 0; u < kElems; ++u) {
                     const u64 v = sp[src[u]];
-                    s0[u].mad(v, join_word<kSplitBig>(k0[u * blockDim.x]));
-                    s1[u].mad(v, join_word<kSplitBig>(k0[kpoly + u * blockDim.x]));
+                    s0[u].mad(v, k0[u * blockDim.x]);
+                    s1[u].mad(v, k0[kpoly + u * blockDim.x]);
                 }
             }
 #pragma unroll
@@ -643,7 +658,7 @@ __global__ void k_ks_inner_pair(u64 *__restrict__ E, const u64 *__restrict__ c0,
 // sum_dg digit_dg * (mask * key_dg) = mask * sum_dg digit_dg * key_dg modulo q, so a key multiplied by the mask once
 // (k_mask_key) turns the masked pair of rotations into ONE lazy inner product with ONE reduction per output residue;
 // the residues are those of k_ks_inner_pair.
-// mkey[dg][p][j][i] = (mask[j][i] + mask2[j][i]) * key[dg][p][prime(j)][i], read and written in split form;  grid = (N/(256*kElems), ne, nd*2)
+// mkey[dg][p][j][i] = (mask[j][i] + mask2[j][i]) * key[dg][p][prime(j)][i];  grid = (N/(256*kElems), ne, nd*2)
 __global__ void k_mask_key(u64 *__restrict__ mkey, const u64 *__restrict__ key, int key_primes, const u64 *__restrict__ mask, const u64 *__restrict__ mask2,
                            const KsPlan *__restrict__ pl, const PrimeConst *__restrict__ pc, int N) {
     const int j = blockIdx.y, dgp = blockIdx.z, ne = pl->ne;
@@ -655,12 +670,10 @@ __global__ void k_mask_key(u64 *__restrict__ mkey, const u64 *__restrict__ key, 
         if (i >= N) break;
         u64 w = mask[(size_t)j * N + i];
         if (mask2) w = add_mod(w, mask2[(size_t)j * N + i], m.q);
-        const u64 ks = key[((size_t)dgp * key_primes + pj) * N + i];
-        const u64 r = mul_mod_any(w, m.fp ? join_word<kSplitSmall>(ks) : join_word<kSplitBig>(ks), m);
-        mkey[((size_t)dgp * ne + j) * N + i] = m.fp ? split_word<kSplitSmall>(r) : split_word<kSplitBig>(r);
+        mkey[((size_t)dgp * ne + j) * N + i] = mul_mod_any(w, key[((size_t)dgp * key_primes + pj) * N + i], m);
     }
 }
-// pm[j][i] = P * (mask[j][i] + mask2[j][i]) mod q_j for the Q limbs, in split form;  grid = (N/(256*kElems), n)
+// pm[j][i] = P * (mask[j][i] + mask2[j][i]) mod q_j for the Q limbs;  grid = (N/(256*kElems), n)
 __global__ void k_mask_p(u64 *__restrict__ pm, const u64 *__restrict__ mask, const u64 *__restrict__ mask2, const DivPlan *__restrict__ dv, const PrimeConst *__restrict__ pc, int N) {
     const int j = blockIdx.y;
     const PrimeConst m = pc[j];
@@ -670,13 +683,12 @@ __global__ void k_mask_p(u64 *__restrict__ pm, const u64 *__restrict__ mask, con
         if (i >= N) break;
         u64 w = mask[(size_t)j * N + i];
         if (mask2) w = add_mod(w, mask2[(size_t)j * N + i], m.q);
-        const u64 r = mul_mod_any(w, dv->p_mod[j], m);
-        pm[(size_t)j * N + i] = m.fp ? split_word<kSplitSmall>(r) : split_word<kSplitBig>(r);
+        pm[(size_t)j * N + i] = mul_mod_any(w, dv->p_mod[j], m);
     }
 }
 struct MaskedRot {
-    const u64 *mkey[2];   // [nd][2][ne][N], split form
-    const u64 *pm[2];     // [n][N], split form
+    const u64 *mkey[2];   // [nd][2][ne][N]
+    const u64 *pm[2];     // [n][N]
     u32 g[2];
     int count;            // 1 or 2 rotations
 };
@@ -685,57 +697,79 @@ struct MaskedRotList { MaskedRot r[kMaxRotGroups]; }; // one entry per wrapped c
 // E[b][p][j][i] = sum_r sum_dg digit_dg[j][perm_r(i)] * mkey_r[dg][p][j][i]  +  (p == 0, j < n) sum_r c0[b][j][perm_r(i)] * pm_r[j][i]
 // grid = (N/(256*EL), groups * batch, ne); EL coefficients per thread.  Output member g * batch + b is wrapped copy
 // number g (its own pair of masked keys) of input member b: several iterations of a shift loop in one launch.
-// One lazy sum of at most 2 * (nd + 1) products and ONE reduction per output residue.
-template <int SH, int EL>
-__device__ __forceinline__ void ks_inner_mk_body(u64 *__restrict__ E, const u64 *__restrict__ c0, const u64 *__restrict__ a_ntt, size_t a_outer, const u64 *__restrict__ dt,
-                                                 const MaskedRot &mr, int ob, int b, int j, const KsPlan *__restrict__ pl, const PrimeConst &m, int logn, int N) {
-    const int nd = pl->nd, ne = pl->ne, n = pl->n;
+template <int EL>
+__global__ void __launch_bounds__(256, EL == 2 ? 3 : 2) k_ks_inner_mk(u64 *__restrict__ E, const u64 *__restrict__ c0, const u64 *__restrict__ a_ntt, size_t a_outer, const u64 *__restrict__ dt, MaskedRotList mrl,
+                              int batch, const KsPlan *__restrict__ pl, const PrimeConst *__restrict__ pc, int logn, int N) {
+    const int j = blockIdx.z, ob = blockIdx.y, b = ob % batch; // limb-major block order: the key limbs stay in L2 across the members
+    const MaskedRot &mr = mrl.r[ob / batch];
+    const int pj = pl->ext_prime[j], nd = pl->nd, ne = pl->ne, n = pl->n;
+    const PrimeConst m = pc[pj];
     const u32 x0 = blockIdx.x * (blockDim.x * EL) + threadIdx.x;
     const u64 *abase = a_ntt + (size_t)b * a_outer + (size_t)j * N;
     const u64 *cbase = c0 + (size_t)b * a_outer + (size_t)j * N;
     const u64 *dbase = dt + (size_t)b * pl->dt_count * N;
     const size_t kpoly = (size_t)ne * N;
-    SplitAcc<SH> s0[EL], s1[EL];
+    u64 r0[EL], r1[EL];
+    if (m.fp) {
 #pragma unroll
-    for (int u = 0; u < EL; ++u) { s0[u].zero(); s1[u].zero(); }
-    for (int r = 0; r < mr.count; ++r) {
-        u32 src[EL];
+        for (int u = 0; u < EL; ++u) { r0[u] = 0; r1[u] = 0; }
+        for (int r = 0; r < mr.count; ++r) {
+            u32 src[EL];
 #pragma unroll
-        for (int u = 0; u < EL; ++u) src[u] = ntt_perm(x0 + u * blockDim.x, mr.g[r], logn);
-        if (SH == kSplitBig && r == 1 && 2 * (nd + 1) > 16) { // more than 16 terms in all: fold the first rotation's
+            for (int u = 0; u < EL; ++u) src[u] = ntt_perm(x0 + u * blockDim.x, mr.g[r], logn);
+            const u64 *kbase = mr.mkey[r] + (size_t)j * N + x0;
+            for (int dg = 0; dg < nd; ++dg) {
+                const int en = pl->dt_entry[dg][j];
+                const u64 *sp = en < 0 ? abase : dbase + (size_t)en * N;
+                const u64 *k0 = kbase + (size_t)dg * 2 * kpoly;
 #pragma unroll
-            for (int u = 0; u < EL; ++u) { s0[u].flush(); s1[u].flush(); }
-        }
-        const u64 *kbase = mr.mkey[r] + (size_t)j * N + x0;
-        for (int dg = 0; dg < nd; ++dg) {
-            const int en = pl->dt_entry[dg][j];
-            const u64 *sp = en < 0 ? abase : dbase + (size_t)en * N;
-            const u64 *k0 = kbase + (size_t)dg * 2 * kpoly;
+                for (int u = 0; u < EL; ++u) {
+                    const u64 v = sp[src[u]], ka = k0[u * blockDim.x], kb = k0[kpoly + u * blockDim.x];
+                    const double vd = u52_to_double(v);
+                    r0[u] += mul_small_lazy_d(v, vd, ka, u52_to_double(ka), m.q_inv_f, m.q);
+                    r1[u] += mul_small_lazy_d(v, vd, kb, u52_to_double(kb), m.q_inv_f, m.q);
+                }
+            }
+            if (j < n) {
+                const u64 *pmb = mr.pm[r] + (size_t)j * N + x0;
 #pragma unroll
-            for (int u = 0; u < EL; ++u) {
-                const u64 v = sp[src[u]];
-                s0[u].mac(v, k0[u * blockDim.x]);
-                s1[u].mac(v, k0[kpoly + u * blockDim.x]);
+                for (int u = 0; u < EL; ++u) r0[u] += mul_small_lazy(cbase[src[u]], pmb[u * blockDim.x], m.q_inv_f, m.q);
             }
         }
-        if (j < n) {
-            const u64 *pmb = mr.pm[r] + (size_t)j * N + x0;
 #pragma unroll
-            for (int u = 0; u < EL; ++u) s0[u].mac(cbase[src[u]], pmb[u * blockDim.x]);
+        for (int u = 0; u < EL; ++u) { r0[u] = reduce_fp(r0[u], m.q_inv_f, m.q); r1[u] = reduce_fp(r1[u], m.q_inv_f, m.q); }
+    } else {
+        Acc128 s0[EL], s1[EL];
+#pragma unroll
+        for (int u = 0; u < EL; ++u) { s0[u].zero(); s1[u].zero(); }
+        for (int r = 0; r < mr.count; ++r) {
+            u32 src[EL];
+#pragma unroll
+            for (int u = 0; u < EL; ++u) src[u] = ntt_perm(x0 + u * blockDim.x, mr.g[r], logn);
+            const u64 *kbase = mr.mkey[r] + (size_t)j * N + x0;
+            for (int dg = 0; dg < nd; ++dg) {
+                const int en = pl->dt_entry[dg][j];
+                const u64 *sp = en < 0 ? abase : dbase + (size_t)en * N;
+                const u64 *k0 = kbase + (size_t)dg * 2 * kpoly;
+#pragma unroll
+                for (int u = 0; u < EL; ++u) {
+                    const u64 v = sp[src[u]];
+                    s0[u].mad(v, k0[u * blockDim.x]);
+                    s1[u].mad(v, k0[kpoly + u * blockDim.x]);
+                }
+            }
+            if (j < n) {
+                const u64 *pmb = mr.pm[r] + (size_t)j * N + x0;
+#pragma unroll
+                for (int u = 0; u < EL; ++u) s0[u].mad(cbase[src[u]], pmb[u * blockDim.x]);
+            }
         }
+#pragma unroll
+        for (int u = 0; u < EL; ++u) { r0[u] = barrett128(s0[u].hi, s0[u].lo, m); r1[u] = barrett128(s1[u].hi, s1[u].lo, m); }
     }
     u64 *o0 = E + (((size_t)ob * 2) * ne + j) * N + x0, *o1 = o0 + (size_t)ne * N;
 #pragma unroll
-    for (int u = 0; u < EL; ++u) { o0[u * blockDim.x] = s0[u].finish(m); o1[u * blockDim.x] = s1[u].finish(m); }
-}
-template <int EL>
-__global__ void __launch_bounds__(256, 3) k_ks_inner_mk(u64 *__restrict__ E, const u64 *__restrict__ c0, const u64 *__restrict__ a_ntt, size_t a_outer, const u64 *__restrict__ dt,
-                                                        const __grid_constant__ MaskedRotList mrl, int batch, const KsPlan *__restrict__ pl, const PrimeConst *__restrict__ pc, int logn, int N) {
-    const int j = blockIdx.z, ob = blockIdx.y, b = ob % batch; // limb-major block order: the key limbs stay in L2 across the members
-    const MaskedRot &mr = mrl.r[ob / batch];
-    const PrimeConst m = pc[pl->ext_prime[j]];
-    if (m.fp) ks_inner_mk_body<kSplitSmall, EL>(E, c0, a_ntt, a_outer, dt, mr, ob, b, j, pl, m, logn, N);
-    else ks_inner_mk_body<kSplitBig, EL>(E, c0, a_ntt, a_outer, dt, mr, ob, b, j, pl, m, logn, N);
+    for (int u = 0; u < EL; ++u) { o0[u * blockDim.x] = r0[u]; o1[u * blockDim.x] = r1[u]; }
 }
 // Base conversion of the division: src [bp][ns][N] (limbs q_level, P; coefficient form) -> t [bp][level][N]
 // grid = (N/256, 1, nbp)
@@ -747,11 +781,11 @@ __device__ __forceinline__ void div_conv_body(u64 *__restrict__ t, const u64 *__
     for (int k = 0; k < NS; ++k) y[k] = mul_shoup(src[((size_t)bp * NS + k) * N + i], dv->hat_inv[k], dv->hat_inv_sh[k], pc[dv->src_prime[k]].q);
     u64 *o = t + (size_t)bp * nl * N + i;
     for (int l = 0; l < nl; ++l) {
-        Acc128 s; s.zero();
+        PieceAcc s; s.zero();
 #pragma unroll
-        for (int k = 0; k < NS; ++k) s.mad(y[k], dv->hat_mod[k][l]);
+        for (int k = 0; k < NS; ++k) s.mac(y[k], dv->hat_mod[k][l]);
         PrimeConst mm; mm.q = pc[l].q; mm.mu_hi = pc[l].mu_hi; mm.mu_lo = pc[l].mu_lo;
-        *o = barrett128(s.hi, s.lo, mm);
+        *o = s.finish(mm);
         o += N;
     }
 }

@@ -140,37 +140,30 @@ struct Acc128 {
     }
 };
 
-// ---- split multiply-accumulate for inner products with switching keys ----------------------------------------
-// A residue is cut into two pieces of SH bits (SH = 21 for primes below 2^44, whose residues have at most 44 bits;
-// SH = 30 for the primes below 2^60).  A product v*k is then four 32 x 32 -> 64-bit multiply-adds, one per pair of
-// pieces, each into its own 64-bit accumulator -- no carries, no per-term reduction.  The sum of products is
-//     a0 + (a1 + a2) * 2^SH + a3 * 2^(2 SH),
-// assembled and reduced once per output residue.  With SH = 30 a piece product is below 2^60, so an accumulator
-// holds 16 terms (flush() folds them into a 128-bit running sum); with SH = 21 it holds more than 2^17 terms.
-// Switching keys are stored with the pieces already in the two 32-bit halves of each word (split_word), so the key
-// operand costs nothing to split.
-constexpr int kSplitSmall = 21, kSplitBig = 30;
+// ---- sums of products modulo the primes of 44 to 60 bits ---------------------------------------------------------
+// A full 64 x 64 -> 128-bit product with its carries costs about thirty 32-bit multiply-adds on this GPU.  For lazy
+// sums of a few products the operands are cut into two pieces of 30 bits instead: a product is then four
+// 32 x 32 -> 64-bit multiply-adds, one per pair of pieces, each into its own 64-bit accumulator with no carries, and
+// the sum of products is  a0 + (a1 + a2) * 2^30 + a3 * 2^60,  assembled and reduced once per output residue.
+// A piece product is below 2^60, so an accumulator holds 16 terms; flush() folds them into a 128-bit running sum.
 __device__ __forceinline__ u64 mad_wide(u32 a, u32 b, u64 c) {
     u64 r;
     asm("mad.wide.u32 %0, %1, %2, %3;" : "=l"(r) : "r"(a), "r"(b), "l"(c));
     return r;
 }
-template <int SH> __device__ __forceinline__ u64 split_word(u64 v) { return (v & ((1ull << SH) - 1)) | ((v >> SH) << 32); }
-template <int SH> __device__ __forceinline__ u64 join_word(u64 s) { return (s & 0xFFFFFFFFull) + ((s >> 32) << SH); }
-template <int SH> struct SplitAcc {
+struct PieceAcc {
     u64 a0, a1, a2, a3, lo, hi;
     __device__ __forceinline__ void zero() { a0 = a1 = a2 = a3 = 0; lo = hi = 0; }
-    // v: a plain residue; ks: a key word in split form
-    __device__ __forceinline__ void mac(u64 v, u64 ks) {
-        const u32 v0 = (u32)v & ((1u << SH) - 1), v1 = (u32)(v >> SH), k0 = (u32)ks, k1 = (u32)(ks >> 32);
+    __device__ __forceinline__ void mac(u64 v, u64 k) { // v, k < 2^60
+        const u32 v0 = (u32)v & 0x3FFFFFFFu, v1 = (u32)(v >> 30), k0 = (u32)k & 0x3FFFFFFFu, k1 = (u32)(k >> 30);
         a0 = mad_wide(v0, k0, a0); a1 = mad_wide(v0, k1, a1); a2 = mad_wide(v1, k0, a2); a3 = mad_wide(v1, k1, a3);
     }
     __device__ __forceinline__ void add128(u64 l, u64 h) { lo += l; hi += h + (lo < l); }
     __device__ __forceinline__ void flush() {
         add128(a0, 0);
-        add128(a1 << SH, a1 >> (64 - SH));
-        add128(a2 << SH, a2 >> (64 - SH));
-        add128(a3 << (2 * SH), a3 >> (64 - 2 * SH));
+        add128(a1 << 30, a1 >> 34);
+        add128(a2 << 30, a2 >> 34);
+        add128(a3 << 60, a3 >> 4);
         a0 = a1 = a2 = a3 = 0;
     }
     __device__ __forceinline__ u64 finish(const PrimeConst &m) { flush(); return barrett128(hi, lo, m); }

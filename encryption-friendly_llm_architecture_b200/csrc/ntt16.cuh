@@ -88,28 +88,29 @@ __device__ __forceinline__ void gs_bfly(u64 &x, u64 &y, u64 w, u64 ws, u64 q, u6
     y = mul_shoup_lazy(d, w, ws, q);
 }
 // four Cooley-Tukey stages on 16 register values; twiddle j = (1 << s) - 1 + g of local stage s, group g, at tp[j * STRIDE]
-template <int STRIDE> __device__ __forceinline__ void fwd16_int(u64 (&v)[16], const ulonglong2 *__restrict__ tp, u64 q) {
+template <bool GL> __device__ __forceinline__ ulonglong2 tw_load(const ulonglong2 *p) { if (GL) return __ldg(p); return *p; }
+template <int STRIDE, bool GL = true> __device__ __forceinline__ void fwd16_int(u64 (&v)[16], const ulonglong2 *__restrict__ tp, u64 q) {
     const u64 q2 = q << 1;
 #pragma unroll
     for (int s = 0; s < 4; ++s) {
         const int half = 8 >> s;
 #pragma unroll
         for (int g = 0; g < (1 << s); ++g) {
-            const ulonglong2 tw = __ldg(tp + ((1 << s) - 1 + g) * STRIDE);
+            const ulonglong2 tw = tw_load<GL>(tp + ((1 << s) - 1 + g) * STRIDE);
 #pragma unroll
             for (int j = 0; j < half; ++j) ct_bfly(v[g * 2 * half + j], v[g * 2 * half + j + half], tw.x, tw.y, q, q2);
         }
     }
 }
 // four Gentleman-Sande stages, the mirror image
-template <int STRIDE> __device__ __forceinline__ void inv16_int(u64 (&v)[16], const ulonglong2 *__restrict__ tp, u64 q) {
+template <int STRIDE, bool GL = true> __device__ __forceinline__ void inv16_int(u64 (&v)[16], const ulonglong2 *__restrict__ tp, u64 q) {
     const u64 q2 = q << 1;
 #pragma unroll
     for (int s = 3; s >= 0; --s) {
         const int half = 8 >> s;
 #pragma unroll
         for (int g = 0; g < (1 << s); ++g) {
-            const ulonglong2 tw = __ldg(tp + ((1 << s) - 1 + g) * STRIDE);
+            const ulonglong2 tw = tw_load<GL>(tp + ((1 << s) - 1 + g) * STRIDE);
 #pragma unroll
             for (int j = 0; j < half; ++j) gs_bfly(v[g * 2 * half + j], v[g * 2 * half + j + half], tw.x, tw.y, q, q2);
         }
@@ -151,13 +152,13 @@ __device__ __forceinline__ u64 ds_store(double v, const DsConst &c, double shift
     const double rb = __fma_rn(-k, c.qd, v2 + kTwo52);                   // 2^52 + (v2 - k q), exact
     return (u64)__double_as_longlong(rb) & 0x000FFFFFFFFFFFFFull;
 }
-template <int STRIDE> __device__ __forceinline__ void fwd16_ds(double (&v)[16], const ulonglong2 *__restrict__ tp, const DsConst &c) {
+template <int STRIDE, bool GL = true> __device__ __forceinline__ void fwd16_ds(double (&v)[16], const ulonglong2 *__restrict__ tp, const DsConst &c) {
 #pragma unroll
     for (int s = 0; s < 4; ++s) {
         const int half = 8 >> s;
 #pragma unroll
         for (int g = 0; g < (1 << s); ++g) {
-            const ulonglong2 tw = __ldg(tp + ((1 << s) - 1 + g) * STRIDE);
+            const ulonglong2 tw = tw_load<GL>(tp + ((1 << s) - 1 + g) * STRIDE);
             const double wf = __longlong_as_double((long long)tw.y);
 #pragma unroll
             for (int j = 0; j < half; ++j) {
@@ -172,13 +173,13 @@ template <int STRIDE> __device__ __forceinline__ void fwd16_ds(double (&v)[16], 
 // Gentleman-Sande round.  The sum path doubles per stage; only v[0] takes the sum at all four stages (16 x its
 // inputs), v[1] ends below 4.2 q whatever came in, the others lower: the caller reduces v[0] after each round, so
 // every round starts from values below 4.2 q and stays below 68 q.
-template <int STRIDE> __device__ __forceinline__ void inv16_ds(double (&v)[16], const ulonglong2 *__restrict__ tp, const DsConst &c) {
+template <int STRIDE, bool GL = true> __device__ __forceinline__ void inv16_ds(double (&v)[16], const ulonglong2 *__restrict__ tp, const DsConst &c) {
 #pragma unroll
     for (int s = 3; s >= 0; --s) {
         const int half = 8 >> s;
 #pragma unroll
         for (int g = 0; g < (1 << s); ++g) {
-            const ulonglong2 tw = __ldg(tp + ((1 << s) - 1 + g) * STRIDE);
+            const ulonglong2 tw = tw_load<GL>(tp + ((1 << s) - 1 + g) * STRIDE);
             const double wf = __longlong_as_double((long long)tw.y);
 #pragma unroll
             for (int j = 0; j < half; ++j) {
@@ -396,340 +397,11 @@ __global__ void __launch_bounds__(256, MINB) ntt16v2_inv_cols(const u64 *__restr
     }
 }
 
-// =====================================================================================================================
-// Persistent variant: asynchronous bulk copies keep the next tile in flight while the current one is transformed.
-//
-// The kernels above load a tile with ordinary loads at the start of a CTA's life, so every CTA begins with a full
-// memory round trip during which it issues nothing; with four CTAs per SM the copy engine sees too few bytes in
-// flight to fill HBM.  Here a CTA lives for the whole launch and walks over tiles t = blockIdx.x, blockIdx.x +
-// gridDim.x, ...; before it transforms tile k it starts the copy of tile k+1 into the other half of a double buffer
-// in shared memory (cp.async.bulk, 128 bytes per thread, completion counted by an mbarrier), so the copy engine
-// always holds one tile per resident CTA.  The tile lands in the layout the first round reads; the exchange between
-// the two rounds happens in place (row pass: with the low four bits of the column index XORed with the next four,
-// which keeps both the strided and the transposed access free of bank conflicts without padding).
-// Waits on the mbarrier are bounded: after kSpinLimit failed polls the kernel sets *err and carries on, so a copy that
-// never lands cannot hang the device; the host reads the flag at the next synchronisation.
-// =====================================================================================================================
-constexpr int kSpinLimit = 1 << 22;
-__device__ __forceinline__ u32 smem_u32(const void *p) { return (u32)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ void mbar_init(u64 *bar, u32 count) { asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory"); }
-__device__ __forceinline__ void mbar_fence_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
-__device__ __forceinline__ void mbar_arrive_expect_tx(u64 *bar, u32 bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-// global -> this CTA's shared memory, 16-byte aligned on both sides, size a multiple of 16
-__device__ __forceinline__ void bulk_load(void *dst_smem, const void *src_gmem, u32 bytes, u64 *bar) {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_u32(dst_smem)), "l"(src_gmem), "r"(bytes),
-                 "r"(smem_u32(bar))
-                 : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(u64 *bar, u32 parity) {
-    u32 ok;
-    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
-    return ok != 0;
-}
-__device__ __forceinline__ void mbar_wait_bounded(u64 *bar, u32 parity, int *err) {
-    for (int spin = 0; spin < kSpinLimit; ++spin)
-        if (mbar_try_wait(bar, parity)) return;
-    *err = 1; // the copy did not land: the results of this launch are void, but nothing waits for ever
-}
-// orders this thread's ordinary shared-memory accesses before later asynchronous copies into the same buffer
-__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
-
-struct TileCtl { // double-buffer bookkeeping shared by the four persistent kernels
-    u64 *bar;    // two mbarriers
-    u32 parity[2];
-    __device__ __forceinline__ void init(u64 *b) {
-        bar = b; parity[0] = parity[1] = 0;
-        if (threadIdx.x == 0) { mbar_init(bar, 1); mbar_init(bar + 1, 1); mbar_fence_init(); }
-        __syncthreads();
-    }
-    __device__ __forceinline__ void expect(int b) { if (threadIdx.x == 0) mbar_arrive_expect_tx(bar + b, 4096 * 8); }
-    __device__ __forceinline__ void wait(int b, int *err) { mbar_wait_bounded(bar + b, parity[b], err); parity[b] ^= 1; }
-};
-// column-pass tile t: limb t / 16, columns 16 * (t % 16) ..; thread r copies row r (16 words) to buf[r * 16]
-__device__ __forceinline__ void issue_cols_tile(TileCtl &tc, int b, u64 *buf, const u64 *src, const LimbAddr16 &sa, int period, int t) {
-    tc.expect(b);
-    const u64 *g = src + sa.off(t >> 4, period) + (size_t)threadIdx.x * 256 + (t & 15) * 16;
-    bulk_load(buf + threadIdx.x * 16, g, 128, tc.bar + b);
-}
-// row-pass tile t: limb t / 16, rows 16 * (t % 16) ..: 4096 contiguous words; thread k copies words 16 k ..
-__device__ __forceinline__ void issue_rows_tile(TileCtl &tc, int b, u64 *buf, const u64 *src, const LimbAddr16 &sa, int period, int t) {
-    tc.expect(b);
-    const u64 *g = src + sa.off(t >> 4, period) + (size_t)(t & 15) * 4096 + threadIdx.x * 16;
-    bulk_load(buf + threadIdx.x * 16, g, 128, tc.bar + b);
-}
-// in-place exchange layout of a row: column c of row r at r * 256 + (c ^ (c >> 4))
-__device__ __forceinline__ int swz(int c) { return c ^ (c >> 4); }
-
-template <int MINB>
-__global__ void __launch_bounds__(256, MINB) ntt16v3_fwd_cols(const u64 *__restrict__ src, LimbAddr16 sa, u64 *__restrict__ dst, LimbAddr16 da,
-                                                           const __grid_constant__ LimbMap map, const PrimeConst *__restrict__ pc, Ntt16Tables tb, int ntiles, int *err) {
-    extern __shared__ __align__(128) unsigned char smem_raw[]; // two 32 KiB tile buffers, then two mbarriers
-    u64(*sm)[4096] = reinterpret_cast<u64(*)[4096]>(smem_raw);
-    TileCtl tc; tc.init(reinterpret_cast<u64 *>(smem_raw + 2 * 4096 * 8));
-    const int tid = threadIdx.x, lane = tid & 15, sub = tid >> 4;
-    int t = blockIdx.x;
-    if (t < ntiles) issue_cols_tile(tc, 0, sm[0], src, sa, map.n, t);
-    for (int it = 0; t < ntiles; t += gridDim.x, ++it) {
-        const int b = it & 1;
-        if (t + (int)gridDim.x < ntiles) issue_cols_tile(tc, b ^ 1, sm[b ^ 1], src, sa, map.n, t + gridDim.x);
-        const int li = t >> 4, pi = map.prime[li % map.n];
-        const PrimeConst m = pc[pi];
-        const ulonglong2 *tab = tb.fwd + (size_t)pi * Ntt16Layout::kEntries;
-        u64 *o = dst + da.off(li, map.n) + (t & 15) * 16 + lane;
-        u64 *buf = sm[b];
-        tc.wait(b, err);
-        if (m.small) {
-            const DsConst c = ds_const(m);
-            double *smd = reinterpret_cast<double *>(buf);
-            double v[16];
-#pragma unroll
-            for (int e = 0; e < 16; ++e) v[e] = ds_load(buf[(e * 16 + sub) * 16 + lane]);
-            fwd16_ds<1>(v, tab + Ntt16Layout::colsA(0), c);
-#pragma unroll
-            for (int e = 0; e < 16; ++e) smd[(e * 16 + sub) * 16 + lane] = v[e]; // the words this thread read itself
-            __syncthreads();
-#pragma unroll
-            for (int e = 0; e < 16; ++e) v[e] = smd[(sub * 16 + e) * 16 + lane];
-            fwd16_ds<1>(v, tab + Ntt16Layout::colsB(sub, 0), c);
-            double *od = reinterpret_cast<double *>(o);
-#pragma unroll
-            for (int e = 0; e < 16; ++e) od[(sub * 16 + e) * 256] = v[e];
-        } else {
-            u64 v[16];
-#pragma unroll
-            for (int e = 0; e < 16; ++e) v[e] = buf[(e * 16 + sub) * 16 + lane];
-            fwd16_int<1>(v, tab + Ntt16Layout::colsA(0), m.q);
-#pragma unroll
-            for (int e = 0; e < 16; ++e) buf[(e * 16 + sub) * 16 + lane] = v[e];
-            __syncthreads();
-#pragma unroll
-            for (int e = 0; e < 16; ++e) v[e] = buf[(sub * 16 + e) * 16 + lane];
-            fwd16_int<1>(v, tab + Ntt16Layout::colsB(sub, 0), m.q);
-#pragma unroll
-            for (int e = 0; e < 16; ++e) o[(sub * 16 + e) * 256] = v[e];
-        }
-        fence_async_smem();
-        __syncthreads(); // everybody is done with this buffer before the next copy into it starts
-    }
-}
-
-template <int MINB, class Store>
-__global__ void __launch_bounds__(256, MINB) ntt16v3_fwd_rows(const u64 *__restrict__ src, LimbAddr16 sa, u64 *__restrict__ dst, LimbAddr16 da,
-                                                           const __grid_constant__ LimbMap map, const PrimeConst *__restrict__ pc, Ntt16Tables tb, Store store, int ntiles, int *err) {
-    extern __shared__ __align__(128) unsigned char smem_raw[]; // two 32 KiB tile buffers, then two mbarriers
-    u64(*sm)[4096] = reinterpret_cast<u64(*)[4096]>(smem_raw);
-    TileCtl tc; tc.init(reinterpret_cast<u64 *>(smem_raw + 2 * 4096 * 8));
-    const int tid = threadIdx.x, clo = tid & 15, rl = tid >> 4;
-    int t = blockIdx.x;
-    if (t < ntiles) issue_rows_tile(tc, 0, sm[0], src, sa, map.n, t);
-    for (int it = 0; t < ntiles; t += gridDim.x, ++it) {
-        const int b = it & 1;
-        if (t + (int)gridDim.x < ntiles) issue_rows_tile(tc, b ^ 1, sm[b ^ 1], src, sa, map.n, t + gridDim.x);
-        const int li = t >> 4, pi = map.prime[li % map.n];
-        const PrimeConst m = pc[pi];
-        const ulonglong2 *tab = tb.fwd + (size_t)pi * Ntt16Layout::kEntries;
-        const int row = (t & 15) * 16 + rl;
-        u64 *o = dst + da.off(li, map.n) + (size_t)row * 256 + clo;
-        u64 *smr = sm[b] + rl * 256;
-        tc.wait(b, err);
-        if (m.small) {
-            const DsConst c = ds_const(m);
-            double *smd = reinterpret_cast<double *>(smr);
-            double v[16];
-#pragma unroll
-            for (int e = 0; e < 16; ++e) v[e] = smd[e * 16 + clo];
-            __syncthreads(); // all first-round inputs are in registers before the in-place exchange overwrites them
-            fwd16_ds<1>(v, tab + Ntt16Layout::rowsA(row, 0), c);
-#pragma unroll
-            for (int e = 0; e < 16; ++e) smd[e * 16 + (clo ^ e)] = v[e];
-            __syncthreads();
-#pragma unroll
-            for (int e = 0; e < 16; ++e) v[e] = smd[clo * 16 + (e ^ clo)];
-            fwd16_ds<16>(v, tab + Ntt16Layout::rowsB(row, 0, clo), c);
-            const double shift = 16.0 * c.qd, qinv_up = c.qinv * (1.0 + 0x1p-50);
-#pragma unroll
-            for (int e = 0; e < 16; ++e) smr[clo * 16 + (e ^ clo)] = ds_store(v[e], c, shift, qinv_up); // the words this thread read itself
-        } else {
-            const u64 q = m.q, q2 = q << 1;
-            u64 v[16];
-#pragma unroll
-            for (int e = 0; e < 16; ++e) v[e] = smr[e * 16 + clo];
-            __syncthreads();
-            fwd16_int<1>(v, tab + Ntt16Layout::rowsA(row, 0), q);
-#pragma unroll
-            for (int e = 0; e < 16; ++e) smr[e * 16 + (clo ^ e)] = v[e];
-            __syncthreads();
-#pragma unroll
-            for (int e = 0; e < 16; ++e) v[e] = smr[clo * 16 + (e ^ clo)];
-            fwd16_int<16>(v, tab + Ntt16Layout::rowsB(row, 0, clo), q);
-#pragma unroll
-            for (int e = 0; e < 16; ++e) {
-                u64 x = v[e];
-                x = x >= q2 ? x - q2 : x;
-                smr[clo * 16 + (e ^ clo)] = x >= q ? x - q : x;
-            }
-        }
-        __syncthreads();
-#pragma unroll
-        for (int e = 0; e < 16; ++e) o[e * 16] = store(smr[e * 16 + (clo ^ e)], li, row * 256 + clo + e * 16, m);
-        fence_async_smem();
-        __syncthreads();
-    }
-}
-
-template <int MINB, class Load>
-__global__ void __launch_bounds__(256, MINB) ntt16v3_inv_rows(const u64 *__restrict__ src, LimbAddr16 sa, u64 *__restrict__ dst, LimbAddr16 da,
-                                                           const __grid_constant__ LimbMap map, const PrimeConst *__restrict__ pc, Ntt16Tables tb, Load load, int ntiles, int *err) {
-    extern __shared__ __align__(128) unsigned char smem_raw[]; // two 32 KiB tile buffers, then two mbarriers
-    u64(*sm)[4096] = reinterpret_cast<u64(*)[4096]>(smem_raw);
-    TileCtl tc; tc.init(reinterpret_cast<u64 *>(smem_raw + 2 * 4096 * 8));
-    const int tid = threadIdx.x, clo = tid & 15, rl = tid >> 4;
-    int t = blockIdx.x;
-    if (t < ntiles) issue_rows_tile(tc, 0, sm[0], src, sa, map.n, t);
-    for (int it = 0; t < ntiles; t += gridDim.x, ++it) {
-        const int b = it & 1;
-        if (t + (int)gridDim.x < ntiles) issue_rows_tile(tc, b ^ 1, sm[b ^ 1], src, sa, map.n, t + gridDim.x);
-        const int li = t >> 4, pi = map.prime[li % map.n];
-        const PrimeConst m = pc[pi];
-        const ulonglong2 *tab = tb.inv + (size_t)pi * Ntt16Layout::kEntries;
-        const int row = (t & 15) * 16 + rl;
-        u64 *o = dst + da.off(li, map.n) + (size_t)row * 256 + clo;
-        u64 *smr = sm[b] + rl * 256;
-        tc.wait(b, err);
-        // the tile arrived in natural order; the first round needs 16 consecutive columns per thread: re-lay it out
-        u64 w[16];
-#pragma unroll
-        for (int e = 0; e < 16; ++e) w[e] = load(smr + e * 16 + clo, li, row * 256 + clo + e * 16, m);
-        __syncthreads();
-#pragma unroll
-        for (int e = 0; e < 16; ++e) smr[e * 16 + (clo ^ e)] = w[e];
-        __syncthreads();
-        if (m.small) {
-            const DsConst c = ds_const(m);
-            double *smd = reinterpret_cast<double *>(smr);
-            double v[16];
-#pragma unroll
-            for (int e = 0; e < 16; ++e) v[e] = ds_load(smr[clo * 16 + (e ^ clo)]);
-            inv16_ds<16>(v, tab + Ntt16Layout::rowsB(row, 0, clo), c);
-#pragma unroll
-            for (int e = 0; e < 16; ++e) smd[clo * 16 + (e ^ clo)] = v[e]; // the words this thread read itself
-            __syncthreads();
-#pragma unroll
-            for (int e = 0; e < 16; ++e) v[e] = smd[e * 16 + (clo ^ e)];
-            inv16_ds<1>(v, tab + Ntt16Layout::rowsA(row, 0), c);
-            double *od = reinterpret_cast<double *>(o);
-#pragma unroll
-            for (int e = 0; e < 16; ++e) od[e * 16] = v[e];
-        } else {
-            u64 v[16];
-#pragma unroll
-            for (int e = 0; e < 16; ++e) v[e] = smr[clo * 16 + (e ^ clo)];
-            inv16_int<16>(v, tab + Ntt16Layout::rowsB(row, 0, clo), m.q);
-#pragma unroll
-            for (int e = 0; e < 16; ++e) smr[clo * 16 + (e ^ clo)] = v[e];
-            __syncthreads();
-#pragma unroll
-            for (int e = 0; e < 16; ++e) v[e] = smr[e * 16 + (clo ^ e)];
-            inv16_int<1>(v, tab + Ntt16Layout::rowsA(row, 0), m.q);
-#pragma unroll
-            for (int e = 0; e < 16; ++e) o[e * 16] = v[e];
-        }
-        fence_async_smem();
-        __syncthreads();
-    }
-}
-
-template <int MINB>
-__global__ void __launch_bounds__(256, MINB) ntt16v3_inv_cols(const u64 *__restrict__ src, LimbAddr16 sa, u64 *__restrict__ dst, LimbAddr16 da,
-                                                           const __grid_constant__ LimbMap map, const PrimeConst *__restrict__ pc, Ntt16Tables tb, int ntiles, int *err) {
-    extern __shared__ __align__(128) unsigned char smem_raw[]; // two 32 KiB tile buffers, then two mbarriers
-    u64(*sm)[4096] = reinterpret_cast<u64(*)[4096]>(smem_raw);
-    TileCtl tc; tc.init(reinterpret_cast<u64 *>(smem_raw + 2 * 4096 * 8));
-    const int tid = threadIdx.x, lane = tid & 15, sub = tid >> 4;
-    int t = blockIdx.x;
-    if (t < ntiles) issue_cols_tile(tc, 0, sm[0], src, sa, map.n, t);
-    for (int it = 0; t < ntiles; t += gridDim.x, ++it) {
-        const int b = it & 1;
-        if (t + (int)gridDim.x < ntiles) issue_cols_tile(tc, b ^ 1, sm[b ^ 1], src, sa, map.n, t + gridDim.x);
-        const int li = t >> 4, pi = map.prime[li % map.n];
-        const PrimeConst m = pc[pi];
-        const ulonglong2 *tab = tb.inv + (size_t)pi * Ntt16Layout::kEntries;
-        u64 *o = dst + da.off(li, map.n) + (t & 15) * 16 + lane;
-        u64 *buf = sm[b];
-        tc.wait(b, err);
-        if (m.small) {
-            const DsConst c = ds_const(m);
-            double *smd = reinterpret_cast<double *>(buf);
-            double v[16];
-#pragma unroll
-            for (int e = 0; e < 16; ++e) v[e] = smd[(sub * 16 + e) * 16 + lane];
-            inv16_ds<1>(v, tab + Ntt16Layout::colsB(sub, 0), c);
-#pragma unroll
-            for (int e = 0; e < 16; ++e) smd[(sub * 16 + e) * 16 + lane] = v[e];
-            __syncthreads();
-#pragma unroll
-            for (int e = 0; e < 16; ++e) v[e] = smd[(e * 16 + sub) * 16 + lane];
-            inv16_ds<1>(v, tab + Ntt16Layout::colsA(0), c);
-            const double qinv_up = c.qinv * (1.0 + 0x1p-50);
-#pragma unroll
-            for (int e = 0; e < 16; ++e) {
-                const double x = ds_mul(v[e], m.n_inv, m.n_inv_f, c); // x * N^-1 in (-0.52 q, 0.52 q)
-                o[(e * 16 + sub) * 256] = ds_store(x, c, c.qd, qinv_up);
-            }
-        } else {
-            u64 v[16];
-#pragma unroll
-            for (int e = 0; e < 16; ++e) v[e] = buf[(sub * 16 + e) * 16 + lane];
-            inv16_int<1>(v, tab + Ntt16Layout::colsB(sub, 0), m.q);
-#pragma unroll
-            for (int e = 0; e < 16; ++e) buf[(sub * 16 + e) * 16 + lane] = v[e];
-            __syncthreads();
-#pragma unroll
-            for (int e = 0; e < 16; ++e) v[e] = buf[(e * 16 + sub) * 16 + lane];
-            inv16_int<1>(v, tab + Ntt16Layout::colsA(0), m.q);
-#pragma unroll
-            for (int e = 0; e < 16; ++e) o[(e * 16 + sub) * 256] = mul_shoup(v[e], m.n_inv, m.n_inv_sh, m.q);
-        }
-        fence_async_smem();
-        __syncthreads();
-    }
-}
-
-constexpr size_t kNtt16v3Smem = 2 * 4096 * 8 + 16;
-template <class K> inline cudaError_t ntt16v3_prepare(K kernel) { return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kNtt16v3Smem); }
-// persistent launch: `ctas` CTAs (at most one per tile) walk over the 16 * count tiles
-template <int MINB = 3>
-inline cudaError_t launch_ntt16_persistent(cudaStream_t st, const u64 *src, size_t src_outer, u64 *dst, size_t dst_outer, int count, const LimbMap &map,
-                                           const PrimeConst *pc, const Ntt16Tables &tb, bool inverse, int ctas, int *err) {
-    if (count == 0) return cudaSuccess;
-    static bool prepared = false; // the opt-in to more than 48 KiB of shared memory is per kernel and per process
-    if (!prepared) {
-        cudaError_t e = ntt16v3_prepare(ntt16v3_fwd_cols<MINB>);
-        if (e == cudaSuccess) e = ntt16v3_prepare(ntt16v3_fwd_rows<MINB, StorePlain>);
-        if (e == cudaSuccess) e = ntt16v3_prepare(ntt16v3_inv_rows<MINB, LoadPlain>);
-        if (e == cudaSuccess) e = ntt16v3_prepare(ntt16v3_inv_cols<MINB>);
-        if (e != cudaSuccess) return e;
-        prepared = true;
-    }
-    LimbAddr16 sa{src_outer}, da{dst_outer};
-    const int ntiles = 16 * count;
-    const int grid = ctas < ntiles ? ctas : ntiles;
-    if (!inverse) {
-        ntt16v3_fwd_cols<MINB><<<grid, 256, kNtt16v3Smem, st>>>(src, sa, dst, da, map, pc, tb, ntiles, err);
-        ntt16v3_fwd_rows<MINB, StorePlain><<<grid, 256, kNtt16v3Smem, st>>>(dst, da, dst, da, map, pc, tb, StorePlain{}, ntiles, err);
-    } else {
-        ntt16v3_inv_rows<MINB, LoadPlain><<<grid, 256, kNtt16v3Smem, st>>>(src, sa, dst, da, map, pc, tb, LoadPlain{}, ntiles, err);
-        ntt16v3_inv_cols<MINB><<<grid, 256, kNtt16v3Smem, st>>>(dst, da, dst, da, map, pc, tb, ntiles, err);
-    }
-    return cudaGetLastError();
-}
-
 // Launch a batched transform of `count` limb instances of 2^16 coefficients.  src == dst gives an in-place transform;
 // with distinct buffers `dst` also serves as the intermediate between the two passes.  MINB = CTAs per SM the kernels
-// are compiled for (register budget 65536 / (256 * MINB)).
-template <int MINB = 4>
+// are compiled for (register budget 65536 / (256 * MINB)); two measured fastest (the compiler then has the registers
+// to fetch the twiddles of a round ahead of the butterflies that use them).
+template <int MINB = 2>
 inline cudaError_t launch_ntt16(cudaStream_t st, const u64 *src, size_t src_outer, u64 *dst, size_t dst_outer, int count, const LimbMap &map,
                                 const PrimeConst *pc, const Ntt16Tables &tb, bool inverse) {
     if (count == 0) return cudaSuccess;
