@@ -206,6 +206,30 @@ class Lib:
         self._chk(self._fn("pt_export")(self.ctx, pt.ptr, out.ctypes.data_as(c_u64p)))
         return out
 
+    # ---- files (the library's own container; see include/hemmer_b200.h) ----
+    def ct_save(self, ct, path):
+        self._chk(self._fn("ct_save")(self.ctx, ct.ptr, str(path).encode()))
+
+    def ct_load(self, path):
+        out = C.c_void_p()
+        self._chk(self._fn("ct_load")(self.ctx, str(path).encode(), C.byref(out)))
+        return Handle(self, out, "ct")
+
+    def pt_save(self, pt, path):
+        self._chk(self._fn("pt_save")(self.ctx, pt.ptr, str(path).encode()))
+
+    def pt_load(self, path):
+        out = C.c_void_p()
+        self._chk(self._fn("pt_load")(self.ctx, str(path).encode(), C.byref(out)))
+        return Handle(self, out, "pt")
+
+    def keys_save(self, directory):
+        self._chk(self._fn("keys_save")(self.ctx, str(directory).encode()))
+
+    def keys_load(self, directory, galois=()):
+        g = (C.c_uint64 * max(1, len(galois)))(*[int(x) for x in galois])
+        self._chk(self._fn("keys_load")(self.ctx, str(directory).encode(), g, C.c_int(len(galois))))
+
     def batch_set(self, dst, idx, src):
         self._chk(self._fn("batch_set")(self.ctx, dst.ptr, C.c_int(idx), src.ptr))
 

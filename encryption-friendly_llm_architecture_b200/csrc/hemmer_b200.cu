@@ -281,6 +281,19 @@ void ks_decompose(hb_ctx *c, const u64 *a, size_t a_outer, int level, int batch,
     LAUNCH(c), k_modup<<<dim3(gx1, d.nd, batch), 256, 0, c->st>>>(dt, acoef.p, pl, c->pc, N);
     ntt_inplace(c, dt, batch * d.dt_count, d.dtmap, false);
 }
+// ModDown of acc [batch*2][ne][N] into out: conversion of the special limbs, forward transform, final combination
+void moddown(hb_ctx *c, const u64 *acc, u64 *pco, u64 *tbuf, int level, int batch, u64 *out, size_t out_outer, const u64 *add0, const u64 *add1, size_t add_outer, u32 g) {
+    const KsPlan *pl = get_plan(c, level);
+    const PlanDims d = plan_dims(c, level);
+    const int N = c->N, n = d.n, ne = d.ne, K = d.K;
+    const unsigned gx1 = (unsigned)((N + 255) / 256), gx = c->gx();
+    LimbMap pm{}; pm.n = K; for (int k = 0; k < K; ++k) pm.prime[k] = (unsigned char)(c->L + 1 + k);
+    ntt(c, acc + (size_t)n * N, (size_t)ne * N, pco, (size_t)K * N, batch * 2 * K, pm, true);
+    LAUNCH(c), k_moddown_conv<<<dim3(gx1, 1, batch * 2), 256, 0, c->st>>>(tbuf, pco, pl, c->pc, c->L + 1, N);
+    ntt_inplace(c, tbuf, batch * 2 * n, c->qmap(level), false);
+    LAUNCH(c), k_moddown_fin<<<dim3(gx, n, batch * 2), 256, 0, c->st>>>(out, out_outer, acc, tbuf, add0, add1, add_outer, pl, c->pc, g, c->logn, N);
+    CK(cudaGetLastError());
+}
 // Phase 2: inner product of the (permuted) digits with the key over Q_level u P, then ModDown:
 //   out[b][p][l] = ModDown(sum_dg perm_g(digit_dg) (.) key_dg)[p][l] + add_p[b][l] o perm_g
 void ks_apply(hb_ctx *c, const u64 *a, size_t a_outer, const u64 *dt, int level, int batch, const Evk &key, u32 g, u64 *out, size_t out_outer, const u64 *add0,
@@ -288,15 +301,10 @@ void ks_apply(hb_ctx *c, const u64 *a, size_t a_outer, const u64 *dt, int level,
     const KsPlan *pl = get_plan(c, level);
     const PlanDims d = plan_dims(c, level);
     const int N = c->N, n = d.n, ne = d.ne, K = d.K;
-    const unsigned gx1 = (unsigned)((N + 255) / 256), gx = c->gx();
+    const unsigned gx = c->gx();
     Tmp acc(c, (size_t)batch * 2 * ne), pco(c, (size_t)batch * 2 * K), t(c, (size_t)batch * 2 * n);
     LAUNCH(c), k_ks_inner<<<dim3(gx, batch, ne), 256, 0, c->st>>>(acc.p, a, a_outer, dt, key.d, c->nprimes, pl, c->pc, g, c->logn, N);
-    LimbMap pm{}; pm.n = K; for (int k = 0; k < K; ++k) pm.prime[k] = (unsigned char)(c->L + 1 + k);
-    ntt(c, acc.p + (size_t)n * N, (size_t)ne * N, pco.p, (size_t)K * N, batch * 2 * K, pm, true);
-    LAUNCH(c), k_moddown_conv<<<dim3(gx1, 1, batch * 2), 256, 0, c->st>>>(t.p, pco.p, pl, c->pc, c->L + 1, N);
-    ntt_inplace(c, t.p, batch * 2 * n, c->qmap(level), false);
-    LAUNCH(c), k_moddown_fin<<<dim3(gx, n, batch * 2), 256, 0, c->st>>>(out, out_outer, acc.p, t.p, add0, add1, add_outer, pl, c->pc, g, c->logn, N);
-    CK(cudaGetLastError());
+    moddown(c, acc.p, pco.p, t.p, level, batch, out, out_outer, add0, add1, add_outer, g);
 }
 // Hybrid key switch of polynomial a (NTT form, `n` limbs, per-batch stride a_outer) with key `key`
 void keyswitch(hb_ctx *c, const u64 *a, size_t a_outer, int level, int batch, const Evk &key, u32 g, u64 *out, size_t out_outer, const u64 *add0, const u64 *add1,
@@ -1294,7 +1302,7 @@ int hb_rotate_sum(hb_ctx *c, const hb_ct *const *xs, const int64_t *steps, int c
                 ks_decompose(c, xs[t]->d + (size_t)n * N, ct_outer, level, batch, dt);
                 rot.t[rot.count++] = RotTerm{xs[t]->d + (size_t)n * N, dt, key.d, (u32)g, 0u};
             }
-            const unsigned gx1 = (unsigned)((N + 255) / 256), gx = c->gx();
+            const unsigned gx = c->gx();
             ALG(c, (size_t)(count + 1) * batch * 2 * n + (size_t)rot.count * key_limbs(c, level));
             Tmp add(c, (size_t)batch * 2 * n);
             LAUNCH(c), k_rot_sum_addend<<<dim3(gx, n, batch * 2), 256, 0, c->st>>>(add.p, rot, plain, n, c->qmap(level), c->pc, c->logn, N);
@@ -1303,11 +1311,7 @@ int hb_rotate_sum(hb_ctx *c, const hb_ct *const *xs, const int64_t *steps, int c
             } else {
                 Tmp acc(c, (size_t)batch * 2 * ne), pco(c, (size_t)batch * 2 * K), t(c, (size_t)batch * 2 * n);
                 LAUNCH(c), k_ks_inner_sum<<<dim3(gx, batch, ne), 256, 0, c->st>>>(acc.p, rot, ct_outer, c->nprimes, pl, c->pc, c->logn, N);
-                LimbMap pm{}; pm.n = K; for (int k = 0; k < K; ++k) pm.prime[k] = (unsigned char)(c->L + 1 + k);
-                ntt(c, acc.p + (size_t)n * N, (size_t)ne * N, pco.p, (size_t)K * N, batch * 2 * K, pm, true);
-                LAUNCH(c), k_moddown_conv<<<dim3(gx1, 1, batch * 2), 256, 0, c->st>>>(t.p, pco.p, pl, c->pc, c->L + 1, N);
-                ntt_inplace(c, t.p, batch * 2 * n, c->qmap(level), false);
-                LAUNCH(c), k_moddown_fin<<<dim3(gx, n, batch * 2), 256, 0, c->st>>>(r->d, ct_outer, acc.p, t.p, add.p, add.p + (size_t)n * N, ct_outer, pl, c->pc, 0u, c->logn, N);
+                moddown(c, acc.p, pco.p, t.p, level, batch, r->d, ct_outer, add.p, add.p + (size_t)n * N, ct_outer, 0u);
             }
             CK(cudaGetLastError());
         } catch (...) { for (u64 *p : dts) c->pool.put(p); hb_ct_free(r); throw; }

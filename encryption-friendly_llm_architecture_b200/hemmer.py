@@ -102,26 +102,69 @@ class Hemmer:
         self._nonce += 1
         return self._nonce
 
+    def _native(self, name):
+        """The library's own entry point for a HEMMer method that takes host matrices, when it has one (the CUDA library's
+        C++ layer does; a library that only exports the tile schedules gets the layout done here)."""
+        return getattr(self.dll, self.prefix + name, None)
+
+    @staticmethod
+    def _mat(m):
+        a = np.ascontiguousarray(m, dtype=np.float64)
+        return a, a.ctypes.data_as(C.POINTER(C.c_double))
+
+    def _native_out(self, fn, kind, *args):
+        out = C.c_void_p()
+        rc = fn(self.h, *args, C.byref(out))
+        if rc != 0:
+            f = self._fn("last_error")
+            f.restype = C.c_char_p
+            raise HBError(rc, f().decode())
+        return Handle(self.lib, out, kind)
+
     def encode(self, data, level=0):
-        level = level or self.lib.L
-        return PtxtTensor(self.lib.encode(layout1(data, self.lib.slots), level), data.shape[0], data.shape[1])
+        fn = self._native("encode")
+        if fn is None:
+            level = level or self.lib.L
+            return PtxtTensor(self.lib.encode(layout1(data, self.lib.slots), level), data.shape[0], data.shape[1])
+        a, pa = self._mat(data)
+        return PtxtTensor(self._native_out(fn, "pt", pa, C.c_int(a.shape[0]), C.c_int(a.shape[1]), C.c_int(level)), a.shape[0], a.shape[1])
 
     def encode2(self, d1, d2, level=0):
-        level = level or self.lib.L
-        return PtxtTensor(self.lib.encode(layout2(d1, d2, self.lib.slots), level), d1.shape[0], d1.shape[1], 2 * d1.shape[1])
+        fn = self._native("encode2")
+        if fn is None:
+            level = level or self.lib.L
+            return PtxtTensor(self.lib.encode(layout2(d1, d2, self.lib.slots), level), d1.shape[0], d1.shape[1], 2 * d1.shape[1])
+        (a, pa), (b, pb) = self._mat(d1), self._mat(d2)
+        return PtxtTensor(self._native_out(fn, "pt", pa, pb, C.c_int(a.shape[0]), C.c_int(a.shape[1]), C.c_int(level)), a.shape[0], a.shape[1], 2 * a.shape[1])
 
     def encode_diagonal_to_row4(self, w1, w2, w3, w4, level=0):
-        level = level or self.lib.L
-        return PtxtTensor(self.lib.encode(layout_diag_to_row4(w1, w2, w3, w4, self.lib.slots), level),
-                          w1.shape[0], w1.shape[1], 2 * w1.shape[1])
+        fn = self._native("encode_diagonal_to_row4")
+        if fn is None:
+            level = level or self.lib.L
+            return PtxtTensor(self.lib.encode(layout_diag_to_row4(w1, w2, w3, w4, self.lib.slots), level),
+                              w1.shape[0], w1.shape[1], 2 * w1.shape[1])
+        ms = [self._mat(w) for w in (w1, w2, w3, w4)]
+        a = ms[0][0]
+        return PtxtTensor(self._native_out(fn, "pt", *[p for _, p in ms], C.c_int(a.shape[0]), C.c_int(a.shape[1]), C.c_int(level)),
+                          a.shape[0], a.shape[1], 2 * a.shape[1])
 
     def encrypt(self, data, nonce=None):
-        pt = self.encode(data)
-        return CtxtTensor(self.lib.encrypt(pt.ct, self.next_nonce() if nonce is None else nonce), pt.rows, pt.cols, pt.width)
+        nonce = self.next_nonce() if nonce is None else nonce
+        fn = self._native("encrypt")
+        if fn is None:
+            pt = self.encode(data)
+            return CtxtTensor(self.lib.encrypt(pt.ct, nonce), pt.rows, pt.cols, pt.width)
+        a, pa = self._mat(data)
+        return CtxtTensor(self._native_out(fn, "ct", pa, C.c_int(a.shape[0]), C.c_int(a.shape[1]), C.c_uint64(nonce)), a.shape[0], a.shape[1])
 
     def encrypt2(self, d1, d2, nonce=None):
-        pt = self.encode2(d1, d2)
-        return CtxtTensor(self.lib.encrypt(pt.ct, self.next_nonce() if nonce is None else nonce), pt.rows, pt.cols, pt.width)
+        nonce = self.next_nonce() if nonce is None else nonce
+        fn = self._native("encrypt2")
+        if fn is None:
+            pt = self.encode2(d1, d2)
+            return CtxtTensor(self.lib.encrypt(pt.ct, nonce), pt.rows, pt.cols, pt.width)
+        (a, pa), (b, pb) = self._mat(d1), self._mat(d2)
+        return CtxtTensor(self._native_out(fn, "ct", pa, pb, C.c_int(a.shape[0]), C.c_int(a.shape[1]), C.c_uint64(nonce)), a.shape[0], a.shape[1], 2 * a.shape[1])
 
     def encrypt2_many(self, pairs, nonces):
         """encrypt2 for a list of (left, right) tile pairs: one batched CtxtTensor, member i = encrypt2(*pairs[i], nonces[i])."""
@@ -130,12 +173,31 @@ class Hemmer:
         return CtxtTensor(self.lib.encrypt_many(msgs, self.lib.L, nonces), d[0], d[1], 2 * d[1])
 
     def decrypt(self, t):
-        z = self.lib.decrypt(t.ct)
-        return z[: t.rows * t.cols].real.reshape(t.rows, t.cols)
+        fn = self._native("decrypt")
+        if fn is None:
+            z = self.lib.decrypt(t.ct)
+            return z[: t.rows * t.cols].real.reshape(t.rows, t.cols)
+        out = np.zeros((t.rows, t.cols))
+        self.lib._chk(fn(self.h, t.ct.ptr, *self._shp(t), out.ctypes.data_as(C.POINTER(C.c_double))))
+        return out
 
     def decrypt2(self, t):
-        z = self.lib.decrypt(t.ct)[: t.rows * 2 * t.cols].real.reshape(t.rows, 2 * t.cols)
-        return np.stack([z[:, : t.cols], z[:, t.cols:]])
+        fn = self._native("decrypt2")
+        if fn is None:
+            z = self.lib.decrypt(t.ct)[: t.rows * 2 * t.cols].real.reshape(t.rows, 2 * t.cols)
+            return np.stack([z[:, : t.cols], z[:, t.cols:]])
+        out = np.zeros((2, t.rows, t.cols))
+        self.lib._chk(fn(self.h, t.ct.ptr, *self._shp(t), out.ctypes.data_as(C.POINTER(C.c_double))))
+        return out
+
+    def hadamard_mult_inplace(self, a, b):
+        """HEMMer::hadamardMultInplace: slot-wise product with a ciphertext tensor or a plaintext tensor."""
+        name = "hadamard_mult_pt" if isinstance(b, PtxtTensor) else "hadamard_mult"
+        a.ct = self._call(name, a.ct.ptr, b.ct.ptr)
+
+    def one_mat_rot_sum_inplace(self, a, b):
+        """HEMMer::oneMatRotSumInplace: row sums of the left halves of a's tiles / right halves of b's, spread over the rows."""
+        a.ct, b.ct = self._call("one_mat_rot_sum", a.ct.ptr, b.ct.ptr, n_out=2)
 
     # ---- matmul family ----
     def add_inplace(self, a, b):

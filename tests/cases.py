@@ -324,7 +324,30 @@ def sc_repack_lora_opti(lib, H, target=2):
     return [lib.ct_export(rp.ct)], np.abs(lib.decrypt(rp.ct) - want).max()
 
 
+def sc_rot_sum_hadamard(lib, H, target=0):
+    """oneMatRotSumInplace (HEMMer.cpp:882-919) and hadamardMultInplace with a ciphertext and with a plaintext operand."""
+    d = tile_dim(lib)
+    A, A2, B, B2 = _mats(130, d, 4)
+    a, b = H.encrypt2(A, A2, nonce=90), H.encrypt2(B, B2, nonce=91)
+    H.one_mat_rot_sum_inplace(a, b)
+    Da, Db = H.decrypt2(a), H.decrypt2(b)
+    half = d // 2
+    bc = lambda M: np.repeat(M.sum(axis=1, keepdims=True), d, axis=1)
+    err = max(np.abs(Da[0] - bc(A[:, :half])).max(), np.abs(Da[1] - bc(A2[:, :half])).max(),
+              np.abs(Db[0] - bc(B[:, half:])).max(), np.abs(Db[1] - bc(B2[:, half:])).max())
+    x, y = H.encrypt2(A, A2, nonce=92), H.encrypt2(B, B2, nonce=93)
+    H.hadamard_mult_inplace(x, y)
+    Dx = H.decrypt2(x)
+    err = max(err, np.abs(Dx[0] - A * B).max(), np.abs(Dx[1] - A2 * B2).max())
+    z = H.encrypt2(A, A2, nonce=94)
+    H.hadamard_mult_inplace(z, H.encode2(B, B2))
+    Dz = H.decrypt2(z)
+    err = max(err, np.abs(Dz[0] - A * B).max(), np.abs(Dz[1] - A2 * B2).max())
+    return [lib.ct_export(t.ct) for t in (a, b, x, z)], err
+
+
 SCENARIOS = {
+    "rot_sum_hadamard": sc_rot_sum_hadamard,
     "repack_lora_opti": sc_repack_lora_opti,
     "lora_forward": sc_lora_forward,
     "lora_backward": sc_lora_backward,
