@@ -7,6 +7,7 @@
 
 #include <map>
 #include <tuple>
+#include <vector>
 
 namespace HELLM {
 
@@ -96,6 +97,16 @@ class HEMMer {
     // HEMMer::oneMatRotSumInplace (HEMMer.cpp:882-919): row sums of the left half of a's tiles and of the right half of
     // b's tiles, spread over every column -- the norm terms of the Gaussian-kernel attention scores
     void oneMatRotSumInplace(CtxtTensor &a, CtxtTensor &b);
+    // The rank-2 LoRA branch of a projection as the reference's layer runs it (TransformerBlock::attention2_bert_loraOpti,
+    // TransformerBlock.cpp:2199-2365, without the bootstraps around it): the two rank vectors are picked row by row
+    // out of the factor ciphertexts, spread over all token rows by rotations, multiplied slot-wise with the three
+    // activation pairs and summed across the row (X A), then spread across the row again and multiplied with the
+    // rows of the second factor ((X A) B).  cur: three [X_2i | X_2i+1] pairs; wa / wb: row 2i+j of the two-tile
+    // ciphertext holds rank vector j for pair i.  Returns the three output pairs.
+    std::vector<CtxtTensor> loraOptiForward(const std::vector<CtxtTensor> &cur, const CtxtTensor &lora_wa, const CtxtTensor &lora_wb);
+    // HEMMer::maskFirstRowInplace / maskFirstColOnlyInplace (HEMMer.cpp:1255-1261)
+    void maskFirstRowInplace(CtxtTensor &t);
+    void maskFirstColOnlyInplace(CtxtTensor &t);
     // HEMMer::getRank / getMaxRank (HEMMer.hpp:56-57): this process's GPU among the GPUs of the job
     int getRank() const { return rank_; }
     int getMaxRank() const { return max_rank_; }

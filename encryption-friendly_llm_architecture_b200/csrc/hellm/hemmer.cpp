@@ -6,7 +6,7 @@
 namespace HELLM {
 
 namespace {
-enum HemmerMask { kColEven = 1, kRowEven = 2, kLeftHalf = 3, kLeftHalfScaled = 4, kFirstCol = 5, kLastCol = 6 };
+enum HemmerMask { kColEven = 1, kRowEven = 2, kLeftHalf = 3, kLeftHalfScaled = 4, kFirstCol = 5, kLastCol = 6, kFirstRow = 7, kFirstColOnly = 8 };
 }
 
 HEMMer::HEMMer(hb_ctx *ctx) : ctx_(ctx), eval_(ctx) {
@@ -137,7 +137,8 @@ static const Plaintext &hemmer_mask(HEMMer &h, int which, int level) {
     Message m((size_t)h.slots());
     for (i64 r = 0; r < d; ++r)
         for (i64 c = 0; c < 2 * d; ++c) {
-            bool on = which == kColEven ? ((c % d) % 2 == 0) : which == kRowEven ? (r % 2 == 0) : which == kFirstCol ? (c % d == 0) : which == kLastCol ? (c % d == d - 1) : (c < d);
+            bool on = which == kColEven ? ((c % d) % 2 == 0) : which == kRowEven ? (r % 2 == 0) : which == kFirstCol ? (c % d == 0) : which == kLastCol ? (c % d == d - 1) :
+                      which == kFirstRow ? (r == 0) : which == kFirstColOnly ? (c == 0) : (c < d);
             if (on) m.re[(size_t)(r * 2 * d + c)] = which == kLeftHalfScaled ? 0.5 : 1.0;
         }
     return h.masks().put(k, h.eval().encode(m, level));
@@ -173,6 +174,47 @@ void HEMMer::oneMatRotSumInplace(CtxtTensor &a, CtxtTensor &b) {
         a.get() = eval_.add(a.get(), eval_.rightRotate(a.get(), rot));
         b.get() = eval_.add(b.get(), eval_.leftRotate(b.get(), rot));
     }
+}
+// HEMMer::maskFirstRowInplace / maskFirstColOnlyInplace -- HEMMer.cpp:1255-1261, masks :2384-2388, :2418
+void HEMMer::maskFirstRowInplace(CtxtTensor &t) { t.get() = eval_.mult(t.get(), hemmer_mask(*this, kFirstRow, t.getLevel())); }
+void HEMMer::maskFirstColOnlyInplace(CtxtTensor &t) { t.get() = eval_.mult(t.get(), hemmer_mask(*this, kFirstColOnly, t.getLevel())); }
+// the rank-2 LoRA branch of TransformerBlock::attention2_bert_loraOpti -- TransformerBlock.cpp:2199-2365
+std::vector<CtxtTensor> HEMMer::loraOptiForward(const std::vector<CtxtTensor> &cur, const CtxtTensor &lora_wa, const CtxtTensor &lora_wb) {
+    if (cur.size() != 3) throw std::invalid_argument("[loraOptiForward] three activation pairs expected");
+    const i64 d = tile_, w = 2 * tile_;
+    // rows 2i and 2i+1 of a factor ciphertext, each moved to row 0, masked and spread over all d rows
+    auto rank_rows = [&](const CtxtTensor &factor) {
+        std::vector<std::vector<CtxtTensor>> rows;
+        for (i64 i = 0; i < 3; ++i) {
+            CtxtTensor base = i == 0 ? factor : CtxtTensor(factor.getShape(), eval_.leftRotate(factor.get(), i * 2 * w));
+            std::vector<CtxtTensor> pair{base, CtxtTensor(base.getShape(), eval_.leftRotate(base.get(), w))};
+            for (auto &t : pair) {
+                maskFirstRowInplace(t);
+                for (i64 rot = 1; rot < d; rot <<= 1) t.get() = eval_.add(t.get(), eval_.rightRotate(t.get(), rot * w));
+            }
+            rows.push_back(std::move(pair));
+        }
+        return rows;
+    };
+    // X A: slot-wise products summed over the three pairs, then across the 2 d columns of a row into column 0
+    const auto wa = rank_rows(lora_wa);
+    std::vector<CtxtTensor> xa;
+    for (int j = 0; j < 2; ++j) {
+        Ciphertext acc = eval_.mult(cur[0].get(), wa[0][(size_t)j].get());
+        for (size_t i = 1; i < 3; ++i) acc = eval_.add(acc, eval_.mult(cur[i].get(), wa[i][(size_t)j].get()));
+        for (i64 rot = 1; rot < w; rot <<= 1) acc = eval_.add(acc, eval_.leftRotate(acc, rot));
+        CtxtTensor t(cur[0].getShape(), std::move(acc));
+        maskFirstColOnlyInplace(t);
+        xa.push_back(std::move(t));
+    }
+    // (X A) B: column 0 spread over the row, times the rows of the second factor
+    const auto wb = rank_rows(lora_wb);
+    for (auto &t : xa)
+        for (i64 rot = 1; rot < w; rot <<= 1) t.get() = eval_.add(t.get(), eval_.rightRotate(t.get(), rot));
+    std::vector<CtxtTensor> out;
+    for (size_t i = 0; i < 3; ++i)
+        out.emplace_back(cur[0].getShape(), eval_.add(eval_.mult(xa[0].get(), wb[i][0].get()), eval_.mult(xa[1].get(), wb[i][1].get())));
+    return out;
 }
 // HEMMer::splitInTwo -- HEMMer.cpp:819-831
 void HEMMer::splitInTwo(const CtxtTensor &t, CtxtTensor &t1, CtxtTensor &t2) {

@@ -109,6 +109,18 @@ int hb_hemmer_one_mat_rot_sum(hb_hemmer *h, const hb_ct *a, const hb_ct *b, hb_c
     });
 }
 
+int hb_hemmer_lora_opti_forward(hb_hemmer *h, const hb_ct *cur0, const hb_ct *cur1, const hb_ct *cur2, const hb_ct *lora_wa, const hb_ct *lora_wb, hb_ct **out0,
+                                hb_ct **out1, hb_ct **out2) {
+    return guard([&] {
+        Borrow b0(h->ctx, cur0), b1(h->ctx, cur1), b2(h->ctx, cur2), ba(h->ctx, lora_wa), bb(h->ctx, lora_wb);
+        const i64 d = h->h.tile();
+        const TileTensorShape s(d, d, 2 * d);
+        std::vector<CtxtTensor> cur{CtxtTensor(s, Ciphertext(b0.c)), CtxtTensor(s, Ciphertext(b1.c)), CtxtTensor(s, Ciphertext(b2.c))};
+        std::vector<CtxtTensor> r = h->h.loraOptiForward(cur, CtxtTensor(s, Ciphertext(ba.c)), CtxtTensor(s, Ciphertext(bb.c)));
+        *out0 = r[0].get().release(); *out1 = r[1].get().release(); *out2 = r[2].get().release();
+    });
+}
+
 #define SHAPE_ARGS int rows, int cols, int width
 #define IN_TENSOR(name, p) Borrow name##_b(h->ctx, p); CtxtTensor name(TileTensorShape(rows, cols, width), Ciphertext(name##_b.c))
 

@@ -195,6 +195,12 @@ class Hemmer:
         name = "hadamard_mult_pt" if isinstance(b, PtxtTensor) else "hadamard_mult"
         a.ct = self._call(name, a.ct.ptr, b.ct.ptr)
 
+    def lora_opti_forward(self, cur, lora_wa, lora_wb):
+        """The rank-2 LoRA branch of TransformerBlock::attention2_bert_loraOpti (TransformerBlock.cpp:2199-2365): three
+        activation pairs and the two factor ciphertexts in, the three pairs of X A B out."""
+        outs = self._call("lora_opti_forward", cur[0].ct.ptr, cur[1].ct.ptr, cur[2].ct.ptr, lora_wa.ct.ptr, lora_wb.ct.ptr, n_out=3)
+        return [CtxtTensor(o, *cur[0].shape) for o in outs]
+
     def one_mat_rot_sum_inplace(self, a, b):
         """HEMMer::oneMatRotSumInplace: row sums of the left halves of a's tiles / right halves of b's, spread over the rows."""
         a.ct, b.ct = self._call("one_mat_rot_sum", a.ct.ptr, b.ct.ptr, n_out=2)

@@ -75,6 +75,14 @@ int hb_hemmer_hadamard_mult_pt(hb_hemmer *h, const hb_ct *a, const hb_pt *p, hb_
 /* HEMMer::oneMatRotSumInplace (HEMMer.hpp:168; HEMMer.cpp:882-919) on two-tile ciphertexts */
 int hb_hemmer_one_mat_rot_sum(hb_hemmer *h, const hb_ct *a, const hb_ct *b, hb_ct **out_a, hb_ct **out_b);
 
+/* The rank-2 LoRA branch of a projection in the reference's layer, TransformerBlock::attention2_bert_loraOpti
+ * (TransformerBlock.cpp:2199-2365) without the bootstraps around it: X A by slot-wise products with the rank vectors
+ * spread over the token rows and a rotate-and-add across each row, then (X A) B the same way.  cur0..2: the three
+ * [X_2i | X_2i+1] activation pairs; lora_wa / lora_wb: two-tile ciphertexts whose row 2i+j holds rank vector j for
+ * pair i.  out0..2: the three output pairs. */
+int hb_hemmer_lora_opti_forward(hb_hemmer *h, const hb_ct *cur0, const hb_ct *cur1, const hb_ct *cur2, const hb_ct *lora_wa, const hb_ct *lora_wb,
+                                hb_ct **out0, hb_ct **out1, hb_ct **out2);
+
 /* HEMMer::transposeInplace (HEMMer.hpp:129; HEMMer.cpp:1166-1172; MatrixUtils.cpp:671-739) */
 int hb_hemmer_transpose(hb_hemmer *h, const hb_ct *a, int rows, int cols, int width, int target_level, hb_ct **out);
 /* MatrixTransformer::diagonalToColumn / diagonalToRow (MatrixUtils.cpp:776-848, 924-996) */

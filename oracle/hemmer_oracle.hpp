@@ -816,6 +816,42 @@ struct Hemmer {
             b.ct = ev.add(b.ct, rotL(b.ct, rot));
         }
     }
+    // the rank-2 LoRA branch of attention2_bert_loraOpti -- TransformerBlock.cpp:2199-2365 (without the bootstraps)
+    std::vector<Ct> lora_opti_forward(const std::vector<Ct> &cur, const Ct &lora_wa, const Ct &lora_wb) {
+        const i64 d = tile, w = 2 * tile;
+        Mask first_row, first_col_only;
+        first_row.msg.assign((size_t)slots, cplx(0, 0));
+        first_col_only.msg.assign((size_t)slots, cplx(0, 0));
+        for (i64 c = 0; c < w; ++c) first_row.msg[(size_t)c] = 1;
+        for (i64 r = 0; r < d; ++r) first_col_only.msg[(size_t)(r * w)] = 1;
+        auto rank_rows = [&](const Ct &factor) {
+            std::vector<std::vector<Ct>> rows;
+            for (i64 i = 0; i < 3; ++i) {
+                Ct base = i == 0 ? factor : rotL(factor, i * 2 * w);
+                std::vector<Ct> pair{base, rotL(base, w)};
+                for (auto &t : pair) {
+                    t = mult_msg(t, first_row);
+                    for (i64 rot = 1; rot < d; rot <<= 1) t = ev.add(t, rotR(t, rot * w));
+                }
+                rows.push_back(std::move(pair));
+            }
+            return rows;
+        };
+        const auto wa = rank_rows(lora_wa);
+        std::vector<Ct> xa;
+        for (int j = 0; j < 2; ++j) {
+            Ct acc = ev.mul(cur[0], wa[0][(size_t)j]);
+            for (size_t i = 1; i < 3; ++i) acc = ev.add(acc, ev.mul(cur[i], wa[i][(size_t)j]));
+            for (i64 rot = 1; rot < w; rot <<= 1) acc = ev.add(acc, rotL(acc, rot));
+            xa.push_back(mult_msg(acc, first_col_only));
+        }
+        const auto wb = rank_rows(lora_wb);
+        for (auto &t : xa)
+            for (i64 rot = 1; rot < w; rot <<= 1) t = ev.add(t, rotR(t, rot));
+        std::vector<Ct> out;
+        for (size_t i = 0; i < 3; ++i) out.push_back(ev.add(ev.mul(xa[0], wb[i][0]), ev.mul(xa[1], wb[i][1])));
+        return out;
+    }
     // repackCC -- HEMMer.cpp:964-969
     CtT repack_cc(const CtT &t) {
         ev.gen_galois_key(cx.galois_conj());

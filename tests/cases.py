@@ -346,7 +346,30 @@ def sc_rot_sum_hadamard(lib, H, target=0):
     return [lib.ct_export(t.ct) for t in (a, b, x, z)], err
 
 
+def sc_lora_opti(lib, H, target=0):
+    """The rank-2 LoRA branch of the reference's attention layer (TransformerBlock.cpp:2199-2365): X A B by slot-wise
+    products and rotate-and-add, factors packed one rank vector per row."""
+    d = tile_dim(lib)
+    rng = np.random.default_rng(131)
+    X, Wa, Wb = rng.uniform(-1, 1, (d, 6 * d)), rng.normal(0, 0.2, (6 * d, 2)), rng.normal(0, 0.2, (2, 6 * d))
+    cur = _pairs(H, X, d, 95)
+    fa, fb = np.zeros((d, 2 * d)), np.zeros((d, 2 * d))
+    for i in range(3):
+        for j in range(2):
+            fa[2 * i + j] = Wa[2 * d * i:2 * d * (i + 1), j]
+            fb[2 * i + j] = Wb[j, 2 * d * i:2 * d * (i + 1)]
+    wa, wb = H.encrypt2(fa[:, :d].copy(), fa[:, d:].copy(), nonce=98), H.encrypt2(fb[:, :d].copy(), fb[:, d:].copy(), nonce=99)
+    outs = H.lora_opti_forward(cur, wa, wb)
+    want = X @ Wa @ Wb
+    err = 0.0
+    for i, o in enumerate(outs):
+        z = lib.decrypt(o.ct).real.reshape(d, 2 * d)
+        err = max(err, np.abs(z - want[:, 2 * d * i:2 * d * (i + 1)]).max())
+    return [lib.ct_export(o.ct) for o in outs], err
+
+
 SCENARIOS = {
+    "lora_opti": sc_lora_opti,
     "rot_sum_hadamard": sc_rot_sum_hadamard,
     "repack_lora_opti": sc_repack_lora_opti,
     "lora_forward": sc_lora_forward,
