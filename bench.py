@@ -347,6 +347,7 @@ def run_gpu(args):
     # exchange time: one host-launched pass with CUDA events around the K-split exchange (nothing overlaps it: the
     # library runs on one stream, so all of it is exposed)
     comm_ms = 0.0
+    before_exchange = None
     if world > 1:
         evs = []
         def hook(phase):
@@ -355,6 +356,8 @@ def run_gpu(args):
             evs.append(e)
         wl.on_comm = hook
         barrier()
+        e_start = torch.cuda.Event(enable_timing=True)
+        e_start.record(stream)
         wl.step_resident()
         lib.sync()
         wl.on_comm = None
@@ -362,6 +365,12 @@ def run_gpu(args):
         t = torch.tensor([own_comm], device="cuda", dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         comm_ms = float(t.item())
+        # this rank's own work before it meets its peers, and what it consisted of
+        mix = {}
+        for i in wl.mine:
+            k = layer.unit_kind(wl.units[i])
+            mix[k] = mix.get(k, 0) + 1
+        before_exchange = gather({"ms": round(e_start.elapsed_time(evs[0]), 2), "units": mix})
     # the same layer with the reference's own rotation sequence (no hoisting), for comparison
     ms_faithful = None
     faithful_exact = None
@@ -479,7 +488,7 @@ def run_gpu(args):
             "schedule_roofline_ms": alg_bytes / (hbm * 1e6), "algorithmic_bytes_per_step": alg_bytes,
             "comm_ms": comm_ms, "exposed_comm_frac": comm_ms / ms_step if ms_step else None,
             "compute_ms_per_rank": {"min": min(p["ms"] for p in per_rank), "max": max(p["ms"] for p in per_rank), "all": [round(p["ms"], 2) for p in per_rank],
-                                    "units": [p["units"] for p in per_rank]},
+                                    "units": [p["units"] for p in per_rank], "host_launched_before_exchange": before_exchange},
             "roofline": roofline, "cpu_baseline": cpu,
             "e2e": {"value": ms_e2e, "unit": "ms", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "phases_ms_rank0": e2e_phases},
             "gpu_launches": launches, "clocks": clocks}

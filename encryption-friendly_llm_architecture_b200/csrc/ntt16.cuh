@@ -88,29 +88,28 @@ __device__ __forceinline__ void gs_bfly(u64 &x, u64 &y, u64 w, u64 ws, u64 q, u6
     y = mul_shoup_lazy(d, w, ws, q);
 }
 // four Cooley-Tukey stages on 16 register values; twiddle j = (1 << s) - 1 + g of local stage s, group g, at tp[j * STRIDE]
-template <bool GL> __device__ __forceinline__ ulonglong2 tw_load(const ulonglong2 *p) { if (GL) return __ldg(p); return *p; }
-template <int STRIDE, bool GL = true> __device__ __forceinline__ void fwd16_int(u64 (&v)[16], const ulonglong2 *__restrict__ tp, u64 q) {
+template <int STRIDE> __device__ __forceinline__ void fwd16_int(u64 (&v)[16], const ulonglong2 *__restrict__ tp, u64 q) {
     const u64 q2 = q << 1;
 #pragma unroll
     for (int s = 0; s < 4; ++s) {
         const int half = 8 >> s;
 #pragma unroll
         for (int g = 0; g < (1 << s); ++g) {
-            const ulonglong2 tw = tw_load<GL>(tp + ((1 << s) - 1 + g) * STRIDE);
+            const ulonglong2 tw = __ldg(tp + ((1 << s) - 1 + g) * STRIDE);
 #pragma unroll
             for (int j = 0; j < half; ++j) ct_bfly(v[g * 2 * half + j], v[g * 2 * half + j + half], tw.x, tw.y, q, q2);
         }
     }
 }
 // four Gentleman-Sande stages, the mirror image
-template <int STRIDE, bool GL = true> __device__ __forceinline__ void inv16_int(u64 (&v)[16], const ulonglong2 *__restrict__ tp, u64 q) {
+template <int STRIDE> __device__ __forceinline__ void inv16_int(u64 (&v)[16], const ulonglong2 *__restrict__ tp, u64 q) {
     const u64 q2 = q << 1;
 #pragma unroll
     for (int s = 3; s >= 0; --s) {
         const int half = 8 >> s;
 #pragma unroll
         for (int g = 0; g < (1 << s); ++g) {
-            const ulonglong2 tw = tw_load<GL>(tp + ((1 << s) - 1 + g) * STRIDE);
+            const ulonglong2 tw = __ldg(tp + ((1 << s) - 1 + g) * STRIDE);
 #pragma unroll
             for (int j = 0; j < half; ++j) gs_bfly(v[g * 2 * half + j], v[g * 2 * half + j + half], tw.x, tw.y, q, q2);
         }
@@ -152,13 +151,13 @@ __device__ __forceinline__ u64 ds_store(double v, const DsConst &c, double shift
     const double rb = __fma_rn(-k, c.qd, v2 + kTwo52);                   // 2^52 + (v2 - k q), exact
     return (u64)__double_as_longlong(rb) & 0x000FFFFFFFFFFFFFull;
 }
-template <int STRIDE, bool GL = true> __device__ __forceinline__ void fwd16_ds(double (&v)[16], const ulonglong2 *__restrict__ tp, const DsConst &c) {
+template <int STRIDE> __device__ __forceinline__ void fwd16_ds(double (&v)[16], const ulonglong2 *__restrict__ tp, const DsConst &c) {
 #pragma unroll
     for (int s = 0; s < 4; ++s) {
         const int half = 8 >> s;
 #pragma unroll
         for (int g = 0; g < (1 << s); ++g) {
-            const ulonglong2 tw = tw_load<GL>(tp + ((1 << s) - 1 + g) * STRIDE);
+            const ulonglong2 tw = __ldg(tp + ((1 << s) - 1 + g) * STRIDE);
             const double wf = __longlong_as_double((long long)tw.y);
 #pragma unroll
             for (int j = 0; j < half; ++j) {
@@ -173,13 +172,13 @@ template <int STRIDE, bool GL = true> __device__ __forceinline__ void fwd16_ds(d
 // Gentleman-Sande round.  The sum path doubles per stage; only v[0] takes the sum at all four stages (16 x its
 // inputs), v[1] ends below 4.2 q whatever came in, the others lower: the caller reduces v[0] after each round, so
 // every round starts from values below 4.2 q and stays below 68 q.
-template <int STRIDE, bool GL = true> __device__ __forceinline__ void inv16_ds(double (&v)[16], const ulonglong2 *__restrict__ tp, const DsConst &c) {
+template <int STRIDE> __device__ __forceinline__ void inv16_ds(double (&v)[16], const ulonglong2 *__restrict__ tp, const DsConst &c) {
 #pragma unroll
     for (int s = 3; s >= 0; --s) {
         const int half = 8 >> s;
 #pragma unroll
         for (int g = 0; g < (1 << s); ++g) {
-            const ulonglong2 tw = tw_load<GL>(tp + ((1 << s) - 1 + g) * STRIDE);
+            const ulonglong2 tw = __ldg(tp + ((1 << s) - 1 + g) * STRIDE);
             const double wf = __longlong_as_double((long long)tw.y);
 #pragma unroll
             for (int j = 0; j < half; ++j) {
@@ -192,12 +191,6 @@ template <int STRIDE, bool GL = true> __device__ __forceinline__ void inv16_ds(d
     }
     v[0] = ds_reduce(v[0], c);
 }
-
-// Per-limb epilogue of the forward row pass / inverse column pass: what is done with the canonical residue of output
-// coefficient `idx` of limb instance `li` before it is stored.  The plain transform stores it as it is.
-struct StorePlain {
-    __device__ __forceinline__ u64 operator()(u64 r, int /*li*/, int /*idx*/, const PrimeConst & /*m*/) const { return r; }
-};
 
 // ---- forward, column pass: stages 1..8 ----
 template <int MINB>
@@ -242,10 +235,10 @@ __global__ void __launch_bounds__(256, MINB) ntt16v2_fwd_cols(const u64 *__restr
     }
 }
 
-// ---- forward, row pass: stages 9..16; stores canonical residues through `store` ----
-template <int MINB, class Store>
+// ---- forward, row pass: stages 9..16; stores canonical residues ----
+template <int MINB>
 __global__ void __launch_bounds__(256, MINB) ntt16v2_fwd_rows(const u64 *__restrict__ src, LimbAddr16 sa, u64 *__restrict__ dst, LimbAddr16 da,
-                                                        const __grid_constant__ LimbMap map, const PrimeConst *__restrict__ pc, Ntt16Tables tb, Store store) {
+                                                        const __grid_constant__ LimbMap map, const PrimeConst *__restrict__ pc, Ntt16Tables tb) {
     __shared__ u64 sm[16 * kRowStride];
     const int li = blockIdx.y, pi = map.prime[li % map.n];
     const PrimeConst m = pc[pi];
@@ -293,19 +286,13 @@ __global__ void __launch_bounds__(256, MINB) ntt16v2_fwd_rows(const u64 *__restr
     }
     __syncthreads();
 #pragma unroll
-    for (int e = 0; e < 16; ++e) o[e * 16] = store(smr[e * 17 + clo], li, row * 256 + clo + e * 16, m);
+    for (int e = 0; e < 16; ++e) o[e * 16] = smr[e * 17 + clo];
 }
 
-// Per-limb prologue of the inverse row pass: the canonical residue that enters the transform at coefficient `idx`
-// of limb instance `li`.  The plain transform takes the stored value.
-struct LoadPlain {
-    __device__ __forceinline__ u64 operator()(const u64 *p, int /*li*/, int /*idx*/, const PrimeConst & /*m*/) const { return *p; }
-};
-
 // ---- inverse, row pass: undoes stages 16..9 ----
-template <int MINB, class Load>
+template <int MINB>
 __global__ void __launch_bounds__(256, MINB) ntt16v2_inv_rows(const u64 *__restrict__ src, LimbAddr16 sa, u64 *__restrict__ dst, LimbAddr16 da,
-                                                        const __grid_constant__ LimbMap map, const PrimeConst *__restrict__ pc, Ntt16Tables tb, Load load) {
+                                                        const __grid_constant__ LimbMap map, const PrimeConst *__restrict__ pc, Ntt16Tables tb) {
     __shared__ u64 sm[16 * kRowStride];
     const int li = blockIdx.y, pi = map.prime[li % map.n];
     const PrimeConst m = pc[pi];
@@ -316,7 +303,7 @@ __global__ void __launch_bounds__(256, MINB) ntt16v2_inv_rows(const u64 *__restr
     u64 *o = dst + da.off(li, map.n) + (size_t)row * 256 + clo;
     u64 *smr = sm + rl * kRowStride;
 #pragma unroll
-    for (int e = 0; e < 16; ++e) smr[e * 17 + clo] = load(p + e * 16, li, row * 256 + clo + e * 16, m);
+    for (int e = 0; e < 16; ++e) smr[e * 17 + clo] = p[e * 16];
     __syncthreads();
     if (m.small) {
         const DsConst c = ds_const(m);
@@ -409,9 +396,9 @@ inline cudaError_t launch_ntt16(cudaStream_t st, const u64 *src, size_t src_oute
     dim3 grid(16, count);
     if (!inverse) {
         ntt16v2_fwd_cols<MINB><<<grid, 256, 0, st>>>(src, sa, dst, da, map, pc, tb);
-        ntt16v2_fwd_rows<MINB, StorePlain><<<grid, 256, 0, st>>>(dst, da, dst, da, map, pc, tb, StorePlain{});
+        ntt16v2_fwd_rows<MINB><<<grid, 256, 0, st>>>(dst, da, dst, da, map, pc, tb);
     } else {
-        ntt16v2_inv_rows<MINB, LoadPlain><<<grid, 256, 0, st>>>(src, sa, dst, da, map, pc, tb, LoadPlain{});
+        ntt16v2_inv_rows<MINB><<<grid, 256, 0, st>>>(src, sa, dst, da, map, pc, tb);
         ntt16v2_inv_cols<MINB><<<grid, 256, 0, st>>>(dst, da, dst, da, map, pc, tb);
     }
     return cudaGetLastError();

@@ -33,9 +33,9 @@ FFN = 24         # 3072 / 128
 HEADS = 12
 LORA_RANK = 8
 
-# Relative device time of the parts of a unit, from the launch list of one pass on one B200 (the shifted copies of
-# one operand, one sigma / tau / transpose, one fused plaintext accumulate per output tile).  Only the ratios matter.
-COST_COPIES, COST_TRANSFORM, COST_ACC_TILE = 4.8, 2.4, 0.37
+# Device time of one unit of each cost class in milliseconds, fitted to the per-rank times of an 8-GPU pass on B200s
+# (ranks with different mixes of units; batching makes the figures marginal costs, and only their ratios matter).
+UNIT_COST_MS = {"qkv": 18.5, "wo": 11.8, "w1": 20.2, "w2": 12.6, "ccmm": 16.3, "ccmm_t": 19.0}
 
 
 def synthetic(seed: int):
@@ -62,11 +62,13 @@ def tiles(m, r, c):
     return out
 
 
+def unit_kind(u):
+    """Cost class of a unit: the ct x pt sublayer, or ct x ct with / without a transpose."""
+    return u[1] if u[0] == "pcmm" else ("ccmm_t" if u[4] else "ccmm")
+
+
 def unit_cost(u):
-    if u[0] == "pcmm":
-        _, name, xname, weights, g, kt, nt = u
-        return COST_COPIES + COST_TRANSFORM + COST_ACC_TILE * nt * len(weights)
-    return 2 * COST_COPIES + (3 if u[4] else 2) * COST_TRANSFORM
+    return UNIT_COST_MS[unit_kind(u)]
 
 
 def deal_units(units, world):
@@ -292,8 +294,6 @@ class LayerWorkload:
                         acc = part if acc is None else CtxtTensor(self.lib.add(acc.ct, part.ct), *part.shape)
                     if acc is not None:
                         out["pcmm"][(name, wname, j)] = acc
-        if self.world > 1:
-            self._exchange_partials(out["pcmm"])
         # ct x ct: one batched transpose for every operand that needs it; the transforms sigma / tau run per group
         # (a transposed tile sits one level lower), then ONE product loop serves all units of this rank
         cc = res["ccmm"]
@@ -321,6 +321,10 @@ class LayerWorkload:
             sa = lib.batch_concat(sas) if len(sas) > 1 else sas[0]
             tb = lib.batch_concat(tbs) if len(tbs) > 1 else tbs[0]
             out["ccmm"]["all"] = ([i for tr in order for i in cc[tr][0]], H.cc_matmul_core(sa, tb, D, D, D, 2 * D, t))
+        # the K-split exchange comes last: a rank that finishes its own units early waits for its peers once, at the
+        # end of the pass, instead of in the middle of it
+        if self.world > 1:
+            self._exchange_partials(out["pcmm"])
         return out
 
     def exchange_plan(self):
