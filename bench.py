@@ -498,9 +498,9 @@ def run_gpu(args):
 
 
 # which kernels the roofline object describes, and how their DRAM traffic relates to the algorithmic bytes
-NTT_KERNELS = "ntt16_fwd_cols+ntt16_fwd_rows (one forward NTT of 64 ciphertexts, level 12)"
+NTT_KERNELS = "ntt16v2_fwd_cols+ntt16v2_fwd_rows (one forward NTT of 64 ciphertexts, level 12)"
 NTT_TRAFFIC_FACTOR = 2
-NTT_TRAFFIC_NOTE = "ncu dram bytes of a 32-ciphertext capture, scaled by limbs: each of the two passes reads and writes every limb once"
+NTT_TRAFFIC_NOTE = "ncu dram bytes of a 32-ciphertext capture, scaled by limbs: each of the two passes reads and writes every limb once (profiles/ntt16v2_passes_level12.md)"
 
 
 def run_sweep(args):

@@ -104,6 +104,14 @@ class HEMMer {
     // rows of the second factor ((X A) B).  cur: three [X_2i | X_2i+1] pairs; wa / wb: row 2i+j of the two-tile
     // ciphertext holds rank vector j for pair i.  Returns the three output pairs.
     std::vector<CtxtTensor> loraOptiForward(const std::vector<CtxtTensor> &cur, const CtxtTensor &lora_wa, const CtxtTensor &lora_wb);
+    // The score assembly of the Gaussian-kernel attention in the reference's layer (TransformerBlock::attention2_bert_loraOpti,
+    // TransformerBlock.cpp:2420-2482, up to the bootstrap): a two-tile ciphertext holds two heads per tile (columns 0..d/2-1
+    // and d/2..d-1).  maskRightLeft separates the heads, square + oneMatRotSumInplace give |q_r|^2 spread over the rows
+    // and (after a transpose) |k_c|^2 spread over the columns, complexPacking* + packedMatMul + repackCC give q_r . k_c,
+    // and the result is |q_r|^2 + |k_c|^2 - 2 q_r . k_c.  Returns one ciphertext per head position, at target_level.
+    std::vector<CtxtTensor> gaussianKernelScores(const CtxtTensor &query, const CtxtTensor &key, int target_level = 4);
+    // HEMMer::maskRightLeft (HEMMer.cpp, masks :2366-2376): the first / second head of every tile
+    void maskRightLeft(const CtxtTensor &t, CtxtTensor &left, CtxtTensor &right);
     // HEMMer::maskFirstRowInplace / maskFirstColOnlyInplace (HEMMer.cpp:1255-1261)
     void maskFirstRowInplace(CtxtTensor &t);
     void maskFirstColOnlyInplace(CtxtTensor &t);

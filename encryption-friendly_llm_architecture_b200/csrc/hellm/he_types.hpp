@@ -129,6 +129,8 @@ class Evaluator {
     HB_BINARY(sub, hb_sub)
     HB_BINARY(tensor, hb_tensor)
     HB_BINARY(mult, hb_mul)
+    Ciphertext multInteger(const Ciphertext &a, i64 k) const { hb_ct *o = nullptr; check(c_, hb_mult_int(c_, a.raw(), k, &o)); return Ciphertext(c_, o); }
+    Ciphertext square(const Ciphertext &a) const { hb_ct *o = nullptr; check(c_, hb_square(c_, a.raw(), &o)); return Ciphertext(c_, o); }
     HB_UNARY(negate, hb_negate)
     HB_UNARY(multImagUnit, hb_mult_imag)
     HB_UNARY(rescale, hb_rescale)

@@ -6,7 +6,7 @@
 namespace HELLM {
 
 namespace {
-enum HemmerMask { kColEven = 1, kRowEven = 2, kLeftHalf = 3, kLeftHalfScaled = 4, kFirstCol = 5, kLastCol = 6, kFirstRow = 7, kFirstColOnly = 8 };
+enum HemmerMask { kColEven = 1, kRowEven = 2, kLeftHalf = 3, kLeftHalfScaled = 4, kFirstCol = 5, kLastCol = 6, kFirstRow = 7, kFirstColOnly = 8, kHeadLeft = 9, kHeadRight = 10 };
 }
 
 HEMMer::HEMMer(hb_ctx *ctx) : ctx_(ctx), eval_(ctx) {
@@ -138,7 +138,8 @@ static const Plaintext &hemmer_mask(HEMMer &h, int which, int level) {
     for (i64 r = 0; r < d; ++r)
         for (i64 c = 0; c < 2 * d; ++c) {
             bool on = which == kColEven ? ((c % d) % 2 == 0) : which == kRowEven ? (r % 2 == 0) : which == kFirstCol ? (c % d == 0) : which == kLastCol ? (c % d == d - 1) :
-                      which == kFirstRow ? (r == 0) : which == kFirstColOnly ? (c == 0) : (c < d);
+                      which == kFirstRow ? (r == 0) : which == kFirstColOnly ? (c == 0) :
+                      which == kHeadLeft ? (c % d < d / 2) : which == kHeadRight ? (c % d >= d / 2) : (c < d);
             if (on) m.re[(size_t)(r * 2 * d + c)] = which == kLeftHalfScaled ? 0.5 : 1.0;
         }
     return h.masks().put(k, h.eval().encode(m, level));
@@ -178,6 +179,37 @@ void HEMMer::oneMatRotSumInplace(CtxtTensor &a, CtxtTensor &b) {
 // HEMMer::maskFirstRowInplace / maskFirstColOnlyInplace -- HEMMer.cpp:1255-1261, masks :2384-2388, :2418
 void HEMMer::maskFirstRowInplace(CtxtTensor &t) { t.get() = eval_.mult(t.get(), hemmer_mask(*this, kFirstRow, t.getLevel())); }
 void HEMMer::maskFirstColOnlyInplace(CtxtTensor &t) { t.get() = eval_.mult(t.get(), hemmer_mask(*this, kFirstColOnly, t.getLevel())); }
+// HEMMer::maskRightLeft -- mask_one_left_ / mask_one_right_ of generateRightLeftMasks, HEMMer.cpp:2366-2376
+void HEMMer::maskRightLeft(const CtxtTensor &t, CtxtTensor &left, CtxtTensor &right) {
+    left = CtxtTensor(t.getShape(), eval_.mult(t.get(), hemmer_mask(*this, kHeadLeft, t.getLevel())));
+    right = CtxtTensor(t.getShape(), eval_.mult(t.get(), hemmer_mask(*this, kHeadRight, t.getLevel())));
+}
+// Gaussian-kernel score assembly -- TransformerBlock.cpp:2420-2482 (one query / key pair; the reference loops over three)
+std::vector<CtxtTensor> HEMMer::gaussianKernelScores(const CtxtTensor &query, const CtxtTensor &key, int target_level) {
+    std::vector<CtxtTensor> mq(2), mk(2);
+    maskRightLeft(query, mq[0], mq[1]);
+    maskRightLeft(key, mk[0], mk[1]);
+    std::vector<CtxtTensor> oq, ok;
+    for (int j = 0; j < 2; ++j) {
+        oq.emplace_back(query.getShape(), eval_.square(mq[(size_t)j].get()));
+        ok.emplace_back(key.getShape(), eval_.square(mk[(size_t)j].get()));
+    }
+    oneMatRotSumInplace(oq[0], oq[1]);
+    oneMatRotSumInplace(ok[0], ok[1]);
+    for (auto &t : ok) transposeInplace(t, target_level);
+    std::vector<CtxtTensor> out;
+    for (size_t j = 0; j < 2; ++j) {
+        complexPackingInplace(mq[j]);
+        transposeInplace(mk[j]);
+        complexPackingRowInplace(mk[j]);
+        CtxtTensor s = repackCC(packedMatMul(mq[j], mk[j], target_level));
+        s.get() = eval_.multInteger(s.get(), -2);
+        s.get() = eval_.add(s.get(), oq[j].get());
+        s.get() = eval_.add(s.get(), ok[j].get());
+        out.push_back(std::move(s));
+    }
+    return out;
+}
 // the rank-2 LoRA branch of TransformerBlock::attention2_bert_loraOpti -- TransformerBlock.cpp:2199-2365
 std::vector<CtxtTensor> HEMMer::loraOptiForward(const std::vector<CtxtTensor> &cur, const CtxtTensor &lora_wa, const CtxtTensor &lora_wb) {
     if (cur.size() != 3) throw std::invalid_argument("[loraOptiForward] three activation pairs expected");

@@ -109,6 +109,13 @@ int hb_hemmer_one_mat_rot_sum(hb_hemmer *h, const hb_ct *a, const hb_ct *b, hb_c
     });
 }
 
+int hb_hemmer_gaussian_kernel_scores(hb_hemmer *h, const hb_ct *query, const hb_ct *key, int rows, int cols, int width, int target, hb_ct **out0, hb_ct **out1) {
+    return guard([&] {
+        Borrow bq(h->ctx, query), bk(h->ctx, key);
+        std::vector<CtxtTensor> r = h->h.gaussianKernelScores(view(bq, rows, cols, width), view(bk, rows, cols, width), target);
+        *out0 = r[0].get().release(); *out1 = r[1].get().release();
+    });
+}
 int hb_hemmer_lora_opti_forward(hb_hemmer *h, const hb_ct *cur0, const hb_ct *cur1, const hb_ct *cur2, const hb_ct *lora_wa, const hb_ct *lora_wb, hb_ct **out0,
                                 hb_ct **out1, hb_ct **out2) {
     return guard([&] {

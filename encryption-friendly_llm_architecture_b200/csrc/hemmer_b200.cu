@@ -126,6 +126,7 @@ struct hb_ctx {
     unsigned long long launches_at_capture = 0, alg_at_capture = 0;
     int N = 0, logn = 0, L = 0, K = 0, nprimes = 0;
     unsigned long long launches = 0; // kernels launched by this context
+    int *dev_err = nullptr;          // raised by a kernel whose bounded wait ran out; read by hb_sync
     // Compulsory HBM traffic of the primitives called so far, in limbs of N words: every input of a primitive read once,
     // every output written once, a switching key or plaintext once per batch (temporaries and transforms inside a
     // primitive do not count).  Divided by the HBM peak this is the time the call sequence cannot go below.
@@ -475,6 +476,21 @@ hb_ct *do_assemble_mk(hb_ctx *c, const hb_ct *a, const u64 *dt, const hb_mkey *c
     Tmp E(c, (size_t)groups * batch * 2 * ne);
     for (int g = 0; g < groups; ++g) ALG(c, (size_t)mrl.r[g].count * ((size_t)d.nd * 2 * ne + n) + (size_t)batch * 2 * (n - 1));
     ALG(c, (size_t)batch * (2 * n + d.dt_count));
+    // Up to two digits: the bulk-copy kernel (three members per CTA, 512 coefficients; 112 KB of shared memory, two CTAs
+    // per SM).  With more digits its staging buffers leave room for one CTA per SM only and the register kernel is faster.
+    if (d.nd <= 2 && N % 512 == 0) {
+        constexpr int M = 3, EL = 2, T = 256 * EL;
+        const int chunks = (batch + M - 1) / M;
+        int maxcount = 1;
+        for (int g = 0; g < groups; ++g) maxcount = std::max(maxcount, mrl.r[g].count);
+        const size_t smem = ((size_t)maxcount * d.nd * 2 + maxcount + (size_t)M * maxcount * (d.nd + 1)) * T * 8;
+        static bool attr_set = false;
+        if (!attr_set) { CK(cudaFuncSetAttribute(k_ks_inner_mkb<M, EL>, cudaFuncAttributeMaxDynamicSharedMemorySize, 28 * T * 8)); attr_set = true; }
+        LAUNCH(c), k_ks_inner_mkb<M, EL><<<dim3((unsigned)(N / T), (unsigned)(groups * chunks), (unsigned)ne), 256, smem, c->st>>>(E.p, a->d, a->d + (size_t)n * N, (size_t)2 * n * N, dt, mrl, batch,
+                                                                                                                              maxcount, pl, c->pc, c->logn, N, c->dev_err);
+        CK(cudaGetLastError());
+        return divide_by_p_ql(c, E.p, level, groups * batch);
+    }
     constexpr int kEl = 4; // coefficients per thread (2, with three CTAs resident per SM, measured no faster)
     LAUNCH(c), k_ks_inner_mk<kEl><<<dim3((unsigned)((N + 256 * kEl - 1) / (256 * kEl)), groups * batch, ne), 256, 0, c->st>>>(E.p, a->d, a->d + (size_t)n * N, (size_t)2 * n * N, dt, mrl, batch, pl, c->pc,
                                                                                                                         c->logn, N);
@@ -681,6 +697,8 @@ int hb_ctx_create(const hb_params *prm, int device, hb_ctx **out) {
         for (int i = 0; i < 8; ++i) c->ckey.k[i] = c->h->cha.key[i];
         CK(cudaSetDevice(device));
         CK(cudaStreamCreateWithFlags(&c->st, cudaStreamNonBlocking));
+        CK(cudaMalloc(&c->dev_err, sizeof(int)));
+        CK(cudaMemset(c->dev_err, 0, sizeof(int)));
         const int np = c->nprimes, N = c->N;
         std::vector<PrimeConst> pcs(np);
         const bool big = c->logn == 16;   // 2^16 coefficients: tables in the order the two-pass kernels read them
@@ -714,8 +732,9 @@ int hb_ctx_create(const hb_params *prm, int device, hb_ctx **out) {
                 }
             }
             if (big) {
-                ntt16_fill_table(&t16[(size_t)i * Ntt16Layout::kEntries], [&](unsigned k) { return make_ulonglong2(f[k], fs[k]); });
-                ntt16_fill_table(&t16[((size_t)np + i) * Ntt16Layout::kEntries], [&](unsigned k) { return make_ulonglong2(iv[k], ivs[k]); });
+                auto word = [&](u64 w) { return p.small ? ds_twiddle_word(w) : w; };
+                ntt16_fill_table(&t16[(size_t)i * Ntt16Layout::kEntries], [&](unsigned k) { return make_ulonglong2(word(f[k]), fs[k]); });
+                ntt16_fill_table(&t16[((size_t)np + i) * Ntt16Layout::kEntries], [&](unsigned k) { return make_ulonglong2(word(iv[k]), ivs[k]); });
             } else {
                 std::memcpy(&tw[((size_t)0 * np + i) * N], f.data(), (size_t)N * 8);
                 std::memcpy(&tw[((size_t)1 * np + i) * N], fs.data(), (size_t)N * 8);
@@ -753,6 +772,7 @@ void hb_ctx_destroy(hb_ctx *c) {
     if (c->pc) cudaFree(c->pc);
     if (c->tw) cudaFree(c->tw);
     if (c->sk) cudaFree(c->sk);
+    if (c->dev_err) cudaFree(c->dev_err);
     if (c->st) cudaStreamDestroy(c->st);
     delete c;
 }
@@ -768,7 +788,18 @@ int hb_ctx_dims(const hb_ctx *c, int *log_n, int *max_level, int *num_special) {
     if (log_n) *log_n = c->logn; if (max_level) *max_level = c->L; if (num_special) *num_special = c->K;
     return HB_OK;
 }
-int hb_sync(hb_ctx *c) { return guard(c, [&] { no_capture(c, "sync"); CK(cudaStreamSynchronize(c->st)); }); }
+int hb_sync(hb_ctx *c) {
+    return guard(c, [&] {
+        no_capture(c, "sync");
+        int flag = 0;
+        CK(cudaMemcpyAsync(&flag, c->dev_err, sizeof(int), cudaMemcpyDeviceToHost, c->st));
+        CK(cudaStreamSynchronize(c->st));
+        if (flag) {
+            CK(cudaMemsetAsync(c->dev_err, 0, sizeof(int), c->st));
+            fail(HB_E_TIMEOUT, "a bounded wait inside a kernel ran out; the results since the last sync are void");
+        }
+    });
+}
 int hb_mem_info(const hb_ctx *c, uint64_t *pool_bytes, uint64_t *in_use) {
     if (pool_bytes) *pool_bytes = c->pool.total;
     if (in_use) *in_use = c->pool.in_use;
@@ -1184,6 +1215,20 @@ int hb_mul(hb_ctx *c, const hb_ct *a, const hb_ct *b, hb_ct **out) {
         try { *out = do_rescale(c, r); } catch (...) { hb_ct_free(r); throw; }
         hb_ct_free(r);
     });
+}
+// HomEvaluator::square (HomEvaluator.hpp:363): mult(a, a)
+int hb_square(hb_ctx *c, const hb_ct *a, hb_ct **out) { return hb_mul(c, a, a, out); }
+// HomEvaluator::mult(ct, Complex / Real constant) (HomEvaluator.hpp:275-278): the constant in every slot, encoded at the
+// ciphertext's level, one rescale
+int hb_mul_const(hb_ctx *c, const hb_ct *a, double re, double im, hb_ct **out) {
+    if (!c || !a || !out) return HB_E_ARG;
+    std::vector<double> vr((size_t)c->h->slots, re), vi((size_t)c->h->slots, im);
+    hb_pt *p = nullptr;
+    int rc = hb_encode(c, vr.data(), vi.data(), vr.size(), a->level, &p);
+    if (rc != HB_OK) return rc;
+    rc = hb_mul_pt(c, a, p, out);
+    hb_pt_free(p);
+    return rc;
 }
 int hb_decompose(hb_ctx *c, const hb_ct *a, hb_digits **out) {
     return guard(c, [&] {

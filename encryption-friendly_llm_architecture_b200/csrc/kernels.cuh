@@ -6,6 +6,7 @@
 // of the bit-reversed index as units), so they cost no extra sectors.
 #pragma once
 #include "modarith.cuh"
+#include "bulk.cuh"
 
 namespace hb {
 
@@ -770,6 +771,160 @@ __global__ void __launch_bounds__(256, EL == 2 ? 3 : 2) k_ks_inner_mk(u64 *__res
     u64 *o0 = E + (((size_t)ob * 2) * ne + j) * N + x0, *o1 = o0 + (size_t)ne * N;
 #pragma unroll
     for (int u = 0; u < EL; ++u) { o0[u * blockDim.x] = r0[u]; o1[u * blockDim.x] = r1[u]; }
+}
+// The same sums fed by bulk copies.  The automorphism maps every aligned block of 2^k outputs onto one aligned block
+// of 2^k inputs, so a CTA that owns T consecutive coefficients of limb j needs, per (member, rotation, digit), exactly
+// one contiguous chunk of T words -- and one chunk per key word.  One warp issues all those copies at once (tens of KB
+// per CTA in flight from its first instruction on, which 8-byte register loads cannot keep up), every thread then
+// waits on the mbarrier and works from shared memory: the permutation becomes an index into the staged chunk, key
+// words are read once and meet M members.  Other resident CTAs of the SM compute while this one's copies land.
+// Dynamic shared memory: (count*nd*2 + count + M*count*(nd+1)) * T words, count = most rotations of any group.
+// grid = (N / T, groups * ceil(batch / M), ne), T = 256 * EL
+template <int M, int EL>
+__global__ void __launch_bounds__(256) k_ks_inner_mkb(u64 *__restrict__ E, const u64 *__restrict__ c0, const u64 *__restrict__ a_ntt, size_t a_outer, const u64 *__restrict__ dt,
+                                                      const __grid_constant__ MaskedRotList mrl, int batch, int maxcount, const KsPlan *__restrict__ pl, const PrimeConst *__restrict__ pc, int logn,
+                                                      int N, int *__restrict__ err) {
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    __shared__ __align__(8) u64 bar;
+    constexpr int T = 256 * EL;
+    const int chunks = (batch + M - 1) / M;
+    const int j = blockIdx.z, grp = blockIdx.y / chunks, b0 = (blockIdx.y % chunks) * M;
+    const int nm = min(M, batch - b0);
+    const MaskedRot &mr = mrl.r[grp];
+    const int pj = pl->ext_prime[j], nd = pl->nd, ne = pl->ne, n = pl->n, count = mr.count;
+    const bool has_c0 = j < n;
+    const int nsrc = nd + 1; // chunks per (member, rotation): the digits, then c0 (left empty on the limbs of P)
+    u64 *keyb = reinterpret_cast<u64 *>(smem_raw), *pmb = keyb + (size_t)maxcount * nd * 2 * T, *srcb = pmb + (size_t)maxcount * T;
+    const u32 tile0 = blockIdx.x * T;
+    const int tid = threadIdx.x;
+    if (tid == 0) { mbar_init(&bar, 1); mbar_fence_init(); }
+    __syncthreads();
+    if (tid < 32) {
+        const int nkey = count * nd * 2, npm = has_c0 ? count : 0, per_member = count * (nd + (has_c0 ? 1 : 0));
+        const int total = nkey + npm + nm * per_member;
+        if (tid == 0) mbar_arrive_expect_tx(&bar, (u32)total * T * 8);
+        __syncwarp();
+        for (int ci = tid; ci < total; ci += 32) {
+            const u64 *src;
+            u64 *dst;
+            if (ci < nkey) {
+                const int r = ci / (nd * 2), rem = ci % (nd * 2); // rem = digit * 2 + poly
+                src = mr.mkey[r] + ((size_t)rem * ne + j) * N + tile0;
+                dst = keyb + (size_t)ci * T;
+            } else if (ci < nkey + npm) {
+                const int r = ci - nkey;
+                src = mr.pm[r] + (size_t)j * N + tile0;
+                dst = pmb + (size_t)r * T;
+            } else {
+                const int k = ci - nkey - npm, u = k / per_member, rem = k % per_member, r = rem % count, dg = rem / count;
+                const u32 st0 = ntt_perm(tile0, mr.g[r], logn) & ~(u32)(T - 1);
+                if (dg < nd) {
+                    const int en = pl->dt_entry[dg][j];
+                    src = en < 0 ? a_ntt + (size_t)(b0 + u) * a_outer + (size_t)j * N : dt + ((size_t)(b0 + u) * pl->dt_count + en) * N;
+                } else src = c0 + (size_t)(b0 + u) * a_outer + (size_t)j * N;
+                src += st0;
+                dst = srcb + ((size_t)(u * count + r) * nsrc + dg) * T;
+            }
+            bulk_load(dst, src, T * 8, &bar);
+        }
+    }
+    mbar_wait_bounded(&bar, 0, err);
+    const PrimeConst m = pc[pj];
+    u64 r0[M][EL], r1[M][EL];
+    if (m.fp) {
+#pragma unroll
+        for (int u = 0; u < M; ++u)
+#pragma unroll
+            for (int e = 0; e < EL; ++e) { r0[u][e] = 0; r1[u][e] = 0; }
+        for (int r = 0; r < count; ++r) {
+            u32 li[EL];
+#pragma unroll
+            for (int e = 0; e < EL; ++e) li[e] = ntt_perm(tile0 + e * 256 + tid, mr.g[r], logn) & (u32)(T - 1);
+            for (int dg = 0; dg < nd; ++dg) {
+                const u64 *kp = keyb + (size_t)((r * nd + dg) * 2) * T + tid;
+                const u64 *sp = srcb + (size_t)(r * nsrc + dg) * T;
+#pragma unroll
+                for (int e = 0; e < EL; ++e) {
+                    const u64 ka = kp[e * 256], kb = kp[T + e * 256];
+                    const double kad = u52_to_double(ka), kbd = u52_to_double(kb);
+#pragma unroll
+                    for (int u = 0; u < M; ++u)
+                        if (u < nm) {
+                            const u64 v = sp[(size_t)u * count * nsrc * T + li[e]];
+                            const double vd = u52_to_double(v);
+                            r0[u][e] += mul_small_lazy_d(v, vd, ka, kad, m.q_inv_f, m.q);
+                            r1[u][e] += mul_small_lazy_d(v, vd, kb, kbd, m.q_inv_f, m.q);
+                        }
+                }
+            }
+            if (has_c0) {
+                const u64 *sp = srcb + (size_t)(r * nsrc + nd) * T;
+#pragma unroll
+                for (int e = 0; e < EL; ++e) {
+                    const u64 pmv = pmb[(size_t)r * T + e * 256 + tid];
+                    const double pmd = u52_to_double(pmv);
+#pragma unroll
+                    for (int u = 0; u < M; ++u)
+                        if (u < nm) {
+                            const u64 v = sp[(size_t)u * count * nsrc * T + li[e]];
+                            r0[u][e] += mul_small_lazy_d(v, u52_to_double(v), pmv, pmd, m.q_inv_f, m.q);
+                        }
+                }
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < M; ++u)
+#pragma unroll
+            for (int e = 0; e < EL; ++e) { r0[u][e] = reduce_fp(r0[u][e], m.q_inv_f, m.q); r1[u][e] = reduce_fp(r1[u][e], m.q_inv_f, m.q); }
+    } else {
+        Acc128 s0[M][EL], s1[M][EL];
+#pragma unroll
+        for (int u = 0; u < M; ++u)
+#pragma unroll
+            for (int e = 0; e < EL; ++e) { s0[u][e].zero(); s1[u][e].zero(); }
+        for (int r = 0; r < count; ++r) {
+            u32 li[EL];
+#pragma unroll
+            for (int e = 0; e < EL; ++e) li[e] = ntt_perm(tile0 + e * 256 + tid, mr.g[r], logn) & (u32)(T - 1);
+            for (int dg = 0; dg < nd; ++dg) {
+                const u64 *kp = keyb + (size_t)((r * nd + dg) * 2) * T + tid;
+                const u64 *sp = srcb + (size_t)(r * nsrc + dg) * T;
+#pragma unroll
+                for (int e = 0; e < EL; ++e) {
+                    const u64 ka = kp[e * 256], kb = kp[T + e * 256];
+#pragma unroll
+                    for (int u = 0; u < M; ++u)
+                        if (u < nm) {
+                            const u64 v = sp[(size_t)u * count * nsrc * T + li[e]];
+                            s0[u][e].mad(v, ka);
+                            s1[u][e].mad(v, kb);
+                        }
+                }
+            }
+            if (has_c0) {
+                const u64 *sp = srcb + (size_t)(r * nsrc + nd) * T;
+#pragma unroll
+                for (int e = 0; e < EL; ++e) {
+                    const u64 pmv = pmb[(size_t)r * T + e * 256 + tid];
+#pragma unroll
+                    for (int u = 0; u < M; ++u)
+                        if (u < nm) s0[u][e].mad(sp[(size_t)u * count * nsrc * T + li[e]], pmv);
+                }
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < M; ++u)
+#pragma unroll
+            for (int e = 0; e < EL; ++e) { r0[u][e] = barrett128(s0[u][e].hi, s0[u][e].lo, m); r1[u][e] = barrett128(s1[u][e].hi, s1[u][e].lo, m); }
+    }
+    const size_t kpoly = (size_t)ne * N;
+    u64 *o0 = E + (((size_t)(grp * batch + b0) * 2) * ne + j) * N + tile0 + tid;
+#pragma unroll
+    for (int u = 0; u < M; ++u)
+        if (u < nm) {
+#pragma unroll
+            for (int e = 0; e < EL; ++e) { o0[(size_t)u * 2 * kpoly + e * 256] = r0[u][e]; o0[(size_t)u * 2 * kpoly + kpoly + e * 256] = r1[u][e]; }
+        }
 }
 // Base conversion of the division: src [bp][ns][N] (limbs q_level, P; coefficient form) -> t [bp][level][N]
 // grid = (N/256, 1, nbp)

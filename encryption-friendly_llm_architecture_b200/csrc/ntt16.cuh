@@ -30,6 +30,7 @@
 //    Primes of 44 bits and more use Shoup butterflies on integers in [0, 4q).
 #pragma once
 #include "modarith.cuh"
+#include <cstring>
 
 namespace hb {
 
@@ -132,12 +133,41 @@ __device__ __forceinline__ DsConst ds_const(const PrimeConst &m) {
 // canonical residue -> double, exact for values below 2^52
 __device__ __forceinline__ double ds_load(u64 a) { return u52_to_double(a); }
 // t = y * w mod q as a signed double in (-0.52 q, 0.52 q); y integer-valued, |y| < 2^49; wf = w / q
+#ifndef HB_DS_FP
+#define HB_DS_FP 1
+#endif
+#if HB_DS_FP
+// wbits = bits of the double w.  Six FP64 instructions, every one exact: p + e = y * w (product and its rounding error),
+// qh = rint(y * w / q) up to 0.02, p - qh * q is an integer below 2^45 and so is its sum with e.
+__device__ __forceinline__ double ds_mul(double y, u64 wbits, double wf, const DsConst &c) {
+    const double wd = __longlong_as_double((long long)wbits);
+    const double qh = __dadd_rn(__fma_rn(y, wf, kMagic), -kMagic);
+    const double p = __dmul_rn(y, wd);
+    const double e = __fma_rn(y, wd, -p);
+    const double t1 = __fma_rn(-qh, c.qd, p);
+    return __dadd_rn(t1, e);
+}
+#else
 __device__ __forceinline__ double ds_mul(double y, u64 w, double wf, const DsConst &c) {
     const double qh = __fma_rn(y, wf, kMagic);
     const double yb = __dadd_rn(y, kMagic);
     const u64 r = mad2_lo64((u64)__double_as_longlong(yb), w, (u64)__double_as_longlong(qh), c.nq, c.q); // y*w - qh*q + q, exact in its low 48 bits
     const u32 hi = ((u32)(r >> 32) & 0xFFFFu) | 0x43300000u;
     return __hiloint2double((int)hi, (int)(u32)r) - c.coff;
+}
+#endif
+// the form of a twiddle w that ds_mul takes as its second operand
+__host__ __device__ __forceinline__ u64 ds_twiddle_word(u64 w) {
+#if HB_DS_FP
+    const double d = (double)w; // exact below 2^53
+#ifdef __CUDA_ARCH__
+    return (u64)__double_as_longlong(d);
+#else
+    u64 b; memcpy(&b, &d, 8); return b;
+#endif
+#else
+    return w;
+#endif
 }
 // x - rint(x / q) * q, |result| <= 0.52 q
 __device__ __forceinline__ double ds_reduce(double x, const DsConst &c) {
@@ -365,7 +395,7 @@ __global__ void __launch_bounds__(256, MINB) ntt16v2_inv_cols(const u64 *__restr
         const double qinv_up = c.qinv * (1.0 + 0x1p-50);
 #pragma unroll
         for (int e = 0; e < 16; ++e) {
-            const double t = ds_mul(v[e], m.n_inv, m.n_inv_f, c); // x * N^-1 in (-0.52 q, 0.52 q)
+            const double t = ds_mul(v[e], ds_twiddle_word(m.n_inv), m.n_inv_f, c); // x * N^-1 in (-0.52 q, 0.52 q)
             o[(e * 16 + sub) * 256] = ds_store(t, c, c.qd, qinv_up);
         }
     } else {
@@ -388,7 +418,7 @@ __global__ void __launch_bounds__(256, MINB) ntt16v2_inv_cols(const u64 *__restr
 // with distinct buffers `dst` also serves as the intermediate between the two passes.  MINB = CTAs per SM the kernels
 // are compiled for (register budget 65536 / (256 * MINB)); two measured fastest (the compiler then has the registers
 // to fetch the twiddles of a round ahead of the butterflies that use them).
-template <int MINB = 2>
+template <int MINB = 4>
 inline cudaError_t launch_ntt16(cudaStream_t st, const u64 *src, size_t src_outer, u64 *dst, size_t dst_outer, int count, const LimbMap &map,
                                 const PrimeConst *pc, const Ntt16Tables &tb, bool inverse) {
     if (count == 0) return cudaSuccess;

@@ -195,6 +195,12 @@ class Hemmer:
         name = "hadamard_mult_pt" if isinstance(b, PtxtTensor) else "hadamard_mult"
         a.ct = self._call(name, a.ct.ptr, b.ct.ptr)
 
+    def gaussian_kernel_scores(self, query, key, target_level=4):
+        """Score assembly of the reference's Gaussian-kernel attention (TransformerBlock.cpp:2420-2482) for one query / key
+        pair: [|q_r|^2 + |k_c|^2 - 2 q_r . k_c] per head; returns the two head positions."""
+        outs = self._call("gaussian_kernel_scores", query.ct.ptr, key.ct.ptr, *self._shp(query), C.c_int(target_level), n_out=2)
+        return [CtxtTensor(o, *query.shape) for o in outs]
+
     def lora_opti_forward(self, cur, lora_wa, lora_wb):
         """The rank-2 LoRA branch of TransformerBlock::attention2_bert_loraOpti (TransformerBlock.cpp:2199-2365): three
         activation pairs and the two factor ciphertexts in, the three pairs of X A B out."""

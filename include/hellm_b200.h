@@ -75,6 +75,12 @@ int hb_hemmer_hadamard_mult_pt(hb_hemmer *h, const hb_ct *a, const hb_pt *p, hb_
 /* HEMMer::oneMatRotSumInplace (HEMMer.hpp:168; HEMMer.cpp:882-919) on two-tile ciphertexts */
 int hb_hemmer_one_mat_rot_sum(hb_hemmer *h, const hb_ct *a, const hb_ct *b, hb_ct **out_a, hb_ct **out_b);
 
+/* The score assembly of the Gaussian-kernel attention in the reference's layer, TransformerBlock::attention2_bert_loraOpti
+ * (TransformerBlock.cpp:2420-2482, for one query / key pair, up to the bootstrap): heads separated by maskRightLeft,
+ * squared norms by square + oneMatRotSumInplace (+ transposeInplace on the key side), the products by complexPacking* +
+ * packedMatMul + repackCC; out_j = |q_r|^2 + |k_c|^2 - 2 q_r . k_c for head position j of both tiles, at target_level. */
+int hb_hemmer_gaussian_kernel_scores(hb_hemmer *h, const hb_ct *query, const hb_ct *key, int rows, int cols, int width, int target_level,
+                                     hb_ct **out0, hb_ct **out1);
 /* The rank-2 LoRA branch of a projection in the reference's layer, TransformerBlock::attention2_bert_loraOpti
  * (TransformerBlock.cpp:2199-2365) without the bootstraps around it: X A by slot-wise products with the rank vectors
  * spread over the token rows and a rotate-and-add across each row, then (X A) B the same way.  cur0..2: the three

@@ -164,6 +164,8 @@ int hb_rescale_noalloc(hb_ctx *ctx, const hb_ct *a, hb_ct *out);
 int hb_tensor(hb_ctx *ctx, const hb_ct *a, const hb_ct *b, hb_ct **out);        /* tensor :518 */
 int hb_relin(hb_ctx *ctx, const hb_ct *a, hb_ct **out);                         /* relinearize :524 */
 int hb_mul(hb_ctx *ctx, const hb_ct *a, const hb_ct *b, hb_ct **out);           /* mult(ct,ct) :311-312 */
+int hb_square(hb_ctx *ctx, const hb_ct *a, hb_ct **out);                        /* square :363 */
+int hb_mul_const(hb_ctx *ctx, const hb_ct *a, double re, double im, hb_ct **out); /* mult(ct, Complex / Real) :275-278 */
 int hb_rotate(hb_ctx *ctx, const hb_ct *a, int64_t left_steps, hb_ct **out);    /* leftRotate :383 / rightRotate :403 */
 int hb_conjugate(hb_ctx *ctx, const hb_ct *a, hb_ct **out);                     /* conjugate :465 */
 /* Hoisted rotations: hb_decompose does the part of leftRotate that does not depend on the step (inverse NTT,

@@ -816,6 +816,37 @@ struct Hemmer {
             b.ct = ev.add(b.ct, rotL(b.ct, rot));
         }
     }
+    // Gaussian-kernel score assembly of attention2_bert_loraOpti -- TransformerBlock.cpp:2420-2482 (one query / key pair)
+    std::vector<CtT> gaussian_kernel_scores(const CtT &query, const CtT &key, int target_level) {
+        const i64 d = tile;
+        Mask left, right;
+        left.msg.assign((size_t)slots, cplx(0, 0));
+        right.msg.assign((size_t)slots, cplx(0, 0));
+        for (i64 r = 0; r < d; ++r)
+            for (i64 c = 0; c < 2 * d; ++c) ((c % d) < d / 2 ? left : right).msg[(size_t)(r * 2 * d + c)] = 1;
+        std::vector<CtT> mq{CtT{mult_msg(query.ct, left), query.sh}, CtT{mult_msg(query.ct, right), query.sh}};
+        std::vector<CtT> mk{CtT{mult_msg(key.ct, left), key.sh}, CtT{mult_msg(key.ct, right), key.sh}};
+        std::vector<CtT> oq, ok;
+        for (int j = 0; j < 2; ++j) {
+            oq.push_back(CtT{ev.mul(mq[(size_t)j].ct, mq[(size_t)j].ct), query.sh});
+            ok.push_back(CtT{ev.mul(mk[(size_t)j].ct, mk[(size_t)j].ct), key.sh});
+        }
+        one_mat_rot_sum_inplace(oq[0], oq[1]);
+        one_mat_rot_sum_inplace(ok[0], ok[1]);
+        for (auto &t : ok) transpose_inplace(t, target_level);
+        std::vector<CtT> out;
+        for (size_t j = 0; j < 2; ++j) {
+            complex_packing_inplace(mq[j]);
+            transpose_inplace(mk[j], 0);
+            complex_packing_row_inplace(mk[j]);
+            CtT s = repack_cc(mult_packed_mat_mat(mq[j], mk[j], target_level));
+            s.ct = ev.mult_int(s.ct, -2);
+            s.ct = ev.add(s.ct, oq[j].ct);
+            s.ct = ev.add(s.ct, ok[j].ct);
+            out.push_back(std::move(s));
+        }
+        return out;
+    }
     // the rank-2 LoRA branch of attention2_bert_loraOpti -- TransformerBlock.cpp:2199-2365 (without the bootstraps)
     std::vector<Ct> lora_opti_forward(const std::vector<Ct> &cur, const Ct &lora_wa, const Ct &lora_wb) {
         const i64 d = tile, w = 2 * tile;

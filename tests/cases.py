@@ -368,7 +368,27 @@ def sc_lora_opti(lib, H, target=0):
     return [lib.ct_export(o.ct) for o in outs], err
 
 
+def sc_gaussian_kernel(lib, H, target=2):
+    """Score assembly of the reference's Gaussian-kernel attention (TransformerBlock.cpp:2420-2482): squared distances
+    between query and key rows, per head (two heads per tile, two tiles per ciphertext), with chained levels."""
+    d = tile_dim(lib)
+    Q, Q2, K, K2 = _mats(132, d, 4, -0.5, 0.5)
+    q, k = H.encrypt2(Q, Q2, nonce=100), H.encrypt2(K, K2, nonce=101)
+    outs = H.gaussian_kernel_scores(q, k, target)
+    err = 0.0
+    half = d // 2
+    for j, o in enumerate(outs):
+        assert lib.ct_meta(o.ct)[0] == target
+        D = H.decrypt2(o)
+        for t, (A, B) in enumerate(((Q, K), (Q2, K2))):
+            a, b = A[:, j * half:(j + 1) * half], B[:, j * half:(j + 1) * half]
+            want = (a * a).sum(1)[:, None] + (b * b).sum(1)[None, :] - 2 * a @ b.T
+            err = max(err, np.abs(D[t] - want).max())
+    return [lib.ct_export(o.ct) for o in outs], err
+
+
 SCENARIOS = {
+    "gaussian_kernel": sc_gaussian_kernel,
     "lora_opti": sc_lora_opti,
     "rot_sum_hadamard": sc_rot_sum_hadamard,
     "repack_lora_opti": sc_repack_lora_opti,

@@ -21,7 +21,7 @@ def _same(a, b, what=""):
 
 
 @pytest.mark.parametrize("size", ["small", "mid"])
-@pytest.mark.parametrize("name", ["packed", "packed_reuse", "cc_reuse", "transforms", "single_matmul", "lora_backward", "transpose_packing", "repack_lora_opti"])
+@pytest.mark.parametrize("name", ["packed", "packed_reuse", "cc_reuse", "transforms", "single_matmul", "lora_backward", "transpose_packing", "repack_lora_opti", "gaussian_kernel"])
 def test_lazy_schedule_parity_remaining_scenarios(request, pkg, size, name):
     """Schedule 2 on the scenarios that test_gpu_parity.py runs in the other schedules only."""
     g, o = request.getfixturevalue(f"gpu_{size}"), request.getfixturevalue(f"orc_{size}")
@@ -167,3 +167,17 @@ def test_collectives_on_a_one_rank_communicator(pkg, gpu_mid):
     other = pkg.open_gpu(pkg.make_params(log_n=10, max_level=8, dnum=3, num_special=3, hamming_weight=32))
     with pytest.raises(pkg.HBError):     # a handle of another context
         other.mod_reduce(ct)
+
+
+def test_square_and_constant_product(gpu_mid):
+    """hb_square = mult(a, a); hb_mul_const = product with the constant in every slot, one rescale."""
+    g = gpu_mid
+    rng = np.random.default_rng(21)
+    z = rng.uniform(-1, 1, g.slots)
+    ct = g.encrypt(g.encode(z, 5), 88)
+    sq = g._op("square", ct.ptr)
+    _same(g.ct_export(sq), g.ct_export(g.mul(ct, ct)), "square")
+    assert np.abs(g.decrypt(sq).real - z * z).max() < 1e-6
+    mc = g._op("mul_const", ct.ptr, C.c_double(0.25), C.c_double(-0.5))
+    _same(g.ct_export(mc), g.ct_export(g.mul_pt(ct, g.encode(np.full(g.slots, 0.25 - 0.5j), 5))), "mul_const")
+    assert np.abs(g.decrypt(mc) - z * (0.25 - 0.5j)).max() < 1e-6
