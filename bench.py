@@ -17,6 +17,7 @@ from __future__ import annotations
 import argparse
 import ctypes as C
 import importlib
+import gc
 import json
 import os
 import statistics
@@ -552,7 +553,10 @@ def run_sweep(args):
             ms = timed_single(torch, stream, lib, fn, 3)
             alg = limbs * LIMB
             out["rows"].append({"op": name, "level": lv, "ms": round(ms, 4), "algorithmic_bytes": alg, "gbs": round(alg / ms / 1e6, 1), "frac": round(alg / ms / 1e6 / hbm, 4)})
-        del ct
+        del ct, pt, ops
+        prod = k1 = k2 = dg = None
+        gc.collect()
+        lib.dll.hb_release_cached(lib.ctx)  # the next level's buffers have other sizes: do not let the pool run the device out of memory
     print(json.dumps(out), flush=True)
 
 

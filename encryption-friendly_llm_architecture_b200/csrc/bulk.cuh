@@ -28,11 +28,20 @@ __device__ __forceinline__ bool mbar_try_wait(u64 *bar, u32 parity) {
     return ok != 0;
 }
 // true when the phase completed; false (and *err raised) when the limit ran out
-__device__ __forceinline__ bool mbar_wait_bounded(u64 *bar, u32 parity, int *err) {
-    for (int spin = 0; spin < kBulkSpinLimit; ++spin)
+__device__ __forceinline__ bool mbar_wait_bounded(u64 *bar, u32 parity, int *err, int limit = kBulkSpinLimit) {
+    for (int spin = 0; spin < limit; ++spin)
         if (mbar_try_wait(bar, parity)) return true;
     *err = 1;
     return false;
+}
+
+// One CTA waits on a barrier that nothing completes, with a short limit: exercises the give-up path (flag raised,
+// kernel returns, context stays usable) without any fault.
+__global__ void k_bounded_wait_probe(int *err, int limit) {
+    __shared__ __align__(8) u64 bar;
+    if (threadIdx.x == 0) { mbar_init(&bar, 1); mbar_fence_init(); }
+    __syncthreads();
+    mbar_wait_bounded(&bar, 0, err, limit);
 }
 
 } // namespace hb

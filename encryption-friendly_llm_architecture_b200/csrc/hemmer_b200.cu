@@ -805,6 +805,20 @@ int hb_mem_info(const hb_ctx *c, uint64_t *pool_bytes, uint64_t *in_use) {
     if (in_use) *in_use = c->pool.in_use;
     return HB_OK;
 }
+int hb_selftest_bounded_wait(hb_ctx *c) {
+    return guard(c, [&] {
+        no_capture(c, "selftest");
+        LAUNCH(c), k_bounded_wait_probe<<<1, 32, 0, c->st>>>(c->dev_err, 64);
+        CK(cudaGetLastError());
+    });
+}
+int hb_release_cached(hb_ctx *c) {
+    return guard(c, [&] {
+        no_capture(c, "release_cached");
+        CK(cudaStreamSynchronize(c->st));
+        c->pool.release_cached();
+    });
+}
 void *hb_stream(const hb_ctx *c) { return (void *)c->st; }
 uint64_t hb_launch_count(const hb_ctx *c) { return c ? c->launches : 0; }
 uint64_t hb_algorithmic_bytes(const hb_ctx *c) { return c ? c->alg_limbs * (uint64_t)c->N * 8 : 0; }

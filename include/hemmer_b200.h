@@ -67,6 +67,12 @@ int hb_ctx_dims(const hb_ctx *ctx, int *log_n, int *max_level, int *num_special)
 int hb_sync(hb_ctx *ctx);
 /* bytes currently held by the context's device pool (cudaMemGetInfo print in bert-matmul.cpp:240-243) */
 int hb_mem_info(const hb_ctx *ctx, uint64_t *pool_bytes, uint64_t *in_use_bytes);
+/* Launches one warp that waits, with a limit of 64 polls, on a barrier nothing completes.  The wait gives up, the kernel
+ * returns, and the next hb_sync reports HB_E_TIMEOUT once; the context stays usable.  Exercises the path every bounded
+ * device-side wait of the library takes when a copy does not land. */
+int hb_selftest_bounded_wait(hb_ctx *ctx);
+/* hands the pool's idle device buffers back to the driver (the buffers of live handles stay); refused while a graph records */
+int hb_release_cached(hb_ctx *ctx);
 /* the CUDA stream all kernels of this context run on (as a void* cudaStream_t) */
 void *hb_stream(const hb_ctx *ctx);
 /* number of kernels this context has launched since creation */

@@ -7,7 +7,7 @@ import subprocess
 import numpy as np
 import pytest
 
-from conftest import ROOT, MID, rand_ct_residues
+from conftest import ROOT, MID, SMALL, rand_ct_residues
 
 pytestmark = pytest.mark.gpu
 PKG_DIR = os.path.join(ROOT, "encryption-friendly_llm_architecture_b200")
@@ -114,3 +114,33 @@ def test_cpp_class_from_a_separately_compiled_program(pkg, tmp_path):
     H = pkg.open_hemmer(g)
     c = H.single_cc_matmul(H.encrypt2(x0, x1, nonce=1), H.encrypt2(w0, w1, nonce=2), 3)
     _same(g.ct_export(c.ct), residues, "C++ program and ctypes path")
+
+
+def test_bounded_wait_gives_up_and_reports_timeout(pkg):
+    """A device-side wait that nothing completes runs out of polls, raises the context's flag and returns: the next
+    sync reports HB_E_TIMEOUT (-8) once, and the context computes correctly afterwards."""
+    g = pkg.open_gpu(pkg.make_params(**SMALL))
+    g.keygen()
+    assert g.dll.hb_selftest_bounded_wait(g.ctx) == 0
+    assert g.dll.hb_sync(g.ctx) == -8
+    assert b"bounded wait" in g.dll.hb_last_error(g.ctx)
+    assert g.dll.hb_sync(g.ctx) == 0
+    z = np.random.default_rng(3).uniform(-1, 1, g.slots)
+    ct = g.encrypt(g.encode(z, g.L), 7)
+    assert np.abs(g.decrypt(ct).real - z).max() < 2.0 ** -14
+
+
+def test_release_cached_returns_idle_buffers(pkg):
+    g = pkg.open_gpu(pkg.make_params(**SMALL))
+    g.keygen()
+    z = np.random.default_rng(4).uniform(-1, 1, g.slots)
+    ct = g.encrypt(g.encode(z, g.L), 9)
+    tmp = g.rescale(g.mul_pt_norescale(ct, g.encode(z, g.L)))
+    del tmp
+    pool, used = C.c_uint64(), C.c_uint64()
+    g.dll.hb_mem_info(g.ctx, C.byref(pool), C.byref(used))
+    before = pool.value
+    assert g.dll.hb_release_cached(g.ctx) == 0
+    g.dll.hb_mem_info(g.ctx, C.byref(pool), C.byref(used))
+    assert pool.value < before and pool.value >= used.value
+    assert np.abs(g.decrypt(ct).real - z).max() < 2.0 ** -14
