@@ -455,20 +455,19 @@ def run_gpu(args):
     ks["wrapped_copy_l6"] = {"algorithmic_bytes": alg, "ms": ms, "gbs": alg / ms / 1e6, "frac": alg / ms / 1e6 / hbm}
     del cb, dgt, k1, k2
     top = roof["ntt"]
-    # Instruction roofline of the same transform: a radix-2 butterfly on a prime below 2^44 needs at least six 32-bit
-    # multiply-adds (the exact low words of y*w and of quotient*q) on a pipe that issues 64 of them per SM per clock,
-    # plus two FP64 operations (quotient estimate) and about six adds / logic operations for the conversions and the
-    # two 64-bit sums: 14 issue slots of the 128 per SM per clock.  The four 60-bit limbs of the 26 cost at least as much.
+    # Instruction roofline of the same transform: a butterfly on a prime below 2^44 is eight FP64 instructions (exact
+    # product and its error term, quotient estimate, remainder, the two outputs), and this GPU issues one FP64 warp
+    # instruction per two cycles per SM sub-partition (16 lanes), so the FP64 pipe alone bounds the transform below.
     mhz = clocks.get("sm_mhz") or clocks.get("sm_max_mhz") or 1965.0
     bfly = nb * 2 * (lvl + 1) * (65536 // 2) * 16
-    issue_ms = bfly * 14 / (148 * 128 * mhz * 1e6) * 1e3
-    imad_ms = bfly * 6 / (148 * 64 * mhz * 1e6) * 1e3
+    fp64_ms = bfly * 8 / (148 * 4 * 16 * mhz * 1e6) * 1e3
+    hbm_ms = NTT_TRAFFIC_FACTOR * top["algorithmic_bytes"] / (hbm * 1e6)
     # two launches (column pass, row pass) make one transform: per-launch algorithmic bytes are half of the transform's
     roofline = {"bound": "hbm", "kernel": NTT_KERNELS, "achieved": top["gbs"], "peak": hbm,
                 "unit": "GB/s", "frac": top["gbs"] / hbm, "peak_source": which, "traffic": NTT_TRAFFIC_FACTOR * top["algorithmic_bytes"],
                 "traffic_source": NTT_TRAFFIC_NOTE,
-                "issue_bound_ms": issue_ms, "imad_pipe_bound_ms": imad_ms, "measured_ms": top["ms"],
-                "issue_note": "butterflies x 14 issue slots / (148 SMs x 128 lanes x sampled SM clock); multiply-add pipe: butterflies x 6 / (148 x 64 x clock)",
+                "fp64_pipe_bound_ms": fp64_ms, "hbm_traffic_bound_ms": hbm_ms, "measured_ms": top["ms"],
+                "bound_note": "FP64 pipe: butterflies x 8 instructions / (148 SMs x 4 sub-partitions x 16 lanes x sampled SM clock); HBM: both passes' traffic / measured copy bandwidth",
                 "intt_gbs": roof["intt"]["gbs"], "keyswitch": ks}
 
     pb, iu = C.c_uint64(), C.c_uint64()
