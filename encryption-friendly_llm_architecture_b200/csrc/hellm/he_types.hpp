@@ -217,6 +217,21 @@ class Evaluator {
         for (auto *x : p) rp.push_back(x->raw());
         hb_ct *o = nullptr; check(c_, hb_sum_mul_pt_rescale(c_, ra.data(), rp.data(), (int)ra.size(), &o)); return Ciphertext(c_, o);
     }
+    // all giant-step parts of a baby-step / giant-step transform in one pass over the shared terms:
+    // part g = rescale(sum_j multWithoutRescale(a[j], p[g][j])), null entries skipped; members part-major in the result
+    static constexpr size_t kMaxPartTerms = 17, kMaxParts = 17;
+    Ciphertext multSumRescaledOnceParts(const std::vector<const Ciphertext *> &a, const std::vector<std::vector<const Plaintext *>> &p) const {
+        std::vector<const hb_ct *> ra; std::vector<const hb_pt *> rp;
+        for (auto *x : a) ra.push_back(x->raw());
+        for (const auto &row : p)
+            for (size_t j = 0; j < a.size(); ++j) rp.push_back(j < row.size() && row[j] ? row[j]->raw() : nullptr);
+        hb_ct *o = nullptr; check(c_, hb_mul_pt_sum_parts(c_, ra.data(), rp.data(), (int)ra.size(), (int)p.size(), &o)); return Ciphertext(c_, o);
+    }
+    // sum_t leftRotate(member group t of x, steps[t]) with one lift of the digits and one ModDown
+    Ciphertext rotateSumGrouped(const Ciphertext &x, const std::vector<i64> &steps) const {
+        check(c_, hb_gen_rot_keys(c_, steps.data(), (int)steps.size()));
+        hb_ct *o = nullptr; check(c_, hb_rotate_sum_grouped(c_, x.raw(), steps.data(), (int)steps.size(), &o)); return Ciphertext(c_, o);
+    }
     // acc += tensor(a, b)
     void tensorAccumulate(Ciphertext &acc, const Ciphertext &a, const Ciphertext &b) const {
         hb_ct *p = acc.release();

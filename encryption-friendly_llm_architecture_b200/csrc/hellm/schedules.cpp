@@ -117,7 +117,31 @@ Ciphertext bsgs_diagonals(Env &e, const Ciphertext &op, const TileTensorShape &s
         baby.push_back(e.ev.leftRotate(op, f.gap));
         for (i64 j = 1; j < f.bs; ++j) baby.push_back(e.ev.leftRotate(baby.back(), f.gap));
     }
-    // kLazy: the parts and their giant steps are collected and rotated by ONE call that shares the ModDown
+    // kLazy: the parts and their giant steps are collected and rotated by ONE call that shares the ModDown; when they
+    // fit its limits, all parts are also formed by one pass over the baby steps (terms: op, baby[0], baby[1], ...)
+    if (e.mode == kLazy && (size_t)f.bs + 1 <= Evaluator::kMaxPartTerms && (size_t)(2 * f.gs + 1) <= Evaluator::kMaxParts) {
+        std::vector<const Ciphertext *> terms{&op};
+        for (i64 j = 0; j < f.bs; ++j) terms.push_back(&baby[(size_t)j]);
+        std::vector<std::vector<const Plaintext *>> rows;
+        std::vector<i64> steps;
+        rows.push_back({&mask(0)}); steps.push_back(0);
+        for (i64 i = 0; i < f.gs; ++i) {
+            const i64 rot_num = i * f.bs * f.gap;
+            for (int sign = -1; sign <= 1; sign += 2) {
+                i64 idx = 1 + i * f.bs + (sign < 0 ? -f.main : 0);
+                const i64 limit = sign < 0 ? f.sub - f.main : f.sub;
+                std::vector<const Plaintext *> row(terms.size(), nullptr);
+                row[1] = &mask(idx);
+                for (i64 j = 1; j < f.bs; ++j) {
+                    if (++idx >= limit) break;
+                    row[(size_t)j + 1] = &mask(idx);
+                }
+                rows.push_back(std::move(row));
+                steps.push_back(sign < 0 ? -(f.main * f.gap - rot_num) : rot_num);
+            }
+        }
+        return e.ev.rotateSumGrouped(e.ev.multSumRescaledOnceParts(terms, rows), steps);
+    }
     std::vector<Ciphertext> parts; std::vector<i64> part_steps;
     Ciphertext res = e.ev.mult(op, mask(0));
     if (e.mode == kLazy) { parts.push_back(std::move(res)); part_steps.push_back(0); }
@@ -232,6 +256,24 @@ CtxtTensor transpose(Env &e, const CtxtTensor &op) {
         for (i64 j = 1; j < bs; ++j) baby.push_back(e.ev.leftRotate(baby.back(), gap));
     }
     Ciphertext res;
+    if (e.mode == kLazy && (size_t)bs <= Evaluator::kMaxPartTerms && (size_t)gs <= Evaluator::kMaxParts) { // all parts by one pass over the baby steps
+        std::vector<const Ciphertext *> terms;
+        for (i64 j = 0; j < bs; ++j) terms.push_back(&baby[(size_t)j]);
+        std::vector<std::vector<const Plaintext *>> rows;
+        std::vector<i64> steps;
+        for (i64 i = 0; i < gs; ++i) {
+            i64 idx = 1 - num_rows + i * bs;
+            std::vector<const Plaintext *> row(terms.size(), nullptr);
+            row[0] = &mask(idx);
+            for (i64 j = 1; j < bs; ++j) {
+                if (++idx >= num_cols) break;
+                row[(size_t)j] = &mask(idx);
+            }
+            rows.push_back(std::move(row));
+            steps.push_back(i * bs * gap);
+        }
+        return CtxtTensor(s, e.ev.rotateSumGrouped(e.ev.multSumRescaledOnceParts(terms, rows), steps));
+    }
     std::vector<Ciphertext> parts; std::vector<i64> part_steps; // kLazy: all giant steps in one call
     for (i64 i = 0; i < gs; ++i) {
         i64 idx = 1 - num_rows + i * bs;

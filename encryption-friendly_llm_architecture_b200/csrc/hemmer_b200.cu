@@ -554,6 +554,59 @@ hb_ct *do_prod_rescale(hb_ctx *c, const hb_ct *const *a, const hb_pt *const *p, 
     } catch (...) { hb_ct_free(r); throw; }
     return r;
 }
+// out_g = rescale(sum_j a_j (.) p[g * count + j]) for every part g in one pass over the a_j; out holds parts * batch members, part-major
+hb_ct *do_prod_rescale_parts(hb_ctx *c, const hb_ct *const *a, const hb_pt *const *p, int count, int parts) {
+    if (count < 1 || count > kMaxPartTerms || parts < 1 || parts > kMaxParts) fail(HB_E_LIMIT, "product sums: 1 to 17 terms, 1 to 17 parts");
+    const hb_ct *a0 = a[0];
+    if (!a0) fail(HB_E_ARG, "product sums: null ciphertext");
+    if (a0->level < 1) fail(HB_E_LEVEL, "rescale: level 0");
+    if (c->N % 256) fail(HB_E_LIMIT, "product sums: ring degree below 256");
+    PartTerms pt{}; pt.count = count; pt.parts = parts;
+    size_t used = 0;
+    for (int j = 0; j < count; ++j) {
+        if (!a[j]) fail(HB_E_ARG, "product sums: null ciphertext");
+        own(c, a[j]);
+        if (a[j]->level != a0->level) fail(HB_E_LEVEL, "mul_pt: level mismatch");
+        if (a[j]->np != a0->np || a[j]->batch != a0->batch) fail(HB_E_SHAPE, "product sums: shape mismatch");
+        if (a[j]->spow != 1) fail(HB_E_SHAPE, "mul_pt: operand not rescaled");
+        pt.a[j] = a[j]->d;
+    }
+    for (int g = 0; g < parts; ++g) {
+        int terms = 0;
+        for (int j = 0; j < count; ++j) {
+            const hb_pt *q = p[(size_t)g * count + j];
+            if (!q) continue;
+            own(c, q);
+            if (q->level != a0->level) fail(HB_E_LEVEL, "mul_pt: level mismatch");
+            if (q->spow != 1) fail(HB_E_SHAPE, "mul_pt: operand not rescaled");
+            pt.p[g][j] = q->d; ++terms; ++used;
+        }
+        if (!terms) fail(HB_E_ARG, "product sums: a part without terms");
+    }
+    const int l = a0->level, N = c->N, nbp = a0->batch * a0->np, gnbp = parts * nbp;
+    const unsigned gx1 = (unsigned)((N + 255) / 256);
+    hb_ct *r = new_ct(c, l - 1, a0->np, parts * a0->batch, 1);
+    ALG(c, (size_t)count * nbp * (l + 1) + used * (l + 1) + (size_t)gnbp * l);
+    try {
+        Tmp last(c, (size_t)gnbp), S(c, (size_t)gnbp), t(c, (size_t)gnbp * l);
+        constexpr int G = 4; // parts per CTA: 4 x 17 mask chunks of 2 KB = 136 KB of shared memory
+        const size_t smem = (size_t)G * count * 2048;
+        const unsigned pg = (unsigned)((parts + G - 1) / G);
+        static bool attr_set = false;
+        if (!attr_set) { CK(cudaFuncSetAttribute(k_prod_parts<G>, cudaFuncAttributeMaxDynamicSharedMemorySize, G * kMaxPartTerms * 2048)); attr_set = true; }
+        Scalars qi{};
+        for (int i = 0; i < l; ++i) qi.v[i] = hbhost::invmod(c->h->q[l] % c->h->q[i], c->h->q[i]);
+        LAUNCH(c), k_prod_parts<G><<<dim3(gx1, 1, pg), 1024, smem, c->st>>>(last.p, pt, nullptr, l, nbp, c->pc, N, qi, c->dev_err);
+        LimbMap lm{}; lm.n = 1; lm.prime[0] = (unsigned char)l;
+        ntt_inplace(c, last.p, gnbp, lm, true);
+        LAUNCH(c), k_centre_sum<<<dim3(c->gx(), gnbp), 256, 0, c->st>>>((i64 *)S.p, last.p, 1, gnbp, l, c->pc, N);
+        LAUNCH(c), k_lift_mod<<<c->egrid(gnbp * l), 256, 0, c->st>>>(t.p, (const i64 *)S.p, l, c->pc, N);
+        ntt_inplace(c, t.p, gnbp * l, c->qmap(l - 1), false);
+        LAUNCH(c), k_prod_parts<G><<<dim3(gx1, (unsigned)l, pg), 1024, smem, c->st>>>(r->d, pt, t.p, l, nbp, c->pc, N, qi, c->dev_err);
+        CK(cudaGetLastError());
+    } catch (...) { hb_ct_free(r); throw; }
+    return r;
+}
 hb_ct *do_level_down(hb_ctx *c, const hb_ct *a, int target) {
     own(c, a);
     if (target > a->level || target < 0) fail(HB_E_LEVEL, "level_down: bad target");
@@ -1331,57 +1384,90 @@ int hb_assemble_masked_multi(hb_ctx *c, const hb_ct *a, const hb_digits *dg, con
 int hb_tensor_acc_groups(hb_ctx *c, const hb_ct *a, const hb_ct *b, int groups, hb_ct **acc) { return guard(c, [&] { *acc = do_tensor(c, a, b, *acc, groups); }); }
 // sum_t rot(xs[t], steps[t]): every term is decomposed, the inner products of all terms are added up in Q_level u P by
 // one kernel, and one ModDown serves the sum; unrotated terms (step 0) are added as they are.
+// sum_t rot(x_t, steps[t]) with one ModDown; x_t = `batch` members starting at base[t] (all of one shape)
+static hb_ct *rotate_sum_core(hb_ctx *c, const u64 *const *base, const int64_t *steps, int count, int level, int batch, int spow, const u64 *dt_all, size_t dt_term_stride) {
+    const int N = c->N;
+    const KsPlan *pl = get_plan(c, level);
+    const PlanDims d = plan_dims(c, level);
+    const int n = d.n, ne = d.ne, K = d.K;
+    const size_t ct_outer = (size_t)2 * n * N;
+    RotTermList rot{}; PlainTermList plain{};
+    std::vector<u64 *> dts;
+    hb_ct *r = new_ct(c, level, 2, batch, spow);
+    try {
+        for (int t = 0; t < count; ++t) {
+            const u64 g = c->h->galois_rot(steps[t]);
+            if (g == 1) {
+                if (plain.count == 16) fail(HB_E_LIMIT, "rotate_sum: at most 16 unrotated terms");
+                plain.x[plain.count++] = base[t];
+                continue;
+            }
+            if (rot.count == 16) fail(HB_E_LIMIT, "rotate_sum: at most 16 rotated terms");
+            const Evk &key = galois_key(c, g);
+            const u64 *dt;
+            if (dt_all) dt = dt_all + (size_t)t * dt_term_stride;
+            else {
+                u64 *fresh = c->alloc_limbs((size_t)batch * d.dt_count);
+                dts.push_back(fresh);
+                ks_decompose(c, base[t] + (size_t)n * N, ct_outer, level, batch, fresh);
+                dt = fresh;
+            }
+            rot.t[rot.count++] = RotTerm{base[t] + (size_t)n * N, dt, key.d, (u32)g, 0u};
+        }
+        const unsigned gx = c->gx();
+        ALG(c, (size_t)(count + 1) * batch * 2 * n + (size_t)rot.count * key_limbs(c, level));
+        Tmp add(c, (size_t)batch * 2 * n);
+        LAUNCH(c), k_rot_sum_addend<<<dim3(gx, n, batch * 2), 256, 0, c->st>>>(add.p, rot, plain, n, c->qmap(level), c->pc, c->logn, N);
+        if (rot.count == 0) {
+            CK(cudaMemcpyAsync(r->d, add.p, r->limbs() * N * 8, cudaMemcpyDeviceToDevice, c->st));
+        } else {
+            Tmp acc(c, (size_t)batch * 2 * ne), pco(c, (size_t)batch * 2 * K), t(c, (size_t)batch * 2 * n);
+            LAUNCH(c), k_ks_inner_sum<<<dim3(gx, batch, ne), 256, 0, c->st>>>(acc.p, rot, ct_outer, c->nprimes, pl, c->pc, c->logn, N);
+            moddown(c, acc.p, pco.p, t.p, level, batch, r->d, ct_outer, add.p, add.p + (size_t)n * N, ct_outer, 0u);
+        }
+        CK(cudaGetLastError());
+    } catch (...) { for (u64 *p : dts) c->pool.put(p); hb_ct_free(r); throw; }
+    for (u64 *p : dts) c->pool.put(p);
+    return r;
+}
 int hb_rotate_sum(hb_ctx *c, const hb_ct *const *xs, const int64_t *steps, int count, hb_ct **out) {
     return guard(c, [&] {
         if (count < 1 || count > 32 || !xs || !steps) fail(HB_E_LIMIT, "rotate_sum: 1 to 32 terms");
         const hb_ct *x0 = xs[0];
         for (int t = 0; t < count; ++t)
             if (!xs[t] || xs[t]->np != 2 || xs[t]->level != x0->level || xs[t]->batch != x0->batch || xs[t]->spow != x0->spow) fail(HB_E_SHAPE, "rotate_sum: operands differ in shape");
-        for (int t = 0; t < count; ++t) own(c, xs[t]);
-        const int level = x0->level, batch = x0->batch, N = c->N;
-        const KsPlan *pl = get_plan(c, level);
+        std::vector<const u64 *> base((size_t)count);
+        for (int t = 0; t < count; ++t) { own(c, xs[t]); base[(size_t)t] = xs[t]->d; }
+        *out = rotate_sum_core(c, base.data(), steps, count, x0->level, x0->batch, x0->spow, nullptr, 0);
+    });
+}
+// the same when the terms are the member groups of one ciphertext (group t = members t * batch/groups ...): the digits of
+// all groups are lifted by one batched call
+int hb_rotate_sum_grouped(hb_ctx *c, const hb_ct *x, const int64_t *steps, int groups, hb_ct **out) {
+    return guard(c, [&] {
+        if (!x || !steps || groups < 1 || groups > 32) fail(HB_E_LIMIT, "rotate_sum: 1 to 32 terms");
+        own(c, x);
+        if (x->np != 2 || x->batch % groups) fail(HB_E_SHAPE, "rotate_sum: the batch does not split into that many groups");
+        const int level = x->level, batch = x->batch / groups, N = c->N;
         const PlanDims d = plan_dims(c, level);
-        const int n = d.n, ne = d.ne, K = d.K;
-        const size_t ct_outer = (size_t)2 * n * N;
-        RotTermList rot{}; PlainTermList plain{};
-        std::vector<u64 *> dts;
-        hb_ct *r = new_ct(c, level, 2, batch, x0->spow);
-        try {
-            for (int t = 0; t < count; ++t) {
-                const u64 g = c->h->galois_rot(steps[t]);
-                if (g == 1) {
-                    if (plain.count == 16) fail(HB_E_LIMIT, "rotate_sum: at most 16 unrotated terms");
-                    plain.x[plain.count++] = xs[t]->d;
-                    continue;
-                }
-                if (rot.count == 16) fail(HB_E_LIMIT, "rotate_sum: at most 16 rotated terms");
-                const Evk &key = galois_key(c, g);
-                u64 *dt = c->alloc_limbs((size_t)batch * d.dt_count);
-                dts.push_back(dt);
-                ks_decompose(c, xs[t]->d + (size_t)n * N, ct_outer, level, batch, dt);
-                rot.t[rot.count++] = RotTerm{xs[t]->d + (size_t)n * N, dt, key.d, (u32)g, 0u};
-            }
-            const unsigned gx = c->gx();
-            ALG(c, (size_t)(count + 1) * batch * 2 * n + (size_t)rot.count * key_limbs(c, level));
-            Tmp add(c, (size_t)batch * 2 * n);
-            LAUNCH(c), k_rot_sum_addend<<<dim3(gx, n, batch * 2), 256, 0, c->st>>>(add.p, rot, plain, n, c->qmap(level), c->pc, c->logn, N);
-            if (rot.count == 0) {
-                CK(cudaMemcpyAsync(r->d, add.p, r->limbs() * N * 8, cudaMemcpyDeviceToDevice, c->st));
-            } else {
-                Tmp acc(c, (size_t)batch * 2 * ne), pco(c, (size_t)batch * 2 * K), t(c, (size_t)batch * 2 * n);
-                LAUNCH(c), k_ks_inner_sum<<<dim3(gx, batch, ne), 256, 0, c->st>>>(acc.p, rot, ct_outer, c->nprimes, pl, c->pc, c->logn, N);
-                moddown(c, acc.p, pco.p, t.p, level, batch, r->d, ct_outer, add.p, add.p + (size_t)n * N, ct_outer, 0u);
-            }
-            CK(cudaGetLastError());
-        } catch (...) { for (u64 *p : dts) c->pool.put(p); hb_ct_free(r); throw; }
-        for (u64 *p : dts) c->pool.put(p);
-        *out = r;
+        const size_t ct_outer = (size_t)2 * d.n * N, dt_stride = (size_t)batch * d.dt_count * N;
+        std::vector<const u64 *> base((size_t)groups);
+        for (int t = 0; t < groups; ++t) base[(size_t)t] = x->d + (size_t)t * batch * ct_outer;
+        Tmp dt(c, (size_t)x->batch * d.dt_count);
+        ks_decompose(c, x->d + (size_t)d.n * N, ct_outer, level, x->batch, dt.p);
+        *out = rotate_sum_core(c, base.data(), steps, groups, level, batch, x->spow, dt.p, dt_stride);
     });
 }
 int hb_rotate(hb_ctx *c, const hb_ct *a, int64_t steps, hb_ct **out) { return guard(c, [&] { *out = do_galois(c, a, c->h->galois_rot(steps)); }); }
 int hb_conjugate(hb_ctx *c, const hb_ct *a, hb_ct **out) { return guard(c, [&] { *out = do_galois(c, a, c->h->galois_conj()); }); }
 int hb_ntt(hb_ctx *c, hb_ct *a, int inverse) { return guard(c, [&] { own(c, a); ntt_inplace(c, a->d, (int)a->limbs(), c->qmap(a->level), inverse != 0); }); }
 
+int hb_mul_pt_sum_parts(hb_ctx *c, const hb_ct *const *a, const hb_pt *const *p, int count, int parts, hb_ct **out) {
+    return guard(c, [&] {
+        if (!a || !p) fail(HB_E_ARG, "product sums: null argument");
+        *out = do_prod_rescale_parts(c, a, p, count, parts);
+    });
+}
 int hb_mul2_add_rescale(hb_ctx *c, const hb_ct *a, const hb_pt *pa, const hb_ct *b, const hb_pt *pb, hb_ct **out) {
     return guard(c, [&] {
         const hb_ct *as[2] = {a, b};

@@ -305,6 +305,99 @@ __global__ void k_prod_rescale_fin(u64 *__restrict__ out, TermList tl, const u64
     for (int u = 0; u < kElems; ++u) op[u * blockDim.x] = mul_mod_any(sub_mod(v[u], tp[u * blockDim.x], m.q), qlinv.v[l], m);
 }
 
+// ---- the same for all giant-step parts of a baby-step / giant-step transform at once ----
+// A transform with bs baby rotations a_j and 2 gs parts computes  out_g = rescale(sum_j a_j (.) p_gj): every part reads
+// the same a_j.  One pass per limb keeps a part accumulator per g in registers and reads every a_j once (and, for
+// primes below 2^44, converts it once) instead of once per part; the masks p_gj are shared by all members and come
+// from L2.  Absent terms of a part are null pointers.
+constexpr int kMaxParts = 17, kMaxPartTerms = 17;
+struct PartTerms { const u64 *a[kMaxPartTerms]; const u64 *p[kMaxParts][kMaxPartTerms]; int count, parts; };
+// A CTA of 1024 threads keeps the mask chunks of G parts for its 256 coefficients of one limb in shared memory (bulk
+// copies, up to G * 17 chunks of 2 KB, one mbarrier, bounded wait) and walks over the batch members, four at a time
+// (thread = coefficient + 256 * member slot): the masks cross L2 once per CTA instead of once per member, the a_j of a
+// member are read by the ceil(parts / G) CTAs of the chunk (from L2 after the first), and every thread has the next
+// two a_j in flight while it works on the current one.
+// t == nullptr: raw sums of limb `level`, out[(g * nbp + bp) * N + x]                       grid = (N/256, 1, ceil(parts/G))
+// else: out[((g * nbp + bp) * level + l) * N + x] = (sum - t[same]) * q_level^-1 mod q_l      grid = (N/256, level, ceil(parts/G))
+template <int G>
+__global__ void __launch_bounds__(1024, 1) k_prod_parts(u64 *__restrict__ out, const __grid_constant__ PartTerms pt, const u64 *__restrict__ t, int level, int nbp,
+                                                        const PrimeConst *__restrict__ pc, int N, const __grid_constant__ Scalars qlinv, int *__restrict__ err) {
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    __shared__ __align__(8) u64 bar;
+    u64 *ptile = reinterpret_cast<u64 *>(smem_raw); // [G][count][256]
+    const int tid = threadIdx.x, lane = tid & 255, slot = tid >> 8;
+    const int l = t ? (int)blockIdx.y : level, g0 = blockIdx.z * G, count = pt.count;
+    const int gn = min(G, pt.parts - g0);
+    const u32 x0 = blockIdx.x * 256;
+    if (tid == 0) { mbar_init(&bar, 1); mbar_fence_init(); }
+    __syncthreads();
+    if (tid < 32) {
+        if (tid == 0) {
+            u32 present = 0;
+            for (int ci = 0; ci < gn * count; ++ci) present += pt.p[g0 + ci / count][ci % count] != nullptr;
+            mbar_arrive_expect_tx(&bar, present * 2048u);
+        }
+        __syncwarp();
+        for (int ci = tid; ci < gn * count; ci += 32) {
+            const u64 *src = pt.p[g0 + ci / count][ci % count];
+            if (src) bulk_load(ptile + (size_t)ci * 256, src + (size_t)l * N + x0, 2048u, &bar);
+        }
+    }
+    u32 have[G]; // bit j: part g0 + g has term j
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+        have[g] = 0;
+        if (g < gn)
+            for (int j = 0; j < count; ++j) have[g] |= (pt.p[g0 + g][j] != nullptr ? 1u : 0u) << j;
+    }
+    mbar_wait_bounded(&bar, 0, err);
+    const PrimeConst m = pc[l];
+    const u64 qli = t ? qlinv.v[l] : 0;
+    for (int bp = slot; bp < nbp; bp += 4) {
+        const size_t ao = ((size_t)bp * (level + 1) + l) * N + x0 + lane;
+        u64 v[G];
+        u64 a_cur = pt.a[0][ao], a_nxt = count > 1 ? pt.a[1][ao] : 0;
+        if (m.fp) {
+            u64 acc[G];
+#pragma unroll
+            for (int g = 0; g < G; ++g) acc[g] = 0;
+            for (int j = 0; j < count; ++j) {
+                const u64 a = a_cur;
+                a_cur = a_nxt;
+                if (j + 2 < count) a_nxt = pt.a[j + 2][ao];
+                const double ad = u52_to_double(a);
+#pragma unroll
+                for (int g = 0; g < G; ++g)
+                    if ((have[g] >> j) & 1u) { const u64 w = ptile[(size_t)(g * count + j) * 256 + lane]; acc[g] += mul_small_lazy_d(a, ad, w, u52_to_double(w), m.q_inv_f, m.q); }
+            }
+#pragma unroll
+            for (int g = 0; g < G; ++g) v[g] = reduce_fp(acc[g], m.q_inv_f, m.q);
+        } else {
+            Acc128 acc[G];
+#pragma unroll
+            for (int g = 0; g < G; ++g) acc[g].zero();
+            for (int j = 0; j < count; ++j) {
+                const u64 a = a_cur;
+                a_cur = a_nxt;
+                if (j + 2 < count) a_nxt = pt.a[j + 2][ao];
+#pragma unroll
+                for (int g = 0; g < G; ++g)
+                    if ((have[g] >> j) & 1u) acc[g].mad(a, ptile[(size_t)(g * count + j) * 256 + lane]);
+            }
+#pragma unroll
+            for (int g = 0; g < G; ++g) v[g] = barrett128(acc[g].hi, acc[g].lo, m);
+        }
+#pragma unroll
+        for (int g = 0; g < G; ++g)
+            if (g < gn) {
+                if (t) {
+                    const size_t w = (((size_t)(g0 + g) * nbp + bp) * level + l) * N + x0 + lane;
+                    out[w] = mul_mod_any(sub_mod(v[g], t[w], m.q), qli, m);
+                } else out[((size_t)(g0 + g) * nbp + bp) * N + x0 + lane] = v[g];
+            }
+    }
+}
+
 // ---------------- key switching ----------------
 // Per-level plan held in device memory.
 struct KsPlan {

@@ -187,6 +187,9 @@ void hb_digits_free(hb_digits *digits);
  * results, different bits (one rounding instead of one per term); the oracle's Evaluator::rotate_sum is the same
  * arithmetic.  No counterpart in HEaaN. */
 int hb_rotate_sum(hb_ctx *ctx, const hb_ct *const *xs, const int64_t *left_steps, int count, hb_ct **out);
+/* The same when the terms are the member groups of ONE ciphertext (group t = members t * batch / groups onwards): the
+ * digits of all groups are lifted by one batched call.  out has batch / groups members. */
+int hb_rotate_sum_grouped(hb_ctx *ctx, const hb_ct *x, const int64_t *left_steps, int groups, hb_ct **out);
 /* The masked pair of rotations that makes one wrapped copy in the shift loops (MatrixUtils.cpp:1416-1427:
  * two leftRotate, two multWithoutRescale, add, rescale) as one operation:
  *     out = p1 (.) rot(a, s1) + p2 (.) rot(a, s2),   at level(a) - 1.
@@ -222,6 +225,11 @@ int hb_mul2_add_rescale(hb_ctx *ctx, const hb_ct *a, const hb_pt *pa, const hb_c
 /* out = sum_j mult(a[j], p[j])  (each product rescaled, then added) -- the baby-step sums of the linear
  * transforms, MatrixUtils.cpp:815-823, 832-840.  At most 24 terms. */
 int hb_mul_pt_sum(hb_ctx *ctx, const hb_ct *const *a, const hb_pt *const *p, int count, hb_ct **out);
+/* out_g = rescale(sum_j multWithoutRescale(a[j], p[g * count + j])) for g < parts, all parts in one pass over the a[j]
+ * (null plaintexts are skipped; at most 17 terms and 17 parts): the giant-step parts of a baby-step / giant-step
+ * transform (MatrixUtils.cpp:776-1070) share their baby-step rotations.  out holds parts * batch members, part-major;
+ * every part has the residues hb_sum_mul_pt_rescale gives for its terms. */
+int hb_mul_pt_sum_parts(hb_ctx *ctx, const hb_ct *const *a, const hb_pt *const *p, int count, int parts, hb_ct **out);
 /* out = rescale(sum_j a[j] (.) p[j]): the products are added un-rescaled and the sum is rescaled once (one inverse
  * transform of the last limb instead of one per term).  The masked sums of the linear transforms in schedule 2. */
 int hb_sum_mul_pt_rescale(hb_ctx *ctx, const hb_ct *const *a, const hb_pt *const *p, int count, hb_ct **out);
