@@ -353,14 +353,26 @@ __global__ void __launch_bounds__(1024, 1) k_prod_parts(u64 *__restrict__ out, c
     mbar_wait_bounded(&bar, 0, err);
     const PrimeConst m = pc[l];
     const u64 qli = t ? qlinv.v[l] : 0;
+    const double qd = (double)m.q;
+    if (m.fp) { // the masks of a prime below 2^44 become doubles once, for every member that follows
+#pragma unroll
+        for (int g = 0; g < G; ++g)
+            for (int j = slot; j < count; j += 4)
+                if ((have[g] >> j) & 1u) {
+                    u64 *w = ptile + (size_t)(g * count + j) * 256 + lane;
+                    *w = (u64)__double_as_longlong(u52_to_double(*w));
+                }
+        __syncthreads();
+    }
     for (int bp = slot; bp < nbp; bp += 4) {
         const size_t ao = ((size_t)bp * (level + 1) + l) * N + x0 + lane;
         u64 v[G];
         u64 a_cur = pt.a[0][ao], a_nxt = count > 1 ? pt.a[1][ao] : 0;
-        if (m.fp) {
-            u64 acc[G];
+        if (m.fp) { // products entirely on the FP64 pipe, signed double sums (17 terms of at most 0.51 q each)
+            double acc[G];
 #pragma unroll
-            for (int g = 0; g < G; ++g) acc[g] = 0;
+            for (int g = 0; g < G; ++g) acc[g] = 0.0;
+            const double *dtile = reinterpret_cast<const double *>(ptile);
             for (int j = 0; j < count; ++j) {
                 const u64 a = a_cur;
                 a_cur = a_nxt;
@@ -368,10 +380,10 @@ __global__ void __launch_bounds__(1024, 1) k_prod_parts(u64 *__restrict__ out, c
                 const double ad = u52_to_double(a);
 #pragma unroll
                 for (int g = 0; g < G; ++g)
-                    if ((have[g] >> j) & 1u) { const u64 w = ptile[(size_t)(g * count + j) * 256 + lane]; acc[g] += mul_small_lazy_d(a, ad, w, u52_to_double(w), m.q_inv_f, m.q); }
+                    if ((have[g] >> j) & 1u) acc[g] = __dadd_rn(acc[g], mul_fp64_lazy(ad, dtile[(size_t)(g * count + j) * 256 + lane], m.q_inv_f, qd));
             }
 #pragma unroll
-            for (int g = 0; g < G; ++g) v[g] = reduce_fp(acc[g], m.q_inv_f, m.q);
+            for (int g = 0; g < G; ++g) v[g] = canon_fp64(acc[g], m.q_inv_f, qd);
         } else {
             Acc128 acc[G];
 #pragma unroll
