@@ -196,6 +196,9 @@ int hb_hemmer_matmul_reuse(hb_hemmer *h, const hb_ct *pre, const hb_pt *p, SHAPE
 int hb_hemmer_matmul_reuse_groups(hb_hemmer *h, const hb_ct *pre, int btotal, int b0, const hb_pt *const *pts, int bcount, int width, hb_ct **out) {
     return guard([&] { hb_ct *o = nullptr; check(h->ctx, hb_matmul_acc_multi(h->ctx, pre, btotal, b0, pts, bcount, width, &o)); *out = o; });
 }
+int hb_hemmer_matmul_reuse_groups_tiles(hb_hemmer *h, const hb_ct *pre, int btotal, int b0, const hb_pt *const *pts, int bcount, int tiles, int width, hb_ct **out) {
+    return guard([&] { check(h->ctx, hb_matmul_acc_tiles(h->ctx, pre, btotal, b0, pts, bcount, tiles, width, out)); });
+}
 int hb_hemmer_matmul_pre_rev(hb_hemmer *h, const hb_ct *b, SHAPE_ARGS, int target, hb_ct **out) {
     return guard([&] { IN_TENSOR(t, b); *out = h->h.matMulPreRev(t, target).get().release(); });
 }

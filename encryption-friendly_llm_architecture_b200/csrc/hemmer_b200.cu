@@ -607,6 +607,16 @@ hb_ct *do_prod_rescale_parts(hb_ctx *c, const hb_ct *const *a, const hb_pt *cons
     } catch (...) { hb_ct_free(r); throw; }
     return r;
 }
+template <int T>
+void launch_matmul_tiles(hb_ctx *c, const hb_ct *pre, int btotal, int b0, const hb_pt *const *pts, int bcount, int kc, const u32 *dg, hb_ct *const *outs) {
+    TilePts<T> tp{};
+    for (int t = 0; t < T; ++t) {
+        for (int b = 0; b < bcount; ++b) tp.p[t][b] = pts[(size_t)t * bcount + b]->d;
+        tp.out[t] = outs[t]->d;
+    }
+    const int n = pre->level + 1;
+    LAUNCH(c), k_matmul_acc_tiles<T><<<dim3((unsigned)(c->N / 512), (unsigned)(2 * n)), 256, 0, c->st>>>(tp, pre->d, kc, btotal, b0, bcount, dg, n, c->qmap(pre->level), c->pc, c->logn, c->N);
+}
 hb_ct *do_level_down(hb_ctx *c, const hb_ct *a, int target) {
     own(c, a);
     if (target > a->level || target < 0) fail(HB_E_LEVEL, "level_down: bad target");
@@ -1493,6 +1503,45 @@ int hb_matmul_acc_multi(hb_ctx *c, const hb_ct *pre, int btotal, int b0, const h
         ALG(c, (size_t)kc * bcount * 2 * n + (size_t)bcount * n + 2 * n);
         LAUNCH(c), k_matmul_acc<<<c->egrid(2 * n), 256, 0, c->st>>>(r->d, pre->d, kc, btotal, b0, bcount, pl, dg, n, c->qmap(pre->level), c->pc, c->logn, c->N);
         *out = r;
+    });
+}
+// `tiles` outputs from the same shifted copies: out[t] = sum over the groups b of matmul(copies of input b0 + b, pts[t * bcount + b])
+int hb_matmul_acc_tiles(hb_ctx *c, const hb_ct *pre, int btotal, int b0, const hb_pt *const *pts, int bcount, int tiles, int64_t row_step, hb_ct **out) {
+    return guard(c, [&] {
+        if (!pre || !pts || !out || tiles < 1) fail(HB_E_ARG, "matmul_acc: null argument");
+        if (btotal < 1 || pre->batch % btotal || b0 < 0 || bcount < 1 || b0 + bcount > btotal || bcount > 16) fail(HB_E_SHAPE, "matmul_acc: group selection");
+        if (pre->np != 2 || pre->spow != 1) fail(HB_E_SHAPE, "matmul_acc: operands");
+        own(c, pre);
+        for (int i = 0; i < tiles * bcount; ++i) {
+            if (!pts[i]) fail(HB_E_ARG, "matmul_acc: null plaintext");
+            own(c, pts[i]);
+            if (pre->level != pts[i]->level) fail(HB_E_LEVEL, "matmul_acc: plaintext level differs from the ciphertexts'");
+            if (pts[i]->spow != 1) fail(HB_E_SHAPE, "matmul_acc: operands");
+        }
+        if (c->N % 512) { // small rings: tile by tile
+            for (int t = 0; t < tiles; ++t) {
+                int rc = hb_matmul_acc_multi(c, pre, btotal, b0, pts + (size_t)t * bcount, bcount, row_step, &out[t]);
+                if (rc != HB_OK) { for (int u = 0; u < t; ++u) { hb_ct_free(out[u]); out[u] = nullptr; } throw ArgFail{rc, c->err}; }
+            }
+            return;
+        }
+        const int n = pre->level + 1, kc = pre->batch / btotal;
+        const u32 *dg = galois_table(c, kc, row_step);
+        std::vector<hb_ct *> rs((size_t)tiles, nullptr);
+        try {
+            for (int t = 0; t < tiles; ++t) rs[(size_t)t] = new_ct(c, pre->level, 2, 1, 2);
+            ALG(c, (size_t)kc * bcount * 2 * n + (size_t)tiles * ((size_t)bcount * n + 2 * n));
+            int t = 0;
+            while (t < tiles) {
+                const int left = tiles - t;
+                if (left >= 4) { launch_matmul_tiles<4>(c, pre, btotal, b0, pts + (size_t)t * bcount, bcount, kc, dg, rs.data() + t); t += 4; }
+                else if (left == 3) { launch_matmul_tiles<3>(c, pre, btotal, b0, pts + (size_t)t * bcount, bcount, kc, dg, rs.data() + t); t += 3; }
+                else if (left == 2) { launch_matmul_tiles<2>(c, pre, btotal, b0, pts + (size_t)t * bcount, bcount, kc, dg, rs.data() + t); t += 2; }
+                else { launch_matmul_tiles<1>(c, pre, btotal, b0, pts + (size_t)t * bcount, bcount, kc, dg, rs.data() + t); t += 1; }
+            }
+            CK(cudaGetLastError());
+        } catch (...) { for (hb_ct *r : rs) if (r) hb_ct_free(r); throw; }
+        for (int t = 0; t < tiles; ++t) out[t] = rs[(size_t)t];
     });
 }
 int hb_matmul_acc(hb_ctx *c, const hb_ct *pre, const hb_pt *pt, int64_t row_step, hb_ct **out) { return hb_matmul_acc_multi(c, pre, 1, 0, &pt, 1, row_step, out); }

@@ -1239,4 +1239,107 @@ __global__ void k_matmul_acc(u64 *__restrict__ out, const u64 *__restrict__ pre,
     for (int u = 0; u < kElems; ++u) op[u * blockDim.x] = total[u];
 }
 
+// The same for T output tiles that share the shifted copies: a copy word is read once and meets the weights of T tiles
+// (all output tiles of a sublayer multiply the same copies of x), so the copies -- the bulk of the traffic -- cross HBM
+// once per T tiles.  Two coefficients per thread.  Primes below 2^44: products on the FP64 pipe, signed double sums folded
+// every 512 terms (512 * 0.51 q stays far below 2^53).  grid = (N/512, 2*n)
+template <int T> struct TilePts { const u64 *p[T][16]; u64 *out[T]; };
+template <int T>
+__global__ void __launch_bounds__(256) k_matmul_acc_tiles(const __grid_constant__ TilePts<T> tp, const u64 *__restrict__ pre, int kcount, int btotal, int b0, int bcount,
+                                                          const u32 *__restrict__ gal, int n, const __grid_constant__ LimbMap map, const PrimeConst *__restrict__ pc, int logn, int N) {
+    constexpr int E = 2;
+    const int pl = blockIdx.y, l = pl % n;
+    const PrimeConst m = pc[map.prime[l]];
+    const size_t estride = (size_t)2 * n * N;
+    const u32 x0 = blockIdx.x * (blockDim.x * E) + threadIdx.x;
+    const u64 *pbase = pre + (size_t)pl * N + x0;
+    u64 total[T][E];
+#pragma unroll
+    for (int t = 0; t < T; ++t)
+#pragma unroll
+        for (int u = 0; u < E; ++u) total[t][u] = 0;
+    if (m.fp) {
+        const double qd = (double)m.q;
+        double acc[T][E];
+#pragma unroll
+        for (int t = 0; t < T; ++t)
+#pragma unroll
+            for (int u = 0; u < E; ++u) acc[t][u] = 0.0;
+        int terms = 0;
+        for (int k = 0; k < kcount; ++k) {
+            const u32 g = __ldg(gal + k);
+            u32 src[E];
+#pragma unroll
+            for (int u = 0; u < E; ++u) src[u] = g == 1 ? x0 + u * blockDim.x : ntt_perm(x0 + u * blockDim.x, g, logn);
+            for (int b = 0; b < bcount; ++b) {
+                const u64 *a = pbase + ((size_t)k * btotal + b0 + b) * estride;
+                double ad[E];
+#pragma unroll
+                for (int u = 0; u < E; ++u) ad[u] = u52_to_double(a[u * blockDim.x]);
+#pragma unroll
+                for (int t = 0; t < T; ++t) {
+                    const u64 *w = tp.p[t][b] + (size_t)l * N;
+#pragma unroll
+                    for (int u = 0; u < E; ++u) acc[t][u] = __dadd_rn(acc[t][u], mul_fp64_lazy(ad[u], u52_to_double(w[src[u]]), m.q_inv_f, qd));
+                }
+            }
+            terms += bcount;
+            if (terms >= 496) {
+#pragma unroll
+                for (int t = 0; t < T; ++t)
+#pragma unroll
+                    for (int u = 0; u < E; ++u) { total[t][u] = add_mod(total[t][u], canon_fp64(acc[t][u], m.q_inv_f, qd), m.q); acc[t][u] = 0.0; }
+                terms = 0;
+            }
+        }
+#pragma unroll
+        for (int t = 0; t < T; ++t)
+#pragma unroll
+            for (int u = 0; u < E; ++u) total[t][u] = add_mod(total[t][u], canon_fp64(acc[t][u], m.q_inv_f, qd), m.q);
+    } else {
+        Acc128 s[T][E];
+#pragma unroll
+        for (int t = 0; t < T; ++t)
+#pragma unroll
+            for (int u = 0; u < E; ++u) s[t][u].zero();
+        int terms = 0;
+        for (int k = 0; k < kcount; ++k) {
+            const u32 g = __ldg(gal + k);
+            u32 src[E];
+#pragma unroll
+            for (int u = 0; u < E; ++u) src[u] = g == 1 ? x0 + u * blockDim.x : ntt_perm(x0 + u * blockDim.x, g, logn);
+            for (int b = 0; b < bcount; ++b) {
+                const u64 *a = pbase + ((size_t)k * btotal + b0 + b) * estride;
+                u64 av[E];
+#pragma unroll
+                for (int u = 0; u < E; ++u) av[u] = a[u * blockDim.x];
+#pragma unroll
+                for (int t = 0; t < T; ++t) {
+                    const u64 *w = tp.p[t][b] + (size_t)l * N;
+#pragma unroll
+                    for (int u = 0; u < E; ++u) s[t][u].mad(av[u], w[src[u]]);
+                }
+            }
+            terms += bcount;
+            if (terms >= 48) { // products below 2^120: the 128-bit accumulator holds 256 of them
+#pragma unroll
+                for (int t = 0; t < T; ++t)
+#pragma unroll
+                    for (int u = 0; u < E; ++u) { total[t][u] = add_mod(total[t][u], barrett128(s[t][u].hi, s[t][u].lo, m), m.q); s[t][u].zero(); }
+                terms = 0;
+            }
+        }
+#pragma unroll
+        for (int t = 0; t < T; ++t)
+#pragma unroll
+            for (int u = 0; u < E; ++u) total[t][u] = add_mod(total[t][u], barrett128(s[t][u].hi, s[t][u].lo, m), m.q);
+    }
+#pragma unroll
+    for (int t = 0; t < T; ++t) {
+        u64 *op = tp.out[t] + (size_t)pl * N + x0;
+#pragma unroll
+        for (int u = 0; u < E; ++u) op[u * blockDim.x] = total[t][u];
+    }
+}
+
 } // namespace hb

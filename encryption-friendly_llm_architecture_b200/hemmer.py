@@ -260,6 +260,22 @@ class Hemmer:
         ct = self._call("matmul_reuse_groups", pre.ptr, C.c_int(btotal), C.c_int(b0), arr, C.c_int(len(weights)), C.c_int(weights[0].width))
         return CtxtTensor(ct, *weights[0].shape)
 
+    def matmul_reuse_groups_tiles(self, pre, btotal, b0, weights_by_tile):
+        """matmul_reuse_groups for several weight tiles that meet the same copies (all output tiles of a sublayer): one
+        pass over the copies per four tiles where the library has the entry point, tile by tile otherwise."""
+        f = getattr(self.dll, self.prefix + "matmul_reuse_groups_tiles", None)
+        if f is None:
+            return [self.matmul_reuse_groups(pre, btotal, b0, ws) for ws in weights_by_tile]
+        tiles, bcount = len(weights_by_tile), len(weights_by_tile[0])
+        arr = (C.c_void_p * (tiles * bcount))(*[w.ct.ptr.value for ws in weights_by_tile for w in ws])
+        outs = (C.c_void_p * tiles)()
+        rc = f(self.h, pre.ptr, C.c_int(btotal), C.c_int(b0), arr, C.c_int(bcount), C.c_int(tiles), C.c_int(weights_by_tile[0][0].width), outs)
+        if rc != 0:
+            g = self._fn("last_error")
+            g.restype = C.c_char_p
+            raise HBError(rc, g().decode())
+        return [CtxtTensor(Handle(self.lib, C.c_void_p(outs[t]), "ct"), *weights_by_tile[0][0].shape) for t in range(tiles)]
+
     def matmul_pre_rev(self, b, target_level=4):
         return CtxtTensor(self._call("matmul_pre_rev", b.ct.ptr, *self._shp(b), C.c_int(target_level)), *b.shape)
 

@@ -280,20 +280,22 @@ class LayerWorkload:
             packed = H.complex_packing(c01, c23) if c23 is not None else c01
             pres[kind] = (idx, H.matmul_pre(packed, t))
         # every (sublayer, weight, output tile): one fused pass per batch of K-groups, partial sums added
+        # (all output tiles of a sublayer meet the same shifted copies: one call per sublayer and kind of copies)
         for name, xname, weights, kt, nt in self.PCMM:
-            for wname in weights:
-                for j in range(nt):
-                    acc = None
-                    for kind, (idx, pre) in pres.items():
-                        sel = [(b, self.units[i]) for b, i in enumerate(idx) if self.units[i][1] == name]
-                        if not sel:
-                            continue
-                        b0 = sel[0][0]
-                        pts = [self._weight_pts(wname, u[4], kt, nt)[j] for _, u in sel]
-                        part = H.matmul_reuse_groups(pre, len(idx), b0, pts)
-                        acc = part if acc is None else CtxtTensor(self.lib.add(acc.ct, part.ct), *part.shape)
-                    if acc is not None:
-                        out["pcmm"][(name, wname, j)] = acc
+            tags = [(wname, j) for wname in weights for j in range(nt)]
+            accs = [None] * len(tags)
+            for kind, (idx, pre) in pres.items():
+                sel = [(b, self.units[i]) for b, i in enumerate(idx) if self.units[i][1] == name]
+                if not sel:
+                    continue
+                b0 = sel[0][0]
+                by_tile = [[self._weight_pts(wname, u[4], kt, nt)[j] for _, u in sel] for wname, j in tags]
+                parts = H.matmul_reuse_groups_tiles(pre, len(idx), b0, by_tile)
+                for k, part in enumerate(parts):
+                    accs[k] = part if accs[k] is None else CtxtTensor(self.lib.add(accs[k].ct, part.ct), *part.shape)
+            for (wname, j), acc in zip(tags, accs):
+                if acc is not None:
+                    out["pcmm"][(name, wname, j)] = acc
         # ct x ct: one batched transpose for every operand that needs it; the transforms sigma / tau run per group
         # (a transposed tile sits one level lower), then ONE product loop serves all units of this rank
         cc = res["ccmm"]

@@ -120,6 +120,9 @@ int hb_hemmer_matmul_reuse(hb_hemmer *h, const hb_ct *pre, const hb_pt *w, int r
  * of `btotal` inputs.  The sum the reference takes with addInplace over K tiles (bert-matmul.cpp:268-287). */
 int hb_hemmer_matmul_reuse_groups(hb_hemmer *h, const hb_ct *pre, int btotal, int b0, const hb_pt *const *pts, int bcount,
                                   int width, hb_ct **out);
+/* the same for `tiles` weights (pts[t * bcount + b]) that meet the same copies: out[t], t < tiles */
+int hb_hemmer_matmul_reuse_groups_tiles(hb_hemmer *h, const hb_ct *pre, int btotal, int b0, const hb_pt *const *pts, int bcount, int tiles,
+                                        int width, hb_ct **out);
 /* HEMMer::matMulPreRev, matMulCCReUse (HEMMer.cpp:1114-1124; MatrixUtils.cpp:1641-1679) */
 int hb_hemmer_matmul_pre_rev(hb_hemmer *h, const hb_ct *b, int rows, int cols, int width, int target_level, hb_ct **out);
 int hb_hemmer_matmul_cc_reuse(hb_hemmer *h, const hb_ct *pre, const hb_ct *b, int rows, int cols, int width, hb_ct **out);

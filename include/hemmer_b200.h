@@ -244,6 +244,10 @@ int hb_matmul_acc(hb_ctx *ctx, const hb_ct *pre, const hb_pt *pt, int64_t row_st
  * input b at batch position k*btotal + b; the products of inputs b0 .. b0+bcount-1 with pts[0..bcount-1] are
  * summed into one ciphertext (matMulReUse + addInplace over groups, bert-matmul.cpp:262-268) */
 int hb_matmul_acc_multi(hb_ctx *ctx, const hb_ct *pre, int btotal, int b0, const hb_pt *const *pts, int bcount, int64_t row_step, hb_ct **out);
+/* The same for `tiles` outputs that share the shifted copies (all output tiles of a sublayer multiply the same copies of x):
+ * out[t] = sum over b of matmul(copies of input b0 + b, pts[t * bcount + b]); the copies are read once per four tiles. */
+int hb_matmul_acc_tiles(hb_ctx *ctx, const hb_ct *pre, int btotal, int b0, const hb_pt *const *pts, int bcount, int tiles, int64_t row_step,
+                        hb_ct **out);
 /* rotation of a plaintext (pure slot permutation, no key) -- leftRotate(ptxt) used at MatrixUtils.cpp:1503 */
 int hb_pt_rotate(hb_ctx *ctx, const hb_pt *p, int64_t left_steps, hb_pt **out);
 /* mult(ptxt, ptxt) with rescale and add(ptxt, ptxt), as multMatMat<Plaintext> uses them -- MatrixUtils.cpp:1556-1558 */
