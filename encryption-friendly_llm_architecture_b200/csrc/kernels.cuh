@@ -936,11 +936,13 @@ __global__ void __launch_bounds__(256) k_ks_inner_mkb(u64 *__restrict__ E, const
     mbar_wait_bounded(&bar, 0, err);
     const PrimeConst m = pc[pj];
     u64 r0[M][EL], r1[M][EL];
-    if (m.fp) {
+    if (m.fp) { // products on the FP64 pipe, signed double sums of at most 2 * (nd + 1) terms
+        const double qd = (double)m.q;
+        double d0[M][EL], d1[M][EL];
 #pragma unroll
         for (int u = 0; u < M; ++u)
 #pragma unroll
-            for (int e = 0; e < EL; ++e) { r0[u][e] = 0; r1[u][e] = 0; }
+            for (int e = 0; e < EL; ++e) { d0[u][e] = 0.0; d1[u][e] = 0.0; }
         for (int r = 0; r < count; ++r) {
             u32 li[EL];
 #pragma unroll
@@ -950,15 +952,13 @@ __global__ void __launch_bounds__(256) k_ks_inner_mkb(u64 *__restrict__ E, const
                 const u64 *sp = srcb + (size_t)(r * nsrc + dg) * T;
 #pragma unroll
                 for (int e = 0; e < EL; ++e) {
-                    const u64 ka = kp[e * 256], kb = kp[T + e * 256];
-                    const double kad = u52_to_double(ka), kbd = u52_to_double(kb);
+                    const double kad = u52_to_double(kp[e * 256]), kbd = u52_to_double(kp[T + e * 256]);
 #pragma unroll
                     for (int u = 0; u < M; ++u)
                         if (u < nm) {
-                            const u64 v = sp[(size_t)u * count * nsrc * T + li[e]];
-                            const double vd = u52_to_double(v);
-                            r0[u][e] += mul_small_lazy_d(v, vd, ka, kad, m.q_inv_f, m.q);
-                            r1[u][e] += mul_small_lazy_d(v, vd, kb, kbd, m.q_inv_f, m.q);
+                            const double vd = u52_to_double(sp[(size_t)u * count * nsrc * T + li[e]]);
+                            d0[u][e] = __dadd_rn(d0[u][e], mul_fp64_lazy(vd, kad, m.q_inv_f, qd));
+                            d1[u][e] = __dadd_rn(d1[u][e], mul_fp64_lazy(vd, kbd, m.q_inv_f, qd));
                         }
                 }
             }
@@ -966,21 +966,17 @@ __global__ void __launch_bounds__(256) k_ks_inner_mkb(u64 *__restrict__ E, const
                 const u64 *sp = srcb + (size_t)(r * nsrc + nd) * T;
 #pragma unroll
                 for (int e = 0; e < EL; ++e) {
-                    const u64 pmv = pmb[(size_t)r * T + e * 256 + tid];
-                    const double pmd = u52_to_double(pmv);
+                    const double pmd = u52_to_double(pmb[(size_t)r * T + e * 256 + tid]);
 #pragma unroll
                     for (int u = 0; u < M; ++u)
-                        if (u < nm) {
-                            const u64 v = sp[(size_t)u * count * nsrc * T + li[e]];
-                            r0[u][e] += mul_small_lazy_d(v, u52_to_double(v), pmv, pmd, m.q_inv_f, m.q);
-                        }
+                        if (u < nm) d0[u][e] = __dadd_rn(d0[u][e], mul_fp64_lazy(u52_to_double(sp[(size_t)u * count * nsrc * T + li[e]]), pmd, m.q_inv_f, qd));
                 }
             }
         }
 #pragma unroll
         for (int u = 0; u < M; ++u)
 #pragma unroll
-            for (int e = 0; e < EL; ++e) { r0[u][e] = reduce_fp(r0[u][e], m.q_inv_f, m.q); r1[u][e] = reduce_fp(r1[u][e], m.q_inv_f, m.q); }
+            for (int e = 0; e < EL; ++e) { r0[u][e] = canon_fp64(d0[u][e], m.q_inv_f, qd); r1[u][e] = canon_fp64(d1[u][e], m.q_inv_f, qd); }
     } else {
         Acc128 s0[M][EL], s1[M][EL];
 #pragma unroll

@@ -181,3 +181,65 @@ def test_square_and_constant_product(gpu_mid):
     mc = g._op("mul_const", ct.ptr, C.c_double(0.25), C.c_double(-0.5))
     _same(g.ct_export(mc), g.ct_export(g.mul_pt(ct, g.encode(np.full(g.slots, 0.25 - 0.5j), 5))), "mul_const")
     assert np.abs(g.decrypt(mc) - z * (0.25 - 0.5j)).max() < 1e-6
+
+
+@pytest.mark.parametrize("tiles", [1, 2, 5, 7])
+def test_tile_batched_accumulate_equals_tile_by_tile(pkg, gpu_mid, tiles):
+    """hb_matmul_acc_tiles (shifted copies read once per four output tiles, FP64 products, with the 60-bit limb on the
+    integer path) against hb_matmul_acc_multi called per tile: identical residues."""
+    g = gpu_mid
+    rng = np.random.default_rng(60 + tiles)
+    copies, groups, lvl = 16, 3, 3
+    data = np.empty((copies * groups, 2, lvl + 1, g.N), dtype=np.uint64)
+    for l in range(lvl + 1):
+        data[:, :, l, :] = rng.integers(0, int(g.primes[l]), size=(copies * groups, 2, g.N), dtype=np.uint64)
+    data[0, :, :, :] = np.array([int(q) - 1 for q in g.primes[: lvl + 1]], dtype=np.uint64)[None, :, None]   # worst-case words
+    pre = g.ct_create(lvl, 2, copies * groups)
+    g.ct_import(pre, data)
+    pts = [[g.encode(rng.uniform(-1, 1, g.slots), lvl) for _ in range(2)] for _ in range(tiles)]
+    arr = (C.c_void_p * (tiles * 2))(*[p.ptr.value for row in pts for p in row])
+    outs = (C.c_void_p * tiles)()
+    g._chk(g.dll.hb_matmul_acc_tiles(g.ctx, pre.ptr, C.c_int(groups), C.c_int(1), arr, C.c_int(2), C.c_int(tiles), C.c_int64(32), outs))
+    for t in range(tiles):
+        one = C.c_void_p()
+        row = (C.c_void_p * 2)(*[p.ptr.value for p in pts[t]])
+        g._chk(g.dll.hb_matmul_acc_multi(g.ctx, pre.ptr, C.c_int(groups), C.c_int(1), row, C.c_int(2), C.c_int64(32), C.byref(one)))
+        _same(g.ct_export(pkg.capi.Handle(g, C.c_void_p(outs[t]), "ct")), g.ct_export(pkg.capi.Handle(g, one, "ct")), f"tile {t}")
+
+
+def test_part_sums_and_grouped_rotate_sum_equal_the_term_by_term_calls(pkg, gpu_mid):
+    """hb_mul_pt_sum_parts against hb_sum_mul_pt_rescale per part (parts with different term sets, one of a single term),
+    then hb_rotate_sum_grouped on the part-major result against hb_rotate_sum on the separate parts."""
+    g = gpu_mid
+    rng = np.random.default_rng(77)
+    lvl, terms, parts, batch = 4, 6, 5, 3
+    cts = []
+    for j in range(terms):
+        data = rand_ct_residues(g, lvl, 2, batch, seed=300 + j)
+        ct = g.ct_create(lvl, 2, batch)
+        g.ct_import(ct, data)
+        cts.append(ct)
+    use = [[0], [1, 2, 3], [1, 2, 3, 4, 5], [2], [3, 4]]
+    masks = [{j: g.encode(rng.uniform(-1, 1, g.slots), lvl) for j in use[p]} for p in range(parts)]
+    a = (C.c_void_p * terms)(*[c.ptr.value for c in cts])
+    pp = (C.c_void_p * (parts * terms))(*[masks[p][j].ptr.value if j in masks[p] else None for p in range(parts) for j in range(terms)])
+    out = C.c_void_p()
+    g._chk(g.dll.hb_mul_pt_sum_parts(g.ctx, a, pp, C.c_int(terms), C.c_int(parts), C.byref(out)))
+    grouped = pkg.capi.Handle(g, out, "ct")
+    got = g.ct_export(grouped)
+    singles = []
+    for p in range(parts):
+        aa = (C.c_void_p * len(use[p]))(*[cts[j].ptr.value for j in use[p]])
+        mm = (C.c_void_p * len(use[p]))(*[masks[p][j].ptr.value for j in use[p]])
+        one = C.c_void_p()
+        g._chk(g.dll.hb_sum_mul_pt_rescale(g.ctx, aa, mm, C.c_int(len(use[p])), C.byref(one)))
+        singles.append(pkg.capi.Handle(g, one, "ct"))
+        _same(got[p * batch:(p + 1) * batch], g.ct_export(singles[-1]), f"part {p}")
+    steps = [0, 3, -5, 64, 7]
+    g.gen_rot_keys([s for s in steps if s])
+    st = (C.c_int64 * parts)(*steps)
+    r1, r2 = C.c_void_p(), C.c_void_p()
+    g._chk(g.dll.hb_rotate_sum_grouped(g.ctx, grouped.ptr, st, C.c_int(parts), C.byref(r1)))
+    xs = (C.c_void_p * parts)(*[s.ptr.value for s in singles])
+    g._chk(g.dll.hb_rotate_sum(g.ctx, xs, st, C.c_int(parts), C.byref(r2)))
+    _same(g.ct_export(pkg.capi.Handle(g, r1, "ct")), g.ct_export(pkg.capi.Handle(g, r2, "ct")), "grouped rotate-sum")
