@@ -481,23 +481,24 @@ __global__ void k_ks_inner(u64 *__restrict__ acc, const u64 *__restrict__ a_ntt,
     const u64 *kbase = key + (size_t)pj * N + x0;
     const size_t kpoly = (size_t)key_primes * N;
     u64 r0[kElems], r1[kElems];
-    if (m.fp) {
+    if (m.fp) { // products on the FP64 pipe, signed double sums
+        const double qd = (double)m.q;
+        double d0[kElems], d1[kElems];
 #pragma unroll
-        for (int u = 0; u < kElems; ++u) { r0[u] = 0; r1[u] = 0; }
+        for (int u = 0; u < kElems; ++u) { d0[u] = 0.0; d1[u] = 0.0; }
         for (int dg = 0; dg < nd; ++dg) {
             const int en = pl->dt_entry[dg][j];
             const u64 *sp = en < 0 ? abase : dbase + (size_t)en * N;
             const u64 *k0 = kbase + (size_t)dg * 2 * kpoly;
 #pragma unroll
             for (int u = 0; u < kElems; ++u) {
-                const u64 v = sp[src[u]], ka = k0[u * blockDim.x], kb = k0[kpoly + u * blockDim.x];
-                const double vd = u52_to_double(v);
-                r0[u] += mul_small_lazy_d(v, vd, ka, u52_to_double(ka), m.q_inv_f, m.q);
-                r1[u] += mul_small_lazy_d(v, vd, kb, u52_to_double(kb), m.q_inv_f, m.q);
+                const double vd = u52_to_double(sp[src[u]]);
+                d0[u] = __dadd_rn(d0[u], mul_fp64_lazy(vd, u52_to_double(k0[u * blockDim.x]), m.q_inv_f, qd));
+                d1[u] = __dadd_rn(d1[u], mul_fp64_lazy(vd, u52_to_double(k0[kpoly + u * blockDim.x]), m.q_inv_f, qd));
             }
         }
 #pragma unroll
-        for (int u = 0; u < kElems; ++u) { r0[u] = reduce_fp(r0[u], m.q_inv_f, m.q); r1[u] = reduce_fp(r1[u], m.q_inv_f, m.q); }
+        for (int u = 0; u < kElems; ++u) { r0[u] = canon_fp64(d0[u], m.q_inv_f, qd); r1[u] = canon_fp64(d1[u], m.q_inv_f, qd); }
     } else {
         Acc128 s0[kElems], s1[kElems];
 #pragma unroll
@@ -590,9 +591,11 @@ __global__ void k_ks_inner_sum(u64 *__restrict__ acc, RotTermList tl, size_t a_o
     const u32 x0 = blockIdx.x * (blockDim.x * kElems) + threadIdx.x;
     const size_t kpoly = (size_t)key_primes * N;
     u64 r0[kElems], r1[kElems];
-    if (m.fp) { // at most 16 terms x 4 digits lazy products below 1.6q: the sums stay below 2^49
+    if (m.fp) { // at most 16 terms x 8 digits of products within 0.51 q of zero: signed double sums far below 2^53
+        const double qd = (double)m.q;
+        double d0[kElems], d1[kElems];
 #pragma unroll
-        for (int u = 0; u < kElems; ++u) { r0[u] = 0; r1[u] = 0; }
+        for (int u = 0; u < kElems; ++u) { d0[u] = 0.0; d1[u] = 0.0; }
         for (int t = 0; t < tl.count; ++t) {
             u32 src[kElems];
 #pragma unroll
@@ -606,15 +609,14 @@ __global__ void k_ks_inner_sum(u64 *__restrict__ acc, RotTermList tl, size_t a_o
                 const u64 *k0 = kbase + (size_t)dg * 2 * kpoly;
 #pragma unroll
                 for (int u = 0; u < kElems; ++u) {
-                    const u64 v = sp[src[u]], ka = k0[u * blockDim.x], kb = k0[kpoly + u * blockDim.x];
-                    const double vd = u52_to_double(v);
-                    r0[u] += mul_small_lazy_d(v, vd, ka, u52_to_double(ka), m.q_inv_f, m.q);
-                    r1[u] += mul_small_lazy_d(v, vd, kb, u52_to_double(kb), m.q_inv_f, m.q);
+                    const double vd = u52_to_double(sp[src[u]]);
+                    d0[u] = __dadd_rn(d0[u], mul_fp64_lazy(vd, u52_to_double(k0[u * blockDim.x]), m.q_inv_f, qd));
+                    d1[u] = __dadd_rn(d1[u], mul_fp64_lazy(vd, u52_to_double(k0[kpoly + u * blockDim.x]), m.q_inv_f, qd));
                 }
             }
         }
 #pragma unroll
-        for (int u = 0; u < kElems; ++u) { r0[u] = reduce_fp(r0[u], m.q_inv_f, m.q); r1[u] = reduce_fp(r1[u], m.q_inv_f, m.q); }
+        for (int u = 0; u < kElems; ++u) { r0[u] = canon_fp64(d0[u], m.q_inv_f, qd); r1[u] = canon_fp64(d1[u], m.q_inv_f, qd); }
     } else {   // 64 products below 2^120 fit the 128-bit accumulator
         Acc128 s0[kElems], s1[kElems];
 #pragma unroll
@@ -816,9 +818,11 @@ __global__ void __launch_bounds__(256, EL == 2 ? 3 : 2) k_ks_inner_mk(u64 *__res
     const u64 *dbase = dt + (size_t)b * pl->dt_count * N;
     const size_t kpoly = (size_t)ne * N;
     u64 r0[EL], r1[EL];
-    if (m.fp) {
+    if (m.fp) { // products on the FP64 pipe, signed double sums
+        const double qd = (double)m.q;
+        double d0[EL], d1[EL];
 #pragma unroll
-        for (int u = 0; u < EL; ++u) { r0[u] = 0; r1[u] = 0; }
+        for (int u = 0; u < EL; ++u) { d0[u] = 0.0; d1[u] = 0.0; }
         for (int r = 0; r < mr.count; ++r) {
             u32 src[EL];
 #pragma unroll
@@ -830,20 +834,19 @@ __global__ void __launch_bounds__(256, EL == 2 ? 3 : 2) k_ks_inner_mk(u64 *__res
                 const u64 *k0 = kbase + (size_t)dg * 2 * kpoly;
 #pragma unroll
                 for (int u = 0; u < EL; ++u) {
-                    const u64 v = sp[src[u]], ka = k0[u * blockDim.x], kb = k0[kpoly + u * blockDim.x];
-                    const double vd = u52_to_double(v);
-                    r0[u] += mul_small_lazy_d(v, vd, ka, u52_to_double(ka), m.q_inv_f, m.q);
-                    r1[u] += mul_small_lazy_d(v, vd, kb, u52_to_double(kb), m.q_inv_f, m.q);
+                    const double vd = u52_to_double(sp[src[u]]);
+                    d0[u] = __dadd_rn(d0[u], mul_fp64_lazy(vd, u52_to_double(k0[u * blockDim.x]), m.q_inv_f, qd));
+                    d1[u] = __dadd_rn(d1[u], mul_fp64_lazy(vd, u52_to_double(k0[kpoly + u * blockDim.x]), m.q_inv_f, qd));
                 }
             }
             if (j < n) {
                 const u64 *pmb = mr.pm[r] + (size_t)j * N + x0;
 #pragma unroll
-                for (int u = 0; u < EL; ++u) r0[u] += mul_small_lazy(cbase[src[u]], pmb[u * blockDim.x], m.q_inv_f, m.q);
+                for (int u = 0; u < EL; ++u) d0[u] = __dadd_rn(d0[u], mul_fp64_lazy(u52_to_double(cbase[src[u]]), u52_to_double(pmb[u * blockDim.x]), m.q_inv_f, qd));
             }
         }
 #pragma unroll
-        for (int u = 0; u < EL; ++u) { r0[u] = reduce_fp(r0[u], m.q_inv_f, m.q); r1[u] = reduce_fp(r1[u], m.q_inv_f, m.q); }
+        for (int u = 0; u < EL; ++u) { r0[u] = canon_fp64(d0[u], m.q_inv_f, qd); r1[u] = canon_fp64(d1[u], m.q_inv_f, qd); }
     } else {
         Acc128 s0[EL], s1[EL];
 #pragma unroll
