@@ -767,6 +767,7 @@ int hb_ctx_create(const hb_params *prm, int device, hb_ctx **out) {
         const bool big = c->logn == 16;   // 2^16 coefficients: tables in the order the two-pass kernels read them
         std::vector<u64> tw(big ? 0 : (size_t)4 * np * N);
         std::vector<ulonglong2> t16(big ? (size_t)2 * np * Ntt16Layout::kEntries : 0);
+        std::vector<double> b8(big ? (size_t)2 * np * kRowsB8 : 0);
         for (int i = 0; i < np; ++i) {
             const u64 q = c->h->q[i];
             PrimeConst &p = pcs[i];
@@ -798,6 +799,10 @@ int hb_ctx_create(const hb_params *prm, int device, hb_ctx **out) {
                 auto word = [&](u64 w) { return p.small ? ds_twiddle_word(w) : w; };
                 ntt16_fill_table(&t16[(size_t)i * Ntt16Layout::kEntries], [&](unsigned k) { return make_ulonglong2(word(f[k]), fs[k]); });
                 ntt16_fill_table(&t16[((size_t)np + i) * Ntt16Layout::kEntries], [&](unsigned k) { return make_ulonglong2(word(iv[k]), ivs[k]); });
+                if (p.small) {
+                    ntt16_fill_rows_b8(&b8[(size_t)i * kRowsB8], [&](unsigned k) { return (double)f[k]; });
+                    ntt16_fill_rows_b8(&b8[((size_t)np + i) * kRowsB8], [&](unsigned k) { return (double)iv[k]; });
+                }
             } else {
                 std::memcpy(&tw[((size_t)0 * np + i) * N], f.data(), (size_t)N * 8);
                 std::memcpy(&tw[((size_t)1 * np + i) * N], fs.data(), (size_t)N * 8);
@@ -808,10 +813,13 @@ int hb_ctx_create(const hb_params *prm, int device, hb_ctx **out) {
         CK(cudaMalloc(&c->pc, sizeof(PrimeConst) * np));
         CK(cudaMemcpy(c->pc, pcs.data(), sizeof(PrimeConst) * np, cudaMemcpyHostToDevice));
         if (big) {
-            CK(cudaMalloc(&c->tw, t16.size() * sizeof(ulonglong2)));
-            CK(cudaMemcpy(c->tw, t16.data(), t16.size() * sizeof(ulonglong2), cudaMemcpyHostToDevice));
+            const size_t t16_bytes = t16.size() * sizeof(ulonglong2);
+            CK(cudaMalloc(&c->tw, t16_bytes + b8.size() * sizeof(double)));
+            CK(cudaMemcpy(c->tw, t16.data(), t16_bytes, cudaMemcpyHostToDevice));
+            CK(cudaMemcpy(reinterpret_cast<char *>(c->tw) + t16_bytes, b8.data(), b8.size() * sizeof(double), cudaMemcpyHostToDevice));
             const ulonglong2 *t = reinterpret_cast<const ulonglong2 *>(c->tw);
-            c->tb.t16 = Ntt16Tables{t, t + (size_t)np * Ntt16Layout::kEntries};
+            const double *tb8 = reinterpret_cast<const double *>(reinterpret_cast<const char *>(c->tw) + t16_bytes);
+            c->tb.t16 = Ntt16Tables{t, t + (size_t)np * Ntt16Layout::kEntries, tb8, tb8 + (size_t)np * kRowsB8};
         } else {
             CK(cudaMalloc(&c->tw, tw.size() * 8));
             CK(cudaMemcpy(c->tw, tw.data(), tw.size() * 8, cudaMemcpyHostToDevice));

@@ -50,7 +50,14 @@ struct Ntt16Layout {
     static __host__ __device__ constexpr int rowsB(int row, int j, int clo) { return kRowsB + (row * 15 + j) * 16 + clo; }
 };
 // entry: x = w, y = companion (bits of the double w/q for primes below 2^44, Shoup quotient otherwise)
-struct Ntt16Tables { const ulonglong2 *fwd, *inv; }; // each [nprimes][Ntt16Layout::kEntries]
+struct Ntt16Tables {
+    const ulonglong2 *fwd, *inv; // each [nprimes][Ntt16Layout::kEntries]
+    // the last round of the row pass for primes below 2^44: the twiddle alone as a double, [nprimes][kRowsB8], entry j of
+    // lane clo of row `row` at (row * 15 + j) * 16 + clo -- half the bytes of the 16-byte entries, and in that round every
+    // thread reads 15 twiddles nobody else uses (more bytes than the coefficients themselves)
+    const double *fwdB8, *invB8;
+};
+constexpr int kRowsB8 = 256 * 15 * 16;
 
 // Fills one prime's table from psi^bitrev(k) (k < 2^16) and the companion words; host side.
 template <class F> inline void ntt16_fill_table(ulonglong2 *out, F entry /* (index into the bit-reversed table) -> ulonglong2 */) {
@@ -66,6 +73,16 @@ template <class F> inline void ntt16_fill_table(ulonglong2 *out, F entry /* (ind
             const unsigned base = ((256u + (unsigned)row) << 4) + (unsigned)clo;
             for (int s = 0; s < 4; ++s)
                 for (int g = 0; g < (1 << s); ++g) out[Ntt16Layout::rowsB(row, (1 << s) - 1 + g, clo)] = entry((base << s) + (unsigned)g);
+        }
+}
+
+// the compact last-round table of one prime below 2^44: w(k) = the twiddle of bit-reversed-table index k as a double
+template <class F> inline void ntt16_fill_rows_b8(double *out, F w) {
+    for (int row = 0; row < 256; ++row)
+        for (int clo = 0; clo < 16; ++clo) {
+            const unsigned base = ((256u + (unsigned)row) << 4) + (unsigned)clo;
+            for (int s = 0; s < 4; ++s)
+                for (int g = 0; g < (1 << s); ++g) out[(row * 15 + (1 << s) - 1 + g) * 16 + clo] = w((base << s) + (unsigned)g);
         }
 }
 
@@ -156,6 +173,14 @@ __device__ __forceinline__ double ds_mul(double y, u64 w, double wf, const DsCon
     return __hiloint2double((int)hi, (int)(u32)r) - c.coff;
 }
 #endif
+// the same with the quotient estimated from the rounded product instead of from a precomputed w / q (one operand less to
+// fetch; the estimate is off by less than 0.07, so the result lies within 0.57 q of zero)
+__device__ __forceinline__ double ds_mul_w(double y, double wd, const DsConst &c) {
+    const double p = __dmul_rn(y, wd);
+    const double e = __fma_rn(y, wd, -p);
+    const double qh = __dadd_rn(__fma_rn(p, c.qinv, kMagic), -kMagic);
+    return __dadd_rn(__fma_rn(-qh, c.qd, p), e);
+}
 // the form of a twiddle w that ds_mul takes as its second operand
 __host__ __device__ __forceinline__ u64 ds_twiddle_word(u64 w) {
 #if HB_DS_FP
@@ -198,6 +223,41 @@ template <int STRIDE> __device__ __forceinline__ void fwd16_ds(double (&v)[16], 
             }
         }
     }
+}
+template <int STRIDE> __device__ __forceinline__ void fwd16_ds8(double (&v)[16], const double *__restrict__ tp, const DsConst &c) {
+#pragma unroll
+    for (int s = 0; s < 4; ++s) {
+        const int half = 8 >> s;
+#pragma unroll
+        for (int g = 0; g < (1 << s); ++g) {
+            const double wd = __ldg(tp + ((1 << s) - 1 + g) * STRIDE);
+#pragma unroll
+            for (int j = 0; j < half; ++j) {
+                double &x = v[g * 2 * half + j], &y = v[g * 2 * half + j + half];
+                const double t = ds_mul_w(y, wd, c);
+                y = x - t;
+                x = x + t;
+            }
+        }
+    }
+}
+template <int STRIDE> __device__ __forceinline__ void inv16_ds8(double (&v)[16], const double *__restrict__ tp, const DsConst &c) {
+#pragma unroll
+    for (int s = 3; s >= 0; --s) {
+        const int half = 8 >> s;
+#pragma unroll
+        for (int g = 0; g < (1 << s); ++g) {
+            const double wd = __ldg(tp + ((1 << s) - 1 + g) * STRIDE);
+#pragma unroll
+            for (int j = 0; j < half; ++j) {
+                double &x = v[g * 2 * half + j], &y = v[g * 2 * half + j + half];
+                const double d = x - y;
+                x = x + y;
+                y = ds_mul_w(d, wd, c);
+            }
+        }
+    }
+    v[0] = ds_reduce(v[0], c);
 }
 // Gentleman-Sande round.  The sum path doubles per stage; only v[0] takes the sum at all four stages (16 x its
 // inputs), v[1] ends below 4.2 q whatever came in, the others lower: the caller reduces v[0] after each round, so
@@ -291,7 +351,7 @@ __global__ void __launch_bounds__(256, MINB) ntt16v2_fwd_rows(const u64 *__restr
         __syncthreads();
 #pragma unroll
         for (int e = 0; e < 16; ++e) v[e] = smd[clo * 17 + e];
-        fwd16_ds<16>(v, tab + Ntt16Layout::rowsB(row, 0, clo), c);
+        fwd16_ds8<16>(v, tb.fwdB8 + (size_t)pi * kRowsB8 + (row * 15) * 16 + clo, c);
         const double shift = 16.0 * c.qd, qinv_up = c.qinv * (1.0 + 0x1p-50);
 #pragma unroll
         for (int e = 0; e < 16; ++e) smr[clo * 17 + e] = ds_store(v[e], c, shift, qinv_up); // the words this thread read itself
@@ -341,7 +401,7 @@ __global__ void __launch_bounds__(256, MINB) ntt16v2_inv_rows(const u64 *__restr
         double v[16];
 #pragma unroll
         for (int e = 0; e < 16; ++e) v[e] = ds_load(smr[clo * 17 + e]);
-        inv16_ds<16>(v, tab + Ntt16Layout::rowsB(row, 0, clo), c);
+        inv16_ds8<16>(v, tb.invB8 + (size_t)pi * kRowsB8 + (row * 15) * 16 + clo, c);
 #pragma unroll
         for (int e = 0; e < 16; ++e) smd[clo * 17 + e] = v[e]; // the words this thread read itself
         __syncthreads();
