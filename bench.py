@@ -411,7 +411,13 @@ def run_gpu(args):
             dist.destroy_process_group()
         return
 
-    # roofline of the dominant kernel family (NTT) on a batch, timed alone with CUDA events
+    # roofline of the dominant kernel family (NTT) on a batch, timed alone with CUDA events.  The layer passes leave the
+    # pool holding most of the device memory in sizes these probes do not use: hand the idle buffers back first.
+    pb, iu = C.c_uint64(), C.c_uint64()
+    lib.dll.hb_mem_info(lib.ctx, C.byref(pb), C.byref(iu))
+    pool_gb = round(pb.value / 2 ** 30, 1)
+    gc.collect()
+    lib.dll.hb_release_cached(lib.ctx)
     hbm, which = peaks()
     roof = {}
     nb, lvl = 64, lib.L
@@ -470,9 +476,6 @@ def run_gpu(args):
                 "bound_note": "FP64 pipe: butterflies x 8 instructions / (148 SMs x 4 sub-partitions x 16 lanes x sampled SM clock); HBM: both passes' traffic / measured copy bandwidth",
                 "intt_gbs": roof["intt"]["gbs"], "keyswitch": ks}
 
-    pb, iu = C.c_uint64(), C.c_uint64()
-    lib.dll.hb_mem_info(lib.ctx, C.byref(pb), C.byref(iu))
-    pool_gb = round(pb.value / 2 ** 30, 1)
     cpu_ms, info = cpu_layer_estimate(pkg) if world == 1 and not args.no_cpu else (None, {})
     cpu = None
     if cpu_ms is not None:
