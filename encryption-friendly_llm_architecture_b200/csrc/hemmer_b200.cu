@@ -118,6 +118,7 @@ struct hb_ctx {
     std::map<u64, Evk> gal_keys;
     std::map<int, KsPlan *> plans; // device copies
     std::map<int, DivPlan *> div_plans;
+    std::map<int, std::vector<u64>> div_hat_inv; // host copy of DivPlan::hat_inv per level (folded into the inverse transform)
     u64 *pinned = nullptr; size_t pinned_bytes = 0; // host staging buffer of hb_decrypt_many
     ChaChaKey ckey{};
     std::map<std::pair<int, long long>, u32 *> gal_tables; // (copies, row_step) -> Galois elements of hb_matmul_acc, on the device
@@ -182,9 +183,26 @@ struct TmpBytes { // the same for a byte count (staging buffers of int64 coeffic
     TmpBytes(const TmpBytes &) = delete;
 };
 
-void ntt(hb_ctx *c, const u64 *src, size_t so, u64 *dst, size_t dof, int count, const LimbMap &m, bool inv) {
+void ntt(hb_ctx *c, const u64 *src, size_t so, u64 *dst, size_t dof, int count, const LimbMap &m, bool inv, const Ntt16Scale *scale = nullptr) {
     c->launches += (count == 0) ? 0 : (c->logn == 16 ? 2 : 1);
-    CK(launch_ntt(c->st, src, so, dst, dof, count, m, c->pc, c->tb, c->logn, inv));
+    CK(launch_ntt(c->st, src, so, dst, dof, count, m, c->pc, c->tb, c->logn, inv, scale));
+}
+// scale table of an inverse transform that also multiplies position k by f[k] (2^16 rings only): s_k = N^-1 * f[k] mod q
+Ntt16Scale ntt_scale(hb_ctx *c, const LimbMap &m, const u64 *f) {
+    Ntt16Scale sc{};
+    if (m.n > 8) fail(HB_E_LIMIT, "scaled inverse transform: at most 8 limb positions");
+    sc.on = 1;
+    for (int k = 0; k < m.n; ++k) {
+        const u64 q = c->h->q[m.prime[k]];
+        const u64 s = hbhost::mulmod(hbhost::invmod((u64)c->N % q, q), f[k] % q, q);
+        if (q >> 44) { sc.w[k] = s; sc.comp[k] = hbhost::shoup(s, q); }
+        else {
+            sc.w[k] = ds_twiddle_word(s);
+            const double sf = (double)s / (double)q;
+            std::memcpy(&sc.comp[k], &sf, 8);
+        }
+    }
+    return sc;
 }
 void ntt_inplace(hb_ctx *c, u64 *d, int count, const LimbMap &m, bool inv) { ntt(c, d, (size_t)m.n * c->N, d, (size_t)m.n * c->N, count, m, inv); }
 
@@ -386,6 +404,7 @@ const DivPlan *get_div_plan(hb_ctx *c, int level) {
         for (int t = 0; t < ns; ++t) if (t != s) hat = hbhost::mulmod(hat, h.q[P->src_prime[t]] % ds, ds);
         const u64 hi_ = hbhost::invmod(hat, ds);
         P->hat_inv[s] = hi_; P->hat_inv_sh[s] = hbhost::shoup(hi_, ds);
+        c->div_hat_inv[level].push_back(hi_);
         for (int l = 0; l < level; ++l) {
             const u64 ql = h.q[l];
             u64 hm = 1;
@@ -417,8 +436,13 @@ hb_ct *divide_by_p_ql(hb_ctx *c, const u64 *E, int level, int batch) {
         const unsigned gx1 = (unsigned)((N + 255) / 256), gx = c->gx();
         Tmp sc(c, (size_t)batch * 2 * ns), t(c, (size_t)batch * 2 * level);
         LimbMap sm{}; sm.n = ns; sm.prime[0] = (unsigned char)level; for (int k = 0; k < d.K; ++k) sm.prime[1 + k] = (unsigned char)(c->L + 1 + k);
-        ntt(c, E + (size_t)(n - 1) * N, (size_t)ne * N, sc.p, (size_t)ns * N, batch * 2 * ns, sm, true);
-        LAUNCH(c), k_div_conv<<<dim3(gx1, 1, batch * 2), 256, 0, c->st>>>(t.p, sc.p, dv, c->pc, N);
+        // 2^16 rings: the inverse transform multiplies limb s by (D / d_s)^-1 on its way out, the conversion starts from there
+        const bool fold = c->logn == 16;
+        if (fold) {
+            const Ntt16Scale scale = ntt_scale(c, sm, c->div_hat_inv[level].data());
+            ntt(c, E + (size_t)(n - 1) * N, (size_t)ne * N, sc.p, (size_t)ns * N, batch * 2 * ns, sm, true, &scale);
+        } else ntt(c, E + (size_t)(n - 1) * N, (size_t)ne * N, sc.p, (size_t)ns * N, batch * 2 * ns, sm, true);
+        LAUNCH(c), k_div_conv<<<dim3(gx1, 1, batch * 2), 256, 0, c->st>>>(t.p, sc.p, dv, c->pc, N, fold ? 1 : 0);
         ntt_inplace(c, t.p, batch * 2 * level, c->qmap(level - 1), false);
         LAUNCH(c), k_div_fin<<<dim3(gx, level, batch * 2), 256, 0, c->st>>>(r->d, E, t.p, ne, dv, c->pc, N);
         CK(cudaGetLastError());

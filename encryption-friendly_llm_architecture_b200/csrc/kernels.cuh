@@ -1032,12 +1032,17 @@ __global__ void __launch_bounds__(256) k_ks_inner_mkb(u64 *__restrict__ E, const
 }
 // Base conversion of the division: src [bp][ns][N] (limbs q_level, P; coefficient form) -> t [bp][level][N]
 // grid = (N/256, 1, nbp)
+// prescaled: the inverse transform that produced src already multiplied limb k by hat_inv[k]
 template <int NS>
-__device__ __forceinline__ void div_conv_body(u64 *__restrict__ t, const u64 *__restrict__ src, const DivPlan *__restrict__ dv, const PrimeConst *__restrict__ pc, int N, int i, int bp) {
+__device__ __forceinline__ void div_conv_body(u64 *__restrict__ t, const u64 *__restrict__ src, const DivPlan *__restrict__ dv, const PrimeConst *__restrict__ pc, int N, int i, int bp,
+                                              int prescaled) {
     const int nl = dv->level;
     u64 y[NS];
 #pragma unroll
-    for (int k = 0; k < NS; ++k) y[k] = mul_shoup(src[((size_t)bp * NS + k) * N + i], dv->hat_inv[k], dv->hat_inv_sh[k], pc[dv->src_prime[k]].q);
+    for (int k = 0; k < NS; ++k) {
+        const u64 v = src[((size_t)bp * NS + k) * N + i];
+        y[k] = prescaled ? v : mul_shoup(v, dv->hat_inv[k], dv->hat_inv_sh[k], pc[dv->src_prime[k]].q);
+    }
     u64 *o = t + (size_t)bp * nl * N + i;
     for (int l = 0; l < nl; ++l) {
         PieceAcc s; s.zero();
@@ -1048,18 +1053,18 @@ __device__ __forceinline__ void div_conv_body(u64 *__restrict__ t, const u64 *__
         o += N;
     }
 }
-__global__ void k_div_conv(u64 *__restrict__ t, const u64 *__restrict__ src, const DivPlan *__restrict__ dv, const PrimeConst *__restrict__ pc, int N) {
+__global__ void k_div_conv(u64 *__restrict__ t, const u64 *__restrict__ src, const DivPlan *__restrict__ dv, const PrimeConst *__restrict__ pc, int N, int prescaled) {
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= N) return;
     const int bp = blockIdx.z;
     switch (dv->ns) {
-    case 2: div_conv_body<2>(t, src, dv, pc, N, i, bp); break;
-    case 3: div_conv_body<3>(t, src, dv, pc, N, i, bp); break;
-    case 4: div_conv_body<4>(t, src, dv, pc, N, i, bp); break;
-    case 5: div_conv_body<5>(t, src, dv, pc, N, i, bp); break;
-    case 6: div_conv_body<6>(t, src, dv, pc, N, i, bp); break;
-    case 7: div_conv_body<7>(t, src, dv, pc, N, i, bp); break;
-    default: div_conv_body<8>(t, src, dv, pc, N, i, bp); break;
+    case 2: div_conv_body<2>(t, src, dv, pc, N, i, bp, prescaled); break;
+    case 3: div_conv_body<3>(t, src, dv, pc, N, i, bp, prescaled); break;
+    case 4: div_conv_body<4>(t, src, dv, pc, N, i, bp, prescaled); break;
+    case 5: div_conv_body<5>(t, src, dv, pc, N, i, bp, prescaled); break;
+    case 6: div_conv_body<6>(t, src, dv, pc, N, i, bp, prescaled); break;
+    case 7: div_conv_body<7>(t, src, dv, pc, N, i, bp, prescaled); break;
+    default: div_conv_body<8>(t, src, dv, pc, N, i, bp, prescaled); break;
     }
 }
 // out[bp][l][i] = (E[bp][l][i] - t[bp][l][i]) * D^-1 for l < level.  grid = (N/(256*kElems), level, batch*2)

@@ -70,9 +70,10 @@ __global__ void __launch_bounds__(256) ntt_small(const u64 *__restrict__ src, Li
 // Launch a batched transform of `count` limb instances.  src == dst gives an in-place transform;
 // with distinct buffers `dst` also serves as the intermediate between the two passes.
 inline cudaError_t launch_ntt(cudaStream_t st, const u64 *src, size_t src_outer, u64 *dst, size_t dst_outer, int count, const LimbMap &map,
-                              const PrimeConst *pc, const NttTables &tb, int logn, bool inverse) {
+                              const PrimeConst *pc, const NttTables &tb, int logn, bool inverse, const Ntt16Scale *scale = nullptr) {
     if (count == 0) return cudaSuccess;
-    if (logn == 16) return launch_ntt16(st, src, src_outer, dst, dst_outer, count, map, pc, tb.t16, inverse);
+    if (logn == 16) return launch_ntt16(st, src, src_outer, dst, dst_outer, count, map, pc, tb.t16, inverse, scale);
+    if (scale) return cudaErrorInvalidValue; // only the 2^16 kernels take a scale
     if (logn > 12) return cudaErrorInvalidValue;
     LimbAddr sa{src_outer}, da{dst_outer};
     ntt_small<<<count, 256, sizeof(u64) << logn, st>>>(src, sa, dst, da, map, pc, tb, logn, inverse ? 1 : 0);

@@ -86,6 +86,12 @@ template <class F> inline void ntt16_fill_rows_b8(double *out, F w) {
         }
 }
 
+// Optional last multiplication of the inverse transform: position k = li % map.n gets scale s_k (which must already
+// contain N^-1) instead of N^-1 -- a base conversion that follows folds its first product (the inverse of a complementary
+// modulus) into the transform.  w: s_k (as ds_twiddle_word for primes below 2^44), comp: s_k / q as a double, or the
+// Shoup companion.
+struct Ntt16Scale { u64 w[8], comp[8]; int on; };
+
 // address of limb instance li: (li / period) * outer + (li % period) * N
 struct LimbAddr16 {
     size_t outer;
@@ -430,9 +436,10 @@ __global__ void __launch_bounds__(256, MINB) ntt16v2_inv_rows(const u64 *__restr
 // ---- inverse, column pass: undoes stages 8..1, scales by N^-1, stores canonical residues ----
 template <int MINB>
 __global__ void __launch_bounds__(256, MINB) ntt16v2_inv_cols(const u64 *__restrict__ src, LimbAddr16 sa, u64 *__restrict__ dst, LimbAddr16 da,
-                                                        const __grid_constant__ LimbMap map, const PrimeConst *__restrict__ pc, Ntt16Tables tb) {
+                                                        const __grid_constant__ LimbMap map, const PrimeConst *__restrict__ pc, Ntt16Tables tb,
+                                                        const __grid_constant__ Ntt16Scale sc) {
     __shared__ u64 sm[4096];
-    const int li = blockIdx.y, pi = map.prime[li % map.n];
+    const int li = blockIdx.y, pos = li % map.n, pi = map.prime[pos];
     const PrimeConst m = pc[pi];
     const ulonglong2 *tab = tb.inv + (size_t)pi * Ntt16Layout::kEntries;
     const int tid = threadIdx.x, lane = tid & 15, sub = tid >> 4;
@@ -453,9 +460,11 @@ __global__ void __launch_bounds__(256, MINB) ntt16v2_inv_cols(const u64 *__restr
         for (int e = 0; e < 16; ++e) v[e] = smd[(e * 16 + sub) * 16 + lane];
         inv16_ds<1>(v, tab + Ntt16Layout::colsA(0), c);
         const double qinv_up = c.qinv * (1.0 + 0x1p-50);
+        const u64 sw = sc.on ? sc.w[pos] : ds_twiddle_word(m.n_inv);
+        const double sf = sc.on ? __longlong_as_double((long long)sc.comp[pos]) : m.n_inv_f;
 #pragma unroll
         for (int e = 0; e < 16; ++e) {
-            const double t = ds_mul(v[e], ds_twiddle_word(m.n_inv), m.n_inv_f, c); // x * N^-1 in (-0.52 q, 0.52 q)
+            const double t = ds_mul(v[e], sw, sf, c); // x * N^-1 (or x * scale) in (-0.52 q, 0.52 q)
             o[(e * 16 + sub) * 256] = ds_store(t, c, c.qd, qinv_up);
         }
     } else {
@@ -470,7 +479,9 @@ __global__ void __launch_bounds__(256, MINB) ntt16v2_inv_cols(const u64 *__restr
         for (int e = 0; e < 16; ++e) v[e] = sm[(e * 16 + sub) * 16 + lane];
         inv16_int<1>(v, tab + Ntt16Layout::colsA(0), m.q);
 #pragma unroll
-        for (int e = 0; e < 16; ++e) o[(e * 16 + sub) * 256] = mul_shoup(v[e], m.n_inv, m.n_inv_sh, m.q);
+        const u64 sw = sc.on ? sc.w[pos] : m.n_inv, ss = sc.on ? sc.comp[pos] : m.n_inv_sh;
+#pragma unroll
+        for (int e = 0; e < 16; ++e) o[(e * 16 + sub) * 256] = mul_shoup(v[e], sw, ss, m.q);
     }
 }
 
@@ -480,7 +491,7 @@ __global__ void __launch_bounds__(256, MINB) ntt16v2_inv_cols(const u64 *__restr
 // to fetch the twiddles of a round ahead of the butterflies that use them).
 template <int MINB = 4>
 inline cudaError_t launch_ntt16(cudaStream_t st, const u64 *src, size_t src_outer, u64 *dst, size_t dst_outer, int count, const LimbMap &map,
-                                const PrimeConst *pc, const Ntt16Tables &tb, bool inverse) {
+                                const PrimeConst *pc, const Ntt16Tables &tb, bool inverse, const Ntt16Scale *scale = nullptr) {
     if (count == 0) return cudaSuccess;
     LimbAddr16 sa{src_outer}, da{dst_outer};
     dim3 grid(16, count);
@@ -489,7 +500,8 @@ inline cudaError_t launch_ntt16(cudaStream_t st, const u64 *src, size_t src_oute
         ntt16v2_fwd_rows<MINB><<<grid, 256, 0, st>>>(dst, da, dst, da, map, pc, tb);
     } else {
         ntt16v2_inv_rows<MINB><<<grid, 256, 0, st>>>(src, sa, dst, da, map, pc, tb);
-        ntt16v2_inv_cols<MINB><<<grid, 256, 0, st>>>(dst, da, dst, da, map, pc, tb);
+        Ntt16Scale none{};
+        ntt16v2_inv_cols<MINB><<<grid, 256, 0, st>>>(dst, da, dst, da, map, pc, tb, scale ? *scale : none);
     }
     return cudaGetLastError();
 }
