@@ -218,10 +218,10 @@ Ciphertext assemble_lazy(Env &e, const Ciphertext &x, const Hoisted &h, const st
     for (const auto &c : w) { ka.push_back(c.main); kb.push_back(c.wrapped); }
     return e.ev.assembleRotationsMulti(x, h, ka, kb);
 }
-// Iterations of a shift loop handled by one launch sequence: batches are stacked until about 256 ciphertexts are in
+// Iterations of a shift loop handled by one launch sequence: batches are stacked until about 168 ciphertexts are in
 // flight.  A batch of 40 fills the GPU on its own; beyond that the gain is the accumulator of the product loop, which is
 // read and written once per launch sequence instead of once per iteration.  The stored residues do not depend on the grouping.
-i64 loop_group(const Ciphertext &x) { return std::max<i64>(1, std::min<i64>(16, 256 / std::max(1, x.getBatch()))); }
+i64 loop_group(const Ciphertext &x) { return std::max<i64>(1, std::min<i64>(16, 168 / std::max(1, x.getBatch()))); }
 
 void require_product_shapes(const CtxtTensor &a, const CtxtTensor &b) {
     if (a.getWidth() != b.getHeight()) throw std::invalid_argument("[getCommonInsideLength] different inside length.");
