@@ -372,6 +372,13 @@ def run_gpu(args):
             k = layer.unit_kind(wl.units[i])
             mix[k] = mix.get(k, 0) + 1
         before_exchange = gather({"ms": round(e_start.elapsed_time(evs[0]), 2), "units": mix})
+    # the recorded pass is not replayed again: drop it and hand the pool's idle buffers back, the passes below use other sizes
+    pb, iu = C.c_uint64(), C.c_uint64()
+    lib.dll.hb_mem_info(lib.ctx, C.byref(pb), C.byref(iu))
+    pool_gb = round(pb.value / 2 ** 30, 1)   # what the timed passes of the default schedule hold
+    graph = graph_out = None
+    gc.collect()
+    lib.dll.hb_release_cached(lib.ctx)
     # the same layer with the reference's own rotation sequence (no hoisting), for comparison
     ms_faithful = None
     faithful_exact = None
@@ -391,6 +398,8 @@ def run_gpu(args):
                 ok += int(merged.get(repr(tag)) == want)
             faithful_exact = f"{ok}/{len(gold0)}"
         H.set_schedule(args.schedule)
+        gc.collect()
+        lib.dll.hb_release_cached(lib.ctx)
 
     # end to end: host matrices in, decrypted host results out, every step
     wl.h2d_bytes = wl.d2h_bytes = 0
@@ -413,9 +422,6 @@ def run_gpu(args):
 
     # roofline of the dominant kernel family (NTT) on a batch, timed alone with CUDA events.  The layer passes leave the
     # pool holding most of the device memory in sizes these probes do not use: hand the idle buffers back first.
-    pb, iu = C.c_uint64(), C.c_uint64()
-    lib.dll.hb_mem_info(lib.ctx, C.byref(pb), C.byref(iu))
-    pool_gb = round(pb.value / 2 ** 30, 1)
     gc.collect()
     lib.dll.hb_release_cached(lib.ctx)
     hbm, which = peaks()
