@@ -128,6 +128,7 @@ struct hb_ctx {
     int N = 0, logn = 0, L = 0, K = 0, nprimes = 0;
     unsigned long long launches = 0; // kernels launched by this context
     int *dev_err = nullptr;          // raised by a kernel whose bounded wait ran out; read by hb_sync
+    bool smem_opt_in_mkb = false, smem_opt_in_parts = false; // the opt-in to more than 48 KB of shared memory is per kernel and per device: once per context
     // Compulsory HBM traffic of the primitives called so far, in limbs of N words: every input of a primitive read once,
     // every output written once, a switching key or plaintext once per batch (temporaries and transforms inside a
     // primitive do not count).  Divided by the HBM peak this is the time the call sequence cannot go below.
@@ -508,8 +509,7 @@ hb_ct *do_assemble_mk(hb_ctx *c, const hb_ct *a, const u64 *dt, const hb_mkey *c
         int maxcount = 1;
         for (int g = 0; g < groups; ++g) maxcount = std::max(maxcount, mrl.r[g].count);
         const size_t smem = ((size_t)maxcount * d.nd * 2 + maxcount + (size_t)M * maxcount * (d.nd + 1)) * T * 8;
-        static bool attr_set = false;
-        if (!attr_set) { CK(cudaFuncSetAttribute(k_ks_inner_mkb<M, EL>, cudaFuncAttributeMaxDynamicSharedMemorySize, 28 * T * 8)); attr_set = true; }
+        if (!c->smem_opt_in_mkb) { CK(cudaFuncSetAttribute(k_ks_inner_mkb<M, EL>, cudaFuncAttributeMaxDynamicSharedMemorySize, 28 * T * 8)); c->smem_opt_in_mkb = true; }
         LAUNCH(c), k_ks_inner_mkb<M, EL><<<dim3((unsigned)(N / T), (unsigned)(groups * chunks), (unsigned)ne), 256, smem, c->st>>>(E.p, a->d, a->d + (size_t)n * N, (size_t)2 * n * N, dt, mrl, batch,
                                                                                                                               maxcount, pl, c->pc, c->logn, N, c->dev_err);
         CK(cudaGetLastError());
@@ -616,8 +616,7 @@ hb_ct *do_prod_rescale_parts(hb_ctx *c, const hb_ct *const *a, const hb_pt *cons
         constexpr int G = 4; // parts per CTA: 4 x 17 mask chunks of 2 KB = 136 KB of shared memory
         const size_t smem = (size_t)G * count * 2048;
         const unsigned pg = (unsigned)((parts + G - 1) / G);
-        static bool attr_set = false;
-        if (!attr_set) { CK(cudaFuncSetAttribute(k_prod_parts<G>, cudaFuncAttributeMaxDynamicSharedMemorySize, G * kMaxPartTerms * 2048)); attr_set = true; }
+        if (!c->smem_opt_in_parts) { CK(cudaFuncSetAttribute(k_prod_parts<G>, cudaFuncAttributeMaxDynamicSharedMemorySize, G * kMaxPartTerms * 2048)); c->smem_opt_in_parts = true; }
         Scalars qi{};
         for (int i = 0; i < l; ++i) qi.v[i] = hbhost::invmod(c->h->q[l] % c->h->q[i], c->h->q[i]);
         LAUNCH(c), k_prod_parts<G><<<dim3(gx1, 1, pg), 1024, smem, c->st>>>(last.p, pt, nullptr, l, nbp, c->pc, N, qi, c->dev_err);
