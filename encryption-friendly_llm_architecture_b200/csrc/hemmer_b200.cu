@@ -613,7 +613,7 @@ hb_ct *do_prod_rescale_parts(hb_ctx *c, const hb_ct *const *a, const hb_pt *cons
     ALG(c, (size_t)count * nbp * (l + 1) + used * (l + 1) + (size_t)gnbp * l);
     try {
         Tmp last(c, (size_t)gnbp), S(c, (size_t)gnbp), t(c, (size_t)gnbp * l);
-        constexpr int G = 4; // parts per CTA: 4 x 17 mask chunks of 2 KB = 136 KB of shared memory
+        constexpr int G = 6; // parts per CTA: 6 x 17 mask chunks of 2 KB = 204 KB of shared memory
         const size_t smem = (size_t)G * count * 2048;
         const unsigned pg = (unsigned)((parts + G - 1) / G);
         if (!c->smem_opt_in_parts) { CK(cudaFuncSetAttribute(k_prod_parts<G>, cudaFuncAttributeMaxDynamicSharedMemorySize, G * kMaxPartTerms * 2048)); c->smem_opt_in_parts = true; }
