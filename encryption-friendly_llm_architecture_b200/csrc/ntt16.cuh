@@ -487,8 +487,7 @@ __global__ void __launch_bounds__(256, MINB) ntt16v2_inv_cols(const u64 *__restr
 
 // Launch a batched transform of `count` limb instances of 2^16 coefficients.  src == dst gives an in-place transform;
 // with distinct buffers `dst` also serves as the intermediate between the two passes.  MINB = CTAs per SM the kernels
-// are compiled for (register budget 65536 / (256 * MINB)); two measured fastest (the compiler then has the registers
-// to fetch the twiddles of a round ahead of the butterflies that use them).
+// are compiled for (register budget 65536 / (256 * MINB)); four measured fastest with the FP64 butterflies.
 template <int MINB = 4>
 inline cudaError_t launch_ntt16(cudaStream_t st, const u64 *src, size_t src_outer, u64 *dst, size_t dst_outer, int count, const LimbMap &map,
                                 const PrimeConst *pc, const Ntt16Tables &tb, bool inverse, const Ntt16Scale *scale = nullptr) {
