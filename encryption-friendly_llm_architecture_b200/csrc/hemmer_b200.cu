@@ -411,6 +411,9 @@ const DivPlan *get_div_plan(hb_ctx *c, int level) {
             u64 hm = 1;
             for (int t = 0; t < ns; ++t) if (t != s) hm = hbhost::mulmod(hm, h.q[P->src_prime[t]] % ql, ql);
             P->hat_mod[s][l] = hm;
+            const double d0 = (double)hm, d1 = (double)hbhost::mulmod(hm, ((u64)1 << 30) % ql, ql);
+            std::memcpy(&P->hat_mod_d0[s][l], &d0, 8);
+            std::memcpy(&P->hat_mod_d1[s][l], &d1, 8);
         }
     }
     for (int l = 0; l <= level; ++l) {

@@ -674,6 +674,8 @@ struct DivPlan {
     unsigned char src_prime[8];
     u64 hat_inv[8], hat_inv_sh[8];     // (D / d_s)^-1 mod d_s
     u64 hat_mod[8][kMaxPrimes];        // (D / d_s) mod q_i, i < level
+    u64 hat_mod_d0[8][kMaxPrimes];     // the same as a double (bit pattern), for targets below 2^44
+    u64 hat_mod_d1[8][kMaxPrimes];     // (D / d_s) * 2^30 mod q_i as a double (bit pattern)
     u64 d_inv[kMaxPrimes];             // D^-1 mod q_i
     u64 p_mod[kMaxPrimes];             // P mod q_j, j <= level
 };
@@ -1044,12 +1046,31 @@ __device__ __forceinline__ void div_conv_body(u64 *__restrict__ t, const u64 *__
         y[k] = prescaled ? v : mul_shoup(v, dv->hat_inv[k], dv->hat_inv_sh[k], pc[dv->src_prime[k]].q);
     }
     u64 *o = t + (size_t)bp * nl * N + i;
-    for (int l = 0; l < nl; ++l) {
-        PieceAcc s; s.zero();
+    // targets below 2^44: y = y1 * 2^30 + y0 with both pieces as doubles, products on the FP64 pipe against the constants
+    // (D / d_s) and (D / d_s) * 2^30 mod q: sixteen exact products of at most 0.51 q each, one canonicalisation
+    double y0[NS], y1[NS];
 #pragma unroll
-        for (int k = 0; k < NS; ++k) s.mac(y[k], dv->hat_mod[k][l]);
-        PrimeConst mm; mm.q = pc[l].q; mm.mu_hi = pc[l].mu_hi; mm.mu_lo = pc[l].mu_lo;
-        *o = s.finish(mm);
+    for (int k = 0; k < NS; ++k) {
+        y0[k] = __hiloint2double(0x43300000, (int)((u32)y[k] & 0x3FFFFFFFu)) - kTwo52;
+        y1[k] = __hiloint2double(0x43300000, (int)(u32)(y[k] >> 30)) - kTwo52;
+    }
+    for (int l = 0; l < nl; ++l) {
+        if (pc[l].fp) {
+            const double qinv = pc[l].q_inv_f, qd = (double)pc[l].q;
+            double acc = 0.0;
+#pragma unroll
+            for (int k = 0; k < NS; ++k) {
+                acc = __dadd_rn(acc, mul_fp64_lazy(y0[k], __longlong_as_double((long long)dv->hat_mod_d0[k][l]), qinv, qd));
+                acc = __dadd_rn(acc, mul_fp64_lazy(y1[k], __longlong_as_double((long long)dv->hat_mod_d1[k][l]), qinv, qd));
+            }
+            *o = canon_fp64(acc, qinv, qd);
+        } else {
+            PieceAcc s; s.zero();
+#pragma unroll
+            for (int k = 0; k < NS; ++k) s.mac(y[k], dv->hat_mod[k][l]);
+            PrimeConst mm; mm.q = pc[l].q; mm.mu_hi = pc[l].mu_hi; mm.mu_lo = pc[l].mu_lo;
+            *o = s.finish(mm);
+        }
         o += N;
     }
 }
