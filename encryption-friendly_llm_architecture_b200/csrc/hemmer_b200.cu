@@ -233,6 +233,9 @@ const KsPlan *get_plan(hb_ctx *c, int level) {
                 u64 hm = 1;
                 for (int t = 0; t < ns; ++t) if (t != s) hm = hbhost::mulmod(hm, h.q[lo + t] % qt, qt);
                 P->hat_mod[dg][s][j] = hm;
+                const double d0 = (double)hm, d1 = (double)hbhost::mulmod(hm, ((u64)1 << 30) % qt, qt);
+                std::memcpy(&P->hat_mod_d0[dg][s][j], &d0, 8);
+                std::memcpy(&P->hat_mod_d1[dg][s][j], &d1, 8);
             }
         }
         for (int j = 0; j < ne; ++j) {
@@ -252,6 +255,9 @@ const KsPlan *get_plan(hb_ctx *c, int level) {
             u64 hm = 1;
             for (int t = 0; t < K; ++t) if (t != k) hm = hbhost::mulmod(hm, h.q[h.L + 1 + t] % ql, ql);
             P->p_hat_mod[k][l] = hm;
+            const double d0 = (double)hm, d1 = (double)hbhost::mulmod(hm, ((u64)1 << 30) % ql, ql);
+            std::memcpy(&P->p_hat_mod_d0[k][l], &d0, 8);
+            std::memcpy(&P->p_hat_mod_d1[k][l], &d1, 8);
         }
     }
     for (int l = 0; l < n; ++l) {

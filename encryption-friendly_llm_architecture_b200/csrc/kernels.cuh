@@ -421,8 +421,11 @@ struct KsPlan {
     unsigned char ext_prime[kMaxPrimes];        // ext limb j -> prime index
     u64 hat_inv[8][kMaxDigitLimbs], hat_inv_sh[8][kMaxDigitLimbs];
     u64 hat_mod[8][kMaxDigitLimbs][kMaxPrimes]; // [digit][source][ext limb j]
+    u64 hat_mod_d0[8][kMaxDigitLimbs][kMaxPrimes]; // the same as a double (bit pattern), and times 2^30 mod the target: for
+    u64 hat_mod_d1[8][kMaxDigitLimbs][kMaxPrimes]; // targets below 2^44 the conversion runs on the FP64 pipe
     u64 p_hat_inv[8], p_hat_inv_sh[8];          // ModDown: per special prime
     u64 p_hat_mod[8][kMaxPrimes];               // [special k][q limb l]
+    u64 p_hat_mod_d0[8][kMaxPrimes], p_hat_mod_d1[8][kMaxPrimes]; // as doubles, and times 2^30 mod q_l
     u64 p_inv[kMaxPrimes];                      // P^-1 mod q_l
 };
 
@@ -437,14 +440,31 @@ __device__ __forceinline__ void modup_body(u64 *__restrict__ dt, const u64 *__re
 #pragma unroll
     for (int s = 0; s < NS; ++s) y[s] = mul_shoup(a_coef[((size_t)b * n + lo + s) * N + i], pl->hat_inv[dg][s], pl->hat_inv_sh[dg][s], pc[lo + s].q);
     u64 *o = dt + ((size_t)b * pl->dt_count + pl->dt_start[dg]) * N + i;
+    double y0[NS], y1[NS]; // 30-bit pieces of the sources as doubles, for the targets below 2^44
+#pragma unroll
+    for (int k = 0; k < NS; ++k) {
+        y0[k] = __hiloint2double(0x43300000, (int)((u32)y[k] & 0x3FFFFFFFu)) - kTwo52;
+        y1[k] = __hiloint2double(0x43300000, (int)(u32)(y[k] >> 30)) - kTwo52;
+    }
     for (int j = 0; j < ne; ++j) {
         if (j >= lo && j < hi) continue;
         const PrimeConst *m = pc + pl->ext_prime[j];
-        PieceAcc s; s.zero(); // at most 8 sources
+        if (m->fp) {
+            const double qinv = m->q_inv_f, qd = (double)m->q;
+            double acc = 0.0;
 #pragma unroll
-        for (int k = 0; k < NS; ++k) s.mac(y[k], pl->hat_mod[dg][k][j]);
-        PrimeConst mm; mm.q = m->q; mm.mu_hi = m->mu_hi; mm.mu_lo = m->mu_lo;
-        *o = s.finish(mm);
+            for (int k = 0; k < NS; ++k) {
+                acc = __dadd_rn(acc, mul_fp64_lazy(y0[k], __longlong_as_double((long long)pl->hat_mod_d0[dg][k][j]), qinv, qd));
+                acc = __dadd_rn(acc, mul_fp64_lazy(y1[k], __longlong_as_double((long long)pl->hat_mod_d1[dg][k][j]), qinv, qd));
+            }
+            *o = canon_fp64(acc, qinv, qd);
+        } else {
+            PieceAcc s; s.zero(); // at most 8 sources
+#pragma unroll
+            for (int k = 0; k < NS; ++k) s.mac(y[k], pl->hat_mod[dg][k][j]);
+            PrimeConst mm; mm.q = m->q; mm.mu_hi = m->mu_hi; mm.mu_lo = m->mu_lo;
+            *o = s.finish(mm);
+        }
         o += N;
     }
 }
@@ -532,12 +552,29 @@ __device__ __forceinline__ void moddown_conv_body(u64 *__restrict__ t, const u64
 #pragma unroll
     for (int k = 0; k < K; ++k) y[k] = mul_shoup(pcoef[((size_t)bp * K + k) * N + i], pl->p_hat_inv[k], pl->p_hat_inv_sh[k], pc[Lp1 + k].q);
     u64 *o = t + (size_t)bp * n * N + i;
-    for (int l = 0; l < n; ++l) {
-        PieceAcc s; s.zero();
+    double y0[K], y1[K]; // 30-bit pieces of the sources as doubles, for the targets below 2^44
 #pragma unroll
-        for (int k = 0; k < K; ++k) s.mac(y[k], pl->p_hat_mod[k][l]);
-        PrimeConst mm; mm.q = pc[l].q; mm.mu_hi = pc[l].mu_hi; mm.mu_lo = pc[l].mu_lo;
-        *o = s.finish(mm);
+    for (int k = 0; k < K; ++k) {
+        y0[k] = __hiloint2double(0x43300000, (int)((u32)y[k] & 0x3FFFFFFFu)) - kTwo52;
+        y1[k] = __hiloint2double(0x43300000, (int)(u32)(y[k] >> 30)) - kTwo52;
+    }
+    for (int l = 0; l < n; ++l) {
+        if (pc[l].fp) {
+            const double qinv = pc[l].q_inv_f, qd = (double)pc[l].q;
+            double acc = 0.0;
+#pragma unroll
+            for (int k = 0; k < K; ++k) {
+                acc = __dadd_rn(acc, mul_fp64_lazy(y0[k], __longlong_as_double((long long)pl->p_hat_mod_d0[k][l]), qinv, qd));
+                acc = __dadd_rn(acc, mul_fp64_lazy(y1[k], __longlong_as_double((long long)pl->p_hat_mod_d1[k][l]), qinv, qd));
+            }
+            *o = canon_fp64(acc, qinv, qd);
+        } else {
+            PieceAcc s; s.zero();
+#pragma unroll
+            for (int k = 0; k < K; ++k) s.mac(y[k], pl->p_hat_mod[k][l]);
+            PrimeConst mm; mm.q = pc[l].q; mm.mu_hi = pc[l].mu_hi; mm.mu_lo = pc[l].mu_lo;
+            *o = s.finish(mm);
+        }
         o += N;
     }
 }
