@@ -354,16 +354,16 @@ __global__ void __launch_bounds__(1024, 1) k_prod_parts(u64 *__restrict__ out, c
     const PrimeConst m = pc[l];
     const u64 qli = t ? qlinv.v[l] : 0;
     const double qd = (double)m.q;
-    if (m.fp) { // the masks of a prime below 2^44 become doubles once, for every member that follows
+    // Absent terms get zero masks, so the product loop below is straight-line code (no test per part and term: the
+    // independent chains of the G parts interleave); the masks of a prime below 2^44 become doubles once.
 #pragma unroll
-        for (int g = 0; g < G; ++g)
-            for (int j = slot; j < count; j += 4)
-                if ((have[g] >> j) & 1u) {
-                    u64 *w = ptile + (size_t)(g * count + j) * 256 + lane;
-                    *w = (u64)__double_as_longlong(u52_to_double(*w));
-                }
-        __syncthreads();
-    }
+    for (int g = 0; g < G; ++g)
+        for (int j = slot; j < count; j += 4) {
+            u64 *w = ptile + (size_t)(g * count + j) * 256 + lane;
+            if (!((have[g] >> j) & 1u)) *w = 0;
+            else if (m.fp) *w = (u64)__double_as_longlong(u52_to_double(*w));
+        }
+    __syncthreads();
     for (int bp = slot; bp < nbp; bp += 4) {
         const size_t ao = ((size_t)bp * (level + 1) + l) * N + x0 + lane;
         u64 v[G];
@@ -379,8 +379,7 @@ __global__ void __launch_bounds__(1024, 1) k_prod_parts(u64 *__restrict__ out, c
                 if (j + 2 < count) a_nxt = pt.a[j + 2][ao];
                 const double ad = u52_to_double(a);
 #pragma unroll
-                for (int g = 0; g < G; ++g)
-                    if ((have[g] >> j) & 1u) acc[g] = __dadd_rn(acc[g], mul_fp64_lazy(ad, dtile[(size_t)(g * count + j) * 256 + lane], m.q_inv_f, qd));
+                for (int g = 0; g < G; ++g) acc[g] = __dadd_rn(acc[g], mul_fp64_lazy(ad, dtile[(size_t)(g * count + j) * 256 + lane], m.q_inv_f, qd));
             }
 #pragma unroll
             for (int g = 0; g < G; ++g) v[g] = canon_fp64(acc[g], m.q_inv_f, qd);
@@ -393,8 +392,7 @@ __global__ void __launch_bounds__(1024, 1) k_prod_parts(u64 *__restrict__ out, c
                 a_cur = a_nxt;
                 if (j + 2 < count) a_nxt = pt.a[j + 2][ao];
 #pragma unroll
-                for (int g = 0; g < G; ++g)
-                    if ((have[g] >> j) & 1u) acc[g].mad(a, ptile[(size_t)(g * count + j) * 256 + lane]);
+                for (int g = 0; g < G; ++g) acc[g].mad(a, ptile[(size_t)(g * count + j) * 256 + lane]);
             }
 #pragma unroll
             for (int g = 0; g < G; ++g) v[g] = barrett128(acc[g].hi, acc[g].lo, m);
