@@ -243,3 +243,30 @@ def test_part_sums_and_grouped_rotate_sum_equal_the_term_by_term_calls(pkg, gpu_
     xs = (C.c_void_p * parts)(*[s.ptr.value for s in singles])
     g._chk(g.dll.hb_rotate_sum(g.ctx, xs, st, C.c_int(parts), C.byref(r2)))
     _same(g.ct_export(pkg.capi.Handle(g, r1, "ct")), g.ct_export(pkg.capi.Handle(g, r2, "ct")), "grouped rotate-sum")
+
+
+def test_tile_batched_accumulate_many_terms_with_44_bit_primes(pkg):
+    """The signed double sums of hb_matmul_acc_tiles at their fold limit: every residue q - 1 (each product is then as far
+    from zero as it gets), 512 copies x 2 groups = 1024 terms per output, primes just below 2^44, ring degree 2^10 ... the
+    tile kernel needs 512 coefficients per CTA, so N = 2^10 gives two CTAs per limb."""
+    prm = dict(log_n=10, max_level=3, dnum=2, num_special=3, hamming_weight=32, q_bits=44)
+    g = pkg.open_gpu(pkg.make_params(**prm))
+    g.keygen()
+    copies, groups, lvl, tiles = 512, 2, 2, 3
+    data = np.empty((copies * groups, 2, lvl + 1, g.N), dtype=np.uint64)
+    for l in range(lvl + 1):
+        data[:, :, l, :] = np.uint64(int(g.primes[l]) - 1)
+    pre = g.ct_create(lvl, 2, copies * groups)
+    g.ct_import(pre, data)
+    rng = np.random.default_rng(5)
+    pts = [[g.encode(rng.uniform(-1, 1, g.slots), lvl) for _ in range(groups)] for _ in range(tiles)]
+    arr = (C.c_void_p * (tiles * groups))(*[p.ptr.value for row in pts for p in row])
+    outs = (C.c_void_p * tiles)()
+    g._chk(g.dll.hb_matmul_acc_tiles(g.ctx, pre.ptr, C.c_int(groups), C.c_int(0), arr, C.c_int(groups), C.c_int(tiles), C.c_int64(0), outs))
+    for t in range(tiles):
+        got = g.ct_export(pkg.capi.Handle(g, C.c_void_p(outs[t]), "ct"))
+        w = [g.pt_export(p) for p in pts[t]]
+        for l in range(lvl + 1):
+            q = int(g.primes[l])
+            want = np.array([(copies * (q - 1) * (int(a) + int(b))) % q for a, b in zip(w[0][l], w[1][l])], dtype=np.uint64)
+            assert np.array_equal(got[0, 0, l], want) and np.array_equal(got[0, 1, l], want), f"tile {t} limb {l}"
