@@ -97,6 +97,8 @@ class HEMMer {
     // HEMMer::oneMatRotSumInplace (HEMMer.cpp:882-919): row sums of the left half of a's tiles and of the right half of
     // b's tiles, spread over every column -- the norm terms of the Gaussian-kernel attention scores
     void oneMatRotSumInplace(CtxtTensor &a, CtxtTensor &b);
+    // HEMMer::tr_oneMatRotSumInplace (HEMMer.cpp:921-962): row sums over the whole tile side, returned on half of it
+    void trOneMatRotSumInplace(CtxtTensor &a, CtxtTensor &b, int target_level = 0);
     // The rank-2 LoRA branch of a projection as the reference's layer runs it (TransformerBlock::attention2_bert_loraOpti,
     // TransformerBlock.cpp:2199-2365, without the bootstraps around it): the two rank vectors are picked row by row
     // out of the factor ciphertexts, spread over all token rows by rotations, multiplied slot-wise with the three

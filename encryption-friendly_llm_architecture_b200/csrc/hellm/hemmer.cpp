@@ -176,6 +176,25 @@ void HEMMer::oneMatRotSumInplace(CtxtTensor &a, CtxtTensor &b) {
         b.get() = eval_.add(b.get(), eval_.leftRotate(b.get(), rot));
     }
 }
+// HEMMer::tr_oneMatRotSumInplace -- HEMMer.cpp:921-962 with ModelArgs::HEAD_DIM equal to the tile side: the sums run over a
+// whole row of a tile and come back on half of it (a: left half, b: right half), after an optional level-down
+void HEMMer::trOneMatRotSumInplace(CtxtTensor &a, CtxtTensor &b, int target_level) {
+    const i64 d = tile_;
+    if (target_level > 0) {
+        a.get() = eval_.levelDown(a.get(), target_level + 1);
+        b.get() = eval_.levelDown(b.get(), target_level + 1);
+    }
+    for (i64 rot = 1; rot < d; rot <<= 1) {
+        a.get() = eval_.add(a.get(), eval_.leftRotate(a.get(), rot));
+        b.get() = eval_.add(b.get(), eval_.rightRotate(b.get(), rot));
+    }
+    a.get() = eval_.mult(a.get(), hemmer_mask(*this, kFirstCol, a.getLevel()));
+    b.get() = eval_.mult(b.get(), hemmer_mask(*this, kLastCol, b.getLevel()));
+    for (i64 rot = 1; rot < d / 2; rot <<= 1) {
+        a.get() = eval_.add(a.get(), eval_.rightRotate(a.get(), rot));
+        b.get() = eval_.add(b.get(), eval_.leftRotate(b.get(), rot));
+    }
+}
 // HEMMer::maskFirstRowInplace / maskFirstColOnlyInplace -- HEMMer.cpp:1255-1261, masks :2384-2388, :2418
 void HEMMer::maskFirstRowInplace(CtxtTensor &t) { t.get() = eval_.mult(t.get(), hemmer_mask(*this, kFirstRow, t.getLevel())); }
 void HEMMer::maskFirstColOnlyInplace(CtxtTensor &t) { t.get() = eval_.mult(t.get(), hemmer_mask(*this, kFirstColOnly, t.getLevel())); }

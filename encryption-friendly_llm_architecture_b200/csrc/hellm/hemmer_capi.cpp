@@ -109,6 +109,15 @@ int hb_hemmer_one_mat_rot_sum(hb_hemmer *h, const hb_ct *a, const hb_ct *b, hb_c
     });
 }
 
+int hb_hemmer_tr_one_mat_rot_sum(hb_hemmer *h, const hb_ct *a, const hb_ct *b, int target, hb_ct **out_a, hb_ct **out_b) {
+    return guard([&] {
+        Borrow ba(h->ctx, a), bb(h->ctx, b);
+        CtxtTensor ta(TileTensorShape(), Ciphertext(ba.c)), tb(TileTensorShape(), Ciphertext(bb.c));
+        h->h.trOneMatRotSumInplace(ta, tb, target);
+        *out_a = ta.get().release(); *out_b = tb.get().release();
+    });
+}
+
 int hb_hemmer_gaussian_kernel_scores(hb_hemmer *h, const hb_ct *query, const hb_ct *key, int rows, int cols, int width, int target, hb_ct **out0, hb_ct **out1) {
     return guard([&] {
         Borrow bq(h->ctx, query), bk(h->ctx, key);

@@ -195,6 +195,10 @@ class Hemmer:
         name = "hadamard_mult_pt" if isinstance(b, PtxtTensor) else "hadamard_mult"
         a.ct = self._call(name, a.ct.ptr, b.ct.ptr)
 
+    def tr_one_mat_rot_sum_inplace(self, a, b, target_level=0):
+        """HEMMer::tr_oneMatRotSumInplace (HEMMer.cpp:921-962): row sums over the whole tile side, on half of the row."""
+        a.ct, b.ct = self._call("tr_one_mat_rot_sum", a.ct.ptr, b.ct.ptr, C.c_int(target_level), n_out=2)
+
     def gaussian_kernel_scores(self, query, key, target_level=4):
         """Score assembly of the reference's Gaussian-kernel attention (TransformerBlock.cpp:2420-2482) for one query / key
         pair: [|q_r|^2 + |k_c|^2 - 2 q_r . k_c] per head; returns the two head positions."""

@@ -74,6 +74,9 @@ int hb_hemmer_hadamard_mult(hb_hemmer *h, const hb_ct *a, const hb_ct *b, hb_ct 
 int hb_hemmer_hadamard_mult_pt(hb_hemmer *h, const hb_ct *a, const hb_pt *p, hb_ct **out);
 /* HEMMer::oneMatRotSumInplace (HEMMer.hpp:168; HEMMer.cpp:882-919) on two-tile ciphertexts */
 int hb_hemmer_one_mat_rot_sum(hb_hemmer *h, const hb_ct *a, const hb_ct *b, hb_ct **out_a, hb_ct **out_b);
+/* HEMMer::tr_oneMatRotSumInplace (HEMMer.cpp:921-962, HEAD_DIM = tile side): after an optional level-down to target_level + 1,
+ * a holds the sum of every tile row on the left half of the row, b on the right half. */
+int hb_hemmer_tr_one_mat_rot_sum(hb_hemmer *h, const hb_ct *a, const hb_ct *b, int target_level, hb_ct **out_a, hb_ct **out_b);
 
 /* The score assembly of the Gaussian-kernel attention in the reference's layer, TransformerBlock::attention2_bert_loraOpti
  * (TransformerBlock.cpp:2420-2482, for one query / key pair, up to the bootstrap): heads separated by maskRightLeft,

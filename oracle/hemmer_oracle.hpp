@@ -816,6 +816,32 @@ struct Hemmer {
             b.ct = ev.add(b.ct, rotL(b.ct, rot));
         }
     }
+    // HEMMer::tr_oneMatRotSumInplace -- HEMMer.cpp:921-962 (HEAD_DIM = tile side)
+    void tr_one_mat_rot_sum_inplace(CtT &a, CtT &b, int target_level) {
+        const i64 d = tile;
+        if (target_level > 0) {
+            a.ct = ev.level_down(a.ct, target_level + 1);
+            b.ct = ev.level_down(b.ct, target_level + 1);
+        }
+        for (i64 rot = 1; rot < d; rot <<= 1) {
+            a.ct = ev.add(a.ct, rotL(a.ct, rot));
+            b.ct = ev.add(b.ct, rotR(b.ct, rot));
+        }
+        Mask first, last;
+        first.msg.assign((size_t)slots, cplx(0, 0));
+        last.msg.assign((size_t)slots, cplx(0, 0));
+        for (i64 r = 0; r < d; ++r)
+            for (i64 t = 0; t < 2; ++t) {
+                first.msg[(size_t)(r * 2 * d + t * d)] = 1;
+                last.msg[(size_t)(r * 2 * d + t * d + d - 1)] = 1;
+            }
+        a.ct = mult_msg(a.ct, first);
+        b.ct = mult_msg(b.ct, last);
+        for (i64 rot = 1; rot < d / 2; rot <<= 1) {
+            a.ct = ev.add(a.ct, rotR(a.ct, rot));
+            b.ct = ev.add(b.ct, rotL(b.ct, rot));
+        }
+    }
     // Gaussian-kernel score assembly of attention2_bert_loraOpti -- TransformerBlock.cpp:2420-2482 (one query / key pair)
     std::vector<CtT> gaussian_kernel_scores(const CtT &query, const CtT &key, int target_level) {
         const i64 d = tile;

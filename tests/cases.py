@@ -346,6 +346,29 @@ def sc_rot_sum_hadamard(lib, H, target=0):
     return [lib.ct_export(t.ct) for t in (a, b, x, z)], err
 
 
+def sc_tr_rot_sum(lib, H, target=2):
+    """tr_oneMatRotSumInplace (HEMMer.cpp:921-962): level-down, sums over a whole tile row, result on half of the row."""
+    d = tile_dim(lib)
+    A, A2, B, B2 = _mats(133, d, 4)
+    a, b = H.encrypt2(A, A2, nonce=96), H.encrypt2(B, B2, nonce=97)
+    H.tr_one_mat_rot_sum_inplace(a, b, target)
+    assert lib.ct_meta(a.ct)[0] == target and lib.ct_meta(b.ct)[0] == target
+    Da, Db = H.decrypt2(a), H.decrypt2(b)
+    half = d // 2
+
+    def want(M, left):
+        out = np.zeros((d, d))
+        s = M.sum(axis=1, keepdims=True)
+        if left:
+            out[:, :half] = s
+        else:
+            out[:, half:] = s
+        return out
+    err = max(np.abs(Da[0] - want(A, True)).max(), np.abs(Da[1] - want(A2, True)).max(),
+              np.abs(Db[0] - want(B, False)).max(), np.abs(Db[1] - want(B2, False)).max())
+    return [lib.ct_export(t.ct) for t in (a, b)], err
+
+
 def sc_lora_opti(lib, H, target=0):
     """The rank-2 LoRA branch of the reference's attention layer (TransformerBlock.cpp:2199-2365): X A B by slot-wise
     products and rotate-and-add, factors packed one rank vector per row."""
@@ -388,6 +411,7 @@ def sc_gaussian_kernel(lib, H, target=2):
 
 
 SCENARIOS = {
+    "tr_rot_sum": sc_tr_rot_sum,
     "gaussian_kernel": sc_gaussian_kernel,
     "lora_opti": sc_lora_opti,
     "rot_sum_hadamard": sc_rot_sum_hadamard,
