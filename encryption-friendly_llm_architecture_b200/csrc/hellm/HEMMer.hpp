@@ -99,6 +99,14 @@ class HEMMer {
     void oneMatRotSumInplace(CtxtTensor &a, CtxtTensor &b);
     // HEMMer::tr_oneMatRotSumInplace (HEMMer.cpp:921-962): row sums over the whole tile side, returned on half of it
     void trOneMatRotSumInplace(CtxtTensor &a, CtxtTensor &b, int target_level = 0);
+    // HEMMer::maskFirstColInplace / maskLeftHalfInplace / maskRightHalfInplace (HEMMer.cpp:1251-1269)
+    void maskFirstColInplace(CtxtTensor &t);
+    void maskLeftHalfInplace(CtxtTensor &t);
+    void maskRightHalfInplace(CtxtTensor &t);
+    // HEMMer::squareSum (HEMMer.cpp:2499-2510)
+    void squareSum(const std::vector<CtxtTensor> &v, CtxtTensor &out);
+    // HEMMer::reduceRowSumWithScaledMask (HEMMer.cpp:2512-2530), single rank; the mask comes encoded at the ciphertext's level
+    void reduceRowSumWithScaledMask(CtxtTensor &t, const PtxtTensor &mask);
     // The rank-2 LoRA branch of a projection as the reference's layer runs it (TransformerBlock::attention2_bert_loraOpti,
     // TransformerBlock.cpp:2199-2365, without the bootstraps around it): the two rank vectors are picked row by row
     // out of the factor ciphertexts, spread over all token rows by rotations, multiplied slot-wise with the three

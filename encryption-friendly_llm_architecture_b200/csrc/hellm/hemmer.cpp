@@ -6,7 +6,7 @@
 namespace HELLM {
 
 namespace {
-enum HemmerMask { kColEven = 1, kRowEven = 2, kLeftHalf = 3, kLeftHalfScaled = 4, kFirstCol = 5, kLastCol = 6, kFirstRow = 7, kFirstColOnly = 8, kHeadLeft = 9, kHeadRight = 10 };
+enum HemmerMask { kColEven = 1, kRowEven = 2, kLeftHalf = 3, kLeftHalfScaled = 4, kFirstCol = 5, kLastCol = 6, kFirstRow = 7, kFirstColOnly = 8, kHeadLeft = 9, kHeadRight = 10, kRightHalf = 11 };
 }
 
 HEMMer::HEMMer(hb_ctx *ctx) : ctx_(ctx), eval_(ctx) {
@@ -139,7 +139,7 @@ static const Plaintext &hemmer_mask(HEMMer &h, int which, int level) {
         for (i64 c = 0; c < 2 * d; ++c) {
             bool on = which == kColEven ? ((c % d) % 2 == 0) : which == kRowEven ? (r % 2 == 0) : which == kFirstCol ? (c % d == 0) : which == kLastCol ? (c % d == d - 1) :
                       which == kFirstRow ? (r == 0) : which == kFirstColOnly ? (c == 0) :
-                      which == kHeadLeft ? (c % d < d / 2) : which == kHeadRight ? (c % d >= d / 2) : (c < d);
+                      which == kHeadLeft ? (c % d < d / 2) : which == kHeadRight ? (c % d >= d / 2) : which == kRightHalf ? (c >= d) : (c < d);
             if (on) m.re[(size_t)(r * 2 * d + c)] = which == kLeftHalfScaled ? 0.5 : 1.0;
         }
     return h.masks().put(k, h.eval().encode(m, level));
@@ -198,6 +198,25 @@ void HEMMer::trOneMatRotSumInplace(CtxtTensor &a, CtxtTensor &b, int target_leve
 // HEMMer::maskFirstRowInplace / maskFirstColOnlyInplace -- HEMMer.cpp:1255-1261, masks :2384-2388, :2418
 void HEMMer::maskFirstRowInplace(CtxtTensor &t) { t.get() = eval_.mult(t.get(), hemmer_mask(*this, kFirstRow, t.getLevel())); }
 void HEMMer::maskFirstColOnlyInplace(CtxtTensor &t) { t.get() = eval_.mult(t.get(), hemmer_mask(*this, kFirstColOnly, t.getLevel())); }
+// HEMMer::maskFirstColInplace / maskLeftHalfInplace / maskRightHalfInplace -- HEMMer.cpp:1251-1269, masks :2378-2394
+void HEMMer::maskFirstColInplace(CtxtTensor &t) { t.get() = eval_.mult(t.get(), hemmer_mask(*this, kFirstCol, t.getLevel())); }
+void HEMMer::maskLeftHalfInplace(CtxtTensor &t) { t.get() = eval_.mult(t.get(), hemmer_mask(*this, kLeftHalf, t.getLevel())); }
+void HEMMer::maskRightHalfInplace(CtxtTensor &t) { t.get() = eval_.mult(t.get(), hemmer_mask(*this, kRightHalf, t.getLevel())); }
+// HEMMer::squareSum -- HEMMer.cpp:2499-2510: sum of the tensor squares, one relinearisation and one rescale for the sum
+void HEMMer::squareSum(const std::vector<CtxtTensor> &v, CtxtTensor &out) {
+    if (v.empty()) throw std::invalid_argument("[squareSum] empty input");
+    Ciphertext acc = eval_.tensor(v[0].get(), v[0].get());
+    for (size_t i = 1; i < v.size(); ++i) acc = eval_.add(acc, eval_.tensor(v[i].get(), v[i].get()));
+    out = CtxtTensor(v[0].getShape(), eval_.rescale(eval_.relinearize(acc)));
+}
+// HEMMer::reduceRowSumWithScaledMask -- HEMMer.cpp:2512-2530 on one rank: rotate-and-add over a row of the block width,
+// the caller's mask (encoded at the ciphertext's level), rotate-and-add back
+void HEMMer::reduceRowSumWithScaledMask(CtxtTensor &t, const PtxtTensor &mask) {
+    const i64 w = t.getBlockWidth();
+    for (i64 i = 1; i < w; i <<= 1) t.get() = eval_.add(t.get(), eval_.leftRotate(t.get(), i));
+    t.get() = eval_.mult(t.get(), mask.get());
+    for (i64 i = 1; i < w; i <<= 1) t.get() = eval_.add(t.get(), eval_.rightRotate(t.get(), i));
+}
 // HEMMer::maskRightLeft -- mask_one_left_ / mask_one_right_ of generateRightLeftMasks, HEMMer.cpp:2366-2376
 void HEMMer::maskRightLeft(const CtxtTensor &t, CtxtTensor &left, CtxtTensor &right) {
     left = CtxtTensor(t.getShape(), eval_.mult(t.get(), hemmer_mask(*this, kHeadLeft, t.getLevel())));

@@ -149,6 +149,34 @@ int hb_hemmer_sigma(hb_hemmer *h, const hb_ct *a, SHAPE_ARGS, hb_ct **out) {
 int hb_hemmer_tau(hb_hemmer *h, const hb_ct *a, SHAPE_ARGS, hb_ct **out) {
     return guard([&] { IN_TENSOR(t, a); *out = h->h.diagonalToRow(t).get().release(); });
 }
+int hb_hemmer_mask_inplace(hb_hemmer *h, const hb_ct *a, int which, SHAPE_ARGS, hb_ct **out) {
+    return guard([&] {
+        IN_TENSOR(t, a);
+        if (which == 0) h->h.maskFirstColInplace(t);
+        else if (which == 1) h->h.maskLeftHalfInplace(t);
+        else if (which == 2) h->h.maskRightHalfInplace(t);
+        else throw std::invalid_argument("[mask] unknown mask");
+        *out = t.get().release();
+    });
+}
+int hb_hemmer_square_sum(hb_hemmer *h, const hb_ct *const *v, int count, SHAPE_ARGS, hb_ct **out) {
+    return guard([&] {
+        std::vector<std::unique_ptr<Borrow>> hold;
+        std::vector<CtxtTensor> ts;
+        for (int i = 0; i < count; ++i) { hold.emplace_back(new Borrow(h->ctx, v[i])); ts.push_back(view(*hold.back(), rows, cols, width)); }
+        CtxtTensor o;
+        h->h.squareSum(ts, o);
+        *out = o.get().release();
+    });
+}
+int hb_hemmer_reduce_row_sum_with_scaled_mask(hb_hemmer *h, const hb_ct *a, const hb_pt *mask, SHAPE_ARGS, hb_ct **out) {
+    return guard([&] {
+        IN_TENSOR(t, a);
+        PtxtTensor m(TileTensorShape(rows, cols, width), Plaintext::borrowed(mask));
+        h->h.reduceRowSumWithScaledMask(t, m);
+        *out = t.get().release();
+    });
+}
 int hb_hemmer_matmul_cc(hb_hemmer *h, const hb_ct *a, int ra, int ca, int wa, const hb_ct *b, int rb, int cb, int wb, int target, hb_ct **out) {
     return guard([&] {
         Borrow ba(h->ctx, a), bb(h->ctx, b);

@@ -195,6 +195,24 @@ class Hemmer:
         name = "hadamard_mult_pt" if isinstance(b, PtxtTensor) else "hadamard_mult"
         a.ct = self._call(name, a.ct.ptr, b.ct.ptr)
 
+    def mask_first_col_inplace(self, t):
+        t.ct = self._call("mask_inplace", t.ct.ptr, C.c_int(0), *self._shp(t))
+
+    def mask_left_half_inplace(self, t):
+        t.ct = self._call("mask_inplace", t.ct.ptr, C.c_int(1), *self._shp(t))
+
+    def mask_right_half_inplace(self, t):
+        t.ct = self._call("mask_inplace", t.ct.ptr, C.c_int(2), *self._shp(t))
+
+    def square_sum(self, tensors):
+        """HEMMer::squareSum (HEMMer.cpp:2499-2510): sum of the squares with one relinearisation and one rescale."""
+        arr = (C.c_void_p * len(tensors))(*[t.ct.ptr.value for t in tensors])
+        return CtxtTensor(self._call("square_sum", arr, C.c_int(len(tensors)), *self._shp(tensors[0])), *tensors[0].shape)
+
+    def reduce_row_sum_with_scaled_mask(self, t, mask):
+        """HEMMer::reduceRowSumWithScaledMask (HEMMer.cpp:2512-2530) on one rank; mask: a plaintext tensor at t's level."""
+        t.ct = self._call("reduce_row_sum_with_scaled_mask", t.ct.ptr, mask.ct.ptr, *self._shp(t))
+
     def tr_one_mat_rot_sum_inplace(self, a, b, target_level=0):
         """HEMMer::tr_oneMatRotSumInplace (HEMMer.cpp:921-962): row sums over the whole tile side, on half of the row."""
         a.ct, b.ct = self._call("tr_one_mat_rot_sum", a.ct.ptr, b.ct.ptr, C.c_int(target_level), n_out=2)

@@ -78,6 +78,12 @@ int hb_hemmer_one_mat_rot_sum(hb_hemmer *h, const hb_ct *a, const hb_ct *b, hb_c
  * a holds the sum of every tile row on the left half of the row, b on the right half. */
 int hb_hemmer_tr_one_mat_rot_sum(hb_hemmer *h, const hb_ct *a, const hb_ct *b, int target_level, hb_ct **out_a, hb_ct **out_b);
 
+/* HEMMer::maskFirstColInplace (which = 0), maskLeftHalfInplace (1), maskRightHalfInplace (2) -- HEMMer.cpp:1251-1269 */
+int hb_hemmer_mask_inplace(hb_hemmer *h, const hb_ct *a, int which, int rows, int cols, int width, hb_ct **out);
+/* HEMMer::squareSum (HEMMer.cpp:2499-2510): rescale(relinearize(sum_i tensor(v[i], v[i]))) */
+int hb_hemmer_square_sum(hb_hemmer *h, const hb_ct *const *v, int count, int rows, int cols, int width, hb_ct **out);
+/* HEMMer::reduceRowSumWithScaledMask (HEMMer.cpp:2512-2530) on one rank; `mask` is encoded at the ciphertext's level */
+int hb_hemmer_reduce_row_sum_with_scaled_mask(hb_hemmer *h, const hb_ct *a, const hb_pt *mask, int rows, int cols, int width, hb_ct **out);
 /* The score assembly of the Gaussian-kernel attention in the reference's layer, TransformerBlock::attention2_bert_loraOpti
  * (TransformerBlock.cpp:2420-2482, for one query / key pair, up to the bootstrap): heads separated by maskRightLeft,
  * squared norms by square + oneMatRotSumInplace (+ transposeInplace on the key side), the products by complexPacking* +

@@ -816,6 +816,29 @@ struct Hemmer {
             b.ct = ev.add(b.ct, rotL(b.ct, rot));
         }
     }
+    // HEMMer::maskFirstColInplace / maskLeftHalfInplace / maskRightHalfInplace -- HEMMer.cpp:1251-1269
+    Ct mask_inplace(const Ct &x, int which) {
+        const i64 d = tile;
+        Mask m;
+        m.msg.assign((size_t)slots, cplx(0, 0));
+        for (i64 r = 0; r < d; ++r)
+            for (i64 c = 0; c < 2 * d; ++c)
+                if (which == 0 ? (c % d == 0) : which == 1 ? (c < d) : (c >= d)) m.msg[(size_t)(r * 2 * d + c)] = 1;
+        return mult_msg(x, m);
+    }
+    // HEMMer::squareSum -- HEMMer.cpp:2499-2510
+    Ct square_sum(const std::vector<Ct> &v) {
+        Ct acc = ev.tensor(v[0], v[0]);
+        for (size_t i = 1; i < v.size(); ++i) acc = ev.add(acc, ev.tensor(v[i], v[i]));
+        return ev.rescale(ev.relin(acc));
+    }
+    // HEMMer::reduceRowSumWithScaledMask -- HEMMer.cpp:2512-2530, one rank
+    Ct reduce_row_sum_with_scaled_mask(Ct x, const Pt &mask, i64 width) {
+        for (i64 i = 1; i < width; i <<= 1) x = ev.add(x, rotL(x, i));
+        x = ev.mul_pt(x, mask);
+        for (i64 i = 1; i < width; i <<= 1) x = ev.add(x, rotR(x, i));
+        return x;
+    }
     // HEMMer::tr_oneMatRotSumInplace -- HEMMer.cpp:921-962 (HEAD_DIM = tile side)
     void tr_one_mat_rot_sum_inplace(CtT &a, CtT &b, int target_level) {
         const i64 d = tile;

@@ -369,6 +369,38 @@ def sc_tr_rot_sum(lib, H, target=2):
     return [lib.ct_export(t.ct) for t in (a, b)], err
 
 
+def sc_masks_and_sums(lib, H, target=0):
+    """maskFirstCol / maskLeftHalf / maskRightHalf (HEMMer.cpp:1251-1269), squareSum (:2499-2510) and
+    reduceRowSumWithScaledMask (:2512-2530, one rank) on two side-by-side tiles."""
+    d = tile_dim(lib)
+    A, A2, B, B2 = _mats(134, d, 4)
+    exports, err = [], 0.0
+    for k, (fn, keep) in enumerate(((H.mask_first_col_inplace, lambda r, c: c % d == 0), (H.mask_left_half_inplace, lambda r, c: c < d),
+                                    (H.mask_right_half_inplace, lambda r, c: c >= d))):
+        x = H.encrypt2(A, A2, nonce=98 + k)
+        fn(x)
+        D = H.decrypt2(x)
+        full = np.concatenate([A, A2], axis=1)
+        want = np.array([[full[r, c] if keep(r, c) else 0.0 for c in range(2 * d)] for r in range(d)])
+        err = max(err, np.abs(np.concatenate([D[0], D[1]], axis=1) - want).max())
+        exports.append(lib.ct_export(x.ct))
+    xs = [H.encrypt2(A, A2, nonce=110), H.encrypt2(B, B2, nonce=111), H.encrypt2(0.5 * A, 0.5 * B2, nonce=112)]
+    sq = H.square_sum(xs)
+    D = H.decrypt2(sq)
+    err = max(err, np.abs(D[0] - (A * A + B * B + 0.25 * A * A)).max(), np.abs(D[1] - (A2 * A2 + B2 * B2 + 0.25 * B2 * B2)).max())
+    exports.append(lib.ct_export(sq.ct))
+    y = H.encrypt2(A, A2, nonce=113)
+    scaled = np.zeros((d, d)); scaled[:, 0] = 1.0 / d
+    H.reduce_row_sum_with_scaled_mask(y, H.encode2(scaled, np.zeros((d, d)), level=lib.ct_meta(y.ct)[0]))
+    D = H.decrypt2(y)
+    # row sums over the 2d-wide row, gathered at the first column and spread back over the row: every entry of a row
+    # holds the mean over the d columns of tile 0 plus the d columns of tile 1, divided by d
+    row = (A.sum(axis=1) + A2.sum(axis=1)) / d
+    err = max(err, np.abs(D[0] - row[:, None]).max(), np.abs(D[1] - row[:, None]).max())
+    exports.append(lib.ct_export(y.ct))
+    return exports, err
+
+
 def sc_lora_opti(lib, H, target=0):
     """The rank-2 LoRA branch of the reference's attention layer (TransformerBlock.cpp:2199-2365): X A B by slot-wise
     products and rotate-and-add, factors packed one rank vector per row."""
@@ -411,6 +443,7 @@ def sc_gaussian_kernel(lib, H, target=2):
 
 
 SCENARIOS = {
+    "masks_and_sums": sc_masks_and_sums,
     "tr_rot_sum": sc_tr_rot_sum,
     "gaussian_kernel": sc_gaussian_kernel,
     "lora_opti": sc_lora_opti,

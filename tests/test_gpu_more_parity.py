@@ -21,7 +21,7 @@ def _same(a, b, what=""):
 
 
 @pytest.mark.parametrize("size", ["small", "mid"])
-@pytest.mark.parametrize("name", ["packed", "packed_reuse", "cc_reuse", "transforms", "single_matmul", "lora_backward", "transpose_packing", "repack_lora_opti", "gaussian_kernel", "tr_rot_sum"])
+@pytest.mark.parametrize("name", ["packed", "packed_reuse", "cc_reuse", "transforms", "single_matmul", "lora_backward", "transpose_packing", "repack_lora_opti", "gaussian_kernel", "tr_rot_sum", "masks_and_sums"])
 def test_lazy_schedule_parity_remaining_scenarios(request, pkg, size, name):
     """Schedule 2 on the scenarios that test_gpu_parity.py runs in the other schedules only."""
     g, o = request.getfixturevalue(f"gpu_{size}"), request.getfixturevalue(f"orc_{size}")
